@@ -1,0 +1,15 @@
+"""blockgtq_b200: B200 (sm_100a) implementation of Block-GTQ's packed-KV-cache decode path
+behind the reference's Python API.  All GPU work is done by ``libbgtq.so`` (hand-written CUDA,
+C ABI in ``include/bgtq.h``); there is no CPU or Triton fallback."""
+from .allocator import greedy_bit_allocation
+from .quantizer import (BlockGTQQuantizer, build_batched_encode_args, build_pack_meta,
+                        compress_k_mixed_batched, compress_k_packed_batched,
+                        compress_v_nibble4_batched, compress_v_packed_batched)
+from .attention import fused_blockgtq_decode_attention
+from .packed_kv_manager import BlockGTQKVManager, decode_step
+
+__all__ = [
+    "greedy_bit_allocation", "BlockGTQQuantizer", "build_batched_encode_args", "build_pack_meta",
+    "compress_k_packed_batched", "compress_v_packed_batched", "compress_k_mixed_batched",
+    "compress_v_nibble4_batched", "fused_blockgtq_decode_attention", "BlockGTQKVManager", "decode_step",
+]

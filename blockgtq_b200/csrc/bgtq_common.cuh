@@ -1,0 +1,124 @@
+// Device-side helpers shared by the sm_100a kernels: PTX wrappers for bulk
+// (TMA) copies with mbarrier completion, bounded mbarrier waits, warp-level
+// tensor-core MMA and small bit utilities.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/bgtq.h"
+
+namespace bgtq {
+
+constexpr int kHD = BGTQ_HEAD_DIM;
+
+// Error codes a kernel may leave in the caller's status word.
+constexpr int kStatusWaitTimeout = 1;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- mbarrier -------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Wait with an iteration limit: returns false if the phase never completed.
+// try_wait itself blocks for a hardware-defined slice, so the bound below is
+// on the order of a second of wall time, far beyond any legitimate wait.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    return false;
+}
+
+// ---- bulk async copy global -> shared (1-D TMA) -----------------------------
+// dst and src 16-byte aligned, bytes a multiple of 16.  No multicast.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// ---- shared memory loads -----------------------------------------------------
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+// 32 bits starting at an arbitrary BIT position of a byte stream in shared
+// memory (two aligned words + funnel shift).  Reads up to 7 bytes past the
+// last needed byte: buffers carry that much slack.
+__device__ __forceinline__ uint32_t lds_bits32(uint32_t base_addr, uint32_t bitpos) {
+    const uint32_t a = base_addr + (bitpos >> 3);
+    const uint32_t wa = a & ~3u;
+    const uint32_t sh = ((a & 3u) << 3) + (bitpos & 7u);
+    return __funnelshift_r(lds32(wa), lds32(wa + 4), sh);
+}
+// 64 bits starting at an arbitrary bit position (three aligned words).
+__device__ __forceinline__ uint2 lds_bits64(uint32_t base_addr, uint32_t bitpos) {
+    const uint32_t a = base_addr + (bitpos >> 3);
+    const uint32_t wa = a & ~3u;
+    const uint32_t sh = ((a & 3u) << 3) + (bitpos & 7u);
+    const uint32_t w0 = lds32(wa), w1 = lds32(wa + 4), w2 = lds32(wa + 8);
+    return make_uint2(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh));
+}
+
+// ---- tensor core -------------------------------------------------------------
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// Transpose an 8x8 tile of 16-bit values held one row-pair per thread.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+__host__ __device__ __forceinline__ int seg_storage_bytes(int bw, int n) {
+    return bw == 1 ? (n + 7) / 8 : bw == 2 ? (n + 3) / 4 : bw == 3 ? ((n + 7) / 8) * 3 : bw == 4 ? (n + 1) / 2 : n;
+}
+
+}  // namespace bgtq

@@ -1,0 +1,296 @@
+// Prefill / append encoder (kernel a): rotate, quantise against the per-position
+// codebooks, bit-pack and write K and V rows straight into their cache slots.
+//
+// Arithmetic follows the reference encoders step by step
+// (blockgtq/quantizer.py:800-850 for K, :560-590 for V): group norms
+// sqrt(sum x^2 + 1e-30), x / norm (skipped below 1e-10 / 1e-8), fp32 rotation,
+// (y - off) * inv clamped to [0,255] and truncated, 256-bin code LUT for K;
+// boundary count for V with the norm divided by the norm of the chosen levels.
+// The packed bytes then follow quantizer.py:861-990 (LSB-first streams for
+// 1-4 bits, raw bytes for 5-8).
+//
+// One CTA = kRows rows of one KV head, 128 threads = one per packed position.
+// The rotation is a register-blocked fp32 product: a thread owns one output
+// position for kRows rows and only walks the input positions of its own
+// width group (the K rotation is block diagonal); V's rotation is dense.
+#include "bgtq_common.cuh"
+
+namespace bgtq {
+namespace {
+
+constexpr int kRows = 8;
+
+struct EncParams {
+    const BgtqHeadDesc* desc;
+    const float* rot_k;
+    const float* rot_v;
+    const __half* k;
+    const __half* v;
+    int64_t k_sb, k_sh, k_ss, v_sb, v_sh, v_ss;
+    int32_t n_batch, n_kv, n_tok, t0;
+    uint8_t* kp; int64_t kp_sb, kp_sh, kp_st; int32_t kp_row_bytes;
+    void* kn; int64_t kn_sb, kn_sh, kn_st; int32_t kn_count;
+    uint8_t* vp; int64_t vp_sb, vp_sh, vp_st;
+    __half* vn; int64_t vn_sb, vn_sh, vn_st;
+    uint8_t* k_codes;
+    uint8_t* v_codes;
+    int32_t flags;
+};
+
+// Byte `t` of a bit-packed run: codes of width bw (1..4) starting at codes[0].
+__device__ __forceinline__ uint32_t pack_byte(const uint8_t* codes, int n, int bw, int t) {
+    const int bit0 = t * 8;
+    uint32_t out = 0;
+    int i = bit0 / bw;
+    for (int pos = i * bw; pos < bit0 + 8; pos += bw, ++i) {
+        if (i >= n) break;
+        const uint32_t c = codes[i] & ((1u << bw) - 1u);
+        const int sh = pos - bit0;
+        out |= sh >= 0 ? (c << sh) : (c >> (-sh));
+    }
+    return out & 0xFFu;
+}
+
+__global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
+    __shared__ __align__(16) float xs[kHD][kRows];          // [packed position][row]
+    __shared__ float gn[BGTQ_MAX_SEGMENTS][kRows];
+    __shared__ float gc[BGTQ_MAX_SEGMENTS][kRows];
+    __shared__ float red[4][kRows];
+    __shared__ float rawn[kRows];
+    __shared__ uint8_t codes[kRows][kHD];
+
+    const int p = threadIdx.x;
+    const int h = blockIdx.y;
+    const bool is_v = blockIdx.z == 1;
+    if (is_v ? (P.flags & BGTQ_ENC_SKIP_V) : (P.flags & BGTQ_ENC_SKIP_K)) return;
+    const BgtqHeadDesc& d = P.desc[h];
+    const int64_t n_rows = (int64_t)P.n_batch * P.n_tok;
+    const int64_t row0 = (int64_t)blockIdx.x * kRows;
+
+    int rb[kRows], rs[kRows];
+    bool rok[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        const int64_t n = row0 + r;
+        rok[r] = n < n_rows;
+        rb[r] = rok[r] ? (int)(n / P.n_tok) : 0;
+        rs[r] = rok[r] ? (int)(n % P.n_tok) : 0;
+    }
+
+    if (!is_v) {
+        // ------------------------------- K -------------------------------
+        const int src_dim = d.head_perm[p];
+        const int g = d.group_of[p];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+            xs[p][r] = rok[r] ? __half2float(P.k[rb[r] * P.k_sb + h * P.k_sh + rs[r] * P.k_ss + src_dim]) : 0.f;
+        __syncthreads();
+        if (p < BGTQ_MAX_SEGMENTS * kRows) {
+            const int r = p % kRows, s = p / kRows;
+            if (s < d.n_seg) {
+                float acc = 0.f;
+                for (int i = d.seg_start[s]; i < d.seg_start[s] + d.seg_len[s]; ++i) acc = fmaf(xs[i][r], xs[i][r], acc);
+                gn[s][r] = sqrtf(acc + 1e-30f);
+            }
+        }
+        __syncthreads();
+        float xn[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const float nr = gn[g][r];
+            xn[r] = xs[p][r] / (nr > 1e-10f ? nr : 1.0f);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) xs[p][r] = xn[r];
+        __syncthreads();
+        float y[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) y[r] = 0.f;
+        const float* W = P.rot_k + (size_t)h * kHD * kHD + p;
+        const int js = d.seg_start[g], je = js + d.seg_len[g];
+        for (int jj = js; jj < je; ++jj) {
+            const float w = __ldg(W + (size_t)jj * kHD);
+            const float4 a = *reinterpret_cast<const float4*>(&xs[jj][0]);
+            const float4 b = *reinterpret_cast<const float4*>(&xs[jj][4]);
+            y[0] = fmaf(a.x, w, y[0]); y[1] = fmaf(a.y, w, y[1]); y[2] = fmaf(a.z, w, y[2]); y[3] = fmaf(a.w, w, y[3]);
+            y[4] = fmaf(b.x, w, y[4]); y[5] = fmaf(b.y, w, y[5]); y[6] = fmaf(b.z, w, y[6]); y[7] = fmaf(b.w, w, y[7]);
+        }
+        const float off = d.lut_off[g], inv = d.lut_inv[g];
+        const int lo = d.seg_lut_off[g];
+        const bool mixed = P.flags & BGTQ_ENC_K_MIXED;
+        float c2[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            float u = (y[r] - off) * inv;
+            u = fminf(fmaxf(u, 0.f), 255.f);
+            const uint8_t c = d.code_lut[g][(int)u];
+            codes[r][p] = c;
+            const float cv = d.k_cents[lo + c];
+            c2[r] = cv * cv;
+            if (P.k_codes && rok[r])
+                P.k_codes[(((size_t)rb[r] * P.n_kv + h) * P.n_tok + rs[r]) * kHD + p] = c;
+        }
+        __syncthreads();
+        if (mixed) {   // norm correction: divide by the norm of the chosen levels per group
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) xs[p][r] = c2[r];
+            __syncthreads();
+            if (p < BGTQ_MAX_SEGMENTS * kRows) {
+                const int r = p % kRows, s = p / kRows;
+                if (s < d.n_seg) {
+                    float acc = 0.f;
+                    for (int i = d.seg_start[s]; i < d.seg_start[s] + d.seg_len[s]; ++i) acc += xs[i][r];
+                    gc[s][r] = fmaxf(sqrtf(acc), 1e-10f);
+                }
+            }
+            __syncthreads();
+        }
+        // norms
+        if (p < P.kn_count * kRows) {
+            const int r = p % kRows, s = p / kRows;
+            if (rok[r]) {
+                float val = s < d.n_seg ? gn[s][r] : 0.f;
+                if (mixed && s < d.n_seg) val = val / gc[s][r];
+                const size_t o = rb[r] * P.kn_sb + h * P.kn_sh + (size_t)(P.t0 + rs[r]) * P.kn_st + s;
+                if (P.flags & BGTQ_ENC_K_NORMS_F16) static_cast<__half*>(P.kn)[o] = __float2half_rn(val);
+                else static_cast<float*>(P.kn)[o] = val;
+            }
+        }
+        // bytes
+        if (p < P.kp_row_bytes) {
+            int mode = 0, s_bw = 0, s_first = 0, s_n = 0, s_t = 0;   // mode 0: zero, 1: bit stream, 2: raw, 3: nibble pair
+            if (mixed) {
+                const int nib = d.nopack_start / 2;
+                if (p < nib) { mode = 3; s_first = 2 * p; }
+                else if (p < nib + d.nopack_len) { mode = 2; s_first = d.nopack_start + (p - nib); }
+            } else {
+                for (int s = 0; s < d.n_seg; ++s) {
+                    const int bw = d.seg_bw[s], nb = seg_storage_bytes(bw, d.seg_len[s]);
+                    if (p >= d.seg_pack_off[s] && p < d.seg_pack_off[s] + nb) {
+                        s_t = p - d.seg_pack_off[s];
+                        if (bw >= 5) { mode = 2; s_first = d.seg_start[s] + s_t; }
+                        else { mode = 1; s_bw = bw; s_first = d.seg_start[s]; s_n = d.seg_len[s]; }
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                if (!rok[r]) continue;
+                uint32_t byte = 0;
+                if (mode == 1) byte = pack_byte(&codes[r][s_first], s_n, s_bw, s_t);
+                else if (mode == 2) byte = codes[r][s_first];
+                else if (mode == 3) byte = (codes[r][s_first] & 15u) | ((codes[r][s_first + 1] & 15u) << 4);
+                P.kp[rb[r] * P.kp_sb + h * P.kp_sh + (size_t)(P.t0 + rs[r]) * P.kp_st + p] = (uint8_t)byte;
+            }
+        }
+    } else {
+        // ------------------------------- V -------------------------------
+        float x[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+            x[r] = rok[r] ? __half2float(P.v[rb[r] * P.v_sb + h * P.v_sh + rs[r] * P.v_ss + p]) : 0.f;
+        auto block_sum = [&](float (&val)[kRows], float* out) {
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                float s = val[r];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if ((p & 31) == 0) red[p >> 5][r] = s;
+            }
+            __syncthreads();
+            if (p < kRows) out[p] = red[0][p] + red[1][p] + red[2][p] + red[3][p];
+            __syncthreads();
+        };
+        float sq[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) sq[r] = x[r] * x[r];
+        block_sum(sq, rawn);
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const float raw = sqrtf(rawn[r] + 1e-30f);
+            xs[p][r] = x[r] / (raw > 1e-8f ? raw : 1.0f);
+        }
+        __syncthreads();
+        float y[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) y[r] = 0.f;
+        const float* W = P.rot_v + (size_t)h * kHD * kHD + p;
+#pragma unroll 4
+        for (int jj = 0; jj < kHD; ++jj) {
+            const float w = __ldg(W + (size_t)jj * kHD);
+            const float4 a = *reinterpret_cast<const float4*>(&xs[jj][0]);
+            const float4 b = *reinterpret_cast<const float4*>(&xs[jj][4]);
+            y[0] = fmaf(a.x, w, y[0]); y[1] = fmaf(a.y, w, y[1]); y[2] = fmaf(a.z, w, y[2]); y[3] = fmaf(a.w, w, y[3]);
+            y[4] = fmaf(b.x, w, y[4]); y[5] = fmaf(b.y, w, y[5]); y[6] = fmaf(b.z, w, y[6]); y[7] = fmaf(b.w, w, y[7]);
+        }
+        const int nb = (1 << d.v_bits) - 1;
+        float c2[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            int c = 0;
+            for (int i = 0; i < nb; ++i) c += y[r] > d.v_bounds[i] ? 1 : 0;
+            codes[r][p] = (uint8_t)c;
+            const float cv = d.v_cents[c];
+            c2[r] = cv * cv;
+            if (P.v_codes && rok[r])
+                P.v_codes[(((size_t)rb[r] * P.n_kv + h) * P.n_tok + rs[r]) * kHD + p] = (uint8_t)c;
+        }
+        __shared__ float cn[kRows];
+        block_sum(c2, cn);
+        if (p < kRows && rok[p]) {
+            const float raw = sqrtf(rawn[p] + 1e-30f);
+            const float cnorm = sqrtf(cn[p] + 1e-20f);
+            const float val = raw / (cnorm > 1e-10f ? cnorm : 1.0f);
+            P.vn[rb[p] * P.vn_sb + h * P.vn_sh + (size_t)(P.t0 + rs[p]) * P.vn_st] = __float2half_rn(val);
+        }
+        const bool nibble = P.flags & BGTQ_ENC_V_NIBBLE;
+        const int vb = nibble ? 4 : d.v_bits;
+        const int n_bytes = seg_storage_bytes(vb, kHD);
+        if (p < n_bytes) {
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                if (!rok[r]) continue;
+                const uint32_t byte = pack_byte(&codes[r][0], kHD, vb, p);
+                P.vp[rb[r] * P.vp_sb + h * P.vp_sh + (size_t)(P.t0 + rs[r]) * P.vp_st + p] = (uint8_t)byte;
+            }
+        }
+    }
+}
+
+}  // namespace
+}  // namespace bgtq
+
+using namespace bgtq;
+
+extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v, const void* k,
+                           int64_t k_sb, int64_t k_sh, int64_t k_ss, const void* v, int64_t v_sb, int64_t v_sh,
+                           int64_t v_ss, int32_t n_batch, int32_t n_kv, int32_t n_tok, int32_t t0, uint8_t* k_packed,
+                           int64_t kp_sb, int64_t kp_sh, int64_t kp_st, int32_t kp_row_bytes, void* k_norms,
+                           int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count, uint8_t* v_packed,
+                           int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
+                           int64_t vn_st, uint8_t* k_codes, uint8_t* v_codes, int32_t flags, void* stream) {
+    const bool do_k = !(flags & BGTQ_ENC_SKIP_K), do_v = !(flags & BGTQ_ENC_SKIP_V);
+    if (!desc || n_batch < 1 || n_kv < 1 || n_tok < 0 || t0 < 0) return BGTQ_E_BADARG;
+    if (do_k && (!rot_k || !k || !k_packed || !k_norms)) return BGTQ_E_BADARG;
+    if (do_v && (!rot_v || !v || !v_packed || !v_norms)) return BGTQ_E_BADARG;
+    if (do_k && (kp_row_bytes < 1 || kp_row_bytes > kHD || kn_count < 1 || kn_count > BGTQ_MAX_SEGMENTS))
+        return BGTQ_E_BADARG;
+    if (n_tok == 0 || (!do_k && !do_v)) return BGTQ_OK;
+    EncParams P;
+    P.desc = desc; P.rot_k = rot_k; P.rot_v = rot_v;
+    P.k = static_cast<const __half*>(k); P.v = static_cast<const __half*>(v);
+    P.k_sb = k_sb; P.k_sh = k_sh; P.k_ss = k_ss; P.v_sb = v_sb; P.v_sh = v_sh; P.v_ss = v_ss;
+    P.n_batch = n_batch; P.n_kv = n_kv; P.n_tok = n_tok; P.t0 = t0;
+    P.kp = k_packed; P.kp_sb = kp_sb; P.kp_sh = kp_sh; P.kp_st = kp_st; P.kp_row_bytes = kp_row_bytes;
+    P.kn = k_norms; P.kn_sb = kn_sb; P.kn_sh = kn_sh; P.kn_st = kn_st; P.kn_count = kn_count;
+    P.vp = v_packed; P.vp_sb = vp_sb; P.vp_sh = vp_sh; P.vp_st = vp_st;
+    P.vn = static_cast<__half*>(v_norms); P.vn_sb = vn_sb; P.vn_sh = vn_sh; P.vn_st = vn_st;
+    P.k_codes = k_codes; P.v_codes = v_codes; P.flags = flags;
+    const int64_t n_rows = (int64_t)n_batch * n_tok;
+    const int64_t gx = (n_rows + kRows - 1) / kRows;
+    if (gx > 0x7fffffffLL || n_kv > 65535) return BGTQ_E_TOOBIG;
+    dim3 grid((unsigned)gx, n_kv, 2);
+    encode_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(P);
+    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+}

@@ -1,0 +1,195 @@
+// Small kernels around the fused decode: query rotation, split-KV combine
+// (kernel c) and attention over the fp16 sink / recent-window tokens (kernel d).
+#include "bgtq_common.cuh"
+
+namespace bgtq {
+namespace {
+
+// ---------------------------------------------------------------------------
+// q_rot[p] = fp16( sum_j q[head_perm[j]] * rot_k[j][p] ), fp32 accumulate.
+// The rotation is block diagonal, so only the inputs of p's own segment count.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) rotate_q_kernel(const BgtqHeadDesc* desc, const float* rot_k,
+                                                        const __half* q, int64_t q_sb, int64_t q_sh,
+                                                        __half* q_rot, int n_q, int n_kv) {
+    __shared__ float qs[kHD];
+    const int p = threadIdx.x, hq = blockIdx.x, b = blockIdx.y;
+    const int h = hq / (n_q / n_kv);
+    const BgtqHeadDesc& d = desc[h];
+    qs[p] = __half2float(q[b * q_sb + hq * q_sh + d.head_perm[p]]);
+    __syncthreads();
+    const int g = d.group_of[p];
+    const int js = d.seg_start[g], je = js + d.seg_len[g];
+    const float* W = rot_k + (size_t)h * kHD * kHD + p;
+    float acc = 0.f;
+    for (int j = js; j < je; ++j) acc = fmaf(qs[j], __ldg(W + (size_t)j * kHD), acc);
+    q_rot[((size_t)b * n_q + hq) * kHD + p] = __float2half_rn(acc);
+}
+
+// ---------------------------------------------------------------------------
+// combine: merge split partials (and optionally the fp16-buffer partial).
+// One CTA per (query head, batch), one thread per output dim.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) combine_kernel(const float* part_o, const float* part_lse, int n_splits,
+                                                       const float* v_rot, const float* buf_o, const float* buf_lse,
+                                                       int n_q, int n_kv, __half* out, int64_t o_sb, int64_t o_sh,
+                                                       float* out_f32, float* lse_out) {
+    __shared__ float merged[kHD];
+    const int d = threadIdx.x, hq = blockIdx.x, b = blockIdx.y;
+    const size_t row = (size_t)b * n_q + hq;
+    const float* lse = part_lse + row * n_splits;
+    float mx = -INFINITY;
+    for (int c = 0; c < n_splits; ++c) mx = fmaxf(mx, lse[c]);
+    float num = 0.f, den = 0.f;
+    if (mx > -INFINITY) {
+        for (int c = 0; c < n_splits; ++c) {
+            const float l = lse[c];
+            if (l == -INFINITY) continue;
+            const float a = expf(l - mx);
+            den += a;
+            num = fmaf(a, part_o[(row * n_splits + c) * kHD + d], num);
+        }
+    }
+    float o = den > 0.f ? num / den : 0.f;
+    float tot = den > 0.f ? mx + logf(den) : -INFINITY;
+    if (v_rot) {
+        merged[d] = o;
+        __syncthreads();
+        const int h = hq / (n_q / n_kv);
+        const float* R = v_rot + (size_t)h * kHD * kHD + d;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < kHD; ++i) acc = fmaf(merged[i], __ldg(R + (size_t)i * kHD), acc);
+        o = acc;
+    }
+    if (buf_o) {
+        const float lb = buf_lse[row];
+        const float m2 = fmaxf(tot, lb);
+        if (m2 > -INFINITY) {
+            const float wp = tot == -INFINITY ? 0.f : expf(tot - m2);
+            const float wb = lb == -INFINITY ? 0.f : expf(lb - m2);
+            o = (wp * o + wb * buf_o[row * kHD + d]) / (wp + wb);
+            tot = m2 + logf(wp + wb);
+        }
+    }
+    if (out) out[b * o_sb + hq * o_sh + d] = __float2half_rn(o);
+    if (out_f32) out_f32[row * kHD + d] = o;
+    if (lse_out && d == 0) lse_out[row] = tot;
+}
+
+// ---------------------------------------------------------------------------
+// fp16 buffer attention: plain softmax(q k^T) v over a few hundred tokens.
+// One CTA per (query head, batch): warps score tokens, then threads own dims.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) buffer_attn_kernel(const __half* q, int64_t q_sb, int64_t q_sh,
+                                                           const __half* kb, const __half* vb, int64_t kb_sb,
+                                                           int64_t kb_sh, int n_sink_tok, int n_ring_tok,
+                                                           int sink_cap, int ring_first, int ring_size, int n_q,
+                                                           int n_kv, float scale, float* buf_o, float* buf_lse) {
+    extern __shared__ float sc[];                      // n_tok logits, then 8 floats of scratch
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hq = blockIdx.x, b = blockIdx.y;
+    const int h = hq / (n_q / n_kv);
+    const size_t row = (size_t)b * n_q + hq;
+    const int n_tok = n_sink_tok + n_ring_tok;
+    // logical token i -> buffer slot: sink prefix, then a ring starting at ring_first
+    auto slot = [&](int i) { return i < n_sink_tok ? i : sink_cap + (ring_first + (i - n_sink_tok)) % ring_size; };
+    if (n_tok <= 0) {
+        buf_o[row * kHD + tid] = 0.f;
+        if (tid == 0) buf_lse[row] = -INFINITY;
+        return;
+    }
+    const __half* qp = q + b * q_sb + hq * q_sh + 4 * lane;
+    const float q0 = __half2float(qp[0]), q1 = __half2float(qp[1]), q2 = __half2float(qp[2]), q3 = __half2float(qp[3]);
+    const __half* kbase = kb + b * kb_sb + h * kb_sh;
+    const __half* vbase = vb + b * kb_sb + h * kb_sh;
+    for (int i = warp; i < n_tok; i += 4) {
+        const __half* kr = kbase + (size_t)slot(i) * kHD + 4 * lane;
+        float s = q0 * __half2float(kr[0]) + q1 * __half2float(kr[1]) + q2 * __half2float(kr[2]) +
+                  q3 * __half2float(kr[3]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) sc[i] = s * scale;
+    }
+    __syncthreads();
+    float* red = sc + n_tok;
+    float mx = -INFINITY;
+    for (int i = tid; i < n_tok; i += 128) mx = fmaxf(mx, sc[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    float sum = 0.f;
+    for (int i = tid; i < n_tok; i += 128) {
+        const float pv = expf(sc[i] - mx);
+        sc[i] = pv;
+        sum += pv;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) red[4 + warp] = sum;
+    __syncthreads();
+    sum = red[4] + red[5] + red[6] + red[7];
+    float acc = 0.f;
+    for (int i = 0; i < n_tok; ++i) acc = fmaf(sc[i], __half2float(vbase[(size_t)slot(i) * kHD + tid]), acc);
+    buf_o[row * kHD + tid] = acc / sum;
+    if (tid == 0) buf_lse[row] = mx + logf(sum);
+}
+
+const char* const kErrNames[] = {"ok", "bad argument", "unsupported shape or mode", "misaligned pointer",
+                                 "kernel launch failed", "size exceeds a library limit"};
+
+}  // namespace
+}  // namespace bgtq
+
+using namespace bgtq;
+
+extern "C" __attribute__((visibility("default"))) int bgtq_abi_version(void) { return BGTQ_ABI_VERSION; }
+extern "C" __attribute__((visibility("default"))) int bgtq_desc_size(void) { return (int)sizeof(BgtqHeadDesc); }
+extern "C" __attribute__((visibility("default"))) const char* bgtq_error_string(int code) {
+    const int i = -code;
+    return (i >= 0 && i < (int)(sizeof(kErrNames) / sizeof(kErrNames[0]))) ? kErrNames[i] : "unknown error";
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_rotate_q(const BgtqHeadDesc* desc, const float* rot_k, const void* q, int64_t q_sb, int64_t q_sh,
+                             void* q_rot, int32_t n_batch, int32_t n_q, int32_t n_kv, void* stream) {
+    if (!desc || !rot_k || !q || !q_rot || n_batch < 1 || n_kv < 1 || n_q < n_kv || n_q % n_kv) return BGTQ_E_BADARG;
+    if (n_batch > 65535) return BGTQ_E_TOOBIG;
+    rotate_q_kernel<<<dim3(n_q, n_batch), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        desc, rot_k, static_cast<const __half*>(q), q_sb, q_sh, static_cast<__half*>(q_rot), n_q, n_kv);
+    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_combine(const float* part_o, const float* part_lse, int32_t n_splits, const float* v_rot,
+                            const float* buf_o, const float* buf_lse, int32_t n_batch, int32_t n_q, int32_t n_kv,
+                            void* out, int64_t o_sb, int64_t o_sh, float* out_f32, float* lse_out, void* stream) {
+    if (!part_o || !part_lse || n_splits < 1 || n_batch < 1 || n_kv < 1 || n_q < n_kv || n_q % n_kv)
+        return BGTQ_E_BADARG;
+    if ((buf_o == nullptr) != (buf_lse == nullptr)) return BGTQ_E_BADARG;
+    if (!out && !out_f32) return BGTQ_E_BADARG;
+    if (n_batch > 65535) return BGTQ_E_TOOBIG;
+    combine_kernel<<<dim3(n_q, n_batch), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        part_o, part_lse, n_splits, v_rot, buf_o, buf_lse, n_q, n_kv, static_cast<__half*>(out), o_sb, o_sh, out_f32,
+        lse_out);
+    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_buffer_attn(const void* q, int64_t q_sb, int64_t q_sh, const void* k_buf, const void* v_buf,
+                                int64_t kb_sb, int64_t kb_sh, int32_t n_sink_tokens, int32_t n_ring_tokens,
+                                int32_t sink_cap, int32_t ring_first, int32_t ring_size, int32_t n_batch, int32_t n_q,
+                                int32_t n_kv, float scale, float* buf_o, float* buf_lse, void* stream) {
+    if (!q || !buf_o || !buf_lse || n_batch < 1 || n_kv < 1 || n_q < n_kv || n_q % n_kv || n_sink_tokens < 0 ||
+        n_ring_tokens < 0 || n_sink_tokens > sink_cap || n_ring_tokens > ring_size || ring_first < 0 ||
+        (n_ring_tokens > 0 && ring_first >= ring_size))
+        return BGTQ_E_BADARG;
+    const int32_t n_buf_tokens = n_sink_tokens + n_ring_tokens;
+    if (n_buf_tokens > 0 && (!k_buf || !v_buf)) return BGTQ_E_BADARG;
+    if (n_buf_tokens > 8192 || n_batch > 65535) return BGTQ_E_TOOBIG;
+    const size_t smem = (size_t)(n_buf_tokens + 8) * sizeof(float);
+    buffer_attn_kernel<<<dim3(n_q, n_batch), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(q), q_sb, q_sh, static_cast<const __half*>(k_buf),
+        static_cast<const __half*>(v_buf), kb_sb, kb_sh, n_sink_tokens, n_ring_tokens, sink_cap, ring_first,
+        ring_size > 0 ? ring_size : 1, n_q, n_kv, scale, buf_o, buf_lse);
+    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+}

@@ -1,0 +1,233 @@
+"""Per-layer device tables and thin operator wrappers over the C ABI.
+
+A :class:`LayerTables` owns, for the KV heads of one layer, the uploaded array
+of ``BgtqHeadDesc`` records, the rotation matrices and the cached decode plans.
+The functions below take torch tensors, pass raw pointers and strides to
+``libbgtq.so`` and return torch tensors; they enqueue on the current stream
+and never synchronise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+from .calib import KHeadTables, VHeadTables, packed_v_bytes
+
+HD = _lib.HD
+
+
+def _fill_desc(d: _lib.HeadDesc, kt: KHeadTables, vt: VHeadTables):
+    if kt.head_dim != HD:
+        raise ValueError("the CUDA kernels support head_dim 128 only")
+    pm = kt.pack_meta
+    d.n_seg = kt.n_groups
+    d.k_row_bytes = kt.total_packed_bytes
+    d.v_bits = vt.bits
+    d.v_row_bytes = vt.packed_bytes
+    d.nopack_start, d.nopack_len = pm["nopack_start"], pm["nopack_len"]
+    d.k_mixed_bytes = pm["nopack_start"] // 2 + pm["nopack_len"]
+    cb16 = kt.codebook_flat.view(torch.int16).numpy().astype(np.uint16)
+    for s, (bw, start, length, pack_off, lut_off, _ni) in enumerate(kt.segments):
+        d.seg_bw[s], d.seg_start[s], d.seg_len[s] = bw, start, length
+        d.seg_pack_off[s], d.seg_lut_off[s] = pack_off, lut_off
+        d.lut_off[s] = float(kt.lut_offsets[start])
+        d.lut_inv[s] = float(kt.lut_inv_scales[start])
+        cents = kt.pos_centroids[start, :1 << bw]
+        for i in range(1 << bw):
+            d.codebook[lut_off + i] = int(cb16[lut_off + i])
+            d.k_cents[lut_off + i] = float(cents[i])
+        row = kt.code_lut[s].numpy()
+        C.memmove(d.code_lut[s], row.ctypes.data, _lib.N_BINS)
+    nc = 1 << vt.bits
+    vl16 = vt.lut_f16.view(torch.int16).numpy().astype(np.uint16)
+    for i in range(16):
+        d.v_cents[i] = float(vt.centroids[i]) if i < nc else 0.0
+        d.v_bounds[i] = float(vt.boundaries[i]) if i < nc - 1 else float("inf")
+        d.v_lut[i] = int(vl16[i]) if i < nc else 0
+    hp = kt.head_perm.numpy().astype(np.uint8)
+    go = kt.group_of.numpy().astype(np.uint8)
+    C.memmove(d.head_perm, hp.ctypes.data, HD)
+    C.memmove(d.group_of, go.ctypes.data, HD)
+
+
+class LayerTables:
+    """Device-resident static tables for the KV heads of one layer."""
+
+    def __init__(self, k_tables, v_tables, device):
+        self.n_kv = len(k_tables)
+        self.device = torch.device(device)
+        self.k_tables, self.v_tables = list(k_tables), list(v_tables)
+        self.desc_host = (_lib.HeadDesc * self.n_kv)()
+        for h in range(self.n_kv):
+            _fill_desc(self.desc_host[h], k_tables[h], v_tables[h])
+        raw = np.frombuffer(self.desc_host, dtype=np.uint8).copy()
+        self.desc_dev = torch.from_numpy(raw).to(self.device)
+        self.rot_k = torch.stack([t.block_rot.T.contiguous() for t in k_tables]).contiguous().to(self.device)
+        self.v_rot = torch.stack([t.rotation for t in v_tables]).contiguous().to(self.device)       # R
+        self.rot_v = torch.stack([t.rotation.T.contiguous() for t in v_tables]).contiguous().to(self.device)
+        self.v_bits = v_tables[0].bits
+        self.vpb = packed_v_bytes(HD, self.v_bits)
+        self.max_tpb = max(t.total_packed_bytes for t in k_tables)
+        self.max_ng = max(t.n_groups for t in k_tables)
+        self.max_mixed_bytes = max(t.pack_meta["nopack_start"] // 2 + t.pack_meta["nopack_len"] for t in k_tables)
+        self._plans = {}
+
+    def plan(self, flags: int = 0) -> _lib.DecodePlan:
+        p = self._plans.get(flags)
+        if p is None:
+            p = _lib.DecodePlan()
+            _lib.check(_lib.lib().bgtq_decode_plan(C.byref(self.desc_host), self.n_kv, flags, C.byref(p)),
+                       "bgtq_decode_plan")
+            self._plans[flags] = p
+        return p
+
+
+def _strides3(t: torch.Tensor):
+    """(batch, head, token) element strides of a (B, H, T, X) tensor with unit last stride."""
+    if t.dim() != 4 or t.stride(3) != 1:
+        raise ValueError(f"expected a (B, H, T, X) tensor with contiguous last dim, got {tuple(t.shape)} "
+                         f"strides {t.stride()}")
+    return t.stride(0), t.stride(1), t.stride(2)
+
+
+def encode(layer: LayerTables, k, v, t0, k_packed, k_norms, v_packed, v_norms, *, flags=0,
+           k_codes=None, v_codes=None):
+    """Encode ``k``/``v`` (B, n_kv, S, 128) fp16 into rows ``t0 .. t0+S`` of the cache tensors
+    ``k_packed`` (B, n_kv, T, bytes) u8, ``k_norms`` (B, n_kv, T, groups) f16|f32,
+    ``v_packed`` (B, n_kv, T, bytes) u8 and ``v_norms`` (B, n_kv, T) f16.  Either side may be None."""
+    L = _lib.lib()
+    ref = k if k is not None else v
+    _lib.require_cuda(ref, "k/v")
+    B, H, S, D = ref.shape
+    if H != layer.n_kv or D != HD:
+        raise ValueError("shape does not match the layer tables")
+    if k is None:
+        flags |= _lib.ENC_SKIP_K
+    if v is None:
+        flags |= _lib.ENC_SKIP_V
+    ks = _strides3(k) if k is not None else (0, 0, 0)
+    vs = _strides3(v) if v is not None else (0, 0, 0)
+    if k is not None:
+        if k.dtype != torch.float16 or k_packed.dtype != torch.uint8:
+            raise TypeError("k must be float16 and k_packed uint8")
+        if k_norms.dtype == torch.float16:
+            flags |= _lib.ENC_K_NORMS_F16
+        elif k_norms.dtype != torch.float32:
+            raise TypeError("k_norms must be float16 or float32")
+        kps, kns = _strides3(k_packed), _strides3(k_norms)
+        if t0 + S > k_packed.shape[2]:
+            raise ValueError("cache overflow")
+        kp_bytes, kn_count = k_packed.shape[3], k_norms.shape[3]
+    else:
+        kps = kns = (0, 0, 0)
+        kp_bytes = kn_count = 1
+    if v is not None:
+        if v.dtype != torch.float16 or v_packed.dtype != torch.uint8 or v_norms.dtype != torch.float16:
+            raise TypeError("v must be float16, v_packed uint8, v_norms float16")
+        vps = _strides3(v_packed)
+        need = HD // 2 if flags & _lib.ENC_V_NIBBLE else layer.vpb
+        if v_packed.shape[3] < need:
+            raise ValueError("v_packed rows are too short")
+        vns = (v_norms.stride(0), v_norms.stride(1), v_norms.stride(2))
+    else:
+        vps = vns = (0, 0, 0)
+    _lib.check(L.bgtq_encode(
+        _lib.ptr(layer.desc_dev), _lib.ptr(layer.rot_k), _lib.ptr(layer.rot_v),
+        _lib.ptr(k), *ks, _lib.ptr(v), *vs, B, H, S, int(t0),
+        _lib.ptr(k_packed), *kps, kp_bytes, _lib.ptr(k_norms), *kns, kn_count,
+        _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns,
+        _lib.ptr(k_codes), _lib.ptr(v_codes), flags, _lib.stream_ptr(ref.device)), "bgtq_encode")
+    _lib.count_launch()
+
+
+def rotate_q(layer: LayerTables, q: torch.Tensor) -> torch.Tensor:
+    """q (B, n_q, 128) or (B, n_q, 1, 128) fp16 -> (B, n_q, 128) fp16 in the packed-K basis."""
+    _lib.require_cuda(q, "q")
+    if q.dim() == 4:
+        q = q[:, :, 0]
+    if q.stride(2) != 1 or q.dtype != torch.float16:
+        q = q.contiguous().to(torch.float16)
+    B, n_q, _ = q.shape
+    out = torch.empty(B, n_q, HD, dtype=torch.float16, device=q.device)
+    _lib.check(_lib.lib().bgtq_rotate_q(_lib.ptr(layer.desc_dev), _lib.ptr(layer.rot_k), _lib.ptr(q),
+                                        q.stride(0), q.stride(1), _lib.ptr(out), B, n_q, layer.n_kv,
+                                        _lib.stream_ptr(q.device)), "bgtq_rotate_q")
+    _lib.count_launch()
+    return out
+
+
+def default_splits(n_batch: int, n_kv: int, n_tokens: int) -> int:
+    return _lib.lib().bgtq_decode_default_splits(n_batch, n_kv, n_tokens)
+
+
+def decode(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_norms, t_begin, t_end, *,
+           n_splits=None, scale=None, flags=0, part_o=None, part_lse=None, status=None):
+    """Split-KV attention partials over cache rows [t_begin, t_end).
+
+    Returns (part_o (B, n_q, n_splits, 128) f32, part_lse (B, n_q, n_splits) f32)."""
+    _lib.require_cuda(q_rot, "q_rot")
+    B, n_q, _ = q_rot.shape
+    if not q_rot.is_contiguous() or q_rot.dtype != torch.float16:
+        raise ValueError("q_rot must be contiguous float16 (B, n_q, 128)")
+    if k_norms.dtype != torch.float16 or v_norms.dtype != torch.float16:
+        raise TypeError("cache norms must be float16")
+    n_tok = t_end - t_begin
+    if n_splits is None:
+        n_splits = default_splits(B, layer.n_kv, n_tok)
+    if scale is None:
+        scale = 1.0 / math.sqrt(HD)
+    if part_o is None:
+        part_o = torch.empty(B, n_q, n_splits, HD, dtype=torch.float32, device=q_rot.device)
+        part_lse = torch.empty(B, n_q, n_splits, dtype=torch.float32, device=q_rot.device)
+    kps, kns, vps = _strides3(k_packed), _strides3(k_norms), _strides3(v_packed)
+    vns = (v_norms.stride(0), v_norms.stride(1), v_norms.stride(2))
+    plan = layer.plan(flags)
+    _lib.check(_lib.lib().bgtq_decode(
+        C.addressof(plan), _lib.ptr(layer.desc_dev), _lib.ptr(q_rot),
+        _lib.ptr(k_packed), *kps, _lib.ptr(k_norms), *kns, _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns,
+        B, n_q, layer.n_kv, int(t_begin), int(t_end), int(n_splits), float(scale),
+        _lib.ptr(part_o), _lib.ptr(part_lse), _lib.ptr(status), _lib.stream_ptr(q_rot.device)), "bgtq_decode")
+    _lib.count_launch()
+    return part_o, part_lse
+
+
+def combine(part_o, part_lse, n_kv, *, v_rot=None, buf_o=None, buf_lse=None, out=None,
+            want_f32=False, want_lse=False):
+    """Merge (B, n_q, S, 128)/(B, n_q, S) partials -> fp16 (B, n_q, 128) [+ f32 copy, total LSE]."""
+    B, n_q, S, _ = part_o.shape
+    dev = part_o.device
+    if out is None:
+        out = torch.empty(B, n_q, HD, dtype=torch.float16, device=dev)
+    o32 = torch.empty(B, n_q, HD, dtype=torch.float32, device=dev) if want_f32 else None
+    lse = torch.empty(B, n_q, dtype=torch.float32, device=dev) if want_lse else None
+    _lib.check(_lib.lib().bgtq_combine(
+        _lib.ptr(part_o), _lib.ptr(part_lse), S, _lib.ptr(v_rot), _lib.ptr(buf_o), _lib.ptr(buf_lse),
+        B, n_q, n_kv, _lib.ptr(out), out.stride(0), out.stride(1), _lib.ptr(o32), _lib.ptr(lse),
+        _lib.stream_ptr(dev)), "bgtq_combine")
+    _lib.count_launch()
+    return out, o32, lse
+
+
+def buffer_attn(q, k_buf, v_buf, n_kv, scale, *, n_sink_tokens, n_ring_tokens, sink_cap, ring_first, ring_size):
+    """Attention over unquantised fp16 tokens.  q (B, n_q, 128) fp16 (original basis);
+    k_buf/v_buf (B, n_kv, cap, 128) fp16 with contiguous token rows: a sink prefix and a ring
+    of ``ring_size`` slots starting at slot ``sink_cap`` (see ``bgtq_buffer_attn``)."""
+    _lib.require_cuda(q, "q")
+    if q.dim() == 4:
+        q = q[:, :, 0]
+    B, n_q, _ = q.shape
+    o = torch.empty(B, n_q, HD, dtype=torch.float32, device=q.device)
+    lse = torch.empty(B, n_q, dtype=torch.float32, device=q.device)
+    if k_buf.stride(2) != HD or k_buf.stride(3) != 1 or v_buf.stride() != k_buf.stride():
+        raise ValueError("buffer tensors must be (B, n_kv, cap, 128) with contiguous token rows")
+    _lib.check(_lib.lib().bgtq_buffer_attn(
+        _lib.ptr(q), q.stride(0), q.stride(1), _lib.ptr(k_buf), _lib.ptr(v_buf), k_buf.stride(0), k_buf.stride(1),
+        int(n_sink_tokens), int(n_ring_tokens), int(sink_cap), int(ring_first), int(ring_size),
+        B, n_q, n_kv, float(scale), _lib.ptr(o), _lib.ptr(lse), _lib.stream_ptr(q.device)),
+        "bgtq_buffer_attn")
+    _lib.count_launch()
+    return o, lse

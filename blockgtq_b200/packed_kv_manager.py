@@ -1,0 +1,334 @@
+"""``BlockGTQKVManager``: the bit-packed KV cache with fused decode attention,
+mirroring blockgtq/packed_kv_manager.py (constructor, methods, storage
+attributes and shapes), with each layer step running as a handful of CUDA
+launches covering every batch entry and KV head at once:
+
+    rotate_q -> encode (K and V of the new token, written in place) -> decode -> combine
+
+Extensions beyond the reference class (all off by default):
+  * ``n_sink`` / ``recent_window`` / ``block_size``: the three-region policy of
+    blockgtq/unaccelerated.py:163-244 on the packed path -- the first ``n_sink``
+    tokens and a recent window stay in fp16 buffers, everything between is
+    packed; the fp16 region is attended by its own kernel and merged by LSE.
+  * ``token_range`` on :meth:`attend`: lets a rank attend a slice of the sequence
+    and return (O, LSE) for a cross-GPU merge.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from .calib import packed_v_bytes
+from .layer import HD, LayerTables, buffer_attn, combine, decode, default_splits, encode, rotate_q
+from .quantizer import BlockGTQQuantizer, build_batched_encode_args
+
+__all__ = ["BlockGTQKVManager", "decode_step"]
+
+
+class BlockGTQKVManager:
+    def __init__(self, n_layers: int, n_q_heads: int, n_kv_heads: int, head_dim: int, max_seq_len: int,
+                 batch_size: int = 1, k_avg_bits: float = 3.0, v_bits: int = 3, device="cuda",
+                 n_sink: int = 0, recent_window: int = 0, block_size: int = 1,
+                 min_bits: int = 1, max_bits: int = 8, rotation_threshold: int = 2):
+        if head_dim != HD:
+            raise ValueError("head_dim must be 128")
+        if n_kv_heads > 8 or n_q_heads // n_kv_heads > 8:
+            raise ValueError("at most 8 KV heads per layer and 8 query heads per KV head are supported")
+        self.n_layers, self.n_q, self.n_kv, self.hd = n_layers, n_q_heads, n_kv_heads, head_dim
+        self.max_T, self.B = max_seq_len, batch_size
+        self.k_avg_bits, self.v_bits = k_avg_bits, v_bits
+        self.device = torch.device(device)
+        self.gqa_ratio = n_q_heads // n_kv_heads
+        self.scale = 1.0 / math.sqrt(head_dim)
+        self.seq_len = 0                      # tokens appended so far (all regions)
+        self._quant_opts = dict(min_bits=min_bits, max_bits=max_bits, rotation_threshold=rotation_threshold)
+        self.quantizers = [[None] * n_kv_heads for _ in range(n_layers)]
+        self._kernel_args = [[None] * n_kv_heads for _ in range(n_layers)]
+        self._batched_args = [None] * n_layers
+        self._layers = [None] * n_layers
+        self._max_k_packed_bytes = 0
+        self._max_n_groups = 0
+        self._k_packed = self._k_norms = self._v_packed = self._v_norms = None
+        # three-region policy
+        self.n_sink, self.recent_window, self.block_size = int(n_sink), int(recent_window), int(block_size)
+        self._buffered = self.n_sink > 0 or self.recent_window > 0
+        self._buf_cap = self.n_sink + self.recent_window + self.block_size if self._buffered else 0
+        self._k_buf = self._v_buf = None
+        self.n_packed = 0                     # tokens in the packed region
+        self._status = None
+
+    # -- calibration -----------------------------------------------------------------
+    def calibrate(self, layer_idx: int, q_data: torch.Tensor, k_data: torch.Tensor):
+        """Per-head tables for one layer; data (N, hd) shared or (n_kv, N, hd) per head
+        (packed_kv_manager.py:85-114)."""
+        if q_data.dim() == 2:
+            q_data = q_data.unsqueeze(0).expand(self.n_kv, -1, -1)
+            k_data = k_data.unsqueeze(0).expand(self.n_kv, -1, -1)
+        for hi in range(self.n_kv):
+            qz = BlockGTQQuantizer(head_dim=self.hd, avg_bits=self.k_avg_bits, device=self.device,
+                                   **self._quant_opts)
+            qz.calibrate(q_data[hi], k_data[hi])
+            qz.init_v_quantizer(v_bits=self.v_bits, seed=42 + hi)
+            self.quantizers[layer_idx][hi] = qz
+            ka = qz.build_kernel_args()
+            self._kernel_args[layer_idx][hi] = ka
+            self._max_k_packed_bytes = max(self._max_k_packed_bytes, ka["total_packed_bytes"])
+            self._max_n_groups = max(self._max_n_groups, qz._n_groups)
+        self._batched_args[layer_idx] = build_batched_encode_args(self.quantizers[layer_idx], device=self.device)
+        self._layers[layer_idx] = self._batched_args[layer_idx]["_layer"]
+
+    def set_quantizers(self, layer_idx: int, quantizers: list):
+        """Install already calibrated quantisers for a layer."""
+        for hi, qz in enumerate(quantizers):
+            self.quantizers[layer_idx][hi] = qz
+            self._kernel_args[layer_idx][hi] = qz.build_kernel_args()
+            self._max_k_packed_bytes = max(self._max_k_packed_bytes, qz._total_packed_bytes)
+            self._max_n_groups = max(self._max_n_groups, qz._n_groups)
+        self._batched_args[layer_idx] = build_batched_encode_args(quantizers, device=self.device)
+        self._layers[layer_idx] = self._batched_args[layer_idx]["_layer"]
+
+    def _ensure_storage(self):
+        if self._k_packed is not None:
+            return
+        vpb = packed_v_bytes(self.hd, self.v_bits)
+        # token capacity rounded up so 64-token tiles never leave the allocation
+        cap = ((self.max_T + 63) // 64) * 64
+        shape = (self.n_layers, self.B, self.n_kv, cap)
+        dev = self.device
+        self._k_packed = torch.zeros(*shape, self._max_k_packed_bytes, dtype=torch.uint8, device=dev)[:, :, :, :self.max_T]
+        self._k_norms = torch.zeros(*shape, self._max_n_groups, dtype=torch.float16, device=dev)[:, :, :, :self.max_T]
+        self._v_packed = torch.zeros(*shape, vpb, dtype=torch.uint8, device=dev)[:, :, :, :self.max_T]
+        self._v_norms = torch.zeros(*shape, dtype=torch.float16, device=dev)[:, :, :, :self.max_T]
+        self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        if self._buffered:
+            self._k_buf = torch.zeros(self.n_layers, self.B, self.n_kv, self._buf_cap, self.hd,
+                                      dtype=torch.float16, device=dev)
+            self._v_buf = torch.zeros_like(self._k_buf)
+
+    # -- encode --------------------------------------------------------------------------
+    def _encode_kv(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, t_start: int, t_end: int):
+        """Encode (B, n_kv, S, hd) fp16 into packed rows [t_start, t_end): one launch, written in place
+        (packed_kv_manager.py:138-180)."""
+        self._ensure_storage()
+        li = layer_idx
+        assert k.shape[2] == t_end - t_start
+        encode(self._layers[li], k.to(torch.float16), v.to(torch.float16), t_start,
+               self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li])
+
+    def init_from_cache(self, past_key_value):
+        """Bulk-encode an HF cache after prefill (packed_kv_manager.py:259-266).  Accepts the
+        legacy ``key_cache``/``value_cache`` lists, the ``layers[i].keys/values`` layout of newer
+        transformers, or a plain sequence of (k, v) pairs."""
+        T = 0
+        for li in range(self.n_layers):
+            k, v = _layer_kv(past_key_value, li)
+            T = k.shape[2]
+            self._append_tokens(li, k, v, 0)
+        self.seq_len = T
+
+    # -- three-region bookkeeping ------------------------------------------------------------
+    # Non-sink token i (i = position - n_sink) lives in ring slot n_sink + i % ring while it is
+    # "recent"; once  (#non-sink tokens) - n_flushed >= block_size + recent_window  the oldest
+    # block_size recent tokens are quantised into packed rows [n_flushed, n_flushed + block_size)
+    # (flush rule of blockgtq/unaccelerated.py:226-233).  n_flushed depends only on the token count.
+    def _flushed(self, n_non_sink: int) -> int:
+        need = self.block_size + self.recent_window
+        if n_non_sink < need:
+            return 0
+        return ((n_non_sink - need) // self.block_size + 1) * self.block_size
+
+    def _region_sizes(self, seq_len: int, flushed: int = None):
+        """(fp16 sink tokens, packed tokens, fp16 recent tokens) for ``seq_len`` appended tokens."""
+        if not self._buffered:
+            return 0, seq_len, 0
+        sink = min(seq_len, self.n_sink)
+        avail = max(0, seq_len - self.n_sink)
+        if flushed is None:
+            flushed = self._flushed(avail)
+        return sink, flushed, avail - flushed
+
+    def _ring_slots(self, lo: int, hi: int) -> torch.Tensor:
+        ring = self._buf_cap - self.n_sink
+        return torch.tensor([self.n_sink + i % ring for i in range(lo, hi)], dtype=torch.long, device=self.device)
+
+    def _append_tokens(self, li: int, k: torch.Tensor, v: torch.Tensor, t: int, defer_flush: bool = False):
+        """Append S tokens with absolute positions t .. t+S-1 to layer ``li``.
+
+        With ``defer_flush`` the new tokens only enter the fp16 buffers (the caller attends first and
+        then calls :meth:`_flush`, the order the reference's post-forward hook produces for a decode
+        step).  Returns the (before, after) packed-region sizes."""
+        S = k.shape[2]
+        if not self._buffered:
+            self._encode_kv(li, k, v, t, t + S)
+            return t, t + S
+        self._ensure_storage()
+        k, v = k.to(torch.float16), v.to(torch.float16)
+        kb, vb = self._k_buf[li], self._v_buf[li]
+        ns = self.n_sink
+        a0, a1 = max(0, t - ns), max(0, t + S - ns)
+        f0, f1 = self._flushed(a0), self._flushed(a1)
+        n_sink_new = max(0, min(ns, t + S) - t)
+        if n_sink_new:
+            kb[:, :, t:t + n_sink_new] = k[:, :, :n_sink_new]
+            vb[:, :, t:t + n_sink_new] = v[:, :, :n_sink_new]
+        if defer_flush:
+            if a1 - f0 > self._buf_cap - ns:
+                raise RuntimeError("recent ring overflow: flush before appending more tokens")
+            lo = a0
+        else:
+            self._flush(li, f0, min(f1, a0))                   # tokens already resident in the ring
+            lo = max(f1, a0)
+            if f1 > a0:                                        # new tokens that go straight to packed rows
+                s0, s1 = max(f0, a0) + ns - t, f1 + ns - t
+                encode(self._layers[li], k[:, :, s0:s1], v[:, :, s0:s1], max(f0, a0), self._k_packed[li],
+                       self._k_norms[li], self._v_packed[li], self._v_norms[li])
+        if a1 > lo:                                            # new tokens that stay recent
+            slots = self._ring_slots(lo, a1)
+            kb.index_copy_(2, slots, k[:, :, lo + ns - t:a1 + ns - t])
+            vb.index_copy_(2, slots, v[:, :, lo + ns - t:a1 + ns - t])
+        return f0, f1
+
+    def _flush(self, li: int, f_lo: int, f_hi: int):
+        """Quantise ring-resident non-sink tokens [f_lo, f_hi) into packed rows [f_lo, f_hi)."""
+        if f_hi <= f_lo:
+            return
+        slots = self._ring_slots(f_lo, f_hi)
+        encode(self._layers[li], self._k_buf[li].index_select(2, slots), self._v_buf[li].index_select(2, slots),
+               f_lo, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li])
+
+    # -- decode ----------------------------------------------------------------------------
+    @torch.no_grad()
+    def append_and_attend(self, layer_idx: int, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+                          n_splits: int = None) -> torch.Tensor:
+        """Quantise and append (B, n_kv, S, hd) K/V, then attend the (B, n_q, 1, hd) query over the
+        whole cache.  Returns (B, n_q, 1, hd) fp16 (packed_kv_manager.py:268-348)."""
+        t, S = self.seq_len, k_new.shape[2]
+        defer = self._buffered and S == 1
+        f0, f1 = self._append_tokens(layer_idx, k_new, v_new, t, defer_flush=defer)
+        out, _, _ = self.attend(layer_idx, q, t + S, n_splits=n_splits, flushed=f0 if defer else None)
+        if defer:
+            self._flush(layer_idx, f0, f1)
+        return out.unsqueeze(2)
+
+    @torch.no_grad()
+    def attend(self, layer_idx: int, q: torch.Tensor, seq_len: int = None, *, n_splits: int = None,
+               token_range=None, want_partial: bool = False, flushed: int = None, with_buffers: bool = True):
+        """Attention of q (B, n_q, [1,] hd) over the first ``seq_len`` cached tokens.
+
+        ``token_range=(lo, hi)`` restricts the packed region to rows [lo, hi) and ``with_buffers``
+        says whether this call also covers the fp16 region (sequence sharding: one rank does).
+        Returns (out fp16 (B, n_q, hd), out_f32 | None, lse | None); the last two when ``want_partial``."""
+        li = layer_idx
+        lt: LayerTables = self._layers[li]
+        seq_len = self.seq_len if seq_len is None else seq_len
+        n_sink_tok, n_packed, n_recent = self._region_sizes(seq_len, flushed)
+        if q.dim() == 4:
+            q = q[:, :, 0]
+        q = q.to(torch.float16)
+        lo, hi = (0, n_packed) if token_range is None else token_range
+        lo = max(0, min(lo, n_packed))
+        hi = max(lo, min(hi, n_packed))
+        baked = all(self.quantizers[li][h]._q_perm_baked for h in range(self.n_kv))
+        q_rot = q.contiguous() if baked else rotate_q(lt, q)
+        part_o, part_lse = decode(lt, q_rot, self._k_packed[li], self._k_norms[li], self._v_packed[li],
+                                  self._v_norms[li], lo, hi, n_splits=n_splits, scale=self.scale,
+                                  status=self._status)
+        buf_o = buf_lse = None
+        if self._buffered and with_buffers:
+            buf_o, buf_lse = self._buffer_partial(li, q, n_sink_tok, n_packed, n_recent)
+        return combine(part_o, part_lse, self.n_kv, v_rot=lt.v_rot, buf_o=buf_o, buf_lse=buf_lse,
+                       want_f32=want_partial, want_lse=want_partial)
+
+    def _buffer_partial(self, li, q, n_sink_tok, n_packed, n_recent):
+        """(O, LSE) of the fp16 region: sink slots [0, n_sink_tok) + ring slots of the recent tokens."""
+        ring = self._buf_cap - self.n_sink
+        return buffer_attn(q, self._k_buf[li], self._v_buf[li], self.n_kv, self.scale,
+                           n_sink_tokens=n_sink_tok, n_ring_tokens=n_recent, sink_cap=self.n_sink,
+                           ring_first=n_packed % ring, ring_size=ring)
+
+    def increment_seq_len(self, by: int = 1):
+        """Call after all layers processed the new token(s) (packed_kv_manager.py:350-352)."""
+        self.seq_len += by
+        _, self.n_packed, _ = self._region_sizes(self.seq_len)
+
+    def check_status(self):
+        """Synchronise and raise if a kernel reported a timed-out wait."""
+        if self._status is not None and int(self._status.item()) != 0:
+            raise RuntimeError(f"decode kernel reported status {int(self._status.item())}")
+
+    def bake_q_permutations(self, model, n_kv_heads: int, n_q_heads: int):
+        """Bake each head's permutation + rotation into q_proj (packed_kv_manager.py:354-373)."""
+        layers = _get_model_layers(model)
+        for li in range(self.n_layers):
+            attn = layers[li].self_attn
+            for hi in range(self.n_kv):
+                self.quantizers[li][hi].bake_permutation_into_qproj(
+                    attn.q_proj.weight.data, kv_head_idx=hi, n_kv_heads=n_kv_heads, n_q_heads=n_q_heads,
+                    q_proj_bias=getattr(attn.q_proj, "bias", None))
+
+    def cache_memory_bytes(self) -> int:
+        """Compressed cache bytes for the current length, padding included (packed_kv_manager.py:375-382)."""
+        _, T, n_rec = self._region_sizes(self.seq_len)
+        per_tok = self._max_k_packed_bytes + packed_v_bytes(self.hd, self.v_bits) + self._max_n_groups * 2 + 2
+        packed = per_tok * T * self.n_kv * self.B * self.n_layers
+        fp16 = (min(self.seq_len, self.n_sink) + n_rec) * self.hd * 2 * 2 * self.n_kv * self.B * self.n_layers
+        return packed + fp16
+
+    def live_bytes_per_step(self) -> int:
+        """Bytes one decode step must read: per head its own packed K size and group count
+        (not the padded strides), V bytes, norms, plus the fp16 buffer tokens."""
+        sink, T, n_rec = self._region_sizes(self.seq_len)
+        vpb = packed_v_bytes(self.hd, self.v_bits)
+        tot = 0
+        for li in range(self.n_layers):
+            for hi in range(self.n_kv):
+                qz = self.quantizers[li][hi]
+                tot += T * (qz._total_packed_bytes + 2 * qz._n_groups + vpb + 2)
+        tot *= self.B
+        tot += (sink + n_rec) * self.hd * 2 * 2 * self.n_kv * self.B * self.n_layers
+        return tot
+
+    def fp16_cache_bytes(self) -> int:
+        return self.n_layers * self.B * self.n_kv * self.seq_len * self.hd * 2 * 2
+
+
+def _layer_kv(pkv, li):
+    if hasattr(pkv, "key_cache"):
+        return pkv.key_cache[li], pkv.value_cache[li]
+    if hasattr(pkv, "layers"):
+        lay = pkv.layers[li]
+        return lay.keys, lay.values
+    return pkv[li][0], pkv[li][1]
+
+
+def _get_model_layers(model):
+    if hasattr(model, "model") and hasattr(model.model, "layers"):
+        return list(model.model.layers)
+    raise ValueError("Cannot find model layers - expected model.model.layers")
+
+
+def decode_step(model, input_ids, position_ids, kv_manager: BlockGTQKVManager):
+    """One decode step of an HF Llama-style model through the packed cache
+    (packed_kv_manager.py:401-453).  input_ids/position_ids (B, 1) -> logits (B, 1, vocab)."""
+    from transformers.models.llama.modeling_llama import apply_rotary_pos_emb
+    hidden = model.model.embed_tokens(input_ids)
+    n_q, n_kv, hd = kv_manager.n_q, kv_manager.n_kv, kv_manager.hd
+    for li, layer in enumerate(_get_model_layers(model)):
+        resid = hidden
+        hidden = layer.input_layernorm(hidden)
+        attn = layer.self_attn
+        B, S, _ = hidden.shape
+        q = attn.q_proj(hidden).view(B, S, n_q, hd).transpose(1, 2)
+        k = attn.k_proj(hidden).view(B, S, n_kv, hd).transpose(1, 2)
+        v = attn.v_proj(hidden).view(B, S, n_kv, hd).transpose(1, 2)
+        rope = getattr(attn, "rotary_emb", None) or model.model.rotary_emb
+        cos, sin = rope(v, position_ids)
+        q, k = apply_rotary_pos_emb(q, k, cos, sin)
+        out = kv_manager.append_and_attend(li, q, k, v)
+        hidden = resid + attn.o_proj(out.transpose(1, 2).reshape(B, S, n_q * hd).to(hidden.dtype))
+        resid = hidden
+        hidden = resid + layer.mlp(layer.post_attention_layernorm(hidden))
+    kv_manager.increment_seq_len()
+    return model.lm_head(model.model.norm(hidden))

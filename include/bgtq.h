@@ -1,0 +1,219 @@
+/*
+ * bgtq.h -- C ABI of the B200 (sm_100a) packed-KV-cache kernels for Block-GTQ.
+ *
+ * The library replaces the GPU side of the reference's packed-cache decode
+ * path (all of which is Triton there).  Each entry point cites the reference
+ * operator it stands in for, by the file's path inside the reference project.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the comment says "host";
+ *   - the caller owns all memory; no entry point allocates, frees or
+ *     synchronises (bgtq_*_noalloc: see its own comment);
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*);
+ *   - return value: BGTQ_OK or a negative BGTQ_E_* code; nothing throws;
+ *   - strides are in ELEMENTS of the pointed-to type unless stated in bytes;
+ *   - head_dim is fixed at 128 (every configuration of the reference's
+ *     benchmarks); other sizes return BGTQ_E_UNSUPPORTED.
+ */
+#ifndef BGTQ_H_
+#define BGTQ_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BGTQ_ABI_VERSION 1
+#define BGTQ_HEAD_DIM 128
+#define BGTQ_MAX_SEGMENTS 8
+#define BGTQ_N_BINS 256
+
+#define BGTQ_OK 0
+#define BGTQ_E_BADARG (-1)
+#define BGTQ_E_UNSUPPORTED (-2)
+#define BGTQ_E_ALIGN (-3)
+#define BGTQ_E_LAUNCH (-4)
+#define BGTQ_E_TOOBIG (-5)
+
+/* Static tables of one (layer, KV head).  The host fills an array of these
+ * (one per KV head of a layer) and uploads it; kernels index it by KV head.
+ * Source of every field: BlockGTQQuantizer.calibrate / build_kernel_args /
+ * init_v_quantizer and build_batched_encode_args
+ * (blockgtq/quantizer.py:1024-1148, 1478-1497, 1598-1747).
+ *
+ * "packed position" p = index of a dim after head_perm (dims sorted by bit
+ * width); segment s = run of packed positions sharing one width = one norm
+ * group = one codebook. */
+typedef struct BgtqHeadDesc {
+    int32_t n_seg;                 /* 1..8 */
+    int32_t k_row_bytes;           /* live packed K bytes per token (bit-packed layout) */
+    int32_t v_bits;                /* 1..4 */
+    int32_t v_row_bytes;           /* packed V bytes per token */
+    int32_t nopack_start;          /* first packed position held as a raw byte (128 if none) */
+    int32_t nopack_len;
+    int32_t k_mixed_bytes;         /* nopack_start/2 + nopack_len (nibble/raw layout) */
+    int32_t reserved0;
+    int32_t seg_bw[BGTQ_MAX_SEGMENTS];        /* code width 1..8 */
+    int32_t seg_start[BGTQ_MAX_SEGMENTS];     /* first packed position */
+    int32_t seg_len[BGTQ_MAX_SEGMENTS];       /* number of positions (even) */
+    int32_t seg_pack_off[BGTQ_MAX_SEGMENTS];  /* byte offset inside a packed K row */
+    int32_t seg_lut_off[BGTQ_MAX_SEGMENTS];   /* offset into codebook[] / k_cents[] */
+    float lut_off[BGTQ_MAX_SEGMENTS];         /* bin = (y - lut_off) * lut_inv, clamp 0..255 */
+    float lut_inv[BGTQ_MAX_SEGMENTS];
+    float v_cents[16];
+    float v_bounds[16];            /* 2^v_bits - 1 used; rest +inf */
+    uint16_t v_lut[16];            /* fp16 bit patterns of v_cents */
+    uint16_t codebook[512];        /* fp16 bit patterns, segment s at seg_lut_off[s] */
+    float k_cents[512];            /* same entries in fp32 (norm correction) */
+    uint8_t head_perm[BGTQ_HEAD_DIM];         /* packed position -> original dim */
+    uint8_t group_of[BGTQ_HEAD_DIM];          /* packed position -> segment index */
+    uint8_t code_lut[BGTQ_MAX_SEGMENTS][BGTQ_N_BINS];
+} BgtqHeadDesc;
+
+/* Build-time identity checks for language bindings. */
+int bgtq_abi_version(void);
+int bgtq_desc_size(void);                      /* sizeof(BgtqHeadDesc) */
+const char* bgtq_error_string(int code);       /* host pointer to a static string */
+
+/* ---- encoder flags ------------------------------------------------------- */
+#define BGTQ_ENC_K_NORMS_F16 1    /* write K norms as fp16 (cache) instead of fp32 (operator API) */
+#define BGTQ_ENC_K_MIXED 2        /* K rows in the nibble/raw "mixed" layout + corrected norms */
+#define BGTQ_ENC_V_NIBBLE 4       /* V rows as 4-bit nibbles regardless of v_bits */
+#define BGTQ_ENC_SKIP_K 8
+#define BGTQ_ENC_SKIP_V 16
+
+/* Encode K and V rows of all KV heads of one layer and write them straight
+ * into their cache slots.
+ *
+ * Replaces compress_k_packed_batched / compress_v_packed_batched
+ * (blockgtq/quantizer.py:2104-2172, 1979-2029; kernels :712-990, :517-706),
+ * their "mixed"/"nibble" variants (:1843-1976, :2032-2101), the unpacked-code
+ * output of BlockGTQQuantizer.compress (blockgtq/kernels/quant_kernels.py:470-565)
+ * and the strided cache writes of BlockGTQKVManager._encode_kv
+ * (blockgtq/packed_kv_manager.py:176-180).
+ *
+ * Rows form a (n_batch, n_kv, n_tok) grid.  Input element (b,h,s,d) is at
+ * k + b*k_sb + h*k_sh + s*k_ss + d (same for v).  Output row (b,h,s) lands at
+ * token slot t0+s: k_packed + b*kp_sb + h*kp_sh + (t0+s)*kp_st bytes, etc.
+ * Each packed K row is written for kp_row_bytes bytes (bytes past the head's
+ * live size are zero); K norms are written for kn_count groups (groups the
+ * head does not have are zero).
+ *
+ * rot_k / rot_v: (n_kv, 128, 128) fp32.  rot_k[h][j][p] = block_rot_T (row j =
+ * packed input position, column p = packed output position); rot_v[h][i][j] =
+ * R^T so that y = v_unit @ rot_v[h].
+ * k_codes / v_codes: optional (may be NULL) outputs of the unpacked indices,
+ * (n_batch, n_kv, n_tok, 128) contiguous uint8, K in packed-position order.
+ */
+int bgtq_encode(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v,
+                const void* k, int64_t k_sb, int64_t k_sh, int64_t k_ss,
+                const void* v, int64_t v_sb, int64_t v_sh, int64_t v_ss,
+                int32_t n_batch, int32_t n_kv, int32_t n_tok, int32_t t0,
+                uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st, int32_t kp_row_bytes,
+                void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
+                uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
+                void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
+                uint8_t* k_codes, uint8_t* v_codes,
+                int32_t flags, void* stream);
+
+/* Rotate decode queries into the packed-K basis:
+ * q_rot[b, hq, p] = fp16( sum_j fp32(q[b, hq, head_perm[j]]) * rot_k[h][j][p] ),
+ * h = hq / (n_q / n_kv).
+ * Replaces BlockGTQQuantizer.rotate_q_for_packed_kernel
+ * (blockgtq/quantizer.py:1160-1187) for all heads of a layer in one launch.
+ * q element (b,hq,d) at q + b*q_sb + hq*q_sh + d; q_rot is (n_batch, n_q, 128)
+ * contiguous fp16. */
+int bgtq_rotate_q(const BgtqHeadDesc* desc, const float* rot_k,
+                  const void* q, int64_t q_sb, int64_t q_sh,
+                  void* q_rot, int32_t n_batch, int32_t n_q, int32_t n_kv, void* stream);
+
+/* ---- decode --------------------------------------------------------------- */
+#define BGTQ_DEC_K_MIXED 1        /* k_packed rows are in the nibble/raw mixed layout */
+#define BGTQ_DEC_V_NIBBLE 2       /* v_packed rows are 4-bit nibbles */
+
+/* Opaque launch plan of the decode kernel for the KV heads of one layer (host
+ * memory, plain bytes, copyable).  Built once per layer from the HOST copy of
+ * the head descriptors; at most 8 KV heads per plan (split wider layers into
+ * groups of heads). */
+typedef struct BgtqDecodePlan {
+    uint8_t opaque[3072];
+} BgtqDecodePlan;
+int bgtq_decode_plan(const BgtqHeadDesc* desc_host, int32_t n_kv, int32_t flags, BgtqDecodePlan* plan_host);
+
+/* Number of token splits the library suggests for a (batch, heads, tokens)
+ * shape on the current device (host helper, no GPU work). */
+int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv, int32_t n_tokens);
+
+/* Fused unpack + dequantise + split-KV attention of one decode query per
+ * (batch, query head) over cache tokens [t_begin, t_end).
+ *
+ * Replaces fused_blockgtq_decode_attention's first phase, _packed_decode_kernel
+ * (blockgtq/kernels/fused_packed_attention.py:152-894, wrapper :1541-1843), for
+ * every KV head of a layer in ONE launch (the reference launches per head).
+ *
+ * plan_host: from bgtq_decode_plan (host memory); desc: the same descriptors on
+ * the device.  q_rot: (n_batch, n_q, 128) fp16 contiguous, already in the
+ * packed-K basis; n_q / n_kv <= 8.
+ * Cache row (b,h,t): k_packed + b*kp_sb + h*kp_sh + t*kp_st  (bytes; rows of one
+ * (b,h) must be equally spaced), k_norms fp16 at + b*kn_sb + h*kn_sh + t*kn_st
+ * (+ segment index), v_packed / v_norms likewise (v_norms: one fp16 per token).
+ * Rows need no particular alignment.
+ * Outputs, for split c of n_splits (tokens are cut into n_splits equal runs
+ * rounded up to 64):
+ *   part_o  (n_batch, n_q, n_splits, 128) fp32  softmax-normalised partial
+ *           output, still in V's rotated basis (16-byte aligned)
+ *   part_lse(n_batch, n_q, n_splits)      fp32  log-sum-exp of the scaled
+ *           logits of the split; -inf for a split with no tokens (part_o = 0).
+ * status: optional int32 on the device; set to a non-zero code if a bounded
+ * wait inside the kernel gave up (the output is then invalid).
+ */
+int bgtq_decode(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot,
+                const uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
+                const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
+                const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
+                const void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
+                int32_t n_batch, int32_t n_q, int32_t n_kv,
+                int32_t t_begin, int32_t t_end, int32_t n_splits, float scale,
+                float* part_o, float* part_lse, int32_t* status, void* stream);
+
+/* Attention of the same queries over tokens kept unquantised in fp16 (the
+ * sink prefix and the recent window of the three-region cache policy,
+ * blockgtq/unaccelerated.py:163-244; the reference has no packed-path kernel
+ * for it).  q is the ORIGINAL query (no permutation/rotation), element
+ * (b,hq,d) at q + b*q_sb + hq*q_sh + d.  Buffer slot j of (b,h) is at
+ * k_buf + b*kb_sb + h*kb_sh + j*128 (fp16).  Slots [0, n_sink_tokens) hold the
+ * sink; the recent tokens sit in a ring of ring_size slots that starts at slot
+ * sink_cap: recent token i is in slot sink_cap + (ring_first + i) % ring_size,
+ * i < n_ring_tokens.
+ * Writes one more partial per (b,hq): buf_o (n_batch, n_q, 128) fp32 in the
+ * ORIGINAL V basis, buf_lse (n_batch, n_q) fp32 (-inf when there are no tokens). */
+int bgtq_buffer_attn(const void* q, int64_t q_sb, int64_t q_sh,
+                     const void* k_buf, const void* v_buf, int64_t kb_sb, int64_t kb_sh,
+                     int32_t n_sink_tokens, int32_t n_ring_tokens, int32_t sink_cap,
+                     int32_t ring_first, int32_t ring_size,
+                     int32_t n_batch, int32_t n_q, int32_t n_kv,
+                     float scale, float* buf_o, float* buf_lse, void* stream);
+
+/* Merge split partials, undo V's rotation, fold in the fp16-buffer partial.
+ *
+ * Replaces _split_t_merge_kernel (blockgtq/kernels/fused_packed_attention.py:59-103),
+ * the per-split V un-rotation (:875-882) and the return_lse log-sum-exp
+ * (:1856-1860).  Splits with lse = -inf are skipped; a row whose every partial
+ * is empty yields zeros and lse = -inf.
+ *   merged_rot = sum_c a_c part_o[c] / sum_c a_c           (a_c = exp(lse_c - max))
+ *   packed_out = merged_rot @ v_rot[h]   if v_rot != NULL  (v_rot: (n_kv,128,128) fp32 = R)
+ *   out        = LSE-weighted mix of packed_out and buf_o  (buf_o may be NULL)
+ * out: fp16 (n_batch, n_q, 128) at out + b*o_sb + hq*o_sh; out_f32 / lse_out
+ * optional: the un-rounded result (n_batch, n_q, 128) and total LSE (n_batch, n_q),
+ * the pair another rank needs to continue the merge. */
+int bgtq_combine(const float* part_o, const float* part_lse, int32_t n_splits,
+                 const float* v_rot, const float* buf_o, const float* buf_lse,
+                 int32_t n_batch, int32_t n_q, int32_t n_kv,
+                 void* out, int64_t o_sb, int64_t o_sh,
+                 float* out_f32, float* lse_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BGTQ_H_ */

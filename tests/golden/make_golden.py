@@ -2,7 +2,9 @@
 
 Run once, in a container where the reference checkout is available:
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/reference
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/reference [manager]
+
+(a second argument regenerates only ``manager.npz``, which has its own random seed)
 
 The reference's Triton kernels are executed by Triton's CPU interpreter
 (``tl.dot`` is a float32 ``np.matmul`` there), so the vectors are the
@@ -227,7 +229,7 @@ def dump_manager(gen, T0=150, B=2, n_kv=2, gqa=2, steps=2):
     v0 = torch.randn(B, n_kv, T0, HD, generator=gen).half()
     mgr._encode_kv(0, k0, v0, 0, T0)
     mgr.seq_len = T0
-    rec = {"cal_q": cq.numpy(), "cal_k": ck.numpy(), "k0": k0.numpy(), "v0": v0.numpy()}
+    rec = {"cal_q": cq.numpy(), "cal_k": ck.numpy(), "k_init": k0.numpy(), "v_init": v0.numpy()}
     for s in range(steps):
         q = (torch.randn(B, n_q, 1, HD, generator=gen) * 2).half()
         kn = torch.stack([torch.stack([synth_head(gen, 1, 1)[1] for _ in range(n_kv)])
@@ -247,15 +249,18 @@ def dump_manager(gen, T0=150, B=2, n_kv=2, gqa=2, steps=2):
 
 
 def main():
+    only = sys.argv[2] if len(sys.argv) > 2 else None
     gen = torch.Generator().manual_seed(20240607)
     for case in CASES:
+        if only is not None:
+            break
         qs, cal = make_quantizers(case, 2, gen)
         dump_tables(case, qs, cal)
         dump_encode(case, qs, gen)
         if case in ("a3_1to6", "a3_1to8", "a2_1to8", "a4_rt1"):
             dump_decode(case, qs, gen)
         print("done", case, flush=True)
-    dump_manager(gen)
+    dump_manager(torch.Generator().manual_seed(777))
     print("done manager")
 
 

@@ -1,0 +1,126 @@
+"""CPU tests of the host layer: calibration tables against the reference's, the allocator, the C-ABI
+library (loads, exports every declared symbol, plans build) and the manager's bookkeeping."""
+import ctypes as C
+import hashlib
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import CASES, HD, ROOT, load, tables_for
+from blockgtq_b200 import _lib, calib, greedy_bit_allocation
+
+
+def _sha(t):
+    return hashlib.sha256(np.ascontiguousarray(t.numpy()).tobytes()).hexdigest()
+
+
+@pytest.mark.parametrize("case", list(CASES))
+def test_tables_equal_reference(case):
+    g = load("tables_" + case)
+    avg, mn, mx, rt, vb = CASES[case]
+    for h in range(2):
+        p = f"h{h}_"
+        alloc = greedy_bit_allocation(torch.from_numpy(g[p + "scores"]), int(64 * avg), mn, mx)
+        assert np.array_equal(alloc.numpy(), g[p + "alloc"])
+        kt, vt = tables_for(case, h, g)
+        assert np.array_equal(kt.head_perm.numpy(), g[p + "head_perm"])
+        assert np.array_equal(kt.group_of.numpy(), g[p + "group_of"])
+        assert np.array_equal(kt.pos_centroids.numpy(), g[p + "pos_centroids"])
+        assert np.array_equal(kt.pos_boundaries.numpy(), g[p + "pos_boundaries"])
+        assert np.array_equal(kt.code_lut.numpy(), g[p + "code_lut"])
+        assert np.array_equal(kt.pos_to_cb.numpy(), g[p + "pos_to_cb"])
+        assert np.array_equal(kt.lut_offsets.numpy(), g[p + "lut_off"])
+        assert np.array_equal(kt.lut_inv_scales.numpy(), g[p + "lut_inv"])
+        assert np.array_equal(np.array(kt.segments), g[p + "segments"])
+        assert np.array_equal(kt.codebook_flat.numpy(), g[p + "codebook"])
+        assert kt.total_packed_bytes == int(g[p + "total_packed_bytes"])
+        pm = kt.pack_meta
+        assert [pm["nopack_start"], pm["nopack_len"], pm["nopack_off"]] == g[p + "nopack"].tolist()
+        assert _sha(kt.block_rot.T.contiguous()) == str(g[p + "rot_t_sha"])
+        assert _sha(vt.rotation) == str(g[p + "v_rot_sha"])
+        assert np.array_equal(vt.centroids.numpy(), g[p + "v_cents"])
+        assert np.array_equal(vt.boundaries.numpy(), g[p + "v_bounds"])
+    # end to end from calibration data (head 0 carries it)
+    kt = calib.build_k_tables(torch.from_numpy(g["h0_cal_q"]).float(), torch.from_numpy(g["h0_cal_k"]).float(),
+                              head_dim=HD, avg_bits=avg, rotation_threshold=rt, min_bits=mn, max_bits=mx)
+    assert np.array_equal(kt.scores.numpy(), g["h0_scores"])
+    assert np.array_equal(kt.bit_allocation.numpy(), g["h0_alloc"])
+    assert np.array_equal(kt.block_rot.T.contiguous().numpy(), g["h0_rot_t"])
+
+
+def test_allocator_edges():
+    s = torch.tensor([1.0, 1.0, 4.0, 0.0])
+    assert greedy_bit_allocation(s, 4, 1, 8).tolist() == [1, 1, 1, 1]          # budget == floor
+    assert greedy_bit_allocation(s, 2, 1, 8).tolist() == [1, 1, 1, 1]          # budget below floor
+    assert greedy_bit_allocation(s, 5, 1, 8).tolist() == [1, 1, 2, 1]
+    assert greedy_bit_allocation(s, 6, 1, 8).tolist() == [2, 1, 2, 1]          # tie -> first index
+    assert greedy_bit_allocation(s, 100, 1, 3).tolist() == [3, 3, 3, 1]        # zero score never gets a bit
+    assert greedy_bit_allocation(torch.ones(3), 100, 2, 4).tolist() == [4, 4, 4]
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "bgtq.h")).read()
+    declared = sorted(set(re.findall(r"^(?:int|const char\*)\s+(bgtq_\w+)\s*\(", header, flags=re.M)))
+    assert declared, "no declarations found"
+    lib = _lib.lib()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in bgtq.h but not exported"
+    assert sorted(_lib.exported_symbols()) == declared
+    assert lib.bgtq_abi_version() == 1
+    assert lib.bgtq_desc_size() == C.sizeof(_lib.HeadDesc)
+    assert lib.bgtq_error_string(-3) == b"misaligned pointer"
+
+
+@pytest.mark.parametrize("case", list(CASES))
+def test_descriptor_and_decode_plan(case):
+    """Descriptor packing and the host-side decode plan (no GPU work)."""
+    from blockgtq_b200.layer import _fill_desc
+    descs = (_lib.HeadDesc * 2)()
+    for h in range(2):
+        kt, vt = tables_for(case, h)
+        _fill_desc(descs[h], kt, vt)
+        d = descs[h]
+        assert d.n_seg == kt.n_groups and d.k_row_bytes == kt.total_packed_bytes
+        assert [d.seg_bw[i] for i in range(d.n_seg)] == kt.group_bits
+        assert bytes(d.head_perm) == bytes(kt.head_perm.numpy().astype(np.uint8))
+        assert bytes(d.code_lut[d.n_seg - 1]) == bytes(kt.code_lut[d.n_seg - 1].numpy())
+    for flags in (0, 1, 2, 3):
+        plan = _lib.DecodePlan()
+        assert _lib.lib().bgtq_decode_plan(C.byref(descs), 2, flags, C.byref(plan)) == 0
+    assert _lib.lib().bgtq_decode_plan(C.byref(descs), 9, 0, C.byref(plan)) == -5
+    assert _lib.lib().bgtq_decode_plan(None, 2, 0, C.byref(plan)) == -1
+    descs[0].seg_len[0] = 3
+    assert _lib.lib().bgtq_decode_plan(C.byref(descs), 2, 0, C.byref(plan)) == -1
+
+
+def test_entry_points_reject_bad_arguments_without_a_gpu():
+    L = _lib.lib()
+    assert L.bgtq_decode(None, None, None, None, 0, 0, 0, None, 0, 0, 0, None, 0, 0, 0, None, 0, 0, 0,
+                         1, 8, 2, 0, 10, 1, 0.1, None, None, None, None) == -1
+    assert L.bgtq_combine(None, None, 1, None, None, None, 1, 8, 2, None, 0, 0, None, None, None) == -1
+    assert L.bgtq_encode(None, None, None, None, 0, 0, 0, None, 0, 0, 0, 1, 2, 1, 0, None, 0, 0, 0, 8,
+                         None, 0, 0, 0, 1, None, 0, 0, 0, None, 0, 0, 0, None, None, 0, None) == -1
+
+
+def test_operators_refuse_cpu_tensors():
+    from blockgtq_b200.layer import LayerTables, rotate_q
+    kt, vt = tables_for("a3_1to8", 0)
+    lt = LayerTables([kt], [vt], "cpu")
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        rotate_q(lt, torch.zeros(1, 4, HD, dtype=torch.float16))
+
+
+def test_manager_region_bookkeeping():
+    from blockgtq_b200 import BlockGTQKVManager
+    from oracle.bgtq_oracle import three_region_plan
+    for n_sink, window, bs in [(4, 128, 1), (0, 16, 4), (2, 5, 3)]:
+        m = BlockGTQKVManager(1, 8, 2, HD, 1024, n_sink=n_sink, recent_window=window, block_size=bs, device="cpu")
+        for seq in range(0, 400, 7):
+            assert m._region_sizes(seq) == three_region_plan(seq, n_sink, window, bs)
+            _s, f, r = m._region_sizes(seq)
+            assert r <= window + bs - 1 or seq - n_sink < window + bs
+    m = BlockGTQKVManager(1, 8, 2, HD, 1024, device="cpu")
+    assert m._region_sizes(77) == (0, 77, 0)

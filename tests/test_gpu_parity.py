@@ -1,0 +1,228 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the reference's golden vectors
+and the NumPy oracle.  Integer outputs must be bit-exact (except where the oracle proves the fp32
+coordinate sits on a bin edge); attention outputs within max-abs 2e-3 (fp16 out, fp32 accumulate)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import CASES, HD, load, oracle_meta, synth_head, tables_for
+from oracle import bgtq_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ATOL = 2e-3
+
+
+def _layer(case, n_kv=2):
+    from blockgtq_b200.layer import LayerTables
+    gt = load("tables_" + case)
+    tabs = [tables_for(case, h, gt) for h in range(n_kv)]
+    return LayerTables([t[0] for t in tabs], [t[1] for t in tabs], DEV), tabs
+
+
+def _quantizers(case, n_kv=2):
+    from blockgtq_b200 import BlockGTQQuantizer
+    gt = load("tables_" + case)
+    avg, mn, mx, rt, vb = CASES[case]
+    qs = []
+    for h in range(n_kv):
+        z = BlockGTQQuantizer(HD, avg_bits=avg, rotation_threshold=rt, min_bits=mn, max_bits=mx, device=DEV)
+        z.calibrate(None, None, bit_allocation=torch.from_numpy(gt[f"h{h}_alloc"]))
+        z.init_v_quantizer(v_bits=vb, seed=42 + h)
+        qs.append(z)
+    return qs
+
+
+@pytest.mark.parametrize("case", list(CASES))
+def test_encode_matches_reference(case):
+    from blockgtq_b200 import (build_batched_encode_args, compress_k_mixed_batched, compress_k_packed_batched,
+                               compress_v_nibble4_batched, compress_v_packed_batched)
+    ge = load("encode_" + case)
+    qs = _quantizers(case)
+    ba = build_batched_encode_args(qs, device=DEV)
+    k = torch.from_numpy(ge["k"]).to(DEV)
+    v = torch.from_numpy(ge["v"]).to(DEV)
+    kp, kn = compress_k_packed_batched(k, ba)
+    vp, vn = compress_v_packed_batched(v, ba)
+    km, knc = compress_k_mixed_batched(k, ba)
+    vnib, vn2 = compress_v_nibble4_batched(v, ba)
+    torch.cuda.synchronize()
+    assert kp.shape == ge["k_packed"].shape and kn.shape == ge["k_norms"].shape
+    assert vp.shape == ge["v_packed"].shape and km.shape == ge["k_mixed"].shape
+    gt = load("tables_" + case)
+    for h in range(2):
+        kt, vt = tables_for(case, h, gt)
+        meta = oracle_meta(kt, vt, int(ge["max_tpb"]))
+        orc = O.encode_k(ge["k"][h], meta, dtype=np.float64)
+        codes = qs[h].compress(k[h])[0].cpu().numpy()
+        bad = codes != ge["k_codes"][h]
+        # any disagreement must sit on a bin edge of the float64 coordinate
+        assert not (bad & ~orc["fragile"]).any(), f"{case} head {h}: {bad.sum()} code mismatches off bin edges"
+        assert bad.mean() < 1e-3
+        if not bad.any():
+            assert np.array_equal(kp[h].cpu().numpy(), ge["k_packed"][h])
+            assert np.array_equal(km[h].cpu().numpy(), ge["k_mixed"][h])
+        else:   # the bytes must still be the exact packing of the codes the kernel chose
+            assert np.array_equal(kp[h].cpu().numpy(), O.pack_k(codes, kt.segments, int(ge["max_tpb"])))
+        np.testing.assert_allclose(kn[h].cpu().numpy(), ge["k_norms"][h], rtol=2e-6, atol=1e-30)
+        np.testing.assert_allclose(knc[h].cpu().numpy(), ge["k_norms_corrected"][h], rtol=5e-6, atol=1e-30)
+        vo = O.encode_v(ge["v"][h], meta, dtype=np.float64)
+        vcodes = qs[h].compress_v(v[h])[0].cpu().numpy()
+        vbad = vcodes != ge["v_codes_torch"][h]
+        assert not (vbad & ~vo["fragile"]).any()
+        if not vbad.any():
+            assert np.array_equal(vp[h].cpu().numpy(), ge["v_packed"][h])
+            assert np.array_equal(vnib[h].cpu().numpy(), ge["v_nibble"][h])
+        dn = np.abs(vn[h].cpu().numpy().astype(np.float32) - ge["v_norms"][h].astype(np.float32))
+        assert (dn <= np.abs(ge["v_norms"][h].astype(np.float32)) * 1e-3).all()      # <= 1 fp16 ulp
+        assert (dn > 0).mean() < 0.02
+
+
+@pytest.mark.parametrize("case", ["a3_1to6", "a3_1to8", "a2_1to8", "a4_rt1"])
+@pytest.mark.parametrize("n_splits", [None, 1, 8])
+def test_decode_matches_reference(case, n_splits):
+    from blockgtq_b200.layer import combine, decode, rotate_q
+    gd = load("decode_" + case)
+    lt, tabs = _layer(case)
+    q = torch.from_numpy(gd["q"]).to(DEV)
+    q_rot = rotate_q(lt, q)
+    torch.cuda.synchronize()
+    d = (q_rot.cpu().numpy().astype(np.float32) - gd["q_rot"][:, :, 0].astype(np.float32))
+    assert np.abs(d).max() <= np.abs(gd["q_rot"]).max() * 1e-3 and (d != 0).mean() < 0.01
+    kp, kn = torch.from_numpy(gd["k_packed"]).to(DEV), torch.from_numpy(gd["k_norms"]).to(DEV)
+    vp, vn = torch.from_numpy(gd["v_packed"]).to(DEV), torch.from_numpy(gd["v_norms"]).to(DEV)
+    T = kp.shape[2]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ns = int(gd["t_splits"]) if n_splits is None else n_splits
+    po, pl = decode(lt, torch.from_numpy(gd["q_rot"][:, :, 0]).to(DEV).contiguous(), kp, kn, vp, vn, 0, T,
+                    n_splits=ns, status=status)
+    out, _, lse = combine(po, pl, lt.n_kv, v_rot=lt.v_rot, want_lse=True)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    err = np.abs(out.cpu().numpy().astype(np.float64) - gd["out"][:, :, 0].astype(np.float64)).max()
+    assert err <= ATOL, f"max-abs {err}"
+    np.testing.assert_allclose(lse.cpu().numpy(), gd["lse"], atol=5e-4, rtol=0)
+
+
+def test_operator_api_matches_reference():
+    """fused_blockgtq_decode_attention with the reference's per-head calling convention."""
+    from blockgtq_b200 import fused_blockgtq_decode_attention
+    case = "a3_1to8"
+    gd = load("decode_" + case)
+    qs = _quantizers(case)
+    gqa = int(gd["gqa"])
+    for h in range(2):
+        ka = qs[h].build_kernel_args()
+        sl = slice(h * gqa, (h + 1) * gqa)
+        o, lse = fused_blockgtq_decode_attention(
+            torch.from_numpy(gd["q_rot"][:, sl]).to(DEV),
+            torch.from_numpy(gd["k_packed"][:, h:h + 1]).to(DEV), torch.from_numpy(gd["k_norms"][:, h:h + 1]).to(DEV),
+            ka["codebook_flat"], ka["lut_offset"], ka["norm_group"], ka["segments_b"],
+            torch.from_numpy(gd["v_packed"][:, h:h + 1]).to(DEV), torch.from_numpy(gd["v_norms"][:, h:h + 1]).to(DEV),
+            qs[h].v_lut, scale=1.0 / HD ** 0.5, t_splits=int(gd["t_splits"]), v_bits=qs[h].v_bits,
+            v_rotation=qs[h]._v_rot, return_lse=True)
+        assert o.shape == (2, gqa, 1, HD) and o.dtype == torch.float16
+        err = np.abs(o.cpu().numpy().astype(np.float64) - gd["out"][:, sl].astype(np.float64)).max()
+        assert err <= ATOL
+
+
+def test_manager_matches_reference():
+    from blockgtq_b200 import BlockGTQKVManager
+    g = load("manager")
+    B, n_kv, T0, _ = g["k_init"].shape
+    n_q = g["q0"].shape[1]
+    mgr = BlockGTQKVManager(1, n_q, n_kv, HD, max_seq_len=T0 + 4, batch_size=B, k_avg_bits=3.0, v_bits=3, device=DEV)
+    mgr.calibrate(0, torch.from_numpy(g["cal_q"]), torch.from_numpy(g["cal_k"]))
+    assert np.array_equal(np.stack([mgr.quantizers[0][h].bit_allocation.numpy() for h in range(n_kv)]), g["alloc"])
+    mgr._encode_kv(0, torch.from_numpy(g["k_init"]).to(DEV), torch.from_numpy(g["v_init"]).to(DEV), 0, T0)
+    mgr.seq_len = T0
+    for s in range(2):
+        out = mgr.append_and_attend(0, torch.from_numpy(g[f"q{s}"]).to(DEV), torch.from_numpy(g[f"k{s}"]).to(DEV),
+                                    torch.from_numpy(g[f"v{s}"]).to(DEV))
+        mgr.increment_seq_len()
+        err = np.abs(out.cpu().numpy().astype(np.float64) - g[f"out{s}"].astype(np.float64)).max()
+        assert out.shape == g[f"out{s}"].shape and err <= ATOL, f"step {s}: {err}"
+    mgr.check_status()
+    T = mgr.seq_len
+    same = (mgr._k_packed[:, :, :, :T].cpu().numpy() == g["k_packed"]).mean()
+    assert same > 0.9999, same
+    assert (mgr._v_packed[:, :, :, :T].cpu().numpy() == g["v_packed"]).mean() > 0.9999
+    kn = mgr._k_norms[:, :, :, :T].float().cpu().numpy()
+    assert (np.abs(kn - g["k_norms"].astype(np.float32)) <= np.abs(kn) * 1e-3).all()
+
+
+@pytest.mark.parametrize("T", [0, 1, 63, 64, 65, 129, 1000])
+def test_decode_ragged_lengths_vs_oracle(T):
+    """Edge lengths around the 64-token tile, empty cache included, against the float64 oracle."""
+    from blockgtq_b200.layer import combine, decode, encode, rotate_q
+    case = "a3_1to8"
+    lt, tabs = _layer(case)
+    gen = torch.Generator().manual_seed(100 + T)
+    B, n_kv, gqa = 2, 2, 4
+    cap = max(T, 1) + 7
+    ks, qs_ = [], []
+    for b in range(B):
+        hk, hq = [], []
+        for h in range(n_kv):
+            q, k = synth_head(gen, T + 1, gqa)
+            hk.append(k[:T] if T else k[:0])
+            hq.append(q.reshape(gqa, T + 1, HD)[:, T])
+        ks.append(torch.stack(hk))
+        qs_.append(torch.cat(hq))
+    k = torch.stack(ks).to(DEV)
+    q = torch.stack(qs_).to(DEV)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half().to(DEV)
+    kp = torch.zeros(B, n_kv, cap, lt.max_tpb, dtype=torch.uint8, device=DEV)
+    kn = torch.zeros(B, n_kv, cap, lt.max_ng, dtype=torch.float16, device=DEV)
+    vp = torch.zeros(B, n_kv, cap, lt.vpb, dtype=torch.uint8, device=DEV)
+    vn = torch.zeros(B, n_kv, cap, dtype=torch.float16, device=DEV)
+    if T:
+        encode(lt, k, v, 0, kp, kn, vp, vn)
+    q_rot = rotate_q(lt, q)
+    po, pl = decode(lt, q_rot, kp, kn, vp, vn, 0, T, n_splits=3)
+    out, o32, lse = combine(po, pl, n_kv, v_rot=lt.v_rot, want_f32=True, want_lse=True)
+    torch.cuda.synchronize()
+    for b in range(B):
+        for h in range(n_kv):
+            meta = oracle_meta(*tabs[h])
+            sl = slice(h * gqa, (h + 1) * gqa)
+            ro, rl = O.attend_packed(q_rot[b, sl].cpu().numpy(), kp[b, h, :T].cpu().numpy(), kn[b, h, :T].cpu().numpy(),
+                                     vp[b, h, :T].cpu().numpy(), vn[b, h, :T].cpu().numpy(), meta, 1 / HD ** 0.5)
+            assert np.abs(o32[b, sl].cpu().numpy() - ro).max() <= ATOL
+            if T:
+                np.testing.assert_allclose(lse[b, sl].cpu().numpy(), rl, atol=5e-4)
+            else:
+                assert np.isneginf(lse[b, sl].cpu().numpy()).all() and (out[b, sl] == 0).all()
+
+
+def test_combine_and_buffer_vs_oracle():
+    from blockgtq_b200.layer import buffer_attn, combine
+    gen = torch.Generator().manual_seed(5)
+    B, n_kv, gqa, S = 2, 2, 4, 5
+    n_q = n_kv * gqa
+    po = torch.randn(B, n_q, S, HD, generator=gen)
+    pl = torch.randn(B, n_q, S, generator=gen) * 3
+    pl[0, 0, :] = float("-inf")              # a row with every split empty
+    pl[1, 2, 1] = float("-inf")
+    out, o32, lse = combine(po.to(DEV), pl.to(DEV), n_kv, want_f32=True, want_lse=True)
+    torch.cuda.synchronize()
+    ro, rl = O.combine(po.numpy().transpose(2, 0, 1, 3).reshape(S, B * n_q, HD), pl.numpy().transpose(2, 0, 1).reshape(S, -1))
+    np.testing.assert_allclose(o32.cpu().numpy().reshape(-1, HD), ro, atol=2e-6)
+    np.testing.assert_allclose(lse.cpu().numpy().reshape(-1), rl, atol=2e-6)
+    assert not torch.isnan(out).any()
+    # fp16 buffer attention with a wrapped ring
+    n_sink, ring, cap = 4, 9, 13
+    kb = (torch.randn(B, n_kv, cap, HD, generator=gen) * 2).half()
+    vb = torch.randn(B, n_kv, cap, HD, generator=gen).half()
+    q = torch.randn(B, n_q, HD, generator=gen).half()
+    first, n_ring = 6, 7
+    bo, bl = buffer_attn(q.to(DEV), kb.to(DEV), vb.to(DEV), n_kv, 0.0884, n_sink_tokens=n_sink,
+                         n_ring_tokens=n_ring, sink_cap=n_sink, ring_first=first, ring_size=ring)
+    torch.cuda.synchronize()
+    slots = list(range(n_sink)) + [n_sink + (first + i) % ring for i in range(n_ring)]
+    for b in range(B):
+        for hq in range(n_q):
+            h = hq // gqa
+            ro, rl = O.attend_fp16(q[b, hq:hq + 1].numpy(), kb[b, h, slots].numpy(), vb[b, h, slots].numpy(), 0.0884)
+            np.testing.assert_allclose(bo[b, hq].cpu().numpy(), ro[0], atol=2e-5)
+            np.testing.assert_allclose(bl[b, hq].cpu().numpy(), rl[0], atol=2e-5)
