@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the packed-cache decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" is one decode step of the hot path over every layer of the workload:
+rotate_q -> encode/append the new token's K,V -> fused packed decode -> combine, for all batch
+entries and KV heads (the model's projections and MLP are not part of this path).  Rank 0 prints
+one JSON line.  With N > 1 (torchrun, one rank per GPU) every rank holds its own batch slice
+(weak scaling, no collective on the data path); the time is the max over ranks.
+
+--impl reference times the CPU restatement of the same path (oracle/) on the host cores.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+HD = 128
+
+WORKLOADS = {
+    # BASELINE.json configs[1]: Qwen2.5-3B shape, K3V3 packed cache, batch 8 per GPU, context 32768
+    "qwen2.5-3b_k3v3_b8_t32768": dict(layers=36, n_q=16, n_kv=2, batch=8, ctx=32768, k_bits=3.0, v_bits=3,
+                                      theta=1e6, n_sink=0, window=0),
+    # BASELINE.json configs[2]: Llama-3.1-8B shape, K2V2, batch 32, context 16384, fp16 sink 4 + window 128
+    "llama3.1-8b_k2v2_b32_t16384_sink4_win128": dict(layers=32, n_q=32, n_kv=8, batch=32, ctx=16384, k_bits=2.0,
+                                                     v_bits=2, theta=5e5, n_sink=4, window=128),
+    # small variant of configs[1] for quick runs and profiler captures
+    "qwen2.5-3b_k3v3_b8_t32768_4layers": dict(layers=4, n_q=16, n_kv=2, batch=8, ctx=32768, k_bits=3.0, v_bits=3,
+                                              theta=1e6, n_sink=0, window=0),
+}
+DEFAULT = "qwen2.5-3b_k3v3_b8_t32768"
+
+
+def synth_keys(gen, shape_bt, theta, device):
+    """Post-RoPE keys (B, T, 128) fp16: N(0,1) x lognormal(0,1) per-RoPE-block scale, two blocks x8."""
+    B, T = shape_bt
+    s = torch.exp(torch.randn(HD // 2, generator=gen, device=device))
+    s[torch.randperm(HD // 2, generator=gen, device=device)[:2]] *= 8
+    scale = torch.cat([s, s])
+    x = (torch.randn(B, T, HD, generator=gen, device=device) * scale).half().float()
+    half = HD // 2
+    inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float32, device=device) / half))
+    ang = torch.arange(T, device=device).float()[:, None] * inv[None, :]
+    c, sn = torch.cos(ang), torch.sin(ang)
+    a, b = x[..., :half], x[..., half:]
+    return torch.cat([a * c - b * sn, a * sn + b * c], dim=-1).half()
+
+
+def build_manager(w, device, seed, extra_tokens):
+    """Calibrate every (layer, head) on 2048 synthetic tokens, then bulk-encode the context."""
+    from blockgtq_b200 import BlockGTQKVManager
+    gen = torch.Generator(device=device).manual_seed(seed)
+    L, n_q, n_kv, B, T = w["layers"], w["n_q"], w["n_kv"], w["batch"], w["ctx"]
+    gqa = n_q // n_kv
+    mgr = BlockGTQKVManager(L, n_q, n_kv, HD, max_seq_len=T + extra_tokens, batch_size=B, k_avg_bits=w["k_bits"],
+                            v_bits=w["v_bits"], device=device, n_sink=w["n_sink"], recent_window=w["window"])
+    for li in range(L):
+        ck = torch.stack([synth_keys(gen, (1, 2048), w["theta"], device)[0] for _ in range(n_kv)])
+        cq = torch.stack([synth_keys(gen, (gqa, 2048), w["theta"], device).reshape(-1, HD) for _ in range(n_kv)])
+        mgr.calibrate(li, cq.float(), ck.float())
+    chunk = 8192
+    for li in range(L):
+        for t in range(0, T, chunk):
+            n = min(chunk, T - t)
+            k = torch.stack([synth_keys(gen, (B, n), w["theta"], device) for _ in range(n_kv)], dim=1)
+            v = torch.randn(B, n_kv, n, HD, generator=gen, device=device).half()
+            mgr._append_tokens(li, k, v, t)
+    mgr.seq_len = T
+    torch.cuda.synchronize()
+    return mgr, gen
+
+
+def clocks_sampler(device_index):
+    q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    try:
+        return subprocess.Popen(["nvidia-smi", "-i", str(device_index), f"--query-gpu={q}",
+                                 "--format=csv,noheader,nounits", "-lms", "100"],
+                                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    except OSError:
+        return None
+
+
+def clocks_summary(proc):
+    if proc is None:
+        return None
+    proc.terminate()
+    try:
+        out = proc.communicate(timeout=5)[0]
+    except Exception:
+        return None
+    sm, mx, reasons = [], 0, set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    for line in out.strip().splitlines():
+        f = [x.strip() for x in line.split(",")]
+        if len(f) < 6:
+            continue
+        try:
+            sm.append(float(f[0]))
+            mx = max(mx, float(f[1]))
+        except ValueError:
+            continue
+        for n, v in zip(names, f[2:6]):
+            if v.lower().startswith("active"):
+                reasons.add(n)
+    if not sm:
+        return None
+    return {"sm_mhz": statistics.median(sm), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_decode_sample(w, seed=0, t_sample=None):
+    """Time the oracle's decode (unpack + dequantise + attention) for ONE (batch, KV-head) pair of one
+    layer on the host cores; returns (seconds per pair, description)."""
+    from helpers import oracle_meta
+    from blockgtq_b200 import calib
+    from oracle import bgtq_oracle as O
+    T = t_sample or w["ctx"]
+    gqa = w["n_q"] // w["n_kv"]
+    gen = torch.Generator().manual_seed(seed)
+    ck = synth_keys(gen, (1, 2048), w["theta"], "cpu")[0]
+    cq = synth_keys(gen, (gqa, 2048), w["theta"], "cpu").reshape(-1, HD)
+    kt = calib.build_k_tables(cq.float(), ck.float(), head_dim=HD, avg_bits=w["k_bits"])
+    vt = calib.build_v_tables(HD, w["v_bits"], 42)
+    meta = oracle_meta(kt, vt)
+    k = synth_keys(gen, (1, T), w["theta"], "cpu")[0].numpy()
+    v = torch.randn(T, HD, generator=gen).half().numpy()
+    ek = O.encode_k_packed(k, meta)
+    ev = O.encode_v(v, meta)
+    kn16 = ek["norms"].astype(np.float16)
+    q = O.rotate_q(synth_keys(gen, (gqa, 1), w["theta"], "cpu")[:, 0].numpy(), meta)
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        O.attend_packed(q, ek["packed"], kn16, ev["packed"], ev["norms"], meta, 1 / math.sqrt(HD))
+        reps += 1
+        if time.perf_counter() - t0 > 8.0 or reps >= 5:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    return dt, f"1 (batch, KV-head) pair of 1 layer, {T} cached tokens, oracle decode x{reps}"
+
+
+def run_reference(args, w, name, rank, world):
+    """CPU arm: the oracle port of the decode path on the host cores, bounded sample."""
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    per_pair = []
+    for i in range(max(1, min(args.steps, 3))):
+        dt, sample = cpu_decode_sample(w, seed=i)
+        per_pair.append(dt)
+    dt = statistics.median(per_pair)
+    pairs = w["layers"] * w["batch"] * w["n_kv"]
+    step_s = dt * pairs
+    val = w["batch"] / step_s
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "note": "CPU restatement of the packed decode path; step time = sample time x "
+                   f"{pairs} (layers x batch x KV heads), cache encode not timed"},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--n-splits", type=int, default=None)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, w, args.workload, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the package has no CPU path); use --impl reference for the CPU arm")
+    import torch.distributed as dist
+    from blockgtq_b200 import _lib
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    K, W = args.steps, args.warmup
+    n_steps_total = 2 * (K + W) + min(K, 5) + 2
+    mgr, gen = build_manager(w, dev, seed=1234 + rank, extra_tokens=n_steps_total + 16)
+    L, B, n_q, n_kv = w["layers"], w["batch"], w["n_q"], w["n_kv"]
+    # one decode token per layer per step, pre-generated; device copies for `value`, pinned host for `e2e`
+    qs = (torch.randn(n_steps_total, L, B, n_q, 1, HD, generator=gen, device=dev) * 2).half()
+    ks = torch.stack([torch.stack([synth_keys(gen, (B * n_kv, 1), w["theta"], dev).reshape(B, n_kv, 1, HD)
+                                   for _ in range(L)]) for _ in range(n_steps_total)])
+    vs = torch.randn(n_steps_total, L, B, n_kv, 1, HD, generator=gen, device=dev).half()
+    hq, hk, hv = qs.cpu().pin_memory(), ks.cpu().pin_memory(), vs.cpu().pin_memory()
+    hout = torch.empty(L, B, n_q, 1, HD, dtype=torch.float16).pin_memory()
+    step_no = [0]
+
+    def step_device():
+        s = step_no[0]
+        for li in range(L):
+            mgr.append_and_attend(li, qs[s, li], ks[s, li], vs[s, li], n_splits=args.n_splits)
+        mgr.increment_seq_len()
+        step_no[0] += 1
+
+    def step_e2e():
+        s = step_no[0]
+        for li in range(L):
+            q = hq[s, li].to(dev, non_blocking=True)
+            k = hk[s, li].to(dev, non_blocking=True)
+            v = hv[s, li].to(dev, non_blocking=True)
+            out = mgr.append_and_attend(li, q, k, v, n_splits=args.n_splits)
+            hout[li].copy_(out, non_blocking=True)
+        mgr.increment_seq_len()
+        torch.cuda.synchronize()
+        step_no[0] += 1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(W):
+        step_device()
+    sampler = clocks_sampler(local) if rank == 0 else None
+    launches0 = _lib.launches
+    ms_total = timed(step_device, K)
+    launches = _lib.launches - launches0
+    clocks = clocks_summary(sampler)
+    live_bytes = mgr.live_bytes_per_step()
+
+    # per-launch duration of the dominant kernel (fused decode), CUDA events on the launching stream
+    import blockgtq_b200.packed_kv_manager as pkm
+    real_decode = pkm.decode
+    ev = []
+
+    def timed_decode(*a, **kw):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r = real_decode(*a, **kw)
+        e1.record()
+        ev.append((e0, e1))
+        return r
+
+    pkm.decode = timed_decode
+    n_prof = min(K, 5)
+    for _ in range(n_prof):
+        step_device()
+    torch.cuda.synchronize()
+    pkm.decode = real_decode
+    dec_ms = [a.elapsed_time(b) for a, b in ev]
+    dec_avg_ms = sum(dec_ms) / len(dec_ms)
+    sink, n_packed, n_rec = mgr._region_sizes(mgr.seq_len)
+    packed_bytes_per_launch = (live_bytes - (sink + n_rec) * HD * 4 * n_kv * B * L) / L
+
+    for _ in range(W):
+        step_e2e()
+    ms_e2e = timed(step_e2e, K)
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        achieved = packed_bytes_per_launch / (dec_avg_ms * 1e-3) / 1e9
+        ms_step = ms_total / K
+        line = {
+            "metric": "decode_tokens_per_s", "value": world * B / (ms_step * 1e-3), "unit": "tok/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "layers": L, "batch_per_gpu": B, "n_q": n_q, "n_kv": n_kv,
+                       "context": w["ctx"], "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"],
+                       "fp16_sink": w["n_sink"], "fp16_window": w["window"], "parallelism": f"batch x{world}",
+                       "l2": "inputs larger than L2 (packed cache bytes per step >> 126 MB), no flush",
+                       "decode_us_per_layer": dec_avg_ms * 1e3, "step_hbm_gbs": live_bytes / (ms_step * 1e-3) / 1e9,
+                       "step_frac_of_8tbs": live_bytes / (ms_step * 1e-3) / 8e12},
+            "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback",
+                         "algorithmic_bytes_per_launch": packed_bytes_per_launch, "launch_ms": dec_avg_ms},
+            "e2e": {"value": world * B / (ms_e2e / K * 1e-3), "unit": "tok/s",
+                    "h2d_bytes_per_step": int(L * (hq[0, 0].numel() + hk[0, 0].numel() + hv[0, 0].numel()) * 2),
+                    "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": ms_e2e / K},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            dt, sample = cpu_decode_sample(w)
+            pairs = L * B * n_kv
+            line["cpu_baseline"] = {"value": B / (dt * pairs), "unit": "tok/s", "cores": cores, "kind": "port",
+                                    "sample": sample + f"; step time = sample x {pairs}"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
