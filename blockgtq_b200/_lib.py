@@ -40,7 +40,7 @@ class HeadDesc(C.Structure):
 
 
 class DecodePlan(C.Structure):
-    _fields_ = [("opaque", C.c_uint8 * 3072)]
+    _fields_ = [("opaque", C.c_uint8 * 4096)]
 
 
 _i32, _i64, _f32, _vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p

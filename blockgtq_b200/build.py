@@ -14,7 +14,7 @@ import sys
 
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
-LIB = os.path.join(PKG, "libbgtq.so")
+LIB = os.environ.get("BGTQ_LIB") or os.path.join(PKG, "libbgtq.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
@@ -49,7 +49,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in sources():
         obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
         cmd = [nvcc] + [f for f in NVCC_FLAGS if f != "--use_fast_math=false"] + \
-            (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+            (["-Xptxas", "-v"] if verbose else []) + os.environ.get("BGTQ_NVCC_EXTRA", "").split() + \
+            ["-c", src, "-o", obj]
         procs.append((obj, cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)))
     objs = []
     for obj, cmd, p in procs:

@@ -14,6 +14,10 @@
 //     so the GQA group (<= 8 query heads) is the N dimension of m16n8k16 and no
 //     tile row is padding.  Softmax state is fp32 and per warp; warps are
 //     merged once at the end of the CTA.
+//   * the four lanes of a quad share a token; each owns a contiguous run of
+//     every K segment's codes, so one unaligned 32-bit shared load feeds several
+//     k-tiles (see bgtq_plan.h).  Because 64-token tiles advance every array by
+//     a multiple of 16 bytes, all byte phases are per-CTA constants.
 //   * rounding points follow the reference kernel
 //     (blockgtq/kernels/fused_packed_attention.py:770-873): fp32 logits,
 //     p rounded to fp16 for the PV product while the denominator uses fp32 p,
@@ -24,11 +28,17 @@
 namespace bgtq {
 namespace {
 
-constexpr int kTileTok = 64;
-constexpr int kConsumerWarps = 4;
+constexpr int kTileTok = 256;      // tokens per CTA tile
+constexpr int kWarpTok = 32;       // tokens per consumer warp and tile (two 16-token MMA row tiles)
+constexpr int kConsumerWarps = 8;
 constexpr int kThreads = 32 * (kConsumerWarps + 1);
-constexpr int kStages = 4;
+constexpr int kStages = 2;
 constexpr int kMergeStride = 132;  // floats per query row in the end-of-CTA merge buffer
+// shared-memory layout (byte offsets from the start of dynamic shared memory)
+// [barriers | codebook staging | per-step uniform params | per-step per-lane params | tables | stages]
+constexpr uint32_t kOffCbk = 128, kOffStepU = 1280, kOffStepL = kOffStepU + kMaxSteps * 16;
+constexpr uint32_t kOffLut = 12288;  // multiple of kLutTableBytes: table bases can be OR-ed into offsets
+static_assert(kOffStepL + kMaxSteps * 32 * 16 <= kOffLut && kOffLut % kLutTableBytes == 0, "layout");
 
 struct DecParams {
     const BgtqHeadDesc* desc;
@@ -45,33 +55,51 @@ struct DecParams {
     float* part_o;
     float* part_lse;
     int32_t* status;
-    uint32_t lut_off, stage_off, stage_bytes, off_kn, off_v, off_vn;  // shared-memory layout
+    uint32_t stage_off, stage_bytes, off_kn, off_v, off_vn;  // shared-memory layout
     DecPlanDev plan;
 };
 
-template <int VB>
-struct VBits;
-template <>
-struct VBits<1> { using T = uint32_t; static constexpr uint32_t M = 0x55555555u; };
-template <>
-struct VBits<2> { using T = uint32_t; static constexpr uint32_t M = 0x33333333u; };
-template <>
-struct VBits<3> { using T = uint64_t; static constexpr uint64_t M = 0x00001C71C71C71C7ull; };
-template <>
-struct VBits<4> { using T = uint64_t; static constexpr uint64_t M = 0x0F0F0F0F0F0F0F0Full; };
+// V unpack parameters per stored width: mask of the even-indexed codes of one
+// 32-bit group, groups per 16 codes, lane replication of the table.
+template <int VB> struct VCfg;
+template <> struct VCfg<1> { static constexpr uint32_t M = 0x5555u, GROUPS = 1, REP_SHIFT = 5; };
+template <> struct VCfg<2> { static constexpr uint32_t M = 0x33333333u, GROUPS = 1, REP_SHIFT = 5; };
+template <> struct VCfg<3> { static constexpr uint32_t M = 0x001C71C7u, GROUPS = 2, REP_SHIFT = 4; };
+template <> struct VCfg<4> { static constexpr uint32_t M = 0x0F0F0F0Fu, GROUPS = 2, REP_SHIFT = 2; };
 
+__device__ __forceinline__ uint32_t ld32(const uint8_t* sm, uint32_t off) {
+    return *reinterpret_cast<const uint32_t*>(sm + off);
+}
+__device__ __forceinline__ uint32_t ld16(const uint8_t* sm, uint32_t off) {
+    return *reinterpret_cast<const uint16_t*>(sm + off);
+}
+__device__ __forceinline__ uint32_t rotl32(uint32_t x, uint32_t n) { return __funnelshift_l(x, x, n); }
+
+// 16 codes of one token (bits [bit, bit + 16*VB) past word-aligned offset `row_al`) as one or two
+// 32-bit groups of 8 codes.
 template <int VB>
-__device__ __forceinline__ typename VBits<VB>::T load_v16(uint32_t row, uint32_t bitpos) {
+__device__ __forceinline__ void load_v16(const uint8_t* sm, uint32_t row_al, uint32_t bit, uint32_t (&g)[2]) {
+    const uint32_t wa = row_al + ((bit >> 5) << 2);
+    const uint32_t w0 = ld32(sm, wa), w1 = ld32(sm, wa + 4);
+    const uint32_t sh = bit & 31u;
     if constexpr (VB <= 2) {
-        return lds_bits32(row, bitpos);
+        g[0] = __funnelshift_r(w0, w1, sh);
+        g[1] = 0;
     } else {
-        uint2 w = lds_bits64(row, bitpos);
-        return (static_cast<uint64_t>(w.y) << 32) | w.x;
+        const uint32_t w2 = (sh + 16u * VB > 64u) ? ld32(sm, wa + 8) : 0u;
+        const uint32_t lo = __funnelshift_r(w0, w1, sh), hi = __funnelshift_r(w1, w2, sh);
+        if constexpr (VB == 3) {
+            g[0] = lo & 0xFFFFFFu;
+            g[1] = __funnelshift_r(lo, hi, 24) & 0xFFFFFFu;
+        } else {
+            g[0] = lo;
+            g[1] = hi;
+        }
     }
 }
 
 template <int VB>
-__global__ void __launch_bounds__(kThreads) decode_kernel(const __grid_constant__ DecParams P) {
+__global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_constant__ DecParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -84,9 +112,15 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const __grid_constant_
 
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kStages;
-    uint16_t* cbk = reinterpret_cast<uint16_t*>(smem + 128);  // 512 K entries + 16 V entries
-    uint32_t* lut = reinterpret_cast<uint32_t*>(smem + P.lut_off);
-    uint8_t* stages = smem + P.stage_off;
+    uint16_t* cbk = reinterpret_cast<uint16_t*>(smem + kOffCbk);  // 512 K entries + 16 V entries
+    // Per k-tile parameters, expanded once so the inner loop does no decoding:
+    //   stepu[s]       = {flags | norm byte offset << 8, rotate 0, rotate 1, index mask}      (same for all lanes)
+    //   stepl[s][lane] = {Qrot fragment lo, hi, table offset incl. lane column, unit bit offset of this lane}
+    uint4* stepu = reinterpret_cast<uint4*>(smem + kOffStepU);
+    uint4* stepl = reinterpret_cast<uint4*>(smem + kOffStepL);
+    constexpr uint32_t lut_rel = kOffLut;
+    uint32_t* lut = reinterpret_cast<uint32_t*>(smem + lut_rel);
+    const uint8_t* sm = smem;
 
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
@@ -99,24 +133,48 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const __grid_constant_
         const BgtqHeadDesc& d = P.desc[h];
         for (int i = tid; i < 528; i += kThreads) cbk[i] = i < 512 ? d.codebook[i] : d.v_lut[i - 512];
     }
+    if (warp == 0) {   // lane (r, j): query r, this lane's 4 codes of every k-tile
+        const int r = lane >> 2, j = lane & 3;
+        const bool q_ok = r < P.gqa;
+        const __half* qrow = P.q_rot + ((size_t)b * P.n_q + (size_t)h * P.gqa + (q_ok ? r : 0)) * kHD;
+        for (int s = 0; s < hp.n_steps; ++s) {
+            const DecStep stp = hp.steps[s];
+            const int d0 = (int)(stp.q & 0xFFu) + j * (int)((stp.q >> 8) & 0x3Fu);
+            const int end = (int)((stp.q >> 14) & 0xFFu);
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(qrow + d0);
+            const uint32_t esh = (stp.b >> 10) & 31u;
+            uint4 v;
+            v.x = (q_ok && d0 < end) ? __ldg(src) : 0u;
+            v.y = (q_ok && d0 + 2 < end) ? __ldg(src + 1) : 0u;
+            v.z = lut_rel + (stp.c >> 16) + (((uint32_t)lane << 2) & ((1u << esh) - 1u));
+            v.w = (stp.a & 0xFFFu) + j * ((stp.a >> 12) & 0x3FFu);
+            stepl[s * 32 + lane] = v;
+            if (lane == 0) {
+                const uint32_t pair = (stp.a >> 23) & 1u;
+                const uint32_t fl = ((stp.a >> 22) & 1u) | (pair << 1) | (((stp.a >> 24) & 1u) << 2);
+                stepu[s] = make_uint4(fl | ((2u * ((stp.b >> 15) & 15u)) << 8), pair ? (stp.b & 31u) : esh,
+                                      (stp.b >> 5) & 31u, stp.c & 0xFFFFu);
+            }
+        }
+    }
     __syncthreads();
     // Expand codebooks into lane-replicated fp16x2 tables.
     for (int s = 0; s < hp.n_seg; ++s) {
         const DecSegTbl tb = hp.seg[s];
-        const uint32_t cm = (1u << tb.bw) - 1u, sm = (1u << tb.sbits) - 1u;
+        const uint32_t cm = (1u << tb.bw) - 1u, smk = (1u << tb.sbits) - 1u;
         for (uint32_t i = tid; i < tb.n_words; i += kThreads) {
             const uint32_t e = i >> tb.rep_shift;
             uint32_t v;
-            if (tb.pair) v = cbk[tb.cb_off + ((e & sm) & cm)] | (uint32_t(cbk[tb.cb_off + ((e >> tb.sbits) & cm)]) << 16);
+            if (tb.pair) v = cbk[tb.cb_off + ((e & smk) & cm)] | (uint32_t(cbk[tb.cb_off + ((e >> tb.sbits) & cm)]) << 16);
             else v = cbk[tb.cb_off + (e & cm)];
             lut[tb.word_off + i] = v;
         }
     }
     {
-        const uint32_t vm = (1u << P.plan.v_bits) - 1u, sm = (1u << VB) - 1u;
+        const uint32_t vm = (1u << P.plan.v_bits) - 1u, smk = (1u << VB) - 1u;
         for (uint32_t i = tid; i < (uint32_t)P.plan.v_n_words; i += kThreads) {
-            const uint32_t e = i >> P.plan.v_rep_shift;
-            lut[hp.v_word_off + i] = cbk[512 + ((e & sm) & vm)] | (uint32_t(cbk[512 + ((e >> VB) & vm)]) << 16);
+            const uint32_t e = i >> VCfg<VB>::REP_SHIFT;
+            lut[hp.v_word_off + i] = cbk[512 + ((e & smk) & vm)] | (uint32_t(cbk[512 + ((e >> VB) & vm)]) << 16);
         }
     }
     __syncthreads();
@@ -137,7 +195,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const __grid_constant_
                 }
                 const int t = t0 + it * kTileTok;
                 const int nt = min(kTileTok, t1 - t);
-                uint8_t* sb = stages + (size_t)st * P.stage_bytes;
+                uint8_t* sb = smem + P.stage_off + (size_t)st * P.stage_bytes;
                 const uint8_t* src[4] = {P.kp + bh_kp + (size_t)t * P.kp_st, P.kn + bh_kn + (size_t)t * P.kn_st,
                                          P.vp + bh_vp + (size_t)t * P.vp_st, P.vn + bh_vn + (size_t)t * P.vn_st};
                 const uint32_t len[4] = {(uint32_t)nt * P.kp_st, (uint32_t)nt * P.kn_st, (uint32_t)nt * P.vp_st,
@@ -161,98 +219,107 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const __grid_constant_
 
     // -------------------------------- consumers --------------------------------
     const int r = lane >> 2, j = lane & 3;
-    const bool q_ok = r < P.gqa;
-    uint32_t qf[kMaxSteps][2];
-    {
-        const __half* qrow = P.q_rot + ((size_t)b * P.n_q + (size_t)h * P.gqa + (q_ok ? r : 0)) * kHD;
-#pragma unroll
-        for (int s = 0; s < kMaxSteps; ++s) {
-            qf[s][0] = qf[s][1] = 0u;
-            if (s < hp.n_steps) {
-                const uint32_t c = hp.steps[s].c;
-                const int qb = c & 0xFF, nv = (c >> 8) & 0xFF;
-                const uint32_t* src = reinterpret_cast<const uint32_t*>(qrow + qb + 4 * j);
-                if (q_ok && 4 * j < nv) qf[s][0] = __ldg(src);
-                if (q_ok && 4 * j + 2 < nv) qf[s][1] = __ldg(src + 1);
-            }
-        }
-    }
-
     float O[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    const uint32_t lut_a = smem_u32(lut);
-    const uint32_t vtbl = lut_a + (hp.v_word_off << 2) + ((lane << 2) & ((4u << P.plan.v_rep_shift) - 1u));
-    const uint32_t v_sh = P.plan.v_rep_shift + 2;
-    bool dead = false;
+    // Per-CTA byte phases of the four arrays inside a stage (tiles advance every array by a multiple
+    // of 16 bytes), and this lane's row offsets.  K side: tokens tok0 + 8 i, i = 0..3.
+    const uint32_t k_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.kp) + bh_kp + (size_t)t0 * P.kp_st) & 15u);
+    const uint32_t kn_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.kn) + bh_kn + (size_t)t0 * P.kn_st) & 15u);
+    const uint32_t v_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.vp) + bh_vp + (size_t)t0 * P.vp_st) & 15u);
+    const uint32_t vn_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.vn) + bh_vn + (size_t)t0 * P.vn_st) & 15u);
+    const int tok0 = warp * kWarpTok + r;
+    const uint32_t k_off = k_pre + tok0 * P.kp_st;
+    const uint32_t k_row_al = k_off & ~3u, k_p0 = (k_off & 3u) << 3;
+    const uint32_t k_row8 = 8u * P.kp_st, kn_row8 = 8u * P.kn_st;
+    const uint32_t kn_row = P.off_kn + kn_pre + tok0 * P.kn_st;
+    const int tkv = warp * kWarpTok + 2 * j;     // V side, row tile u: tokens tkv + 16u + {0, 1, 8, 9}
+    const uint32_t v_off = P.off_v + v_pre + tkv * P.vp_st;
+    const uint32_t vn_row = P.off_vn + vn_pre + tkv * P.vn_st;
+
+    const uint32_t lane4 = (uint32_t)lane << 2;
+    constexpr uint32_t kVSh = VCfg<VB>::REP_SHIFT + 2;
+    const uint32_t vtbl = lut_rel + (hp.v_word_off << 2) + (lane4 & ((1u << kVSh) - 1u));
+    const int n_steps = hp.n_steps;
 
     for (int it = 0; it < n_tiles; ++it) {
         const int st = it % kStages, use = it / kStages;
         if (!mbar_wait_bounded(&full[st], use & 1)) {
             if (P.status && lane == 0) atomicExch(P.status, kStatusWaitTimeout);
-            dead = true;
             break;
         }
-        const int t = t0 + it * kTileTok;
-        const int nt = min(kTileTok, t1 - t);
-        const uint32_t sb = smem_u32(stages + (size_t)st * P.stage_bytes);
-        const uint32_t k_a = sb + (uint32_t)((reinterpret_cast<uintptr_t>(P.kp) + bh_kp + (size_t)t * P.kp_st) & 15u);
-        const uint32_t kn_a =
-            sb + P.off_kn + (uint32_t)((reinterpret_cast<uintptr_t>(P.kn) + bh_kn + (size_t)t * P.kn_st) & 15u);
-        const uint32_t v_a =
-            sb + P.off_v + (uint32_t)((reinterpret_cast<uintptr_t>(P.vp) + bh_vp + (size_t)t * P.vp_st) & 15u);
-        const uint32_t vn_a =
-            sb + P.off_vn + (uint32_t)((reinterpret_cast<uintptr_t>(P.vn) + bh_vn + (size_t)t * P.vn_st) & 15u);
+        const int nt = min(kTileTok, t1 - (t0 + it * kTileTok));
+        const uint32_t sb = P.stage_off + st * P.stage_bytes;
 
-        if (warp * 16 < nt) {
-            // ---------------- S^T = Khat . Qrot^T ----------------
-            const int tokA = warp * 16 + r, tokB = tokA + 8;
-            const bool okA = tokA < nt, okB = tokB < nt;
-            const uint32_t rowA = k_a + tokA * P.kp_st, rowB = k_a + tokB * P.kp_st;
-            const uint32_t nrA = kn_a + tokA * P.kn_st, nrB = kn_a + tokB * P.kn_st;
-            float S[4] = {0.f, 0.f, 0.f, 0.f};
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (warp * kWarpTok < nt) {
+            // ---------------- S^T = Khat . Qrot^T for two 16-token row tiles ----------------
+            float S[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            uint32_t cur[4] = {0u, 0u, 0u, 0u};
+            float nrm[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t rowK = sb + k_row_al, rowN = sb + kn_row;
+#pragma unroll 2
+            for (int s = 0; s < n_steps; ++s) {
+                const uint4 su = stepu[s];
+                const uint4 sl = stepl[s * 32 + lane];
+                if (su.x & 1u) {            // next unit: 32 bits of this lane's run, four tokens
+                    const uint32_t pbit = k_p0 + sl.w;
+                    const uint32_t wa = rowK + ((pbit >> 5) << 2);
 #pragma unroll
-            for (int s = 0; s < kMaxSteps; ++s) {
-                if (s < hp.n_steps) {
-                    const uint32_t sa = hp.steps[s].a, sbw = hp.steps[s].b;
-                    const uint32_t sbits = sbw & 15u, rsh = ((sbw >> 4) & 15u) + 2u;
-                    const uint32_t mask = sbw >> 16;
-                    const uint32_t bitpos = (sa & 0xFFFFu) + j * 4u * sbits;
-                    const uint32_t tb = lut_a + ((sa >> 16) << 2) + ((lane << 2) & ((1u << rsh) - 1u));
-                    const uint32_t FA = lds_bits32(rowA, bitpos), FB = lds_bits32(rowB, bitpos);
-                    uint32_t a[4];
-                    if (sbw & 0x100u) {  // two codes per lookup
-                        const uint32_t w2 = 2u * sbits;
-                        a[0] = lds32(tb + ((FA & mask) << rsh));
-                        a[1] = lds32(tb + ((FB & mask) << rsh));
-                        a[2] = lds32(tb + (((FA >> w2) & mask) << rsh));
-                        a[3] = lds32(tb + (((FB >> w2) & mask) << rsh));
-                    } else {             // raw bytes, one code per lookup
-                        a[0] = lds32(tb + ((FA & mask) << rsh)) | (lds32(tb + (((FA >> 8) & mask) << rsh)) << 16);
-                        a[1] = lds32(tb + ((FB & mask) << rsh)) | (lds32(tb + (((FB >> 8) & mask) << rsh)) << 16);
-                        a[2] = lds32(tb + (((FA >> 16) & mask) << rsh)) | (lds32(tb + (((FA >> 24) & mask) << rsh)) << 16);
-                        a[3] = lds32(tb + (((FB >> 16) & mask) << rsh)) | (lds32(tb + (((FB >> 24) & mask) << rsh)) << 16);
+                    for (int i = 0; i < 4; ++i)
+                        cur[i] = __funnelshift_r(ld32(sm, wa + i * k_row8), ld32(sm, wa + i * k_row8 + 4), pbit);
+                }
+                if (su.x & 4u) {            // new segment: its per-token norms
+                    const uint32_t sg = rowN + (su.x >> 8);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        nrm[i] = __half2float(__ushort_as_half((unsigned short)ld16(sm, sg + i * kn_row8)));
+                }
+                const uint32_t mask = su.w, tb = sl.z;
+                uint32_t lo[4], hi[4];   // fp16x2 of codes (0,1) and (2,3) of this k-tile, per token
+                if (su.x & 2u) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        lo[i] = ld32(sm, (rotl32(cur[i], su.y) & mask) | tb);
+                        hi[i] = ld32(sm, (rotl32(cur[i], su.z) & mask) | tb);
                     }
-                    mma_16816(acc, a, qf[s]);
-                    if (sbw & 0x200u) {  // last k-tile of the segment: apply its norm
-                        const uint32_t sg = (sbw >> 12) & 15u;
-                        const float nA = __half2float(__ushort_as_half((unsigned short)lds16(nrA + 2u * sg)));
-                        const float nB = __half2float(__ushort_as_half((unsigned short)lds16(nrB + 2u * sg)));
-                        S[0] = fmaf(nA, acc[0], S[0]);
-                        S[1] = fmaf(nA, acc[1], S[1]);
-                        S[2] = fmaf(nB, acc[2], S[2]);
-                        S[3] = fmaf(nB, acc[3], S[3]);
-                        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                } else {                   // raw bytes, one code per lookup; su.y = log2(entry stride)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t c0 = ld32(sm, (rotl32(cur[i], su.y) & mask) | tb);
+                        const uint32_t c1 = ld32(sm, (rotl32(cur[i], su.y + 24u) & mask) | tb);
+                        const uint32_t c2 = ld32(sm, (rotl32(cur[i], su.y + 16u) & mask) | tb);
+                        const uint32_t c3 = ld32(sm, (rotl32(cur[i], su.y + 8u) & mask) | tb);
+                        lo[i] = c0 | (c1 << 16);
+                        hi[i] = c2 | (c3 << 16);
                     }
                 }
+                const uint32_t bq[2] = {sl.x, sl.y};
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const uint32_t a[4] = {lo[2 * u], lo[2 * u + 1], hi[2 * u], hi[2 * u + 1]};
+                    float acc[4];
+                    mma_16816_z(acc, a, bq);
+                    S[u][0] = fmaf(nrm[2 * u], acc[0], S[u][0]);
+                    S[u][1] = fmaf(nrm[2 * u], acc[1], S[u][1]);
+                    S[u][2] = fmaf(nrm[2 * u + 1], acc[2], S[u][2]);
+                    S[u][3] = fmaf(nrm[2 * u + 1], acc[3], S[u][3]);
+                }
             }
-            // ---------------- online softmax (log2 domain) ----------------
-            float s0 = okA ? S[0] * P.scale_log2 : -INFINITY, s1 = okA ? S[1] * P.scale_log2 : -INFINITY;
-            float s2 = okB ? S[2] * P.scale_log2 : -INFINITY, s3 = okB ? S[3] * P.scale_log2 : -INFINITY;
-            float x0 = fmaxf(s0, s2), x1 = fmaxf(s1, s3);
+            // ---------------- online softmax (log2 domain) over the 32 tokens ----------------
+            float sv[2][4];
+            float x0 = -INFINITY, x1 = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const bool okA = tok0 + 16 * u < nt, okB = tok0 + 16 * u + 8 < nt;
+                sv[u][0] = okA ? S[u][0] * P.scale_log2 : -INFINITY;
+                sv[u][1] = okA ? S[u][1] * P.scale_log2 : -INFINITY;
+                sv[u][2] = okB ? S[u][2] * P.scale_log2 : -INFINITY;
+                sv[u][3] = okB ? S[u][3] * P.scale_log2 : -INFINITY;
+                x0 = fmaxf(x0, fmaxf(sv[u][0], sv[u][2]));
+                x1 = fmaxf(x1, fmaxf(sv[u][1], sv[u][3]));
+            }
 #pragma unroll
             for (int o = 4; o < 32; o <<= 1) {
                 x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, o));
@@ -261,11 +328,21 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const __grid_constant_
             const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
             const float z0 = n0 == -INFINITY ? 0.f : n0, z1 = n1 == -INFINITY ? 0.f : n1;
             const float al0 = exp2f(m0 - z0), al1 = exp2f(m1 - z1);
-            const float p0 = exp2f(s0 - z0), p1 = exp2f(s1 - z1), p2 = exp2f(s2 - z0), p3 = exp2f(s3 - z1);
-            l0 = fmaf(l0, al0, p0 + p2);
-            l1 = fmaf(l1, al1, p1 + p3);
             m0 = n0;
             m1 = n1;
+            uint32_t pf[2][2];
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const float p0 = exp2f(sv[u][0] - z0), p1 = exp2f(sv[u][1] - z1);
+                const float p2 = exp2f(sv[u][2] - z0), p3 = exp2f(sv[u][3] - z1);
+                ps0 += p0 + p2;
+                ps1 += p1 + p3;
+                pf[u][0] = movmatrix_trans(pack_half2(p0, p1));
+                pf[u][1] = movmatrix_trans(pack_half2(p2, p3));
+            }
+            l0 = fmaf(l0, al0, ps0);
+            l1 = fmaf(l1, al1, ps1);
             if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -275,39 +352,49 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const __grid_constant_
                     O[i][3] *= al1;
                 }
             }
-            uint32_t pf[2];
-            pf[0] = movmatrix_trans(pack_half2(p0, p1));
-            pf[1] = movmatrix_trans(pack_half2(p2, p3));
 
             // ---------------- O^T += Vhat^T . P^T ----------------
-            const int tk = warp * 16 + 2 * j;
-            using VT = typename VBits<VB>::T;
-            const uint32_t vbit = 16u * VB * r;
-            const VT fA = load_v16<VB>(v_a + (tk + 0) * P.vp_st, vbit), fB = load_v16<VB>(v_a + (tk + 1) * P.vp_st, vbit);
-            const VT fC = load_v16<VB>(v_a + (tk + 8) * P.vp_st, vbit), fD = load_v16<VB>(v_a + (tk + 9) * P.vp_st, vbit);
-            constexpr VT M = VBits<VB>::M;
-            const VT xab = (fA & M) | ((fB & M) << VB), yab = ((fA >> VB) & M) | (fB & (M << VB));
-            const VT xcd = (fC & M) | ((fD & M) << VB), ycd = ((fC >> VB) & M) | (fD & (M << VB));
-            const uint32_t hA = tk + 0 < nt ? lds16(vn_a + (tk + 0) * P.vn_st) : 0u;
-            const uint32_t hB = tk + 1 < nt ? lds16(vn_a + (tk + 1) * P.vn_st) : 0u;
-            const uint32_t hC = tk + 8 < nt ? lds16(vn_a + (tk + 8) * P.vn_st) : 0u;
-            const uint32_t hD = tk + 9 < nt ? lds16(vn_a + (tk + 9) * P.vn_st) : 0u;
-            const uint32_t nab = hA | (hB << 16), ncd = hC | (hD << 16);
-            constexpr uint32_t IM = (1u << (2 * VB)) - 1u;
+            // Row tile u, this lane: tokens tkv+16u+{0,1} (pair AB) and +{8,9} (pair CD); dims 16r .. 16r+15.
+            constexpr uint32_t M = VCfg<VB>::M, G = VCfg<VB>::GROUPS, FW = 2 * VB;
+            constexpr uint32_t IMS = ((1u << FW) - 1u) << kVSh;
+            constexpr int PER = 8 / G;   // k-tiles (dim pairs) per 32-bit group
 #pragma unroll
-            for (int mt = 0; mt < 8; ++mt) {
-                uint32_t a[4];
-                a[0] = hmul2_u32(lds32(vtbl + (((uint32_t)(xab >> (2 * VB * mt)) & IM) << v_sh)), nab);
-                a[1] = hmul2_u32(lds32(vtbl + (((uint32_t)(yab >> (2 * VB * mt)) & IM) << v_sh)), nab);
-                a[2] = hmul2_u32(lds32(vtbl + (((uint32_t)(xcd >> (2 * VB * mt)) & IM) << v_sh)), ncd);
-                a[3] = hmul2_u32(lds32(vtbl + (((uint32_t)(ycd >> (2 * VB * mt)) & IM) << v_sh)), ncd);
-                mma_16816(O[mt], a, pf);
+            for (int u = 0; u < 2; ++u) {
+                uint32_t gA[2], gB[2], gC[2], gD[2];
+                const uint32_t rv = sb + v_off + 16u * u * P.vp_st;
+                const uint32_t base = rv & ~3u, bit = ((rv & 3u) << 3) + 16u * VB * r;
+                load_v16<VB>(sm, base, bit, gA);
+                load_v16<VB>(sm, base, bit + 8u * P.vp_st, gB);
+                load_v16<VB>(sm, base, bit + 64u * P.vp_st, gC);
+                load_v16<VB>(sm, base, bit + 72u * P.vp_st, gD);
+                const int tq = tkv + 16 * u;
+                const uint32_t rn = sb + vn_row + 16u * u * P.vn_st;
+                const uint32_t hA = tq + 0 < nt ? ld16(sm, rn) : 0u;
+                const uint32_t hB = tq + 1 < nt ? ld16(sm, rn + P.vn_st) : 0u;
+                const uint32_t hC = tq + 8 < nt ? ld16(sm, rn + 8 * P.vn_st) : 0u;
+                const uint32_t hD = tq + 9 < nt ? ld16(sm, rn + 9 * P.vn_st) : 0u;
+                const uint32_t nab = hA | (hB << 16), ncd = hC | (hD << 16);
+#pragma unroll
+                for (int g = 0; g < (int)G; ++g) {
+                    const uint32_t xab = (gA[g] & M) | ((gB[g] & M) << VB), yab = ((gA[g] >> VB) & M) | (gB[g] & (M << VB));
+                    const uint32_t xcd = (gC[g] & M) | ((gD[g] & M) << VB), ycd = ((gC[g] >> VB) & M) | (gD[g] & (M << VB));
+#pragma unroll
+                    for (int k = 0; k < PER; ++k) {
+                        // index pre-scaled by the entry stride: rotate so the field sits at bit kVSh
+                        const uint32_t rt = (32u + kVSh - FW * k) & 31u;
+                        uint32_t a[4];
+                        a[0] = hmul2_u32(ld32(sm, vtbl + (rotl32(xab, rt) & IMS)), nab);
+                        a[1] = hmul2_u32(ld32(sm, vtbl + (rotl32(yab, rt) & IMS)), nab);
+                        a[2] = hmul2_u32(ld32(sm, vtbl + (rotl32(xcd, rt) & IMS)), ncd);
+                        a[3] = hmul2_u32(ld32(sm, vtbl + (rotl32(ycd, rt) & IMS)), ncd);
+                        mma_16816(O[g * PER + k], a, pf[u]);
+                    }
+                }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[st]);
     }
-    (void)dead;
 
     // ---------------- merge the four warps, write the split's partial ----------------
 #pragma unroll
@@ -336,7 +423,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const __grid_constant_
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32));
     {
-        const int q = tid >> 4, d0 = (tid & 15) * 8;
+        const int q = tid >> 5, d0 = (tid & 31) * 4;
         if (q < P.gqa) {
             float mx = -INFINITY;
 #pragma unroll
@@ -348,39 +435,32 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const __grid_constant_
                 den = fmaf(ml[w * 8 + q], wgt[w], den);
             }
             const float inv = den > 0.f ? 1.f / den : 0.f;
-            float o[8];
+            float o[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < 4; ++i) {
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < kConsumerWarps; ++w) v = fmaf(mo[(w * 8 + q) * kMergeStride + d0 + i], wgt[w], v);
                 o[i] = v * inv;
             }
             const size_t row = ((size_t)b * P.n_q + (size_t)h * P.gqa + q) * P.n_splits + split;
-            float4* dst = reinterpret_cast<float4*>(P.part_o + row * kHD + d0);
-            dst[0] = make_float4(o[0], o[1], o[2], o[3]);
-            dst[1] = make_float4(o[4], o[5], o[6], o[7]);
-            if ((tid & 15) == 0)
+            *reinterpret_cast<float4*>(P.part_o + row * kHD + d0) = make_float4(o[0], o[1], o[2], o[3]);
+            if ((tid & 31) == 0)
                 P.part_lse[row] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -INFINITY;
         }
     }
 }
 
-// Shared-memory size of the per-head table region: K tables + V table, but at
-// least the end-of-CTA merge buffer that reuses the same bytes.
-uint32_t lut_region_bytes(const DecPlanDev& pl) {
-    uint32_t w = 0;
-    for (int h = 0; h < pl.n_heads; ++h) w = max(w, (uint32_t)(pl.head[h].v_word_off + pl.v_n_words));
-    const uint32_t merge = (kConsumerWarps * 8 * kMergeStride + 2 * kConsumerWarps * 8) * 4;
-    return ((max(w * 4u, merge) + 127u) / 128u) * 128u;
-}
+constexpr uint32_t v_rep_shift_for(int vb) { return vb <= 2 ? 5 : (vb == 3 ? 4 : 2); }
+constexpr uint32_t kMergeBytes = (kConsumerWarps * 8 * kMergeStride + 2 * kConsumerWarps * 8) * 4;
 
 }  // namespace
 }  // namespace bgtq
 
 using namespace bgtq;
 
-extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const BgtqHeadDesc* desc_host, int32_t n_kv, int32_t flags, BgtqDecodePlan* out) {
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const BgtqHeadDesc* desc_host, int32_t n_kv,
+                                                                       int32_t flags, BgtqDecodePlan* out) {
     if (!desc_host || !out || n_kv < 1) return BGTQ_E_BADARG;
     if (n_kv > kMaxPlanHeads) return BGTQ_E_TOOBIG;
     static_assert(sizeof(DecPlanDev) <= sizeof(BgtqDecodePlan), "plan does not fit its public container");
@@ -391,84 +471,106 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const Bgt
     pl.v_bits = desc_host[0].v_bits;
     if (pl.v_bits < 1 || pl.v_bits > 4) return BGTQ_E_UNSUPPORTED;
     pl.v_sbits = (flags & BGTQ_DEC_V_NIBBLE) ? 4 : pl.v_bits;
-    {
-        const uint32_t entries = 1u << (2 * pl.v_sbits);
-        uint32_t rep = kLutTableBytes / 4 / entries;
-        rep = rep < 1 ? 1 : (rep > 32 ? 32 : rep);
-        pl.v_rep_shift = 31 - __builtin_clz(rep);
-        pl.v_n_words = entries << pl.v_rep_shift;
-    }
+    pl.v_rep_shift = v_rep_shift_for(pl.v_sbits);
+    pl.v_n_words = (1u << (2 * pl.v_sbits)) << pl.v_rep_shift;
+    uint32_t lut_words = 0;
     for (int h = 0; h < n_kv; ++h) {
         const BgtqHeadDesc& d = desc_host[h];
         if (d.v_bits != pl.v_bits) return BGTQ_E_UNSUPPORTED;
         if (d.n_seg < 1 || d.n_seg > BGTQ_MAX_SEGMENTS) return BGTQ_E_BADARG;
         DecHeadPlan& hp = pl.head[h];
         hp.n_seg = d.n_seg;
-        uint32_t word = 0;
-        int step = 0;
+        int sbits_of[BGTQ_MAX_SEGMENTS];
+        uint32_t bitbase_of[BGTQ_MAX_SEGMENTS];
         for (int s = 0; s < d.n_seg; ++s) {
             const int bw = d.seg_bw[s], len = d.seg_len[s], start = d.seg_start[s];
-            if (bw < 1 || bw > 8 || len < 2 || (len & 1) || start + len > kHD) return BGTQ_E_BADARG;
-            int sbits;
-            uint32_t bitbase;
+            if (bw < 1 || bw > 8 || len < 2 || (len & 1) || start < 0 || start + len > kHD) return BGTQ_E_BADARG;
             if (flags & BGTQ_DEC_K_MIXED) {
-                sbits = bw <= 4 ? 4 : 8;
-                bitbase = bw <= 4 ? start * 4u : 8u * (d.nopack_start / 2 + (start - d.nopack_start));
+                sbits_of[s] = bw <= 4 ? 4 : 8;
+                bitbase_of[s] = bw <= 4 ? start * 4u : 8u * (d.nopack_start / 2 + (start - d.nopack_start));
             } else {
-                sbits = bw <= 4 ? bw : 8;
-                bitbase = 8u * d.seg_pack_off[s];
+                sbits_of[s] = bw <= 4 ? bw : 8;
+                bitbase_of[s] = 8u * d.seg_pack_off[s];
             }
-            const bool pair = sbits <= 4;
-            const uint32_t entries = pair ? 1u << (2 * sbits) : 1u << bw;
+            const bool pair = sbits_of[s] <= 4;
+            const uint32_t entries = pair ? 1u << (2 * sbits_of[s]) : 1u << bw;
             uint32_t rep = kLutTableBytes / 4 / entries;
             rep = rep < 1 ? 1 : (rep > 32 ? 32 : rep);
             DecSegTbl& tb = hp.seg[s];
-            tb.word_off = word;
             tb.cb_off = d.seg_lut_off[s];
-            tb.sbits = sbits;
+            tb.sbits = sbits_of[s];
             tb.bw = bw;
             tb.rep_shift = 31 - __builtin_clz(rep);
             tb.pair = pair;
             tb.n_words = entries << tb.rep_shift;
+            if (tb.n_words * 4 > kLutTableBytes) return BGTQ_E_UNSUPPORTED;
+        }
+        // Place tables largest first: every size is a power of two, so each lands on a multiple of its size.
+        uint32_t word = 0;
+        bool placed[BGTQ_MAX_SEGMENTS] = {false};
+        for (int n = 0; n < d.n_seg; ++n) {
+            int best = -1;
+            for (int s = 0; s < d.n_seg; ++s)
+                if (!placed[s] && (best < 0 || hp.seg[s].n_words > hp.seg[best].n_words)) best = s;
+            placed[best] = true;
+            hp.seg[best].word_off = (uint16_t)word;
+            word += hp.seg[best].n_words;
+        }
+        hp.v_word_off = word;     // V table last; addressed by addition, no alignment needed
+        word += pl.v_n_words;
+        if (word * 4 > 0xFFFFu) return BGTQ_E_TOOBIG;
+        lut_words = word > lut_words ? word : lut_words;
+
+        int step = 0;
+        for (int s = 0; s < d.n_seg; ++s) {
+            const DecSegTbl& tb = hp.seg[s];
+            const int sbits = tb.sbits, len = d.seg_len[s], start = d.seg_start[s];
             const int n_kt = (len + 15) / 16;
+            const int q = 4 * n_kt;                                  // codes per lane in this segment
+            const int cap = sbits == 1 ? 32 : sbits == 2 ? 16 : sbits == 8 ? 4 : 8;   // codes per 32-bit unit
+            const uint32_t esh = tb.rep_shift + 2u;
+            const uint32_t mask = (tb.pair ? (1u << (2 * sbits)) - 1u : (1u << tb.bw) - 1u) << esh;
             for (int kt = 0; kt < n_kt; ++kt) {
                 if (step >= kMaxSteps) return BGTQ_E_UNSUPPORTED;
                 DecStep& stp = hp.steps[step++];
-                const uint32_t bb = bitbase + kt * 16u * sbits;
-                const uint32_t mask = pair ? (1u << (2 * sbits)) - 1u : (1u << bw) - 1u;
-                stp.a = (bb & 0xFFFFu) | (word << 16);
-                stp.b = sbits | (tb.rep_shift << 4) | (pair ? 0x100u : 0u) | (kt == n_kt - 1 ? 0x200u : 0u) |
-                        ((uint32_t)s << 12) | (mask << 16);
-                const int nv = len - 16 * kt < 16 ? len - 16 * kt : 16;
-                stp.c = (uint32_t)(start + 16 * kt) | ((uint32_t)nv << 8);
+                const int code0 = 4 * kt;                            // first code of this k-tile in the lane's run
+                const int unit = code0 / cap, in_unit = code0 % cap;
+                const uint32_t ubit = bitbase_of[s] + (uint32_t)(unit * cap * sbits);
+                const uint32_t jstride = (uint32_t)(q * sbits);
+                if (ubit + 3 * jstride + 32 > 0x1000u || jstride > 0x3FFu) return BGTQ_E_UNSUPPORTED;
+                const uint32_t ush = (uint32_t)(in_unit * sbits);
+                stp.a = ubit | (jstride << 12) | (in_unit == 0 ? 1u << 22 : 0u) | (tb.pair ? 1u << 23 : 0u) |
+                        (kt == 0 ? 1u << 24 : 0u);
+                const uint32_t r0 = (esh + 64u - ush) & 31u, r1 = (esh + 64u - ush - 2u * sbits) & 31u;
+                stp.b = r0 | (r1 << 5) | (esh << 10) | ((uint32_t)s << 15);
+                stp.c = mask | (((uint32_t)tb.word_off * 4u) << 16);
+                stp.q = (uint32_t)(start + code0) | ((uint32_t)q << 8) | ((uint32_t)(start + len) << 14);
             }
-            word += tb.n_words;
-            if (word > 0xFFFFu) return BGTQ_E_TOOBIG;
         }
         hp.n_steps = step;
-        hp.v_word_off = word;
     }
+    pl.lut_bytes = ((lut_words * 4u > kMergeBytes ? lut_words * 4u : kMergeBytes) + 127u) / 128u * 128u;
     memcpy(out, &pl, sizeof(pl));
     return BGTQ_OK;
 }
 
-extern "C" __attribute__((visibility("default"))) int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv, int32_t n_tokens) {
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv,
+                                                                                 int32_t n_tokens) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int pairs = n_batch * n_kv > 0 ? n_batch * n_kv : 1;
-    const int by_len = (n_tokens + 255) / 256;  // keep at least 256 tokens per split
+    const int by_len = (n_tokens + 511) / 512;  // keep at least 512 tokens per split
     int want = (2 * sms + pairs - 1) / pairs;   // two CTAs per SM
     if (want > by_len) want = by_len;
     return want < 1 ? 1 : want;
 }
 
-extern "C" __attribute__((visibility("default"))) int bgtq_decode(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot,
-                           const uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
-                           const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
-                           const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
-                           const void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st, int32_t n_batch,
-                           int32_t n_q, int32_t n_kv, int32_t t_begin, int32_t t_end, int32_t n_splits, float scale,
-                           float* part_o, float* part_lse, int32_t* status, void* stream) {
+extern "C" __attribute__((visibility("default"))) int bgtq_decode(
+    const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot, const uint8_t* k_packed,
+    int64_t kp_sb, int64_t kp_sh, int64_t kp_st, const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
+    const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, const void* v_norms, int64_t vn_sb,
+    int64_t vn_sh, int64_t vn_st, int32_t n_batch, int32_t n_q, int32_t n_kv, int32_t t_begin, int32_t t_end,
+    int32_t n_splits, float scale, float* part_o, float* part_lse, int32_t* status, void* stream) {
     if (!plan_host || !desc || !q_rot || !k_packed || !k_norms || !v_packed || !v_norms || !part_o || !part_lse)
         return BGTQ_E_BADARG;
     if (n_batch < 1 || n_kv < 1 || n_q < n_kv || n_q % n_kv || n_splits < 1 || t_end < t_begin || t_begin < 0)
@@ -481,6 +583,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode(const BgtqDeco
     if (kp_st < 1 || kp_st > 160 || vp_st < 1 || vp_st > 128 || kn_st < 1 || kn_st > 16 || vn_st < 1 || vn_st > 8)
         return BGTQ_E_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(part_o) & 15u) || (reinterpret_cast<uintptr_t>(q_rot) & 3u)) return BGTQ_E_ALIGN;
+    if (n_batch > 65535 || n_splits > 65535) return BGTQ_E_TOOBIG;
 
     P.desc = desc;
     P.q_rot = static_cast<const __half*>(q_rot);
@@ -502,13 +605,12 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode(const BgtqDeco
     P.part_o = part_o; P.part_lse = part_lse; P.status = status;
 
     auto r16 = [](uint32_t x) { return (x + 15u) & ~15u; };
-    // each array: 64 rows + 15 bytes of leading phase + rounding + slack for the bit-field over-read
+    // each array: one tile of rows + 15 bytes of leading phase + rounding + slack for the bit-field over-read
     const uint32_t sz_k = r16(kTileTok * P.kp_st + 48), sz_kn = r16(kTileTok * P.kn_st + 48);
     const uint32_t sz_v = r16(kTileTok * P.vp_st + 48), sz_vn = r16(kTileTok * P.vn_st + 48);
     P.off_kn = sz_k; P.off_v = sz_k + sz_kn; P.off_vn = sz_k + sz_kn + sz_v;
     P.stage_bytes = sz_k + sz_kn + sz_v + sz_vn;
-    P.lut_off = 128 + 1152;
-    P.stage_off = P.lut_off + lut_region_bytes(P.plan);
+    P.stage_off = kOffLut + P.plan.lut_bytes;
     const size_t smem = (size_t)P.stage_off + (size_t)kStages * P.stage_bytes;
     if (smem > 227 * 1024) return BGTQ_E_TOOBIG;
 

@@ -137,7 +137,7 @@ int bgtq_rotate_q(const BgtqHeadDesc* desc, const float* rot_k,
  * the head descriptors; at most 8 KV heads per plan (split wider layers into
  * groups of heads). */
 typedef struct BgtqDecodePlan {
-    uint8_t opaque[3072];
+    uint8_t opaque[4096];
 } BgtqDecodePlan;
 int bgtq_decode_plan(const BgtqHeadDesc* desc_host, int32_t n_kv, int32_t flags, BgtqDecodePlan* plan_host);
 
@@ -160,7 +160,7 @@ int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv, int32_t n_tokens);
  * (+ segment index), v_packed / v_norms likewise (v_norms: one fp16 per token).
  * Rows need no particular alignment.
  * Outputs, for split c of n_splits (tokens are cut into n_splits equal runs
- * rounded up to 64):
+ * rounded up to the 128-token tile):
  *   part_o  (n_batch, n_q, n_splits, 128) fp32  softmax-normalised partial
  *           output, still in V's rotated basis (16-byte aligned)
  *   part_lse(n_batch, n_q, n_splits)      fp32  log-sum-exp of the scaled
