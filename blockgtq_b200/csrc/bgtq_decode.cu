@@ -51,6 +51,8 @@ struct DecParams {
     int32_t kp_st, kn_st, vp_st, vn_st;  // bytes per token
     int32_t n_q, n_kv, gqa;
     int32_t t_begin, t_end, n_splits, chunk;
+    const int32_t* pos_dev;
+    int32_t pos_add;
     float scale_log2;
     float* part_o;
     float* part_lse;
@@ -105,8 +107,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const DecHeadPlan& hp = P.plan.head[h];
 
+    const int t_end = P.pos_dev ? min(P.t_end, *P.pos_dev + P.pos_add) : P.t_end;
     const int t0 = P.t_begin + split * P.chunk;
-    const int t1 = min(P.t_end, t0 + P.chunk);
+    const int t1 = min(t_end, t0 + P.chunk);
     const int n_tok = max(0, t1 - t0);
     const int n_tiles = (n_tok + kTileTok - 1) / kTileTok;
 
@@ -187,6 +190,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     if (warp == kConsumerWarps) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
+            const uint64_t pol = l2_evict_first_policy();
             for (int it = 0; it < n_tiles; ++it) {
                 const int st = it % kStages, use = it / kStages;
                 if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
@@ -210,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
                 mbar_arrive_expect_tx(&full[st], total);
                 for (int c = 0; c < 4; ++c) {
                     const uint8_t* al = src[c] - (reinterpret_cast<uintptr_t>(src[c]) & 15u);
-                    bulk_g2s(sb + dst[c], al, sz[c], &full[st]);
+                    bulk_g2s_hint(sb + dst[c], al, sz[c], &full[st], pol);
                 }
             }
         }
@@ -570,7 +574,8 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode(
     int64_t kp_sb, int64_t kp_sh, int64_t kp_st, const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
     const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, const void* v_norms, int64_t vn_sb,
     int64_t vn_sh, int64_t vn_st, int32_t n_batch, int32_t n_q, int32_t n_kv, int32_t t_begin, int32_t t_end,
-    int32_t n_splits, float scale, float* part_o, float* part_lse, int32_t* status, void* stream) {
+    int32_t n_splits, float scale, float* part_o, float* part_lse, int32_t* status, const int32_t* pos_dev,
+    int32_t pos_add, void* stream) {
     if (!plan_host || !desc || !q_rot || !k_packed || !k_norms || !v_packed || !v_norms || !part_o || !part_lse)
         return BGTQ_E_BADARG;
     if (n_batch < 1 || n_kv < 1 || n_q < n_kv || n_q % n_kv || n_splits < 1 || t_end < t_begin || t_begin < 0)
@@ -603,6 +608,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode(
     P.chunk = chunk < kTileTok ? kTileTok : chunk;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.part_o = part_o; P.part_lse = part_lse; P.status = status;
+    P.pos_dev = pos_dev; P.pos_add = pos_add;
 
     auto r16 = [](uint32_t x) { return (x + 15u) & ~15u; };
     // each array: one tile of rows + 15 bytes of leading phase + rounding + slack for the bit-field over-read

@@ -28,6 +28,7 @@ struct EncParams {
     const __half* v;
     int64_t k_sb, k_sh, k_ss, v_sb, v_sh, v_ss;
     int32_t n_batch, n_kv, n_tok, t0;
+    const int32_t* pos_dev;
     uint8_t* kp; int64_t kp_sb, kp_sh, kp_st; int32_t kp_row_bytes;
     void* kn; int64_t kn_sb, kn_sh, kn_st; int32_t kn_count;
     uint8_t* vp; int64_t vp_sb, vp_sh, vp_st;
@@ -51,7 +52,23 @@ __device__ __forceinline__ uint32_t pack_byte(const uint8_t* codes, int n, int b
     return out & 0xFFu;
 }
 
+// Copy one 128x128 fp32 rotation into shared memory with every load independent (the matrix is
+// usually cold in L2 after a decode step streamed the cache, so latency, not bandwidth, matters).
+__device__ __forceinline__ void stage_rotation(float* dst, const float* src, int tid) {
+    const float4* s4 = reinterpret_cast<const float4*>(src);
+    float4* d4 = reinterpret_cast<float4*>(dst);
+    float4 buf[8];
+#pragma unroll
+    for (int base = 0; base < kHD * kHD / 4; base += 8 * 128) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) buf[i] = __ldg(s4 + base + i * 128 + tid);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d4[base + i * 128 + tid] = buf[i];
+    }
+}
+
 __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
+    extern __shared__ __align__(16) float wsm[];            // staged rotation, [input position][output position]
     __shared__ __align__(16) float xs[kHD][kRows];          // [packed position][row]
     __shared__ float gn[BGTQ_MAX_SEGMENTS][kRows];
     __shared__ float gc[BGTQ_MAX_SEGMENTS][kRows];
@@ -62,6 +79,7 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
     const int p = threadIdx.x;
     const int h = blockIdx.y;
     const bool is_v = blockIdx.z == 1;
+    const int t0 = P.pos_dev ? *P.pos_dev : P.t0;   // first destination token slot
     if (is_v ? (P.flags & BGTQ_ENC_SKIP_V) : (P.flags & BGTQ_ENC_SKIP_K)) return;
     const BgtqHeadDesc& d = P.desc[h];
     const int64_t n_rows = (int64_t)P.n_batch * P.n_tok;
@@ -77,6 +95,7 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
         rs[r] = rok[r] ? (int)(n % P.n_tok) : 0;
     }
 
+    stage_rotation(wsm, (is_v ? P.rot_v : P.rot_k) + (size_t)h * kHD * kHD, p);
     if (!is_v) {
         // ------------------------------- K -------------------------------
         const int src_dim = d.head_perm[p];
@@ -107,10 +126,10 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
         float y[kRows];
 #pragma unroll
         for (int r = 0; r < kRows; ++r) y[r] = 0.f;
-        const float* W = P.rot_k + (size_t)h * kHD * kHD + p;
+        const float* W = wsm + p;
         const int js = d.seg_start[g], je = js + d.seg_len[g];
         for (int jj = js; jj < je; ++jj) {
-            const float w = __ldg(W + (size_t)jj * kHD);
+            const float w = W[jj * kHD];
             const float4 a = *reinterpret_cast<const float4*>(&xs[jj][0]);
             const float4 b = *reinterpret_cast<const float4*>(&xs[jj][4]);
             y[0] = fmaf(a.x, w, y[0]); y[1] = fmaf(a.y, w, y[1]); y[2] = fmaf(a.z, w, y[2]); y[3] = fmaf(a.w, w, y[3]);
@@ -152,7 +171,7 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
             if (rok[r]) {
                 float val = s < d.n_seg ? gn[s][r] : 0.f;
                 if (mixed && s < d.n_seg) val = val / gc[s][r];
-                const size_t o = rb[r] * P.kn_sb + h * P.kn_sh + (size_t)(P.t0 + rs[r]) * P.kn_st + s;
+                const size_t o = rb[r] * P.kn_sb + h * P.kn_sh + (size_t)(t0 + rs[r]) * P.kn_st + s;
                 if (P.flags & BGTQ_ENC_K_NORMS_F16) static_cast<__half*>(P.kn)[o] = __float2half_rn(val);
                 else static_cast<float*>(P.kn)[o] = val;
             }
@@ -181,7 +200,7 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
                 if (mode == 1) byte = pack_byte(&codes[r][s_first], s_n, s_bw, s_t);
                 else if (mode == 2) byte = codes[r][s_first];
                 else if (mode == 3) byte = (codes[r][s_first] & 15u) | ((codes[r][s_first + 1] & 15u) << 4);
-                P.kp[rb[r] * P.kp_sb + h * P.kp_sh + (size_t)(P.t0 + rs[r]) * P.kp_st + p] = (uint8_t)byte;
+                P.kp[rb[r] * P.kp_sb + h * P.kp_sh + (size_t)(t0 + rs[r]) * P.kp_st + p] = (uint8_t)byte;
             }
         }
     } else {
@@ -215,10 +234,10 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
         float y[kRows];
 #pragma unroll
         for (int r = 0; r < kRows; ++r) y[r] = 0.f;
-        const float* W = P.rot_v + (size_t)h * kHD * kHD + p;
+        const float* W = wsm + p;
 #pragma unroll 4
         for (int jj = 0; jj < kHD; ++jj) {
-            const float w = __ldg(W + (size_t)jj * kHD);
+            const float w = W[jj * kHD];
             const float4 a = *reinterpret_cast<const float4*>(&xs[jj][0]);
             const float4 b = *reinterpret_cast<const float4*>(&xs[jj][4]);
             y[0] = fmaf(a.x, w, y[0]); y[1] = fmaf(a.y, w, y[1]); y[2] = fmaf(a.z, w, y[2]); y[3] = fmaf(a.w, w, y[3]);
@@ -242,7 +261,7 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
             const float raw = sqrtf(rawn[p] + 1e-30f);
             const float cnorm = sqrtf(cn[p] + 1e-20f);
             const float val = raw / (cnorm > 1e-10f ? cnorm : 1.0f);
-            P.vn[rb[p] * P.vn_sb + h * P.vn_sh + (size_t)(P.t0 + rs[p]) * P.vn_st] = __float2half_rn(val);
+            P.vn[rb[p] * P.vn_sb + h * P.vn_sh + (size_t)(t0 + rs[p]) * P.vn_st] = __float2half_rn(val);
         }
         const bool nibble = P.flags & BGTQ_ENC_V_NIBBLE;
         const int vb = nibble ? 4 : d.v_bits;
@@ -252,7 +271,7 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
             for (int r = 0; r < kRows; ++r) {
                 if (!rok[r]) continue;
                 const uint32_t byte = pack_byte(&codes[r][0], kHD, vb, p);
-                P.vp[rb[r] * P.vp_sb + h * P.vp_sh + (size_t)(P.t0 + rs[r]) * P.vp_st + p] = (uint8_t)byte;
+                P.vp[rb[r] * P.vp_sb + h * P.vp_sh + (size_t)(t0 + rs[r]) * P.vp_st + p] = (uint8_t)byte;
             }
         }
     }
@@ -269,7 +288,8 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
                            int64_t kp_sb, int64_t kp_sh, int64_t kp_st, int32_t kp_row_bytes, void* k_norms,
                            int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count, uint8_t* v_packed,
                            int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
-                           int64_t vn_st, uint8_t* k_codes, uint8_t* v_codes, int32_t flags, void* stream) {
+                           int64_t vn_st, uint8_t* k_codes, uint8_t* v_codes, int32_t flags, const int32_t* pos_dev,
+                           void* stream) {
     const bool do_k = !(flags & BGTQ_ENC_SKIP_K), do_v = !(flags & BGTQ_ENC_SKIP_V);
     if (!desc || n_batch < 1 || n_kv < 1 || n_tok < 0 || t0 < 0) return BGTQ_E_BADARG;
     if (do_k && (!rot_k || !k || !k_packed || !k_norms)) return BGTQ_E_BADARG;
@@ -281,7 +301,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
     P.desc = desc; P.rot_k = rot_k; P.rot_v = rot_v;
     P.k = static_cast<const __half*>(k); P.v = static_cast<const __half*>(v);
     P.k_sb = k_sb; P.k_sh = k_sh; P.k_ss = k_ss; P.v_sb = v_sb; P.v_sh = v_sh; P.v_ss = v_ss;
-    P.n_batch = n_batch; P.n_kv = n_kv; P.n_tok = n_tok; P.t0 = t0;
+    P.n_batch = n_batch; P.n_kv = n_kv; P.n_tok = n_tok; P.t0 = t0; P.pos_dev = pos_dev;
     P.kp = k_packed; P.kp_sb = kp_sb; P.kp_sh = kp_sh; P.kp_st = kp_st; P.kp_row_bytes = kp_row_bytes;
     P.kn = k_norms; P.kn_sb = kn_sb; P.kn_sh = kn_sh; P.kn_st = kn_st; P.kn_count = kn_count;
     P.vp = v_packed; P.vp_sb = vp_sb; P.vp_sh = vp_sh; P.vp_st = vp_st;
@@ -291,6 +311,15 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
     const int64_t gx = (n_rows + kRows - 1) / kRows;
     if (gx > 0x7fffffffLL || n_kv > 65535) return BGTQ_E_TOOBIG;
     dim3 grid((unsigned)gx, n_kv, 2);
-    encode_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(P);
+    constexpr int kWsmBytes = kHD * kHD * (int)sizeof(float);
+    static bool attr_set = false;   // same value every time; racing first calls are harmless
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(encode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsmBytes) != cudaSuccess) {
+            cudaGetLastError();
+            return BGTQ_E_LAUNCH;
+        }
+        attr_set = true;
+    }
+    encode_kernel<<<grid, 128, kWsmBytes, static_cast<cudaStream_t>(stream)>>>(P);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }

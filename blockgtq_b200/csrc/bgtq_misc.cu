@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(128) rotate_q_kernel(const BgtqHeadDesc* desc,
     const int js = d.seg_start[g], je = js + d.seg_len[g];
     const float* W = rot_k + (size_t)h * kHD * kHD + p;
     float acc = 0.f;
+#pragma unroll 8
     for (int j = js; j < je; ++j) acc = fmaf(qs[j], __ldg(W + (size_t)j * kHD), acc);
     q_rot[((size_t)b * n_q + hq) * kHD + p] = __float2half_rn(acc);
 }
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(128) combine_kernel(const float* part_o, const
         const int h = hq / (n_q / n_kv);
         const float* R = v_rot + (size_t)h * kHD * kHD + d;
         float acc = 0.f;
-#pragma unroll 8
+#pragma unroll 32
         for (int i = 0; i < kHD; ++i) acc = fmaf(merged[i], __ldg(R + (size_t)i * kHD), acc);
         o = acc;
     }

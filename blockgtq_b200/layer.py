@@ -95,7 +95,7 @@ def _strides3(t: torch.Tensor):
 
 
 def encode(layer: LayerTables, k, v, t0, k_packed, k_norms, v_packed, v_norms, *, flags=0,
-           k_codes=None, v_codes=None):
+           k_codes=None, v_codes=None, pos_dev=None):
     """Encode ``k``/``v`` (B, n_kv, S, 128) fp16 into rows ``t0 .. t0+S`` of the cache tensors
     ``k_packed`` (B, n_kv, T, bytes) u8, ``k_norms`` (B, n_kv, T, groups) f16|f32,
     ``v_packed`` (B, n_kv, T, bytes) u8 and ``v_norms`` (B, n_kv, T) f16.  Either side may be None."""
@@ -140,11 +140,11 @@ def encode(layer: LayerTables, k, v, t0, k_packed, k_norms, v_packed, v_norms, *
         _lib.ptr(k), *ks, _lib.ptr(v), *vs, B, H, S, int(t0),
         _lib.ptr(k_packed), *kps, kp_bytes, _lib.ptr(k_norms), *kns, kn_count,
         _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns,
-        _lib.ptr(k_codes), _lib.ptr(v_codes), flags, _lib.stream_ptr(ref.device)), "bgtq_encode")
+        _lib.ptr(k_codes), _lib.ptr(v_codes), flags, _lib.ptr(pos_dev), _lib.stream_ptr(ref.device)), "bgtq_encode")
     _lib.count_launch()
 
 
-def rotate_q(layer: LayerTables, q: torch.Tensor) -> torch.Tensor:
+def rotate_q(layer: LayerTables, q: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
     """q (B, n_q, 128) or (B, n_q, 1, 128) fp16 -> (B, n_q, 128) fp16 in the packed-K basis."""
     _lib.require_cuda(q, "q")
     if q.dim() == 4:
@@ -152,7 +152,8 @@ def rotate_q(layer: LayerTables, q: torch.Tensor) -> torch.Tensor:
     if q.stride(2) != 1 or q.dtype != torch.float16:
         q = q.contiguous().to(torch.float16)
     B, n_q, _ = q.shape
-    out = torch.empty(B, n_q, HD, dtype=torch.float16, device=q.device)
+    if out is None:
+        out = torch.empty(B, n_q, HD, dtype=torch.float16, device=q.device)
     _lib.check(_lib.lib().bgtq_rotate_q(_lib.ptr(layer.desc_dev), _lib.ptr(layer.rot_k), _lib.ptr(q),
                                         q.stride(0), q.stride(1), _lib.ptr(out), B, n_q, layer.n_kv,
                                         _lib.stream_ptr(q.device)), "bgtq_rotate_q")
@@ -165,7 +166,7 @@ def default_splits(n_batch: int, n_kv: int, n_tokens: int) -> int:
 
 
 def decode(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_norms, t_begin, t_end, *,
-           n_splits=None, scale=None, flags=0, part_o=None, part_lse=None, status=None):
+           n_splits=None, scale=None, flags=0, part_o=None, part_lse=None, status=None, pos_dev=None, pos_add=0):
     """Split-KV attention partials over cache rows [t_begin, t_end).
 
     Returns (part_o (B, n_q, n_splits, 128) f32, part_lse (B, n_q, n_splits) f32)."""
@@ -190,7 +191,8 @@ def decode(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_norms, t_be
         C.addressof(plan), _lib.ptr(layer.desc_dev), _lib.ptr(q_rot),
         _lib.ptr(k_packed), *kps, _lib.ptr(k_norms), *kns, _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns,
         B, n_q, layer.n_kv, int(t_begin), int(t_end), int(n_splits), float(scale),
-        _lib.ptr(part_o), _lib.ptr(part_lse), _lib.ptr(status), _lib.stream_ptr(q_rot.device)), "bgtq_decode")
+        _lib.ptr(part_o), _lib.ptr(part_lse), _lib.ptr(status), _lib.ptr(pos_dev), int(pos_add),
+        _lib.stream_ptr(q_rot.device)), "bgtq_decode")
     _lib.count_launch()
     return part_o, part_lse
 

@@ -31,7 +31,8 @@ class BlockGTQKVManager:
     def __init__(self, n_layers: int, n_q_heads: int, n_kv_heads: int, head_dim: int, max_seq_len: int,
                  batch_size: int = 1, k_avg_bits: float = 3.0, v_bits: int = 3, device="cuda",
                  n_sink: int = 0, recent_window: int = 0, block_size: int = 1,
-                 min_bits: int = 1, max_bits: int = 8, rotation_threshold: int = 2):
+                 min_bits: int = 1, max_bits: int = 8, rotation_threshold: int = 2,
+                 use_cuda_graph: bool = None):
         if head_dim != HD:
             raise ValueError("head_dim must be 128")
         if n_kv_heads > 8 or n_q_heads // n_kv_heads > 8:
@@ -42,7 +43,8 @@ class BlockGTQKVManager:
         self.device = torch.device(device)
         self.gqa_ratio = n_q_heads // n_kv_heads
         self.scale = 1.0 / math.sqrt(head_dim)
-        self.seq_len = 0                      # tokens appended so far (all regions)
+        self._seq_len = 0                     # tokens appended so far (all regions)
+        self._pos_dirty = True
         self._quant_opts = dict(min_bits=min_bits, max_bits=max_bits, rotation_threshold=rotation_threshold)
         self.quantizers = [[None] * n_kv_heads for _ in range(n_layers)]
         self._kernel_args = [[None] * n_kv_heads for _ in range(n_layers)]
@@ -58,6 +60,22 @@ class BlockGTQKVManager:
         self._k_buf = self._v_buf = None
         self.n_packed = 0                     # tokens in the packed region
         self._status = None
+        # single-token decode steps are captured once per layer and replayed (the reference graphs only
+        # its T=1 encode, packed_kv_manager.py:182-257); needs the plain (unbuffered) cache
+        self._use_graph = (not self._buffered) if use_cuda_graph is None else bool(use_cuda_graph)
+        if self._use_graph and self._buffered:
+            raise ValueError("CUDA-graph replay is not available with fp16 sink/recent buffers")
+        self._graphs = [None] * n_layers
+        self._g_qkv = self._g_out = self._pos = None
+
+    @property
+    def seq_len(self) -> int:
+        return self._seq_len
+
+    @seq_len.setter
+    def seq_len(self, value: int):
+        self._seq_len = int(value)
+        self._pos_dirty = True
 
     # -- calibration -----------------------------------------------------------------
     def calibrate(self, layer_idx: int, q_data: torch.Tensor, k_data: torch.Tensor):
@@ -102,6 +120,14 @@ class BlockGTQKVManager:
         self._v_packed = torch.zeros(*shape, vpb, dtype=torch.uint8, device=dev)[:, :, :, :self.max_T]
         self._v_norms = torch.zeros(*shape, dtype=torch.float16, device=dev)[:, :, :, :self.max_T]
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        # scratch reused by every layer step (stream ordered): rotated queries and split partials
+        self._n_splits = default_splits(self.B, self.n_kv, self.max_T) if dev.type == "cuda" else 1
+        self._q_rot = torch.empty(self.B, self.n_q, self.hd, dtype=torch.float16, device=dev)
+        self._part_o = torch.empty(self.B, self.n_q, self._n_splits, self.hd, dtype=torch.float32, device=dev)
+        self._part_lse = torch.empty(self.B, self.n_q, self._n_splits, dtype=torch.float32, device=dev)
+        self._g_qkv = torch.zeros(self.B, self.n_q + 2 * self.n_kv, 1, self.hd, dtype=torch.float16, device=dev)
+        self._g_out = torch.zeros(self.n_layers, self.B, self.n_q, self.hd, dtype=torch.float16, device=dev)
+        self._pos = torch.zeros(1, dtype=torch.int32, device=dev)
         if self._buffered:
             self._k_buf = torch.zeros(self.n_layers, self.B, self.n_kv, self._buf_cap, self.hd,
                                       dtype=torch.float16, device=dev)
@@ -198,6 +224,62 @@ class BlockGTQKVManager:
         encode(self._layers[li], self._k_buf[li].index_select(2, slots), self._v_buf[li].index_select(2, slots),
                f_lo, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li])
 
+    # -- graph replay of one layer step ----------------------------------------------------------
+    def static_qkv(self) -> torch.Tensor:
+        """(B, n_q + 2 n_kv, 1, hd) fp16 input buffer of the captured layer step: rows [0, n_q) are the
+        query heads, then the new K heads, then the new V heads.  Writing a step's inputs here (for
+        instance as the output of a fused QKV projection or an H2D copy) and passing these views to
+        :meth:`append_and_attend` skips the staging copies."""
+        self._ensure_storage()
+        return self._g_qkv
+
+    def static_inputs(self):
+        b = self.static_qkv()
+        return b[:, :self.n_q], b[:, self.n_q:self.n_q + self.n_kv], b[:, self.n_q + self.n_kv:]
+
+    def _sync_pos(self):
+        if self._pos_dirty:
+            self._pos.fill_(self._seq_len)
+            self._pos_dirty = False
+
+    def _layer_step(self, li: int):
+        """rotate_q -> append K,V at *pos -> decode over [0, *pos + 1) -> combine, all on static buffers."""
+        lt = self._layers[li]
+        gq, gk, gv = self.static_inputs()
+        encode(lt, gk, gv, 0, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
+               pos_dev=self._pos)
+        baked = all(self.quantizers[li][h]._q_perm_baked for h in range(self.n_kv))
+        q_rot = gq[:, :, 0].contiguous() if baked else rotate_q(lt, gq, out=self._q_rot)
+        decode(lt, q_rot, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
+               0, self.max_T, n_splits=self._n_splits, scale=self.scale, status=self._status,
+               part_o=self._part_o, part_lse=self._part_lse, pos_dev=self._pos, pos_add=1)
+        combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li])
+
+    def _replay_layer(self, li: int, q, k_new, v_new) -> torch.Tensor:
+        self._ensure_storage()
+        if self._seq_len + 1 > self.max_T:
+            raise ValueError("cache overflow")
+        self._sync_pos()
+        gq, gk, gv = self.static_inputs()
+        if q.data_ptr() != gq.data_ptr():
+            gq.copy_(q.reshape(gq.shape))
+        if k_new.data_ptr() != gk.data_ptr():
+            gk.copy_(k_new)
+        if v_new.data_ptr() != gv.data_ptr():
+            gv.copy_(v_new)
+        g = self._graphs[li]
+        if g is None:
+            self._layer_step(li)                      # eager once: sets kernel attributes, validates shapes
+            torch.cuda.current_stream().synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._layer_step(li)
+            self._graphs[li] = g
+        else:
+            g.replay()
+            _lib.count_launch(4)
+        return self._g_out[li]
+
     # -- decode ----------------------------------------------------------------------------
     @torch.no_grad()
     def append_and_attend(self, layer_idx: int, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
@@ -205,6 +287,8 @@ class BlockGTQKVManager:
         """Quantise and append (B, n_kv, S, hd) K/V, then attend the (B, n_q, 1, hd) query over the
         whole cache.  Returns (B, n_q, 1, hd) fp16 (packed_kv_manager.py:268-348)."""
         t, S = self.seq_len, k_new.shape[2]
+        if self._use_graph and S == 1 and n_splits is None and q.is_cuda:
+            return self._replay_layer(layer_idx, q, k_new, v_new).unsqueeze(2)
         defer = self._buffered and S == 1
         f0, f1 = self._append_tokens(layer_idx, k_new, v_new, t, defer_flush=defer)
         out, _, _ = self.attend(layer_idx, q, t + S, n_splits=n_splits, flushed=f0 if defer else None)
@@ -250,8 +334,10 @@ class BlockGTQKVManager:
 
     def increment_seq_len(self, by: int = 1):
         """Call after all layers processed the new token(s) (packed_kv_manager.py:350-352)."""
-        self.seq_len += by
-        _, self.n_packed, _ = self._region_sizes(self.seq_len)
+        self._seq_len += by
+        if self._pos is not None and not self._pos_dirty:
+            self._pos.add_(by)
+        _, self.n_packed, _ = self._region_sizes(self._seq_len)
 
     def check_status(self):
         """Synchronise and raise if a kernel reported a timed-out wait."""

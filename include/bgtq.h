@@ -105,6 +105,9 @@ const char* bgtq_error_string(int code);       /* host pointer to a static strin
  * R^T so that y = v_unit @ rot_v[h].
  * k_codes / v_codes: optional (may be NULL) outputs of the unpacked indices,
  * (n_batch, n_kv, n_tok, 128) contiguous uint8, K in packed-position order.
+ * pos_dev: optional device int32; when non-NULL the first destination slot is
+ * *pos_dev instead of t0, read when the kernel runs (lets a captured CUDA graph
+ * append at a position that advances between replays).
  */
 int bgtq_encode(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v,
                 const void* k, int64_t k_sb, int64_t k_sh, int64_t k_ss,
@@ -115,7 +118,7 @@ int bgtq_encode(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v
                 uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
                 void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
                 uint8_t* k_codes, uint8_t* v_codes,
-                int32_t flags, void* stream);
+                int32_t flags, const int32_t* pos_dev, void* stream);
 
 /* Rotate decode queries into the packed-K basis:
  * q_rot[b, hq, p] = fp16( sum_j fp32(q[b, hq, head_perm[j]]) * rot_k[h][j][p] ),
@@ -167,6 +170,9 @@ int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv, int32_t n_tokens);
  *           logits of the split; -inf for a split with no tokens (part_o = 0).
  * status: optional int32 on the device; set to a non-zero code if a bounded
  * wait inside the kernel gave up (the output is then invalid).
+ * pos_dev / pos_add: optional device int32; when non-NULL the range ends at
+ * min(t_end, *pos_dev + pos_add), read when the kernel runs; t_end then only
+ * bounds the range and fixes how tokens are cut into splits (graph replay).
  */
 int bgtq_decode(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot,
                 const uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
@@ -175,7 +181,8 @@ int bgtq_decode(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const
                 const void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
                 int32_t n_batch, int32_t n_q, int32_t n_kv,
                 int32_t t_begin, int32_t t_end, int32_t n_splits, float scale,
-                float* part_o, float* part_lse, int32_t* status, void* stream);
+                float* part_o, float* part_lse, int32_t* status,
+                const int32_t* pos_dev, int32_t pos_add, void* stream);
 
 /* Attention of the same queries over tokens kept unquantised in fp16 (the
  * sink prefix and the recent window of the three-region cache policy,
