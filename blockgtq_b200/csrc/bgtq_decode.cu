@@ -214,7 +214,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
                 mbar_arrive_expect_tx(&full[st], total);
                 for (int c = 0; c < 4; ++c) {
                     const uint8_t* al = src[c] - (reinterpret_cast<uintptr_t>(src[c]) & 15u);
+                    #ifdef BGTQ_EXP_NO_HINT
+                    bulk_g2s(sb + dst[c], al, sz[c], &full[st]);
+#else
                     bulk_g2s_hint(sb + dst[c], al, sz[c], &full[st], pol);
+#endif
                 }
             }
         }

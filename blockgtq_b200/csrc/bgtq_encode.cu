@@ -277,6 +277,175 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Single-token step preparation: query rotation and K/V append in ONE launch,
+// organised for latency (a decode step appends n_batch x n_kv rows only).
+// One CTA of 512 threads per work item; thread (p = tid % 128, c = tid / 128)
+// prefetches 32 entries of column p of the rotation before the inputs arrive and
+// produces a quarter of the dot product; the four quarters are added in order.
+// Work items: [0, n_rot) query rows (b, hq); then K rows (b, h); then V rows (b, h).
+// ---------------------------------------------------------------------------
+struct PrepParams {
+    EncParams e;            // n_tok == 1
+    const __half* q;
+    int64_t q_sb, q_sh;
+    __half* q_rot;
+    int32_t n_q, do_rot;
+};
+
+__global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
+    __shared__ float xs[kHD];
+    __shared__ float xn[kHD];
+    __shared__ float part[4][kHD];
+    __shared__ float gn[BGTQ_MAX_SEGMENTS];
+    __shared__ float gc[BGTQ_MAX_SEGMENTS];
+    __shared__ float red[4];
+    __shared__ uint8_t codes[kHD];
+    const EncParams& E = P.e;
+    const int tid = threadIdx.x, p = tid & 127, c = tid >> 7, warp = tid >> 5, lane = tid & 31;
+    const int n_rot = P.do_rot ? E.n_batch * P.n_q : 0;
+    const int n_rows = E.n_batch * E.n_kv;
+    int item = blockIdx.x, kind;   // 0 rotate, 1 K, 2 V
+    int b, h, hq = 0;
+    if (item < n_rot) {
+        kind = 0; b = item / P.n_q; hq = item % P.n_q; h = hq / (P.n_q / E.n_kv);
+    } else {
+        item -= n_rot;
+        kind = item < n_rows ? 1 : 2;
+        if (kind == 2) item -= n_rows;
+        b = item / E.n_kv; h = item % E.n_kv;
+        if ((kind == 1 && (E.flags & BGTQ_ENC_SKIP_K)) || (kind == 2 && (E.flags & BGTQ_ENC_SKIP_V))) return;
+    }
+    const BgtqHeadDesc& d = E.desc[h];
+    // rotation column p, rows 32c .. 32c+31: independent loads issued before anything else
+    const float* W = (kind == 2 ? E.rot_v : E.rot_k) + (size_t)h * kHD * kHD + (size_t)(32 * c) * kHD + p;
+    float w[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) w[i] = __ldg(W + (size_t)i * kHD);
+    const int t0 = E.pos_dev ? *E.pos_dev : E.t0;
+
+    float x = 0.f;
+    int g = 0;
+    if (c == 0) {
+        if (kind == 0) x = __half2float(P.q[b * P.q_sb + hq * P.q_sh + d.head_perm[p]]);
+        else if (kind == 1) x = __half2float(E.k[b * E.k_sb + h * E.k_sh + d.head_perm[p]]);
+        else x = __half2float(E.v[b * E.v_sb + h * E.v_sh + p]);
+        xs[p] = x;
+        g = d.group_of[p];
+    }
+    __syncthreads();
+    float raw_v = 0.f;
+    if (kind == 1) {            // group norms: warp s reduces segment s
+        if (warp < d.n_seg) {
+            float acc = 0.f;
+            for (int i = d.seg_start[warp] + lane; i < d.seg_start[warp] + d.seg_len[warp]; i += 32) acc = fmaf(xs[i], xs[i], acc);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) gn[warp] = sqrtf(acc + 1e-30f);
+        }
+    } else if (kind == 2) {
+        if (c == 0) {
+            float acc = x * x;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) red[warp] = acc;
+        }
+    }
+    __syncthreads();
+    if (c == 0) {
+        if (kind == 0) xn[p] = x;
+        else if (kind == 1) { const float nr = gn[g]; xn[p] = x / (nr > 1e-10f ? nr : 1.0f); }
+        else { raw_v = sqrtf(red[0] + red[1] + red[2] + red[3] + 1e-30f); xn[p] = x / (raw_v > 1e-8f ? raw_v : 1.0f); }
+    }
+    __syncthreads();
+    {
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc = fmaf(xn[32 * c + i], w[i], acc);
+        part[c][p] = acc;
+    }
+    __syncthreads();
+    if (c != 0 && kind != 2) { if (kind == 0) return; }
+    const float y = (part[0][p] + part[1][p]) + (part[2][p] + part[3][p]);
+    if (kind == 0) {
+        if (c == 0) P.q_rot[((size_t)b * P.n_q + hq) * kHD + p] = __float2half_rn(y);
+        return;
+    }
+    if (kind == 1) {
+        const bool mixed = E.flags & BGTQ_ENC_K_MIXED;
+        float c2 = 0.f;
+        if (c == 0) {
+            float u = (y - d.lut_off[g]) * d.lut_inv[g];
+            u = fminf(fmaxf(u, 0.f), 255.f);
+            const uint8_t cd = d.code_lut[g][(int)u];
+            codes[p] = cd;
+            const float cv = d.k_cents[d.seg_lut_off[g] + cd];
+            c2 = cv * cv;
+            if (E.k_codes) E.k_codes[((size_t)b * E.n_kv + h) * kHD + p] = cd;
+            xs[p] = c2;
+        }
+        __syncthreads();
+        if (mixed && warp < d.n_seg) {
+            float acc = 0.f;
+            for (int i = d.seg_start[warp] + lane; i < d.seg_start[warp] + d.seg_len[warp]; i += 32) acc += xs[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) gc[warp] = fmaxf(sqrtf(acc), 1e-10f);
+        }
+        __syncthreads();
+        if (c != 0) return;
+        if (p < E.kn_count) {
+            float val = p < d.n_seg ? gn[p] : 0.f;
+            if (mixed && p < d.n_seg) val = val / gc[p];
+            const size_t o = b * E.kn_sb + h * E.kn_sh + (size_t)t0 * E.kn_st + p;
+            if (E.flags & BGTQ_ENC_K_NORMS_F16) static_cast<__half*>(E.kn)[o] = __float2half_rn(val);
+            else static_cast<float*>(E.kn)[o] = val;
+        }
+        if (p < E.kp_row_bytes) {
+            uint32_t byte = 0;
+            if (mixed) {
+                const int nib = d.nopack_start / 2;
+                if (p < nib) byte = (codes[2 * p] & 15u) | ((codes[2 * p + 1] & 15u) << 4);
+                else if (p < nib + d.nopack_len) byte = codes[d.nopack_start + (p - nib)];
+            } else {
+                for (int s = 0; s < d.n_seg; ++s) {
+                    const int bw = d.seg_bw[s], nb = seg_storage_bytes(bw, d.seg_len[s]);
+                    if (p >= d.seg_pack_off[s] && p < d.seg_pack_off[s] + nb) {
+                        const int st = p - d.seg_pack_off[s];
+                        byte = bw >= 5 ? codes[d.seg_start[s] + st] : pack_byte(&codes[d.seg_start[s]], d.seg_len[s], bw, st);
+                    }
+                }
+            }
+            E.kp[b * E.kp_sb + h * E.kp_sh + (size_t)t0 * E.kp_st + p] = (uint8_t)byte;
+        }
+        return;
+    }
+    // ---- V ----
+    float c2 = 0.f;
+    if (c == 0) {
+        const int nb = (1 << d.v_bits) - 1;
+        int cd = 0;
+        for (int i = 0; i < nb; ++i) cd += y > d.v_bounds[i] ? 1 : 0;
+        codes[p] = (uint8_t)cd;
+        const float cv = d.v_cents[cd];
+        c2 = cv * cv;
+        if (E.v_codes) E.v_codes[((size_t)b * E.n_kv + h) * kHD + p] = (uint8_t)cd;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c2 += __shfl_xor_sync(0xffffffffu, c2, o);
+        if (lane == 0) gn[warp] = c2;
+    }
+    __syncthreads();
+    if (c != 0) return;
+    if (p == 0) {
+        const float cnorm = sqrtf(gn[0] + gn[1] + gn[2] + gn[3] + 1e-20f);
+        E.vn[b * E.vn_sb + h * E.vn_sh + (size_t)t0 * E.vn_st] = __float2half_rn(raw_v / (cnorm > 1e-10f ? cnorm : 1.0f));
+    }
+    const int vb = (E.flags & BGTQ_ENC_V_NIBBLE) ? 4 : d.v_bits;
+    if (p < seg_storage_bytes(vb, kHD))
+        E.vp[b * E.vp_sb + h * E.vp_sh + (size_t)t0 * E.vp_st + p] = (uint8_t)pack_byte(&codes[0], kHD, vb, p);
+}
+
 }  // namespace
 }  // namespace bgtq
 
@@ -321,5 +490,37 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
         attr_set = true;
     }
     encode_kernel<<<grid, 128, kWsmBytes, static_cast<cudaStream_t>(stream)>>>(P);
+    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare(
+    const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v, const void* q, int64_t q_sb, int64_t q_sh,
+    void* q_rot, int32_t n_q, const void* k, int64_t k_sb, int64_t k_sh, const void* v, int64_t v_sb, int64_t v_sh,
+    int32_t n_batch, int32_t n_kv, int32_t t0, uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
+    int32_t kp_row_bytes, void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
+    uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
+    int64_t vn_st, int32_t flags, const int32_t* pos_dev, void* stream) {
+    if (!desc || !rot_k || !rot_v || !k || !v || !k_packed || !k_norms || !v_packed || !v_norms) return BGTQ_E_BADARG;
+    if (n_batch < 1 || n_kv < 1 || t0 < 0 || kp_row_bytes < 1 || kp_row_bytes > kHD || kn_count < 1 ||
+        kn_count > BGTQ_MAX_SEGMENTS)
+        return BGTQ_E_BADARG;
+    const bool do_rot = q != nullptr && q_rot != nullptr;
+    if (do_rot && (n_q < n_kv || n_q % n_kv)) return BGTQ_E_BADARG;
+    PrepParams P;
+    EncParams& E = P.e;
+    E.desc = desc; E.rot_k = rot_k; E.rot_v = rot_v;
+    E.k = static_cast<const __half*>(k); E.v = static_cast<const __half*>(v);
+    E.k_sb = k_sb; E.k_sh = k_sh; E.k_ss = 0; E.v_sb = v_sb; E.v_sh = v_sh; E.v_ss = 0;
+    E.n_batch = n_batch; E.n_kv = n_kv; E.n_tok = 1; E.t0 = t0; E.pos_dev = pos_dev;
+    E.kp = k_packed; E.kp_sb = kp_sb; E.kp_sh = kp_sh; E.kp_st = kp_st; E.kp_row_bytes = kp_row_bytes;
+    E.kn = k_norms; E.kn_sb = kn_sb; E.kn_sh = kn_sh; E.kn_st = kn_st; E.kn_count = kn_count;
+    E.vp = v_packed; E.vp_sb = vp_sb; E.vp_sh = vp_sh; E.vp_st = vp_st;
+    E.vn = static_cast<__half*>(v_norms); E.vn_sb = vn_sb; E.vn_sh = vn_sh; E.vn_st = vn_st;
+    E.k_codes = nullptr; E.v_codes = nullptr; E.flags = flags;
+    P.q = static_cast<const __half*>(q); P.q_sb = q_sb; P.q_sh = q_sh; P.q_rot = static_cast<__half*>(q_rot);
+    P.n_q = n_q; P.do_rot = do_rot ? 1 : 0;
+    const int64_t items = (int64_t)(do_rot ? n_batch * n_q : 0) + 2LL * n_batch * n_kv;
+    if (items > 0x7fffffffLL) return BGTQ_E_TOOBIG;
+    prep_kernel<<<(unsigned)items, 512, 0, static_cast<cudaStream_t>(stream)>>>(P);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }

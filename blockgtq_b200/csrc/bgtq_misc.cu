@@ -31,38 +31,54 @@ __global__ void __launch_bounds__(128) rotate_q_kernel(const BgtqHeadDesc* desc,
 // combine: merge split partials (and optionally the fp16-buffer partial).
 // One CTA per (query head, batch), one thread per output dim.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) combine_kernel(const float* part_o, const float* part_lse, int n_splits,
+__global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const float* part_lse, int n_splits,
                                                        const float* v_rot, const float* buf_o, const float* buf_lse,
                                                        int n_q, int n_kv, __half* out, int64_t o_sb, int64_t o_sh,
                                                        float* out_f32, float* lse_out) {
+    // thread (d = tid % 128, c = tid / 128): output dim d; quarter c of the splits and of the rotation rows
+    __shared__ float pnum[4][kHD];
+    __shared__ float pden[4];
     __shared__ float merged[kHD];
-    const int d = threadIdx.x, hq = blockIdx.x, b = blockIdx.y;
+    const int tid = threadIdx.x, d = tid & 127, c = tid >> 7;
+    const int hq = blockIdx.x, b = blockIdx.y;
     const size_t row = (size_t)b * n_q + hq;
+    float w[32];
+    if (v_rot) {   // rows 32c .. 32c+31 of column d, requested before anything depends on them
+        const float* R = v_rot + (size_t)(hq / (n_q / n_kv)) * kHD * kHD + (size_t)(32 * c) * kHD + d;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) w[i] = __ldg(R + (size_t)i * kHD);
+    }
     const float* lse = part_lse + row * n_splits;
     float mx = -INFINITY;
-    for (int c = 0; c < n_splits; ++c) mx = fmaxf(mx, lse[c]);
+    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, lse[s]);
     float num = 0.f, den = 0.f;
     if (mx > -INFINITY) {
-        for (int c = 0; c < n_splits; ++c) {
-            const float l = lse[c];
+        for (int s = c; s < n_splits; s += 4) {
+            const float l = lse[s];
             if (l == -INFINITY) continue;
             const float a = expf(l - mx);
             den += a;
-            num = fmaf(a, part_o[(row * n_splits + c) * kHD + d], num);
+            num = fmaf(a, part_o[(row * n_splits + s) * kHD + d], num);
         }
     }
-    float o = den > 0.f ? num / den : 0.f;
+    pnum[c][d] = num;
+    if (d == 0) pden[c] = den;
+    __syncthreads();
+    den = (pden[0] + pden[1]) + (pden[2] + pden[3]);
+    float o = den > 0.f ? ((pnum[0][d] + pnum[1][d]) + (pnum[2][d] + pnum[3][d])) / den : 0.f;
     float tot = den > 0.f ? mx + logf(den) : -INFINITY;
     if (v_rot) {
-        merged[d] = o;
+        if (c == 0) merged[d] = o;
         __syncthreads();
-        const int h = hq / (n_q / n_kv);
-        const float* R = v_rot + (size_t)h * kHD * kHD + d;
         float acc = 0.f;
-#pragma unroll 32
-        for (int i = 0; i < kHD; ++i) acc = fmaf(merged[i], __ldg(R + (size_t)i * kHD), acc);
-        o = acc;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc = fmaf(merged[32 * c + i], w[i], acc);
+        __syncthreads();
+        pnum[c][d] = acc;
+        __syncthreads();
+        o = (pnum[0][d] + pnum[1][d]) + (pnum[2][d] + pnum[3][d]);
     }
+    if (c != 0) return;
     if (buf_o) {
         const float lb = buf_lse[row];
         const float m2 = fmaxf(tot, lb);
@@ -170,7 +186,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_combine(const float* 
     if ((buf_o == nullptr) != (buf_lse == nullptr)) return BGTQ_E_BADARG;
     if (!out && !out_f32) return BGTQ_E_BADARG;
     if (n_batch > 65535) return BGTQ_E_TOOBIG;
-    combine_kernel<<<dim3(n_q, n_batch), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    combine_kernel<<<dim3(n_q, n_batch), 512, 0, static_cast<cudaStream_t>(stream)>>>(
         part_o, part_lse, n_splits, v_rot, buf_o, buf_lse, n_q, n_kv, static_cast<__half*>(out), o_sb, o_sh, out_f32,
         lse_out);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;

@@ -161,6 +161,42 @@ def rotate_q(layer: LayerTables, q: torch.Tensor, out: torch.Tensor = None) -> t
     return out
 
 
+def step_prepare(layer: LayerTables, q, k, v, t0, k_packed, k_norms, v_packed, v_norms, *, q_rot=None,
+                 flags=0, pos_dev=None):
+    """Rotate q (B, n_q, [1,] 128) into ``q_rot`` and append one token k/v (B, n_kv, 1, 128) at slot
+    ``t0`` (or ``*pos_dev``) of the cache tensors, in one launch.  ``q=None`` skips the rotation."""
+    _lib.require_cuda(k, "k")
+    B, H, S, D = k.shape
+    if S != 1 or H != layer.n_kv or D != HD or v.shape != k.shape:
+        raise ValueError("step_prepare appends exactly one token per (batch, KV head)")
+    if k.dtype != torch.float16 or v.dtype != torch.float16 or k.stride(3) != 1 or v.stride(3) != 1:
+        raise TypeError("k and v must be float16 with contiguous last dim")
+    if k_norms.dtype == torch.float16:
+        flags |= _lib.ENC_K_NORMS_F16
+    n_q = 0
+    qa = (0, 0, 0)
+    if q is not None:
+        if q.dim() == 4:
+            q = q[:, :, 0]
+        if q.dtype != torch.float16 or q.stride(2) != 1:
+            q = q.to(torch.float16).contiguous()
+        n_q = q.shape[1]
+        if q_rot is None:
+            q_rot = torch.empty(B, n_q, HD, dtype=torch.float16, device=k.device)
+        qa = (_lib.ptr(q), q.stride(0), q.stride(1))
+    kps, kns, vps = _strides3(k_packed), _strides3(k_norms), _strides3(v_packed)
+    vns = (v_norms.stride(0), v_norms.stride(1), v_norms.stride(2))
+    _lib.check(_lib.lib().bgtq_step_prepare(
+        _lib.ptr(layer.desc_dev), _lib.ptr(layer.rot_k), _lib.ptr(layer.rot_v), *qa,
+        _lib.ptr(q_rot) if q is not None else 0, n_q,
+        _lib.ptr(k), k.stride(0), k.stride(1), _lib.ptr(v), v.stride(0), v.stride(1), B, H, int(t0),
+        _lib.ptr(k_packed), *kps, k_packed.shape[3], _lib.ptr(k_norms), *kns, k_norms.shape[3],
+        _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns, flags, _lib.ptr(pos_dev),
+        _lib.stream_ptr(k.device)), "bgtq_step_prepare")
+    _lib.count_launch()
+    return q_rot
+
+
 def default_splits(n_batch: int, n_kv: int, n_tokens: int) -> int:
     return _lib.lib().bgtq_decode_default_splits(n_batch, n_kv, n_tokens)
 

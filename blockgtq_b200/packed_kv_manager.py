@@ -21,7 +21,8 @@ import torch
 
 from . import _lib
 from .calib import packed_v_bytes
-from .layer import HD, LayerTables, buffer_attn, combine, decode, default_splits, encode, rotate_q
+from .layer import (HD, LayerTables, buffer_attn, combine, decode, default_splits, encode, rotate_q,
+                    step_prepare)
 from .quantizer import BlockGTQQuantizer, build_batched_encode_args
 
 __all__ = ["BlockGTQKVManager", "decode_step"]
@@ -246,10 +247,10 @@ class BlockGTQKVManager:
         """rotate_q -> append K,V at *pos -> decode over [0, *pos + 1) -> combine, all on static buffers."""
         lt = self._layers[li]
         gq, gk, gv = self.static_inputs()
-        encode(lt, gk, gv, 0, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
-               pos_dev=self._pos)
         baked = all(self.quantizers[li][h]._q_perm_baked for h in range(self.n_kv))
-        q_rot = gq[:, :, 0].contiguous() if baked else rotate_q(lt, gq, out=self._q_rot)
+        step_prepare(lt, None if baked else gq, gk, gv, 0, self._k_packed[li], self._k_norms[li],
+                     self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos)
+        q_rot = gq[:, :, 0].contiguous() if baked else self._q_rot
         decode(lt, q_rot, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
                0, self.max_T, n_splits=self._n_splits, scale=self.scale, status=self._status,
                part_o=self._part_o, part_lse=self._part_lse, pos_dev=self._pos, pos_add=1)
@@ -277,7 +278,7 @@ class BlockGTQKVManager:
             self._graphs[li] = g
         else:
             g.replay()
-            _lib.count_launch(4)
+            _lib.count_launch(3)
         return self._g_out[li]
 
     # -- decode ----------------------------------------------------------------------------

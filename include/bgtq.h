@@ -131,6 +131,25 @@ int bgtq_rotate_q(const BgtqHeadDesc* desc, const float* rot_k,
                   const void* q, int64_t q_sb, int64_t q_sh,
                   void* q_rot, int32_t n_batch, int32_t n_q, int32_t n_kv, void* stream);
 
+/* One decode step's preparation in a single latency-oriented launch: the query
+ * rotation of bgtq_rotate_q and the append of ONE new token per (batch, KV head)
+ * of bgtq_encode (same arguments, n_tok = 1, no code outputs).  q / q_rot may be
+ * NULL to skip the rotation (queries baked into q_proj).  Replaces, per layer
+ * and step, the n_kv rotate_q_for_packed_kernel calls and the CUDA-graphed T=1
+ * encode of the reference (blockgtq/packed_kv_manager.py:221-257, 318-329).
+ * The rotation sums are formed in a different order than in bgtq_encode, so a
+ * coordinate sitting exactly on a bin edge may land on the neighbouring code. */
+int bgtq_step_prepare(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v,
+                      const void* q, int64_t q_sb, int64_t q_sh, void* q_rot, int32_t n_q,
+                      const void* k, int64_t k_sb, int64_t k_sh,
+                      const void* v, int64_t v_sb, int64_t v_sh,
+                      int32_t n_batch, int32_t n_kv, int32_t t0,
+                      uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st, int32_t kp_row_bytes,
+                      void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
+                      uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
+                      void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
+                      int32_t flags, const int32_t* pos_dev, void* stream);
+
 /* ---- decode --------------------------------------------------------------- */
 #define BGTQ_DEC_K_MIXED 1        /* k_packed rows are in the nibble/raw mixed layout */
 #define BGTQ_DEC_V_NIBBLE 2       /* v_packed rows are 4-bit nibbles */
