@@ -68,6 +68,11 @@ _SIGNATURES = {
                               _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
                               _i32, _i32, _i32, _i32, _i32, _i32, _f32,
                               _vp, _vp, _vp, _vp, _i32, _vp]),
+    "bgtq_decode_combined_noalloc": (C.c_int, [_vp, _vp, _vp,
+                                               _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
+                                               _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
+                                               _i32, _i32, _i32, _i32, _i32, _i32, _f32,
+                                               _vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "bgtq_buffer_attn": (C.c_int, [_vp, _i64, _i64, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
                                    _i32, _i32, _i32, _f32,
                                    _vp, _vp, _vp]),

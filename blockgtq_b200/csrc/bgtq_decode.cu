@@ -640,3 +640,59 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode(
     kern<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(P);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
+
+// ---------------------------------------------------------------------------
+// Decode + combine for callers that cannot allocate device memory.
+//
+// bgtq_decode leaves its per-split partial outputs in a buffer the caller must
+// provide.  Some callers have no way to get one: code running inside a CUDA
+// graph capture or a stream callback, plugins handed a fixed set of tensors by
+// their host framework, and processes whose memory pool is owned by someone
+// else.  For them the partials live in the file-scope array below, which every
+// GPU that loads this library reserves until the process exits.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int kNoAllocMaxRows = 8192;    // n_batch * n_q * n_splits
+constexpr int kNoAllocMaxDevices = 64;
+struct NoAllocScratch {
+    float part_o[kNoAllocMaxRows * BGTQ_HEAD_DIM];
+    float part_lse[kNoAllocMaxRows];
+};
+static __device__ __align__(256) NoAllocScratch g_noalloc_scratch;
+// Device address of g_noalloc_scratch per device ordinal.  In host code the symbol's name is only a
+// handle; the address a kernel can use has to be asked for, with that device current.
+NoAllocScratch* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_combined_noalloc(
+    const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot, const uint8_t* k_packed,
+    int64_t kp_sb, int64_t kp_sh, int64_t kp_st, const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
+    const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, const void* v_norms, int64_t vn_sb,
+    int64_t vn_sh, int64_t vn_st, int32_t n_batch, int32_t n_q, int32_t n_kv, int32_t t_begin, int32_t t_end,
+    int32_t n_splits, float scale, const float* v_rot, void* out, int64_t o_sb, int64_t o_sh, float* lse_out,
+    int32_t* status, void* stream) {
+    if (n_batch < 1 || n_q < 1 || n_splits < 1 || !out) return BGTQ_E_BADARG;
+    if ((int64_t)n_batch * n_q * n_splits > kNoAllocMaxRows) return BGTQ_E_TOOBIG;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) {
+        cudaGetLastError();
+        return BGTQ_E_LAUNCH;
+    }
+    if (!g_noalloc_ptr[dev]) {   // first call on this device: look the array's device address up once
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return BGTQ_E_LAUNCH;
+        }
+        g_noalloc_ptr[dev] = static_cast<NoAllocScratch*>(p);
+    }
+    NoAllocScratch* sc = g_noalloc_ptr[dev];
+    // Every split of every row is rewritten by the decode kernel (empty splits get zeros and -inf), so
+    // nothing left over from the previous call is ever read and nothing needs clearing.
+    const int rc = bgtq_decode(plan_host, desc, q_rot, k_packed, kp_sb, kp_sh, kp_st, k_norms, kn_sb, kn_sh, kn_st,
+                               v_packed, vp_sb, vp_sh, vp_st, v_norms, vn_sb, vn_sh, vn_st, n_batch, n_q, n_kv,
+                               t_begin, t_end, n_splits, scale, sc->part_o, sc->part_lse, status, nullptr, 0, stream);
+    if (rc != BGTQ_OK) return rc;
+    return bgtq_combine(sc->part_o, sc->part_lse, n_splits, v_rot, nullptr, nullptr, n_batch, n_q, n_kv, out, o_sb,
+                        o_sh, nullptr, lse_out, stream);
+}

@@ -239,6 +239,39 @@ int bgtq_combine(const float* part_o, const float* part_lse, int32_t n_splits,
                  void* out, int64_t o_sb, int64_t o_sh,
                  float* out_f32, float* lse_out, void* stream);
 
+/* bgtq_decode followed by bgtq_combine with NO caller-provided scratch: the
+ * split partials go to a fixed array inside the library instead of part_o /
+ * part_lse.  This entry point has no counterpart in the reference.
+ *
+ * It exists for callers that cannot allocate device memory at the point of the
+ * call: code being captured into or replayed from a stream-ordered sequence that
+ * forbids allocation, plugins that only receive the tensors their host
+ * framework hands them, and processes whose device memory is owned by another
+ * pool.  Inputs are as for bgtq_decode; out / o_sb / o_sh / lse_out / v_rot as
+ * for bgtq_combine (out: fp16 (n_batch, n_q, 128); lse_out optional).
+ *
+ * Limits and rules:
+ *   - n_batch * n_q * n_splits <= 8192, else BGTQ_E_TOOBIG (the array holds
+ *     8192 partial rows: about 4.2 MB on every GPU that loads the library, kept
+ *     until the process exits);
+ *   - it calls no cudaMalloc / cudaFree or other allocating routine;
+ *   - the FIRST call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) with that device current; make that first call
+ *     before starting any stream capture on the device;
+ *   - all calls on a device share the one array: two calls whose kernels can
+ *     overlap on the GPU (different streams without ordering) race.  Nothing in
+ *     the array has to be cleared between calls: every partial that is read was
+ *     written by the same call. */
+int bgtq_decode_combined_noalloc(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot,
+                const uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
+                const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
+                const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
+                const void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
+                int32_t n_batch, int32_t n_q, int32_t n_kv,
+                int32_t t_begin, int32_t t_end, int32_t n_splits, float scale,
+                const float* v_rot, void* out, int64_t o_sb, int64_t o_sh, float* lse_out,
+                int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
