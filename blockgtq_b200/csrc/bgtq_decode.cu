@@ -36,7 +36,7 @@ constexpr int kStages = 2;
 constexpr int kMergeStride = 132;  // floats per query row in the end-of-CTA merge buffer
 // shared-memory layout (byte offsets from the start of dynamic shared memory)
 // [barriers | codebook staging | per-step uniform params | per-step per-lane params | tables | stages]
-constexpr uint32_t kOffCbk = 128, kOffStepU = 1280, kOffStepL = kOffStepU + kMaxSteps * 16;
+constexpr uint32_t kOffCbk = 128, kOffStepU = 1280, kOffStepL = kOffStepU + kMaxSteps * 16;   // StepU: per segment
 constexpr uint32_t kOffLut = 12288;  // multiple of kLutTableBytes: table bases can be OR-ed into offsets
 static_assert(kOffStepL + kMaxSteps * 32 * 16 <= kOffLut && kOffLut % kLutTableBytes == 0, "layout");
 
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     uint64_t* empty = full + kStages;
     uint16_t* cbk = reinterpret_cast<uint16_t*>(smem + kOffCbk);  // 512 K entries + 16 V entries
     // Per k-tile parameters, expanded once so the inner loop does no decoding:
-    //   stepu[s]       = {flags | norm byte offset << 8, rotate 0, rotate 1, index mask}      (same for all lanes)
+    //   stepu[seg]     = per-segment constants (same for all lanes), see below
     //   stepl[s][lane] = {Qrot fragment lo, hi, table offset incl. lane column, unit bit offset of this lane}
     uint4* stepu = reinterpret_cast<uint4*>(smem + kOffStepU);
     uint4* stepl = reinterpret_cast<uint4*>(smem + kOffStepL);
@@ -132,63 +132,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
         }
         mbar_fence_init();
     }
-    {
-        const BgtqHeadDesc& d = P.desc[h];
-        for (int i = tid; i < 528; i += kThreads) cbk[i] = i < 512 ? d.codebook[i] : d.v_lut[i - 512];
-    }
-    if (warp == 0) {   // lane (r, j): query r, this lane's 4 codes of every k-tile
-        const int r = lane >> 2, j = lane & 3;
-        const bool q_ok = r < P.gqa;
-        const __half* qrow = P.q_rot + ((size_t)b * P.n_q + (size_t)h * P.gqa + (q_ok ? r : 0)) * kHD;
-        for (int s = 0; s < hp.n_steps; ++s) {
-            const DecStep stp = hp.steps[s];
-            const int d0 = (int)(stp.q & 0xFFu) + j * (int)((stp.q >> 8) & 0x3Fu);
-            const int end = (int)((stp.q >> 14) & 0xFFu);
-            const uint32_t* src = reinterpret_cast<const uint32_t*>(qrow + d0);
-            const uint32_t esh = (stp.b >> 10) & 31u;
-            uint4 v;
-            v.x = (q_ok && d0 < end) ? __ldg(src) : 0u;
-            v.y = (q_ok && d0 + 2 < end) ? __ldg(src + 1) : 0u;
-            v.z = lut_rel + (stp.c >> 16) + (((uint32_t)lane << 2) & ((1u << esh) - 1u));
-            v.w = (stp.a & 0xFFFu) + j * ((stp.a >> 12) & 0x3FFu);
-            stepl[s * 32 + lane] = v;
-            if (lane == 0) {
-                const uint32_t pair = (stp.a >> 23) & 1u;
-                const uint32_t fl = ((stp.a >> 22) & 1u) | (pair << 1) | (((stp.a >> 24) & 1u) << 2);
-                stepu[s] = make_uint4(fl | ((2u * ((stp.b >> 15) & 15u)) << 8), pair ? (stp.b & 31u) : esh,
-                                      (stp.b >> 5) & 31u, stp.c & 0xFFFFu);
-            }
-        }
-    }
     __syncthreads();
-    // Expand codebooks into lane-replicated fp16x2 tables.
-    for (int s = 0; s < hp.n_seg; ++s) {
-        const DecSegTbl tb = hp.seg[s];
-        const uint32_t cm = (1u << tb.bw) - 1u, smk = (1u << tb.sbits) - 1u;
-        for (uint32_t i = tid; i < tb.n_words; i += kThreads) {
-            const uint32_t e = i >> tb.rep_shift;
-            uint32_t v;
-            if (tb.pair) v = cbk[tb.cb_off + ((e & smk) & cm)] | (uint32_t(cbk[tb.cb_off + ((e >> tb.sbits) & cm)]) << 16);
-            else v = cbk[tb.cb_off + (e & cm)];
-            lut[tb.word_off + i] = v;
-        }
-    }
-    {
-        const uint32_t vm = (1u << P.plan.v_bits) - 1u, smk = (1u << VB) - 1u;
-        for (uint32_t i = tid; i < (uint32_t)P.plan.v_n_words; i += kThreads) {
-            const uint32_t e = i >> VCfg<VB>::REP_SHIFT;
-            lut[hp.v_word_off + i] = cbk[512 + ((e & smk) & vm)] | (uint32_t(cbk[512 + ((e >> VB) & vm)]) << 16);
-        }
-    }
-    __syncthreads();
-
     const size_t bh_kp = (size_t)b * P.kp_sb + (size_t)h * P.kp_sh;
     const size_t bh_kn = (size_t)b * P.kn_sb + (size_t)h * P.kn_sh;
     const size_t bh_vp = (size_t)b * P.vp_sb + (size_t)h * P.vp_sh;
     const size_t bh_vn = (size_t)b * P.vn_sb + (size_t)h * P.vn_sh;
-
     if (warp == kConsumerWarps) {
         // ------------------------------ producer ------------------------------
+        // Starts streaming at once; the consumer warps build their tables meanwhile.
         if (lane == 0) {
             const uint64_t pol = l2_evict_first_policy();
             for (int it = 0; it < n_tiles; ++it) {
@@ -214,7 +165,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
                 mbar_arrive_expect_tx(&full[st], total);
                 for (int c = 0; c < 4; ++c) {
                     const uint8_t* al = src[c] - (reinterpret_cast<uintptr_t>(src[c]) & 15u);
-                    #ifdef BGTQ_EXP_NO_HINT
+#ifdef BGTQ_EXP_NO_HINT
                     bulk_g2s(sb + dst[c], al, sz[c], &full[st]);
 #else
                     bulk_g2s_hint(sb + dst[c], al, sz[c], &full[st], pol);
@@ -224,6 +175,59 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
         }
         return;
     }
+    // ------------------- consumer warps: tables first (named barrier 1 = consumers only) -------------------
+    {
+        const BgtqHeadDesc& d = P.desc[h];
+        for (int i = tid; i < 528; i += kConsumerWarps * 32) cbk[i] = i < 512 ? d.codebook[i] : d.v_lut[i - 512];
+    }
+    if (warp == 0) {   // lane (r, j): query r, this lane's 4 codes of every k-tile
+        const int r = lane >> 2, j = lane & 3;
+        const bool q_ok = r < P.gqa;
+        const __half* qrow = P.q_rot + ((size_t)b * P.n_q + (size_t)h * P.gqa + (q_ok ? r : 0)) * kHD;
+        for (int s = 0; s < hp.n_steps; ++s) {
+            const DecStep stp = hp.steps[s];
+            const int d0 = (int)(stp.q & 0xFFu) + j * (int)((stp.q >> 8) & 0x3Fu);
+            const int end = (int)((stp.q >> 14) & 0xFFu);
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(qrow + d0);
+            const uint32_t esh = (stp.b >> 10) & 31u;
+            uint4 v;
+            v.x = (q_ok && d0 < end) ? __ldg(src) : 0u;
+            v.y = (q_ok && d0 + 2 < end) ? __ldg(src + 1) : 0u;
+            v.z = lut_rel + (stp.c >> 16) + (((uint32_t)lane << 2) & ((1u << esh) - 1u));
+            v.w = (stp.a & 0xFFFu) + j * ((stp.a >> 12) & 0x3FFu);
+            stepl[s * 32 + lane] = v;
+        }
+    }
+    if (warp == 1 && lane < hp.n_seg) {   // per segment: {n_kt | kt/unit << 8 | pair << 16 | norm offset << 20,
+                                          //  first rotate, rotate step | pair stride << 8, scaled index mask}
+        const DecSegTbl tb = hp.seg[lane];
+        const uint32_t esh = tb.rep_shift + 2u;
+        const uint32_t mask = (tb.pair ? (1u << (2 * tb.sbits)) - 1u : (1u << tb.bw) - 1u) << esh;
+        stepu[lane] = make_uint4(tb.n_kt | ((uint32_t)tb.kt_per_unit << 8) | ((uint32_t)tb.pair << 16) |
+                                     ((2u * lane) << 20),
+                                 esh, (4u * tb.sbits) | ((2u * tb.sbits) << 8), mask);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+    // Expand codebooks into lane-replicated fp16x2 tables.
+    for (int s = 0; s < hp.n_seg; ++s) {
+        const DecSegTbl tb = hp.seg[s];
+        const uint32_t cm = (1u << tb.bw) - 1u, smk = (1u << tb.sbits) - 1u;
+        for (uint32_t i = tid; i < tb.n_words; i += kConsumerWarps * 32) {
+            const uint32_t e = i >> tb.rep_shift;
+            uint32_t v;
+            if (tb.pair) v = cbk[tb.cb_off + ((e & smk) & cm)] | (uint32_t(cbk[tb.cb_off + ((e >> tb.sbits) & cm)]) << 16);
+            else v = cbk[tb.cb_off + (e & cm)];
+            lut[tb.word_off + i] = v;
+        }
+    }
+    {
+        const uint32_t vm = (1u << P.plan.v_bits) - 1u, smk = (1u << VB) - 1u;
+        for (uint32_t i = tid; i < (uint32_t)P.plan.v_n_words; i += kConsumerWarps * 32) {
+            const uint32_t e = i >> VCfg<VB>::REP_SHIFT;
+            lut[hp.v_word_off + i] = cbk[512 + ((e & smk) & vm)] | (uint32_t(cbk[512 + ((e >> VB) & vm)]) << 16);
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
 
     // -------------------------------- consumers --------------------------------
     const int r = lane >> 2, j = lane & 3;
@@ -250,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     const uint32_t lane4 = (uint32_t)lane << 2;
     constexpr uint32_t kVSh = VCfg<VB>::REP_SHIFT + 2;
     const uint32_t vtbl = lut_rel + (hp.v_word_off << 2) + (lane4 & ((1u << kVSh) - 1u));
-    const int n_steps = hp.n_steps;
+    const int n_seg = hp.n_seg;
 
     for (int it = 0; it < n_tiles; ++it) {
         const int st = it % kStages, use = it / kStages;
@@ -264,55 +268,66 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
         if (warp * kWarpTok < nt) {
             // ---------------- S^T = Khat . Qrot^T for two 16-token row tiles ----------------
             float S[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            uint32_t cur[4] = {0u, 0u, 0u, 0u};
-            float nrm[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t rowK = sb + k_row_al, rowN = sb + kn_row;
-#pragma unroll 2
-            for (int s = 0; s < n_steps; ++s) {
-                const uint4 su = stepu[s];
-                const uint4 sl = stepl[s * 32 + lane];
-                if (su.x & 1u) {            // next unit: 32 bits of this lane's run, four tokens
-                    const uint32_t pbit = k_p0 + sl.w;
-                    const uint32_t wa = rowK + ((pbit >> 5) << 2);
+            int s = 0;
+            for (int sg = 0; sg < n_seg; ++sg) {
+                const uint4 su = stepu[sg];
+                const int n_kt = su.x & 0xFF, kpu = (su.x >> 8) & 0xFF;
+                const uint32_t mask = su.w, dr = su.z & 0xFFu, dp = su.z >> 8;
+                float nrm[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        cur[i] = __funnelshift_r(ld32(sm, wa + i * k_row8), ld32(sm, wa + i * k_row8 + 4), pbit);
-                }
-                if (su.x & 4u) {            // new segment: its per-token norms
-                    const uint32_t sg = rowN + (su.x >> 8);
+                for (int i = 0; i < 4; ++i)
+                    nrm[i] = __half2float(__ushort_as_half((unsigned short)ld16(sm, rowN + (su.x >> 20) + i * kn_row8)));
+                float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                uint32_t cur[4] = {0u, 0u, 0u, 0u};
+                uint32_t r0 = su.y;
+                int left = 0;
+                for (int kt = 0; kt < n_kt; ++kt, ++s) {
+                    const uint4 sl = stepl[s * 32 + lane];
+                    if (left == 0) {        // next unit: 32 bits of this lane's run, four tokens
+                        const uint32_t pbit = k_p0 + sl.w;
+                        const uint32_t wa = rowK + ((pbit >> 5) << 2);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        nrm[i] = __half2float(__ushort_as_half((unsigned short)ld16(sm, sg + i * kn_row8)));
-                }
-                const uint32_t mask = su.w, tb = sl.z;
-                uint32_t lo[4], hi[4];   // fp16x2 of codes (0,1) and (2,3) of this k-tile, per token
-                if (su.x & 2u) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        lo[i] = ld32(sm, (rotl32(cur[i], su.y) & mask) | tb);
-                        hi[i] = ld32(sm, (rotl32(cur[i], su.z) & mask) | tb);
+                        for (int i = 0; i < 4; ++i)
+                            cur[i] = __funnelshift_r(ld32(sm, wa + i * k_row8), ld32(sm, wa + i * k_row8 + 4), pbit);
+                        left = kpu;
+                        r0 = su.y;
                     }
-                } else {                   // raw bytes, one code per lookup; su.y = log2(entry stride)
+                    --left;
+                    const uint32_t tb = sl.z;
+                    uint32_t lo[4], hi[4];   // fp16x2 of codes (0,1) and (2,3) of this k-tile, per token
+                    if (su.x & 0x10000u) {
+                        const uint32_t r1 = r0 - dp;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t c0 = ld32(sm, (rotl32(cur[i], su.y) & mask) | tb);
-                        const uint32_t c1 = ld32(sm, (rotl32(cur[i], su.y + 24u) & mask) | tb);
-                        const uint32_t c2 = ld32(sm, (rotl32(cur[i], su.y + 16u) & mask) | tb);
-                        const uint32_t c3 = ld32(sm, (rotl32(cur[i], su.y + 8u) & mask) | tb);
-                        lo[i] = c0 | (c1 << 16);
-                        hi[i] = c2 | (c3 << 16);
+                        for (int i = 0; i < 4; ++i) {
+                            lo[i] = ld32(sm, (rotl32(cur[i], r0) & mask) | tb);
+                            hi[i] = ld32(sm, (rotl32(cur[i], r1) & mask) | tb);
+                        }
+                    } else {                   // raw bytes, one code per lookup
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint32_t c0 = ld32(sm, (rotl32(cur[i], r0) & mask) | tb);
+                            const uint32_t c1 = ld32(sm, (rotl32(cur[i], r0 + 24u) & mask) | tb);
+                            const uint32_t c2 = ld32(sm, (rotl32(cur[i], r0 + 16u) & mask) | tb);
+                            const uint32_t c3 = ld32(sm, (rotl32(cur[i], r0 + 8u) & mask) | tb);
+                            lo[i] = c0 | (c1 << 16);
+                            hi[i] = c2 | (c3 << 16);
+                        }
+                    }
+                    r0 -= dr;
+                    const uint32_t bq[2] = {sl.x, sl.y};
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const uint32_t a[4] = {lo[2 * u], lo[2 * u + 1], hi[2 * u], hi[2 * u + 1]};
+                        mma_16816(acc[u], a, bq);
                     }
                 }
-                const uint32_t bq[2] = {sl.x, sl.y};
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const uint32_t a[4] = {lo[2 * u], lo[2 * u + 1], hi[2 * u], hi[2 * u + 1]};
-                    float acc[4];
-                    mma_16816_z(acc, a, bq);
-                    S[u][0] = fmaf(nrm[2 * u], acc[0], S[u][0]);
-                    S[u][1] = fmaf(nrm[2 * u], acc[1], S[u][1]);
-                    S[u][2] = fmaf(nrm[2 * u + 1], acc[2], S[u][2]);
-                    S[u][3] = fmaf(nrm[2 * u + 1], acc[3], S[u][3]);
+                    S[u][0] = fmaf(nrm[2 * u], acc[u][0], S[u][0]);
+                    S[u][1] = fmaf(nrm[2 * u], acc[u][1], S[u][1]);
+                    S[u][2] = fmaf(nrm[2 * u + 1], acc[u][2], S[u][2]);
+                    S[u][3] = fmaf(nrm[2 * u + 1], acc[u][3], S[u][3]);
                 }
             }
             // ---------------- online softmax (log2 domain) over the 32 tokens ----------------
@@ -391,10 +406,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
                         // index pre-scaled by the entry stride: rotate so the field sits at bit kVSh
                         const uint32_t rt = (32u + kVSh - FW * k) & 31u;
                         uint32_t a[4];
-                        a[0] = hmul2_u32(ld32(sm, vtbl + (rotl32(xab, rt) & IMS)), nab);
-                        a[1] = hmul2_u32(ld32(sm, vtbl + (rotl32(yab, rt) & IMS)), nab);
-                        a[2] = hmul2_u32(ld32(sm, vtbl + (rotl32(xcd, rt) & IMS)), ncd);
-                        a[3] = hmul2_u32(ld32(sm, vtbl + (rotl32(ycd, rt) & IMS)), ncd);
+                        a[0] = hmul2_u32(ld32(sm, (rotl32(xab, rt) & IMS) | vtbl), nab);
+                        a[1] = hmul2_u32(ld32(sm, (rotl32(yab, rt) & IMS) | vtbl), nab);
+                        a[2] = hmul2_u32(ld32(sm, (rotl32(xcd, rt) & IMS) | vtbl), ncd);
+                        a[3] = hmul2_u32(ld32(sm, (rotl32(ycd, rt) & IMS) | vtbl), ncd);
                         mma_16816(O[g * PER + k], a, pf[u]);
                     }
                 }
@@ -512,20 +527,25 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const Bgt
             tb.pair = pair;
             tb.n_words = entries << tb.rep_shift;
             if (tb.n_words * 4 > kLutTableBytes) return BGTQ_E_UNSUPPORTED;
+            const int n_kt_s = (len + 15) / 16;
+            const int cap_s = tb.sbits == 1 ? 32 : tb.sbits == 2 ? 16 : tb.sbits == 8 ? 4 : 8;
+            tb.n_kt = (uint8_t)n_kt_s;
+            tb.kt_per_unit = (uint8_t)(cap_s / 4);
         }
         // Place tables largest first: every size is a power of two, so each lands on a multiple of its size.
+        // (the V table takes part: index d.n_seg)
         uint32_t word = 0;
-        bool placed[BGTQ_MAX_SEGMENTS] = {false};
-        for (int n = 0; n < d.n_seg; ++n) {
+        bool placed[BGTQ_MAX_SEGMENTS + 1] = {false};
+        auto words_of = [&](int s) { return s < d.n_seg ? hp.seg[s].n_words : pl.v_n_words; };
+        for (int n = 0; n <= d.n_seg; ++n) {
             int best = -1;
-            for (int s = 0; s < d.n_seg; ++s)
-                if (!placed[s] && (best < 0 || hp.seg[s].n_words > hp.seg[best].n_words)) best = s;
+            for (int s = 0; s <= d.n_seg; ++s)
+                if (!placed[s] && (best < 0 || words_of(s) > words_of(best))) best = s;
             placed[best] = true;
-            hp.seg[best].word_off = (uint16_t)word;
-            word += hp.seg[best].n_words;
+            if (best < d.n_seg) hp.seg[best].word_off = (uint16_t)word;
+            else hp.v_word_off = word;
+            word += words_of(best);
         }
-        hp.v_word_off = word;     // V table last; addressed by addition, no alignment needed
-        word += pl.v_n_words;
         if (word * 4 > 0xFFFFu) return BGTQ_E_TOOBIG;
         lut_words = word > lut_words ? word : lut_words;
 
@@ -564,13 +584,27 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const Bgt
 
 extern "C" __attribute__((visibility("default"))) int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv,
                                                                                  int32_t n_tokens) {
+    // Pick the split count with the shortest makespan, counted in CTA tiles: a CTA works through
+    // ceil(tiles / splits) tiles, two CTAs are resident per SM, and CTAs beyond the resident slots
+    // queue behind the first wave; every CTA also pays a fixed set-up (tables, first tile latency, final
+    // merge) worth about one and a half tiles.  Ties go to fewer splits (fewer partials to merge).
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int pairs = n_batch * n_kv > 0 ? n_batch * n_kv : 1;
-    const int by_len = (n_tokens + 511) / 512;  // keep at least 512 tokens per split
-    int want = (2 * sms + pairs - 1) / pairs;   // two CTAs per SM
-    if (want > by_len) want = by_len;
-    return want < 1 ? 1 : want;
+    const long pairs = (long)n_batch * n_kv > 0 ? (long)n_batch * n_kv : 1;
+    const long tiles = (n_tokens + kTileTok - 1) / kTileTok;
+    if (tiles <= 1) return 1;
+    const long slots = 2L * sms;
+    long best = 1, best_span = -1;
+    for (long ns = 1; ns <= tiles && ns <= 512; ++ns) {
+        const long per = (tiles + ns - 1) / ns;                  // tiles per CTA
+        const long used = (tiles + per - 1) / per;               // non-empty splits
+        const long ctas = pairs * used;
+        const long waves = (ctas + slots - 1) / slots;
+        // single-CTA SMs run their CTA faster; charge a half-occupied machine a little more per tile
+        const long span = waves * (per * 16 + 24) + (ctas < slots ? (slots - ctas) * per * 4 / slots : 0);
+        if (best_span < 0 || span < best_span) { best_span = span; best = used; }
+    }
+    return (int)best;
 }
 
 extern "C" __attribute__((visibility("default"))) int bgtq_decode(

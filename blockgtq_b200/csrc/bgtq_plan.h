@@ -29,6 +29,9 @@ struct DecSegTbl {
     uint8_t rep_shift;   // log2 of the per-lane replication
     uint8_t pair;        // 1: entry = two codes -> fp16x2, 0: one code -> fp16
     uint32_t n_words;
+    uint8_t n_kt;        // MMA k-tiles of the segment
+    uint8_t kt_per_unit; // k-tiles fed by one 32-bit unit load
+    uint16_t pad;
 };
 
 // One m16n8k16 k-tile.
