@@ -7,9 +7,14 @@ from .quantizer import (BlockGTQQuantizer, build_batched_encode_args, build_pack
                         compress_v_nibble4_batched, compress_v_packed_batched)
 from .attention import fused_blockgtq_decode_attention
 from .packed_kv_manager import BlockGTQKVManager, decode_step
+from .production_cache import BlockGTQProductionCache
+from .production_decode import production_decode_step, production_prefill
+from .calibration import bake_q_rotations, build_quantizers, collect_qk_activations
 
 __all__ = [
     "greedy_bit_allocation", "BlockGTQQuantizer", "build_batched_encode_args", "build_pack_meta",
     "compress_k_packed_batched", "compress_v_packed_batched", "compress_k_mixed_batched",
     "compress_v_nibble4_batched", "fused_blockgtq_decode_attention", "BlockGTQKVManager", "decode_step",
+    "BlockGTQProductionCache", "production_decode_step", "production_prefill", "collect_qk_activations",
+    "build_quantizers", "bake_q_rotations",
 ]

@@ -19,7 +19,7 @@ MAX_SEG = 8
 N_BINS = 256
 
 OK = 0
-ENC_K_NORMS_F16, ENC_K_MIXED, ENC_V_NIBBLE, ENC_SKIP_K, ENC_SKIP_V = 1, 2, 4, 8, 16
+ENC_K_NORMS_F16, ENC_K_MIXED, ENC_V_NIBBLE, ENC_SKIP_K, ENC_SKIP_V, ENC_FORCE_SIMT = 1, 2, 4, 8, 16, 32
 DEC_K_MIXED, DEC_V_NIBBLE = 1, 2
 
 

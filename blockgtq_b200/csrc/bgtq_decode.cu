@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
         const uint32_t esh = tb.rep_shift + 2u;
         const uint32_t mask = (tb.pair ? (1u << (2 * tb.sbits)) - 1u : (1u << tb.bw) - 1u) << esh;
         stepu[lane] = make_uint4(tb.n_kt | ((uint32_t)tb.kt_per_unit << 8) | ((uint32_t)tb.pair << 16) |
-                                     ((2u * lane) << 20),
+                                     ((uint32_t)tb.f16_norm << 17) | ((2u * lane) << 20),
                                  esh, (4u * tb.sbits) | ((2u * tb.sbits) << 8), mask);
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
@@ -274,10 +274,18 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
                 const uint4 su = stepu[sg];
                 const int n_kt = su.x & 0xFF, kpu = (su.x >> 8) & 0xFF;
                 const uint32_t mask = su.w, dr = su.z & 0xFFu, dp = su.z >> 8;
+                // Norm handling: bit-packed layout scales the fp32 dot product of a segment by its fp16
+                // norm; the nibble layout rounds centroid * norm to fp16 per element before the product
+                // (fused_packed_attention.py:1449-1452), so there the norm is folded into the operand.
+                const bool f16n = su.x & 0x20000u;
                 float nrm[4];
+                uint32_t n2[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    nrm[i] = __half2float(__ushort_as_half((unsigned short)ld16(sm, rowN + (su.x >> 20) + i * kn_row8)));
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t nh = ld16(sm, rowN + (su.x >> 20) + i * kn_row8);
+                    n2[i] = nh | (nh << 16);
+                    nrm[i] = f16n ? 1.0f : __half2float(__ushort_as_half((unsigned short)nh));
+                }
                 float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
                 uint32_t cur[4] = {0u, 0u, 0u, 0u};
                 uint32_t r0 = su.y;
@@ -315,6 +323,13 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
                         }
                     }
                     r0 -= dr;
+                    if (f16n) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            lo[i] = hmul2_u32(lo[i], n2[i]);
+                            hi[i] = hmul2_u32(hi[i], n2[i]);
+                        }
+                    }
                     const uint32_t bq[2] = {sl.x, sl.y};
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
@@ -531,6 +546,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const Bgt
             const int cap_s = tb.sbits == 1 ? 32 : tb.sbits == 2 ? 16 : tb.sbits == 8 ? 4 : 8;
             tb.n_kt = (uint8_t)n_kt_s;
             tb.kt_per_unit = (uint8_t)(cap_s / 4);
+            tb.f16_norm = ((flags & BGTQ_DEC_K_MIXED) && len >= 16 && s < 5) ? 1 : 0;   // reference: segments 5-7 stay scalar
         }
         // Place tables largest first: every size is a power of two, so each lands on a multiple of its size.
         // (the V table takes part: index d.n_seg)

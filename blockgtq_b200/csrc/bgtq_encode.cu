@@ -14,42 +14,15 @@
 // position for kRows rows and only walks the input positions of its own
 // width group (the K rotation is block diagonal); V's rotation is dense.
 #include "bgtq_common.cuh"
+#include "bgtq_encode_params.cuh"
 
 namespace bgtq {
 namespace {
 
 constexpr int kRows = 8;
 
-struct EncParams {
-    const BgtqHeadDesc* desc;
-    const float* rot_k;
-    const float* rot_v;
-    const __half* k;
-    const __half* v;
-    int64_t k_sb, k_sh, k_ss, v_sb, v_sh, v_ss;
-    int32_t n_batch, n_kv, n_tok, t0;
-    const int32_t* pos_dev;
-    uint8_t* kp; int64_t kp_sb, kp_sh, kp_st; int32_t kp_row_bytes;
-    void* kn; int64_t kn_sb, kn_sh, kn_st; int32_t kn_count;
-    uint8_t* vp; int64_t vp_sb, vp_sh, vp_st;
-    __half* vn; int64_t vn_sb, vn_sh, vn_st;
-    uint8_t* k_codes;
-    uint8_t* v_codes;
-    int32_t flags;
-};
-
-// Byte `t` of a bit-packed run: codes of width bw (1..4) starting at codes[0].
 __device__ __forceinline__ uint32_t pack_byte(const uint8_t* codes, int n, int bw, int t) {
-    const int bit0 = t * 8;
-    uint32_t out = 0;
-    int i = bit0 / bw;
-    for (int pos = i * bw; pos < bit0 + 8; pos += bw, ++i) {
-        if (i >= n) break;
-        const uint32_t c = codes[i] & ((1u << bw) - 1u);
-        const int sh = pos - bit0;
-        out |= sh >= 0 ? (c << sh) : (c >> (-sh));
-    }
-    return out & 0xFFu;
+    return enc_pack_byte(codes, n, bw, t);
 }
 
 // Copy one 128x128 fp32 rotation into shared memory with every load independent (the matrix is
@@ -477,6 +450,14 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
     P.vn = static_cast<__half*>(v_norms); P.vn_sb = vn_sb; P.vn_sh = vn_sh; P.vn_st = vn_st;
     P.k_codes = k_codes; P.v_codes = v_codes; P.flags = flags;
     const int64_t n_rows = (int64_t)n_batch * n_tok;
+    {   // bulk row counts go to the tensor-core kernel when every input row is 16-byte aligned
+        auto al16 = [](const void* ptr, int64_t a, int64_t b2, int64_t c) {
+            return ptr == nullptr || (((reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) && a % 8 == 0 && b2 % 8 == 0 && c % 8 == 0);
+        };
+        if (n_rows >= 64 && !(flags & BGTQ_ENC_FORCE_SIMT) && al16(do_k ? k : nullptr, k_sb, k_sh, k_ss) &&
+            al16(do_v ? v : nullptr, v_sb, v_sh, v_ss))
+            return launch_encode_tc(P, static_cast<cudaStream_t>(stream));
+    }
     const int64_t gx = (n_rows + kRows - 1) / kRows;
     if (gx > 0x7fffffffLL || n_kv > 65535) return BGTQ_E_TOOBIG;
     dim3 grid((unsigned)gx, n_kv, 2);

@@ -1,0 +1,42 @@
+// Launch parameters and helpers shared by the encoder kernels.
+#pragma once
+#include "bgtq_common.cuh"
+
+namespace bgtq {
+
+struct EncParams {
+    const BgtqHeadDesc* desc;
+    const float* rot_k;
+    const float* rot_v;
+    const __half* k;
+    const __half* v;
+    int64_t k_sb, k_sh, k_ss, v_sb, v_sh, v_ss;
+    int32_t n_batch, n_kv, n_tok, t0;
+    const int32_t* pos_dev;
+    uint8_t* kp; int64_t kp_sb, kp_sh, kp_st; int32_t kp_row_bytes;
+    void* kn; int64_t kn_sb, kn_sh, kn_st; int32_t kn_count;
+    uint8_t* vp; int64_t vp_sb, vp_sh, vp_st;
+    __half* vn; int64_t vn_sb, vn_sh, vn_st;
+    uint8_t* k_codes;
+    uint8_t* v_codes;
+    int32_t flags;
+};
+
+// Byte `t` of a bit-packed run: codes of width bw (1..4) starting at codes[0].
+__device__ __forceinline__ uint32_t enc_pack_byte(const uint8_t* codes, int n, int bw, int t) {
+    const int bit0 = t * 8;
+    uint32_t out = 0;
+    int i = bit0 / bw;
+    for (int pos = i * bw; pos < bit0 + 8; pos += bw, ++i) {
+        if (i >= n) break;
+        const uint32_t c = codes[i] & ((1u << bw) - 1u);
+        const int sh = pos - bit0;
+        out |= sh >= 0 ? (c << sh) : (c >> (-sh));
+    }
+    return out & 0xFFu;
+}
+
+// Tensor-core bulk path (bgtq_encode_tc.cu).  Rows must be 16-byte aligned.
+int launch_encode_tc(const EncParams& P, cudaStream_t stream);
+
+}  // namespace bgtq

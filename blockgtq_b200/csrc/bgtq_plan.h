@@ -31,7 +31,8 @@ struct DecSegTbl {
     uint32_t n_words;
     uint8_t n_kt;        // MMA k-tiles of the segment
     uint8_t kt_per_unit; // k-tiles fed by one 32-bit unit load
-    uint16_t pad;
+    uint8_t f16_norm;    // 1: fold the norm into each value as fp16(centroid * norm) (nibble-layout numerics)
+    uint8_t pad;
 };
 
 // One m16n8k16 k-tile.

@@ -33,7 +33,7 @@ class BlockGTQKVManager:
                  batch_size: int = 1, k_avg_bits: float = 3.0, v_bits: int = 3, device="cuda",
                  n_sink: int = 0, recent_window: int = 0, block_size: int = 1,
                  min_bits: int = 1, max_bits: int = 8, rotation_threshold: int = 2,
-                 use_cuda_graph: bool = None):
+                 use_cuda_graph: bool = None, k_mixed: bool = False, v_nibble: bool = False):
         if head_dim != HD:
             raise ValueError("head_dim must be 128")
         if n_kv_heads > 8 or n_q_heads // n_kv_heads > 8:
@@ -61,6 +61,11 @@ class BlockGTQKVManager:
         self._k_buf = self._v_buf = None
         self.n_packed = 0                     # tokens in the packed region
         self._status = None
+        # storage layout: bit-packed (this class in the reference) or the production cache's
+        # nibble/raw "mixed" K rows with corrected norms and 4-bit V rows (production_cache.py:60-86)
+        self.k_mixed, self.v_nibble = bool(k_mixed), bool(v_nibble)
+        self._enc_flags = (_lib.ENC_K_MIXED if k_mixed else 0) | (_lib.ENC_V_NIBBLE if v_nibble else 0)
+        self._dec_flags = (_lib.DEC_K_MIXED if k_mixed else 0) | (_lib.DEC_V_NIBBLE if v_nibble else 0)
         # single-token decode steps are captured once per layer and replayed (the reference graphs only
         # its T=1 encode, packed_kv_manager.py:182-257); needs the plain (unbuffered) cache
         self._use_graph = (not self._buffered) if use_cuda_graph is None else bool(use_cuda_graph)
@@ -111,7 +116,9 @@ class BlockGTQKVManager:
     def _ensure_storage(self):
         if self._k_packed is not None:
             return
-        vpb = packed_v_bytes(self.hd, self.v_bits)
+        vpb = self.hd // 2 if self.v_nibble else packed_v_bytes(self.hd, self.v_bits)
+        if self.k_mixed:
+            self._max_k_packed_bytes = max(lt.max_mixed_bytes for lt in self._layers if lt is not None)
         # token capacity rounded up so 64-token tiles never leave the allocation
         cap = ((self.max_T + 63) // 64) * 64
         shape = (self.n_layers, self.B, self.n_kv, cap)
@@ -142,7 +149,7 @@ class BlockGTQKVManager:
         li = layer_idx
         assert k.shape[2] == t_end - t_start
         encode(self._layers[li], k.to(torch.float16), v.to(torch.float16), t_start,
-               self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li])
+               self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li], flags=self._enc_flags)
 
     def init_from_cache(self, past_key_value):
         """Bulk-encode an HF cache after prefill (packed_kv_manager.py:259-266).  Accepts the
@@ -210,7 +217,7 @@ class BlockGTQKVManager:
             if f1 > a0:                                        # new tokens that go straight to packed rows
                 s0, s1 = max(f0, a0) + ns - t, f1 + ns - t
                 encode(self._layers[li], k[:, :, s0:s1], v[:, :, s0:s1], max(f0, a0), self._k_packed[li],
-                       self._k_norms[li], self._v_packed[li], self._v_norms[li])
+                       self._k_norms[li], self._v_packed[li], self._v_norms[li], flags=self._enc_flags)
         if a1 > lo:                                            # new tokens that stay recent
             slots = self._ring_slots(lo, a1)
             kb.index_copy_(2, slots, k[:, :, lo + ns - t:a1 + ns - t])
@@ -223,7 +230,8 @@ class BlockGTQKVManager:
             return
         slots = self._ring_slots(f_lo, f_hi)
         encode(self._layers[li], self._k_buf[li].index_select(2, slots), self._v_buf[li].index_select(2, slots),
-               f_lo, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li])
+               f_lo, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
+               flags=self._enc_flags)
 
     # -- graph replay of one layer step ----------------------------------------------------------
     def static_qkv(self) -> torch.Tensor:
@@ -249,11 +257,12 @@ class BlockGTQKVManager:
         gq, gk, gv = self.static_inputs()
         baked = all(self.quantizers[li][h]._q_perm_baked for h in range(self.n_kv))
         step_prepare(lt, None if baked else gq, gk, gv, 0, self._k_packed[li], self._k_norms[li],
-                     self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos)
+                     self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos,
+                     flags=self._enc_flags)
         q_rot = gq[:, :, 0].contiguous() if baked else self._q_rot
         decode(lt, q_rot, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
                0, self.max_T, n_splits=self._n_splits, scale=self.scale, status=self._status,
-               part_o=self._part_o, part_lse=self._part_lse, pos_dev=self._pos, pos_add=1)
+               part_o=self._part_o, part_lse=self._part_lse, pos_dev=self._pos, pos_add=1, flags=self._dec_flags)
         combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li])
 
     def _replay_layer(self, li: int, q, k_new, v_new) -> torch.Tensor:
@@ -319,7 +328,7 @@ class BlockGTQKVManager:
         q_rot = q.contiguous() if baked else rotate_q(lt, q)
         part_o, part_lse = decode(lt, q_rot, self._k_packed[li], self._k_norms[li], self._v_packed[li],
                                   self._v_norms[li], lo, hi, n_splits=n_splits, scale=self.scale,
-                                  status=self._status)
+                                  status=self._status, flags=self._dec_flags)
         buf_o = buf_lse = None
         if self._buffered and with_buffers:
             buf_o, buf_lse = self._buffer_partial(li, q, n_sink_tok, n_packed, n_recent)

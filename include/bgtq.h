@@ -82,6 +82,7 @@ const char* bgtq_error_string(int code);       /* host pointer to a static strin
 #define BGTQ_ENC_V_NIBBLE 4       /* V rows as 4-bit nibbles regardless of v_bits */
 #define BGTQ_ENC_SKIP_K 8
 #define BGTQ_ENC_SKIP_V 16
+#define BGTQ_ENC_FORCE_SIMT 32  /* always use the small-batch fp32 kernel (>= 64 rows normally use tensor cores) */
 
 /* Encode K and V rows of all KV heads of one layer and write them straight
  * into their cache slots.

@@ -4,7 +4,7 @@ Run once, in a container where the reference checkout is available:
 
     TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/reference [manager]
 
-(a second argument regenerates only ``manager.npz``, which has its own random seed)
+(a second argument, ``manager`` or ``production``, regenerates only that fixture; each has its own seed)
 
 The reference's Triton kernels are executed by Triton's CPU interpreter
 (``tl.dot`` is a float32 ``np.matmul`` there), so the vectors are the
@@ -16,6 +16,7 @@ Fixtures
   encode_<case>.npz   K/V rows -> packed bytes, norms, unpacked codes, nibble/mixed layouts
   decode_<case>.npz   packed cache + query -> attention output and LSE per KV head
   manager.npz         BlockGTQKVManager: bulk encode + two append_and_attend steps, batch 2
+  production.npz      BlockGTQProductionCache (nibble/mixed layout): bulk encode + two decode steps, batch 1
 """
 import hashlib
 import os
@@ -248,6 +249,36 @@ def dump_manager(gen, T0=150, B=2, n_kv=2, gqa=2, steps=2):
     np.savez_compressed(os.path.join(HERE, "manager.npz"), **rec)
 
 
+def dump_production(gen, T0=150, n_kv=2, gqa=4, steps=2):
+    """BlockGTQProductionCache (nibble/mixed layout, batch 1): bulk encode + decode steps.  The T=1 encode
+    goes through the batched encoder instead of the CUDA-graph replay (same kernels, no GPU needed)."""
+    from blockgtq.production_cache import BlockGTQProductionCache
+    n_q = n_kv * gqa
+    qs, cal = make_quantizers("a3_1to8", n_kv, gen, gqa=gqa)
+    ba = [build_batched_encode_args(qs, device="cpu")]
+    ka = [[z.build_kernel_args() for z in qs]]
+    cache = BlockGTQProductionCache([qs], ba, ka, 1, n_kv, n_q, HD, T0 + steps + 2, v_bits=3, device="cpu")
+    cache._encode_graphed = lambda li, k, v, t: cache._encode_batched(li, k, v, t)
+    k0 = torch.stack([synth_head(gen, T0, 1)[1] for _ in range(n_kv)]).unsqueeze(0)
+    v0 = torch.randn(1, n_kv, T0, HD, generator=gen).half()
+    cache._encode_batched(0, k0, v0, 0)
+    cache.seq_len = T0
+    rec = {"alloc": np.stack([z.bit_allocation.numpy() for z in qs]), "k_init": k0.numpy(), "v_init": v0.numpy()}
+    for s in range(steps):
+        q = (torch.randn(1, n_q, 1, HD, generator=gen) * 2).half()
+        kn = torch.stack([synth_head(gen, 1, 1)[1] for _ in range(n_kv)]).unsqueeze(0)
+        vn = torch.randn(1, n_kv, 1, HD, generator=gen).half()
+        out = cache.encode_and_attend(0, q, kn, vn)
+        cache.increment_seq_len()
+        rec[f"q{s}"], rec[f"k{s}"], rec[f"v{s}"], rec[f"out{s}"] = q.numpy(), kn.numpy(), vn.numpy(), out.numpy()
+    T = cache.seq_len
+    rec["k_packed"] = cache.k_packed[:, :, :, :T].numpy()
+    rec["k_norms"] = cache.k_norms[:, :, :, :T].numpy()
+    rec["v_packed"] = cache.v_packed[:, :, :, :T].numpy()
+    rec["v_norms"] = cache.v_norms[:, :, :, :T].numpy()
+    np.savez_compressed(os.path.join(HERE, "production.npz"), **rec)
+
+
 def main():
     only = sys.argv[2] if len(sys.argv) > 2 else None
     gen = torch.Generator().manual_seed(20240607)
@@ -260,8 +291,12 @@ def main():
         if case in ("a3_1to6", "a3_1to8", "a2_1to8", "a4_rt1"):
             dump_decode(case, qs, gen)
         print("done", case, flush=True)
-    dump_manager(torch.Generator().manual_seed(777))
-    print("done manager")
+    if only in (None, "manager"):
+        dump_manager(torch.Generator().manual_seed(777))
+        print("done manager")
+    if only in (None, "production"):
+        dump_production(torch.Generator().manual_seed(778))
+        print("done production")
 
 
 if __name__ == "__main__":

@@ -226,3 +226,147 @@ def test_combine_and_buffer_vs_oracle():
             ro, rl = O.attend_fp16(q[b, hq:hq + 1].numpy(), kb[b, h, slots].numpy(), vb[b, h, slots].numpy(), 0.0884)
             np.testing.assert_allclose(bo[b, hq].cpu().numpy(), ro[0], atol=2e-5)
             np.testing.assert_allclose(bl[b, hq].cpu().numpy(), rl[0], atol=2e-5)
+
+
+@pytest.mark.parametrize("n_sink,window,bs", [(2, 5, 1), (3, 4, 3), (0, 6, 2)])
+def test_three_region_manager_vs_oracle(n_sink, window, bs):
+    """fp16 sink + packed middle + fp16 recent ring: every decode step against the float64 oracle built
+    from the same token stream (flush order of blockgtq/unaccelerated.py:226-233)."""
+    from blockgtq_b200 import BlockGTQKVManager
+    gen = torch.Generator().manual_seed(11)
+    B, n_kv, gqa = 2, 2, 4
+    n_q = n_kv * gqa
+    T0, steps = 9, 14
+    mgr = BlockGTQKVManager(1, n_q, n_kv, HD, max_seq_len=64, batch_size=B, k_avg_bits=3.0, v_bits=3, device=DEV,
+                            n_sink=n_sink, recent_window=window, block_size=bs)
+    cal = [synth_head(gen, 256, gqa) for _ in range(n_kv)]
+    mgr.calibrate(0, torch.stack([c[0] for c in cal]).float(), torch.stack([c[1] for c in cal]).float())
+    k_all = torch.stack([torch.stack([synth_head(gen, T0 + steps, 1)[1] for _ in range(n_kv)]) for _ in range(B)])
+    v_all = torch.randn(B, n_kv, T0 + steps, HD, generator=gen).half()
+    mgr._append_tokens(0, k_all[:, :, :T0].to(DEV), v_all[:, :, :T0].to(DEV), 0)      # bulk prefill
+    mgr.seq_len = T0
+    metas = [oracle_meta(mgr.quantizers[0][h]._tables, mgr.quantizers[0][h]._v_tables) for h in range(n_kv)]
+    for s in range(steps):
+        t = T0 + s
+        q = (torch.randn(B, n_q, 1, HD, generator=gen) * 2).half()
+        # regions the step must see: flushed count as of the previous step, new token still fp16
+        _sink, f_prev, _ = O.three_region_plan(t, n_sink, window, bs)
+        out = mgr.append_and_attend(0, q.to(DEV), k_all[:, :, t:t + 1].to(DEV), v_all[:, :, t:t + 1].to(DEV))
+        mgr.increment_seq_len()
+        torch.cuda.synchronize()
+        n_sk = min(t + 1, n_sink)
+        fp16_idx = list(range(n_sk)) + list(range(n_sink + f_prev, t + 1))
+        for b in range(B):
+            for h in range(n_kv):
+                sl = slice(h * gqa, (h + 1) * gqa)
+                qz = mgr.quantizers[0][h]
+                qr = O.rotate_q(q[b, sl, 0].numpy(), metas[h])
+                po, pl = O.attend_packed(qr, mgr._k_packed[0, b, h, :f_prev, :qz._total_packed_bytes].cpu().numpy(),
+                                         mgr._k_norms[0, b, h, :f_prev].cpu().numpy(),
+                                         mgr._v_packed[0, b, h, :f_prev].cpu().numpy(),
+                                         mgr._v_norms[0, b, h, :f_prev].cpu().numpy(), metas[h], mgr.scale)
+                bo, bl = O.attend_fp16(q[b, sl, 0].numpy(), k_all[b, h, fp16_idx].numpy(), v_all[b, h, fp16_idx].numpy(),
+                                       mgr.scale)
+                want, _ = O.combine(np.stack([po, bo]), np.stack([pl, bl]))
+                err = np.abs(out[b, sl, 0].float().cpu().numpy() - want).max()
+                assert err <= 3e-3, f"step {s} b{b} h{h}: {err}"
+        # packed rows hold exactly the non-sink tokens in order
+        _s2, f_now, n_rec = mgr._region_sizes(mgr.seq_len)
+        assert (_s2, f_now, n_rec) == O.three_region_plan(t + 1, n_sink, window, bs)
+    h = 0
+    enc = O.encode_k_packed(k_all[0, h, n_sink:n_sink + f_now].numpy(), metas[h])
+    got = mgr._k_packed[0, 0, h, :f_now, :mgr.quantizers[0][h]._total_packed_bytes].cpu().numpy()
+    assert (got != enc["packed"]).mean() < 2e-3
+
+
+def test_production_cache_matches_reference():
+    """Nibble/mixed layout end to end: bytes of the bulk encode and two decode steps vs the reference class."""
+    from blockgtq_b200 import BlockGTQProductionCache, BlockGTQQuantizer, build_batched_encode_args
+    g = load("production")
+    n_kv, T0 = g["k_init"].shape[1], g["k_init"].shape[2]
+    n_q = g["q0"].shape[1]
+    qs = []
+    for h in range(n_kv):
+        z = BlockGTQQuantizer(HD, avg_bits=3.0, device=DEV)
+        z.calibrate(None, None, bit_allocation=torch.from_numpy(g["alloc"][h]))
+        z.init_v_quantizer(v_bits=3, seed=42 + h)
+        qs.append(z)
+    ba = [build_batched_encode_args(qs, device=DEV)]
+    ka = [[z.build_kernel_args() for z in qs]]
+    for graph in (False, True):
+        cache = BlockGTQProductionCache([qs], ba, ka, 1, n_kv, n_q, HD, T0 + 4, v_bits=3, device=DEV,
+                                        use_cuda_graph=graph)
+        assert cache.k_packed.shape[-1] == g["k_packed"].shape[-1] and cache.vpb == HD // 2
+        cache._encode_batched(0, torch.from_numpy(g["k_init"]).to(DEV), torch.from_numpy(g["v_init"]).to(DEV), 0)
+        cache.seq_len = T0
+        for s in range(2):
+            out = cache.encode_and_attend(0, torch.from_numpy(g[f"q{s}"]).to(DEV), torch.from_numpy(g[f"k{s}"]).to(DEV),
+                                          torch.from_numpy(g[f"v{s}"]).to(DEV))
+            cache.increment_seq_len()
+            err = np.abs(out.cpu().numpy().astype(np.float64) - g[f"out{s}"].astype(np.float64)).max()
+            assert out.shape == g[f"out{s}"].shape and err <= ATOL, f"graph={graph} step {s}: {err}"
+        T = cache.seq_len
+        assert (cache.k_packed[:, :, :, :T].cpu().numpy() == g["k_packed"]).mean() > 0.9995
+        assert (cache.v_packed[:, :, :, :T].cpu().numpy() == g["v_packed"]).mean() > 0.9995
+        kn = cache.k_norms[:, :, :, :T].float().cpu().numpy()
+        assert (np.abs(kn - g["k_norms"].astype(np.float32)) <= np.abs(kn) * 2e-3 + 1e-6).all()
+
+
+@pytest.mark.parametrize("case", ["a3_1to8", "a4_rt1", "u3"])
+@pytest.mark.parametrize("mixed", [False, True])
+def test_encoder_tensor_core_and_fp32_paths_vs_oracle(case, mixed):
+    """Bulk row counts run the tensor-core encoder, small ones (or BGTQ_ENC_FORCE_SIMT) the fp32
+    one.  Both must give the oracle's codes off bin edges, and bytes that are the exact packing
+    of the codes each chose; rows land at the requested slot offset; ragged tile tails."""
+    from blockgtq_b200 import _lib
+    from blockgtq_b200.layer import encode
+    lt, tabs = _layer(case)
+    gen = torch.Generator().manual_seed(31)
+    B, n_kv, S, t0 = 3, 2, 150, 5          # 450 rows: 7 full 64-row tiles + a 2-row tail
+    k = torch.stack([torch.stack([synth_head(gen, S, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
+    v = torch.randn(B, n_kv, S, HD, generator=gen).half().to(DEV)
+    k[0, 0, 3] = 0
+    v[1, 1, 7] = 0
+    k[2, 1, 11] *= 1e-4
+    base = (_lib.ENC_K_MIXED | _lib.ENC_V_NIBBLE) if mixed else 0
+    outs = []
+    for extra in (0, _lib.ENC_FORCE_SIMT):
+        kb = lt.max_mixed_bytes if mixed else lt.max_tpb
+        kp = torch.full((B, n_kv, t0 + S + 2, kb), 0xEE, dtype=torch.uint8, device=DEV)
+        kn = torch.full((B, n_kv, t0 + S + 2, lt.max_ng), -1.0, dtype=torch.float32, device=DEV)
+        vp = torch.full((B, n_kv, t0 + S + 2, HD // 2 if mixed else lt.vpb), 0xEE, dtype=torch.uint8, device=DEV)
+        vn = torch.full((B, n_kv, t0 + S + 2), -1.0, dtype=torch.float16, device=DEV)
+        kc = torch.zeros(B, n_kv, S, HD, dtype=torch.uint8, device=DEV)
+        vc = torch.zeros(B, n_kv, S, HD, dtype=torch.uint8, device=DEV)
+        encode(lt, k, v, t0, kp, kn, vp, vn, flags=base | extra, k_codes=kc, v_codes=vc)
+        torch.cuda.synchronize()
+        outs.append([t.cpu().numpy() for t in (kp, kn, vp, vn, kc, vc)])
+    for kp, kn, vp, vn, kc, vc in outs:
+        # rows outside [t0, t0+S) untouched
+        assert (kp[:, :, :t0] == 0xEE).all() and (kp[:, :, t0 + S:] == 0xEE).all()
+        assert (vn[:, :, :t0] == -1).all() and (vn[:, :, t0 + S:] == -1).all()
+        for b in range(B):
+            for h in range(n_kv):
+                kt, vt = tabs[h]
+                meta = oracle_meta(kt, vt, lt.max_tpb)
+                ok = O.encode_k(k[b, h].cpu().numpy(), meta, dtype=np.float64)
+                bad = kc[b, h] != ok["codes"]
+                assert not (bad & ~ok["fragile"]).any()
+                live = np.abs(k[b, h].cpu().numpy()).max(axis=1) > 0    # an all-zero row sits exactly on the middle edge
+                assert bad[live].mean() < 2e-3
+                rows = kp[b, h, t0:t0 + S]
+                if mixed:
+                    pm = kt.pack_meta
+                    assert np.array_equal(rows, O.pack_k_mixed(kc[b, h], pm["nopack_start"], pm["nopack_len"], rows.shape[1]))
+                else:
+                    assert np.array_equal(rows, O.pack_k(kc[b, h], kt.segments, lt.max_tpb))
+                    np.testing.assert_allclose(kn[b, h, t0:t0 + S, :kt.n_groups], ok["norms"], rtol=3e-6, atol=1e-30)
+                ov = O.encode_v(v[b, h].cpu().numpy(), meta, dtype=np.float64)
+                vbad = vc[b, h] != ov["codes"]
+                assert not (vbad & ~ov["fragile"]).any()
+                vrows = vp[b, h, t0:t0 + S]
+                want = O.pack_nibble4(vc[b, h]) if mixed else O.pack_v(vc[b, h], vt.bits)
+                assert np.array_equal(vrows, want)
+    # the two paths agree with each other except on bin edges (already bounded above), norms to fp32 noise
+    np.testing.assert_allclose(outs[0][1], outs[1][1], rtol=1e-5, atol=1e-30)
+    assert (outs[0][4] != outs[1][4]).mean() < 2e-3
