@@ -454,7 +454,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
         auto al16 = [](const void* ptr, int64_t a, int64_t b2, int64_t c) {
             return ptr == nullptr || (((reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) && a % 8 == 0 && b2 % 8 == 0 && c % 8 == 0);
         };
-        if (n_rows >= 64 && !(flags & BGTQ_ENC_FORCE_SIMT) && al16(do_k ? k : nullptr, k_sb, k_sh, k_ss) &&
+        if (n_rows >= 64 && n_tok >= 16 && kn_count <= BGTQ_MAX_SEGMENTS && !(flags & BGTQ_ENC_FORCE_SIMT) && al16(do_k ? k : nullptr, k_sb, k_sh, k_ss) &&
             al16(do_v ? v : nullptr, v_sb, v_sh, v_ss))
             return launch_encode_tc(P, static_cast<cudaStream_t>(stream));
     }

@@ -1,27 +1,32 @@
 // Bulk (prefill) encoder on tensor cores.
 //
-// Same arithmetic contract as encode_kernel (bgtq_encode.cu) but organised for throughput:
-//   * persistent CTAs: one CTA owns (KV head, K or V) and loops over 64-row tiles, so the 128x128
-//     rotation is staged in shared memory once;
-//   * the rotation y = x_unit . W runs as fp16 m16n8k16 MMAs with fp32 accumulation.  The inputs are
-//     fp16 already, so x is exact; W (fp32) is split while staging into hi = fp16(W) and
-//     lo = fp16((W - hi) * 2^10), two MMAs per tile, y = acc_hi + acc_lo * 2^-10 (about 22 bits of W,
-//     the same order as fp32 summation noise).  Dividing by the group norm happens after the product;
-//     norm groups coincide with the diagonal blocks of the K rotation, so this equals normalising first;
-//   * K rows are gathered into packed-position order when the tile is loaded, which keeps the K
-//     rotation block diagonal: k-tiles outside the blocks of a 16-column output strip are skipped;
-//   * the epilogue bins / counts boundaries straight from the accumulators, writes codes to a shared
-//     tile, then packs bytes and stores rows.
+// Same arithmetic contract as encode_kernel (bgtq_encode.cu), organised for throughput:
+//   * a CTA serves one (KV head, K or V) role: the 128x128 fp32 rotation is staged in shared memory
+//     once, split into hi = fp16(W) and lo = fp16((W - hi) * 2^10);  y = (x . lo) * 2^-10 + x . hi with
+//     fp32 accumulation carries about 22 bits of W, the same order as fp32 summation noise (the fp16
+//     inputs x are exact);
+//   * each of the 16 warps runs its own loop over 16-row slabs, start to finish, with no CTA barrier:
+//     load rows (K gathered into packed-position order, which keeps its rotation block diagonal so that
+//     k-tiles outside the blocks of a 16-column strip are skipped), group norms, A fragments into
+//     registers, then the slab's shared memory is reused for the codes and the packed rows;
+//   * dividing by the group norm happens after the product (norm groups are the diagonal blocks);
+//   * packing is table driven: one task = up to 8 consecutive codes of one width -> up to 8 bytes;
+//   * packed rows of a slab are one contiguous byte range in the cache and leave as 32-bit stores.
 #include "bgtq_common.cuh"
 #include "bgtq_encode_params.cuh"
 
 namespace bgtq {
 namespace {
 
-constexpr int kTileRows = 64;
-constexpr int kWarps = 4;
-constexpr int kLd = 136;                 // halfs per shared row (128 + 8 pad): conflict-free ldmatrix
+constexpr int kTcWarps = 16;
+constexpr int kSlab = 16;                       // rows per warp iteration
+constexpr int kLd = 136;                        // halfs per shared row (128 + 8 pad): conflict-free ldmatrix
+constexpr int kSlabBytes = kSlab * kLd * 2;     // 4352
+constexpr int kCodeLd = 132;                    // bytes per code row (bank-conflict-free row walks)
+constexpr int kStageOff = kSlab * kCodeLd;      // packed-row staging follows the code rows
+constexpr int kMaxTasks = 32;
 constexpr float kLoScale = 1024.0f;
+static_assert(kStageOff + 4 + kSlab * 128 <= kSlabBytes, "codes + staged rows must fit in the slab");
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -30,164 +35,267 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
 }
 
 struct TcSmem {
-    __half w_hi[kHD * kLd];              // [output position n][input position k]
+    __half w_hi[kHD * kLd];                     // [output position n][input position k]
     __half w_lo[kHD * kLd];
-    __half x[kTileRows * kLd];           // [row][packed input position]
-    uint8_t codes[kTileRows][kHD];
-    float gn[kTileRows][BGTQ_MAX_SEGMENTS];   // group norms (V: [.][0] raw norm)
-    float gc[kTileRows][BGTQ_MAX_SEGMENTS];   // sum of squared chosen levels per group (V: [.][0])
+    __align__(16) uint8_t slab[kTcWarps][kSlabBytes];
+    float gn[kTcWarps][kSlab][BGTQ_MAX_SEGMENTS];     // group norms (V: [.][0] = raw row norm)
+    float rinv[kTcWarps][kSlab][BGTQ_MAX_SEGMENTS];   // 1 / norm, or 1 where the norm is below the floor
+    float4 colp[kHD / 2];                       // per column pair: {lut_off, lut_inv, bits(group), bits(group * 256)}
+    float kcent[512];
     uint8_t code_lut[BGTQ_MAX_SEGMENTS][BGTQ_N_BINS];
-    uint8_t kt_lo[8], kt_hi[8];          // k-tile range per 16-column strip
-    uint8_t inv_perm[kHD];
-    uint8_t grp[kHD];
-    float loff[BGTQ_MAX_SEGMENTS], linv[BGTQ_MAX_SEGMENTS];
     float vbounds[16], vcents[16];
+    uint32_t tasks[kMaxTasks];                  // first code | count << 8 | width << 12 | byte offset << 16
+    int32_t n_tasks, task_shift, row_bytes, n_seg, v_steps;
+    int32_t seg_start[BGTQ_MAX_SEGMENTS], seg_len[BGTQ_MAX_SEGMENTS], seg_lut_off[BGTQ_MAX_SEGMENTS];
+    uint8_t kt_lo[8], kt_hi[8];                 // k-tile range per 16-column strip
+    uint8_t inv_perm[kHD];
 };
 
-__global__ void __launch_bounds__(kWarps * 32, 2) encode_tc_kernel(const EncParams P) {
+// bits of up to four byte-held codes (in the bytes of w) squeezed together, `bw` bits each
+__device__ __forceinline__ uint32_t squeeze4(uint32_t w, int bw) {
+    switch (bw) {
+        case 1: return ((w & 0x01010101u) * 0x10204080u) >> 28;
+        case 2: return ((w & 0x03030303u) * 0x01041040u) >> 24;
+        case 3: return (w & 7u) | ((w >> 5) & 0x38u) | ((w >> 10) & 0x1C0u) | ((w >> 15) & 0xE00u);
+        default: return (w & 0xFu) | ((w >> 4) & 0xF0u) | ((w >> 8) & 0xF00u) | ((w >> 12) & 0xF000u);
+    }
+}
+
+// Per-CTA tables: rotation split, bin tables, pack tasks.
+__device__ void tc_setup(TcSmem& S, const EncParams& P, const BgtqHeadDesc& d, bool is_v, int h) {
+    const int tid = threadIdx.x;
+    const float* W = (is_v ? P.rot_v : P.rot_k) + (size_t)h * kHD * kHD;
+    for (int i = tid; i < kHD * kHD; i += kTcWarps * 32) {
+        const int k = i >> 7, n = i & 127;          // coalesced over n
+        const float w = __ldg(W + i);
+        const __half hi = __float2half_rn(w);
+        S.w_hi[n * kLd + k] = hi;
+        S.w_lo[n * kLd + k] = __float2half_rn((w - __half2float(hi)) * kLoScale);
+    }
+    for (int i = tid; i < BGTQ_MAX_SEGMENTS * BGTQ_N_BINS; i += kTcWarps * 32) S.code_lut[i >> 8][i & 255] = d.code_lut[i >> 8][i & 255];
+    if (tid < 512) S.kcent[tid] = d.k_cents[tid];
+    if (tid < kHD) S.inv_perm[d.head_perm[tid]] = (uint8_t)tid;
+    if (tid < kHD / 2) {
+        const int g = d.group_of[2 * tid];
+        S.colp[tid] = make_float4(d.lut_off[g], d.lut_inv[g], __int_as_float(g), __int_as_float(g * BGTQ_N_BINS));
+    }
+    if (tid < 16) {
+        S.vbounds[tid] = d.v_bounds[tid];
+        S.vcents[tid] = d.v_cents[tid];
+    }
+    if (tid < BGTQ_MAX_SEGMENTS) {
+        S.seg_start[tid] = d.seg_start[tid];
+        S.seg_len[tid] = d.seg_len[tid];
+        S.seg_lut_off[tid] = d.seg_lut_off[tid];
+    }
+    if (tid < 8) {     // k-tiles a 16-column strip needs: the blocks its columns belong to (V: all)
+        int lo = 0, hi = 8;
+        if (!is_v) {
+            const int g0 = d.group_of[16 * tid], g1 = d.group_of[16 * tid + 15];
+            lo = d.seg_start[g0] / 16;
+            hi = (d.seg_start[g1] + d.seg_len[g1] + 15) / 16;
+        }
+        S.kt_lo[tid] = (uint8_t)lo;
+        S.kt_hi[tid] = (uint8_t)hi;
+    }
+    if (tid == 0) {
+        int nt = 0;
+        auto add_run = [&](int first, int len, int bw, int out) {
+            for (int c = 0; c < len; c += 8) {
+                const int n = len - c < 8 ? len - c : 8;
+                S.tasks[nt++] = (uint32_t)(first + c) | (uint32_t)n << 8 | (uint32_t)bw << 12 | (uint32_t)(out + (bw >= 5 ? c : (c / 8) * bw)) << 16;
+            }
+        };
+        if (is_v) {
+            const int vb = (P.flags & BGTQ_ENC_V_NIBBLE) ? 4 : d.v_bits;
+            add_run(0, kHD, vb, 0);
+            S.row_bytes = seg_storage_bytes(vb, kHD);
+        } else if (P.flags & BGTQ_ENC_K_MIXED) {
+            add_run(0, d.nopack_start, 4, 0);
+            add_run(d.nopack_start, d.nopack_len, 8, d.nopack_start / 2);
+            S.row_bytes = P.kp_row_bytes;
+        } else {
+            for (int s = 0; s < d.n_seg; ++s) add_run(d.seg_start[s], d.seg_len[s], d.seg_bw[s], d.seg_pack_off[s]);
+            S.row_bytes = P.kp_row_bytes;
+        }
+        S.n_tasks = nt;
+        S.task_shift = nt <= 16 ? 4 : 5;
+        S.n_seg = is_v ? 1 : d.n_seg;
+        S.v_steps = d.v_bits;
+    }
+}
+
+// Copy `n_bytes` staged bytes (shared, same address phase mod 4 as dst) to global memory.
+__device__ __forceinline__ void flat_store(uint8_t* dst, const uint8_t* stg, int n_bytes, int lane) {
+    const int head = (int)((4u - (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 3u)) & 3u);
+    const int h = head < n_bytes ? head : n_bytes;
+    if (lane < h) dst[lane] = stg[lane];
+    const int n_words = (n_bytes - h) >> 2;
+    const uint32_t* sw = reinterpret_cast<const uint32_t*>(stg + h);
+    uint32_t* dw = reinterpret_cast<uint32_t*>(dst + h);
+    for (int i = lane; i < n_words; i += 32) dw[i] = sw[i];
+    const int done = h + 4 * n_words;
+    if (lane < n_bytes - done) dst[done + lane] = stg[done + lane];
+}
+
+__global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncParams P, const int n_k_ctas) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     TcSmem& S = *reinterpret_cast<TcSmem*>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y;
-    const bool is_v = blockIdx.z == 1;
-    if (is_v ? (P.flags & BGTQ_ENC_SKIP_V) : (P.flags & BGTQ_ENC_SKIP_K)) return;
+    const bool is_v = (int)blockIdx.x >= n_k_ctas;
+    const int role_cta = is_v ? blockIdx.x - n_k_ctas : blockIdx.x;
+    const int role_ctas = is_v ? gridDim.x - n_k_ctas : n_k_ctas;
     const BgtqHeadDesc& d = P.desc[h];
     const int64_t n_rows = (int64_t)P.n_batch * P.n_tok;
-    const int n_tiles = (int)((n_rows + kTileRows - 1) / kTileRows);
+    const int n_slabs = (int)((n_rows + kSlab - 1) / kSlab);
     const int t0 = P.pos_dev ? *P.pos_dev : P.t0;
 
-    // ---- stage the rotation once: Wt[n][k] = W[k][n], split into hi / scaled lo ----
-    {
-        const float* W = (is_v ? P.rot_v : P.rot_k) + (size_t)h * kHD * kHD;
-        for (int i = tid; i < kHD * kHD; i += kWarps * 32) {
-            const int k = i >> 7, n = i & 127;          // coalesced over n
-            const float w = __ldg(W + i);
-            const __half hi = __float2half_rn(w);
-            S.w_hi[n * kLd + k] = hi;
-            S.w_lo[n * kLd + k] = __float2half_rn((w - __half2float(hi)) * kLoScale);
-        }
-        for (int i = tid; i < BGTQ_MAX_SEGMENTS * BGTQ_N_BINS; i += kWarps * 32)
-            S.code_lut[i >> 8][i & 255] = d.code_lut[i >> 8][i & 255];
-        if (tid < kHD) {
-            S.inv_perm[d.head_perm[tid]] = (uint8_t)tid;
-            S.grp[tid] = d.group_of[tid];
-        }
-        if (tid < BGTQ_MAX_SEGMENTS) {
-            S.loff[tid] = d.lut_off[tid];
-            S.linv[tid] = d.lut_inv[tid];
-        }
-        if (tid < 16) {
-            S.vbounds[tid] = d.v_bounds[tid];
-            S.vcents[tid] = d.v_cents[tid];
-        }
-        if (tid < 8) {     // k-tiles a 16-column strip needs: the blocks its columns belong to (V: all)
-            int lo = 0, hi = 8;
-            if (!is_v) {
-                const int g0 = d.group_of[16 * tid], g1 = d.group_of[16 * tid + 15];
-                lo = d.seg_start[g0] / 16;
-                hi = (d.seg_start[g1] + d.seg_len[g1] + 15) / 16;
-            }
-            S.kt_lo[tid] = (uint8_t)lo;
-            S.kt_hi[tid] = (uint8_t)hi;
-        }
-    }
+    tc_setup(S, P, d, is_v, h);
     __syncthreads();
 
     const int r = lane >> 2, j = lane & 3;
-    const uint32_t x_base = smem_u32(S.x), whi_base = smem_u32(S.w_hi), wlo_base = smem_u32(S.w_lo);
-    const int n_seg = is_v ? 1 : d.n_seg;
+    uint8_t* const slab = S.slab[warp];
+    const uint32_t slab_u32 = smem_u32(slab), whi_base = smem_u32(S.w_hi), wlo_base = smem_u32(S.w_lo);
+    const int n_seg = S.n_seg, n_tasks = S.n_tasks, tshift = S.task_shift, rb = S.row_bytes;
     const bool mixed = !is_v && (P.flags & BGTQ_ENC_K_MIXED);
-    const int v_nb = (1 << d.v_bits) - 1;
-
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int64_t row0 = (int64_t)tile * kTileRows;
-        // ---- load 64 rows (K: gathered into packed order) ----
-        for (int i = tid; i < kTileRows * 16; i += kWarps * 32) {
-            const int row = i >> 4, c8 = (i & 15) * 8;
-            const int64_t n = row0 + row;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (n < n_rows) {
-                const int b = (int)(n / P.n_tok), s = (int)(n % P.n_tok);
-                const __half* src = is_v ? P.v + b * P.v_sb + h * P.v_sh + s * P.v_ss : P.k + b * P.k_sb + h * P.k_sh + s * P.k_ss;
-                v = *reinterpret_cast<const uint4*>(src + c8);
-            }
-            if (is_v) {
-                *reinterpret_cast<uint4*>(&S.x[row * kLd + c8]) = v;
-            } else {
-                const __half* e = reinterpret_cast<const __half*>(&v);
+    const bool f16n = P.flags & BGTQ_ENC_K_NORMS_F16;
+    // destination shared offsets (in halfs) of this lane's 8 input columns
+    uint32_t dpos[8];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) S.x[row * kLd + S.inv_perm[c8 + q]] = e[q];
-            }
-        }
-        __syncthreads();
-        // ---- group norms: lane (row = lane & 15, parity) walks its warp's 16 rows ----
+    for (int q = 0; q < 8; ++q) dpos[q] = is_v ? (lane & 15) * 8 + q : S.inv_perm[(lane & 15) * 8 + q];
+    const __half* const src_base = is_v ? P.v + h * P.v_sh : P.k + h * P.k_sh;
+    const int64_t s_sb = is_v ? P.v_sb : P.k_sb, s_ss = is_v ? P.v_ss : P.k_ss;
+    uint8_t* const out_base = is_v ? P.vp + h * P.vp_sh : P.kp + h * P.kp_sh;
+    const int64_t o_sb = is_v ? P.vp_sb : P.kp_sb, o_st = is_v ? P.vp_st : P.kp_st;
+
+    for (int sl = role_cta * kTcWarps + warp; sl < n_slabs; sl += role_ctas * kTcWarps) {
+        const int64_t n0 = (int64_t)sl * kSlab;
+        const int n_valid = n_rows - n0 < kSlab ? (int)(n_rows - n0) : kSlab;
+        const int b0 = (int)(n0 / P.n_tok), s0 = (int)(n0 - (int64_t)b0 * P.n_tok);   // n_tok >= kSlab: a slab wraps at most once
+        // ---- load 16 rows: lane -> 16-byte column chunk (lane & 15) of rows 2q + (lane >> 4) ----
         {
-            const int row = warp * 16 + (lane & 15), par = lane >> 4;
-            for (int s = 0; s < n_seg; ++s) {
-                const int st = is_v ? 0 : d.seg_start[s], en = is_v ? kHD : st + d.seg_len[s];
-                float acc = 0.f;
-                for (int p = st + par; p < en; p += 2) {
-                    const float xv = __half2float(S.x[row * kLd + p]);
-                    acc = fmaf(xv, xv, acc);
+            uint4 v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int row = 2 * q + (lane >> 4);
+                v[q] = make_uint4(0, 0, 0, 0);
+                if (row < n_valid) {
+                    int b = b0, s = s0 + row;
+                    if (s >= P.n_tok) { s -= P.n_tok; ++b; }
+                    v[q] = __ldg(reinterpret_cast<const uint4*>(src_base + b * s_sb + s * s_ss) + (lane & 15));
                 }
-                acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-                if (par == 0) {
-                    S.gn[row][s] = sqrtf(acc + 1e-30f);
-                    S.gc[row][s] = 0.f;
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int row = 2 * q + (lane >> 4);
+                __half* xr = reinterpret_cast<__half*>(slab) + row * kLd;
+                if (is_v) {
+                    *reinterpret_cast<uint4*>(xr + (lane & 15) * 8) = v[q];
+                } else {
+                    const __half* e = reinterpret_cast<const __half*>(&v[q]);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) xr[dpos[c]] = e[c];
                 }
             }
         }
         __syncwarp();
-        // ---- rotation + quantisation, one 16-column strip at a time ----
-        const int rowA = warp * 16 + r, rowB = rowA + 8;
-        float csqA = 0.f, csqB = 0.f;       // V: running sum of squared levels of this lane's columns
-        for (int np = 0; np < 8; ++np) {
-            float hi0[4] = {0, 0, 0, 0}, hi1[4] = {0, 0, 0, 0}, lo0[4] = {0, 0, 0, 0}, lo1[4] = {0, 0, 0, 0};
-            const int k0 = S.kt_lo[np], k1 = S.kt_hi[np];
-            for (int kt = k0; kt < k1; ++kt) {
-                uint32_t a[4], bh[4], bl[4];
-                ldmatrix_x4(a, x_base + 2u * ((warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kLd + kt * 16 + (lane >> 4) * 8));
-                const uint32_t boff = 2u * ((np * 16 + (lane & 7) + (lane >> 4) * 8) * kLd + kt * 16 + ((lane >> 3) & 1) * 8);
-                ldmatrix_x4(bh, whi_base + boff);
-                ldmatrix_x4(bl, wlo_base + boff);
-                const uint32_t bh0[2] = {bh[0], bh[1]}, bh1[2] = {bh[2], bh[3]};
-                const uint32_t bl0[2] = {bl[0], bl[1]}, bl1[2] = {bl[2], bl[3]};
-                mma_16816(hi0, a, bh0);
-                mma_16816(hi1, a, bh1);
-                mma_16816(lo0, a, bl0);
-                mma_16816(lo1, a, bl1);
+        // ---- group norms: lane (row = lane & 15, parity = lane >> 4) walks half2 pairs ----
+        {
+            const int row = lane & 15, par = lane >> 4;
+            const __half2* xr = reinterpret_cast<const __half2*>(slab) + row * (kLd / 2);
+            for (int s = 0; s < n_seg; ++s) {
+                const int st = is_v ? 0 : S.seg_start[s] >> 1, en = is_v ? kHD / 2 : st + (S.seg_len[s] >> 1);
+                float acc = 0.f;
+                for (int p2 = st + par; p2 < en; p2 += 2) {
+                    const float2 xv = __half22float2(xr[p2]);
+                    acc = fmaf(xv.x, xv.x, acc);
+                    acc = fmaf(xv.y, xv.y, acc);
+                }
+                acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+                if (par == 0) {
+                    const float nr = sqrtf(acc + 1e-30f);
+                    S.gn[warp][row][s] = nr;
+                    S.rinv[warp][row][s] = nr > (is_v ? 1e-8f : 1e-10f) ? 1.0f / nr : 1.0f;
+                }
             }
-            // this lane: rows rowA / rowB, columns c, c+1 (strip half 0) and c+8, c+9 (half 1)
+        }
+        // ---- A fragments of the 16 rows into registers; the slab memory is free afterwards ----
+        uint32_t a[8][4];
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt)
+            ldmatrix_x4(a[kt], slab_u32 + 2u * (((lane & 7) + ((lane >> 3) & 1) * 8) * kLd + kt * 16 + (lane >> 4) * 8));
+        __syncwarp();
+        const float rvA = S.rinv[warp][r][0], rvB = S.rinv[warp][r + 8][0];
+        float csqA = 0.f, csqB = 0.f;       // V: running sum of squared levels of this lane's columns
+        // ---- rotation + quantisation, one 16-column strip at a time ----
+#pragma unroll 1
+        for (int np = 0; np < 8; ++np) {
+            float acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
+            const int k0 = S.kt_lo[np], k1 = S.kt_hi[np];
+            const uint32_t boff = 2u * ((np * 16 + (lane & 7) + (lane >> 4) * 8) * kLd + ((lane >> 3) & 1) * 8);
+#pragma unroll
+            for (int kt = 0; kt < 8; ++kt) {
+                if (kt >= k0 && kt < k1) {
+                    uint32_t bl[4];
+                    ldmatrix_x4(bl, wlo_base + boff + 32u * kt);
+                    const uint32_t bl0[2] = {bl[0], bl[1]}, bl1[2] = {bl[2], bl[3]};
+                    mma_16816(acc0, a[kt], bl0);
+                    mma_16816(acc1, a[kt], bl1);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc0[e] *= 1.0f / kLoScale;
+                acc1[e] *= 1.0f / kLoScale;
+            }
+#pragma unroll
+            for (int kt = 0; kt < 8; ++kt) {
+                if (kt >= k0 && kt < k1) {
+                    uint32_t bh[4];
+                    ldmatrix_x4(bh, whi_base + boff + 32u * kt);
+                    const uint32_t bh0[2] = {bh[0], bh[1]}, bh1[2] = {bh[2], bh[3]};
+                    mma_16816(acc0, a[kt], bh0);
+                    mma_16816(acc1, a[kt], bh1);
+                }
+            }
+            // this lane: rows r / r+8, column pairs (16np + 2j) and (16np + 8 + 2j)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const float* ah = half ? hi1 : hi0;
-                const float* al = half ? lo1 : lo0;
+                const float* ac = half ? acc1 : acc0;
+                const int col = np * 16 + half * 8 + 2 * j;
+                uint32_t cA, cB;      // two codes of row r / row r+8
+                if (!is_v) {
+                    const float4 cp = S.colp[col >> 1];
+                    const int g = __float_as_int(cp.z);
+                    const uint8_t* lut = &S.code_lut[0][0] + __float_as_int(cp.w);
+                    const float ra = S.rinv[warp][r][g], rb2 = S.rinv[warp][r + 8][g];
+                    uint32_t c[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int col = np * 16 + half * 8 + 2 * j + (e & 1);
-                    const int row = (e & 2) ? rowB : rowA;
-                    const float acc = ah[e] + al[e] * (1.0f / kLoScale);
-                    uint8_t code;
-                    float cv = 0.f;
-                    (void)cv;
-                    if (!is_v) {
-                        const int g = S.grp[col];
-                        const float nr = S.gn[row][g];
-                        const float y = acc / (nr > 1e-10f ? nr : 1.0f);
-                        float u = (y - S.loff[g]) * S.linv[g];
+                    for (int e = 0; e < 4; ++e) {
+                        const float y = ac[e] * ((e & 2) ? rb2 : ra);
+                        float u = (y - cp.x) * cp.y;
                         u = fminf(fmaxf(u, 0.f), 255.f);
-                        code = S.code_lut[g][(int)u];
-                    } else {
-                        const float nr = S.gn[row][0];
-                        const float y = acc / (nr > 1e-8f ? nr : 1.0f);
-                        int c = 0;
-                        for (int i = 0; i < v_nb; ++i) c += y > S.vbounds[i] ? 1 : 0;
-                        code = (uint8_t)c;
-                        cv = S.vcents[c];
+                        c[e] = lut[(int)u];
+                    }
+                    cA = c[0] | c[1] << 8;
+                    cB = c[2] | c[3] << 8;
+                } else {
+                    uint32_t c[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float y = ac[e] * ((e & 2) ? rvB : rvA);
+                        int cc = 0;
+                        for (int st = S.v_steps - 1; st >= 0; --st) cc += y > S.vbounds[cc + (1 << st) - 1] ? (1 << st) : 0;
+                        c[e] = (uint32_t)cc;
+                        const float cv = S.vcents[cc];
                         if (e & 2) csqB = fmaf(cv, cv, csqB); else csqA = fmaf(cv, cv, csqA);
                     }
-                    S.codes[row][col] = code;
+                    cA = c[0] | c[1] << 8;
+                    cB = c[2] | c[3] << 8;
                 }
+                *reinterpret_cast<uint16_t*>(slab + r * kCodeLd + col) = (uint16_t)cA;
+                *reinterpret_cast<uint16_t*>(slab + (r + 8) * kCodeLd + col) = (uint16_t)cB;
             }
         }
         if (is_v) {    // squared level norms: add the four lanes of a quad
@@ -196,73 +304,96 @@ __global__ void __launch_bounds__(kWarps * 32, 2) encode_tc_kernel(const EncPara
             csqB += __shfl_xor_sync(0xffffffffu, csqB, 1);
             csqB += __shfl_xor_sync(0xffffffffu, csqB, 2);
             if (j == 0) {
-                S.gc[rowA][0] = csqA;
-                S.gc[rowB][0] = csqB;
+                S.rinv[warp][r][1] = csqA;
+                S.rinv[warp][r + 8][1] = csqB;
+            }
+        }
+        // byte phase of the staged rows = phase of their cache address, so both sides move as words
+        int bfirst = b0, sfirst = s0;
+        uint8_t* const dst0 = out_base + bfirst * o_sb + (int64_t)(t0 + sfirst) * o_st;
+        const bool flat = o_st == rb && s0 + n_valid <= P.n_tok;
+        uint8_t* const stg = slab + kStageOff + (flat ? (int)(reinterpret_cast<uintptr_t>(dst0) & 3u) : 0);
+        for (int i = lane; i < (kSlab * rb + 3) / 4 + 1; i += 32) reinterpret_cast<uint32_t*>(slab + kStageOff)[i] = 0u;
+        __syncwarp();
+        // ---- norms ----
+        if (!is_v) {
+            if (mixed) {   // norm correction: divide by the norm of the chosen levels, per group
+                const int row = lane & 15, par = lane >> 4;
+                for (int s = 0; s < n_seg; ++s) {
+                    const int st = S.seg_start[s], en = st + S.seg_len[s];
+                    const float* cent = S.kcent + S.seg_lut_off[s];
+                    float acc = 0.f;
+                    for (int p = st + par; p < en; p += 2) {
+                        const float cv = cent[slab[row * kCodeLd + p]];
+                        acc = fmaf(cv, cv, acc);
+                    }
+                    acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+                    if (par == 0) S.gn[warp][row][s] = S.gn[warp][row][s] / fmaxf(sqrtf(acc), 1e-10f);
+                }
+                __syncwarp();
+            }
+            // lane -> (group = lane & 7, row = 4 * pass + (lane >> 3))
+            for (int pass = 0; pass < 4; ++pass) {
+                const int row = 4 * pass + (lane >> 3), s = lane & 7;
+                if (row < n_valid && s < P.kn_count) {
+                    int b = b0, t = s0 + row;
+                    if (t >= P.n_tok) { t -= P.n_tok; ++b; }
+                    const float val = s < n_seg ? S.gn[warp][row][s] : 0.f;
+                    const size_t o = b * P.kn_sb + h * P.kn_sh + (size_t)(t0 + t) * P.kn_st + s;
+                    if (f16n) static_cast<__half*>(P.kn)[o] = __float2half_rn(val);
+                    else static_cast<float*>(P.kn)[o] = val;
+                }
+            }
+        } else if (lane < n_valid) {
+            int b = b0, t = s0 + lane;
+            if (t >= P.n_tok) { t -= P.n_tok; ++b; }
+            const float cnorm = sqrtf(S.rinv[warp][lane][1] + 1e-20f);
+            P.vn[b * P.vn_sb + h * P.vn_sh + (size_t)(t0 + t) * P.vn_st] =
+                __float2half_rn(S.gn[warp][lane][0] / (cnorm > 1e-10f ? cnorm : 1.0f));
+        }
+        // ---- pack: one task = up to 8 codes of one width ----
+        for (int i = lane; i < (kSlab << tshift); i += 32) {
+            const int row = i >> tshift, ti = i & ((1 << tshift) - 1);
+            if (ti >= n_tasks) continue;
+            const uint32_t tk = S.tasks[ti];
+            const int first = tk & 0xFF, n = (tk >> 8) & 0xF, bw = (tk >> 12) & 0xF, out = tk >> 16;
+            const uint16_t* cs = reinterpret_cast<const uint16_t*>(slab + row * kCodeLd + first);
+            uint32_t lo = cs[0] | (uint32_t)cs[1] << 16, hi = cs[2] | (uint32_t)cs[3] << 16;
+            if (n < 8) {        // codes past the run belong to the next segment
+                if (n <= 4) { hi = 0; lo &= n == 4 ? 0xFFFFFFFFu : (1u << (8 * n)) - 1u; }
+                else hi &= (1u << (8 * (n - 4))) - 1u;
+            }
+            uint8_t* o = stg + row * rb + out;
+            if (bw >= 5) {
+                for (int c = 0; c < n; ++c) o[c] = (uint8_t)((c < 4 ? lo >> (8 * c) : hi >> (8 * (c - 4))) & 0xFFu);
+            } else {
+                const uint32_t word = squeeze4(lo, bw) | squeeze4(hi, bw) << (4 * bw);
+                const int nb = bw == 3 ? 3 : (n * bw + 7) >> 3;
+                for (int c = 0; c < nb; ++c) o[c] = (uint8_t)(word >> (8 * c));
             }
         }
         __syncwarp();
-        // ---- outputs of this warp's 16 rows ----
-        for (int rr = 0; rr < 16; ++rr) {
-            const int row = warp * 16 + rr;
-            const int64_t n = row0 + row;
-            if (n >= n_rows) break;
-            const int b = (int)(n / P.n_tok), s = (int)(n % P.n_tok);
-            const size_t slot = (size_t)(t0 + s);
-            if (!is_v) {
-                if (lane < P.kn_count) {
-                    float val = lane < d.n_seg ? S.gn[row][lane] : 0.f;
-                    if (mixed && lane < d.n_seg) {   // norm correction: divide by the norm of the chosen levels
-                        float csq = 0.f;
-                        for (int p = d.seg_start[lane]; p < d.seg_start[lane] + d.seg_len[lane]; ++p) {
-                            const float c1 = d.k_cents[d.seg_lut_off[lane] + S.codes[row][p]];
-                            csq += c1 * c1;
-                        }
-                        val = val / fmaxf(sqrtf(csq), 1e-10f);
-                    }
-                    const size_t o = b * P.kn_sb + h * P.kn_sh + slot * P.kn_st + lane;
-                    if (P.flags & BGTQ_ENC_K_NORMS_F16) static_cast<__half*>(P.kn)[o] = __float2half_rn(val);
-                    else static_cast<float*>(P.kn)[o] = val;
-                }
-                uint8_t* dst = P.kp + b * P.kp_sb + h * P.kp_sh + slot * P.kp_st;
-                for (int p = lane; p < P.kp_row_bytes; p += 32) {
-                    uint32_t byte = 0;
-                    if (mixed) {
-                        const int nib = d.nopack_start / 2;
-                        if (p < nib) byte = (S.codes[row][2 * p] & 15u) | ((S.codes[row][2 * p + 1] & 15u) << 4);
-                        else if (p < nib + d.nopack_len) byte = S.codes[row][d.nopack_start + (p - nib)];
-                    } else {
-                        for (int sg = 0; sg < d.n_seg; ++sg) {
-                            const int bw = d.seg_bw[sg], nb = seg_storage_bytes(bw, d.seg_len[sg]);
-                            if (p >= d.seg_pack_off[sg] && p < d.seg_pack_off[sg] + nb) {
-                                const int st = p - d.seg_pack_off[sg];
-                                byte = bw >= 5 ? S.codes[row][d.seg_start[sg] + st]
-                                               : enc_pack_byte(&S.codes[row][d.seg_start[sg]], d.seg_len[sg], bw, st);
-                            }
-                        }
-                    }
-                    dst[p] = (uint8_t)byte;
-                }
-                if (P.k_codes) {
-                    uint8_t* cd = P.k_codes + (((size_t)b * P.n_kv + h) * P.n_tok + s) * kHD;
-                    for (int p = lane; p < kHD; p += 32) cd[p] = S.codes[row][p];
-                }
-            } else {
-                if (lane == 0) {
-                    const float cnorm = sqrtf(S.gc[row][0] + 1e-20f);
-                    P.vn[b * P.vn_sb + h * P.vn_sh + slot * P.vn_st] =
-                        __float2half_rn(S.gn[row][0] / (cnorm > 1e-10f ? cnorm : 1.0f));
-                }
-                const int vb = (P.flags & BGTQ_ENC_V_NIBBLE) ? 4 : d.v_bits;
-                uint8_t* dst = P.vp + b * P.vp_sb + h * P.vp_sh + slot * P.vp_st;
-                for (int p = lane; p < seg_storage_bytes(vb, kHD); p += 32)
-                    dst[p] = (uint8_t)enc_pack_byte(&S.codes[row][0], kHD, vb, p);
-                if (P.v_codes) {
-                    uint8_t* cd = P.v_codes + (((size_t)b * P.n_kv + h) * P.n_tok + s) * kHD;
-                    for (int p = lane; p < kHD; p += 32) cd[p] = S.codes[row][p];
-                }
+        // ---- rows out ----
+        if (flat) {
+            flat_store(dst0, stg, n_valid * rb, lane);
+        } else {
+            for (int row = 0; row < n_valid; ++row) {
+                int b = b0, t = s0 + row;
+                if (t >= P.n_tok) { t -= P.n_tok; ++b; }
+                uint8_t* dst = out_base + b * o_sb + (int64_t)(t0 + t) * o_st;
+                for (int p = lane; p < rb; p += 32) dst[p] = stg[row * rb + p];
             }
         }
-        __syncthreads();    // tile buffers are reused
+        uint8_t* const codes_out = is_v ? P.v_codes : P.k_codes;
+        if (codes_out) {
+            for (int row = 0; row < n_valid; ++row) {
+                int b = b0, t = s0 + row;
+                if (t >= P.n_tok) { t -= P.n_tok; ++b; }
+                uint32_t* cd = reinterpret_cast<uint32_t*>(codes_out + (((size_t)b * P.n_kv + h) * P.n_tok + t) * kHD);
+                cd[lane] = *reinterpret_cast<const uint32_t*>(slab + row * kCodeLd + 4 * lane);
+            }
+        }
+        __syncwarp();       // the slab is reloaded next
     }
 }
 
@@ -270,12 +401,26 @@ __global__ void __launch_bounds__(kWarps * 32, 2) encode_tc_kernel(const EncPara
 
 int launch_encode_tc(const EncParams& P, cudaStream_t stream) {
     const int64_t n_rows = (int64_t)P.n_batch * P.n_tok;
-    const int n_tiles = (int)((n_rows + kTileRows - 1) / kTileRows);
+    const int n_slabs = (int)((n_rows + kSlab - 1) / kSlab);
+    const bool do_k = !(P.flags & BGTQ_ENC_SKIP_K), do_v = !(P.flags & BGTQ_ENC_SKIP_V);
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int per = (2 * sms + 2 * P.n_kv - 1) / (2 * P.n_kv);        // CTAs per (head, side): fill two per SM
-    if (per > n_tiles) per = n_tiles;
-    if (per < 1) per = 1;
+    // CTAs per head: fill the SMs once; K and V roles share them in proportion to their cost
+    int per = sms / P.n_kv;
+    if (per < 2) per = 2;
+    const int useful = (n_slabs + kTcWarps - 1) / kTcWarps;     // CTAs of one role that still get a slab per warp
+    int n_k = 0, n_v = 0;
+    if (do_k && do_v) {
+        n_k = (per * 9 + 10) / 20;
+        if (n_k < 1) n_k = 1;
+        n_v = per - n_k;
+        if (n_k > useful) n_k = useful;
+        if (n_v > useful) n_v = useful;
+    } else if (do_k) {
+        n_k = per < useful ? per : useful;
+    } else {
+        n_v = per < useful ? per : useful;
+    }
     const int smem = (int)sizeof(TcSmem);
     static bool attr_set = false;
     if (!attr_set) {
@@ -285,7 +430,7 @@ int launch_encode_tc(const EncParams& P, cudaStream_t stream) {
         }
         attr_set = true;
     }
-    encode_tc_kernel<<<dim3(per, P.n_kv, 2), kWarps * 32, smem, stream>>>(P);
+    encode_tc_kernel<<<dim3(n_k + n_v, P.n_kv), kTcWarps * 32, smem, stream>>>(P, n_k);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 
