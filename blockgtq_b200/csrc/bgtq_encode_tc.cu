@@ -15,6 +15,10 @@
 #include "bgtq_common.cuh"
 #include "bgtq_encode_params.cuh"
 
+#ifndef BGTQ_TC_ABL
+#define BGTQ_TC_ABL 0
+#endif
+
 namespace bgtq {
 namespace {
 
@@ -45,10 +49,10 @@ struct TcSmem {
     uint8_t code_lut[BGTQ_MAX_SEGMENTS][BGTQ_N_BINS];
     float vbounds[16], vcents[16];
     uint32_t tasks[kMaxTasks];                  // first code | count << 8 | width << 12 | byte offset << 16
-    int32_t n_tasks, task_shift, row_bytes, n_seg, v_steps;
+    int32_t n_tasks, row_bytes, n_seg;
     int32_t seg_start[BGTQ_MAX_SEGMENTS], seg_len[BGTQ_MAX_SEGMENTS], seg_lut_off[BGTQ_MAX_SEGMENTS];
     uint8_t kt_lo[8], kt_hi[8];                 // k-tile range per 16-column strip
-    uint8_t inv_perm[kHD];
+    __align__(8) uint8_t inv_perm[kHD];
 };
 
 // bits of up to four byte-held codes (in the bytes of w) squeezed together, `bw` bits each
@@ -119,9 +123,7 @@ __device__ void tc_setup(TcSmem& S, const EncParams& P, const BgtqHeadDesc& d, b
             S.row_bytes = P.kp_row_bytes;
         }
         S.n_tasks = nt;
-        S.task_shift = nt <= 16 ? 4 : 5;
         S.n_seg = is_v ? 1 : d.n_seg;
-        S.v_steps = d.v_bits;
     }
 }
 
@@ -138,41 +140,29 @@ __device__ __forceinline__ void flat_store(uint8_t* dst, const uint8_t* stg, int
     if (lane < n_bytes - done) dst[done + lane] = stg[done + lane];
 }
 
-__global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncParams P, const int n_k_ctas) {
-    extern __shared__ __align__(128) uint8_t smem_raw[];
-    TcSmem& S = *reinterpret_cast<TcSmem*>(smem_raw);
+template <bool IS_V>
+__device__ __forceinline__ void tc_role(TcSmem& S, const EncParams& P, const int h, const int role_cta, const int role_ctas) {
+    constexpr bool is_v = IS_V;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.y;
-    const bool is_v = (int)blockIdx.x >= n_k_ctas;
-    const int role_cta = is_v ? blockIdx.x - n_k_ctas : blockIdx.x;
-    const int role_ctas = is_v ? gridDim.x - n_k_ctas : n_k_ctas;
-    const BgtqHeadDesc& d = P.desc[h];
-    const int64_t n_rows = (int64_t)P.n_batch * P.n_tok;
-    const int n_slabs = (int)((n_rows + kSlab - 1) / kSlab);
+    const int n_rows = P.n_batch * P.n_tok;                  // the launcher checks that this fits
+    const int n_slabs = (n_rows + kSlab - 1) / kSlab;
     const int t0 = P.pos_dev ? *P.pos_dev : P.t0;
-
-    tc_setup(S, P, d, is_v, h);
-    __syncthreads();
 
     const int r = lane >> 2, j = lane & 3;
     uint8_t* const slab = S.slab[warp];
     const uint32_t slab_u32 = smem_u32(slab), whi_base = smem_u32(S.w_hi), wlo_base = smem_u32(S.w_lo);
-    const int n_seg = S.n_seg, n_tasks = S.n_tasks, tshift = S.task_shift, rb = S.row_bytes;
+    const int n_seg = S.n_seg, n_tasks = S.n_tasks, rb = S.row_bytes;
     const bool mixed = !is_v && (P.flags & BGTQ_ENC_K_MIXED);
     const bool f16n = P.flags & BGTQ_ENC_K_NORMS_F16;
-    // destination shared offsets (in halfs) of this lane's 8 input columns
-    uint32_t dpos[8];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) dpos[q] = is_v ? (lane & 15) * 8 + q : S.inv_perm[(lane & 15) * 8 + q];
     const __half* const src_base = is_v ? P.v + h * P.v_sh : P.k + h * P.k_sh;
     const int64_t s_sb = is_v ? P.v_sb : P.k_sb, s_ss = is_v ? P.v_ss : P.k_ss;
     uint8_t* const out_base = is_v ? P.vp + h * P.vp_sh : P.kp + h * P.kp_sh;
     const int64_t o_sb = is_v ? P.vp_sb : P.kp_sb, o_st = is_v ? P.vp_st : P.kp_st;
 
     for (int sl = role_cta * kTcWarps + warp; sl < n_slabs; sl += role_ctas * kTcWarps) {
-        const int64_t n0 = (int64_t)sl * kSlab;
-        const int n_valid = n_rows - n0 < kSlab ? (int)(n_rows - n0) : kSlab;
-        const int b0 = (int)(n0 / P.n_tok), s0 = (int)(n0 - (int64_t)b0 * P.n_tok);   // n_tok >= kSlab: a slab wraps at most once
+        const int n0 = sl * kSlab;
+        const int n_valid = n_rows - n0 < kSlab ? n_rows - n0 : kSlab;
+        const int b0 = (int)((uint32_t)n0 / (uint32_t)P.n_tok), s0 = n0 - b0 * P.n_tok;   // n_tok >= kSlab: a slab wraps at most once
         // ---- load 16 rows: lane -> 16-byte column chunk (lane & 15) of rows 2q + (lane >> 4) ----
         {
             uint4 v[8];
@@ -186,11 +176,17 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncPa
                     v[q] = __ldg(reinterpret_cast<const uint4*>(src_base + b * s_sb + s * s_ss) + (lane & 15));
                 }
             }
+            uint32_t dpos[8];       // packed positions of this lane's 8 input columns
+            if (!is_v) {
+                const uint2 ip = *reinterpret_cast<const uint2*>(&S.inv_perm[(lane & 15) * 8]);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) dpos[c] = ((c < 4 ? ip.x : ip.y) >> (8 * (c & 3))) & 0xFFu;
+            }
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const int row = 2 * q + (lane >> 4);
                 __half* xr = reinterpret_cast<__half*>(slab) + row * kLd;
-                if (is_v) {
+                if (is_v || (BGTQ_TC_ABL & 16)) {
                     *reinterpret_cast<uint4*>(xr + (lane & 15) * 8) = v[q];
                 } else {
                     const __half* e = reinterpret_cast<const __half*>(&v[q]);
@@ -204,10 +200,19 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncPa
         {
             const int row = lane & 15, par = lane >> 4;
             const __half2* xr = reinterpret_cast<const __half2*>(slab) + row * (kLd / 2);
-            for (int s = 0; s < n_seg; ++s) {
+            for (int s = 0; s < ((BGTQ_TC_ABL & 4) ? 0 : n_seg); ++s) {
                 const int st = is_v ? 0 : S.seg_start[s] >> 1, en = is_v ? kHD / 2 : st + (S.seg_len[s] >> 1);
                 float acc = 0.f;
-                for (int p2 = st + par; p2 < en; p2 += 2) {
+                int p2 = st + par;
+                for (; p2 + 6 < en; p2 += 8) {
+                    const float2 x0 = __half22float2(xr[p2]), x1 = __half22float2(xr[p2 + 2]);
+                    const float2 x2 = __half22float2(xr[p2 + 4]), x3 = __half22float2(xr[p2 + 6]);
+                    acc = fmaf(x0.x, x0.x, acc); acc = fmaf(x0.y, x0.y, acc);
+                    acc = fmaf(x1.x, x1.x, acc); acc = fmaf(x1.y, x1.y, acc);
+                    acc = fmaf(x2.x, x2.x, acc); acc = fmaf(x2.y, x2.y, acc);
+                    acc = fmaf(x3.x, x3.x, acc); acc = fmaf(x3.y, x3.y, acc);
+                }
+                for (; p2 < en; p2 += 2) {
                     const float2 xv = __half22float2(xr[p2]);
                     acc = fmaf(xv.x, xv.x, acc);
                     acc = fmaf(xv.y, xv.y, acc);
@@ -231,33 +236,27 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncPa
         // ---- rotation + quantisation, one 16-column strip at a time ----
 #pragma unroll 1
         for (int np = 0; np < 8; ++np) {
-            float acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
-            const int k0 = S.kt_lo[np], k1 = S.kt_hi[np];
+            float acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0}, lo0[4] = {0, 0, 0, 0}, lo1[4] = {0, 0, 0, 0};
+            const uint32_t kmask = is_v ? 0xFFu : ((1u << S.kt_hi[np]) - (1u << S.kt_lo[np]));
             const uint32_t boff = 2u * ((np * 16 + (lane & 7) + (lane >> 4) * 8) * kLd + ((lane >> 3) & 1) * 8);
 #pragma unroll
             for (int kt = 0; kt < 8; ++kt) {
-                if (kt >= k0 && kt < k1) {
-                    uint32_t bl[4];
+                if (!(BGTQ_TC_ABL & 8) && (is_v || (kmask >> kt & 1u))) {
+                    uint32_t bl[4], bh[4];
                     ldmatrix_x4(bl, wlo_base + boff + 32u * kt);
+                    ldmatrix_x4(bh, whi_base + boff + 32u * kt);
                     const uint32_t bl0[2] = {bl[0], bl[1]}, bl1[2] = {bl[2], bl[3]};
-                    mma_16816(acc0, a[kt], bl0);
-                    mma_16816(acc1, a[kt], bl1);
+                    const uint32_t bh0[2] = {bh[0], bh[1]}, bh1[2] = {bh[2], bh[3]};
+                    mma_16816(lo0, a[kt], bl0);
+                    mma_16816(lo1, a[kt], bl1);
+                    mma_16816(acc0, a[kt], bh0);
+                    mma_16816(acc1, a[kt], bh1);
                 }
             }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                acc0[e] *= 1.0f / kLoScale;
-                acc1[e] *= 1.0f / kLoScale;
-            }
-#pragma unroll
-            for (int kt = 0; kt < 8; ++kt) {
-                if (kt >= k0 && kt < k1) {
-                    uint32_t bh[4];
-                    ldmatrix_x4(bh, whi_base + boff + 32u * kt);
-                    const uint32_t bh0[2] = {bh[0], bh[1]}, bh1[2] = {bh[2], bh[3]};
-                    mma_16816(acc0, a[kt], bh0);
-                    mma_16816(acc1, a[kt], bh1);
-                }
+                acc0[e] = fmaf(lo0[e], 1.0f / kLoScale, acc0[e]);
+                acc1[e] = fmaf(lo1[e], 1.0f / kLoScale, acc1[e]);
             }
             // this lane: rows r / r+8, column pairs (16np + 2j) and (16np + 8 + 2j)
 #pragma unroll
@@ -265,7 +264,10 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncPa
                 const float* ac = half ? acc1 : acc0;
                 const int col = np * 16 + half * 8 + 2 * j;
                 uint32_t cA, cB;      // two codes of row r / row r+8
-                if (!is_v) {
+                if (BGTQ_TC_ABL & 2) {
+                    cA = __float_as_uint(ac[0] + ac[1]) & 0x0101u;
+                    cB = __float_as_uint(ac[2] + ac[3]) & 0x0101u;
+                } else if (!is_v) {
                     const float4 cp = S.colp[col >> 1];
                     const int g = __float_as_int(cp.z);
                     const uint8_t* lut = &S.code_lut[0][0] + __float_as_int(cp.w);
@@ -285,8 +287,9 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncPa
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const float y = ac[e] * ((e & 2) ? rvB : rvA);
-                        int cc = 0;
-                        for (int st = S.v_steps - 1; st >= 0; --st) cc += y > S.vbounds[cc + (1 << st) - 1] ? (1 << st) : 0;
+                        int cc = 0;      // boundaries are sorted and padded with +inf: four fixed halving steps
+#pragma unroll
+                        for (int st = 3; st >= 0; --st) cc += y > S.vbounds[cc + (1 << st) - 1] ? (1 << st) : 0;
                         c[e] = (uint32_t)cc;
                         const float cv = S.vcents[cc];
                         if (e & 2) csqB = fmaf(cv, cv, csqB); else csqA = fmaf(cv, cv, csqA);
@@ -352,9 +355,9 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncPa
                 __float2half_rn(S.gn[warp][lane][0] / (cnorm > 1e-10f ? cnorm : 1.0f));
         }
         // ---- pack: one task = up to 8 codes of one width ----
-        for (int i = lane; i < (kSlab << tshift); i += 32) {
-            const int row = i >> tshift, ti = i & ((1 << tshift) - 1);
-            if (ti >= n_tasks) continue;
+        // lane -> row (lane & 15); the two half-warps take alternate tasks, so a warp runs at most two widths at a time
+        for (int ti = lane >> 4; ti < ((BGTQ_TC_ABL & 1) ? 0 : n_tasks); ti += 2) {
+            const int row = lane & 15;
             const uint32_t tk = S.tasks[ti];
             const int first = tk & 0xFF, n = (tk >> 8) & 0xF, bw = (tk >> 12) & 0xF, out = tk >> 16;
             const uint16_t* cs = reinterpret_cast<const uint16_t*>(slab + row * kCodeLd + first);
@@ -365,11 +368,15 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncPa
             }
             uint8_t* o = stg + row * rb + out;
             if (bw >= 5) {
-                for (int c = 0; c < n; ++c) o[c] = (uint8_t)((c < 4 ? lo >> (8 * c) : hi >> (8 * (c - 4))) & 0xFFu);
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    if (c < n) o[c] = (uint8_t)((c < 4 ? lo >> (8 * c) : hi >> (8 * (c - 4))) & 0xFFu);
             } else {
                 const uint32_t word = squeeze4(lo, bw) | squeeze4(hi, bw) << (4 * bw);
                 const int nb = bw == 3 ? 3 : (n * bw + 7) >> 3;
-                for (int c = 0; c < nb; ++c) o[c] = (uint8_t)(word >> (8 * c));
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (c < nb) o[c] = (uint8_t)(word >> (8 * c));
             }
         }
         __syncwarp();
@@ -397,10 +404,36 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncPa
     }
 }
 
+__global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncParams P, const int n_k_ctas) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    TcSmem& S = *reinterpret_cast<TcSmem*>(smem_raw);
+    const int h = blockIdx.y;
+    if (n_k_ctas < 0) {      // bulk: every CTA takes its share of the K slabs, then of the V slabs
+        if (!(P.flags & BGTQ_ENC_SKIP_K)) {
+            tc_setup(S, P, P.desc[h], false, h);
+            __syncthreads();
+            tc_role<false>(S, P, h, blockIdx.x, gridDim.x);
+            __syncthreads();
+        }
+        if (!(P.flags & BGTQ_ENC_SKIP_V)) {
+            tc_setup(S, P, P.desc[h], true, h);
+            __syncthreads();
+            tc_role<true>(S, P, h, blockIdx.x, gridDim.x);
+        }
+        return;
+    }
+    const bool is_v = (int)blockIdx.x >= n_k_ctas;     // few rows: K and V in separate CTAs, side by side
+    tc_setup(S, P, P.desc[h], is_v, h);
+    __syncthreads();
+    if (is_v) tc_role<true>(S, P, h, blockIdx.x - n_k_ctas, gridDim.x - n_k_ctas);
+    else tc_role<false>(S, P, h, blockIdx.x, n_k_ctas);
+}
+
 }  // namespace
 
 int launch_encode_tc(const EncParams& P, cudaStream_t stream) {
     const int64_t n_rows = (int64_t)P.n_batch * P.n_tok;
+    if (n_rows > (1LL << 30)) return BGTQ_E_TOOBIG;
     const int n_slabs = (int)((n_rows + kSlab - 1) / kSlab);
     const bool do_k = !(P.flags & BGTQ_ENC_SKIP_K), do_v = !(P.flags & BGTQ_ENC_SKIP_V);
     int dev = 0, sms = 148;
@@ -409,18 +442,12 @@ int launch_encode_tc(const EncParams& P, cudaStream_t stream) {
     int per = sms / P.n_kv;
     if (per < 2) per = 2;
     const int useful = (n_slabs + kTcWarps - 1) / kTcWarps;     // CTAs of one role that still get a slab per warp
-    int n_k = 0, n_v = 0;
-    if (do_k && do_v) {
-        n_k = (per * 9 + 10) / 20;
-        if (n_k < 1) n_k = 1;
-        n_v = per - n_k;
-        if (n_k > useful) n_k = useful;
-        if (n_v > useful) n_v = useful;
-    } else if (do_k) {
-        n_k = per < useful ? per : useful;
-    } else {
-        n_v = per < useful ? per : useful;
-    }
+    const int fill = per < useful ? per : useful;
+    int n_k, grid_x;        // n_k < 0: every CTA runs the K role, then the V role
+    if (do_k && do_v && 2 * useful <= per) { n_k = useful; grid_x = 2 * useful; }
+    else if (do_k && do_v) { n_k = -1; grid_x = fill; }
+    else if (do_k) { n_k = fill; grid_x = fill; }
+    else { n_k = 0; grid_x = fill; }
     const int smem = (int)sizeof(TcSmem);
     static bool attr_set = false;
     if (!attr_set) {
@@ -430,7 +457,7 @@ int launch_encode_tc(const EncParams& P, cudaStream_t stream) {
         }
         attr_set = true;
     }
-    encode_tc_kernel<<<dim3(n_k + n_v, P.n_kv), kTcWarps * 32, smem, stream>>>(P, n_k);
+    encode_tc_kernel<<<dim3(grid_x, P.n_kv), kTcWarps * 32, smem, stream>>>(P, n_k);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 
