@@ -69,6 +69,7 @@ def build_manager(w, device, seed, extra_tokens):
     gqa = n_q // n_kv
     mgr = BlockGTQKVManager(L, n_q, n_kv, HD, max_seq_len=T + extra_tokens, batch_size=B, k_avg_bits=w["k_bits"],
                             v_bits=w["v_bits"], device=device, n_sink=w["n_sink"], recent_window=w["window"])
+    mgr.programmatic = os.environ.get("BGTQ_NO_PROGRAMMATIC", "") == ""
     for li in range(L):
         ck = torch.stack([synth_keys(gen, (1, 2048), w["theta"], device)[0] for _ in range(n_kv)])
         cq = torch.stack([synth_keys(gen, (gqa, 2048), w["theta"], device).reshape(-1, HD) for _ in range(n_kv)])

@@ -19,8 +19,9 @@ MAX_SEG = 8
 N_BINS = 256
 
 OK = 0
-ENC_K_NORMS_F16, ENC_K_MIXED, ENC_V_NIBBLE, ENC_SKIP_K, ENC_SKIP_V, ENC_FORCE_SIMT = 1, 2, 4, 8, 16, 32
-DEC_K_MIXED, DEC_V_NIBBLE = 1, 2
+ENC_K_NORMS_F16, ENC_K_MIXED, ENC_V_NIBBLE, ENC_SKIP_K, ENC_SKIP_V, ENC_FORCE_SIMT, ENC_PROGRAMMATIC = 1, 2, 4, 8, 16, 32, 64
+DEC_K_MIXED, DEC_V_NIBBLE, DEC_PROGRAMMATIC = 1, 2, 4
+COMBINE_PROGRAMMATIC = 1
 
 
 class HeadDesc(C.Structure):
@@ -76,7 +77,7 @@ _SIGNATURES = {
     "bgtq_buffer_attn": (C.c_int, [_vp, _i64, _i64, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
                                    _i32, _i32, _i32, _f32,
                                    _vp, _vp, _vp]),
-    "bgtq_combine": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _i64, _i64, _vp, _vp, _vp]),
+    "bgtq_combine": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _i64, _i64, _vp, _vp, _i32, _vp]),
 }
 
 _lib = None

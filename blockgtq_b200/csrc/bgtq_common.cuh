@@ -140,6 +140,32 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     return *reinterpret_cast<uint32_t*>(&r);
 }
 
+// Programmatic dependent launch (a kernel launched with the stream-serialization attribute may start
+// while its predecessor in the stream still runs).  grid_launch_dependents lets the NEXT kernel's blocks
+// become resident early; grid_dependency_wait blocks until the PREVIOUS kernel has completed and its
+// writes are visible.  Both are no-ops for a kernel launched the ordinary way.  Every kernel of a chain
+// executes the wait before it ends, so completion stays transitive along the stream.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with or without the programmatic stream-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool programmatic, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    return e == cudaSuccess ? cudaGetLastError() : e;
+}
+
 __host__ __device__ __forceinline__ int seg_storage_bytes(int bw, int n) {
     return bw == 1 ? (n + 7) / 8 : bw == 2 ? (n + 3) / 4 : bw == 3 ? ((n + 7) / 8) * 3 : bw == 4 ? (n + 1) / 2 : n;
 }

@@ -107,11 +107,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const DecHeadPlan& hp = P.plan.head[h];
 
-    const int t_end = P.pos_dev ? min(P.t_end, *P.pos_dev + P.pos_add) : P.t_end;
+    // Everything up to grid_dependency_wait() touches only static tables, so under a programmatic
+    // launch it overlaps the tail of the preceding kernel (the step's append / query rotation).
+    grid_launch_dependents();
     const int t0 = P.t_begin + split * P.chunk;
-    const int t1 = min(t_end, t0 + P.chunk);
-    const int n_tok = max(0, t1 - t0);
-    const int n_tiles = (n_tok + kTileTok - 1) / kTileTok;
 
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kStages;
@@ -139,8 +138,13 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     const size_t bh_vn = (size_t)b * P.vn_sb + (size_t)h * P.vn_sh;
     if (warp == kConsumerWarps) {
         // ------------------------------ producer ------------------------------
-        // Starts streaming at once; the consumer warps build their tables meanwhile.
+        // Starts streaming as soon as the preceding kernel's rows are visible; the consumer warps build
+        // their tables meanwhile.
         if (lane == 0) {
+            grid_dependency_wait();
+            const int t_end = P.pos_dev ? min(P.t_end, *P.pos_dev + P.pos_add) : P.t_end;
+            const int t1 = min(t_end, t0 + P.chunk);
+            const int n_tiles = (max(0, t1 - t0) + kTileTok - 1) / kTileTok;
             const uint64_t pol = l2_evict_first_policy();
             for (int it = 0; it < n_tiles; ++it) {
                 const int st = it % kStages, use = it / kStages;
@@ -165,11 +169,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
                 mbar_arrive_expect_tx(&full[st], total);
                 for (int c = 0; c < 4; ++c) {
                     const uint8_t* al = src[c] - (reinterpret_cast<uintptr_t>(src[c]) & 15u);
-#ifdef BGTQ_EXP_NO_HINT
-                    bulk_g2s(sb + dst[c], al, sz[c], &full[st]);
-#else
                     bulk_g2s_hint(sb + dst[c], al, sz[c], &full[st], pol);
-#endif
                 }
             }
         }
@@ -179,24 +179,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     {
         const BgtqHeadDesc& d = P.desc[h];
         for (int i = tid; i < 528; i += kConsumerWarps * 32) cbk[i] = i < 512 ? d.codebook[i] : d.v_lut[i - 512];
-    }
-    if (warp == 0) {   // lane (r, j): query r, this lane's 4 codes of every k-tile
-        const int r = lane >> 2, j = lane & 3;
-        const bool q_ok = r < P.gqa;
-        const __half* qrow = P.q_rot + ((size_t)b * P.n_q + (size_t)h * P.gqa + (q_ok ? r : 0)) * kHD;
-        for (int s = 0; s < hp.n_steps; ++s) {
-            const DecStep stp = hp.steps[s];
-            const int d0 = (int)(stp.q & 0xFFu) + j * (int)((stp.q >> 8) & 0x3Fu);
-            const int end = (int)((stp.q >> 14) & 0xFFu);
-            const uint32_t* src = reinterpret_cast<const uint32_t*>(qrow + d0);
-            const uint32_t esh = (stp.b >> 10) & 31u;
-            uint4 v;
-            v.x = (q_ok && d0 < end) ? __ldg(src) : 0u;
-            v.y = (q_ok && d0 + 2 < end) ? __ldg(src + 1) : 0u;
-            v.z = lut_rel + (stp.c >> 16) + (((uint32_t)lane << 2) & ((1u << esh) - 1u));
-            v.w = (stp.a & 0xFFFu) + j * ((stp.a >> 12) & 0x3FFu);
-            stepl[s * 32 + lane] = v;
-        }
     }
     if (warp == 1 && lane < hp.n_seg) {   // per segment: {n_kt | kt/unit << 8 | pair << 16 | norm offset << 20,
                                           //  first rotate, rotate step | pair stride << 8, scaled index mask}
@@ -225,6 +207,28 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
         for (uint32_t i = tid; i < (uint32_t)P.plan.v_n_words; i += kConsumerWarps * 32) {
             const uint32_t e = i >> VCfg<VB>::REP_SHIFT;
             lut[hp.v_word_off + i] = cbk[512 + ((e & smk) & vm)] | (uint32_t(cbk[512 + ((e >> VB) & vm)]) << 16);
+        }
+    }
+    grid_dependency_wait();
+    const int t_end = P.pos_dev ? min(P.t_end, *P.pos_dev + P.pos_add) : P.t_end;
+    const int t1 = min(t_end, t0 + P.chunk);
+    const int n_tiles = (max(0, t1 - t0) + kTileTok - 1) / kTileTok;
+    if (warp == 0) {   // lane (r, j): query r, this lane's 4 codes of every k-tile
+        const int r = lane >> 2, j = lane & 3;
+        const bool q_ok = r < P.gqa;
+        const __half* qrow = P.q_rot + ((size_t)b * P.n_q + (size_t)h * P.gqa + (q_ok ? r : 0)) * kHD;
+        for (int s = 0; s < hp.n_steps; ++s) {
+            const DecStep stp = hp.steps[s];
+            const int d0 = (int)(stp.q & 0xFFu) + j * (int)((stp.q >> 8) & 0x3Fu);
+            const int end = (int)((stp.q >> 14) & 0xFFu);
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(qrow + d0);
+            const uint32_t esh = (stp.b >> 10) & 31u;
+            uint4 v;
+            v.x = (q_ok && d0 < end) ? __ldg(src) : 0u;
+            v.y = (q_ok && d0 + 2 < end) ? __ldg(src + 1) : 0u;
+            v.z = lut_rel + (stp.c >> 16) + (((uint32_t)lane << 2) & ((1u << esh) - 1u));
+            v.w = (stp.a & 0xFFFu) + j * ((stp.a >> 12) & 0x3FFu);
+            stepl[s * 32 + lane] = v;
         }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
@@ -687,8 +691,8 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode(
         return BGTQ_E_LAUNCH;
     }
     dim3 grid(n_splits, n_kv, n_batch);
-    kern<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(P);
-    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+    return launch_kernel(kern, grid, dim3(kThreads), smem, static_cast<cudaStream_t>(stream),
+                         (P.plan.flags & BGTQ_DEC_PROGRAMMATIC) != 0, P) == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 
 // ---------------------------------------------------------------------------
@@ -744,5 +748,5 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_combined_noall
                                t_begin, t_end, n_splits, scale, sc->part_o, sc->part_lse, status, nullptr, 0, stream);
     if (rc != BGTQ_OK) return rc;
     return bgtq_combine(sc->part_o, sc->part_lse, n_splits, v_rot, nullptr, nullptr, n_batch, n_q, n_kv, out, o_sb,
-                        o_sh, nullptr, lse_out, stream);
+                        o_sh, nullptr, lse_out, 0, stream);
 }

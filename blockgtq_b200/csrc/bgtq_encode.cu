@@ -296,6 +296,8 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     float w[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) w[i] = __ldg(W + (size_t)i * kHD);
+    grid_launch_dependents();
+    grid_dependency_wait();       // inputs and the slot position come from earlier work in the stream
     const int t0 = E.pos_dev ? *E.pos_dev : E.t0;
 
     float x = 0.f;
@@ -502,6 +504,6 @@ extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare(
     P.n_q = n_q; P.do_rot = do_rot ? 1 : 0;
     const int64_t items = (int64_t)(do_rot ? n_batch * n_q : 0) + 2LL * n_batch * n_kv;
     if (items > 0x7fffffffLL) return BGTQ_E_TOOBIG;
-    prep_kernel<<<(unsigned)items, 512, 0, static_cast<cudaStream_t>(stream)>>>(P);
-    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+    return launch_kernel(prep_kernel, dim3((unsigned)items), dim3(512), 0, static_cast<cudaStream_t>(stream),
+                         (flags & BGTQ_ENC_PROGRAMMATIC) != 0, P) == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }

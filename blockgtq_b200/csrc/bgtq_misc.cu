@@ -48,6 +48,8 @@ __global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const
 #pragma unroll
         for (int i = 0; i < 32; ++i) w[i] = __ldg(R + (size_t)i * kHD);
     }
+    grid_launch_dependents();
+    grid_dependency_wait();       // the partials come from the preceding kernel
     const float* lse = part_lse + row * n_splits;
     float mx = -INFINITY;
     for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, lse[s]);
@@ -180,16 +182,16 @@ extern "C" __attribute__((visibility("default"))) int bgtq_rotate_q(const BgtqHe
 
 extern "C" __attribute__((visibility("default"))) int bgtq_combine(const float* part_o, const float* part_lse, int32_t n_splits, const float* v_rot,
                             const float* buf_o, const float* buf_lse, int32_t n_batch, int32_t n_q, int32_t n_kv,
-                            void* out, int64_t o_sb, int64_t o_sh, float* out_f32, float* lse_out, void* stream) {
+                            void* out, int64_t o_sb, int64_t o_sh, float* out_f32, float* lse_out, int32_t flags, void* stream) {
     if (!part_o || !part_lse || n_splits < 1 || n_batch < 1 || n_kv < 1 || n_q < n_kv || n_q % n_kv)
         return BGTQ_E_BADARG;
     if ((buf_o == nullptr) != (buf_lse == nullptr)) return BGTQ_E_BADARG;
     if (!out && !out_f32) return BGTQ_E_BADARG;
     if (n_batch > 65535) return BGTQ_E_TOOBIG;
-    combine_kernel<<<dim3(n_q, n_batch), 512, 0, static_cast<cudaStream_t>(stream)>>>(
-        part_o, part_lse, n_splits, v_rot, buf_o, buf_lse, n_q, n_kv, static_cast<__half*>(out), o_sb, o_sh, out_f32,
-        lse_out);
-    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+    return launch_kernel(combine_kernel, dim3(n_q, n_batch), dim3(512), 0, static_cast<cudaStream_t>(stream),
+                         (flags & BGTQ_COMBINE_PROGRAMMATIC) != 0, part_o, part_lse, n_splits, v_rot, buf_o, buf_lse,
+                         n_q, n_kv, static_cast<__half*>(out), o_sb, o_sh, out_f32, lse_out) == cudaSuccess
+               ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 
 extern "C" __attribute__((visibility("default"))) int bgtq_buffer_attn(const void* q, int64_t q_sb, int64_t q_sh, const void* k_buf, const void* v_buf,

@@ -234,8 +234,9 @@ def decode(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_norms, t_be
 
 
 def combine(part_o, part_lse, n_kv, *, v_rot=None, buf_o=None, buf_lse=None, out=None,
-            want_f32=False, want_lse=False):
-    """Merge (B, n_q, S, 128)/(B, n_q, S) partials -> fp16 (B, n_q, 128) [+ f32 copy, total LSE]."""
+            want_f32=False, want_lse=False, programmatic=False):
+    """Merge (B, n_q, S, 128)/(B, n_q, S) partials -> fp16 (B, n_q, 128) [+ f32 copy, total LSE].
+    ``programmatic``: launch as a programmatic dependent of the preceding kernel (see bgtq.h)."""
     B, n_q, S, _ = part_o.shape
     dev = part_o.device
     if out is None:
@@ -245,7 +246,7 @@ def combine(part_o, part_lse, n_kv, *, v_rot=None, buf_o=None, buf_lse=None, out
     _lib.check(_lib.lib().bgtq_combine(
         _lib.ptr(part_o), _lib.ptr(part_lse), S, _lib.ptr(v_rot), _lib.ptr(buf_o), _lib.ptr(buf_lse),
         B, n_q, n_kv, _lib.ptr(out), out.stride(0), out.stride(1), _lib.ptr(o32), _lib.ptr(lse),
-        _lib.stream_ptr(dev)), "bgtq_combine")
+        _lib.COMBINE_PROGRAMMATIC if programmatic else 0, _lib.stream_ptr(dev)), "bgtq_combine")
     _lib.count_launch()
     return out, o32, lse
 

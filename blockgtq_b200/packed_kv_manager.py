@@ -64,6 +64,7 @@ class BlockGTQKVManager:
         # storage layout: bit-packed (this class in the reference) or the production cache's
         # nibble/raw "mixed" K rows with corrected norms and 4-bit V rows (production_cache.py:60-86)
         self.k_mixed, self.v_nibble = bool(k_mixed), bool(v_nibble)
+        self.programmatic = True              # chain the step's kernels as programmatic dependent launches
         self._enc_flags = (_lib.ENC_K_MIXED if k_mixed else 0) | (_lib.ENC_V_NIBBLE if v_nibble else 0)
         self._dec_flags = (_lib.DEC_K_MIXED if k_mixed else 0) | (_lib.DEC_V_NIBBLE if v_nibble else 0)
         # single-token decode steps are captured once per layer and replayed (the reference graphs only
@@ -256,14 +257,18 @@ class BlockGTQKVManager:
         lt = self._layers[li]
         gq, gk, gv = self.static_inputs()
         baked = all(self.quantizers[li][h]._q_perm_baked for h in range(self.n_kv))
+        # the three kernels are chained as programmatic dependents: each sets up its static tables while
+        # the one before it drains, and waits on the device before touching the step's data
+        pd = self.programmatic
         step_prepare(lt, None if baked else gq, gk, gv, 0, self._k_packed[li], self._k_norms[li],
                      self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos,
-                     flags=self._enc_flags)
+                     flags=self._enc_flags | (_lib.ENC_PROGRAMMATIC if pd else 0))
         q_rot = gq[:, :, 0].contiguous() if baked else self._q_rot
         decode(lt, q_rot, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
                0, self.max_T, n_splits=self._n_splits, scale=self.scale, status=self._status,
-               part_o=self._part_o, part_lse=self._part_lse, pos_dev=self._pos, pos_add=1, flags=self._dec_flags)
-        combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li])
+               part_o=self._part_o, part_lse=self._part_lse, pos_dev=self._pos, pos_add=1,
+               flags=self._dec_flags | (_lib.DEC_PROGRAMMATIC if pd else 0))
+        combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li], programmatic=pd)
 
     def _replay_layer(self, li: int, q, k_new, v_new) -> torch.Tensor:
         self._ensure_storage()

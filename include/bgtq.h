@@ -83,6 +83,16 @@ const char* bgtq_error_string(int code);       /* host pointer to a static strin
 #define BGTQ_ENC_SKIP_K 8
 #define BGTQ_ENC_SKIP_V 16
 #define BGTQ_ENC_FORCE_SIMT 32  /* always use the small-batch fp32 kernel (>= 64 rows normally use tensor cores) */
+#define BGTQ_ENC_PROGRAMMATIC 64  /* bgtq_step_prepare only: programmatic dependent launch, see below */
+
+/* Programmatic dependent launch (BGTQ_ENC_PROGRAMMATIC, BGTQ_DEC_PROGRAMMATIC,
+ * BGTQ_COMBINE_PROGRAMMATIC).  The kernel is launched with CUDA's programmatic
+ * stream-serialization attribute: its blocks may become resident while the
+ * preceding kernel of the stream is still running, set up their static tables,
+ * and wait on the device for that kernel to complete before they touch any
+ * per-call input or output.  Results are identical; the launch latency and the
+ * set-up of each kernel of a decode step overlap the previous kernel's tail.
+ * Safe after any kind of preceding work; capturable in a CUDA graph. */
 
 /* Encode K and V rows of all KV heads of one layer and write them straight
  * into their cache slots.
@@ -154,6 +164,7 @@ int bgtq_step_prepare(const BgtqHeadDesc* desc, const float* rot_k, const float*
 /* ---- decode --------------------------------------------------------------- */
 #define BGTQ_DEC_K_MIXED 1        /* k_packed rows are in the nibble/raw mixed layout */
 #define BGTQ_DEC_V_NIBBLE 2       /* v_packed rows are 4-bit nibbles */
+#define BGTQ_DEC_PROGRAMMATIC 4   /* launch bgtq_decode as a programmatic dependent of the preceding kernel */
 
 /* Opaque launch plan of the decode kernel for the KV heads of one layer (host
  * memory, plain bytes, copyable).  Built once per layer from the HOST copy of
@@ -233,12 +244,14 @@ int bgtq_buffer_attn(const void* q, int64_t q_sb, int64_t q_sh,
  *   out        = LSE-weighted mix of packed_out and buf_o  (buf_o may be NULL)
  * out: fp16 (n_batch, n_q, 128) at out + b*o_sb + hq*o_sh; out_f32 / lse_out
  * optional: the un-rounded result (n_batch, n_q, 128) and total LSE (n_batch, n_q),
- * the pair another rank needs to continue the merge. */
+ * the pair another rank needs to continue the merge.
+ * flags: 0 or BGTQ_COMBINE_PROGRAMMATIC. */
+#define BGTQ_COMBINE_PROGRAMMATIC 1
 int bgtq_combine(const float* part_o, const float* part_lse, int32_t n_splits,
                  const float* v_rot, const float* buf_o, const float* buf_lse,
                  int32_t n_batch, int32_t n_q, int32_t n_kv,
                  void* out, int64_t o_sb, int64_t o_sh,
-                 float* out_f32, float* lse_out, void* stream);
+                 float* out_f32, float* lse_out, int32_t flags, void* stream);
 
 /* bgtq_decode followed by bgtq_combine with NO caller-provided scratch: the
  * split partials go to a fixed array inside the library instead of part_o /

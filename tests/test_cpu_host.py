@@ -100,7 +100,7 @@ def test_entry_points_reject_bad_arguments_without_a_gpu():
     L = _lib.lib()
     assert L.bgtq_decode(None, None, None, None, 0, 0, 0, None, 0, 0, 0, None, 0, 0, 0, None, 0, 0, 0,
                          1, 8, 2, 0, 10, 1, 0.1, None, None, None, None, 0, None) == -1
-    assert L.bgtq_combine(None, None, 1, None, None, None, 1, 8, 2, None, 0, 0, None, None, None) == -1
+    assert L.bgtq_combine(None, None, 1, None, None, None, 1, 8, 2, None, 0, 0, None, None, 0, None) == -1
     assert L.bgtq_encode(None, None, None, None, 0, 0, 0, None, 0, 0, 0, 1, 2, 1, 0, None, 0, 0, 0, 8,
                          None, 0, 0, 0, 1, None, 0, 0, 0, None, 0, 0, 0, None, None, 0, None, None) == -1
 
