@@ -36,6 +36,14 @@ WORKLOADS = {
     # BASELINE.json configs[2]: Llama-3.1-8B shape, K2V2, batch 32, context 16384, fp16 sink 4 + window 128
     "llama3.1-8b_k2v2_b32_t16384_sink4_win128": dict(layers=32, n_q=32, n_kv=8, batch=32, ctx=16384, k_bits=2.0,
                                                      v_bits=2, theta=5e5, n_sink=4, window=128),
+    # BASELINE.json configs[3]: one 131072-token sequence, Llama-3.1-8B shape, K2V2, sequence chunks across
+    # GPUs with one all-gather of (O, LSE) per layer (strong scaling: the total context is fixed)
+    "llama3.1-8b_k2v2_b1_t131072_seqshard": dict(layers=32, n_q=32, n_kv=8, batch=1, ctx=131072, k_bits=2.0,
+                                                 v_bits=2, theta=5e5, n_sink=0, window=0, mode="seq"),
+    # BASELINE.json configs[4]: bulk (prefill) encode, Mistral-Nemo-12B shape, 4 x 32768 tokens per layer into the
+    # BlockGTQKVManager layout, then single-token appends; two layers with separate inputs stand for the 40
+    "mistral-nemo-12b_k3v3_encode_b4_t32768": dict(layers=2, n_q=32, n_kv=8, batch=4, ctx=32768, k_bits=3.0,
+                                                   v_bits=3, theta=1e6, n_sink=0, window=0, mode="encode"),
     # small variant of configs[1] for quick runs and profiler captures
     "qwen2.5-3b_k3v3_b8_t32768_4layers": dict(layers=4, n_q=16, n_kv=2, batch=8, ctx=32768, k_bits=3.0, v_bits=3,
                                               theta=1e6, n_sink=0, window=0),
@@ -61,14 +69,16 @@ def synth_keys(gen, shape_bt, theta, device):
     return torch.cat([a * c - b * sn, a * sn + b * c], dim=-1).half()
 
 
-def build_manager(w, device, seed, extra_tokens):
+def build_manager(w, device, seed, extra_tokens, ctx=None, graph=None):
     """Calibrate every (layer, head) on 2048 synthetic tokens, then bulk-encode the context."""
     from blockgtq_b200 import BlockGTQKVManager
     gen = torch.Generator(device=device).manual_seed(seed)
-    L, n_q, n_kv, B, T = w["layers"], w["n_q"], w["n_kv"], w["batch"], w["ctx"]
+    L, n_q, n_kv, B = w["layers"], w["n_q"], w["n_kv"], w["batch"]
+    T = w["ctx"] if ctx is None else ctx
     gqa = n_q // n_kv
     mgr = BlockGTQKVManager(L, n_q, n_kv, HD, max_seq_len=T + extra_tokens, batch_size=B, k_avg_bits=w["k_bits"],
-                            v_bits=w["v_bits"], device=device, n_sink=w["n_sink"], recent_window=w["window"])
+                            v_bits=w["v_bits"], device=device, n_sink=w["n_sink"], recent_window=w["window"],
+                            use_cuda_graph=graph)
     mgr.programmatic = os.environ.get("BGTQ_NO_PROGRAMMATIC", "") == ""
     for li in range(L):
         ck = torch.stack([synth_keys(gen, (1, 2048), w["theta"], device)[0] for _ in range(n_kv)])
@@ -181,6 +191,215 @@ def run_reference(args, w, name, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_seq_sharded(args, w, rank, world, dev):
+    """One long sequence cut into per-rank chunks: every layer runs the local split-KV decode + combine,
+    one all-gather of the (O, LSE) partials, and the final combine on every rank; the rank that owns
+    the tail also appends the step's token.  Strong scaling: the total context is fixed."""
+    import torch.distributed as dist
+    from blockgtq_b200 import _lib
+    from blockgtq_b200.layer import combine
+    from blockgtq_b200.sharding import chunk_bounds, sharded_attend
+    K, W = args.steps, args.warmup
+    n_total = 2 * (K + W) + 4
+    L, B, n_q, n_kv, T = w["layers"], w["batch"], w["n_q"], w["n_kv"], w["ctx"]
+    lo, hi = chunk_bounds(T, world, rank)
+    owner = world - 1                       # appended tokens extend the last chunk
+    mgr, gen = build_manager(w, dev, seed=1234, extra_tokens=n_total + 16, ctx=hi - lo, graph=False)
+    qs = (torch.randn(n_total, L, B, n_q, 1, HD, generator=gen, device=dev) * 2).half()
+    ks = torch.stack([torch.stack([synth_keys(gen, (B * n_kv, 1), w["theta"], dev).reshape(B, n_kv, 1, HD)
+                                   for _ in range(L)]) for _ in range(n_total)])
+    vs = torch.randn(n_total, L, B, n_kv, 1, HD, generator=gen, device=dev).half()
+    hq = torch.cat([qs, ks, vs], dim=3).cpu().pin_memory()
+    hout = torch.empty(L, B, n_q, HD, dtype=torch.float16).pin_memory()
+    stage = torch.empty_like(hq[0, 0], device=dev)
+    step_no = [0]
+
+    def layer(li, q, k, v):
+        t = mgr.seq_len
+        if rank == owner:
+            mgr._append_tokens(li, k, v, t)
+        n_here = t + (1 if rank == owner else 0)
+        if world == 1:
+            return mgr.attend(li, q, n_here)[0]
+        return sharded_attend(mgr, li, q, seq_len=n_here)
+
+    def step_device():
+        s = step_no[0]
+        for li in range(L):
+            layer(li, qs[s, li], ks[s, li], vs[s, li])
+        if rank == owner:
+            mgr.increment_seq_len()
+        step_no[0] += 1
+
+    def step_e2e():
+        s = step_no[0]
+        for li in range(L):
+            stage.copy_(hq[s, li], non_blocking=True)
+            out = layer(li, stage[:, :n_q], stage[:, n_q:n_q + n_kv], stage[:, n_q + n_kv:])
+            hout[li].copy_(out, non_blocking=True)
+        if rank == owner:
+            mgr.increment_seq_len()
+        torch.cuda.synchronize()
+        step_no[0] += 1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(W):
+        step_device()
+    sampler = clocks_sampler(dev.index) if rank == 0 else None
+    l0 = _lib.launches
+    ms_total = timed(step_device, K)
+    launches = _lib.launches - l0
+    clocks = clocks_summary(sampler)
+    for _ in range(W):
+        step_e2e()
+    ms_e2e = timed(step_e2e, K)
+    live = torch.tensor([float(mgr.live_bytes_per_step())], device=dev)
+    if world > 1:
+        dist.all_reduce(live)
+    if rank == 0:
+        ms_step = ms_total / K
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        gbs = float(live.item()) / world / (ms_step * 1e-3) / 1e9        # per GPU, whole step
+        print(json.dumps({
+            "metric": "decode_tokens_per_s", "value": B / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "layers": L, "batch": B, "n_q": n_q, "n_kv": n_kv, "context": T,
+                       "tokens_per_gpu": hi - lo, "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"],
+                       "parallelism": f"sequence chunks x{world}, one all-gather of (O, LSE) per layer",
+                       "exchange_bytes_per_layer": B * n_q * (HD + 1) * 4,
+                       "l2": "inputs larger than L2 (packed cache bytes per step >> 126 MB), no flush"},
+            "roofline": {"bound": "hbm", "kernel": "whole step (eager launches)", "achieved": gbs, "peak": peak,
+                         "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                         "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"},
+            "e2e": {"value": B / (ms_e2e / K * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": int(L * hq[0, 0].numel() * 2),
+                    "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": ms_e2e / K},
+            "gpu_launches": launches, "clocks": clocks}), flush=True)
+
+
+def run_encode(args, w, rank, world, dev):
+    """Bulk encode of a whole context per layer (prefill), then the latency of single-token appends."""
+    import torch.distributed as dist
+    from blockgtq_b200 import BlockGTQKVManager, _lib
+    K, W = args.steps, args.warmup
+    L, B, n_q, n_kv, T = w["layers"], w["batch"], w["n_q"], w["n_kv"], w["ctx"]
+    gqa = n_q // n_kv
+    gen = torch.Generator(device=dev).manual_seed(4321 + rank)
+    mgr = BlockGTQKVManager(L, n_q, n_kv, HD, max_seq_len=T + 1024, batch_size=B, k_avg_bits=w["k_bits"],
+                            v_bits=w["v_bits"], device=dev, use_cuda_graph=False)
+    for li in range(L):
+        ck = torch.stack([synth_keys(gen, (1, 2048), w["theta"], dev)[0] for _ in range(n_kv)])
+        cq = torch.stack([synth_keys(gen, (gqa, 2048), w["theta"], dev).reshape(-1, HD) for _ in range(n_kv)])
+        mgr.calibrate(li, cq.float(), ck.float())
+    ks = [torch.stack([synth_keys(gen, (B, T), w["theta"], dev) for _ in range(n_kv)], dim=1) for _ in range(L)]
+    vs = [torch.randn(B, n_kv, T, HD, generator=gen, device=dev).half() for _ in range(L)]
+    hk = [k.cpu().pin_memory() for k in ks]
+    hv = [v.cpu().pin_memory() for v in vs]
+    stage_k, stage_v = torch.empty_like(ks[0]), torch.empty_like(vs[0])
+
+    def step_device():
+        for li in range(L):
+            mgr._append_tokens(li, ks[li], vs[li], 0)
+
+    def step_e2e():
+        for li in range(L):
+            stage_k.copy_(hk[li], non_blocking=True)
+            stage_v.copy_(hv[li], non_blocking=True)
+            mgr._append_tokens(li, stage_k, stage_v, 0)
+        torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(W):
+        step_device()
+    sampler = clocks_sampler(dev.index) if rank == 0 else None
+    l0 = _lib.launches
+    ms_total = timed(step_device, K)
+    launches = _lib.launches - l0
+    clocks = clocks_summary(sampler)
+    step_e2e()
+    ms_e2e = timed(step_e2e, max(1, K // 4))
+    # single-token appends (B rows per KV head): latency of one layer's append
+    mgr.seq_len = T
+    k1, v1 = ks[0][:, :, :1].contiguous(), vs[0][:, :, :1].contiguous()
+    for i in range(8):
+        mgr._append_tokens(0, k1, v1, T + i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(512):
+        mgr._append_tokens(i % L, k1, v1, T + 8 + i)
+    e1.record()
+    torch.cuda.synchronize()
+    append_us = e0.elapsed_time(e1) / 512 * 1e3
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        pms = [mgr.quantizers[0][h].pack_meta for h in range(n_kv)]
+        row_bytes = sum(pm["total_packed_bytes"] + 2 * sum(1 for key in pm if isinstance(key, int)) for pm in pms) \
+            + n_kv * (mgr._layers[0].vpb + 2)
+        alg = B * T * (n_kv * 512 + row_bytes)               # per launch (one layer)
+        ms_launch = ms_total / (K * L)
+        print(json.dumps({
+            "metric": "prefill_encode_tokens_per_s", "value": world * B * T * L / (ms_total / K * 1e-3),
+            "unit": "token-layers/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "layers_per_step": L, "batch_per_gpu": B, "n_kv": n_kv, "tokens": T,
+                       "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"], "parallelism": f"batch x{world}",
+                       "l2": "each layer's fp16 K/V input is 537 MB, larger than L2; no flush",
+                       "append_us_per_layer": append_us},
+            "roofline": {"bound": "hbm", "kernel": "encode_tc_kernel", "achieved": alg / (ms_launch * 1e-3) / 1e9,
+                         "peak": peak, "unit": "GB/s", "frac": alg / (ms_launch * 1e-3) / 1e9 / peak, "traffic": None,
+                         "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback",
+                         "algorithmic_bytes_per_launch": alg, "launch_ms": ms_launch},
+            "e2e": {"value": world * B * T * L / (ms_e2e / max(1, K // 4) * 1e-3), "unit": "token-layers/s",
+                    "h2d_bytes_per_step": int(L * 2 * ks[0].numel() * 2), "d2h_bytes_per_step": 0,
+                    "ms_per_step": ms_e2e / max(1, K // 4)},
+            "gpu_launches": launches, "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -210,6 +429,17 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+
+    if w.get("mode") == "encode":
+        run_encode(args, w, rank, world, dev)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if w.get("mode") == "seq":
+        run_seq_sharded(args, w, rank, world, dev)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     K, W = args.steps, args.warmup
     n_steps_total = 2 * (K + W) + min(K, 5) + 2
@@ -329,7 +559,7 @@ def main():
             "gpu_launches": launches,
             "clocks": clocks,
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
             dt, sample = cpu_decode_sample(w)

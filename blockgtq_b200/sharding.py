@@ -70,12 +70,14 @@ def gather_partials(o32: torch.Tensor, lse: torch.Tensor, group=None):
     return part_o, part_lse
 
 
-def sharded_attend(mgr, layer_idx: int, q: torch.Tensor, group=None, *, n_splits: int = None) -> torch.Tensor:
+def sharded_attend(mgr, layer_idx: int, q: torch.Tensor, group=None, *, n_splits: int = None,
+                   seq_len: int = None) -> torch.Tensor:
     """Decode attention for one long sequence whose cache is split across the ranks of ``group``:
     local split-KV decode + combine -> all-gather of (O, LSE) -> final combine.  ``mgr`` is this
-    rank's :class:`BlockGTQKVManager` holding only its own chunk.  Returns (B, n_q, 128) fp16."""
+    rank's :class:`BlockGTQKVManager` holding only its own chunk; ``seq_len`` = number of its cached
+    tokens to attend over (default: all).  Returns (B, n_q, 128) fp16."""
     from .layer import combine
-    _out, o32, lse = mgr.attend(layer_idx, q, n_splits=n_splits, want_partial=True)
+    _out, o32, lse = mgr.attend(layer_idx, q, seq_len, n_splits=n_splits, want_partial=True)
     part_o, part_lse = gather_partials(o32, lse, group)
     out, _, _ = combine(part_o, part_lse, mgr.n_kv)
     return out
