@@ -192,19 +192,23 @@ def run_reference(args, w, name, rank, world):
 
 
 def run_seq_sharded(args, w, rank, world, dev):
-    """One long sequence cut into per-rank chunks: every layer runs the local split-KV decode + combine,
-    one all-gather of the (O, LSE) partials, and the final combine on every rank; the rank that owns
-    the tail also appends the step's token.  Strong scaling: the total context is fixed."""
+    """One long sequence cut into per-rank chunks: every layer replays one CUDA graph holding the local
+    split-KV decode + combine, one all-gather of the (O, LSE) messages and the merge of the ranks'
+    messages; the rank that owns the tail also appends the step's token.  Strong scaling: the total
+    context is fixed."""
     import torch.distributed as dist
     from blockgtq_b200 import _lib
     from blockgtq_b200.layer import combine
-    from blockgtq_b200.sharding import chunk_bounds, sharded_attend
+    from blockgtq_b200.sharding import chunk_bounds
     K, W = args.steps, args.warmup
     n_total = 2 * (K + W) + 4
     L, B, n_q, n_kv, T = w["layers"], w["batch"], w["n_q"], w["n_kv"], w["ctx"]
     lo, hi = chunk_bounds(T, world, rank)
     owner = world - 1                       # appended tokens extend the last chunk
-    mgr, gen = build_manager(w, dev, seed=1234, extra_tokens=n_total + 16, ctx=hi - lo, graph=False)
+    mgr, gen = build_manager(w, dev, seed=1234, extra_tokens=n_total + 16, ctx=hi - lo)
+    if world > 1:
+        from blockgtq_b200.sharding import SequenceShard
+        SequenceShard(mgr, owner=owner)
     qs = (torch.randn(n_total, L, B, n_q, 1, HD, generator=gen, device=dev) * 2).half()
     ks = torch.stack([torch.stack([synth_keys(gen, (B * n_kv, 1), w["theta"], dev).reshape(B, n_kv, 1, HD)
                                    for _ in range(L)]) for _ in range(n_total)])
@@ -215,20 +219,13 @@ def run_seq_sharded(args, w, rank, world, dev):
     step_no = [0]
 
     def layer(li, q, k, v):
-        t = mgr.seq_len
-        if rank == owner:
-            mgr._append_tokens(li, k, v, t)
-        n_here = t + (1 if rank == owner else 0)
-        if world == 1:
-            return mgr.attend(li, q, n_here)[0]
-        return sharded_attend(mgr, li, q, seq_len=n_here)
+        return mgr.append_and_attend(li, q, k, v)[:, :, 0]
 
     def step_device():
         s = step_no[0]
         for li in range(L):
             layer(li, qs[s, li], ks[s, li], vs[s, li])
-        if rank == owner:
-            mgr.increment_seq_len()
+        mgr.increment_seq_len()
         step_no[0] += 1
 
     def step_e2e():
@@ -237,8 +234,7 @@ def run_seq_sharded(args, w, rank, world, dev):
             stage.copy_(hq[s, li], non_blocking=True)
             out = layer(li, stage[:, :n_q], stage[:, n_q:n_q + n_kv], stage[:, n_q + n_kv:])
             hout[li].copy_(out, non_blocking=True)
-        if rank == owner:
-            mgr.increment_seq_len()
+        mgr.increment_seq_len()
         torch.cuda.synchronize()
         step_no[0] += 1
 
@@ -291,7 +287,7 @@ def run_seq_sharded(args, w, rank, world, dev):
                        "parallelism": f"sequence chunks x{world}, one all-gather of (O, LSE) per layer",
                        "exchange_bytes_per_layer": B * n_q * (HD + 1) * 4,
                        "l2": "inputs larger than L2 (packed cache bytes per step >> 126 MB), no flush"},
-            "roofline": {"bound": "hbm", "kernel": "whole step (eager launches)", "achieved": gbs, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": gbs, "peak": peak,
                          "unit": "GB/s", "frac": gbs / peak, "traffic": None,
                          "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"},
             "e2e": {"value": B / (ms_e2e / K * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": int(L * hq[0, 0].numel() * 2),

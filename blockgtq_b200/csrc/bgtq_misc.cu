@@ -34,7 +34,10 @@ __global__ void __launch_bounds__(128) rotate_q_kernel(const BgtqHeadDesc* desc,
 __global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const float* part_lse, int n_splits,
                                                        const float* v_rot, const float* buf_o, const float* buf_lse,
                                                        int n_q, int n_kv, __half* out, int64_t o_sb, int64_t o_sh,
-                                                       float* out_f32, float* lse_out) {
+                                                       float* out_f32, float* lse_out, int64_t rank_stride) {
+    // rank_stride == 0: partial s of row r at part_o[(r * n_splits + s) * 128], part_lse[r * n_splits + s];
+    // rank_stride  > 0: partial s is a whole (rows, 128) block + (rows) block, rank_stride floats apart
+    // (the receive buffer of an all-gather of per-rank results)
     // thread (d = tid % 128, c = tid / 128): output dim d; quarter c of the splits and of the rotation rows
     __shared__ float pnum[4][kHD];
     __shared__ float pden[4];
@@ -50,17 +53,19 @@ __global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const
     }
     grid_launch_dependents();
     grid_dependency_wait();       // the partials come from the preceding kernel
-    const float* lse = part_lse + row * n_splits;
+    const float* lse = rank_stride ? part_lse + row : part_lse + row * n_splits;
+    const float* po = rank_stride ? part_o + row * kHD + d : part_o + row * n_splits * kHD + d;
+    const int64_t sl = rank_stride ? rank_stride : 1, so = rank_stride ? rank_stride : kHD;
     float mx = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, lse[s]);
+    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, lse[s * sl]);
     float num = 0.f, den = 0.f;
     if (mx > -INFINITY) {
         for (int s = c; s < n_splits; s += 4) {
-            const float l = lse[s];
+            const float l = lse[s * sl];
             if (l == -INFINITY) continue;
             const float a = expf(l - mx);
             den += a;
-            num = fmaf(a, part_o[(row * n_splits + s) * kHD + d], num);
+            num = fmaf(a, po[s * so], num);
         }
     }
     pnum[c][d] = num;
@@ -190,7 +195,22 @@ extern "C" __attribute__((visibility("default"))) int bgtq_combine(const float* 
     if (n_batch > 65535) return BGTQ_E_TOOBIG;
     return launch_kernel(combine_kernel, dim3(n_q, n_batch), dim3(512), 0, static_cast<cudaStream_t>(stream),
                          (flags & BGTQ_COMBINE_PROGRAMMATIC) != 0, part_o, part_lse, n_splits, v_rot, buf_o, buf_lse,
-                         n_q, n_kv, static_cast<__half*>(out), o_sb, o_sh, out_f32, lse_out) == cudaSuccess
+                         n_q, n_kv, static_cast<__half*>(out), o_sb, o_sh, out_f32, lse_out, (int64_t)0) == cudaSuccess
+               ? BGTQ_OK : BGTQ_E_LAUNCH;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_combine_ranks(const float* gathered, int32_t n_ranks, int64_t rank_stride,
+                                  int32_t n_batch, int32_t n_q, void* out, int64_t o_sb, int64_t o_sh, int32_t flags,
+                                  void* stream) {
+    if (!gathered || !out || n_ranks < 1 || n_batch < 1 || n_q < 1) return BGTQ_E_BADARG;
+    const int64_t rows = (int64_t)n_batch * n_q;
+    if (rank_stride < rows * (kHD + 1)) return BGTQ_E_BADARG;
+    if (n_batch > 65535) return BGTQ_E_TOOBIG;
+    return launch_kernel(combine_kernel, dim3(n_q, n_batch), dim3(512), 0, static_cast<cudaStream_t>(stream),
+                         (flags & BGTQ_COMBINE_PROGRAMMATIC) != 0, gathered, gathered + rows * kHD, n_ranks,
+                         static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
+                         static_cast<const float*>(nullptr), n_q, 1, static_cast<__half*>(out), o_sb, o_sh,
+                         static_cast<float*>(nullptr), static_cast<float*>(nullptr), rank_stride) == cudaSuccess
                ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 

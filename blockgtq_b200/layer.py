@@ -233,16 +233,32 @@ def decode(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_norms, t_be
     return part_o, part_lse
 
 
+def combine_ranks(gathered, n_batch, n_q, *, out=None):
+    """Merge the all-gathered per-rank messages ``gathered`` (W, n_batch*n_q*129) fp32, each
+    [O (B, n_q, 128) | LSE (B, n_q)], into fp16 (B, n_q, 128)."""
+    _lib.require_cuda(gathered, "gathered")
+    W = gathered.shape[0]
+    if out is None:
+        out = torch.empty(n_batch, n_q, HD, dtype=torch.float16, device=gathered.device)
+    _lib.check(_lib.lib().bgtq_combine_ranks(
+        _lib.ptr(gathered), W, gathered.stride(0), n_batch, n_q, _lib.ptr(out), out.stride(0), out.stride(1),
+        0, _lib.stream_ptr(gathered.device)), "bgtq_combine_ranks")
+    _lib.count_launch()
+    return out
+
+
 def combine(part_o, part_lse, n_kv, *, v_rot=None, buf_o=None, buf_lse=None, out=None,
-            want_f32=False, want_lse=False, programmatic=False):
+            want_f32=False, want_lse=False, programmatic=False, o32_out=None, lse_out=None):
     """Merge (B, n_q, S, 128)/(B, n_q, S) partials -> fp16 (B, n_q, 128) [+ f32 copy, total LSE].
     ``programmatic``: launch as a programmatic dependent of the preceding kernel (see bgtq.h)."""
     B, n_q, S, _ = part_o.shape
     dev = part_o.device
     if out is None:
         out = torch.empty(B, n_q, HD, dtype=torch.float16, device=dev)
-    o32 = torch.empty(B, n_q, HD, dtype=torch.float32, device=dev) if want_f32 else None
-    lse = torch.empty(B, n_q, dtype=torch.float32, device=dev) if want_lse else None
+    o32 = o32_out if o32_out is not None else (
+        torch.empty(B, n_q, HD, dtype=torch.float32, device=dev) if want_f32 else None)
+    lse = lse_out if lse_out is not None else (
+        torch.empty(B, n_q, dtype=torch.float32, device=dev) if want_lse else None)
     _lib.check(_lib.lib().bgtq_combine(
         _lib.ptr(part_o), _lib.ptr(part_lse), S, _lib.ptr(v_rot), _lib.ptr(buf_o), _lib.ptr(buf_lse),
         B, n_q, n_kv, _lib.ptr(out), out.stride(0), out.stride(1), _lib.ptr(o32), _lib.ptr(lse),

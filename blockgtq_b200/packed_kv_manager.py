@@ -21,7 +21,7 @@ import torch
 
 from . import _lib
 from .calib import packed_v_bytes
-from .layer import (HD, LayerTables, buffer_attn, combine, decode, default_splits, encode, rotate_q,
+from .layer import (HD, LayerTables, buffer_attn, combine, combine_ranks, decode, default_splits, encode, rotate_q,
                     step_prepare)
 from .quantizer import BlockGTQQuantizer, build_batched_encode_args
 
@@ -65,6 +65,7 @@ class BlockGTQKVManager:
         # nibble/raw "mixed" K rows with corrected norms and 4-bit V rows (production_cache.py:60-86)
         self.k_mixed, self.v_nibble = bool(k_mixed), bool(v_nibble)
         self.programmatic = True              # chain the step's kernels as programmatic dependent launches
+        self._exchange = None                 # sequence sharding: see sharding.SequenceShard
         self._enc_flags = (_lib.ENC_K_MIXED if k_mixed else 0) | (_lib.ENC_V_NIBBLE if v_nibble else 0)
         self._dec_flags = (_lib.DEC_K_MIXED if k_mixed else 0) | (_lib.DEC_V_NIBBLE if v_nibble else 0)
         # single-token decode steps are captured once per layer and replayed (the reference graphs only
@@ -260,15 +261,26 @@ class BlockGTQKVManager:
         # the three kernels are chained as programmatic dependents: each sets up its static tables while
         # the one before it drains, and waits on the device before touching the step's data
         pd = self.programmatic
-        step_prepare(lt, None if baked else gq, gk, gv, 0, self._k_packed[li], self._k_norms[li],
-                     self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos,
-                     flags=self._enc_flags | (_lib.ENC_PROGRAMMATIC if pd else 0))
+        ex = self._exchange
         q_rot = gq[:, :, 0].contiguous() if baked else self._q_rot
+        if ex is None or ex.is_owner:
+            step_prepare(lt, None if baked else gq, gk, gv, 0, self._k_packed[li], self._k_norms[li],
+                         self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos,
+                         flags=self._enc_flags | (_lib.ENC_PROGRAMMATIC if pd else 0))
+        elif not baked:                           # this rank does not hold the tail: nothing to append
+            rotate_q(lt, gq[:, :, 0], out=self._q_rot)
         decode(lt, q_rot, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
                0, self.max_T, n_splits=self._n_splits, scale=self.scale, status=self._status,
-               part_o=self._part_o, part_lse=self._part_lse, pos_dev=self._pos, pos_add=1,
+               part_o=self._part_o, part_lse=self._part_lse, pos_dev=self._pos,
+               pos_add=1 if (ex is None or ex.is_owner) else 0,
                flags=self._dec_flags | (_lib.DEC_PROGRAMMATIC if pd else 0))
-        combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li], programmatic=pd)
+        if ex is None:
+            combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li], programmatic=pd)
+        else:       # local result straight into the message, one all-gather, merge of the ranks' messages
+            combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li], programmatic=pd,
+                    o32_out=ex.msg_o, lse_out=ex.msg_lse)
+            ex.all_gather()
+            combine_ranks(ex.gathered, self.B, self.n_q, out=self._g_out[li])
 
     def _replay_layer(self, li: int, q, k_new, v_new) -> torch.Tensor:
         self._ensure_storage()
@@ -349,6 +361,8 @@ class BlockGTQKVManager:
 
     def increment_seq_len(self, by: int = 1):
         """Call after all layers processed the new token(s) (packed_kv_manager.py:350-352)."""
+        if self._exchange is not None and not self._exchange.is_owner:
+            return                                # appended tokens live on the owner rank
         self._seq_len += by
         if self._pos is not None and not self._pos_dirty:
             self._pos.add_(by)

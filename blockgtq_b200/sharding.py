@@ -20,7 +20,7 @@ import torch.distributed as dist
 HD = 128
 
 __all__ = ["block_partition", "chunk_bounds", "owner_of_append", "pack_partial", "gather_partials",
-           "sharded_attend"]
+           "sharded_attend", "SequenceShard"]
 
 
 def block_partition(n_items: int, world: int, rank: int):
@@ -81,3 +81,36 @@ def sharded_attend(mgr, layer_idx: int, q: torch.Tensor, group=None, *, n_splits
     part_o, part_lse = gather_partials(o32, lse, group)
     out, _, _ = combine(part_o, part_lse, mgr.n_kv)
     return out
+
+
+class SequenceShard:
+    """Attach sequence sharding to a :class:`BlockGTQKVManager` that holds this rank's chunk of one
+    long sequence, so that ``mgr.append_and_attend`` returns the attention over ALL ranks' tokens.
+
+    Per layer the manager then runs, inside its replayed CUDA graph: query rotation (+ the append on
+    the rank that owns the tail), split-KV decode over the local chunk, a combine that writes the
+    local ``[O fp32 | LSE]`` message in place, ONE all-gather of the messages, and the merge of the
+    gathered messages (``bgtq_combine_ranks``).  Every rank must call ``append_and_attend`` for every
+    layer with the same query; only the owner's ``k_new`` / ``v_new`` are used.  Remote results are
+    read from the local receive buffer only."""
+
+    def __init__(self, mgr, group=None, owner: int = None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.is_owner = self.rank == (self.world - 1 if owner is None else owner)
+        rows = mgr.B * mgr.n_q
+        dev = mgr.device
+        self.msg = torch.zeros(rows * (HD + 1), dtype=torch.float32, device=dev)
+        self.msg_o = self.msg[:rows * HD].view(mgr.B, mgr.n_q, HD)
+        self.msg_lse = self.msg[rows * HD:].view(mgr.B, mgr.n_q)
+        self.gathered = torch.zeros(self.world, rows * (HD + 1), dtype=torch.float32, device=dev)
+        self.all_gather()                      # communicator set-up outside any graph capture
+        torch.cuda.synchronize(dev) if dev.type == "cuda" else None
+        mgr._exchange = self
+
+    def all_gather(self):
+        if dist.get_backend(self.group) == "nccl":
+            dist.all_gather_into_tensor(self.gathered, self.msg, group=self.group)
+        else:
+            dist.all_gather(list(self.gathered.unbind(0)), self.msg, group=self.group)

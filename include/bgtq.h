@@ -253,6 +253,18 @@ int bgtq_combine(const float* part_o, const float* part_lse, int32_t n_splits,
                  void* out, int64_t o_sb, int64_t o_sh,
                  float* out_f32, float* lse_out, int32_t flags, void* stream);
 
+/* Final merge of per-rank results after an all-gather (sequence-sharded cache: every rank ran
+ * bgtq_decode + bgtq_combine over its own token chunk with out_f32 / lse_out pointing into one message
+ * [O (n_batch, n_q, 128) fp32 | LSE (n_batch, n_q) fp32]; the messages of all ranks were gathered into
+ * `gathered`, rank r's message starting at gathered + r * rank_stride floats).  The reference is
+ * single-GPU; the merge itself is _split_t_merge_kernel (blockgtq/kernels/fused_packed_attention.py:59-103)
+ * applied across ranks.  The partials are already in V's original basis, so no rotation is applied.
+ * Ranks with LSE = -inf (no tokens) are skipped.  out: fp16 (n_batch, n_q, 128) at out + b*o_sb + hq*o_sh.
+ * Only local memory is read: pass the all-gather's receive buffer, never a peer pointer. */
+int bgtq_combine_ranks(const float* gathered, int32_t n_ranks, int64_t rank_stride,
+                       int32_t n_batch, int32_t n_q, void* out, int64_t o_sb, int64_t o_sh,
+                       int32_t flags, void* stream);
+
 /* bgtq_decode followed by bgtq_combine with NO caller-provided scratch: the
  * split partials go to a fixed array inside the library instead of part_o /
  * part_lse.  This entry point has no counterpart in the reference.

@@ -370,3 +370,47 @@ def test_encoder_tensor_core_and_fp32_paths_vs_oracle(case, mixed):
     # the two paths agree with each other except on bin edges (already bounded above), norms to fp32 noise
     np.testing.assert_allclose(outs[0][1], outs[1][1], rtol=1e-5, atol=1e-30)
     assert (outs[0][4] != outs[1][4]).mean() < 2e-3
+
+
+def test_combine_ranks_matches_single_range():
+    """Sequence sharding on one GPU: two token chunks decoded and combined separately, their
+    [O | LSE] messages laid out like an all-gather receive buffer and merged by bgtq_combine_ranks,
+    against one decode over the whole range.  A third, empty "rank" (LSE = -inf) must be ignored."""
+    from blockgtq_b200.layer import combine, combine_ranks, decode, encode, rotate_q
+    case = "a3_1to8"
+    lt, tabs = _layer(case)
+    gen = torch.Generator().manual_seed(77)
+    B, n_kv, gqa, T = 2, 2, 4, 1000
+    n_q = n_kv * gqa
+    ks, qs_ = [], []
+    for b in range(B):
+        hk, hq = [], []
+        for h in range(n_kv):
+            q, k = synth_head(gen, T + 1, gqa)
+            hk.append(k[:T])
+            hq.append(q.reshape(gqa, T + 1, HD)[:, T])
+        ks.append(torch.stack(hk))
+        qs_.append(torch.cat(hq))
+    k = torch.stack(ks).to(DEV)
+    q = torch.stack(qs_).to(DEV)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half().to(DEV)
+    kp = torch.zeros(B, n_kv, T + 8, lt.max_tpb, dtype=torch.uint8, device=DEV)
+    kn = torch.zeros(B, n_kv, T + 8, lt.max_ng, dtype=torch.float16, device=DEV)
+    vp = torch.zeros(B, n_kv, T + 8, lt.vpb, dtype=torch.uint8, device=DEV)
+    vn = torch.zeros(B, n_kv, T + 8, dtype=torch.float16, device=DEV)
+    encode(lt, k, v, 0, kp, kn, vp, vn)
+    q_rot = rotate_q(lt, q)
+    rows = B * n_q
+    gathered = torch.zeros(3, rows * (HD + 1) + 5, dtype=torch.float32, device=DEV)[:, :rows * (HD + 1) + 5]
+    for r, (lo, hi) in enumerate([(0, 400), (400, 1000), (1000, 1000)]):
+        po, pl = decode(lt, q_rot, kp, kn, vp, vn, lo, hi, n_splits=2)
+        msg = gathered[r]
+        combine(po, pl, n_kv, v_rot=lt.v_rot, o32_out=msg[:rows * HD].view(B, n_q, HD),
+                lse_out=msg[rows * HD:rows * (HD + 1)].view(B, n_q))
+    assert torch.isneginf(gathered[2, rows * HD:rows * (HD + 1)]).all()
+    out = combine_ranks(gathered, B, n_q)
+    po, pl = decode(lt, q_rot, kp, kn, vp, vn, 0, T, n_splits=3)
+    ref, ref32, _ = combine(po, pl, n_kv, v_rot=lt.v_rot, want_f32=True)
+    torch.cuda.synchronize()
+    assert (out.float() - ref32).abs().max().item() <= 1e-3
+    assert (out.float() - ref.float()).abs().max().item() <= 2e-3
