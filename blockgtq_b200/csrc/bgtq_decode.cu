@@ -615,18 +615,25 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_default_splits
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long pairs = (long)n_batch * n_kv > 0 ? (long)n_batch * n_kv : 1;
-    const long tiles = (n_tokens + kTileTok - 1) / kTileTok;
-    if (tiles <= 1) return 1;
+    if (n_tokens <= kTileTok) return 1;
     const long slots = 2L * sms;
-    long best = 1, best_span = -1;
-    for (long ns = 1; ns <= tiles && ns <= 512; ++ns) {
-        const long per = (tiles + ns - 1) / ns;                  // tiles per CTA
-        const long used = (tiles + per - 1) / per;               // non-empty splits
+    const long max_ns = (n_tokens + kWarpTok - 1) / kWarpTok;
+    long best = 1;
+    double best_span = -1.0;
+    for (long ns = 1; ns <= max_ns && ns <= 512; ++ns) {
+        long per = (n_tokens + ns - 1) / ns;                     // tokens per CTA, in warp units
+        per = ((per + kWarpTok - 1) / kWarpTok) * kWarpTok;
+        const long used = (n_tokens + per - 1) / per;            // non-empty splits
         const long ctas = pairs * used;
         const long waves = (ctas + slots - 1) / slots;
+        // full tiles cost 16 units; a partial last tile costs in proportion to its busy warps but not
+        // less than a third of a tile; fixed set-up / first-load / merge cost per CTA: 24 units
+        const long full = per / kTileTok, rem = per % kTileTok;
+        const double tail = rem ? (16.0 * rem / kTileTok > 5.5 ? 16.0 * rem / kTileTok : 5.5) : 0.0;
+        double span = waves * (full * 16.0 + tail + 24.0);
         // single-CTA SMs run their CTA faster; charge a half-occupied machine a little more per tile
-        const long span = waves * (per * 16 + 24) + (ctas < slots ? (slots - ctas) * per * 4 / slots : 0);
-        if (best_span < 0 || span < best_span) { best_span = span; best = used; }
+        if (ctas < slots) span += (double)(slots - ctas) * (full * 16.0 + tail) / 4.0 / slots;
+        if (best_span < 0 || span < best_span - 1e-9) { best_span = span; best = used; }
     }
     return (int)best;
 }
@@ -665,9 +672,12 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode(
     P.n_q = n_q; P.n_kv = n_kv; P.gqa = gqa;
     P.t_begin = t_begin; P.t_end = t_end; P.n_splits = n_splits;
     const int n_tok = t_end - t_begin;
+    // Splits are equal runs of tokens rounded up to a warp's 32 tokens, not to the 256-token tile: the
+    // last tile of a CTA may be partial (warps without tokens skip it), which lets the split count fill
+    // the resident CTA slots exactly instead of jumping between whole-tile multiples.
     int chunk = (n_tok + n_splits - 1) / n_splits;
-    chunk = ((chunk + kTileTok - 1) / kTileTok) * kTileTok;
-    P.chunk = chunk < kTileTok ? kTileTok : chunk;
+    chunk = ((chunk + kWarpTok - 1) / kWarpTok) * kWarpTok;
+    P.chunk = chunk < kWarpTok ? kWarpTok : chunk;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.part_o = part_o; P.part_lse = part_lse; P.status = status;
     P.pos_dev = pos_dev; P.pos_add = pos_add;

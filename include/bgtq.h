@@ -194,7 +194,7 @@ int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv, int32_t n_tokens);
  * (+ segment index), v_packed / v_norms likewise (v_norms: one fp16 per token).
  * Rows need no particular alignment.
  * Outputs, for split c of n_splits (tokens are cut into n_splits equal runs
- * rounded up to the 128-token tile):
+ * rounded up to 32 tokens):
  *   part_o  (n_batch, n_q, n_splits, 128) fp32  softmax-normalised partial
  *           output, still in V's rotated basis (16-byte aligned)
  *   part_lse(n_batch, n_q, n_splits)      fp32  log-sum-exp of the scaled
