@@ -15,10 +15,6 @@
 #include "bgtq_common.cuh"
 #include "bgtq_encode_params.cuh"
 
-#ifndef BGTQ_TC_ABL
-#define BGTQ_TC_ABL 0
-#endif
-
 namespace bgtq {
 namespace {
 
@@ -186,7 +182,7 @@ __device__ __forceinline__ void tc_role(TcSmem& S, const EncParams& P, const int
             for (int q = 0; q < 8; ++q) {
                 const int row = 2 * q + (lane >> 4);
                 __half* xr = reinterpret_cast<__half*>(slab) + row * kLd;
-                if (is_v || (BGTQ_TC_ABL & 16)) {
+                if (is_v) {
                     *reinterpret_cast<uint4*>(xr + (lane & 15) * 8) = v[q];
                 } else {
                     const __half* e = reinterpret_cast<const __half*>(&v[q]);
@@ -200,7 +196,7 @@ __device__ __forceinline__ void tc_role(TcSmem& S, const EncParams& P, const int
         {
             const int row = lane & 15, par = lane >> 4;
             const __half2* xr = reinterpret_cast<const __half2*>(slab) + row * (kLd / 2);
-            for (int s = 0; s < ((BGTQ_TC_ABL & 4) ? 0 : n_seg); ++s) {
+            for (int s = 0; s < n_seg; ++s) {
                 const int st = is_v ? 0 : S.seg_start[s] >> 1, en = is_v ? kHD / 2 : st + (S.seg_len[s] >> 1);
                 float acc = 0.f;
                 int p2 = st + par;
@@ -241,7 +237,7 @@ __device__ __forceinline__ void tc_role(TcSmem& S, const EncParams& P, const int
             const uint32_t boff = 2u * ((np * 16 + (lane & 7) + (lane >> 4) * 8) * kLd + ((lane >> 3) & 1) * 8);
 #pragma unroll
             for (int kt = 0; kt < 8; ++kt) {
-                if (!(BGTQ_TC_ABL & 8) && (is_v || (kmask >> kt & 1u))) {
+                if (is_v || (kmask >> kt & 1u)) {
                     uint32_t bl[4], bh[4];
                     ldmatrix_x4(bl, wlo_base + boff + 32u * kt);
                     ldmatrix_x4(bh, whi_base + boff + 32u * kt);
@@ -264,10 +260,7 @@ __device__ __forceinline__ void tc_role(TcSmem& S, const EncParams& P, const int
                 const float* ac = half ? acc1 : acc0;
                 const int col = np * 16 + half * 8 + 2 * j;
                 uint32_t cA, cB;      // two codes of row r / row r+8
-                if (BGTQ_TC_ABL & 2) {
-                    cA = __float_as_uint(ac[0] + ac[1]) & 0x0101u;
-                    cB = __float_as_uint(ac[2] + ac[3]) & 0x0101u;
-                } else if (!is_v) {
+                if (!is_v) {
                     const float4 cp = S.colp[col >> 1];
                     const int g = __float_as_int(cp.z);
                     const uint8_t* lut = &S.code_lut[0][0] + __float_as_int(cp.w);
@@ -356,7 +349,7 @@ __device__ __forceinline__ void tc_role(TcSmem& S, const EncParams& P, const int
         }
         // ---- pack: one task = up to 8 codes of one width ----
         // lane -> row (lane & 15); the two half-warps take alternate tasks, so a warp runs at most two widths at a time
-        for (int ti = lane >> 4; ti < ((BGTQ_TC_ABL & 1) ? 0 : n_tasks); ti += 2) {
+        for (int ti = lane >> 4; ti < n_tasks; ti += 2) {
             const int row = lane & 15;
             const uint32_t tk = S.tasks[ti];
             const int first = tk & 0xFF, n = (tk >> 8) & 0xF, bw = (tk >> 12) & 0xF, out = tk >> 16;

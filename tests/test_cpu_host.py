@@ -101,6 +101,10 @@ def test_entry_points_reject_bad_arguments_without_a_gpu():
     assert L.bgtq_decode(None, None, None, None, 0, 0, 0, None, 0, 0, 0, None, 0, 0, 0, None, 0, 0, 0,
                          1, 8, 2, 0, 10, 1, 0.1, None, None, None, None, 0, None) == -1
     assert L.bgtq_combine(None, None, 1, None, None, None, 1, 8, 2, None, 0, 0, None, None, 0, None) == -1
+    assert L.bgtq_combine_ranks(None, 2, 8 * 129, 1, 8, None, 0, 0, 0, None) == -1
+    import ctypes as C
+    dummy = (C.c_float * 4)()           # never dereferenced: the stride check fails first
+    assert L.bgtq_combine_ranks(C.addressof(dummy), 2, 8 * 128, 1, 8, C.addressof(dummy), 0, 0, 0, None) == -1
     assert L.bgtq_encode(None, None, None, None, 0, 0, 0, None, 0, 0, 0, 1, 2, 1, 0, None, 0, 0, 0, 8,
                          None, 0, 0, 0, 1, None, 0, 0, 0, None, 0, 0, 0, None, None, 0, None, None) == -1
 
