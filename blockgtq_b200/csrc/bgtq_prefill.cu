@@ -1,0 +1,386 @@
+// Packed-cache prefill attention: many query positions per KV head against the quantised cache, causal.
+//
+// One CTA owns 128 query rows of one (batch, KV head): 128 / gqa consecutive positions x the gqa query
+// heads of the group (row = position * gqa + head), one m16 MMA tile per warp.  Cache tokens are walked
+// in tiles of 64: the packed rows are copied to shared memory, dequantised ONCE per tile into fp16 K and V
+// tiles (the cost the decode kernel pays per 8 query rows is shared by 128 here), then
+//   S = Q . Khat^T   per width segment, scaled by that segment's per-token norm in fp32,
+//   online softmax in the log2 domain (causal limit per row), P rounded to fp16,
+//   O += P . Vhat    with vhat = fp16(centroid * norm)
+// on mma.sync m16n8k16.  Rounding points are those of the decode kernel (bgtq_decode.cu).  The result is
+// written as fp32 in V's rotated basis; the caller applies V's rotation as one plain GEMM.
+#include "bgtq_common.cuh"
+
+namespace bgtq {
+namespace {
+
+constexpr int kPfTok = 64;        // cache tokens per tile
+constexpr int kPfRows = 128;      // query rows per CTA
+constexpr int kPfWarps = 8;
+constexpr int kPfLd = 136;        // halfs per row of the dequantised tiles (conflict-free ldmatrix)
+constexpr int kPfMaxTasks = 32;
+
+struct PfParams {
+    const BgtqHeadDesc* desc;
+    const __half* q;
+    int64_t q_sb, q_sh, q_ss;
+    const uint8_t *kp, *kn, *vp, *vn;
+    int64_t kp_sb, kp_sh, kn_sb, kn_sh, vp_sb, vp_sh, vn_sb, vn_sh;
+    int32_t kp_st, kn_st, vp_st, vn_st;      // bytes between token rows
+    int32_t n_q, n_kv, gqa, s_q, n_tok, q_pos_offset, causal, flags;
+    float scale_log2;
+    float* out;
+};
+
+struct PfSmem {
+    __half kh[kPfTok * kPfLd];
+    __half vh[kPfTok * kPfLd];
+    float kn_f[BGTQ_MAX_SEGMENTS][kPfTok];          // per-token segment norms (1 where folded into kh)
+    __align__(16) uint8_t raw_k[kPfTok * 160 + 16];
+    __align__(16) uint8_t raw_kn[kPfTok * 32 + 16];
+    __align__(16) uint8_t raw_v[kPfTok * 128 + 16];
+    __align__(16) uint8_t raw_vn[kPfTok * 16 + 16];
+    uint16_t cb[528];                               // 512 K entries + 16 V entries (fp16 bits)
+    uint2 ktask[kPfMaxTasks];   // x: first code | count << 8 | stored bits << 12 | segment << 16 | fold-norm << 20
+    uint2 vtask[16];            // y: byte offset | codebook offset << 16
+    int32_t n_ktask, n_vtask, n_seg;
+    int32_t seg_start[BGTQ_MAX_SEGMENTS], seg_len[BGTQ_MAX_SEGMENTS];
+};
+
+__device__ __forceinline__ void pf_ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void pf_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// Copy n_bytes starting at src (any alignment) into dst so that dst[(src & 3) + i] = src[i].
+__device__ __forceinline__ void pf_stage(uint8_t* dst, const uint8_t* src, int n_bytes, int tid) {
+    const uint32_t ph = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 3u);
+    const uint32_t* s4 = reinterpret_cast<const uint32_t*>(src - ph);
+    uint32_t* d4 = reinterpret_cast<uint32_t*>(dst);
+    const int n_words = (int)((ph + n_bytes) >> 2);           // whole words; the ragged tail goes byte by byte
+    for (int i = tid; i < n_words; i += kPfWarps * 32) d4[i] = __ldg(s4 + i);
+    const int tail = (int)((ph + n_bytes) & 3u);
+    if (tid < tail) dst[4 * n_words + tid] = __ldg(src - ph + 4 * n_words + tid);
+}
+
+// Tables of one head: dequantisation tasks of 8 consecutive codes of one width.
+__device__ void pf_setup(PfSmem& S, const PfParams& P, const BgtqHeadDesc& d) {
+    const int tid = threadIdx.x;
+    for (int i = tid; i < 528; i += kPfWarps * 32) S.cb[i] = i < 512 ? d.codebook[i] : d.v_lut[i - 512];
+    if (tid < BGTQ_MAX_SEGMENTS) {
+        S.seg_start[tid] = d.seg_start[tid];
+        S.seg_len[tid] = d.seg_len[tid];
+    }
+    if (tid == 0) {
+        const bool mixed = P.flags & BGTQ_DEC_K_MIXED;
+        int nt = 0;
+        for (int s = 0; s < d.n_seg; ++s) {
+            const int bw = d.seg_bw[s], st = d.seg_start[s], len = d.seg_len[s];
+            const int sb = mixed ? (bw <= 4 ? 4 : 8) : (bw <= 4 ? bw : 8);
+            const int base = mixed ? (bw <= 4 ? st / 2 : d.nopack_start / 2 + (st - d.nopack_start)) : d.seg_pack_off[s];
+            const int fold = (mixed && len >= 16 && s < 5) ? 1 : 0;     // nibble-layout numerics, as in the decode plan
+            for (int c = 0; c < len; c += 8) {
+                const int n = len - c < 8 ? len - c : 8;
+                S.ktask[nt] = make_uint2((uint32_t)(st + c) | (uint32_t)n << 8 | (uint32_t)sb << 12 | (uint32_t)s << 16 |
+                                             (uint32_t)fold << 20,
+                                         (uint32_t)(base + (c * sb) / 8) | (uint32_t)d.seg_lut_off[s] << 16);
+                ++nt;
+            }
+        }
+        S.n_ktask = nt;
+        const int vsb = (P.flags & BGTQ_DEC_V_NIBBLE) ? 4 : d.v_bits;
+        for (int c = 0; c < kHD; c += 8)
+            S.vtask[c / 8] = make_uint2((uint32_t)c | 8u << 8 | (uint32_t)vsb << 12, (uint32_t)((c * vsb) / 8) | 512u << 16);
+        S.n_vtask = kHD / 8;
+        S.n_seg = d.n_seg;
+    }
+}
+
+// Up to 8 codes of `sb` bits starting at byte p -> fp16 values (optionally times an fp16 norm) at dst.
+__device__ __forceinline__ void pf_dequant8(const uint8_t* p, int n, int sb, const uint16_t* cb, bool fold, __half nrm,
+                                            __half* dst) {
+    const int nbytes = (n * sb + 7) >> 3;
+    uint64_t w = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (i < nbytes) w |= (uint64_t)p[i] << (8 * i);
+    const uint32_t m = (1u << sb) - 1u;
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        if (i < n) {
+            __half a = __ushort_as_half(cb[(uint32_t)(w >> (i * sb)) & m]);
+            __half b = __ushort_as_half(cb[(uint32_t)(w >> ((i + 1) * sb)) & m]);
+            if (fold) {
+                a = __hmul(a, nrm);
+                b = __hmul(b, nrm);
+            }
+            *reinterpret_cast<__half2*>(dst + i) = __halves2half2(a, b);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParams P) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    PfSmem& S = *reinterpret_cast<PfSmem*>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = lane >> 2, j = lane & 3;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int bq = kPfRows / P.gqa;                  // query positions per CTA
+    const int q0 = blockIdx.x * bq;
+    const BgtqHeadDesc& d = P.desc[h];
+
+    pf_setup(S, P, d);
+
+    // this thread's two query rows (A-fragment rows r and r + 8 of the warp's tile)
+    int qi[2], hq[2];
+    bool rok[2];
+    uint32_t qa[8][4];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int row = warp * 16 + r + 8 * e;
+        qi[e] = row / P.gqa;
+        hq[e] = h * P.gqa + row % P.gqa;
+        rok[e] = row < bq * P.gqa && q0 + qi[e] < P.s_q;
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(P.q + b * P.q_sb + hq[e] * P.q_sh + (int64_t)(q0 + qi[e]) * P.q_ss);
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) {
+            qa[kt][e] = rok[e] ? __ldg(src + kt * 8 + j) : 0u;            // dims 16 kt + 2j, +1
+            qa[kt][2 + e] = rok[e] ? __ldg(src + kt * 8 + 4 + j) : 0u;    // dims 16 kt + 8 + 2j, +1
+        }
+    }
+    // causal limit (exclusive cache token index) per row, and for the whole CTA
+    int lim[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+        lim[e] = !rok[e] ? 0 : (P.causal ? min(P.n_tok, P.q_pos_offset + q0 + qi[e] + 1) : P.n_tok);
+    const int last_q = min(q0 + bq, P.s_q) - 1;
+    const int t_max = P.causal ? min(P.n_tok, P.q_pos_offset + last_q + 1) : P.n_tok;
+
+    float O[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
+    float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+
+    const size_t bh_kp = (size_t)b * P.kp_sb + (size_t)h * P.kp_sh, bh_kn = (size_t)b * P.kn_sb + (size_t)h * P.kn_sh;
+    const size_t bh_vp = (size_t)b * P.vp_sb + (size_t)h * P.vp_sh, bh_vn = (size_t)b * P.vn_sb + (size_t)h * P.vn_sh;
+    const uint32_t kh_u32 = smem_u32(S.kh), vh_u32 = smem_u32(S.vh);
+    __syncthreads();
+    const int n_seg = S.n_seg, n_ktask = S.n_ktask, n_vtask = S.n_vtask;
+
+    for (int t0 = 0; t0 < t_max; t0 += kPfTok) {
+        const int nt = min(kPfTok, t_max - t0);
+        // ---- 1. packed rows of the tile -> shared memory ----
+        const uint8_t* gk = P.kp + bh_kp + (size_t)t0 * P.kp_st;
+        const uint8_t* gn = P.kn + bh_kn + (size_t)t0 * P.kn_st;
+        const uint8_t* gv = P.vp + bh_vp + (size_t)t0 * P.vp_st;
+        const uint8_t* gw = P.vn + bh_vn + (size_t)t0 * P.vn_st;
+        pf_stage(S.raw_k, gk, nt * P.kp_st, tid);
+        pf_stage(S.raw_kn, gn, nt * P.kn_st, tid);
+        pf_stage(S.raw_v, gv, nt * P.vp_st, tid);
+        pf_stage(S.raw_vn, gw, nt * P.vn_st, tid);
+        __syncthreads();
+        const uint8_t* rk = S.raw_k + (reinterpret_cast<uintptr_t>(gk) & 3u);
+        const uint8_t* rn = S.raw_kn + (reinterpret_cast<uintptr_t>(gn) & 3u);
+        const uint8_t* rv = S.raw_v + (reinterpret_cast<uintptr_t>(gv) & 3u);
+        const uint8_t* rw = S.raw_vn + (reinterpret_cast<uintptr_t>(gw) & 3u);
+        // ---- 2. dequantise: task index = (task << 6) | token, so a warp works on one width at a time ----
+        for (int i = tid; i < kPfTok * n_ktask; i += kPfWarps * 32) {
+            const int tok = i & (kPfTok - 1);
+            const uint2 tk = S.ktask[i >> 6];
+            const int first = tk.x & 0xFF, n = (tk.x >> 8) & 0xF, sb = (tk.x >> 12) & 0xF, sg = (tk.x >> 16) & 0xF;
+            const bool fold = (tk.x >> 20) & 1u;
+            __half* dst = S.kh + tok * kPfLd + first;
+            if (tok < nt) {
+                const __half nrm = __ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + tok * P.kn_st + 2 * sg));
+                pf_dequant8(rk + tok * P.kp_st + (tk.y & 0xFFFFu), n, sb, S.cb + (tk.y >> 16), fold, nrm, dst);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 8; c += 2)
+                    if (c < n) *reinterpret_cast<uint32_t*>(dst + c) = 0u;
+            }
+        }
+        for (int i = tid; i < kPfTok * n_vtask; i += kPfWarps * 32) {
+            const int tok = i & (kPfTok - 1);
+            const uint2 tk = S.vtask[i >> 6];
+            const int first = tk.x & 0xFF, sb = (tk.x >> 12) & 0xF;
+            __half* dst = S.vh + tok * kPfLd + first;
+            if (tok < nt) {
+                const __half nrm = __ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + tok * P.vn_st));
+                pf_dequant8(rv + tok * P.vp_st + (tk.y & 0xFFFFu), 8, sb, S.cb + 512, true, nrm, dst);
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        for (int i = tid; i < kPfTok * n_seg; i += kPfWarps * 32) {
+            const int tok = i & (kPfTok - 1), sg = i >> 6;
+            const bool fold = (P.flags & BGTQ_DEC_K_MIXED) && S.seg_len[sg] >= 16 && sg < 5;
+            float v = 0.f;
+            if (tok < nt)
+                v = fold ? 1.0f : __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + tok * P.kn_st + 2 * sg)));
+            S.kn_f[sg][tok] = v;
+        }
+        __syncthreads();
+        // ---- 3. S = Q . Khat^T per segment, scaled by the per-token segment norm ----
+        float Sv[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) Sv[i][0] = Sv[i][1] = Sv[i][2] = Sv[i][3] = 0.f;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {            // 32 tokens at a time (four n-tiles) to bound registers
+            for (int sg = 0; sg < n_seg; ++sg) {
+                const int st = S.seg_start[sg], en = st + S.seg_len[sg];
+                float acc[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll
+                for (int kt = 0; kt < 8; ++kt) {
+                    if (kt * 16 + 16 <= st || kt * 16 >= en) continue;      // k-tile outside the segment
+                    uint32_t a[4] = {qa[kt][0], qa[kt][1], qa[kt][2], qa[kt][3]};
+                    if (kt * 16 < st || kt * 16 + 16 > en) {                // straddles: keep this segment's dims only
+                        const int dlo = kt * 16 + 2 * j, dhi = dlo + 8;
+                        if (dlo < st || dlo >= en) a[0] = a[1] = 0u;
+                        if (dhi < st || dhi >= en) a[2] = a[3] = 0u;
+                    }
+#pragma unroll
+                    for (int np = 0; np < 2; ++np) {     // two n-tiles (16 tokens) per ldmatrix.x4
+                        uint32_t bm[4];
+                        const int tok = hf * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8;
+                        pf_ldmatrix_x4(bm, kh_u32 + 2u * (tok * kPfLd + kt * 16 + ((lane >> 3) & 1) * 8));
+                        const uint32_t b0[2] = {bm[0], bm[1]}, b1[2] = {bm[2], bm[3]};
+                        mma_16816(acc[2 * np], a, b0);
+                        mma_16816(acc[2 * np + 1], a, b1);
+                    }
+                }
+#pragma unroll
+                for (int nt4 = 0; nt4 < 4; ++nt4) {
+                    const float n0 = S.kn_f[sg][hf * 32 + nt4 * 8 + 2 * j], n1 = S.kn_f[sg][hf * 32 + nt4 * 8 + 2 * j + 1];
+                    Sv[hf * 4 + nt4][0] = fmaf(n0, acc[nt4][0], Sv[hf * 4 + nt4][0]);
+                    Sv[hf * 4 + nt4][1] = fmaf(n1, acc[nt4][1], Sv[hf * 4 + nt4][1]);
+                    Sv[hf * 4 + nt4][2] = fmaf(n0, acc[nt4][2], Sv[hf * 4 + nt4][2]);
+                    Sv[hf * 4 + nt4][3] = fmaf(n1, acc[nt4][3], Sv[hf * 4 + nt4][3]);
+                }
+            }
+        }
+        // ---- 4. online softmax (log2 domain); rows r (e = 0) and r + 8 (e = 1) ----
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int e = c >> 1, tok = t0 + i * 8 + 2 * j + (c & 1);
+                Sv[i][c] = tok < lim[e] ? Sv[i][c] * P.scale_log2 : -INFINITY;
+                mx[e] = fmaxf(mx[e], Sv[i][c]);
+            }
+        }
+        float al[2], z[2], ps[2] = {0.f, 0.f};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 1));
+            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 2));
+            const float nm = fmaxf(mrow[e], mx[e]);
+            z[e] = nm == -INFINITY ? 0.f : nm;
+            al[e] = exp2f(mrow[e] - z[e]);
+            mrow[e] = nm;
+        }
+        uint32_t pa[4][4];     // P as A fragments of the four 16-token k-tiles
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float p0 = exp2f(Sv[i][0] - z[0]), p1 = exp2f(Sv[i][1] - z[0]);
+            const float p2 = exp2f(Sv[i][2] - z[1]), p3 = exp2f(Sv[i][3] - z[1]);
+            ps[0] += p0 + p1;
+            ps[1] += p2 + p3;
+            pa[i >> 1][(i & 1) * 2] = pack_half2(p0, p1);
+            pa[i >> 1][(i & 1) * 2 + 1] = pack_half2(p2, p3);
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) lrow[e] = fmaf(lrow[e], al[e], ps[e]);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            O[i][0] *= al[0];
+            O[i][1] *= al[0];
+            O[i][2] *= al[1];
+            O[i][3] *= al[1];
+        }
+        // ---- 5. O += P . Vhat ----
+#pragma unroll
+        for (int kt = 0; kt < 4; ++kt) {
+#pragma unroll
+            for (int nd = 0; nd < 8; ++nd) {         // two n-tiles (16 dims) per ldmatrix.x4.trans
+                uint32_t bm[4];
+                const int tok = kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                pf_ldmatrix_x4_trans(bm, vh_u32 + 2u * (tok * kPfLd + nd * 16 + (lane >> 4) * 8));
+                const uint32_t b0[2] = {bm[0], bm[1]}, b1[2] = {bm[2], bm[3]};
+                mma_16816(O[2 * nd], pa[kt], b0);
+                mma_16816(O[2 * nd + 1], pa[kt], b1);
+            }
+        }
+        __syncthreads();       // the tiles are rebuilt next
+    }
+
+    // ---- normalise and write (fp32, V's rotated basis) ----
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        lrow[e] += __shfl_xor_sync(0xffffffffu, lrow[e], 1);
+        lrow[e] += __shfl_xor_sync(0xffffffffu, lrow[e], 2);
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        if (!rok[e]) continue;
+        const float inv = lrow[e] > 0.f ? 1.0f / lrow[e] : 0.f;
+        float* dst = P.out + (((size_t)b * P.n_q + hq[e]) * P.s_q + (q0 + qi[e])) * kHD;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            *reinterpret_cast<float2*>(dst + i * 8 + 2 * j) = make_float2(O[i][2 * e] * inv, O[i][2 * e + 1] * inv);
+    }
+}
+
+}  // namespace
+}  // namespace bgtq
+
+using namespace bgtq;
+
+extern "C" __attribute__((visibility("default"))) int bgtq_prefill_attention(
+    const BgtqHeadDesc* desc, const void* q_rot, int64_t q_sb, int64_t q_sh, int64_t q_ss, const uint8_t* k_packed,
+    int64_t kp_sb, int64_t kp_sh, int64_t kp_st, const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
+    const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, const void* v_norms, int64_t vn_sb,
+    int64_t vn_sh, int64_t vn_st, int32_t n_batch, int32_t n_q, int32_t n_kv, int32_t s_q, int32_t n_tokens,
+    int32_t q_pos_offset, int32_t causal, float scale, int32_t flags, float* out_rot, void* stream) {
+    if (!desc || !q_rot || !k_packed || !k_norms || !v_packed || !v_norms || !out_rot) return BGTQ_E_BADARG;
+    if (n_batch < 1 || n_kv < 1 || n_q < n_kv || n_q % n_kv || s_q < 1 || n_tokens < 0 || q_pos_offset < 0)
+        return BGTQ_E_BADARG;
+    const int gqa = n_q / n_kv;
+    if (gqa > 16) return BGTQ_E_UNSUPPORTED;
+    if (kp_st < 1 || kp_st > 160 || vp_st < 1 || vp_st > 128 || kn_st < 1 || kn_st > 16 || vn_st < 1 || vn_st > 8)
+        return BGTQ_E_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(q_rot) & 3u) || (q_sb & 1) || (q_sh & 1) || (q_ss & 1) ||
+        (reinterpret_cast<uintptr_t>(out_rot) & 7u) || (reinterpret_cast<uintptr_t>(k_norms) & 1u) ||
+        (reinterpret_cast<uintptr_t>(v_norms) & 1u))
+        return BGTQ_E_ALIGN;
+    const int bq = kPfRows / gqa;
+    const int64_t q_blocks = ((int64_t)s_q + bq - 1) / bq;
+    if (q_blocks > 0x7FFFFFFF || n_kv > 65535 || n_batch > 65535) return BGTQ_E_TOOBIG;
+    PfParams P;
+    P.desc = desc;
+    P.q = static_cast<const __half*>(q_rot);
+    P.q_sb = q_sb; P.q_sh = q_sh; P.q_ss = q_ss;
+    P.kp = k_packed; P.kn = static_cast<const uint8_t*>(k_norms);
+    P.vp = v_packed; P.vn = static_cast<const uint8_t*>(v_norms);
+    P.kp_sb = kp_sb; P.kp_sh = kp_sh; P.kp_st = (int32_t)kp_st;
+    P.kn_sb = 2 * kn_sb; P.kn_sh = 2 * kn_sh; P.kn_st = (int32_t)(2 * kn_st);
+    P.vp_sb = vp_sb; P.vp_sh = vp_sh; P.vp_st = (int32_t)vp_st;
+    P.vn_sb = 2 * vn_sb; P.vn_sh = 2 * vn_sh; P.vn_st = (int32_t)(2 * vn_st);
+    P.n_q = n_q; P.n_kv = n_kv; P.gqa = gqa; P.s_q = s_q; P.n_tok = n_tokens;
+    P.q_pos_offset = q_pos_offset; P.causal = causal ? 1 : 0; P.flags = flags;
+    P.scale_log2 = scale * 1.4426950408889634f;
+    P.out = out_rot;
+    const int smem = (int)sizeof(PfSmem);
+    if (cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return BGTQ_E_LAUNCH;
+    }
+    prefill_kernel<<<dim3((unsigned)q_blocks, n_kv, n_batch), kPfWarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(P);
+    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+}

@@ -74,6 +74,7 @@ class LayerTables:
         self.max_tpb = max(t.total_packed_bytes for t in k_tables)
         self.max_ng = max(t.n_groups for t in k_tables)
         self.max_mixed_bytes = max(t.pack_meta["nopack_start"] // 2 + t.pack_meta["nopack_len"] for t in k_tables)
+        self.head_perm = torch.stack([t.head_perm for t in k_tables]).long().to(self.device)   # (n_kv, 128)
         self._plans = {}
 
     def plan(self, flags: int = 0) -> _lib.DecodePlan:
@@ -161,6 +162,19 @@ def rotate_q(layer: LayerTables, q: torch.Tensor, out: torch.Tensor = None) -> t
     return out
 
 
+def rotate_q_bulk(layer: LayerTables, q: torch.Tensor) -> torch.Tensor:
+    """Many positions at once: q (B, n_q, S, 128) fp16 -> same shape in the packed-K basis, as one
+    gather + fp32 GEMM per KV head group (the per-row kernel behind :func:`rotate_q` is meant for the
+    handful of rows of a decode step)."""
+    _lib.require_cuda(q, "q")
+    B, n_q, S, D = q.shape
+    gqa = n_q // layer.n_kv
+    qg = q.reshape(B, layer.n_kv, gqa * S, D).float()
+    idx = layer.head_perm.view(1, layer.n_kv, 1, D).expand(B, layer.n_kv, gqa * S, D)
+    out = torch.matmul(torch.gather(qg, 3, idx), layer.rot_k.view(1, layer.n_kv, D, D))
+    return out.to(torch.float16).view(B, n_q, S, D)
+
+
 def step_prepare(layer: LayerTables, q, k, v, t0, k_packed, k_norms, v_packed, v_norms, *, q_rot=None,
                  flags=0, pos_dev=None):
     """Rotate q (B, n_q, [1,] 128) into ``q_rot`` and append one token k/v (B, n_kv, 1, 128) at slot
@@ -231,6 +245,36 @@ def decode(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_norms, t_be
         _lib.stream_ptr(q_rot.device)), "bgtq_decode")
     _lib.count_launch()
     return part_o, part_lse
+
+
+def prefill_attention(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_norms, n_tokens, *,
+                      q_pos_offset=0, causal=True, scale=None, flags=0, v_rot=None):
+    """Attention of q_rot (B, n_q, S_q, 128) fp16 (packed-K basis) over the first ``n_tokens`` cache rows;
+    query i has absolute position ``q_pos_offset + i`` and, when ``causal``, sees tokens up to it.
+    ``v_rot`` (n_kv, 128, 128) fp32 = R finishes V's rotation with one batched fp32 GEMM.
+    Returns (B, n_q, S_q, 128) fp16."""
+    _lib.require_cuda(q_rot, "q_rot")
+    B, n_q, S_q, D = q_rot.shape
+    if D != HD or q_rot.dtype != torch.float16 or q_rot.stride(3) != 1:
+        raise ValueError("q_rot must be float16 (B, n_q, S_q, 128) with contiguous rows")
+    if k_norms.dtype != torch.float16 or v_norms.dtype != torch.float16:
+        raise TypeError("cache norms must be float16")
+    if scale is None:
+        scale = 1.0 / math.sqrt(HD)
+    out_rot = torch.empty(B, n_q, S_q, HD, dtype=torch.float32, device=q_rot.device)
+    kps, kns, vps = _strides3(k_packed), _strides3(k_norms), _strides3(v_packed)
+    vns = (v_norms.stride(0), v_norms.stride(1), v_norms.stride(2))
+    _lib.check(_lib.lib().bgtq_prefill_attention(
+        _lib.ptr(layer.desc_dev), _lib.ptr(q_rot), q_rot.stride(0), q_rot.stride(1), q_rot.stride(2),
+        _lib.ptr(k_packed), *kps, _lib.ptr(k_norms), *kns, _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns,
+        B, n_q, layer.n_kv, S_q, int(n_tokens), int(q_pos_offset), 1 if causal else 0, float(scale), int(flags),
+        _lib.ptr(out_rot), _lib.stream_ptr(q_rot.device)), "bgtq_prefill_attention")
+    _lib.count_launch()
+    if v_rot is None:
+        return out_rot.to(torch.float16)
+    gqa = n_q // layer.n_kv
+    o = torch.matmul(out_rot.view(B, layer.n_kv, gqa * S_q, HD), v_rot.view(1, layer.n_kv, HD, HD))
+    return o.view(B, n_q, S_q, HD).to(torch.float16)
 
 
 def combine_ranks(gathered, n_batch, n_q, *, out=None):

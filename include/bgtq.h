@@ -253,6 +253,27 @@ int bgtq_combine(const float* part_o, const float* part_lse, int32_t n_splits,
                  void* out, int64_t o_sb, int64_t o_sh,
                  float* out_f32, float* lse_out, int32_t flags, void* stream);
 
+/* Prefill attention: s_q query positions per (batch, query head) against the packed cache, causal.
+ *
+ * Replaces _packed_prefill_kernel / fused_blockgtq_prefill_attention
+ * (blockgtq/kernels/fused_packed_attention.py:1875-2760) for every KV head of a layer in one launch; the
+ * caller is layer_major_prefill (blockgtq/prefill.py:25-125).
+ * Query i of (b, hq) sits at q_rot + b*q_sb + hq*q_sh + i*q_ss (fp16, 128 contiguous dims, already in the
+ * packed-K basis like bgtq_decode's q_rot) and has absolute position q_pos_offset + i; with causal != 0 it
+ * attends cache tokens t <= q_pos_offset + i, t < n_tokens, else all n_tokens.  Cache arguments and
+ * flags (BGTQ_DEC_K_MIXED, BGTQ_DEC_V_NIBBLE) are as for bgtq_decode.
+ * out_rot: (n_batch, n_q, s_q, 128) fp32 contiguous, softmax-normalised and still in V's rotated basis:
+ * multiply each KV head's rows by its R (one plain GEMM) to finish.  A query with no visible token
+ * yields zeros.  n_q / n_kv <= 16. */
+int bgtq_prefill_attention(const BgtqHeadDesc* desc, const void* q_rot, int64_t q_sb, int64_t q_sh, int64_t q_ss,
+                const uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
+                const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
+                const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
+                const void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
+                int32_t n_batch, int32_t n_q, int32_t n_kv, int32_t s_q, int32_t n_tokens,
+                int32_t q_pos_offset, int32_t causal, float scale, int32_t flags,
+                float* out_rot, void* stream);
+
 /* Final merge of per-rank results after an all-gather (sequence-sharded cache: every rank ran
  * bgtq_decode + bgtq_combine over its own token chunk with out_f32 / lse_out pointing into one message
  * [O (n_batch, n_q, 128) fp32 | LSE (n_batch, n_q) fp32]; the messages of all ranks were gathered into

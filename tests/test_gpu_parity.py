@@ -414,3 +414,55 @@ def test_combine_ranks_matches_single_range():
     torch.cuda.synchronize()
     assert (out.float() - ref32).abs().max().item() <= 1e-3
     assert (out.float() - ref.float()).abs().max().item() <= 2e-3
+
+
+@pytest.mark.parametrize("case,gqa,S_q,offset,causal", [("a3_1to8", 4, 70, 50, True), ("a2_1to8", 8, 33, 0, True),
+                                                        ("a4_rt1", 2, 40, 88, True), ("a3_1to6", 4, 20, 100, False)])
+def test_prefill_attention_vs_oracle(case, gqa, S_q, offset, causal):
+    """Causal multi-query attention over the packed cache: every query row against the float64 oracle
+    decode over exactly the tokens it may see (query i sits at position offset + i)."""
+    from blockgtq_b200.layer import encode, prefill_attention, rotate_q, rotate_q_bulk
+    lt, tabs = _layer(case)
+    gen = torch.Generator().manual_seed(11 + S_q)
+    B, n_kv = 2, 2
+    n_q = n_kv * gqa
+    T = offset + S_q
+    ks, qs_ = [], []
+    for b in range(B):
+        hk, hq = [], []
+        for h in range(n_kv):
+            q, k = synth_head(gen, T, gqa)
+            hk.append(k)
+            hq.append(q.reshape(gqa, T, HD)[:, offset:])
+        ks.append(torch.stack(hk))
+        qs_.append(torch.cat(hq))
+    k = torch.stack(ks).to(DEV)
+    q = torch.stack(qs_).to(DEV)                     # (B, n_q, S_q, 128)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half().to(DEV)
+    kp = torch.zeros(B, n_kv, T + 5, lt.max_tpb, dtype=torch.uint8, device=DEV)
+    kn = torch.zeros(B, n_kv, T + 5, lt.max_ng, dtype=torch.float16, device=DEV)
+    vp = torch.zeros(B, n_kv, T + 5, lt.vpb, dtype=torch.uint8, device=DEV)
+    vn = torch.zeros(B, n_kv, T + 5, dtype=torch.float16, device=DEV)
+    encode(lt, k, v, 0, kp, kn, vp, vn)
+    q_rot = rotate_q_bulk(lt, q)
+    # the bulk rotation equals the per-row kernel up to fp16 rounding of the result
+    one = rotate_q(lt, q[:, :, 3].contiguous())
+    assert (q_rot[:, :, 3].float() - one.float()).abs().max().item() <= 2e-3 * max(1.0, one.float().abs().max().item())
+    out = prefill_attention(lt, q_rot, kp, kn, vp, vn, T, q_pos_offset=offset, causal=causal, v_rot=lt.v_rot)
+    out_rot = prefill_attention(lt, q_rot, kp, kn, vp, vn, T, q_pos_offset=offset, causal=causal)
+    torch.cuda.synchronize()
+    assert out.shape == (B, n_q, S_q, HD) and out.dtype == torch.float16
+    worst = 0.0
+    for b in range(B):
+        for h in range(n_kv):
+            meta = oracle_meta(*tabs[h])
+            sl = slice(h * gqa, (h + 1) * gqa)
+            for i in (0, 1, S_q // 2, S_q - 2, S_q - 1):
+                lim = offset + i + 1 if causal else T
+                args = (q_rot[b, sl, i].cpu().numpy(), kp[b, h, :lim].cpu().numpy(), kn[b, h, :lim].cpu().numpy(),
+                        vp[b, h, :lim].cpu().numpy(), vn[b, h, :lim].cpu().numpy(), meta, 1 / HD ** 0.5)
+                ro_rot, _ = O.attend_packed(*args, unrotate=False)
+                ro, _ = O.attend_packed(*args)
+                worst = max(worst, np.abs(out_rot[b, sl, i].float().cpu().numpy() - ro_rot).max())
+                worst = max(worst, np.abs(out[b, sl, i].float().cpu().numpy() - ro).max())
+    assert worst <= ATOL, worst
