@@ -5,10 +5,11 @@ from .allocator import greedy_bit_allocation
 from .quantizer import (BlockGTQQuantizer, build_batched_encode_args, build_pack_meta,
                         compress_k_mixed_batched, compress_k_packed_batched,
                         compress_v_nibble4_batched, compress_v_packed_batched)
-from .attention import fused_blockgtq_decode_attention
+from .attention import fused_blockgtq_decode_attention, fused_blockgtq_prefill_attention
 from .packed_kv_manager import BlockGTQKVManager, decode_step
 from .production_cache import BlockGTQProductionCache
 from .production_decode import production_decode_step, production_prefill
+from .prefill import layer_major_prefill
 from .calibration import bake_q_rotations, build_quantizers, collect_qk_activations
 
 __all__ = [
@@ -16,5 +17,5 @@ __all__ = [
     "compress_k_packed_batched", "compress_v_packed_batched", "compress_k_mixed_batched",
     "compress_v_nibble4_batched", "fused_blockgtq_decode_attention", "BlockGTQKVManager", "decode_step",
     "BlockGTQProductionCache", "production_decode_step", "production_prefill", "collect_qk_activations",
-    "build_quantizers", "bake_q_rotations",
+    "build_quantizers", "bake_q_rotations", "fused_blockgtq_prefill_attention", "layer_major_prefill",
 ]

@@ -114,3 +114,41 @@ def fused_blockgtq_decode_attention(
     if return_lse:
         return out.unsqueeze(2), lse
     return out.unsqueeze(2)
+
+
+@torch.no_grad()
+def fused_blockgtq_prefill_attention(
+        q, k_packed, k_norms, codebook_flat, lut_offset, norm_group, segments,
+        v_codes, v_norms, v_lut, scale=None, block_q=64, block_t=64, v_skip_thresh=0.0,
+        v_norm_scale=None, v_bits=0, v_rotation=None, is_causal=True, q_pos_offset=0,
+        k_nibble=False, v_nibble=False, min_seg_for_dot=16):
+    """q (B, n_q, S_q, 128) fp16 (already rotated for packed K) x packed cache -> (B, n_q, S_q, 128) fp16
+    (blockgtq/kernels/fused_packed_attention.py:2597-2760).  Query i has position ``q_pos_offset + i``
+    and, when ``is_causal``, attends cache tokens up to and including it.  ``block_q`` / ``block_t`` /
+    ``v_skip_thresh`` / ``min_seg_for_dot`` select tile shapes and equal-valued code paths in the
+    Triton kernel and are accepted and ignored; raw V codes and int4 V norms are not supported."""
+    from .layer import prefill_attention
+    assert q.dim() == 4 and len(segments) <= 8
+    if v_nibble:
+        vb_codebook = int(round(math.log2(v_lut.numel())))
+    elif v_bits and v_bits > 0:
+        vb_codebook = int(v_bits)
+    else:
+        raise NotImplementedError("raw uint8 V codes are not supported; pack V (v_bits=1..4) or use v_nibble")
+    if v_norms.dtype != torch.float16:
+        raise NotImplementedError("int4 V norms are not supported")
+    n_kv, T = k_packed.shape[1], k_packed.shape[2]
+    if v_norms.dim() == 4:
+        v_norms = v_norms[..., 0]
+    lt = _layer_for(segments, codebook_flat, v_lut, vb_codebook, n_kv, q.device)
+    flags = (_lib.DEC_K_MIXED if k_nibble else 0) | (_lib.DEC_V_NIBBLE if v_nibble else 0)
+    rot = None
+    if v_rotation is not None:
+        rot = v_rotation.to(torch.float32).contiguous()
+        rot = rot.unsqueeze(0).expand(n_kv, -1, -1).contiguous() if rot.dim() == 2 else rot
+    q16 = q.to(torch.float16)
+    if q16.stride(3) != 1:
+        q16 = q16.contiguous()
+    return prefill_attention(lt, q16, k_packed, k_norms.to(torch.float16), v_codes, v_norms, T,
+                             q_pos_offset=int(q_pos_offset), causal=bool(is_causal), scale=scale, flags=flags,
+                             v_rot=rot)

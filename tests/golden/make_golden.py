@@ -15,6 +15,7 @@ Fixtures
   tables_<case>.npz   calibration inputs (or scores), bit map and every static table
   encode_<case>.npz   K/V rows -> packed bytes, norms, unpacked codes, nibble/mixed layouts
   decode_<case>.npz   packed cache + query -> attention output and LSE per KV head
+  prefill.npz         packed cache + 24 queries at positions 40..63 -> causal prefill attention output
   manager.npz         BlockGTQKVManager: bulk encode + two append_and_attend steps, batch 2
   production.npz      BlockGTQProductionCache (nibble/mixed layout): bulk encode + two decode steps, batch 1
 """
@@ -32,7 +33,8 @@ import torch  # noqa: E402
 from blockgtq.quantizer import (  # noqa: E402
     BlockGTQQuantizer, build_batched_encode_args, compress_k_packed_batched,
     compress_v_packed_batched, compress_k_mixed_batched, compress_v_nibble4_batched)
-from blockgtq.kernels.fused_packed_attention import fused_blockgtq_decode_attention  # noqa: E402
+from blockgtq.kernels.fused_packed_attention import (fused_blockgtq_decode_attention,  # noqa: E402
+                                                     fused_blockgtq_prefill_attention)
 from blockgtq.packed_kv_manager import BlockGTQKVManager  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -279,6 +281,53 @@ def dump_production(gen, T0=150, n_kv=2, gqa=4, steps=2):
     np.savez_compressed(os.path.join(HERE, "production.npz"), **rec)
 
 
+def dump_prefill(gen, case="a3_1to8", S_q=24, offset=40, B=2, n_kv=2, gqa=4):
+    """Causal prefill attention of S_q queries at positions offset .. offset+S_q-1 over a packed cache of
+    offset+S_q tokens, through the reference's prefill kernel, per KV head.  Self-contained fixture: its own
+    bit allocations, cache and outputs."""
+    qs, _cal = make_quantizers(case, n_kv, gen, gqa=gqa)
+    ba = build_batched_encode_args(qs, device="cpu")
+    T = offset + S_q
+    ks, qn = [], []
+    for b in range(B):
+        row_k, row_q = [], []
+        for hi in range(n_kv):
+            q, k = synth_head(gen, T, gqa)
+            row_k.append(k)
+            row_q.append(q.reshape(gqa, T, HD)[:, offset:])
+        ks.append(torch.stack(row_k))
+        qn.append(torch.cat(row_q))
+    k = torch.stack(ks)                                      # (B, n_kv, T, hd)
+    q = torch.stack(qn)                                      # (B, n_q, S_q, hd)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half()
+    k_flat = k.permute(1, 0, 2, 3).reshape(n_kv, B * T, HD).contiguous()
+    v_flat = v.permute(1, 0, 2, 3).reshape(n_kv, B * T, HD).contiguous()
+    kp, kn = compress_k_packed_batched(k_flat, ba)
+    vp, vn = compress_v_packed_batched(v_flat, ba)
+    kp = kp.reshape(n_kv, B, T, -1).permute(1, 0, 2, 3).contiguous()
+    kn = kn.reshape(n_kv, B, T, -1).permute(1, 0, 2, 3).to(torch.float16).contiguous()
+    vp = vp.reshape(n_kv, B, T, -1).permute(1, 0, 2, 3).contiguous()
+    vn = vn.reshape(n_kv, B, T).permute(1, 0, 2).contiguous()
+    outs, qrots = [], []
+    for hi in range(n_kv):
+        z = qs[hi]
+        ka = z.build_kernel_args()
+        q_h = q[:, hi * gqa:(hi + 1) * gqa]
+        q_rot = z.rotate_q_for_packed_kernel(q_h.reshape(-1, HD)).reshape(q_h.shape)
+        o = fused_blockgtq_prefill_attention(
+            q_rot, kp[:, hi:hi + 1], kn[:, hi:hi + 1], ka["codebook_flat"], ka["lut_offset"], ka["norm_group"],
+            ka["segments_b"], vp[:, hi:hi + 1], vn[:, hi:hi + 1], z.v_lut, scale=1.0 / HD ** 0.5,
+            block_q=32, block_t=64, v_bits=z.v_bits, v_rotation=z._v_rot, is_causal=True, q_pos_offset=offset)
+        outs.append(o)
+        qrots.append(q_rot)
+    rec = dict(q=q.numpy(), q_rot=torch.cat(qrots, dim=1).numpy(), k_packed=kp.numpy(), k_norms=kn.numpy(),
+               v_packed=vp.numpy(), v_norms=vn.numpy(), out=torch.cat(outs, dim=1).numpy(),
+               offset=np.array(offset), gqa=np.array(gqa), case=np.array(case))
+    for hi, z in enumerate(qs):
+        rec[f"h{hi}_alloc"] = z.bit_allocation.cpu().numpy()
+    np.savez_compressed(os.path.join(HERE, "prefill.npz"), **rec)
+
+
 def main():
     only = sys.argv[2] if len(sys.argv) > 2 else None
     gen = torch.Generator().manual_seed(20240607)
@@ -297,6 +346,9 @@ def main():
     if only in (None, "production"):
         dump_production(torch.Generator().manual_seed(778))
         print("done production")
+    if only in (None, "prefill"):
+        dump_prefill(torch.Generator().manual_seed(779))
+        print("done prefill")
 
 
 if __name__ == "__main__":

@@ -96,3 +96,26 @@ def test_three_region_plan_matches_flush_loop():
             while avail - flushed >= bs + window:
                 flushed += bs
             assert O.three_region_plan(seq, n_sink, window, bs) == (min(seq, n_sink), flushed, avail - flushed)
+
+
+def test_oracle_prefill_attention_vs_reference_golden():
+    """The reference's causal prefill kernel (run under the Triton interpreter, tests/golden/prefill.npz)
+    against the oracle's per-query attention over the tokens each query may see."""
+    import torch
+    from blockgtq_b200 import calib
+    g = load("prefill")
+    avg, mn, mx, rt, vb = CASES[str(g["case"])]
+    gqa, off = int(g["gqa"]), int(g["offset"])
+    worst = 0.0
+    for h in range(2):
+        kt = calib.build_k_tables(None, None, head_dim=HD, avg_bits=avg, rotation_threshold=rt, min_bits=mn,
+                                  max_bits=mx, bit_allocation=torch.from_numpy(g[f"h{h}_alloc"]))
+        meta = oracle_meta(kt, calib.build_v_tables(HD, vb, 42 + h))
+        sl = slice(h * gqa, (h + 1) * gqa)
+        for b in range(2):
+            for i in range(0, g["q"].shape[2], 5):
+                lim = off + i + 1
+                ro, _ = O.attend_packed(g["q_rot"][b, sl, i], g["k_packed"][b, h, :lim], g["k_norms"][b, h, :lim],
+                                        g["v_packed"][b, h, :lim], g["v_norms"][b, h, :lim], meta, 1 / HD ** 0.5)
+                worst = max(worst, np.abs(ro - g["out"][b, sl, i].astype(np.float64)).max())
+    assert worst <= 2e-3, worst

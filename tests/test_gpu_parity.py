@@ -466,3 +466,58 @@ def test_prefill_attention_vs_oracle(case, gqa, S_q, offset, causal):
                 worst = max(worst, np.abs(out_rot[b, sl, i].float().cpu().numpy() - ro_rot).max())
                 worst = max(worst, np.abs(out[b, sl, i].float().cpu().numpy() - ro).max())
     assert worst <= ATOL, worst
+
+
+def test_prefill_attention_matches_reference_golden():
+    """The operator with the reference's signature against the reference's own prefill kernel output."""
+    from blockgtq_b200 import BlockGTQQuantizer, fused_blockgtq_prefill_attention
+    g = load("prefill")
+    avg, mn, mx, rt, vb = CASES[str(g["case"])]
+    gqa, off = int(g["gqa"]), int(g["offset"])
+    kp, kn = torch.from_numpy(g["k_packed"]).to(DEV), torch.from_numpy(g["k_norms"]).to(DEV)
+    vp, vn = torch.from_numpy(g["v_packed"]).to(DEV), torch.from_numpy(g["v_norms"]).to(DEV)
+    q = torch.from_numpy(g["q"]).to(DEV)
+    for h in range(2):
+        z = BlockGTQQuantizer(HD, avg_bits=avg, rotation_threshold=rt, min_bits=mn, max_bits=mx, device=DEV)
+        z.calibrate(None, None, bit_allocation=torch.from_numpy(g[f"h{h}_alloc"]))
+        z.init_v_quantizer(v_bits=vb, seed=42 + h)
+        ka = z.build_kernel_args()
+        q_h = q[:, h * gqa:(h + 1) * gqa]
+        q_rot = z.rotate_q_for_packed_kernel(q_h.reshape(-1, HD)).reshape(q_h.shape)
+        ref_rot = torch.from_numpy(g["q_rot"][:, h * gqa:(h + 1) * gqa]).to(DEV)
+        assert (q_rot.float() - ref_rot.float()).abs().max().item() <= 2e-3 * max(1.0, ref_rot.float().abs().max().item())
+        out = fused_blockgtq_prefill_attention(
+            ref_rot, kp[:, h:h + 1], kn[:, h:h + 1], ka["codebook_flat"], ka["lut_offset"], ka["norm_group"],
+            ka["segments_b"], vp[:, h:h + 1], vn[:, h:h + 1], z.v_lut, scale=1.0 / HD ** 0.5, block_q=32, block_t=64,
+            v_bits=z.v_bits, v_rotation=z._v_rot, is_causal=True, q_pos_offset=off)
+        torch.cuda.synchronize()
+        ref = torch.from_numpy(g["out"][:, h * gqa:(h + 1) * gqa]).to(DEV)
+        assert out.shape == ref.shape and out.dtype == torch.float16
+        assert (out.float() - ref.float()).abs().max().item() <= ATOL
+
+
+def test_prefill_attention_mixed_layout_matches_decode_kernel():
+    """Nibble/raw K rows + nibble V rows (the production cache's layout): every prefill query row must
+    equal the decode kernel run over exactly the tokens that row may see."""
+    from blockgtq_b200 import _lib
+    from blockgtq_b200.layer import combine, decode, encode, prefill_attention, rotate_q_bulk
+    lt, tabs = _layer("a3_1to8")
+    gen = torch.Generator().manual_seed(5150)
+    B, n_kv, gqa, S_q, off = 1, 2, 4, 37, 100
+    n_q, T = n_kv * gqa, off + S_q
+    k = torch.stack([torch.stack([synth_head(gen, T, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
+    q = (torch.randn(B, n_q, S_q, HD, generator=gen) * 2).half().to(DEV)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half().to(DEV)
+    kp = torch.zeros(B, n_kv, T + 3, lt.max_mixed_bytes, dtype=torch.uint8, device=DEV)
+    kn = torch.zeros(B, n_kv, T + 3, lt.max_ng, dtype=torch.float16, device=DEV)
+    vp = torch.zeros(B, n_kv, T + 3, HD // 2, dtype=torch.uint8, device=DEV)
+    vn = torch.zeros(B, n_kv, T + 3, dtype=torch.float16, device=DEV)
+    encode(lt, k, v, 0, kp, kn, vp, vn, flags=_lib.ENC_K_MIXED | _lib.ENC_V_NIBBLE)
+    q_rot = rotate_q_bulk(lt, q)
+    fl = _lib.DEC_K_MIXED | _lib.DEC_V_NIBBLE
+    out = prefill_attention(lt, q_rot, kp, kn, vp, vn, T, q_pos_offset=off, causal=True, flags=fl, v_rot=lt.v_rot)
+    for i in (0, 7, 20, S_q - 1):
+        po, pl = decode(lt, q_rot[:, :, i].contiguous(), kp, kn, vp, vn, 0, off + i + 1, n_splits=2, flags=fl)
+        ref, _, _ = combine(po, pl, n_kv, v_rot=lt.v_rot)
+        torch.cuda.synchronize()
+        assert (out[:, :, i].float() - ref.float()).abs().max().item() <= ATOL
