@@ -44,6 +44,10 @@ WORKLOADS = {
     # BlockGTQKVManager layout, then single-token appends; two layers with separate inputs stand for the 40
     "mistral-nemo-12b_k3v3_encode_b4_t32768": dict(layers=2, n_q=32, n_kv=8, batch=4, ctx=32768, k_bits=3.0,
                                                    v_bits=3, theta=1e6, n_sink=0, window=0, mode="encode"),
+    # packed-cache prefill attention (the attention half of layer-major prefill): Llama-3.1-8B shape, one
+    # 16384-token prompt, K3V3; a step = bulk encode + causal prefill attention of one layer
+    "llama3.1-8b_k3v3_prefill_t16384": dict(layers=1, n_q=32, n_kv=8, batch=1, ctx=16384, k_bits=3.0, v_bits=3,
+                                            theta=5e5, n_sink=0, window=0, mode="prefill"),
     # small variant of configs[1] for quick runs and profiler captures
     "qwen2.5-3b_k3v3_b8_t32768_4layers": dict(layers=4, n_q=16, n_kv=2, batch=8, ctx=32768, k_bits=3.0, v_bits=3,
                                               theta=1e6, n_sink=0, window=0),
@@ -396,6 +400,112 @@ def run_encode(args, w, rank, world, dev):
             "gpu_launches": launches, "clocks": clocks}), flush=True)
 
 
+def run_prefill(args, w, rank, world, dev):
+    """Layer-major prefill of one layer: bulk encode of the prompt's K/V, then causal attention of every
+    prompt position over the packed cache (queries rotated with one GEMM, V un-rotated with one GEMM)."""
+    import torch.distributed as dist
+    from blockgtq_b200 import BlockGTQKVManager, _lib
+    from blockgtq_b200.layer import prefill_attention, rotate_q_bulk
+    K, W = args.steps, args.warmup
+    B, n_q, n_kv, T = w["batch"], w["n_q"], w["n_kv"], w["ctx"]
+    gqa = n_q // n_kv
+    gen = torch.Generator(device=dev).manual_seed(99 + rank)
+    mgr = BlockGTQKVManager(1, n_q, n_kv, HD, max_seq_len=T, batch_size=B, k_avg_bits=w["k_bits"], v_bits=w["v_bits"],
+                            device=dev, use_cuda_graph=False)
+    ck = torch.stack([synth_keys(gen, (1, 2048), w["theta"], dev)[0] for _ in range(n_kv)])
+    cq = torch.stack([synth_keys(gen, (gqa, 2048), w["theta"], dev).reshape(-1, HD) for _ in range(n_kv)])
+    mgr.calibrate(0, cq.float(), ck.float())
+    k = torch.stack([synth_keys(gen, (B, T), w["theta"], dev) for _ in range(n_kv)], dim=1)
+    q = torch.stack([synth_keys(gen, (B, T), w["theta"], dev) for _ in range(n_q)], dim=1)
+    v = torch.randn(B, n_kv, T, HD, generator=gen, device=dev).half()
+    hq, hk, hv = q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory()
+    sq, sk, sv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    hout = torch.empty(B, n_q, T, HD, dtype=torch.float16).pin_memory()
+    lt = None
+    t_attn = []
+
+    def layer(q_, k_, v_):
+        mgr._append_tokens(0, k_, v_, 0)
+        q_rot = rotate_q_bulk(mgr._layers[0], q_)
+        return prefill_attention(mgr._layers[0], q_rot, mgr._k_packed[0], mgr._k_norms[0], mgr._v_packed[0],
+                                 mgr._v_norms[0], T, causal=True, scale=mgr.scale, v_rot=mgr._layers[0].v_rot)
+
+    def step_device():
+        layer(q, k, v)
+
+    def step_e2e():
+        sq.copy_(hq, non_blocking=True)
+        sk.copy_(hk, non_blocking=True)
+        sv.copy_(hv, non_blocking=True)
+        hout.copy_(layer(sq, sk, sv), non_blocking=True)
+        torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(W):
+        step_device()
+    sampler = clocks_sampler(dev.index) if rank == 0 else None
+    l0 = _lib.launches
+    ms_total = timed(step_device, K)
+    launches = _lib.launches - l0
+    clocks = clocks_summary(sampler)
+    # the attention kernel alone
+    q_rot = rotate_q_bulk(mgr._layers[0], q)
+    args_ = (mgr._layers[0], q_rot, mgr._k_packed[0], mgr._k_norms[0], mgr._v_packed[0], mgr._v_norms[0], T)
+    prefill_attention(*args_)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        prefill_attention(*args_)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_kernel = e0.elapsed_time(e1) / 3
+    step_e2e()
+    ms_e2e = timed(step_e2e, max(1, K // 2))
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("bf16_tflops", 1590.0))
+        flops = 4.0 * (T * (T + 1) / 2) * HD * n_q * B              # QK^T and PV over the causal triangle
+        tf = flops / (ms_kernel * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "prefill_tokens_per_s", "value": world * B * T / (ms_total / K * 1e-3), "unit": "token-layers/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "layers_per_step": 1, "batch_per_gpu": B, "n_q": n_q, "n_kv": n_kv,
+                       "tokens": T, "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"], "parallelism": f"batch x{world}",
+                       "l2": "q/k/v inputs of a layer are 0.8 GB, larger than L2; no flush",
+                       "attention_kernel_ms": ms_kernel},
+            "roofline": {"bound": "tensor", "kernel": "prefill_kernel", "achieved": tf, "peak": peak, "unit": "TFLOP/s",
+                         "frac": tf / peak, "traffic": None,
+                         "peak_source": "MEASURED_PEAKS.json (bf16 burst)" if peaks else "fallback",
+                         "algorithmic_flops_per_launch": flops, "launch_ms": ms_kernel},
+            "e2e": {"value": world * B * T / (ms_e2e / max(1, K // 2) * 1e-3), "unit": "token-layers/s",
+                    "h2d_bytes_per_step": int((hq.numel() + hk.numel() + hv.numel()) * 2),
+                    "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": ms_e2e / max(1, K // 2)},
+            "gpu_launches": launches, "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -426,6 +536,11 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    if w.get("mode") == "prefill":
+        run_prefill(args, w, rank, world, dev)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if w.get("mode") == "encode":
         run_encode(args, w, rank, world, dev)
         if world > 1:

@@ -36,10 +36,12 @@ struct PfSmem {
     __half kh[kPfTok * kPfLd];
     __half vh[kPfTok * kPfLd];
     float kn_f[BGTQ_MAX_SEGMENTS][kPfTok];          // per-token segment norms (1 where folded into kh)
-    __align__(16) uint8_t raw_k[kPfTok * 160 + 16];
-    __align__(16) uint8_t raw_kn[kPfTok * 32 + 16];
-    __align__(16) uint8_t raw_v[kPfTok * 128 + 16];
-    __align__(16) uint8_t raw_vn[kPfTok * 16 + 16];
+    // packed rows of a tile, as they lie in the cache; two buffers: the next tile streams in (cp.async)
+    // while the current one is dequantised and multiplied
+    __align__(16) uint8_t raw_k[2][kPfTok * 160 + 16];
+    __align__(16) uint8_t raw_kn[2][kPfTok * 32 + 16];
+    __align__(16) uint8_t raw_v[2][kPfTok * 128 + 16];
+    __align__(16) uint8_t raw_vn[2][kPfTok * 16 + 16];
     uint16_t cb[528];                               // 512 K entries + 16 V entries (fp16 bits)
     uint2 ktask[kPfMaxTasks];   // x: first code | count << 8 | stored bits << 12 | segment << 16 | fold-norm << 20
     uint2 vtask[16];            // y: byte offset | codebook offset << 16
@@ -56,16 +58,19 @@ __device__ __forceinline__ void pf_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t 
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-// Copy n_bytes starting at src (any alignment) into dst so that dst[(src & 3) + i] = src[i].
+// Start copying n_bytes from src (any alignment) into dst so that dst[(src & 3) + i] = src[i]:
+// whole 32-bit words asynchronously (cp.async), the ragged tail byte by byte.
 __device__ __forceinline__ void pf_stage(uint8_t* dst, const uint8_t* src, int n_bytes, int tid) {
     const uint32_t ph = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 3u);
-    const uint32_t* s4 = reinterpret_cast<const uint32_t*>(src - ph);
-    uint32_t* d4 = reinterpret_cast<uint32_t*>(dst);
-    const int n_words = (int)((ph + n_bytes) >> 2);           // whole words; the ragged tail goes byte by byte
-    for (int i = tid; i < n_words; i += kPfWarps * 32) d4[i] = __ldg(s4 + i);
+    const uint8_t* s4 = src - ph;
+    const uint32_t d4 = smem_u32(dst);
+    const int n_words = (int)((ph + n_bytes) >> 2);
+    for (int i = tid; i < n_words; i += kPfWarps * 32)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d4 + 4u * i), "l"(s4 + 4 * i) : "memory");
     const int tail = (int)((ph + n_bytes) & 3u);
-    if (tid < tail) dst[4 * n_words + tid] = __ldg(src - ph + 4 * n_words + tid);
+    if (tid < tail) dst[4 * n_words + tid] = __ldg(s4 + 4 * n_words + tid);
 }
+__device__ __forceinline__ void pf_stage_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // Tables of one head: dequantisation tasks of 8 consecutive codes of one width.
 __device__ void pf_setup(PfSmem& S, const PfParams& P, const BgtqHeadDesc& d) {
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParam
     const int r = lane >> 2, j = lane & 3;
     const int h = blockIdx.y, b = blockIdx.z;
     const int bq = kPfRows / P.gqa;                  // query positions per CTA
-    const int q0 = blockIdx.x * bq;
+    const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * bq;      // latest positions (most tiles under the causal mask) first
     const BgtqHeadDesc& d = P.desc[h];
 
     pf_setup(S, P, d);
@@ -171,22 +176,25 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParam
     __syncthreads();
     const int n_seg = S.n_seg, n_ktask = S.n_ktask, n_vtask = S.n_vtask;
 
-    for (int t0 = 0; t0 < t_max; t0 += kPfTok) {
+    auto stage_tile = [&](int t0, int buf) {
         const int nt = min(kPfTok, t_max - t0);
-        // ---- 1. packed rows of the tile -> shared memory ----
-        const uint8_t* gk = P.kp + bh_kp + (size_t)t0 * P.kp_st;
-        const uint8_t* gn = P.kn + bh_kn + (size_t)t0 * P.kn_st;
-        const uint8_t* gv = P.vp + bh_vp + (size_t)t0 * P.vp_st;
-        const uint8_t* gw = P.vn + bh_vn + (size_t)t0 * P.vn_st;
-        pf_stage(S.raw_k, gk, nt * P.kp_st, tid);
-        pf_stage(S.raw_kn, gn, nt * P.kn_st, tid);
-        pf_stage(S.raw_v, gv, nt * P.vp_st, tid);
-        pf_stage(S.raw_vn, gw, nt * P.vn_st, tid);
+        pf_stage(S.raw_k[buf], P.kp + bh_kp + (size_t)t0 * P.kp_st, nt * P.kp_st, tid);
+        pf_stage(S.raw_kn[buf], P.kn + bh_kn + (size_t)t0 * P.kn_st, nt * P.kn_st, tid);
+        pf_stage(S.raw_v[buf], P.vp + bh_vp + (size_t)t0 * P.vp_st, nt * P.vp_st, tid);
+        pf_stage(S.raw_vn[buf], P.vn + bh_vn + (size_t)t0 * P.vn_st, nt * P.vn_st, tid);
+    };
+    if (t_max > 0) stage_tile(0, 0);
+    int buf = 0;
+    for (int t0 = 0; t0 < t_max; t0 += kPfTok, buf ^= 1) {
+        const int nt = min(kPfTok, t_max - t0);
+        // ---- 1. packed rows of this tile have been streaming in; start the next tile's ----
+        pf_stage_wait();
         __syncthreads();
-        const uint8_t* rk = S.raw_k + (reinterpret_cast<uintptr_t>(gk) & 3u);
-        const uint8_t* rn = S.raw_kn + (reinterpret_cast<uintptr_t>(gn) & 3u);
-        const uint8_t* rv = S.raw_v + (reinterpret_cast<uintptr_t>(gv) & 3u);
-        const uint8_t* rw = S.raw_vn + (reinterpret_cast<uintptr_t>(gw) & 3u);
+        if (t0 + kPfTok < t_max) stage_tile(t0 + kPfTok, buf ^ 1);
+        const uint8_t* rk = S.raw_k[buf] + (reinterpret_cast<uintptr_t>(P.kp + bh_kp + (size_t)t0 * P.kp_st) & 3u);
+        const uint8_t* rn = S.raw_kn[buf] + (reinterpret_cast<uintptr_t>(P.kn + bh_kn + (size_t)t0 * P.kn_st) & 3u);
+        const uint8_t* rv = S.raw_v[buf] + (reinterpret_cast<uintptr_t>(P.vp + bh_vp + (size_t)t0 * P.vp_st) & 3u);
+        const uint8_t* rw = S.raw_vn[buf] + (reinterpret_cast<uintptr_t>(P.vn + bh_vn + (size_t)t0 * P.vn_st) & 3u);
         // ---- 2. dequantise: task index = (task << 6) | token, so a warp works on one width at a time ----
         for (int i = tid; i < kPfTok * n_ktask; i += kPfWarps * 32) {
             const int tok = i & (kPfTok - 1);
@@ -317,7 +325,6 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParam
                 mma_16816(O[2 * nd + 1], pa[kt], b1);
             }
         }
-        __syncthreads();       // the tiles are rebuilt next
     }
 
     // ---- normalise and write (fp32, V's rotated basis) ----
