@@ -1,9 +1,9 @@
 // Packed-cache prefill attention: many query positions per KV head against the quantised cache, causal.
 //
-// One CTA owns 128 query rows of one (batch, KV head): 128 / gqa consecutive positions x the gqa query
-// heads of the group (row = position * gqa + head), one m16 MMA tile per warp.  Cache tokens are walked
+// One CTA owns 256 query rows of one (batch, KV head): 256 / gqa consecutive positions x the gqa query
+// heads of the group (row = position * gqa + head), one m16 MMA tile per warp, queries staged in shared memory.  Cache tokens are walked
 // in tiles of 64: the packed rows are copied to shared memory, dequantised ONCE per tile into fp16 K and V
-// tiles (the cost the decode kernel pays per 8 query rows is shared by 128 here), then
+// tiles (the cost the decode kernel pays per 8 query rows is shared by 256 here), then
 //   S = Q . Khat^T   per width segment, scaled by that segment's per-token norm in fp32,
 //   online softmax in the log2 domain (causal limit per row), P rounded to fp16,
 //   O += P . Vhat    with vhat = fp16(centroid * norm)
@@ -15,8 +15,8 @@ namespace bgtq {
 namespace {
 
 constexpr int kPfTok = 64;        // cache tokens per tile
-constexpr int kPfRows = 128;      // query rows per CTA
-constexpr int kPfWarps = 8;
+constexpr int kPfRows = 256;      // query rows per CTA
+constexpr int kPfWarps = 16;
 constexpr int kPfLd = 136;        // halfs per row of the dequantised tiles (conflict-free ldmatrix)
 constexpr int kPfMaxTasks = 32;
 
@@ -33,6 +33,7 @@ struct PfParams {
 };
 
 struct PfSmem {
+    __half qs[kPfRows * kPfLd];                      // the CTA's query rows (packed-K basis)
     __half kh[kPfTok * kPfLd];
     __half vh[kPfTok * kPfLd];
     float kn_f[BGTQ_MAX_SEGMENTS][kPfTok];          // per-token segment norms (1 where folded into kh)
@@ -140,22 +141,30 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParam
 
     pf_setup(S, P, d);
 
-    // this thread's two query rows (A-fragment rows r and r + 8 of the warp's tile)
+    // the CTA's query rows -> shared memory (16-byte chunks, coalesced); rows past the end are zero
+    for (int i = tid; i < kPfRows * 16; i += kPfWarps * 32) {
+        const int row = i >> 4, c8 = (i & 15) * 8;
+        const int qi_ = row / P.gqa, hq_ = h * P.gqa + row % P.gqa;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < bq * P.gqa && q0 + qi_ < P.s_q) {
+            const __half* src = P.q + b * P.q_sb + hq_ * P.q_sh + (int64_t)(q0 + qi_) * P.q_ss + c8;
+            if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) v = __ldg(reinterpret_cast<const uint4*>(src));
+            else {
+                const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src);
+                v = make_uint4(__ldg(s32), __ldg(s32 + 1), __ldg(s32 + 2), __ldg(s32 + 3));
+            }
+        }
+        *reinterpret_cast<uint4*>(&S.qs[row * kPfLd + c8]) = v;
+    }
+    // this thread's two query rows (accumulator rows r and r + 8 of the warp's tile)
     int qi[2], hq[2];
     bool rok[2];
-    uint32_t qa[8][4];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
         const int row = warp * 16 + r + 8 * e;
         qi[e] = row / P.gqa;
         hq[e] = h * P.gqa + row % P.gqa;
         rok[e] = row < bq * P.gqa && q0 + qi[e] < P.s_q;
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(P.q + b * P.q_sb + hq[e] * P.q_sh + (int64_t)(q0 + qi[e]) * P.q_ss);
-#pragma unroll
-        for (int kt = 0; kt < 8; ++kt) {
-            qa[kt][e] = rok[e] ? __ldg(src + kt * 8 + j) : 0u;            // dims 16 kt + 2j, +1
-            qa[kt][2 + e] = rok[e] ? __ldg(src + kt * 8 + 4 + j) : 0u;    // dims 16 kt + 8 + 2j, +1
-        }
     }
     // causal limit (exclusive cache token index) per row, and for the whole CTA
     int lim[2];
@@ -173,6 +182,7 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParam
     const size_t bh_kp = (size_t)b * P.kp_sb + (size_t)h * P.kp_sh, bh_kn = (size_t)b * P.kn_sb + (size_t)h * P.kn_sh;
     const size_t bh_vp = (size_t)b * P.vp_sb + (size_t)h * P.vp_sh, bh_vn = (size_t)b * P.vn_sb + (size_t)h * P.vn_sh;
     const uint32_t kh_u32 = smem_u32(S.kh), vh_u32 = smem_u32(S.vh);
+    const uint32_t qa_u32 = smem_u32(S.qs) + 2u * ((warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kPfLd + (lane >> 4) * 8);
     __syncthreads();
     const int n_seg = S.n_seg, n_ktask = S.n_ktask, n_vtask = S.n_vtask;
 
@@ -232,21 +242,22 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParam
             S.kn_f[sg][tok] = v;
         }
         __syncthreads();
-        // ---- 3. S = Q . Khat^T per segment, scaled by the per-token segment norm ----
-        float Sv[8][4];
+        // ---- 3-5. per 32-token half tile: S = Q . Khat^T per segment (scaled by the per-token segment
+        //           norm), online softmax in the log2 domain, O += P . Vhat ----
+#pragma unroll 1
+        for (int hf = 0; hf < 2; ++hf) {
+            if (hf * 32 >= nt) break;
+            float Sv[4][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) Sv[i][0] = Sv[i][1] = Sv[i][2] = Sv[i][3] = 0.f;
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {            // 32 tokens at a time (four n-tiles) to bound registers
+            for (int i = 0; i < 4; ++i) Sv[i][0] = Sv[i][1] = Sv[i][2] = Sv[i][3] = 0.f;
             for (int sg = 0; sg < n_seg; ++sg) {
                 const int st = S.seg_start[sg], en = st + S.seg_len[sg];
                 float acc[4][4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-#pragma unroll
-                for (int kt = 0; kt < 8; ++kt) {
-                    if (kt * 16 + 16 <= st || kt * 16 >= en) continue;      // k-tile outside the segment
-                    uint32_t a[4] = {qa[kt][0], qa[kt][1], qa[kt][2], qa[kt][3]};
+                for (int kt = st >> 4; kt * 16 < en; ++kt) {
+                    uint32_t a[4];
+                    pf_ldmatrix_x4(a, qa_u32 + 32u * kt);
                     if (kt * 16 < st || kt * 16 + 16 > en) {                // straddles: keep this segment's dims only
                         const int dlo = kt * 16 + 2 * j, dhi = dlo + 8;
                         if (dlo < st || dlo >= en) a[0] = a[1] = 0u;
@@ -264,65 +275,66 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParam
                 }
 #pragma unroll
                 for (int nt4 = 0; nt4 < 4; ++nt4) {
-                    const float n0 = S.kn_f[sg][hf * 32 + nt4 * 8 + 2 * j], n1 = S.kn_f[sg][hf * 32 + nt4 * 8 + 2 * j + 1];
-                    Sv[hf * 4 + nt4][0] = fmaf(n0, acc[nt4][0], Sv[hf * 4 + nt4][0]);
-                    Sv[hf * 4 + nt4][1] = fmaf(n1, acc[nt4][1], Sv[hf * 4 + nt4][1]);
-                    Sv[hf * 4 + nt4][2] = fmaf(n0, acc[nt4][2], Sv[hf * 4 + nt4][2]);
-                    Sv[hf * 4 + nt4][3] = fmaf(n1, acc[nt4][3], Sv[hf * 4 + nt4][3]);
+                    const float2 nn = *reinterpret_cast<const float2*>(&S.kn_f[sg][hf * 32 + nt4 * 8 + 2 * j]);
+                    Sv[nt4][0] = fmaf(nn.x, acc[nt4][0], Sv[nt4][0]);
+                    Sv[nt4][1] = fmaf(nn.y, acc[nt4][1], Sv[nt4][1]);
+                    Sv[nt4][2] = fmaf(nn.x, acc[nt4][2], Sv[nt4][2]);
+                    Sv[nt4][3] = fmaf(nn.y, acc[nt4][3], Sv[nt4][3]);
                 }
             }
-        }
-        // ---- 4. online softmax (log2 domain); rows r (e = 0) and r + 8 (e = 1) ----
-        float mx[2] = {-INFINITY, -INFINITY};
+            // online softmax; rows r (e = 0) and r + 8 (e = 1)
+            float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < 4; ++i) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int e = c >> 1, tok = t0 + i * 8 + 2 * j + (c & 1);
-                Sv[i][c] = tok < lim[e] ? Sv[i][c] * P.scale_log2 : -INFINITY;
-                mx[e] = fmaxf(mx[e], Sv[i][c]);
+                for (int c = 0; c < 4; ++c) {
+                    const int e = c >> 1, tok = t0 + hf * 32 + i * 8 + 2 * j + (c & 1);
+                    Sv[i][c] = tok < lim[e] ? Sv[i][c] * P.scale_log2 : -INFINITY;
+                    mx[e] = fmaxf(mx[e], Sv[i][c]);
+                }
             }
-        }
-        float al[2], z[2], ps[2] = {0.f, 0.f};
+            float al[2], z[2], ps[2] = {0.f, 0.f};
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 1));
-            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 2));
-            const float nm = fmaxf(mrow[e], mx[e]);
-            z[e] = nm == -INFINITY ? 0.f : nm;
-            al[e] = exp2f(mrow[e] - z[e]);
-            mrow[e] = nm;
-        }
-        uint32_t pa[4][4];     // P as A fragments of the four 16-token k-tiles
+            for (int e = 0; e < 2; ++e) {
+                mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 1));
+                mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 2));
+                const float nm = fmaxf(mrow[e], mx[e]);
+                z[e] = nm == -INFINITY ? 0.f : nm;
+                al[e] = exp2f(mrow[e] - z[e]);
+                mrow[e] = nm;
+            }
+            uint32_t pa[2][4];     // P as A fragments of the two 16-token k-tiles
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float p0 = exp2f(Sv[i][0] - z[0]), p1 = exp2f(Sv[i][1] - z[0]);
-            const float p2 = exp2f(Sv[i][2] - z[1]), p3 = exp2f(Sv[i][3] - z[1]);
-            ps[0] += p0 + p1;
-            ps[1] += p2 + p3;
-            pa[i >> 1][(i & 1) * 2] = pack_half2(p0, p1);
-            pa[i >> 1][(i & 1) * 2 + 1] = pack_half2(p2, p3);
-        }
+            for (int i = 0; i < 4; ++i) {
+                const float p0 = exp2f(Sv[i][0] - z[0]), p1 = exp2f(Sv[i][1] - z[0]);
+                const float p2 = exp2f(Sv[i][2] - z[1]), p3 = exp2f(Sv[i][3] - z[1]);
+                ps[0] += p0 + p1;
+                ps[1] += p2 + p3;
+                pa[i >> 1][(i & 1) * 2] = pack_half2(p0, p1);
+                pa[i >> 1][(i & 1) * 2 + 1] = pack_half2(p2, p3);
+            }
 #pragma unroll
-        for (int e = 0; e < 2; ++e) lrow[e] = fmaf(lrow[e], al[e], ps[e]);
+            for (int e = 0; e < 2; ++e) lrow[e] = fmaf(lrow[e], al[e], ps[e]);
+            if (__any_sync(0xffffffffu, al[0] != 1.f || al[1] != 1.f)) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            O[i][0] *= al[0];
-            O[i][1] *= al[0];
-            O[i][2] *= al[1];
-            O[i][3] *= al[1];
-        }
-        // ---- 5. O += P . Vhat ----
+                for (int i = 0; i < 16; ++i) {
+                    O[i][0] *= al[0];
+                    O[i][1] *= al[0];
+                    O[i][2] *= al[1];
+                    O[i][3] *= al[1];
+                }
+            }
 #pragma unroll
-        for (int kt = 0; kt < 4; ++kt) {
+            for (int kt = 0; kt < 2; ++kt) {
 #pragma unroll
-            for (int nd = 0; nd < 8; ++nd) {         // two n-tiles (16 dims) per ldmatrix.x4.trans
-                uint32_t bm[4];
-                const int tok = kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                pf_ldmatrix_x4_trans(bm, vh_u32 + 2u * (tok * kPfLd + nd * 16 + (lane >> 4) * 8));
-                const uint32_t b0[2] = {bm[0], bm[1]}, b1[2] = {bm[2], bm[3]};
-                mma_16816(O[2 * nd], pa[kt], b0);
-                mma_16816(O[2 * nd + 1], pa[kt], b1);
+                for (int nd = 0; nd < 8; ++nd) {         // two n-tiles (16 dims) per ldmatrix.x4.trans
+                    uint32_t bm[4];
+                    const int tok = hf * 32 + kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    pf_ldmatrix_x4_trans(bm, vh_u32 + 2u * (tok * kPfLd + nd * 16 + (lane >> 4) * 8));
+                    const uint32_t b0[2] = {bm[0], bm[1]}, b1[2] = {bm[2], bm[3]};
+                    mma_16816(O[2 * nd], pa[kt], b0);
+                    mma_16816(O[2 * nd + 1], pa[kt], b1);
+                }
             }
         }
     }
