@@ -4,11 +4,14 @@
 // heads of the group (row = position * gqa + head), one m16 MMA tile per warp, queries staged in shared memory.  Cache tokens are walked
 // in tiles of 64: the packed rows are copied to shared memory, dequantised ONCE per tile into fp16 K and V
 // tiles (the cost the decode kernel pays per 8 query rows is shared by 256 here), then
-//   S = Q . Khat^T   per width segment, scaled by that segment's per-token norm in fp32,
+//   S = Q . Khat^T   with khat = fp16 centroid * fp16 segment norm held EXACTLY as a sum of two fp16
+//                    tiles (the product has 22 significant bits), so fp32 accumulation reproduces the
+//                    decode kernel's "fp32 dot product per segment times norm" without per-segment
+//                    accumulators or masked k-tiles: a plain 8-k-tile MMA chain, run twice,
 //   online softmax in the log2 domain (causal limit per row), P rounded to fp16,
 //   O += P . Vhat    with vhat = fp16(centroid * norm)
-// on mma.sync m16n8k16.  Rounding points are those of the decode kernel (bgtq_decode.cu).  The result is
-// written as fp32 in V's rotated basis; the caller applies V's rotation as one plain GEMM.
+// on mma.sync m16n8k16.  The result is written as fp32 in V's rotated basis; the caller applies V's
+// rotation as one plain GEMM.
 #include "bgtq_common.cuh"
 
 namespace bgtq {
@@ -34,9 +37,9 @@ struct PfParams {
 
 struct PfSmem {
     __half qs[kPfRows * kPfLd];                      // the CTA's query rows (packed-K basis)
-    __half kh[kPfTok * kPfLd];
+    __half kh[kPfTok * kPfLd];                       // khat, high fp16 part
+    __half kl[kPfTok * kPfLd];                       // khat, low fp16 part (khat = kh + kl exactly)
     __half vh[kPfTok * kPfLd];
-    float kn_f[BGTQ_MAX_SEGMENTS][kPfTok];          // per-token segment norms (1 where folded into kh)
     // packed rows of a tile, as they lie in the cache; two buffers: the next tile streams in (cp.async)
     // while the current one is dequantised and multiplied
     __align__(16) uint8_t raw_k[2][kPfTok * 160 + 16];
@@ -44,10 +47,9 @@ struct PfSmem {
     __align__(16) uint8_t raw_v[2][kPfTok * 128 + 16];
     __align__(16) uint8_t raw_vn[2][kPfTok * 16 + 16];
     uint16_t cb[528];                               // 512 K entries + 16 V entries (fp16 bits)
-    uint2 ktask[kPfMaxTasks];   // x: first code | count << 8 | stored bits << 12 | segment << 16 | fold-norm << 20
+    uint2 ktask[kPfMaxTasks];   // x: first code | count << 8 | stored bits << 12 | segment << 16 | fp16-round << 20
     uint2 vtask[16];            // y: byte offset | codebook offset << 16
-    int32_t n_ktask, n_vtask, n_seg;
-    int32_t seg_start[BGTQ_MAX_SEGMENTS], seg_len[BGTQ_MAX_SEGMENTS];
+    int32_t n_ktask, n_vtask;
 };
 
 __device__ __forceinline__ void pf_ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -77,22 +79,19 @@ __device__ __forceinline__ void pf_stage_wait() { asm volatile("cp.async.wait_al
 __device__ void pf_setup(PfSmem& S, const PfParams& P, const BgtqHeadDesc& d) {
     const int tid = threadIdx.x;
     for (int i = tid; i < 528; i += kPfWarps * 32) S.cb[i] = i < 512 ? d.codebook[i] : d.v_lut[i - 512];
-    if (tid < BGTQ_MAX_SEGMENTS) {
-        S.seg_start[tid] = d.seg_start[tid];
-        S.seg_len[tid] = d.seg_len[tid];
-    }
     if (tid == 0) {
         const bool mixed = P.flags & BGTQ_DEC_K_MIXED;
         int nt = 0;
         for (int s = 0; s < d.n_seg; ++s) {
             const int bw = d.seg_bw[s], st = d.seg_start[s], len = d.seg_len[s];
             const int sb = mixed ? (bw <= 4 ? 4 : 8) : (bw <= 4 ? bw : 8);
+            // nibble-layout numerics of the reference (fused_packed_attention.py:1449-1452), as in the decode
+            // plan: long low-width segments round centroid * norm to fp16
+            const int fold = (mixed && len >= 16 && s < 5) ? 1 : 0;
             const int base = mixed ? (bw <= 4 ? st / 2 : d.nopack_start / 2 + (st - d.nopack_start)) : d.seg_pack_off[s];
-            const int fold = (mixed && len >= 16 && s < 5) ? 1 : 0;     // nibble-layout numerics, as in the decode plan
             for (int c = 0; c < len; c += 8) {
                 const int n = len - c < 8 ? len - c : 8;
-                S.ktask[nt] = make_uint2((uint32_t)(st + c) | (uint32_t)n << 8 | (uint32_t)sb << 12 | (uint32_t)s << 16 |
-                                             (uint32_t)fold << 20,
+                S.ktask[nt] = make_uint2((uint32_t)(st + c) | (uint32_t)n << 8 | (uint32_t)sb << 12 | (uint32_t)s << 16 | (uint32_t)fold << 20,
                                          (uint32_t)(base + (c * sb) / 8) | (uint32_t)d.seg_lut_off[s] << 16);
                 ++nt;
             }
@@ -102,7 +101,6 @@ __device__ void pf_setup(PfSmem& S, const PfParams& P, const BgtqHeadDesc& d) {
         for (int c = 0; c < kHD; c += 8)
             S.vtask[c / 8] = make_uint2((uint32_t)c | 8u << 8 | (uint32_t)vsb << 12, (uint32_t)((c * vsb) / 8) | 512u << 16);
         S.n_vtask = kHD / 8;
-        S.n_seg = d.n_seg;
     }
 }
 
@@ -125,6 +123,30 @@ __device__ __forceinline__ void pf_dequant8(const uint8_t* p, int n, int sb, con
                 b = __hmul(b, nrm);
             }
             *reinterpret_cast<__half2*>(dst + i) = __halves2half2(a, b);
+        }
+    }
+}
+
+// K variant: value = fp16 centroid * fp16 norm, exact in fp32 (22 significant bits), stored as the sum of
+// two fp16 numbers so that the tensor-core product with fp32 accumulation keeps the fp32 norm scaling of
+// the decode kernel without a per-segment accumulator.
+__device__ __forceinline__ void pf_dequant8_k(const uint8_t* p, int n, int sb, const uint16_t* cb, float nrm,
+                                              bool round16, __half* dst_hi, __half* dst_lo) {
+    const int nbytes = (n * sb + 7) >> 3;
+    uint64_t w = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (i < nbytes) w |= (uint64_t)p[i] << (8 * i);
+    const uint32_t m = (1u << sb) - 1u;
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        if (i < n) {
+            const float a = __half2float(__ushort_as_half(cb[(uint32_t)(w >> (i * sb)) & m])) * nrm;
+            const float b = __half2float(__ushort_as_half(cb[(uint32_t)(w >> ((i + 1) * sb)) & m])) * nrm;
+            const __half2 hi = __floats2half2_rn(a, b);
+            const float2 hf = __half22float2(hi);
+            *reinterpret_cast<__half2*>(dst_hi + i) = hi;
+            *reinterpret_cast<__half2*>(dst_lo + i) = round16 ? __floats2half2_rn(0.f, 0.f) : __floats2half2_rn(a - hf.x, b - hf.y);
         }
     }
 }
@@ -181,10 +203,10 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParam
 
     const size_t bh_kp = (size_t)b * P.kp_sb + (size_t)h * P.kp_sh, bh_kn = (size_t)b * P.kn_sb + (size_t)h * P.kn_sh;
     const size_t bh_vp = (size_t)b * P.vp_sb + (size_t)h * P.vp_sh, bh_vn = (size_t)b * P.vn_sb + (size_t)h * P.vn_sh;
-    const uint32_t kh_u32 = smem_u32(S.kh), vh_u32 = smem_u32(S.vh);
+    const uint32_t kh_u32 = smem_u32(S.kh), kl_u32 = smem_u32(S.kl), vh_u32 = smem_u32(S.vh);
     const uint32_t qa_u32 = smem_u32(S.qs) + 2u * ((warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kPfLd + (lane >> 4) * 8);
     __syncthreads();
-    const int n_seg = S.n_seg, n_ktask = S.n_ktask, n_vtask = S.n_vtask;
+    const int n_ktask = S.n_ktask, n_vtask = S.n_vtask;
 
     auto stage_tile = [&](int t0, int buf) {
         const int nt = min(kPfTok, t_max - t0);
@@ -210,15 +232,18 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParam
             const int tok = i & (kPfTok - 1);
             const uint2 tk = S.ktask[i >> 6];
             const int first = tk.x & 0xFF, n = (tk.x >> 8) & 0xF, sb = (tk.x >> 12) & 0xF, sg = (tk.x >> 16) & 0xF;
-            const bool fold = (tk.x >> 20) & 1u;
             __half* dst = S.kh + tok * kPfLd + first;
+            __half* dsl = S.kl + tok * kPfLd + first;
             if (tok < nt) {
-                const __half nrm = __ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + tok * P.kn_st + 2 * sg));
-                pf_dequant8(rk + tok * P.kp_st + (tk.y & 0xFFFFu), n, sb, S.cb + (tk.y >> 16), fold, nrm, dst);
+                const float nrm = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + tok * P.kn_st + 2 * sg)));
+                pf_dequant8_k(rk + tok * P.kp_st + (tk.y & 0xFFFFu), n, sb, S.cb + (tk.y >> 16), nrm, (tk.x >> 20) & 1u, dst, dsl);
             } else {
 #pragma unroll
                 for (int c = 0; c < 8; c += 2)
-                    if (c < n) *reinterpret_cast<uint32_t*>(dst + c) = 0u;
+                    if (c < n) {
+                        *reinterpret_cast<uint32_t*>(dst + c) = 0u;
+                        *reinterpret_cast<uint32_t*>(dsl + c) = 0u;
+                    }
             }
         }
         for (int i = tid; i < kPfTok * n_vtask; i += kPfWarps * 32) {
@@ -233,53 +258,31 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParam
                 *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
         }
-        for (int i = tid; i < kPfTok * n_seg; i += kPfWarps * 32) {
-            const int tok = i & (kPfTok - 1), sg = i >> 6;
-            const bool fold = (P.flags & BGTQ_DEC_K_MIXED) && S.seg_len[sg] >= 16 && sg < 5;
-            float v = 0.f;
-            if (tok < nt)
-                v = fold ? 1.0f : __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + tok * P.kn_st + 2 * sg)));
-            S.kn_f[sg][tok] = v;
-        }
         __syncthreads();
-        // ---- 3-5. per 32-token half tile: S = Q . Khat^T per segment (scaled by the per-token segment
-        //           norm), online softmax in the log2 domain, O += P . Vhat ----
+        // ---- 3-5. per 32-token half tile: S = Q . Khat^T, online softmax in the log2 domain, O += P . Vhat ----
 #pragma unroll 1
         for (int hf = 0; hf < 2; ++hf) {
             if (hf * 32 >= nt) break;
             float Sv[4][4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) Sv[i][0] = Sv[i][1] = Sv[i][2] = Sv[i][3] = 0.f;
-            for (int sg = 0; sg < n_seg; ++sg) {
-                const int st = S.seg_start[sg], en = st + S.seg_len[sg];
-                float acc[4][4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-                for (int kt = st >> 4; kt * 16 < en; ++kt) {
-                    uint32_t a[4];
-                    pf_ldmatrix_x4(a, qa_u32 + 32u * kt);
-                    if (kt * 16 < st || kt * 16 + 16 > en) {                // straddles: keep this segment's dims only
-                        const int dlo = kt * 16 + 2 * j, dhi = dlo + 8;
-                        if (dlo < st || dlo >= en) a[0] = a[1] = 0u;
-                        if (dhi < st || dhi >= en) a[2] = a[3] = 0u;
-                    }
+            for (int kt = 0; kt < 8; ++kt) {
+                uint32_t a[4];
+                pf_ldmatrix_x4(a, qa_u32 + 32u * kt);
 #pragma unroll
-                    for (int np = 0; np < 2; ++np) {     // two n-tiles (16 tokens) per ldmatrix.x4
-                        uint32_t bm[4];
-                        const int tok = hf * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8;
-                        pf_ldmatrix_x4(bm, kh_u32 + 2u * (tok * kPfLd + kt * 16 + ((lane >> 3) & 1) * 8));
-                        const uint32_t b0[2] = {bm[0], bm[1]}, b1[2] = {bm[2], bm[3]};
-                        mma_16816(acc[2 * np], a, b0);
-                        mma_16816(acc[2 * np + 1], a, b1);
-                    }
-                }
-#pragma unroll
-                for (int nt4 = 0; nt4 < 4; ++nt4) {
-                    const float2 nn = *reinterpret_cast<const float2*>(&S.kn_f[sg][hf * 32 + nt4 * 8 + 2 * j]);
-                    Sv[nt4][0] = fmaf(nn.x, acc[nt4][0], Sv[nt4][0]);
-                    Sv[nt4][1] = fmaf(nn.y, acc[nt4][1], Sv[nt4][1]);
-                    Sv[nt4][2] = fmaf(nn.x, acc[nt4][2], Sv[nt4][2]);
-                    Sv[nt4][3] = fmaf(nn.y, acc[nt4][3], Sv[nt4][3]);
+                for (int np = 0; np < 2; ++np) {     // two n-tiles (16 tokens) per ldmatrix.x4
+                    uint32_t bm[4];
+                    const int tok = hf * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8;
+                    const uint32_t off = 2u * (tok * kPfLd + kt * 16 + ((lane >> 3) & 1) * 8);
+                    pf_ldmatrix_x4(bm, kl_u32 + off);                 // small part first
+                    const uint32_t l0[2] = {bm[0], bm[1]}, l1[2] = {bm[2], bm[3]};
+                    mma_16816(Sv[2 * np], a, l0);
+                    mma_16816(Sv[2 * np + 1], a, l1);
+                    pf_ldmatrix_x4(bm, kh_u32 + off);
+                    const uint32_t b0[2] = {bm[0], bm[1]}, b1[2] = {bm[2], bm[3]};
+                    mma_16816(Sv[2 * np], a, b0);
+                    mma_16816(Sv[2 * np + 1], a, b1);
                 }
             }
             // online softmax; rows r (e = 0) and r + 8 (e = 1)
