@@ -37,7 +37,7 @@ constexpr int kMergeStride = 132;  // floats per query row in the end-of-CTA mer
 // shared-memory layout (byte offsets from the start of dynamic shared memory)
 // [barriers | codebook staging | per-step uniform params | per-step per-lane params | tables | stages]
 constexpr uint32_t kOffCbk = 128, kOffStepU = 1280, kOffStepL = kOffStepU + kMaxSteps * 16;   // StepU: per segment
-constexpr uint32_t kOffLut = 16384;  // multiple of kLutTableBytes: table bases can be OR-ed into offsets
+constexpr uint32_t kOffLut = 12288;  // multiple of kLutTableBytes: table bases can be OR-ed into offsets
 static_assert(kOffStepL + kMaxSteps * 32 * 16 <= kOffLut && kOffLut % kLutTableBytes == 0, "layout");
 
 struct DecParams {
@@ -66,7 +66,7 @@ struct DecParams {
 template <int VB> struct VCfg;
 template <> struct VCfg<1> { static constexpr uint32_t M = 0x5555u, GROUPS = 1, REP_SHIFT = 5; };
 template <> struct VCfg<2> { static constexpr uint32_t M = 0x33333333u, GROUPS = 1, REP_SHIFT = 5; };
-template <> struct VCfg<3> { static constexpr uint32_t M = 0x001C71C7u, GROUPS = 2, REP_SHIFT = 5; };
+template <> struct VCfg<3> { static constexpr uint32_t M = 0x001C71C7u, GROUPS = 2, REP_SHIFT = 4; };
 template <> struct VCfg<4> { static constexpr uint32_t M = 0x0F0F0F0Fu, GROUPS = 2, REP_SHIFT = 2; };
 
 __device__ __forceinline__ uint32_t ld32(const uint8_t* sm, uint32_t off) {
@@ -493,7 +493,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     }
 }
 
-constexpr uint32_t v_rep_shift_for(int vb) { return vb <= 3 ? 5 : 2; }
+constexpr uint32_t v_rep_shift_for(int vb) { return vb <= 2 ? 5 : (vb == 3 ? 4 : 2); }
 constexpr uint32_t kMergeBytes = (kConsumerWarps * 8 * kMergeStride + 2 * kConsumerWarps * 8) * 4;
 
 }  // namespace
@@ -536,10 +536,10 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const Bgt
             }
             const bool pair = sbits_of[s] <= 4;
             const uint32_t entries = pair ? 1u << (2 * sbits_of[s]) : 1u << bw;
-            // Replication per table: pair tables of the bit-packed layout may fill 8 KB (3-bit pairs get one
-            // copy per lane and never conflict); single-code tables serve few dims and stay within 2 KB;
-            // the nibble layout has up to four 256-entry pair tables and keeps them at 4 KB each.
-            const uint32_t cap_bytes = !pair ? 2048u : ((flags & BGTQ_DEC_K_MIXED) ? 4096u : kLutTableBytes);
+            // Replication per table: as many per-lane copies as fit in kLutTableBytes.  (8 KB tables, which make
+            // the 3-bit pair tables conflict-free, measured under 1 % faster and push some layers past the
+            // shared-memory budget of two resident CTAs.)
+            const uint32_t cap_bytes = kLutTableBytes;
             uint32_t rep = cap_bytes / 4 / entries;
             rep = rep < 1 ? 1 : (rep > 32 ? 32 : rep);
             DecSegTbl& tb = hp.seg[s];

@@ -18,7 +18,7 @@ namespace bgtq {
 
 constexpr int kMaxSteps = 16;        // MMA k-tiles per token tile: at most 8 + 7 per head
 constexpr int kMaxPlanHeads = 8;     // KV heads per launch
-constexpr uint32_t kLutTableBytes = 8192;  // largest lookup table incl. lane replication (and alignment of the region)
+constexpr uint32_t kLutTableBytes = 4096;  // size cap (and alignment) of one lookup table incl. lane replication
 
 // One lookup table (= one K width segment).
 struct DecSegTbl {
