@@ -4,7 +4,7 @@ Run once, in a container where the reference checkout is available:
 
     TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/reference [manager]
 
-(a second argument, ``manager`` or ``production``, regenerates only that fixture; each has its own seed)
+(a second argument, ``manager``, ``production`` or ``prefill``, regenerates only that fixture; each has its own seed)
 
 The reference's Triton kernels are executed by Triton's CPU interpreter
 (``tl.dot`` is a float32 ``np.matmul`` there), so the vectors are the
@@ -24,7 +24,9 @@ import os
 import sys
 
 os.environ.setdefault("TRITON_INTERPRET", "1")
-ref_path = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py <path to a checkout of the reference> [manager|production|prefill]")
+ref_path = sys.argv[1]
 sys.path.insert(0, ref_path)
 
 import numpy as np  # noqa: E402
