@@ -521,3 +521,60 @@ def test_prefill_attention_mixed_layout_matches_decode_kernel():
         ref, _, _ = combine(po, pl, n_kv, v_rot=lt.v_rot)
         torch.cuda.synchronize()
         assert (out[:, :, i].float() - ref.float()).abs().max().item() <= ATOL
+
+
+def test_bulk_encoder_rows_that_wrap_batches():
+    """Tensor-core path with a token count that is not a multiple of the 16-row slab: slabs span two
+    batch entries and take the per-row store path; must equal the fp32 kernel's bytes off bin edges."""
+    from blockgtq_b200 import _lib
+    from blockgtq_b200.layer import encode
+    lt, tabs = _layer("a2_1to8")
+    gen = torch.Generator().manual_seed(808)
+    B, n_kv, S = 7, 2, 19
+    k = torch.stack([torch.stack([synth_head(gen, S, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
+    v = torch.randn(B, n_kv, S, HD, generator=gen).half().to(DEV)
+    outs = []
+    for extra in (0, _lib.ENC_FORCE_SIMT):
+        kp = torch.zeros(B, n_kv, S + 4, lt.max_tpb, dtype=torch.uint8, device=DEV)
+        kn = torch.zeros(B, n_kv, S + 4, lt.max_ng, dtype=torch.float16, device=DEV)
+        vp = torch.zeros(B, n_kv, S + 4, lt.vpb, dtype=torch.uint8, device=DEV)
+        vn = torch.zeros(B, n_kv, S + 4, dtype=torch.float16, device=DEV)
+        kc = torch.zeros(B, n_kv, S, HD, dtype=torch.uint8, device=DEV)
+        encode(lt, k, v, 2, kp, kn, vp, vn, flags=extra, k_codes=kc)
+        torch.cuda.synchronize()
+        outs.append((kp.cpu().numpy(), kn.cpu().numpy(), vp.cpu().numpy(), vn.cpu().numpy(), kc.cpu().numpy()))
+    a, b = outs
+    assert (a[4] != b[4]).mean() < 2e-3
+    if np.array_equal(a[4], b[4]):
+        assert np.array_equal(a[0], b[0])
+    assert (a[2] != b[2]).mean() < 2e-3
+    np.testing.assert_allclose(a[1].astype(np.float32), b[1].astype(np.float32), rtol=2e-3, atol=1e-6)
+    for h in range(n_kv):
+        for bb in range(B):
+            assert np.array_equal(a[0][bb, h, 2:2 + S], O.pack_k(a[4][bb, h], tabs[h][0].segments, lt.max_tpb))
+    assert (a[0][:, :, :2] == 0).all() and (a[0][:, :, 2 + S:] == 0).all()
+
+
+@pytest.mark.parametrize("gqa,S_q,offset", [(1, 1, 300), (1, 130, 0), (8, 1, 0)])
+def test_prefill_attention_edge_shapes(gqa, S_q, offset):
+    """Single query, MHA (one query head per KV head), and more positions than one CTA holds."""
+    from blockgtq_b200.layer import combine, decode, encode, prefill_attention, rotate_q_bulk
+    lt, tabs = _layer("a3_1to6")
+    gen = torch.Generator().manual_seed(99)
+    B, n_kv = 1, 2
+    n_q, T = n_kv * gqa, offset + S_q
+    k = torch.stack([torch.stack([synth_head(gen, T, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
+    q = (torch.randn(B, n_q, S_q, HD, generator=gen) * 2).half().to(DEV)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half().to(DEV)
+    kp = torch.zeros(B, n_kv, T + 1, lt.max_tpb, dtype=torch.uint8, device=DEV)
+    kn = torch.zeros(B, n_kv, T + 1, lt.max_ng, dtype=torch.float16, device=DEV)
+    vp = torch.zeros(B, n_kv, T + 1, lt.vpb, dtype=torch.uint8, device=DEV)
+    vn = torch.zeros(B, n_kv, T + 1, dtype=torch.float16, device=DEV)
+    encode(lt, k, v, 0, kp, kn, vp, vn)
+    q_rot = rotate_q_bulk(lt, q)
+    out = prefill_attention(lt, q_rot, kp, kn, vp, vn, T, q_pos_offset=offset, causal=True, v_rot=lt.v_rot)
+    for i in sorted({0, S_q // 2, S_q - 1}):
+        po, pl = decode(lt, q_rot[:, :, i].contiguous(), kp, kn, vp, vn, 0, offset + i + 1, n_splits=2)
+        ref, _, _ = combine(po, pl, n_kv, v_rot=lt.v_rot)
+        torch.cuda.synchronize()
+        assert (out[:, :, i].float() - ref.float()).abs().max().item() <= ATOL
