@@ -57,6 +57,12 @@ struct DecParams {
     float* part_o;
     float* part_lse;
     int32_t* status;
+    // fused merge (optional): the last CTA of each (batch, KV head) to finish merges that pair's partials,
+    // applies V's rotation and writes the fp16 result, so no combine launch follows
+    int32_t* tickets;
+    const float* v_rot;
+    __half* out;
+    int64_t o_sb, o_sh;
     uint32_t stage_off, stage_bytes, off_kn, off_v, off_vn;  // shared-memory layout
     DecPlanDev plan;
 };
@@ -491,6 +497,69 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
                 P.part_lse[row] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -INFINITY;
         }
     }
+    if (P.tickets == nullptr) return;
+
+    // ---------------- fused merge: the pair's last CTA combines all splits ----------------
+    // Every CTA publishes its partial (fence), then takes a ticket; the one that draws the last ticket
+    // knows all other partials are visible in L2 and reads them with cache-global loads.
+    __threadfence();
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+    int* flag = reinterpret_cast<int*>(mm);           // the merge scratch is free again
+    if (tid == 0) {
+        const int t = atomicAdd(P.tickets + b * P.n_kv + h, 1);
+        *flag = (t == (int)gridDim.x - 1) ? 1 : 0;
+        if (t == (int)gridDim.x - 1) P.tickets[b * P.n_kv + h] = 0;      // ready for the next launch
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+    if (*flag == 0) return;
+    __threadfence();
+    {
+        const int q = tid >> 5, d0 = (tid & 31) * 4;        // one warp per query head, four dims per lane
+        float* merged = mo;                                   // [8][kHD] merged partial, V's rotated basis
+        const int n_sp = (int)gridDim.x;
+        if (q < P.gqa) {
+            const size_t row = (size_t)b * P.n_q + (size_t)h * P.gqa + q;
+            const float* lse = P.part_lse + row * n_sp;
+            float mx = -INFINITY;
+#pragma unroll 8
+            for (int s = 0; s < n_sp; ++s) mx = fmaxf(mx, __ldcg(lse + s));
+            float den = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+            if (mx > -INFINITY) {
+#pragma unroll 8
+                for (int s = 0; s < n_sp; ++s) {
+                    const float l = __ldcg(lse + s);
+                    if (l == -INFINITY) continue;
+                    const float a = expf(l - mx);
+                    den += a;
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(P.part_o + (row * n_sp + s) * kHD + d0));
+                    o[0] = fmaf(a, v.x, o[0]); o[1] = fmaf(a, v.y, o[1]);
+                    o[2] = fmaf(a, v.z, o[2]); o[3] = fmaf(a, v.w, o[3]);
+                }
+            }
+            const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) merged[q * kHD + d0 + i] = o[i] * inv;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+        if (q < P.gqa) {
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
+            if (P.v_rot) {
+                const float* R = P.v_rot + (size_t)h * kHD * kHD + d0;
+#pragma unroll 32
+                for (int i = 0; i < kHD; ++i) {
+                    const float4 rr = __ldg(reinterpret_cast<const float4*>(R + (size_t)i * kHD));
+                    const float m = merged[q * kHD + i];
+                    o[0] = fmaf(m, rr.x, o[0]); o[1] = fmaf(m, rr.y, o[1]);
+                    o[2] = fmaf(m, rr.z, o[2]); o[3] = fmaf(m, rr.w, o[3]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[i] = merged[q * kHD + d0 + i];
+            }
+            __half* dst = P.out + b * P.o_sb + ((int64_t)h * P.gqa + q) * P.o_sh + d0;
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_half2(o[0], o[1]), pack_half2(o[2], o[3]));
+        }
+    }
 }
 
 constexpr uint32_t v_rep_shift_for(int vb) { return vb <= 2 ? 5 : (vb == 3 ? 4 : 2); }
@@ -638,13 +707,13 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_default_splits
     return (int)best;
 }
 
-extern "C" __attribute__((visibility("default"))) int bgtq_decode(
+static int decode_impl(
     const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot, const uint8_t* k_packed,
     int64_t kp_sb, int64_t kp_sh, int64_t kp_st, const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
     const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, const void* v_norms, int64_t vn_sb,
     int64_t vn_sh, int64_t vn_st, int32_t n_batch, int32_t n_q, int32_t n_kv, int32_t t_begin, int32_t t_end,
     int32_t n_splits, float scale, float* part_o, float* part_lse, int32_t* status, const int32_t* pos_dev,
-    int32_t pos_add, void* stream) {
+    int32_t pos_add, void* stream, int32_t* tickets, const float* v_rot, void* out, int64_t o_sb, int64_t o_sh) {
     if (!plan_host || !desc || !q_rot || !k_packed || !k_norms || !v_packed || !v_norms || !part_o || !part_lse)
         return BGTQ_E_BADARG;
     if (n_batch < 1 || n_kv < 1 || n_q < n_kv || n_q % n_kv || n_splits < 1 || t_end < t_begin || t_begin < 0)
@@ -681,6 +750,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode(
     P.scale_log2 = scale * 1.4426950408889634f;
     P.part_o = part_o; P.part_lse = part_lse; P.status = status;
     P.pos_dev = pos_dev; P.pos_add = pos_add;
+    P.tickets = tickets; P.v_rot = v_rot; P.out = static_cast<__half*>(out); P.o_sb = o_sb; P.o_sh = o_sh;
 
     auto r16 = [](uint32_t x) { return (x + 15u) & ~15u; };
     // each array: one tile of rows + 15 bytes of leading phase + rounding + slack for the bit-field over-read
@@ -707,6 +777,33 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode(
     dim3 grid(n_splits, n_kv, n_batch);
     return launch_kernel(kern, grid, dim3(kThreads), smem, static_cast<cudaStream_t>(stream),
                          (P.plan.flags & BGTQ_DEC_PROGRAMMATIC) != 0, P) == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_decode(
+    const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot, const uint8_t* k_packed,
+    int64_t kp_sb, int64_t kp_sh, int64_t kp_st, const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
+    const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, const void* v_norms, int64_t vn_sb,
+    int64_t vn_sh, int64_t vn_st, int32_t n_batch, int32_t n_q, int32_t n_kv, int32_t t_begin, int32_t t_end,
+    int32_t n_splits, float scale, float* part_o, float* part_lse, int32_t* status, const int32_t* pos_dev,
+    int32_t pos_add, void* stream) {
+    return decode_impl(plan_host, desc, q_rot, k_packed, kp_sb, kp_sh, kp_st, k_norms, kn_sb, kn_sh, kn_st, v_packed,
+                       vp_sb, vp_sh, vp_st, v_norms, vn_sb, vn_sh, vn_st, n_batch, n_q, n_kv, t_begin, t_end, n_splits,
+                       scale, part_o, part_lse, status, pos_dev, pos_add, stream, nullptr, nullptr, nullptr, 0, 0);
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_fused(
+    const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot, const uint8_t* k_packed,
+    int64_t kp_sb, int64_t kp_sh, int64_t kp_st, const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
+    const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, const void* v_norms, int64_t vn_sb,
+    int64_t vn_sh, int64_t vn_st, int32_t n_batch, int32_t n_q, int32_t n_kv, int32_t t_begin, int32_t t_end,
+    int32_t n_splits, float scale, float* part_o, float* part_lse, int32_t* status, const int32_t* pos_dev,
+    int32_t pos_add, const float* v_rot, void* out, int64_t o_sb, int64_t o_sh, int32_t* tickets, void* stream) {
+    if (!out || !tickets) return BGTQ_E_BADARG;
+    if ((reinterpret_cast<uintptr_t>(out) & 7u) || (o_sb & 3) || (o_sh & 3) || (reinterpret_cast<uintptr_t>(v_rot) & 15u))
+        return BGTQ_E_ALIGN;
+    return decode_impl(plan_host, desc, q_rot, k_packed, kp_sb, kp_sh, kp_st, k_norms, kn_sb, kn_sh, kn_st, v_packed,
+                       vp_sb, vp_sh, vp_st, v_norms, vn_sb, vn_sh, vn_st, n_batch, n_q, n_kv, t_begin, t_end, n_splits,
+                       scale, part_o, part_lse, status, pos_dev, pos_add, stream, tickets, v_rot, out, o_sb, o_sh);
 }
 
 // ---------------------------------------------------------------------------

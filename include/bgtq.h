@@ -215,6 +215,26 @@ int bgtq_decode(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const
                 float* part_o, float* part_lse, int32_t* status,
                 const int32_t* pos_dev, int32_t pos_add, void* stream);
 
+/* bgtq_decode with the split merge folded into the same launch: the last CTA of every (batch, KV head)
+ * to finish (a ticket counter per pair) merges that pair's partials, applies V's rotation
+ * (v_rot: (n_kv,128,128) fp32 = R, may be NULL) and writes fp16 out (n_batch, n_q, 128) at
+ * out + b*o_sb + hq*o_sh (8-byte aligned rows) -- the work of bgtq_combine without its launch, for steps
+ * with no fp16-buffer partial to fold in.  part_o / part_lse are still required (scratch).  It saves a
+ * launch; inside a programmatic chain the separate bgtq_combine overlaps the decode tail and is as fast.
+ * tickets: n_batch * n_kv int32, ZERO before the first use; every launch leaves them zero again, so one
+ * buffer serves all layers of a stream.  Two launches that may overlap on the GPU need separate
+ * tickets and partial buffers. */
+int bgtq_decode_fused(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot,
+                const uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
+                const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
+                const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
+                const void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
+                int32_t n_batch, int32_t n_q, int32_t n_kv,
+                int32_t t_begin, int32_t t_end, int32_t n_splits, float scale,
+                float* part_o, float* part_lse, int32_t* status,
+                const int32_t* pos_dev, int32_t pos_add,
+                const float* v_rot, void* out, int64_t o_sb, int64_t o_sh, int32_t* tickets, void* stream);
+
 /* Attention of the same queries over tokens kept unquantised in fp16 (the
  * sink prefix and the recent window of the three-region cache policy,
  * blockgtq/unaccelerated.py:163-244; the reference has no packed-path kernel

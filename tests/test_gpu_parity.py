@@ -578,3 +578,33 @@ def test_prefill_attention_edge_shapes(gqa, S_q, offset):
         ref, _, _ = combine(po, pl, n_kv, v_rot=lt.v_rot)
         torch.cuda.synchronize()
         assert (out[:, :, i].float() - ref.float()).abs().max().item() <= ATOL
+
+
+@pytest.mark.parametrize("gqa,T,n_splits", [(4, 1000, 5), (8, 300, 3), (2, 64, 1)])
+def test_fused_decode_merge_matches_decode_plus_combine(gqa, T, n_splits):
+    """bgtq_decode_fused (last CTA of each pair merges, rotates and stores) against bgtq_decode +
+    bgtq_combine, three launches in a row on one ticket buffer (the kernel must leave it zeroed)."""
+    from blockgtq_b200.layer import combine, decode, encode, rotate_q
+    lt, tabs = _layer("a3_1to8")
+    gen = torch.Generator().manual_seed(4242 + T)
+    B, n_kv = 3, 2
+    n_q = n_kv * gqa
+    k = torch.stack([torch.stack([synth_head(gen, T, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half().to(DEV)
+    kp = torch.zeros(B, n_kv, T + 8, lt.max_tpb, dtype=torch.uint8, device=DEV)
+    kn = torch.zeros(B, n_kv, T + 8, lt.max_ng, dtype=torch.float16, device=DEV)
+    vp = torch.zeros(B, n_kv, T + 8, lt.vpb, dtype=torch.uint8, device=DEV)
+    vn = torch.zeros(B, n_kv, T + 8, dtype=torch.float16, device=DEV)
+    encode(lt, k, v, 0, kp, kn, vp, vn)
+    tickets = torch.zeros(B * n_kv, dtype=torch.int32, device=DEV)
+    for rep in range(3):
+        q = (torch.randn(B, n_q, HD, generator=gen) * 2).half().to(DEV)
+        q_rot = rotate_q(lt, q)
+        po, pl = decode(lt, q_rot, kp, kn, vp, vn, 0, T, n_splits=n_splits)
+        ref, _, _ = combine(po, pl, n_kv, v_rot=lt.v_rot)
+        out = torch.full((B, n_q, HD), float("nan"), dtype=torch.float16, device=DEV)
+        decode(lt, q_rot, kp, kn, vp, vn, 0, T, n_splits=n_splits, fused_out=out, tickets=tickets, v_rot=lt.v_rot)
+        torch.cuda.synchronize()
+        assert (tickets == 0).all()
+        assert torch.isfinite(out).all()
+        assert (out.float() - ref.float()).abs().max().item() <= 1e-3
