@@ -6,7 +6,7 @@ import torch
 
 from .quantizer import BlockGTQQuantizer, build_batched_encode_args
 
-__all__ = ["collect_qk_activations", "build_quantizers", "bake_q_rotations"]
+__all__ = ["collect_qk_activations", "build_quantizers", "bake_q_rotations", "save_calib_cache", "load_calib_cache"]
 
 
 @torch.no_grad()
@@ -81,3 +81,30 @@ def bake_q_rotations(model, quantizers, n_layers, nkv, nq):
             quantizers[li][hi].bake_permutation_into_qproj(
                 attn.q_proj.weight.data, kv_head_idx=hi, n_kv_heads=nkv, n_q_heads=nq,
                 q_proj_bias=getattr(attn.q_proj, "bias", None))
+
+
+def save_calib_cache(path, layer_data, model_name="", arch="llama", source="", score="energy"):
+    """Write the collected activations in the reference's calib-cache layout
+    (examples/build_calib_cache.py:282-298): one ``torch.save`` payload with ``calib_k``
+    (n_layer, n_kv, T, hd), ``calib_q`` (n_layer, n_kv, gqa*T, hd) and the shape metadata."""
+    n_layer = len(layer_data)
+    k0, q0 = layer_data[0]["k"], layer_data[0]["q"]
+    n_kv, T, hd = k0.shape
+    calib_k = torch.stack([layer_data[li]["k"].detach().cpu() for li in range(n_layer)])
+    calib_q = torch.stack([layer_data[li]["q"].detach().cpu() for li in range(n_layer)])
+    q_per_kv = q0.shape[1] // T
+    payload = {"calib_k": calib_k, "calib_q": calib_q, "model": model_name, "arch": arch, "n_tokens": T,
+               "head_dim": hd, "n_kv": n_kv, "n_q": n_kv * q_per_kv, "n_layer": n_layer, "q_per_kv": q_per_kv,
+               "n_samples_q": q0.shape[1], "q_convention": "all_heads_per_kv_group", "source": source, "score": score}
+    torch.save(payload, path)
+    return payload
+
+
+def load_calib_cache(path, device="cpu"):
+    """Read a calib cache (this module's or the reference's) back into the ``layer_data`` form
+    :func:`build_quantizers` takes: ``{layer: {'q': (n_kv, gqa*T, hd), 'k': (n_kv, T, hd)}}``."""
+    ck = torch.load(path, map_location="cpu", weights_only=False)
+    ks, qs = ck["calib_k"], ck["calib_q"]
+    if ks.dim() != 4 or qs.dim() != 4 or ks.shape[:2] != qs.shape[:2] or ks.shape[3] != qs.shape[3]:
+        raise ValueError(f"not a calib cache: calib_k {tuple(ks.shape)}, calib_q {tuple(qs.shape)}")
+    return {li: {"k": ks[li].to(device), "q": qs[li].to(device)} for li in range(ks.shape[0])}
