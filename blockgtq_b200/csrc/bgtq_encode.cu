@@ -265,7 +265,19 @@ struct PrepParams {
     int64_t q_sb, q_sh;
     __half* q_rot;
     int32_t n_q, do_rot;
+    const __half* rope_cos;   // optional (n_batch, 128) fp16 tables of the step's position: q and k arrive pre-RoPE
+    const __half* rope_sin;
+    int64_t rope_sb;
 };
+
+// Element `dim` of a row after rotary embedding in the split-half convention, with the rounding points of
+// the fp16 reference expression (x * cos) + (rotate_half(x) * sin): two rounded products, one rounded sum.
+__device__ __forceinline__ float rope_element(const __half* row, int dim, const __half* cs, const __half* sn) {
+    const __half x = row[dim];
+    if (cs == nullptr) return __half2float(x);
+    const __half xr = dim < kHD / 2 ? __hneg(row[dim + kHD / 2]) : row[dim - kHD / 2];
+    return __half2float(__hadd_rn(__hmul_rn(x, cs[dim]), __hmul_rn(xr, sn[dim])));
+}
 
 __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     __shared__ float xs[kHD];
@@ -303,8 +315,10 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     float x = 0.f;
     int g = 0;
     if (c == 0) {
-        if (kind == 0) x = __half2float(P.q[b * P.q_sb + hq * P.q_sh + d.head_perm[p]]);
-        else if (kind == 1) x = __half2float(E.k[b * E.k_sb + h * E.k_sh + d.head_perm[p]]);
+        const __half* cs = P.rope_cos ? P.rope_cos + b * P.rope_sb : nullptr;
+        const __half* sn = P.rope_cos ? P.rope_sin + b * P.rope_sb : nullptr;
+        if (kind == 0) x = rope_element(P.q + b * P.q_sb + hq * P.q_sh, d.head_perm[p], cs, sn);
+        else if (kind == 1) x = rope_element(E.k + b * E.k_sb + h * E.k_sh, d.head_perm[p], cs, sn);
         else x = __half2float(E.v[b * E.v_sb + h * E.v_sh + p]);
         xs[p] = x;
         g = d.group_of[p];
@@ -476,13 +490,14 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 
-extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare(
+static int step_prepare_impl(
     const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v, const void* q, int64_t q_sb, int64_t q_sh,
     void* q_rot, int32_t n_q, const void* k, int64_t k_sb, int64_t k_sh, const void* v, int64_t v_sb, int64_t v_sh,
     int32_t n_batch, int32_t n_kv, int32_t t0, uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
     int32_t kp_row_bytes, void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
     uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
-    int64_t vn_st, int32_t flags, const int32_t* pos_dev, void* stream) {
+    int64_t vn_st, int32_t flags, const int32_t* pos_dev, void* stream, const void* rope_cos, const void* rope_sin,
+    int64_t rope_sb) {
     if (!desc || !rot_k || !rot_v || !k || !v || !k_packed || !k_norms || !v_packed || !v_norms) return BGTQ_E_BADARG;
     if (n_batch < 1 || n_kv < 1 || t0 < 0 || kp_row_bytes < 1 || kp_row_bytes > kHD || kn_count < 1 ||
         kn_count > BGTQ_MAX_SEGMENTS)
@@ -502,8 +517,35 @@ extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare(
     E.k_codes = nullptr; E.v_codes = nullptr; E.flags = flags;
     P.q = static_cast<const __half*>(q); P.q_sb = q_sb; P.q_sh = q_sh; P.q_rot = static_cast<__half*>(q_rot);
     P.n_q = n_q; P.do_rot = do_rot ? 1 : 0;
+    P.rope_cos = static_cast<const __half*>(rope_cos); P.rope_sin = static_cast<const __half*>(rope_sin);
+    P.rope_sb = rope_sb;
     const int64_t items = (int64_t)(do_rot ? n_batch * n_q : 0) + 2LL * n_batch * n_kv;
     if (items > 0x7fffffffLL) return BGTQ_E_TOOBIG;
     return launch_kernel(prep_kernel, dim3((unsigned)items), dim3(512), 0, static_cast<cudaStream_t>(stream),
                          (flags & BGTQ_ENC_PROGRAMMATIC) != 0, P) == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare(
+    const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v, const void* q, int64_t q_sb, int64_t q_sh,
+    void* q_rot, int32_t n_q, const void* k, int64_t k_sb, int64_t k_sh, const void* v, int64_t v_sb, int64_t v_sh,
+    int32_t n_batch, int32_t n_kv, int32_t t0, uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
+    int32_t kp_row_bytes, void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
+    uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
+    int64_t vn_st, int32_t flags, const int32_t* pos_dev, void* stream) {
+    return step_prepare_impl(desc, rot_k, rot_v, q, q_sb, q_sh, q_rot, n_q, k, k_sb, k_sh, v, v_sb, v_sh, n_batch, n_kv, t0, k_packed,
+                             kp_sb, kp_sh, kp_st, kp_row_bytes, k_norms, kn_sb, kn_sh, kn_st, kn_count, v_packed, vp_sb, vp_sh,
+                             vp_st, v_norms, vn_sb, vn_sh, vn_st, flags, pos_dev, stream, nullptr, nullptr, 0);
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare_rope(
+    const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v, const void* q, int64_t q_sb, int64_t q_sh,
+    void* q_rot, int32_t n_q, const void* k, int64_t k_sb, int64_t k_sh, const void* v, int64_t v_sb, int64_t v_sh,
+    int32_t n_batch, int32_t n_kv, int32_t t0, uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
+    int32_t kp_row_bytes, void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
+    uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
+    int64_t vn_st, int32_t flags, const int32_t* pos_dev, const void* rope_cos, const void* rope_sin, int64_t rope_sb, void* stream) {
+    if (!rope_cos || !rope_sin) return BGTQ_E_BADARG;
+    return step_prepare_impl(desc, rot_k, rot_v, q, q_sb, q_sh, q_rot, n_q, k, k_sb, k_sh, v, v_sb, v_sh, n_batch, n_kv, t0, k_packed,
+                             kp_sb, kp_sh, kp_st, kp_row_bytes, k_norms, kn_sb, kn_sh, kn_st, kn_count, v_packed, vp_sb, vp_sh,
+                             vp_st, v_norms, vn_sb, vn_sh, vn_st, flags, pos_dev, stream, rope_cos, rope_sin, rope_sb);
 }

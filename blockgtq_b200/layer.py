@@ -176,9 +176,11 @@ def rotate_q_bulk(layer: LayerTables, q: torch.Tensor) -> torch.Tensor:
 
 
 def step_prepare(layer: LayerTables, q, k, v, t0, k_packed, k_norms, v_packed, v_norms, *, q_rot=None,
-                 flags=0, pos_dev=None):
+                 flags=0, pos_dev=None, rope=None):
     """Rotate q (B, n_q, [1,] 128) into ``q_rot`` and append one token k/v (B, n_kv, 1, 128) at slot
-    ``t0`` (or ``*pos_dev``) of the cache tensors, in one launch.  ``q=None`` skips the rotation."""
+    ``t0`` (or ``*pos_dev``) of the cache tensors, in one launch.  ``q=None`` skips the rotation.
+    ``rope=(cos, sin)``, each fp16 (B, 128) (or (B, 1, 128)): q and k are pre-RoPE and the kernel applies
+    the rotary embedding of the step's position first (``bgtq_step_prepare_rope``)."""
     _lib.require_cuda(k, "k")
     B, H, S, D = k.shape
     if S != 1 or H != layer.n_kv or D != HD or v.shape != k.shape:
@@ -200,13 +202,20 @@ def step_prepare(layer: LayerTables, q, k, v, t0, k_packed, k_norms, v_packed, v
         qa = (_lib.ptr(q), q.stride(0), q.stride(1))
     kps, kns, vps = _strides3(k_packed), _strides3(k_norms), _strides3(v_packed)
     vns = (v_norms.stride(0), v_norms.stride(1), v_norms.stride(2))
-    _lib.check(_lib.lib().bgtq_step_prepare(
-        _lib.ptr(layer.desc_dev), _lib.ptr(layer.rot_k), _lib.ptr(layer.rot_v), *qa,
-        _lib.ptr(q_rot) if q is not None else 0, n_q,
-        _lib.ptr(k), k.stride(0), k.stride(1), _lib.ptr(v), v.stride(0), v.stride(1), B, H, int(t0),
-        _lib.ptr(k_packed), *kps, k_packed.shape[3], _lib.ptr(k_norms), *kns, k_norms.shape[3],
-        _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns, flags, _lib.ptr(pos_dev),
-        _lib.stream_ptr(k.device)), "bgtq_step_prepare")
+    common = (_lib.ptr(layer.desc_dev), _lib.ptr(layer.rot_k), _lib.ptr(layer.rot_v), *qa,
+              _lib.ptr(q_rot) if q is not None else 0, n_q,
+              _lib.ptr(k), k.stride(0), k.stride(1), _lib.ptr(v), v.stride(0), v.stride(1), B, H, int(t0),
+              _lib.ptr(k_packed), *kps, k_packed.shape[3], _lib.ptr(k_norms), *kns, k_norms.shape[3],
+              _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns, flags, _lib.ptr(pos_dev))
+    if rope is not None:
+        cos, sin = (t.reshape(B, HD) for t in rope)
+        if cos.dtype != torch.float16 or sin.dtype != torch.float16 or cos.stride(1) != 1 or sin.stride(1) != 1 \
+                or cos.stride(0) != sin.stride(0):
+            raise TypeError("rope tables must be float16 (B, 128) with equal row strides")
+        _lib.check(_lib.lib().bgtq_step_prepare_rope(*common, _lib.ptr(cos), _lib.ptr(sin), cos.stride(0),
+                                                     _lib.stream_ptr(k.device)), "bgtq_step_prepare_rope")
+    else:
+        _lib.check(_lib.lib().bgtq_step_prepare(*common, _lib.stream_ptr(k.device)), "bgtq_step_prepare")
     _lib.count_launch()
     return q_rot
 

@@ -77,7 +77,7 @@ class BlockGTQKVManager:
         self._use_graph = (not self._buffered) if use_cuda_graph is None else bool(use_cuda_graph)
         if self._use_graph and self._buffered:
             raise ValueError("CUDA-graph replay is not available with fp16 sink/recent buffers")
-        self._graphs = [None] * n_layers
+        self._graphs = [dict() for _ in range(n_layers)]      # per layer: {rope fused or not: CUDA graph}
         self._g_qkv = self._g_out = self._pos = None
 
     @property
@@ -143,6 +143,7 @@ class BlockGTQKVManager:
         self._g_out = torch.zeros(self.n_layers, self.B, self.n_q, self.hd, dtype=torch.float16, device=dev)
         self._pos = torch.zeros(1, dtype=torch.int32, device=dev)
         self._tickets = torch.zeros(self.B * self.n_kv, dtype=torch.int32, device=dev)
+        self._g_rope = torch.zeros(2, self.B, self.hd, dtype=torch.float16, device=dev)     # cos, sin of the step
         if self._buffered:
             self._k_buf = torch.zeros(self.n_layers, self.B, self.n_kv, self._buf_cap, self.hd,
                                       dtype=torch.float16, device=dev)
@@ -258,7 +259,7 @@ class BlockGTQKVManager:
             self._pos.fill_(self._seq_len)
             self._pos_dirty = False
 
-    def _layer_step(self, li: int):
+    def _layer_step(self, li: int, rope: bool = False):
         """rotate_q -> append K,V at *pos -> decode over [0, *pos + 1) -> combine, all on static buffers."""
         lt = self._layers[li]
         gq, gk, gv = self.static_inputs()
@@ -271,7 +272,8 @@ class BlockGTQKVManager:
         if ex is None or ex.is_owner:
             step_prepare(lt, None if baked else gq, gk, gv, 0, self._k_packed[li], self._k_norms[li],
                          self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos,
-                         flags=self._enc_flags | (_lib.ENC_PROGRAMMATIC if pd else 0))
+                         flags=self._enc_flags | (_lib.ENC_PROGRAMMATIC if pd else 0),
+                         rope=(self._g_rope[0], self._g_rope[1]) if rope else None)
         elif not baked:                           # this rank does not hold the tail: nothing to append
             rotate_q(lt, gq[:, :, 0], out=self._q_rot)
         decode(lt, q_rot, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
@@ -291,7 +293,7 @@ class BlockGTQKVManager:
             ex.all_gather()
             combine_ranks(ex.gathered, self.B, self.n_q, out=self._g_out[li])
 
-    def _replay_layer(self, li: int, q, k_new, v_new) -> torch.Tensor:
+    def _replay_layer(self, li: int, q, k_new, v_new, rope=None) -> torch.Tensor:
         self._ensure_storage()
         if self._seq_len + 1 > self.max_T:
             raise ValueError("cache overflow")
@@ -303,14 +305,18 @@ class BlockGTQKVManager:
             gk.copy_(k_new)
         if v_new.data_ptr() != gv.data_ptr():
             gv.copy_(v_new)
-        g = self._graphs[li]
+        use_rope = rope is not None
+        if use_rope:
+            self._g_rope[0].copy_(rope[0].reshape(self.B, self.hd))
+            self._g_rope[1].copy_(rope[1].reshape(self.B, self.hd))
+        g = self._graphs[li].get(use_rope)
         if g is None:
-            self._layer_step(li)                      # eager once: sets kernel attributes, validates shapes
+            self._layer_step(li, use_rope)            # eager once: sets kernel attributes, validates shapes
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                self._layer_step(li)
-            self._graphs[li] = g
+                self._layer_step(li, use_rope)
+            self._graphs[li][use_rope] = g
         else:
             g.replay()
             _lib.count_launch(2 if (self._exchange is None and self.fused_merge) else (5 if self._exchange else 3))
@@ -319,12 +325,16 @@ class BlockGTQKVManager:
     # -- decode ----------------------------------------------------------------------------
     @torch.no_grad()
     def append_and_attend(self, layer_idx: int, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
-                          n_splits: int = None) -> torch.Tensor:
+                          n_splits: int = None, rope=None) -> torch.Tensor:
         """Quantise and append (B, n_kv, S, hd) K/V, then attend the (B, n_q, 1, hd) query over the
-        whole cache.  Returns (B, n_q, 1, hd) fp16 (packed_kv_manager.py:268-348)."""
+        whole cache.  Returns (B, n_q, 1, hd) fp16 (packed_kv_manager.py:268-348).
+        ``rope=(cos, sin)`` (fp16, (B, [1,] hd), single-token steps): q and k_new are pre-RoPE and the append
+        kernel applies the rotary embedding itself (an extension; the reference's callers rotate first)."""
         t, S = self.seq_len, k_new.shape[2]
         if self._use_graph and S == 1 and n_splits is None and q.is_cuda:
-            return self._replay_layer(layer_idx, q, k_new, v_new).unsqueeze(2)
+            return self._replay_layer(layer_idx, q, k_new, v_new, rope).unsqueeze(2)
+        if rope is not None:
+            raise NotImplementedError("fused RoPE is available on the single-token graph path only")
         defer = self._buffered and S == 1
         f0, f1 = self._append_tokens(layer_idx, k_new, v_new, t, defer_flush=defer)
         out, _, _ = self.attend(layer_idx, q, t + S, n_splits=n_splits, flushed=f0 if defer else None)

@@ -64,10 +64,17 @@ class BlockGTQProductionCache:
         self._mgr._encode_kv(layer_idx, k, v, t_pos, t_pos + 1)
 
     @torch.no_grad()
-    def encode_and_attend(self, layer_idx, q, k, v):
+    def encode_and_attend(self, layer_idx, q, k, v, rope=None):
         """Encode the new (B, n_kv, S, hd) K/V and attend the (B, n_q, 1, hd) query: -> (B, n_q, 1, hd) fp16
-        (production_cache.py:207-264)."""
-        return self._mgr.append_and_attend(layer_idx, q, k, v)
+        (production_cache.py:207-264).  ``rope=(cos, sin)``: q and k are pre-RoPE, see
+        :meth:`BlockGTQKVManager.append_and_attend`."""
+        return self._mgr.append_and_attend(layer_idx, q, k, v, rope=rope)
+
+    @property
+    def can_fuse_rope(self) -> bool:
+        """Single-token steps can take pre-RoPE q/k (graph path, rotations not baked into q_proj)."""
+        m = self._mgr
+        return m._use_graph and not any(qz._q_perm_baked for row in m.quantizers for qz in row if qz is not None)
 
     def increment_seq_len(self, by=1):
         self._mgr.increment_seq_len(by)

@@ -25,8 +25,11 @@ def production_decode_step(model, input_ids, position_ids, cache):
         v = attn.v_proj(hidden).view(B, S, cache.nkv, cache.hd).transpose(1, 2)
         rope = getattr(attn, "rotary_emb", None) or model.model.rotary_emb
         cos, sin = rope(v, position_ids)
-        q, k = apply_rotary_pos_emb(q, k, cos, sin)
-        out = cache.encode_and_attend(li, q, k, v)
+        if S == 1 and q.dtype == torch.float16 and getattr(cache, "can_fuse_rope", False):
+            out = cache.encode_and_attend(li, q, k, v, rope=(cos, sin))     # rotary embedding inside the append kernel
+        else:
+            q, k = apply_rotary_pos_emb(q, k, cos, sin)
+            out = cache.encode_and_attend(li, q, k, v)
         out = out.transpose(1, 2).reshape(B, S, cache.nq * cache.hd).to(hidden.dtype)
         hidden = resid + attn.o_proj(out)
         resid = hidden

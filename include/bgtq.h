@@ -161,6 +161,25 @@ int bgtq_step_prepare(const BgtqHeadDesc* desc, const float* rot_k, const float*
                       void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
                       int32_t flags, const int32_t* pos_dev, void* stream);
 
+/* bgtq_step_prepare for queries and keys that have NOT been through the rotary embedding yet: the kernel
+ * applies it first, x' = x*cos + rotate_half(x)*sin in the split-half convention (dims d and d+64 form a
+ * pair), with fp16 tables of the step's position, rope_cos / rope_sin: (n_batch, 128) fp16, row b at
+ * + b*rope_sb.  Rounding is that of the fp16 expression evaluated by the reference's caller
+ * (transformers' apply_rotary_pos_emb, called in blockgtq/production_decode.py:37-39 and
+ * blockgtq/packed_kv_manager.py:429-431): two rounded products and one rounded sum, so codes and q_rot are
+ * bit-identical to rotating first and calling bgtq_step_prepare.  V is not rotated. */
+int bgtq_step_prepare_rope(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v,
+                      const void* q, int64_t q_sb, int64_t q_sh, void* q_rot, int32_t n_q,
+                      const void* k, int64_t k_sb, int64_t k_sh,
+                      const void* v, int64_t v_sb, int64_t v_sh,
+                      int32_t n_batch, int32_t n_kv, int32_t t0,
+                      uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st, int32_t kp_row_bytes,
+                      void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
+                      uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
+                      void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
+                      int32_t flags, const int32_t* pos_dev,
+                      const void* rope_cos, const void* rope_sin, int64_t rope_sb, void* stream);
+
 /* ---- decode --------------------------------------------------------------- */
 #define BGTQ_DEC_K_MIXED 1        /* k_packed rows are in the nibble/raw mixed layout */
 #define BGTQ_DEC_V_NIBBLE 2       /* v_packed rows are 4-bit nibbles */

@@ -608,3 +608,42 @@ def test_fused_decode_merge_matches_decode_plus_combine(gqa, T, n_splits):
         assert (tickets == 0).all()
         assert torch.isfinite(out).all()
         assert (out.float() - ref.float()).abs().max().item() <= 1e-3
+
+
+def test_step_prepare_with_fused_rope_is_bit_identical():
+    """Rotary embedding applied inside the append kernel against the fp16 expression
+    (x * cos) + (rotate_half(x) * sin) evaluated by torch first: same packed rows, norms and q_rot."""
+    from blockgtq_b200.layer import step_prepare
+    lt, tabs = _layer("a3_1to8")
+    gen = torch.Generator().manual_seed(321)
+    B, n_kv, gqa = 4, 2, 4
+    n_q = n_kv * gqa
+    q = (torch.randn(B, n_q, 1, HD, generator=gen) * 3).half().to(DEV)
+    k = (torch.randn(B, n_kv, 1, HD, generator=gen) * 3).half().to(DEV)
+    v = torch.randn(B, n_kv, 1, HD, generator=gen).half().to(DEV)
+    pos = torch.tensor([5.0, 77.0, 1234.0, 31000.0])
+    inv = 1.0 / (500000.0 ** (torch.arange(0, HD // 2, dtype=torch.float32) / (HD // 2)))
+    ang = pos[:, None] * inv[None, :]
+    cos = torch.cat([ang.cos(), ang.cos()], dim=-1).half().to(DEV)          # (B, 128), as transformers builds them
+    sin = torch.cat([ang.sin(), ang.sin()], dim=-1).half().to(DEV)
+
+    def rot_half(x):
+        return torch.cat([-x[..., HD // 2:], x[..., :HD // 2]], dim=-1)
+
+    c4, s4 = cos[:, None, None, :], sin[:, None, None, :]
+    q_ref = (q * c4) + (rot_half(q) * s4)
+    k_ref = (k * c4) + (rot_half(k) * s4)
+    outs = []
+    for fused in (False, True):
+        kp = torch.zeros(B, n_kv, 8, lt.max_tpb, dtype=torch.uint8, device=DEV)
+        kn = torch.zeros(B, n_kv, 8, lt.max_ng, dtype=torch.float16, device=DEV)
+        vp = torch.zeros(B, n_kv, 8, lt.vpb, dtype=torch.uint8, device=DEV)
+        vn = torch.zeros(B, n_kv, 8, dtype=torch.float16, device=DEV)
+        if fused:
+            qr = step_prepare(lt, q, k, v, 3, kp, kn, vp, vn, rope=(cos, sin))
+        else:
+            qr = step_prepare(lt, q_ref, k_ref, v, 3, kp, kn, vp, vn)
+        torch.cuda.synchronize()
+        outs.append((qr, kp, kn, vp, vn))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
