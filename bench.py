@@ -212,7 +212,7 @@ def run_seq_sharded(args, w, rank, world, dev):
     mgr, gen = build_manager(w, dev, seed=1234, extra_tokens=n_total + 16, ctx=hi - lo)
     if world > 1:
         from blockgtq_b200.sharding import SequenceShard
-        SequenceShard(mgr, owner=owner)
+        SequenceShard(mgr, owner=owner, transport=os.environ.get("BGTQ_SEQ_TRANSPORT", "nccl"))
     qs = (torch.randn(n_total, L, B, n_q, 1, HD, generator=gen, device=dev) * 2).half()
     ks = torch.stack([torch.stack([synth_keys(gen, (B * n_kv, 1), w["theta"], dev).reshape(B, n_kv, 1, HD)
                                    for _ in range(L)]) for _ in range(n_total)])

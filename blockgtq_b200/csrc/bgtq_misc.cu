@@ -232,3 +232,127 @@ extern "C" __attribute__((visibility("default"))) int bgtq_buffer_attn(const voi
         ring_size > 0 ? ring_size : 1, n_q, n_kv, scale, buf_o, buf_lse);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
+
+// ---------------------------------------------------------------------------
+// Sequence-sharded cache: exchange of the per-rank [O | LSE] messages over peer memory (NVLink) instead of
+// a library all-gather.  Every rank owns one exchange buffer [2 parities][n_ranks][stride] fp32 and one
+// flag word per rank, all mapped into every peer (symmetric memory).  Step number s (a device counter, so
+// a captured graph can be replayed):
+//   publish : copy the local message into slot [s & 1][my rank] of EVERY rank's buffer with plain peer
+//             stores, fence at system scope, then (last block of the grid) store s + 1 into flag[my rank]
+//             of every rank;
+//   merge   : wait (bounded) until flag[r] >= s + 1 for all r, merge the n_ranks messages of parity s & 1
+//             from the LOCAL buffer, and (last block) advance the counter.
+// Two parities are enough: a rank can be at most one step ahead of the slowest one, because its next
+// publish needs every peer's flag of the step before.
+// ---------------------------------------------------------------------------
+namespace bgtq {
+namespace {
+
+constexpr int kStatusPeerTimeout = 3;
+
+__global__ void __launch_bounds__(256) publish_kernel(const float* msg, int n_vec4, float* const* peer_bufs,
+                                                      int64_t slot_off, int64_t parity_stride, int32_t* const* peer_flags,
+                                                      int rank, int n_ranks, const int32_t* seq_dev, int32_t* ticket) {
+    const int seq = *seq_dev;
+    const float4* src = reinterpret_cast<const float4*>(msg);
+    for (int p = 0; p < n_ranks; ++p) {
+        float4* dst = reinterpret_cast<float4*>(peer_bufs[p] + (seq & 1) * parity_stride + slot_off);
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_vec4; i += gridDim.x * blockDim.x) dst[i] = src[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int t = atomicAdd(ticket, 1);
+        if (t == (int)gridDim.x - 1) {          // every block's stores are fenced: raise the flag everywhere
+            *ticket = 0;
+            __threadfence_system();
+            for (int p = 0; p < n_ranks; ++p) {
+                volatile int32_t* f = peer_flags[p] + rank;
+                *f = seq + 1;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128) merge_ranks_kernel(const float* local_buf, int n_ranks, int64_t rank_stride,
+                                                          int64_t parity_stride, const int32_t* flags, int32_t* seq_dev,
+                                                          int n_q, int64_t rows, __half* out, int64_t o_sb, int64_t o_sh,
+                                                          int32_t* status, int32_t* ticket) {
+    __shared__ int ok;
+    const int d = threadIdx.x, hq = blockIdx.x, b = blockIdx.y;
+    const int seq = *seq_dev;
+    if (d == 0) {
+        int good = 1;
+        for (int r = 0; r < n_ranks && good; ++r) {
+            const volatile int32_t* f = flags + r;
+            int spins = 0;
+            while (*f < seq + 1) {
+                if (++spins > (1 << 20)) { good = 0; break; }      // give up: report, do not hang
+                __nanosleep(200);
+            }
+        }
+        __threadfence_system();
+        ok = good;
+        if (!good && status) atomicExch(status, kStatusPeerTimeout);
+    }
+    __syncthreads();
+    const size_t row = (size_t)b * n_q + hq;
+    const float* base = local_buf + (seq & 1) * parity_stride;
+    float o = 0.f;
+    if (ok) {
+        float mx = -INFINITY;
+        for (int r = 0; r < n_ranks; ++r) mx = fmaxf(mx, __ldcg(base + r * rank_stride + rows * kHD + row));
+        float num = 0.f, den = 0.f;
+        if (mx > -INFINITY) {
+            for (int r = 0; r < n_ranks; ++r) {
+                const float l = __ldcg(base + r * rank_stride + rows * kHD + row);
+                if (l == -INFINITY) continue;
+                const float a = expf(l - mx);
+                den += a;
+                num = fmaf(a, __ldcg(base + r * rank_stride + row * kHD + d), num);
+            }
+        }
+        o = den > 0.f ? num / den : 0.f;
+    }
+    out[b * o_sb + hq * o_sh + d] = __float2half_rn(o);
+    __syncthreads();
+    if (d == 0) {
+        const int t = atomicAdd(ticket, 1);
+        if (t == (int)(gridDim.x * gridDim.y) - 1) {    // all blocks have read the flags and the messages
+            *ticket = 0;
+            *seq_dev = seq + 1;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace bgtq
+
+extern "C" __attribute__((visibility("default"))) int bgtq_exchange_publish(
+    const float* msg, int64_t n_floats, float* const* peer_bufs, int64_t slot_off, int64_t parity_stride,
+    int32_t* const* peer_flags, int32_t rank, int32_t n_ranks, const int32_t* seq_dev, int32_t* ticket, void* stream) {
+    if (!msg || !peer_bufs || !peer_flags || !seq_dev || !ticket || n_ranks < 1 || rank < 0 || rank >= n_ranks || n_floats < 4)
+        return BGTQ_E_BADARG;
+    if ((n_floats & 3) || (slot_off & 3) || (parity_stride & 3) || (reinterpret_cast<uintptr_t>(msg) & 15u)) return BGTQ_E_ALIGN;
+    const int n_vec4 = (int)(n_floats / 4);
+    int blocks = (n_vec4 + 255) / 256;
+    blocks = blocks > 32 ? 32 : blocks;
+    publish_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(msg, n_vec4, peer_bufs, slot_off, parity_stride,
+                                                                            peer_flags, rank, n_ranks, seq_dev, ticket);
+    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_exchange_merge(
+    const float* local_buf, int32_t n_ranks, int64_t rank_stride, int64_t parity_stride, const int32_t* flags,
+    int32_t* seq_dev, int32_t n_batch, int32_t n_q, void* out, int64_t o_sb, int64_t o_sh, int32_t* status,
+    int32_t* ticket, void* stream) {
+    if (!local_buf || !flags || !seq_dev || !out || !ticket || n_ranks < 1 || n_batch < 1 || n_q < 1) return BGTQ_E_BADARG;
+    const int64_t rows = (int64_t)n_batch * n_q;
+    if (rank_stride < rows * (kHD + 1) || parity_stride < rank_stride * n_ranks) return BGTQ_E_BADARG;
+    if (n_batch > 65535) return BGTQ_E_TOOBIG;
+    merge_ranks_kernel<<<dim3(n_q, n_batch), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        local_buf, n_ranks, rank_stride, parity_stride, flags, seq_dev, n_q, rows, static_cast<__half*>(out), o_sb, o_sh,
+        status, ticket);
+    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+}

@@ -287,11 +287,10 @@ class BlockGTQKVManager:
             pass                                  # merged, rotated and stored by the decode launch itself
         elif ex is None:
             combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li], programmatic=pd)
-        else:       # local result straight into the message, one all-gather, merge of the ranks' messages
+        else:       # local result straight into the message, exchange (all-gather or peer stores), merge of the messages
             combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li], programmatic=pd,
                     o32_out=ex.msg_o, lse_out=ex.msg_lse)
-            ex.all_gather()
-            combine_ranks(ex.gathered, self.B, self.n_q, out=self._g_out[li])
+            ex.exchange_and_merge(self._g_out[li])
 
     def _replay_layer(self, li: int, q, k_new, v_new, rope=None) -> torch.Tensor:
         self._ensure_storage()
@@ -386,6 +385,12 @@ class BlockGTQKVManager:
         if self._pos is not None and not self._pos_dirty:
             self._pos.add_(by)
         _, self.n_packed, _ = self._region_sizes(self._seq_len)
+
+    def release_graphs(self):
+        """Drop the captured per-layer CUDA graphs (they are re-captured on the next step).  Call this before
+        destroying a process group whose collectives the graphs captured (sequence sharding)."""
+        torch.cuda.synchronize(self.device)
+        self._graphs = [dict() for _ in range(self.n_layers)]
 
     def check_status(self):
         """Synchronise and raise if a kernel reported a timed-out wait."""

@@ -94,20 +94,66 @@ class SequenceShard:
     layer with the same query; only the owner's ``k_new`` / ``v_new`` are used.  Remote results are
     read from the local receive buffer only."""
 
-    def __init__(self, mgr, group=None, owner: int = None):
+    def __init__(self, mgr, group=None, owner: int = None, transport: str = "nccl"):
+        """``transport``: "nccl" = one ``all_gather_into_tensor`` per layer; "p2p" = the library's
+        peer-memory exchange (``bgtq_exchange_publish`` / ``bgtq_exchange_merge``) on buffers from
+        ``torch.distributed._symmetric_memory`` (single node, NVLink peers)."""
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.is_owner = self.rank == (self.world - 1 if owner is None else owner)
+        mgr._ensure_storage()
+        self.B, self.n_q = mgr.B, mgr.n_q
         rows = mgr.B * mgr.n_q
         dev = mgr.device
-        self.msg = torch.zeros(rows * (HD + 1), dtype=torch.float32, device=dev)
+        self.stride = rows * (HD + 1)                    # floats per message (a multiple of 4 when rows is)
+        self.msg = torch.zeros(self.stride, dtype=torch.float32, device=dev)
         self.msg_o = self.msg[:rows * HD].view(mgr.B, mgr.n_q, HD)
         self.msg_lse = self.msg[rows * HD:].view(mgr.B, mgr.n_q)
-        self.gathered = torch.zeros(self.world, rows * (HD + 1), dtype=torch.float32, device=dev)
-        self.all_gather()                      # communicator set-up outside any graph capture
-        torch.cuda.synchronize(dev) if dev.type == "cuda" else None
+        self.transport = transport
+        self._status = mgr._status
+        if transport == "p2p":
+            if self.stride % 4:
+                raise ValueError("peer-memory exchange needs batch * query heads to be a multiple of 4")
+            import torch.distributed._symmetric_memory as symm_mem
+            grp = dist.group.WORLD if group is None else group
+            self._buf = symm_mem.empty(2 * self.world * self.stride, dtype=torch.float32, device=dev)
+            self._flags = symm_mem.empty(max(self.world, 16), dtype=torch.int32, device=dev)
+            self._buf.zero_()
+            self._flags.zero_()
+            h_buf = symm_mem.rendezvous(self._buf, grp)
+            h_flg = symm_mem.rendezvous(self._flags, grp)
+            self._peer_bufs = torch.tensor(list(h_buf.buffer_ptrs), dtype=torch.int64, device=dev)
+            self._peer_flags = torch.tensor(list(h_flg.buffer_ptrs), dtype=torch.int64, device=dev)
+            self._seq = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._tickets = torch.zeros(2, dtype=torch.int32, device=dev)
+            self._handles = (h_buf, h_flg)
+            torch.cuda.synchronize(dev)
+            dist.barrier(group)                          # nobody publishes before every flag is zero
+        else:
+            self.gathered = torch.zeros(self.world, self.stride, dtype=torch.float32, device=dev)
+            self.all_gather()                            # communicator set-up outside any graph capture
+            torch.cuda.synchronize(dev) if dev.type == "cuda" else None
         mgr._exchange = self
+
+    def exchange_and_merge(self, out):
+        """Make every rank's message visible here and merge them into ``out`` (B, n_q, 128) fp16."""
+        if self.transport == "p2p":
+            from . import _lib
+            L, sp = _lib.lib(), _lib.stream_ptr(self.msg.device)
+            _lib.check(L.bgtq_exchange_publish(
+                _lib.ptr(self.msg), self.stride, _lib.ptr(self._peer_bufs), self.rank * self.stride,
+                self.world * self.stride, _lib.ptr(self._peer_flags), self.rank, self.world, _lib.ptr(self._seq),
+                _lib.ptr(self._tickets), sp), "bgtq_exchange_publish")
+            _lib.check(L.bgtq_exchange_merge(
+                _lib.ptr(self._buf), self.world, self.stride, self.world * self.stride, _lib.ptr(self._flags),
+                _lib.ptr(self._seq), self.B, self.n_q, _lib.ptr(out), out.stride(0), out.stride(1),
+                _lib.ptr(self._status), _lib.ptr(self._tickets[1:]), sp), "bgtq_exchange_merge")
+            _lib.count_launch(2)
+            return out
+        from .layer import combine_ranks
+        self.all_gather()
+        return combine_ranks(self.gathered, self.B, self.n_q, out=out)
 
     def all_gather(self):
         if dist.get_backend(self.group) == "nccl":

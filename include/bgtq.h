@@ -325,6 +325,28 @@ int bgtq_combine_ranks(const float* gathered, int32_t n_ranks, int64_t rank_stri
                        int32_t n_batch, int32_t n_q, void* out, int64_t o_sb, int64_t o_sh,
                        int32_t flags, void* stream);
 
+/* Exchange of the per-rank [O | LSE] messages of a sequence-sharded cache over PEER MEMORY (NVLink loads
+ * and stores between the GPUs of one node) instead of a library all-gather; no counterpart in the
+ * single-GPU reference.  Every rank owns an exchange buffer [2 parities][n_ranks][rank_stride] fp32
+ * (parity_stride floats between the two halves) and n_ranks int32 flags (initially 0), both mapped into
+ * every peer, plus a private step counter seq_dev (int32, initially 0) and two private int32 tickets
+ * (initially 0).  Per step, on every rank, in stream order:
+ *   bgtq_exchange_publish: copies the local message (n_floats, a multiple of 4) into slot
+ *     [seq & 1][rank] of every rank's buffer (peer_bufs: device array of n_ranks buffer base pointers,
+ *     slot_off = rank * rank_stride) and then stores seq + 1 into flag[rank] of every rank (peer_flags:
+ *     device array of n_ranks flag-array pointers);
+ *   bgtq_exchange_merge: waits until all n_ranks local flags reach seq + 1 (bounded: after about 0.3 s
+ *     it sets *status = 3 and writes zeros instead of hanging), merges the messages like
+ *     bgtq_combine_ranks from the LOCAL buffer, writes fp16 out and advances *seq_dev.
+ * Only plain loads/stores and system-scope fences are used (no multicast).  All ranks must run the same
+ * sequence of steps; each rank's kernels run on its own GPU. */
+int bgtq_exchange_publish(const float* msg, int64_t n_floats, float* const* peer_bufs, int64_t slot_off,
+                          int64_t parity_stride, int32_t* const* peer_flags, int32_t rank, int32_t n_ranks,
+                          const int32_t* seq_dev, int32_t* ticket, void* stream);
+int bgtq_exchange_merge(const float* local_buf, int32_t n_ranks, int64_t rank_stride, int64_t parity_stride,
+                        const int32_t* flags, int32_t* seq_dev, int32_t n_batch, int32_t n_q,
+                        void* out, int64_t o_sb, int64_t o_sh, int32_t* status, int32_t* ticket, void* stream);
+
 /* bgtq_decode followed by bgtq_combine with NO caller-provided scratch: the
  * split partials go to a fixed array inside the library instead of part_o /
  * part_lse.  This entry point has no counterpart in the reference.
