@@ -212,7 +212,8 @@ def run_seq_sharded(args, w, rank, world, dev):
     mgr, gen = build_manager(w, dev, seed=1234, extra_tokens=n_total + 16, ctx=hi - lo)
     if world > 1:
         from blockgtq_b200.sharding import SequenceShard
-        SequenceShard(mgr, owner=owner, transport=os.environ.get("BGTQ_SEQ_TRANSPORT", "nccl"))
+        transport = os.environ.get("BGTQ_SEQ_TRANSPORT", "p2p")      # peer-memory exchange; "nccl" = all-gather
+        SequenceShard(mgr, owner=owner, transport=transport)
     qs = (torch.randn(n_total, L, B, n_q, 1, HD, generator=gen, device=dev) * 2).half()
     ks = torch.stack([torch.stack([synth_keys(gen, (B * n_kv, 1), w["theta"], dev).reshape(B, n_kv, 1, HD)
                                    for _ in range(L)]) for _ in range(n_total)])
@@ -288,7 +289,8 @@ def run_seq_sharded(args, w, rank, world, dev):
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": args.workload, "layers": L, "batch": B, "n_q": n_q, "n_kv": n_kv, "context": T,
                        "tokens_per_gpu": hi - lo, "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"],
-                       "parallelism": f"sequence chunks x{world}, one all-gather of (O, LSE) per layer",
+                       "parallelism": f"sequence chunks x{world}, one exchange of (O, LSE) per layer "
+                                      f"({os.environ.get('BGTQ_SEQ_TRANSPORT', 'p2p') if world > 1 else 'none'})",
                        "exchange_bytes_per_layer": B * n_q * (HD + 1) * 4,
                        "l2": "inputs larger than L2 (packed cache bytes per step >> 126 MB), no flush"},
             "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": gbs, "peak": peak,
