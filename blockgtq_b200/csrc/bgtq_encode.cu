@@ -308,6 +308,20 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     float w[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) w[i] = __ldg(W + (size_t)i * kHD);
+    // static tables of the head, fetched before the dependency wait so their latency is off the critical path
+    __shared__ __align__(16) uint8_t s_lut[BGTQ_MAX_SEGMENTS][BGTQ_N_BINS];
+    __shared__ float s_cent[512];
+    reinterpret_cast<uint32_t*>(&s_lut[0][0])[tid] = reinterpret_cast<const uint32_t*>(&d.code_lut[0][0])[tid];
+    s_cent[tid] = d.k_cents[tid];
+    __shared__ float s_vb[16], s_vc[16];
+    if (tid < 16) {
+        s_vb[tid] = d.v_bounds[tid];
+        s_vc[tid] = d.v_cents[tid];
+    }
+    const int perm_p = d.head_perm[p];
+    const int g_p = d.group_of[p];
+    const float lut_off_p = d.lut_off[g_p], lut_inv_p = d.lut_inv[g_p];
+    const int cent_off_p = d.seg_lut_off[g_p];
     grid_launch_dependents();
     grid_dependency_wait();       // inputs and the slot position come from earlier work in the stream
     const int t0 = E.pos_dev ? *E.pos_dev : E.t0;
@@ -317,11 +331,11 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     if (c == 0) {
         const __half* cs = P.rope_cos ? P.rope_cos + b * P.rope_sb : nullptr;
         const __half* sn = P.rope_cos ? P.rope_sin + b * P.rope_sb : nullptr;
-        if (kind == 0) x = rope_element(P.q + b * P.q_sb + hq * P.q_sh, d.head_perm[p], cs, sn);
-        else if (kind == 1) x = rope_element(E.k + b * E.k_sb + h * E.k_sh, d.head_perm[p], cs, sn);
+        if (kind == 0) x = rope_element(P.q + b * P.q_sb + hq * P.q_sh, perm_p, cs, sn);
+        else if (kind == 1) x = rope_element(E.k + b * E.k_sb + h * E.k_sh, perm_p, cs, sn);
         else x = __half2float(E.v[b * E.v_sb + h * E.v_sh + p]);
         xs[p] = x;
-        g = d.group_of[p];
+        g = g_p;
     }
     __syncthreads();
     float raw_v = 0.f;
@@ -365,11 +379,11 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
         const bool mixed = E.flags & BGTQ_ENC_K_MIXED;
         float c2 = 0.f;
         if (c == 0) {
-            float u = (y - d.lut_off[g]) * d.lut_inv[g];
+            float u = (y - lut_off_p) * lut_inv_p;
             u = fminf(fmaxf(u, 0.f), 255.f);
-            const uint8_t cd = d.code_lut[g][(int)u];
+            const uint8_t cd = s_lut[g][(int)u];
             codes[p] = cd;
-            const float cv = d.k_cents[d.seg_lut_off[g] + cd];
+            const float cv = s_cent[cent_off_p + cd];
             c2 = cv * cv;
             if (E.k_codes) E.k_codes[((size_t)b * E.n_kv + h) * kHD + p] = cd;
             xs[p] = c2;
@@ -415,9 +429,9 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     if (c == 0) {
         const int nb = (1 << d.v_bits) - 1;
         int cd = 0;
-        for (int i = 0; i < nb; ++i) cd += y > d.v_bounds[i] ? 1 : 0;
+        for (int i = 0; i < nb; ++i) cd += y > s_vb[i] ? 1 : 0;
         codes[p] = (uint8_t)cd;
-        const float cv = d.v_cents[cd];
+        const float cv = s_vc[cd];
         c2 = cv * cv;
         if (E.v_codes) E.v_codes[((size_t)b * E.n_kv + h) * kHD + p] = (uint8_t)cd;
 #pragma unroll
