@@ -565,23 +565,30 @@ def main():
     vs = torch.randn(n_steps_total, L, B, n_kv, 1, HD, generator=gen, device=dev).half()
     hqkv = torch.cat([qs, ks, vs], dim=3).cpu().pin_memory()       # (steps, L, B, n_q + 2 n_kv, 1, hd)
     hout = torch.empty(L, B, n_q, 1, HD, dtype=torch.float16).pin_memory()
-    g_qkv = mgr.static_qkv()
-    gq, gk, gv = mgr.static_inputs()
+    g_all = mgr.static_qkv_all()                                    # (L, B, n_q + 2 n_kv, 1, hd): per-layer step inputs
+    g_in = [mgr.static_inputs(li) for li in range(L)]
+    graph_outputs = mgr._use_graph and args.n_splits is None       # results land in the manager's static output buffer
     step_no = [0]
+
+    dqkv = torch.cat([qs, ks, vs], dim=3)                          # the same inputs, resident in HBM
 
     def step_device():
         s = step_no[0]
+        g_all.copy_(dqkv[s])                                        # the step's inputs into the layers' input buffers
         for li in range(L):
-            mgr.append_and_attend(li, qs[s, li], ks[s, li], vs[s, li], n_splits=args.n_splits)
+            mgr.append_and_attend(li, *g_in[li], n_splits=args.n_splits)
         mgr.increment_seq_len()
         step_no[0] += 1
 
     def step_e2e():
         s = step_no[0]
-        for li in range(L):
-            g_qkv.copy_(hqkv[s, li], non_blocking=True)           # H2D straight into the step's input buffer
-            out = mgr.append_and_attend(li, gq, gk, gv, n_splits=args.n_splits)
-            hout[li].copy_(out, non_blocking=True)
+        g_all.copy_(hqkv[s], non_blocking=True)                     # H2D: every layer's q/k/v of this step
+        outs = [mgr.append_and_attend(li, *g_in[li], n_splits=args.n_splits) for li in range(L)]
+        if graph_outputs:                                           # D2H: every layer's attention output
+            hout.copy_(mgr.static_outputs().unsqueeze(3), non_blocking=True)
+        else:
+            for li in range(L):
+                hout[li].copy_(outs[li], non_blocking=True)
         mgr.increment_seq_len()
         torch.cuda.synchronize()
         step_no[0] += 1

@@ -139,7 +139,8 @@ class BlockGTQKVManager:
         self._q_rot = torch.empty(self.B, self.n_q, self.hd, dtype=torch.float16, device=dev)
         self._part_o = torch.empty(self.B, self.n_q, self._n_splits, self.hd, dtype=torch.float32, device=dev)
         self._part_lse = torch.empty(self.B, self.n_q, self._n_splits, dtype=torch.float32, device=dev)
-        self._g_qkv = torch.zeros(self.B, self.n_q + 2 * self.n_kv, 1, self.hd, dtype=torch.float16, device=dev)
+        self._g_qkv = torch.zeros(self.n_layers, self.B, self.n_q + 2 * self.n_kv, 1, self.hd, dtype=torch.float16,
+                                  device=dev)
         self._g_out = torch.zeros(self.n_layers, self.B, self.n_q, self.hd, dtype=torch.float16, device=dev)
         self._pos = torch.zeros(1, dtype=torch.int32, device=dev)
         self._tickets = torch.zeros(self.B * self.n_kv, dtype=torch.int32, device=dev)
@@ -242,17 +243,27 @@ class BlockGTQKVManager:
                flags=self._enc_flags)
 
     # -- graph replay of one layer step ----------------------------------------------------------
-    def static_qkv(self) -> torch.Tensor:
-        """(B, n_q + 2 n_kv, 1, hd) fp16 input buffer of the captured layer step: rows [0, n_q) are the
-        query heads, then the new K heads, then the new V heads.  Writing a step's inputs here (for
+    def static_qkv(self, layer_idx: int = 0) -> torch.Tensor:
+        """(B, n_q + 2 n_kv, 1, hd) fp16 input buffer of layer ``layer_idx``'s captured step: rows [0, n_q)
+        are the query heads, then the new K heads, then the new V heads.  Writing a step's inputs here (for
         instance as the output of a fused QKV projection or an H2D copy) and passing these views to
-        :meth:`append_and_attend` skips the staging copies."""
+        :meth:`append_and_attend` skips the staging copies.  ``static_qkv_all()`` is the whole
+        (n_layers, B, n_q + 2 n_kv, 1, hd) buffer."""
+        self._ensure_storage()
+        return self._g_qkv[layer_idx]
+
+    def static_qkv_all(self) -> torch.Tensor:
         self._ensure_storage()
         return self._g_qkv
 
-    def static_inputs(self):
-        b = self.static_qkv()
+    def static_inputs(self, layer_idx: int = 0):
+        b = self.static_qkv(layer_idx)
         return b[:, :self.n_q], b[:, self.n_q:self.n_q + self.n_kv], b[:, self.n_q + self.n_kv:]
+
+    def static_outputs(self) -> torch.Tensor:
+        """(n_layers, B, n_q, hd) fp16: where the captured layer steps leave their results."""
+        self._ensure_storage()
+        return self._g_out
 
     def _sync_pos(self):
         if self._pos_dirty:
@@ -262,7 +273,7 @@ class BlockGTQKVManager:
     def _layer_step(self, li: int, rope: bool = False):
         """rotate_q -> append K,V at *pos -> decode over [0, *pos + 1) -> combine, all on static buffers."""
         lt = self._layers[li]
-        gq, gk, gv = self.static_inputs()
+        gq, gk, gv = self.static_inputs(li)
         baked = all(self.quantizers[li][h]._q_perm_baked for h in range(self.n_kv))
         # the three kernels are chained as programmatic dependents: each sets up its static tables while
         # the one before it drains, and waits on the device before touching the step's data
@@ -297,7 +308,7 @@ class BlockGTQKVManager:
         if self._seq_len + 1 > self.max_T:
             raise ValueError("cache overflow")
         self._sync_pos()
-        gq, gk, gv = self.static_inputs()
+        gq, gk, gv = self.static_inputs(li)
         if q.data_ptr() != gq.data_ptr():
             gq.copy_(q.reshape(gq.shape))
         if k_new.data_ptr() != gk.data_ptr():

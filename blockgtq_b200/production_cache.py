@@ -79,11 +79,11 @@ class BlockGTQProductionCache:
     def increment_seq_len(self, by=1):
         self._mgr.increment_seq_len(by)
 
-    def static_qkv(self):
-        return self._mgr.static_qkv()
+    def static_qkv(self, layer_idx=0):
+        return self._mgr.static_qkv(layer_idx)
 
-    def static_inputs(self):
-        return self._mgr.static_inputs()
+    def static_inputs(self, layer_idx=0):
+        return self._mgr.static_inputs(layer_idx)
 
     def cache_memory_bytes(self) -> int:
         T = self.seq_len
