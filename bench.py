@@ -517,6 +517,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--n-splits", type=int, default=None)
+    ap.add_argument("--per-layer-graphs", action="store_true",
+                    help="replay one CUDA graph per layer (append_and_attend) instead of one graph per decode step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]
@@ -571,19 +573,38 @@ def main():
     step_no = [0]
 
     dqkv = torch.cat([qs, ks, vs], dim=3)                          # the same inputs, resident in HBM
+    # One CUDA graph for the whole decode step (every layer's append + decode + combine), the way a serving
+    # engine captures its model forward around these launches; --per-layer-graphs replays one graph per layer
+    # through append_and_attend instead.
+    step_graph = None
+    if graph_outputs and not args.per_layer_graphs:
+        for li in range(L):
+            mgr.layer_step(li)                                      # eager once: kernel attributes, shapes
+        torch.cuda.synchronize()
+        step_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(step_graph):
+            for li in range(L):
+                mgr.layer_step(li)
+    launches_per_step = 3 * L
+
+    def run_layers():
+        if step_graph is not None:
+            step_graph.replay()
+            _lib.count_launch(launches_per_step)
+            return None
+        return [mgr.append_and_attend(li, *g_in[li], n_splits=args.n_splits) for li in range(L)]
 
     def step_device():
         s = step_no[0]
         g_all.copy_(dqkv[s])                                        # the step's inputs into the layers' input buffers
-        for li in range(L):
-            mgr.append_and_attend(li, *g_in[li], n_splits=args.n_splits)
+        run_layers()
         mgr.increment_seq_len()
         step_no[0] += 1
 
     def step_e2e():
         s = step_no[0]
         g_all.copy_(hqkv[s], non_blocking=True)                     # H2D: every layer's q/k/v of this step
-        outs = [mgr.append_and_attend(li, *g_in[li], n_splits=args.n_splits) for li in range(L)]
+        outs = run_layers()
         if graph_outputs:                                           # D2H: every layer's attention output
             hout.copy_(mgr.static_outputs().unsqueeze(3), non_blocking=True)
         else:
@@ -666,6 +687,8 @@ def main():
                        "context": w["ctx"], "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"],
                        "fp16_sink": w["n_sink"], "fp16_window": w["window"], "parallelism": f"batch x{world}",
                        "l2": "inputs larger than L2 (packed cache bytes per step >> 126 MB), no flush",
+                       "graphs": "one per decode step" if step_graph is not None else
+                                 ("one per layer" if graph_outputs else "none (eager launches)"),
                        "decode_us_per_layer": dec_avg_ms * 1e3, "step_hbm_gbs": live_bytes / (ms_step * 1e-3) / 1e9,
                        "step_frac_of_8tbs": live_bytes / (ms_step * 1e-3) / 8e12},
             "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": achieved, "peak": peak,

@@ -303,6 +303,17 @@ class BlockGTQKVManager:
                     o32_out=ex.msg_o, lse_out=ex.msg_lse)
             ex.exchange_and_merge(self._g_out[li])
 
+    def layer_step(self, layer_idx: int, rope: bool = False):
+        """Launch one layer's decode step (append the token in ``static_inputs(layer_idx)`` at the current
+        position, attend, leave the result in ``static_outputs()[layer_idx]``) as plain kernel launches on the
+        current stream: no allocation, no synchronisation, position read on the device.  This is the form to
+        call inside a caller's own CUDA-graph capture of a whole decode step (a serving engine capturing its
+        model forward); :meth:`append_and_attend` wraps the same launches in one graph per layer.  Call
+        :meth:`increment_seq_len` once per step, outside the captured region or after the replay."""
+        self._ensure_storage()
+        self._sync_pos()
+        self._layer_step(layer_idx, rope)
+
     def _replay_layer(self, li: int, q, k_new, v_new, rope=None) -> torch.Tensor:
         self._ensure_storage()
         if self._seq_len + 1 > self.max_T:
