@@ -84,6 +84,7 @@ def build_manager(w, device, seed, extra_tokens, ctx=None, graph=None):
                             v_bits=w["v_bits"], device=device, n_sink=w["n_sink"], recent_window=w["window"],
                             use_cuda_graph=graph)
     mgr.programmatic = os.environ.get("BGTQ_NO_PROGRAMMATIC", "") == ""
+    mgr.fused_merge = os.environ.get("BGTQ_FUSED_MERGE", "") != ""
     for li in range(L):
         ck = torch.stack([synth_keys(gen, (1, 2048), w["theta"], device)[0] for _ in range(n_kv)])
         cq = torch.stack([synth_keys(gen, (gqa, 2048), w["theta"], device).reshape(-1, HD) for _ in range(n_kv)])
