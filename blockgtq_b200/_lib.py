@@ -57,6 +57,11 @@ _SIGNATURES = {
                               _vp, _i64, _i64, _i64,
                               _vp, _i64, _i64, _i64,
                               _vp, _vp, _i32, _vp, _vp]),
+    "bgtq_step_prepare_ring": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i32,
+                                    _vp, _i64, _i64, _vp, _i64, _i64, _i32, _i32, _i32,
+                                    _vp, _i64, _i64, _i64, _i32, _vp, _i64, _i64, _i64, _i32,
+                                    _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _vp,
+                                    _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "bgtq_step_prepare_rope": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i32,
                                     _vp, _i64, _i64, _vp, _i64, _i64, _i32, _i32, _i32,
                                     _vp, _i64, _i64, _i64, _i32, _vp, _i64, _i64, _i64, _i32,
@@ -83,6 +88,9 @@ _SIGNATURES = {
                                                _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
                                                _i32, _i32, _i32, _i32, _i32, _i32, _f32,
                                                _vp, _vp, _i64, _i64, _vp, _vp, _vp]),
+    "bgtq_buffer_attn_pos": (C.c_int, [_vp, _i64, _i64, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
+                                   _i32, _i32, _i32, _f32,
+                                   _vp, _vp, _vp, _vp]),
     "bgtq_buffer_attn": (C.c_int, [_vp, _i64, _i64, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
                                    _i32, _i32, _i32, _f32,
                                    _vp, _vp, _vp]),

@@ -268,6 +268,12 @@ struct PrepParams {
     const __half* rope_cos;   // optional (n_batch, 128) fp16 tables of the step's position: q and k arrive pre-RoPE
     const __half* rope_sin;
     int64_t rope_sb;
+    // three-region mode (optional): fp16 sink + recent ring per (batch, KV head); the step's token is written
+    // into its ring (or sink) slot and the token that leaves the recent window is the one that gets encoded
+    __half* k_buf;
+    __half* v_buf;
+    int64_t kb_sb, kb_sh;
+    int32_t n_sink, window;
 };
 
 // Element `dim` of a row after rotary embedding in the split-half convention, with the rounding points of
@@ -291,16 +297,29 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     const int tid = threadIdx.x, p = tid & 127, c = tid >> 7, warp = tid >> 5, lane = tid & 31;
     const int n_rot = P.do_rot ? E.n_batch * P.n_q : 0;
     const int n_rows = E.n_batch * E.n_kv;
-    int item = blockIdx.x, kind;   // 0 rotate, 1 K, 2 V
+    int item = blockIdx.x, kind;   // 0 rotate, 1 K, 2 V, 3 / 4: copy the new K / V token into its fp16 buffer slot
     int b, h, hq = 0;
     if (item < n_rot) {
         kind = 0; b = item / P.n_q; hq = item % P.n_q; h = hq / (P.n_q / E.n_kv);
     } else {
         item -= n_rot;
-        kind = item < n_rows ? 1 : 2;
-        if (kind == 2) item -= n_rows;
+        kind = 1 + item / n_rows;
+        item %= n_rows;
         b = item / E.n_kv; h = item % E.n_kv;
         if ((kind == 1 && (E.flags & BGTQ_ENC_SKIP_K)) || (kind == 2 && (E.flags & BGTQ_ENC_SKIP_V))) return;
+    }
+    if (kind >= 3) {            // three-region mode: the new token enters the sink (first n_sink tokens) or the ring
+        grid_launch_dependents();
+        grid_dependency_wait();
+        if (tid < kHD) {
+            const int pos = E.pos_dev ? *E.pos_dev : E.t0;
+            const int ring = P.window + 1;
+            const int slot = pos < P.n_sink ? pos : P.n_sink + (pos - P.n_sink) % ring;
+            const __half* src = kind == 3 ? E.k + b * E.k_sb + h * E.k_sh : E.v + b * E.v_sb + h * E.v_sh;
+            __half* dst = (kind == 3 ? P.k_buf : P.v_buf) + b * P.kb_sb + h * P.kb_sh + (int64_t)slot * kHD;
+            dst[tid] = src[tid];
+        }
+        return;
     }
     const BgtqHeadDesc& d = E.desc[h];
     // rotation column p, rows 32c .. 32c+31: independent loads issued before anything else
@@ -324,7 +343,22 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     const int cent_off_p = d.seg_lut_off[g_p];
     grid_launch_dependents();
     grid_dependency_wait();       // inputs and the slot position come from earlier work in the stream
-    const int t0 = E.pos_dev ? *E.pos_dev : E.t0;
+    int t0 = E.pos_dev ? *E.pos_dev : E.t0;
+    const __half* k_src = E.k + b * E.k_sb + h * E.k_sh;
+    const __half* v_src = E.v + b * E.v_sb + h * E.v_sh;
+    if (P.k_buf != nullptr && kind != 0) {
+        // Three-region policy with one-token blocks (blockgtq/unaccelerated.py:226-233): t0 tokens exist before
+        // this step.  Of the a0 non-sink tokens, f0 = max(0, a0 - window) are packed already; the step's token
+        // makes a0 + 1, and if that leaves more than `window` + 1 unpacked ones, token f0 is encoded into
+        // packed row f0 from its ring slot.
+        const int a0 = max(0, t0 - P.n_sink), a1 = max(0, t0 + 1 - P.n_sink);
+        const int f0 = max(0, a0 - P.window), f1 = max(0, a1 - P.window);
+        if (f1 <= f0) return;
+        const int64_t slot = P.n_sink + f0 % (P.window + 1);
+        k_src = P.k_buf + b * P.kb_sb + h * P.kb_sh + slot * kHD;
+        v_src = P.v_buf + b * P.kb_sb + h * P.kb_sh + slot * kHD;
+        t0 = f0;
+    }
 
     float x = 0.f;
     int g = 0;
@@ -332,8 +366,8 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
         const __half* cs = P.rope_cos ? P.rope_cos + b * P.rope_sb : nullptr;
         const __half* sn = P.rope_cos ? P.rope_sin + b * P.rope_sb : nullptr;
         if (kind == 0) x = rope_element(P.q + b * P.q_sb + hq * P.q_sh, perm_p, cs, sn);
-        else if (kind == 1) x = rope_element(E.k + b * E.k_sb + h * E.k_sh, perm_p, cs, sn);
-        else x = __half2float(E.v[b * E.v_sb + h * E.v_sh + p]);
+        else if (kind == 1) x = rope_element(k_src, perm_p, cs, sn);
+        else x = __half2float(v_src[p]);
         xs[p] = x;
         g = g_p;
     }
@@ -511,7 +545,8 @@ static int step_prepare_impl(
     int32_t kp_row_bytes, void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
     uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
     int64_t vn_st, int32_t flags, const int32_t* pos_dev, void* stream, const void* rope_cos, const void* rope_sin,
-    int64_t rope_sb) {
+    int64_t rope_sb, void* k_buf = nullptr, void* v_buf = nullptr, int64_t kb_sb = 0, int64_t kb_sh = 0,
+    int32_t n_sink = 0, int32_t window = 0) {
     if (!desc || !rot_k || !rot_v || !k || !v || !k_packed || !k_norms || !v_packed || !v_norms) return BGTQ_E_BADARG;
     if (n_batch < 1 || n_kv < 1 || t0 < 0 || kp_row_bytes < 1 || kp_row_bytes > kHD || kn_count < 1 ||
         kn_count > BGTQ_MAX_SEGMENTS)
@@ -533,7 +568,9 @@ static int step_prepare_impl(
     P.n_q = n_q; P.do_rot = do_rot ? 1 : 0;
     P.rope_cos = static_cast<const __half*>(rope_cos); P.rope_sin = static_cast<const __half*>(rope_sin);
     P.rope_sb = rope_sb;
-    const int64_t items = (int64_t)(do_rot ? n_batch * n_q : 0) + 2LL * n_batch * n_kv;
+    P.k_buf = static_cast<__half*>(k_buf); P.v_buf = static_cast<__half*>(v_buf);
+    P.kb_sb = kb_sb; P.kb_sh = kb_sh; P.n_sink = n_sink; P.window = window;
+    const int64_t items = (int64_t)(do_rot ? n_batch * n_q : 0) + (k_buf ? 4LL : 2LL) * n_batch * n_kv;
     if (items > 0x7fffffffLL) return BGTQ_E_TOOBIG;
     return launch_kernel(prep_kernel, dim3((unsigned)items), dim3(512), 0, static_cast<cudaStream_t>(stream),
                          (flags & BGTQ_ENC_PROGRAMMATIC) != 0, P) == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
@@ -562,4 +599,19 @@ extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare_rope(
     return step_prepare_impl(desc, rot_k, rot_v, q, q_sb, q_sh, q_rot, n_q, k, k_sb, k_sh, v, v_sb, v_sh, n_batch, n_kv, t0, k_packed,
                              kp_sb, kp_sh, kp_st, kp_row_bytes, k_norms, kn_sb, kn_sh, kn_st, kn_count, v_packed, vp_sb, vp_sh,
                              vp_st, v_norms, vn_sb, vn_sh, vn_st, flags, pos_dev, stream, rope_cos, rope_sin, rope_sb);
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare_ring(
+    const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v, const void* q, int64_t q_sb, int64_t q_sh,
+    void* q_rot, int32_t n_q, const void* k, int64_t k_sb, int64_t k_sh, const void* v, int64_t v_sb, int64_t v_sh,
+    int32_t n_batch, int32_t n_kv, int32_t t0, uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
+    int32_t kp_row_bytes, void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
+    uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
+    int64_t vn_st, int32_t flags, const int32_t* pos_dev, void* k_buf, void* v_buf, int64_t kb_sb, int64_t kb_sh, int32_t n_sink,
+    int32_t window, void* stream) {
+    if (!k_buf || !v_buf || n_sink < 0 || window < 1) return BGTQ_E_BADARG;
+    return step_prepare_impl(desc, rot_k, rot_v, q, q_sb, q_sh, q_rot, n_q, k, k_sb, k_sh, v, v_sb, v_sh, n_batch, n_kv, t0, k_packed,
+                             kp_sb, kp_sh, kp_st, kp_row_bytes, k_norms, kn_sb, kn_sh, kn_st, kn_count, v_packed, vp_sb, vp_sh,
+                             vp_st, v_norms, vn_sb, vn_sh, vn_st, flags, pos_dev, stream, nullptr, nullptr, 0, k_buf, v_buf, kb_sb, kb_sh,
+                             n_sink, window);
 }

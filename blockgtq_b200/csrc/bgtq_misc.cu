@@ -109,9 +109,18 @@ __global__ void __launch_bounds__(128) buffer_attn_kernel(const __half* q, int64
                                                            const __half* kb, const __half* vb, int64_t kb_sb,
                                                            int64_t kb_sh, int n_sink_tok, int n_ring_tok,
                                                            int sink_cap, int ring_first, int ring_size, int n_q,
-                                                           int n_kv, float scale, float* buf_o, float* buf_lse) {
+                                                           int n_kv, float scale, float* buf_o, float* buf_lse,
+                                                           const int32_t* pos_dev) {
     extern __shared__ float sc[];                      // n_tok logits, then 8 floats of scratch
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (pos_dev) {      // region sizes from the device-side token count (one-token blocks, window = ring_size - 1)
+        const int avail = *pos_dev + 1;                // tokens including the one appended this step
+        const int a0 = max(0, avail - 1 - sink_cap), a1 = max(0, avail - sink_cap);
+        const int f0 = max(0, a0 - (ring_size - 1));
+        n_sink_tok = min(avail, sink_cap);
+        n_ring_tok = a1 - f0;
+        ring_first = f0 % ring_size;
+    }
     const int hq = blockIdx.x, b = blockIdx.y;
     const int h = hq / (n_q / n_kv);
     const size_t row = (size_t)b * n_q + hq;
@@ -214,22 +223,39 @@ extern "C" __attribute__((visibility("default"))) int bgtq_combine_ranks(const f
                ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 
+extern "C" int bgtq_buffer_attn_pos(const void* q, int64_t q_sb, int64_t q_sh, const void* k_buf, const void* v_buf,
+                                int64_t kb_sb, int64_t kb_sh, int32_t n_sink_tokens, int32_t n_ring_tokens,
+                                int32_t sink_cap, int32_t ring_first, int32_t ring_size, int32_t n_batch, int32_t n_q,
+                                int32_t n_kv, float scale, float* buf_o, float* buf_lse, const int32_t* pos_dev,
+                                void* stream);
+
 extern "C" __attribute__((visibility("default"))) int bgtq_buffer_attn(const void* q, int64_t q_sb, int64_t q_sh, const void* k_buf, const void* v_buf,
                                 int64_t kb_sb, int64_t kb_sh, int32_t n_sink_tokens, int32_t n_ring_tokens,
                                 int32_t sink_cap, int32_t ring_first, int32_t ring_size, int32_t n_batch, int32_t n_q,
                                 int32_t n_kv, float scale, float* buf_o, float* buf_lse, void* stream) {
+    return bgtq_buffer_attn_pos(q, q_sb, q_sh, k_buf, v_buf, kb_sb, kb_sh, n_sink_tokens, n_ring_tokens, sink_cap,
+                                ring_first, ring_size, n_batch, n_q, n_kv, scale, buf_o, buf_lse, nullptr, stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_buffer_attn_pos(const void* q, int64_t q_sb, int64_t q_sh, const void* k_buf, const void* v_buf,
+                                int64_t kb_sb, int64_t kb_sh, int32_t n_sink_tokens, int32_t n_ring_tokens,
+                                int32_t sink_cap, int32_t ring_first, int32_t ring_size, int32_t n_batch, int32_t n_q,
+                                int32_t n_kv, float scale, float* buf_o, float* buf_lse, const int32_t* pos_dev,
+                                void* stream) {
     if (!q || !buf_o || !buf_lse || n_batch < 1 || n_kv < 1 || n_q < n_kv || n_q % n_kv || n_sink_tokens < 0 ||
         n_ring_tokens < 0 || n_sink_tokens > sink_cap || n_ring_tokens > ring_size || ring_first < 0 ||
         (n_ring_tokens > 0 && ring_first >= ring_size))
         return BGTQ_E_BADARG;
-    const int32_t n_buf_tokens = n_sink_tokens + n_ring_tokens;
+    // with a device-side position the region sizes are computed in the kernel: size the scratch for the most
+    const int32_t n_buf_tokens = pos_dev ? sink_cap + ring_size : n_sink_tokens + n_ring_tokens;
     if (n_buf_tokens > 0 && (!k_buf || !v_buf)) return BGTQ_E_BADARG;
+    if (pos_dev && ring_size < 2) return BGTQ_E_BADARG;
     if (n_buf_tokens > 8192 || n_batch > 65535) return BGTQ_E_TOOBIG;
     const size_t smem = (size_t)(n_buf_tokens + 8) * sizeof(float);
     buffer_attn_kernel<<<dim3(n_q, n_batch), 128, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(q), q_sb, q_sh, static_cast<const __half*>(k_buf),
         static_cast<const __half*>(v_buf), kb_sb, kb_sh, n_sink_tokens, n_ring_tokens, sink_cap, ring_first,
-        ring_size > 0 ? ring_size : 1, n_q, n_kv, scale, buf_o, buf_lse);
+        ring_size > 0 ? ring_size : 1, n_q, n_kv, scale, buf_o, buf_lse, pos_dev);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 

@@ -176,8 +176,9 @@ def rotate_q_bulk(layer: LayerTables, q: torch.Tensor) -> torch.Tensor:
 
 
 def step_prepare(layer: LayerTables, q, k, v, t0, k_packed, k_norms, v_packed, v_norms, *, q_rot=None,
-                 flags=0, pos_dev=None, rope=None):
-    """Rotate q (B, n_q, [1,] 128) into ``q_rot`` and append one token k/v (B, n_kv, 1, 128) at slot
+                 flags=0, pos_dev=None, rope=None, ring=None):
+    """``ring=(k_buf, v_buf, n_sink, window)``: three-region mode (``bgtq_step_prepare_ring``), see bgtq.h.
+    Rotate q (B, n_q, [1,] 128) into ``q_rot`` and append one token k/v (B, n_kv, 1, 128) at slot
     ``t0`` (or ``*pos_dev``) of the cache tensors, in one launch.  ``q=None`` skips the rotation.
     ``rope=(cos, sin)``, each fp16 (B, 128) (or (B, 1, 128)): q and k are pre-RoPE and the kernel applies
     the rotary embedding of the step's position first (``bgtq_step_prepare_rope``)."""
@@ -207,7 +208,16 @@ def step_prepare(layer: LayerTables, q, k, v, t0, k_packed, k_norms, v_packed, v
               _lib.ptr(k), k.stride(0), k.stride(1), _lib.ptr(v), v.stride(0), v.stride(1), B, H, int(t0),
               _lib.ptr(k_packed), *kps, k_packed.shape[3], _lib.ptr(k_norms), *kns, k_norms.shape[3],
               _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns, flags, _lib.ptr(pos_dev))
-    if rope is not None:
+    if ring is not None:
+        if rope is not None:
+            raise NotImplementedError("fused RoPE and the three-region mode cannot be combined")
+        k_buf, v_buf, n_sink, window = ring
+        if k_buf.stride(2) != HD or k_buf.stride(3) != 1 or v_buf.stride() != k_buf.stride():
+            raise ValueError("buffer tensors must be (B, n_kv, cap, 128) with contiguous token rows")
+        _lib.check(_lib.lib().bgtq_step_prepare_ring(*common, _lib.ptr(k_buf), _lib.ptr(v_buf), k_buf.stride(0),
+                                                     k_buf.stride(1), int(n_sink), int(window),
+                                                     _lib.stream_ptr(k.device)), "bgtq_step_prepare_ring")
+    elif rope is not None:
         cos, sin = (t.reshape(B, HD) for t in rope)
         if cos.dtype != torch.float16 or sin.dtype != torch.float16 or cos.stride(1) != 1 or sin.stride(1) != 1 \
                 or cos.stride(0) != sin.stride(0):
@@ -333,7 +343,8 @@ def combine(part_o, part_lse, n_kv, *, v_rot=None, buf_o=None, buf_lse=None, out
     return out, o32, lse
 
 
-def buffer_attn(q, k_buf, v_buf, n_kv, scale, *, n_sink_tokens, n_ring_tokens, sink_cap, ring_first, ring_size):
+def buffer_attn(q, k_buf, v_buf, n_kv, scale, *, n_sink_tokens=0, n_ring_tokens=0, sink_cap, ring_first=0, ring_size,
+                pos_dev=None, out=None):
     """Attention over unquantised fp16 tokens.  q (B, n_q, 128) fp16 (original basis);
     k_buf/v_buf (B, n_kv, cap, 128) fp16 with contiguous token rows: a sink prefix and a ring
     of ``ring_size`` slots starting at slot ``sink_cap`` (see ``bgtq_buffer_attn``)."""
@@ -341,14 +352,17 @@ def buffer_attn(q, k_buf, v_buf, n_kv, scale, *, n_sink_tokens, n_ring_tokens, s
     if q.dim() == 4:
         q = q[:, :, 0]
     B, n_q, _ = q.shape
-    o = torch.empty(B, n_q, HD, dtype=torch.float32, device=q.device)
-    lse = torch.empty(B, n_q, dtype=torch.float32, device=q.device)
+    if out is not None:
+        o, lse = out
+    else:
+        o = torch.empty(B, n_q, HD, dtype=torch.float32, device=q.device)
+        lse = torch.empty(B, n_q, dtype=torch.float32, device=q.device)
     if k_buf.stride(2) != HD or k_buf.stride(3) != 1 or v_buf.stride() != k_buf.stride():
         raise ValueError("buffer tensors must be (B, n_kv, cap, 128) with contiguous token rows")
-    _lib.check(_lib.lib().bgtq_buffer_attn(
+    _lib.check(_lib.lib().bgtq_buffer_attn_pos(
         _lib.ptr(q), q.stride(0), q.stride(1), _lib.ptr(k_buf), _lib.ptr(v_buf), k_buf.stride(0), k_buf.stride(1),
         int(n_sink_tokens), int(n_ring_tokens), int(sink_cap), int(ring_first), int(ring_size),
-        B, n_q, n_kv, float(scale), _lib.ptr(o), _lib.ptr(lse), _lib.stream_ptr(q.device)),
-        "bgtq_buffer_attn")
+        B, n_q, n_kv, float(scale), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(pos_dev), _lib.stream_ptr(q.device)),
+        "bgtq_buffer_attn_pos")
     _lib.count_launch()
     return o, lse

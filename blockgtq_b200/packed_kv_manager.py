@@ -74,9 +74,11 @@ class BlockGTQKVManager:
         self._dec_flags = (_lib.DEC_K_MIXED if k_mixed else 0) | (_lib.DEC_V_NIBBLE if v_nibble else 0)
         # single-token decode steps are captured once per layer and replayed (the reference graphs only
         # its T=1 encode, packed_kv_manager.py:182-257); needs the plain (unbuffered) cache
-        self._use_graph = (not self._buffered) if use_cuda_graph is None else bool(use_cuda_graph)
-        if self._use_graph and self._buffered:
-            raise ValueError("CUDA-graph replay is not available with fp16 sink/recent buffers")
+        # (with fp16 regions the captured step needs one-token blocks, the policy's default)
+        graphable = (not self._buffered) or (self.block_size == 1 and self.recent_window >= 1)
+        self._use_graph = graphable if use_cuda_graph is None else bool(use_cuda_graph)
+        if self._use_graph and not graphable:
+            raise ValueError("CUDA-graph replay with fp16 sink/recent buffers needs block_size == 1 and a window")
         self._graphs = [dict() for _ in range(n_layers)]      # per layer: {rope fused or not: CUDA graph}
         self._g_qkv = self._g_out = self._pos = None
 
@@ -145,6 +147,8 @@ class BlockGTQKVManager:
         self._pos = torch.zeros(1, dtype=torch.int32, device=dev)
         self._tickets = torch.zeros(self.B * self.n_kv, dtype=torch.int32, device=dev)
         self._g_rope = torch.zeros(2, self.B, self.hd, dtype=torch.float16, device=dev)     # cos, sin of the step
+        self._buf_o = torch.zeros(self.B, self.n_q, self.hd, dtype=torch.float32, device=dev)
+        self._buf_lse = torch.zeros(self.B, self.n_q, dtype=torch.float32, device=dev)
         if self._buffered:
             self._k_buf = torch.zeros(self.n_layers, self.B, self.n_kv, self._buf_cap, self.hd,
                                       dtype=torch.float16, device=dev)
@@ -280,6 +284,21 @@ class BlockGTQKVManager:
         pd = self.programmatic
         ex = self._exchange
         q_rot = gq[:, :, 0].contiguous() if baked else self._q_rot
+        if self._buffered:          # three regions, everything derived from the device-side token count
+            ns, win = self.n_sink, self.recent_window
+            step_prepare(lt, None if baked else gq, gk, gv, 0, self._k_packed[li], self._k_norms[li],
+                         self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos,
+                         flags=self._enc_flags | (_lib.ENC_PROGRAMMATIC if pd else 0),
+                         ring=(self._k_buf[li], self._v_buf[li], ns, win))
+            decode(lt, q_rot, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
+                   0, self.max_T, n_splits=self._n_splits, scale=self.scale, status=self._status,
+                   part_o=self._part_o, part_lse=self._part_lse, pos_dev=self._pos, pos_add=-(ns + win),
+                   flags=self._dec_flags | (_lib.DEC_PROGRAMMATIC if pd else 0))
+            buffer_attn(gq, self._k_buf[li], self._v_buf[li], self.n_kv, self.scale, sink_cap=ns, ring_size=win + 1,
+                        pos_dev=self._pos, out=(self._buf_o, self._buf_lse))
+            combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, buf_o=self._buf_o, buf_lse=self._buf_lse,
+                    out=self._g_out[li], programmatic=pd)
+            return
         if ex is None or ex.is_owner:
             step_prepare(lt, None if baked else gq, gk, gv, 0, self._k_packed[li], self._k_norms[li],
                          self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos,
@@ -340,7 +359,8 @@ class BlockGTQKVManager:
             self._graphs[li][use_rope] = g
         else:
             g.replay()
-            _lib.count_launch(2 if (self._exchange is None and self.fused_merge) else (5 if self._exchange else 3))
+            _lib.count_launch(4 if self._buffered else
+                              (2 if (self._exchange is None and self.fused_merge) else (5 if self._exchange else 3)))
         return self._g_out[li]
 
     # -- decode ----------------------------------------------------------------------------

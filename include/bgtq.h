@@ -180,6 +180,26 @@ int bgtq_step_prepare_rope(const BgtqHeadDesc* desc, const float* rot_k, const f
                       int32_t flags, const int32_t* pos_dev,
                       const void* rope_cos, const void* rope_sin, int64_t rope_sb, void* stream);
 
+/* bgtq_step_prepare for the three-region cache policy (fp16 sink + packed middle + fp16 recent window,
+ * blockgtq/unaccelerated.py:163-244) with one-token blocks, everything derived from the device-side token
+ * count so that the step can be captured in a CUDA graph: with t = *pos_dev tokens before the step, the new
+ * token's k / v are copied into their slot of the fp16 buffers k_buf / v_buf (slot t while t < n_sink, else
+ * n_sink + (t - n_sink) % (window + 1); slot j of (b,h) at buf + b*kb_sb + h*kb_sh + j*128), and the token
+ * that thereby leaves the recent window (non-sink index f = t - n_sink - window, if >= 0) is read from its
+ * ring slot, encoded and written to packed row f.  Queries are rotated as usual. */
+int bgtq_step_prepare_ring(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v,
+                      const void* q, int64_t q_sb, int64_t q_sh, void* q_rot, int32_t n_q,
+                      const void* k, int64_t k_sb, int64_t k_sh,
+                      const void* v, int64_t v_sb, int64_t v_sh,
+                      int32_t n_batch, int32_t n_kv, int32_t t0,
+                      uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st, int32_t kp_row_bytes,
+                      void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
+                      uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
+                      void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
+                      int32_t flags, const int32_t* pos_dev,
+                      void* k_buf, void* v_buf, int64_t kb_sb, int64_t kb_sh, int32_t n_sink, int32_t window,
+                      void* stream);
+
 /* ---- decode --------------------------------------------------------------- */
 #define BGTQ_DEC_K_MIXED 1        /* k_packed rows are in the nibble/raw mixed layout */
 #define BGTQ_DEC_V_NIBBLE 2       /* v_packed rows are 4-bit nibbles */
@@ -271,6 +291,17 @@ int bgtq_buffer_attn(const void* q, int64_t q_sb, int64_t q_sh,
                      int32_t ring_first, int32_t ring_size,
                      int32_t n_batch, int32_t n_q, int32_t n_kv,
                      float scale, float* buf_o, float* buf_lse, void* stream);
+
+/* bgtq_buffer_attn with the region sizes taken from a device-side token count, for captured graphs: with
+ * pos_dev non-NULL, *pos_dev + 1 tokens exist (the step's token included), the three-region policy with
+ * one-token blocks and a recent window of ring_size - 1 applies (n_sink_tokens / n_ring_tokens / ring_first
+ * are computed in the kernel and the three arguments are ignored). */
+int bgtq_buffer_attn_pos(const void* q, int64_t q_sb, int64_t q_sh,
+                     const void* k_buf, const void* v_buf, int64_t kb_sb, int64_t kb_sh,
+                     int32_t n_sink_tokens, int32_t n_ring_tokens, int32_t sink_cap,
+                     int32_t ring_first, int32_t ring_size,
+                     int32_t n_batch, int32_t n_q, int32_t n_kv,
+                     float scale, float* buf_o, float* buf_lse, const int32_t* pos_dev, void* stream);
 
 /* Merge split partials, undo V's rotation, fold in the fp16-buffer partial.
  *

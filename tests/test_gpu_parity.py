@@ -228,7 +228,7 @@ def test_combine_and_buffer_vs_oracle():
             np.testing.assert_allclose(bl[b, hq].cpu().numpy(), rl[0], atol=2e-5)
 
 
-@pytest.mark.parametrize("n_sink,window,bs", [(2, 5, 1), (3, 4, 3), (0, 6, 2)])
+@pytest.mark.parametrize("n_sink,window,bs", [(2, 5, 1), (3, 4, 3), (0, 6, 2), (0, 6, 1), (4, 3, 1)])
 def test_three_region_manager_vs_oracle(n_sink, window, bs):
     """fp16 sink + packed middle + fp16 recent ring: every decode step against the float64 oracle built
     from the same token stream (flush order of blockgtq/unaccelerated.py:226-233)."""
