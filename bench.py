@@ -197,10 +197,10 @@ def run_reference(args, w, name, rank, world):
 
 
 def run_seq_sharded(args, w, rank, world, dev):
-    """One long sequence cut into per-rank chunks: every layer replays one CUDA graph holding the local
-    split-KV decode + combine, one all-gather of the (O, LSE) messages and the merge of the ranks'
-    messages; the rank that owns the tail also appends the step's token.  Strong scaling: the total
-    context is fixed."""
+    """One long sequence cut into per-rank chunks: per layer the local split-KV decode + combine, one
+    exchange of the (O, LSE) messages and the merge of the ranks' messages; the rank that owns the tail also
+    appends the step's token; all layers of a step are one CUDA graph.  Strong scaling: the total context is
+    fixed."""
     import torch.distributed as dist
     from blockgtq_b200 import _lib
     from blockgtq_b200.layer import combine
@@ -213,33 +213,40 @@ def run_seq_sharded(args, w, rank, world, dev):
     mgr, gen = build_manager(w, dev, seed=1234, extra_tokens=n_total + 16, ctx=hi - lo)
     if world > 1:
         from blockgtq_b200.sharding import SequenceShard
-        transport = os.environ.get("BGTQ_SEQ_TRANSPORT", "p2p")      # peer-memory exchange; "nccl" = all-gather
+        transport = os.environ.get("BGTQ_SEQ_TRANSPORT", "nccl")     # "p2p" = the library's peer-memory exchange
         SequenceShard(mgr, owner=owner, transport=transport)
     qs = (torch.randn(n_total, L, B, n_q, 1, HD, generator=gen, device=dev) * 2).half()
     ks = torch.stack([torch.stack([synth_keys(gen, (B * n_kv, 1), w["theta"], dev).reshape(B, n_kv, 1, HD)
                                    for _ in range(L)]) for _ in range(n_total)])
     vs = torch.randn(n_total, L, B, n_kv, 1, HD, generator=gen, device=dev).half()
-    hq = torch.cat([qs, ks, vs], dim=3).cpu().pin_memory()
+    dq = torch.cat([qs, ks, vs], dim=3)                             # (steps, L, B, n_q + 2 n_kv, 1, hd) in HBM
+    hq = dq.cpu().pin_memory()
     hout = torch.empty(L, B, n_q, HD, dtype=torch.float16).pin_memory()
-    stage = torch.empty_like(hq[0, 0], device=dev)
+    g_all = mgr.static_qkv_all()
     step_no = [0]
-
-    def layer(li, q, k, v):
-        return mgr.append_and_attend(li, q, k, v)[:, :, 0]
+    # the whole decode step (all layers, the exchange included) as one CUDA graph on every rank
+    for li in range(L):
+        mgr.layer_step(li)
+    mgr.increment_seq_len()
+    torch.cuda.synchronize()
+    step_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(step_graph):
+        for li in range(L):
+            mgr.layer_step(li)
+    per_step = (5 if world > 1 else 3) * L
 
     def step_device():
-        s = step_no[0]
-        for li in range(L):
-            layer(li, qs[s, li], ks[s, li], vs[s, li])
+        g_all.copy_(dq[step_no[0]])
+        step_graph.replay()
+        _lib.count_launch(per_step)
         mgr.increment_seq_len()
         step_no[0] += 1
 
     def step_e2e():
-        s = step_no[0]
-        for li in range(L):
-            stage.copy_(hq[s, li], non_blocking=True)
-            out = layer(li, stage[:, :n_q], stage[:, n_q:n_q + n_kv], stage[:, n_q + n_kv:])
-            hout[li].copy_(out, non_blocking=True)
+        g_all.copy_(hq[step_no[0]], non_blocking=True)
+        step_graph.replay()
+        _lib.count_launch(per_step)
+        hout.copy_(mgr.static_outputs(), non_blocking=True)
         mgr.increment_seq_len()
         torch.cuda.synchronize()
         step_no[0] += 1
@@ -291,7 +298,7 @@ def run_seq_sharded(args, w, rank, world, dev):
             "config": {"workload": args.workload, "layers": L, "batch": B, "n_q": n_q, "n_kv": n_kv, "context": T,
                        "tokens_per_gpu": hi - lo, "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"],
                        "parallelism": f"sequence chunks x{world}, one exchange of (O, LSE) per layer "
-                                      f"({os.environ.get('BGTQ_SEQ_TRANSPORT', 'p2p') if world > 1 else 'none'})",
+                                      f"({os.environ.get('BGTQ_SEQ_TRANSPORT', 'nccl') if world > 1 else 'none'})",
                        "exchange_bytes_per_layer": B * n_q * (HD + 1) * 4,
                        "l2": "inputs larger than L2 (packed cache bytes per step >> 126 MB), no flush"},
             "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": gbs, "peak": peak,
