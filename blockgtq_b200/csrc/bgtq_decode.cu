@@ -2,10 +2,15 @@
 // (kernel b).  One launch covers every (batch, KV head, token split) of a layer.
 //
 // Mapping (per CTA = one split of one (batch, KV head)):
-//   * a producer warp streams 64-token tiles of the four cache arrays (packed
-//     K, K norms, packed V, V norms) into shared memory with 1-D bulk (TMA)
-//     copies completed on mbarriers, kStages deep;
-//   * four consumer warps each own 16 tokens of a tile.  Codes are expanded
+//   * 256-token tiles of the four cache arrays (packed K, K norms, packed V, V
+//     norms) are streamed into shared memory with 1-D bulk (TMA) copies
+//     completed on mbarriers, kStages deep.  There is no producer warp: the
+//     last of the eight warps to finish with a stage refills it (a counter in
+//     shared memory tells a warp that it is the last).  A ninth warp would
+//     cost more than its issue slots: 288 threads round up to 320 for register
+//     allocation, which holds a two-CTA kernel to 96 registers (with spills in
+//     the inner loop) where 256 threads get 128;
+//   * each warp owns 32 tokens of a tile.  Codes are expanded
 //     straight into tensor-core operand registers through small fp16x2 lookup
 //     tables in shared memory (one per K width segment, one for V), replicated
 //     per lane so lookups are bank-conflict free:
@@ -25,13 +30,15 @@
 #include "bgtq_common.cuh"
 #include "bgtq_plan.h"
 
+#include <type_traits>
+
 namespace bgtq {
 namespace {
 
 constexpr int kTileTok = 256;      // tokens per CTA tile
 constexpr int kWarpTok = 32;       // tokens per consumer warp and tile (two 16-token MMA row tiles)
 constexpr int kConsumerWarps = 8;
-constexpr int kThreads = 32 * (kConsumerWarps + 1);
+constexpr int kThreads = 32 * kConsumerWarps;
 constexpr int kStages = 2;
 constexpr int kMergeStride = 132;  // floats per query row in the end-of-CTA merge buffer
 // shared-memory layout (byte offsets from the start of dynamic shared memory)
@@ -119,7 +126,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     const int t0 = P.t_begin + split * P.chunk;
 
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-    uint64_t* empty = full + kStages;
+    unsigned int* done = reinterpret_cast<unsigned int*>(full + kStages);   // warps finished with a stage, ever
     uint16_t* cbk = reinterpret_cast<uint16_t*>(smem + kOffCbk);  // 512 K entries + 16 V entries
     // Per k-tile parameters, expanded once so the inner loop does no decoding:
     //   stepu[seg]     = per-segment constants (same for all lanes), see below
@@ -133,7 +140,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&full[i], 1);
-            mbar_init(&empty[i], kConsumerWarps);
+            done[i] = 0u;
         }
         mbar_fence_init();
     }
@@ -142,77 +149,73 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     const size_t bh_kn = (size_t)b * P.kn_sb + (size_t)h * P.kn_sh;
     const size_t bh_vp = (size_t)b * P.vp_sb + (size_t)h * P.vp_sh;
     const size_t bh_vn = (size_t)b * P.vn_sb + (size_t)h * P.vn_sh;
-    if (warp == kConsumerWarps) {
-        // ------------------------------ producer ------------------------------
-        // Starts streaming as soon as the preceding kernel's rows are visible; the consumer warps build
-        // their tables meanwhile.
+    // One lane streams tile `it` of the range [t0, t1) into its stage.
+    auto issue_tile = [&](int it, int t1, uint64_t pol) {
+        const int st = it % kStages;
+        const int t = t0 + it * kTileTok;
+        const int nt = min(kTileTok, t1 - t);
+        uint8_t* sb = smem + P.stage_off + (size_t)st * P.stage_bytes;
+        const uint8_t* s0 = P.kp + bh_kp + (size_t)t * P.kp_st;
+        const uint8_t* s1 = P.kn + bh_kn + (size_t)t * P.kn_st;
+        const uint8_t* s2 = P.vp + bh_vp + (size_t)t * P.vp_st;
+        const uint8_t* s3 = P.vn + bh_vn + (size_t)t * P.vn_st;
+        const uint32_t p0 = (uint32_t)(reinterpret_cast<uintptr_t>(s0) & 15u), p1 = (uint32_t)(reinterpret_cast<uintptr_t>(s1) & 15u);
+        const uint32_t p2 = (uint32_t)(reinterpret_cast<uintptr_t>(s2) & 15u), p3 = (uint32_t)(reinterpret_cast<uintptr_t>(s3) & 15u);
+        const uint32_t z0 = (p0 + (uint32_t)nt * P.kp_st + 15u) & ~15u, z1 = (p1 + (uint32_t)nt * P.kn_st + 15u) & ~15u;
+        const uint32_t z2 = (p2 + (uint32_t)nt * P.vp_st + 15u) & ~15u, z3 = (p3 + (uint32_t)nt * P.vn_st + 15u) & ~15u;
+        mbar_arrive_expect_tx(&full[st], z0 + z1 + z2 + z3);
+        bulk_g2s_hint(sb, s0 - p0, z0, &full[st], pol);
+        bulk_g2s_hint(sb + P.off_kn, s1 - p1, z1, &full[st], pol);
+        bulk_g2s_hint(sb + P.off_v, s2 - p2, z2, &full[st], pol);
+        bulk_g2s_hint(sb + P.off_vn, s3 - p3, z3, &full[st], pol);
+    };
+    const uint64_t pol = l2_evict_first_policy();
+    constexpr int kBuildThreads = kThreads - 32;
+    if (warp == kConsumerWarps - 1) {
+        // First tiles: one lane of the last warp starts streaming as soon as the preceding kernel's rows
+        // are visible, while the other warps build the tables.
         if (lane == 0) {
             grid_dependency_wait();
             const int t_end = P.pos_dev ? min(P.t_end, *P.pos_dev + P.pos_add) : P.t_end;
             const int t1 = min(t_end, t0 + P.chunk);
             const int n_tiles = (max(0, t1 - t0) + kTileTok - 1) / kTileTok;
-            const uint64_t pol = l2_evict_first_policy();
-            for (int it = 0; it < n_tiles; ++it) {
-                const int st = it % kStages, use = it / kStages;
-                if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
-                    if (P.status) atomicExch(P.status, kStatusWaitTimeout);
-                    break;
-                }
-                const int t = t0 + it * kTileTok;
-                const int nt = min(kTileTok, t1 - t);
-                uint8_t* sb = smem + P.stage_off + (size_t)st * P.stage_bytes;
-                const uint8_t* src[4] = {P.kp + bh_kp + (size_t)t * P.kp_st, P.kn + bh_kn + (size_t)t * P.kn_st,
-                                         P.vp + bh_vp + (size_t)t * P.vp_st, P.vn + bh_vn + (size_t)t * P.vn_st};
-                const uint32_t len[4] = {(uint32_t)nt * P.kp_st, (uint32_t)nt * P.kn_st, (uint32_t)nt * P.vp_st,
-                                         (uint32_t)nt * P.vn_st};
-                const uint32_t dst[4] = {0, P.off_kn, P.off_v, P.off_vn};
-                uint32_t sz[4], total = 0;
-                for (int c = 0; c < 4; ++c) {
-                    const uint32_t pre = (uint32_t)(reinterpret_cast<uintptr_t>(src[c]) & 15u);
-                    sz[c] = (pre + len[c] + 15u) & ~15u;
-                    total += sz[c];
-                }
-                mbar_arrive_expect_tx(&full[st], total);
-                for (int c = 0; c < 4; ++c) {
-                    const uint8_t* al = src[c] - (reinterpret_cast<uintptr_t>(src[c]) & 15u);
-                    bulk_g2s_hint(sb + dst[c], al, sz[c], &full[st], pol);
-                }
+            for (int it = 0; it < min(n_tiles, kStages); ++it) issue_tile(it, t1, pol);
+        }
+        __syncwarp();
+    } else {
+        // ------------------- tables (named barrier 2 = the building warps only) -------------------
+        {
+            const BgtqHeadDesc& d = P.desc[h];
+            for (int i = tid; i < 528; i += kBuildThreads) cbk[i] = i < 512 ? d.codebook[i] : d.v_lut[i - 512];
+        }
+        if (warp == 1 && lane < hp.n_seg) {   // per segment: {n_kt | kt/unit << 8 | pair << 16 | norm offset << 20,
+                                              //  first rotate, rotate step | pair stride << 8, scaled index mask}
+            const DecSegTbl tb = hp.seg[lane];
+            const uint32_t esh = tb.rep_shift + 2u;
+            const uint32_t mask = (tb.pair ? (1u << (2 * tb.sbits)) - 1u : (1u << tb.bw) - 1u) << esh;
+            stepu[lane] = make_uint4(tb.n_kt | ((uint32_t)tb.kt_per_unit << 8) | ((uint32_t)tb.pair << 16) |
+                                         ((uint32_t)tb.f16_norm << 17) | ((2u * lane) << 20),
+                                     esh, (4u * tb.sbits) | ((2u * tb.sbits) << 8), mask);
+        }
+        asm volatile("bar.sync 2, %0;" ::"n"(kBuildThreads) : "memory");
+        // Expand codebooks into lane-replicated fp16x2 tables.
+        for (int s = 0; s < hp.n_seg; ++s) {
+            const DecSegTbl tb = hp.seg[s];
+            const uint32_t cm = (1u << tb.bw) - 1u, smk = (1u << tb.sbits) - 1u;
+            for (uint32_t i = tid; i < tb.n_words; i += kBuildThreads) {
+                const uint32_t e = i >> tb.rep_shift;
+                uint32_t v;
+                if (tb.pair) v = cbk[tb.cb_off + ((e & smk) & cm)] | (uint32_t(cbk[tb.cb_off + ((e >> tb.sbits) & cm)]) << 16);
+                else v = cbk[tb.cb_off + (e & cm)];
+                lut[tb.word_off + i] = v;
             }
         }
-        return;
-    }
-    // ------------------- consumer warps: tables first (named barrier 1 = consumers only) -------------------
-    {
-        const BgtqHeadDesc& d = P.desc[h];
-        for (int i = tid; i < 528; i += kConsumerWarps * 32) cbk[i] = i < 512 ? d.codebook[i] : d.v_lut[i - 512];
-    }
-    if (warp == 1 && lane < hp.n_seg) {   // per segment: {n_kt | kt/unit << 8 | pair << 16 | norm offset << 20,
-                                          //  first rotate, rotate step | pair stride << 8, scaled index mask}
-        const DecSegTbl tb = hp.seg[lane];
-        const uint32_t esh = tb.rep_shift + 2u;
-        const uint32_t mask = (tb.pair ? (1u << (2 * tb.sbits)) - 1u : (1u << tb.bw) - 1u) << esh;
-        stepu[lane] = make_uint4(tb.n_kt | ((uint32_t)tb.kt_per_unit << 8) | ((uint32_t)tb.pair << 16) |
-                                     ((uint32_t)tb.f16_norm << 17) | ((2u * lane) << 20),
-                                 esh, (4u * tb.sbits) | ((2u * tb.sbits) << 8), mask);
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
-    // Expand codebooks into lane-replicated fp16x2 tables.
-    for (int s = 0; s < hp.n_seg; ++s) {
-        const DecSegTbl tb = hp.seg[s];
-        const uint32_t cm = (1u << tb.bw) - 1u, smk = (1u << tb.sbits) - 1u;
-        for (uint32_t i = tid; i < tb.n_words; i += kConsumerWarps * 32) {
-            const uint32_t e = i >> tb.rep_shift;
-            uint32_t v;
-            if (tb.pair) v = cbk[tb.cb_off + ((e & smk) & cm)] | (uint32_t(cbk[tb.cb_off + ((e >> tb.sbits) & cm)]) << 16);
-            else v = cbk[tb.cb_off + (e & cm)];
-            lut[tb.word_off + i] = v;
-        }
-    }
-    {
-        const uint32_t vm = (1u << P.plan.v_bits) - 1u, smk = (1u << VB) - 1u;
-        for (uint32_t i = tid; i < (uint32_t)P.plan.v_n_words; i += kConsumerWarps * 32) {
-            const uint32_t e = i >> VCfg<VB>::REP_SHIFT;
-            lut[hp.v_word_off + i] = cbk[512 + ((e & smk) & vm)] | (uint32_t(cbk[512 + ((e >> VB) & vm)]) << 16);
+        {
+            const uint32_t vm = (1u << P.plan.v_bits) - 1u, smk = (1u << VB) - 1u;
+            for (uint32_t i = tid; i < (uint32_t)P.plan.v_n_words; i += kBuildThreads) {
+                const uint32_t e = i >> VCfg<VB>::REP_SHIFT;
+                lut[hp.v_word_off + i] = cbk[512 + ((e & smk) & vm)] | (uint32_t(cbk[512 + ((e >> VB) & vm)]) << 16);
+            }
         }
     }
     grid_dependency_wait();
@@ -247,24 +250,212 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     // Per-CTA byte phases of the four arrays inside a stage (tiles advance every array by a multiple
-    // of 16 bytes), and this lane's row offsets.  K side: tokens tok0 + 8 i, i = 0..3.
+    // of 16 bytes), and this lane's row offsets for a warp whose first token in the tile is `base`.
+    // K side: tokens tok0 + 8 i; V side, row tile u: tokens tkv + 16u + {0, 1, 8, 9}.
     const uint32_t k_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.kp) + bh_kp + (size_t)t0 * P.kp_st) & 15u);
     const uint32_t kn_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.kn) + bh_kn + (size_t)t0 * P.kn_st) & 15u);
     const uint32_t v_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.vp) + bh_vp + (size_t)t0 * P.vp_st) & 15u);
     const uint32_t vn_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.vn) + bh_vn + (size_t)t0 * P.vn_st) & 15u);
-    const int tok0 = warp * kWarpTok + r;
-    const uint32_t k_off = k_pre + tok0 * P.kp_st;
-    const uint32_t k_row_al = k_off & ~3u, k_p0 = (k_off & 3u) << 3;
+    struct Rows {
+        int tok0, tkv;
+        uint32_t k_row_al, k_p0, kn_row, v_off, vn_row;
+    };
+    auto rows_for = [&](int base) {
+        Rows ra;
+        ra.tok0 = base + r;
+        const uint32_t k_off = k_pre + ra.tok0 * P.kp_st;
+        ra.k_row_al = k_off & ~3u;
+        ra.k_p0 = (k_off & 3u) << 3;
+        ra.kn_row = P.off_kn + kn_pre + ra.tok0 * P.kn_st;
+        ra.tkv = base + 2 * j;
+        ra.v_off = P.off_v + v_pre + ra.tkv * P.vp_st;
+        ra.vn_row = P.off_vn + vn_pre + ra.tkv * P.vn_st;
+        return ra;
+    };
+    const Rows rows_full = rows_for(warp * kWarpTok);
     const uint32_t k_row8 = 8u * P.kp_st, kn_row8 = 8u * P.kn_st;
-    const uint32_t kn_row = P.off_kn + kn_pre + tok0 * P.kn_st;
-    const int tkv = warp * kWarpTok + 2 * j;     // V side, row tile u: tokens tkv + 16u + {0, 1, 8, 9}
-    const uint32_t v_off = P.off_v + v_pre + tkv * P.vp_st;
-    const uint32_t vn_row = P.off_vn + vn_pre + tkv * P.vn_st;
 
     const uint32_t lane4 = (uint32_t)lane << 2;
     constexpr uint32_t kVSh = VCfg<VB>::REP_SHIFT + 2;
     const uint32_t vtbl = lut_rel + (hp.v_word_off << 2) + (lane4 & ((1u << kVSh) - 1u));
     const int n_seg = hp.n_seg;
+
+    // One warp's share of a tile: NU row tiles of 16 tokens starting at the warp's base token.  (Spreading a
+    // short last tile over the warps as single row tiles, NU = 1, measured no faster: the kernel is bound by
+    // the SM's instruction throughput, not by the slowest warp of a CTA.)
+    auto tile_body = [&](auto nu_tag, const Rows& ra, const uint32_t sb, const int nt) {
+        constexpr int NU = decltype(nu_tag)::value;
+        const int tok0 = ra.tok0, tkv = ra.tkv;
+        // ---------------- S^T = Khat . Qrot^T for NU 16-token row tiles ----------------
+        float S[NU][4];
+#pragma unroll
+        for (int u = 0; u < NU; ++u) S[u][0] = S[u][1] = S[u][2] = S[u][3] = 0.f;
+        const uint32_t rowK = sb + ra.k_row_al, rowN = sb + ra.kn_row, k_p0 = ra.k_p0;
+        int s = 0;
+        for (int sg = 0; sg < n_seg; ++sg) {
+            const uint4 su = stepu[sg];
+            const int n_kt = su.x & 0xFF, kpu = (su.x >> 8) & 0xFF;
+            const uint32_t mask = su.w, dr = su.z & 0xFFu, dp = su.z >> 8;
+            // Norm handling: bit-packed layout scales the fp32 dot product of a segment by its fp16
+            // norm; the nibble layout rounds centroid * norm to fp16 per element before the product
+            // (fused_packed_attention.py:1449-1452), so there the norm is folded into the operand.
+            const bool f16n = su.x & 0x20000u;
+            float nrm[2 * NU];
+            uint32_t n2[2 * NU];
+#pragma unroll
+            for (int i = 0; i < 2 * NU; ++i) {
+                const uint32_t nh = ld16(sm, rowN + (su.x >> 20) + i * kn_row8);
+                n2[i] = nh | (nh << 16);
+                nrm[i] = f16n ? 1.0f : __half2float(__ushort_as_half((unsigned short)nh));
+            }
+            float acc[NU][4];
+#pragma unroll
+            for (int u = 0; u < NU; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+            uint32_t cur[2 * NU];
+#pragma unroll
+            for (int i = 0; i < 2 * NU; ++i) cur[i] = 0u;
+            uint32_t r0 = su.y;
+            int left = 0;
+            for (int kt = 0; kt < n_kt; ++kt, ++s) {
+                const uint4 sl = stepl[s * 32 + lane];
+                if (left == 0) {        // next unit: 32 bits of this lane's run, one word per token
+                    const uint32_t pbit = k_p0 + sl.w;
+                    const uint32_t wa = rowK + ((pbit >> 5) << 2);
+#pragma unroll
+                    for (int i = 0; i < 2 * NU; ++i)
+                        cur[i] = __funnelshift_r(ld32(sm, wa + i * k_row8), ld32(sm, wa + i * k_row8 + 4), pbit);
+                    left = kpu;
+                    r0 = su.y;
+                }
+                --left;
+                const uint32_t tb = sl.z;
+                uint32_t lo[2 * NU], hi[2 * NU];   // fp16x2 of codes (0,1) and (2,3) of this k-tile, per token
+                if (su.x & 0x10000u) {
+                    const uint32_t r1 = r0 - dp;
+#pragma unroll
+                    for (int i = 0; i < 2 * NU; ++i) {
+                        lo[i] = ld32(sm, (rotl32(cur[i], r0) & mask) | tb);
+                        hi[i] = ld32(sm, (rotl32(cur[i], r1) & mask) | tb);
+                    }
+                } else {                   // raw bytes, one code per lookup
+#pragma unroll
+                    for (int i = 0; i < 2 * NU; ++i) {
+                        const uint32_t c0 = ld32(sm, (rotl32(cur[i], r0) & mask) | tb);
+                        const uint32_t c1 = ld32(sm, (rotl32(cur[i], r0 + 24u) & mask) | tb);
+                        const uint32_t c2 = ld32(sm, (rotl32(cur[i], r0 + 16u) & mask) | tb);
+                        const uint32_t c3 = ld32(sm, (rotl32(cur[i], r0 + 8u) & mask) | tb);
+                        lo[i] = c0 | (c1 << 16);
+                        hi[i] = c2 | (c3 << 16);
+                    }
+                }
+                r0 -= dr;
+                if (f16n) {
+#pragma unroll
+                    for (int i = 0; i < 2 * NU; ++i) {
+                        lo[i] = hmul2_u32(lo[i], n2[i]);
+                        hi[i] = hmul2_u32(hi[i], n2[i]);
+                    }
+                }
+                const uint32_t bq[2] = {sl.x, sl.y};
+#pragma unroll
+                for (int u = 0; u < NU; ++u) {
+                    const uint32_t a[4] = {lo[2 * u], lo[2 * u + 1], hi[2 * u], hi[2 * u + 1]};
+                    mma_16816(acc[u], a, bq);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < NU; ++u) {
+                S[u][0] = fmaf(nrm[2 * u], acc[u][0], S[u][0]);
+                S[u][1] = fmaf(nrm[2 * u], acc[u][1], S[u][1]);
+                S[u][2] = fmaf(nrm[2 * u + 1], acc[u][2], S[u][2]);
+                S[u][3] = fmaf(nrm[2 * u + 1], acc[u][3], S[u][3]);
+            }
+        }
+        // ---------------- online softmax (log2 domain) over the warp's tokens ----------------
+        float sv[NU][4];
+        float x0 = -INFINITY, x1 = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < NU; ++u) {
+            const bool okA = tok0 + 16 * u < nt, okB = tok0 + 16 * u + 8 < nt;
+            sv[u][0] = okA ? S[u][0] * P.scale_log2 : -INFINITY;
+            sv[u][1] = okA ? S[u][1] * P.scale_log2 : -INFINITY;
+            sv[u][2] = okB ? S[u][2] * P.scale_log2 : -INFINITY;
+            sv[u][3] = okB ? S[u][3] * P.scale_log2 : -INFINITY;
+            x0 = fmaxf(x0, fmaxf(sv[u][0], sv[u][2]));
+            x1 = fmaxf(x1, fmaxf(sv[u][1], sv[u][3]));
+        }
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, o));
+            x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, o));
+        }
+        const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+        const float z0 = n0 == -INFINITY ? 0.f : n0, z1 = n1 == -INFINITY ? 0.f : n1;
+        const float al0 = exp2f(m0 - z0), al1 = exp2f(m1 - z1);
+        m0 = n0;
+        m1 = n1;
+        uint32_t pf[NU][2];
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int u = 0; u < NU; ++u) {
+            const float p0 = exp2f(sv[u][0] - z0), p1 = exp2f(sv[u][1] - z1);
+            const float p2 = exp2f(sv[u][2] - z0), p3 = exp2f(sv[u][3] - z1);
+            ps0 += p0 + p2;
+            ps1 += p1 + p3;
+            pf[u][0] = movmatrix_trans(pack_half2(p0, p1));
+            pf[u][1] = movmatrix_trans(pack_half2(p2, p3));
+        }
+        l0 = fmaf(l0, al0, ps0);
+        l1 = fmaf(l1, al1, ps1);
+        if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                O[i][0] *= al0;
+                O[i][1] *= al1;
+                O[i][2] *= al0;
+                O[i][3] *= al1;
+            }
+        }
+
+        // ---------------- O^T += Vhat^T . P^T ----------------
+        // Row tile u, this lane: tokens tkv+16u+{0,1} (pair AB) and +{8,9} (pair CD); dims 16r .. 16r+15.
+        constexpr uint32_t M = VCfg<VB>::M, G = VCfg<VB>::GROUPS, FW = 2 * VB;
+        constexpr uint32_t IMS = ((1u << FW) - 1u) << kVSh;
+        constexpr int PER = 8 / G;   // k-tiles (dim pairs) per 32-bit group
+#pragma unroll
+        for (int u = 0; u < NU; ++u) {
+            uint32_t gA[2], gB[2], gC[2], gD[2];
+            const uint32_t rv = sb + ra.v_off + 16u * u * P.vp_st;
+            const uint32_t base = rv & ~3u, bit = ((rv & 3u) << 3) + 16u * VB * r;
+            load_v16<VB>(sm, base, bit, gA);
+            load_v16<VB>(sm, base, bit + 8u * P.vp_st, gB);
+            load_v16<VB>(sm, base, bit + 64u * P.vp_st, gC);
+            load_v16<VB>(sm, base, bit + 72u * P.vp_st, gD);
+            const int tq = tkv + 16 * u;
+            const uint32_t rn = sb + ra.vn_row + 16u * u * P.vn_st;
+            const uint32_t hA = tq + 0 < nt ? ld16(sm, rn) : 0u;
+            const uint32_t hB = tq + 1 < nt ? ld16(sm, rn + P.vn_st) : 0u;
+            const uint32_t hC = tq + 8 < nt ? ld16(sm, rn + 8 * P.vn_st) : 0u;
+            const uint32_t hD = tq + 9 < nt ? ld16(sm, rn + 9 * P.vn_st) : 0u;
+            const uint32_t nab = hA | (hB << 16), ncd = hC | (hD << 16);
+#pragma unroll
+            for (int g = 0; g < (int)G; ++g) {
+                const uint32_t xab = (gA[g] & M) | ((gB[g] & M) << VB), yab = ((gA[g] >> VB) & M) | (gB[g] & (M << VB));
+                const uint32_t xcd = (gC[g] & M) | ((gD[g] & M) << VB), ycd = ((gC[g] >> VB) & M) | (gD[g] & (M << VB));
+#pragma unroll
+                for (int k = 0; k < PER; ++k) {
+                    // index pre-scaled by the entry stride: rotate so the field sits at bit kVSh
+                    const uint32_t rt = (32u + kVSh - FW * k) & 31u;
+                    uint32_t a[4];
+                    a[0] = hmul2_u32(ld32(sm, (rotl32(xab, rt) & IMS) | vtbl), nab);
+                    a[1] = hmul2_u32(ld32(sm, (rotl32(yab, rt) & IMS) | vtbl), nab);
+                    a[2] = hmul2_u32(ld32(sm, (rotl32(xcd, rt) & IMS) | vtbl), ncd);
+                    a[3] = hmul2_u32(ld32(sm, (rotl32(ycd, rt) & IMS) | vtbl), ncd);
+                    mma_16816(O[g * PER + k], a, pf[u]);
+                }
+            }
+        }
+    };
 
     for (int it = 0; it < n_tiles; ++it) {
         const int st = it % kStages, use = it / kStages;
@@ -274,177 +465,21 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const __grid_consta
         }
         const int nt = min(kTileTok, t1 - (t0 + it * kTileTok));
         const uint32_t sb = P.stage_off + st * P.stage_bytes;
-
-        if (warp * kWarpTok < nt) {
-            // ---------------- S^T = Khat . Qrot^T for two 16-token row tiles ----------------
-            float S[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            const uint32_t rowK = sb + k_row_al, rowN = sb + kn_row;
-            int s = 0;
-            for (int sg = 0; sg < n_seg; ++sg) {
-                const uint4 su = stepu[sg];
-                const int n_kt = su.x & 0xFF, kpu = (su.x >> 8) & 0xFF;
-                const uint32_t mask = su.w, dr = su.z & 0xFFu, dp = su.z >> 8;
-                // Norm handling: bit-packed layout scales the fp32 dot product of a segment by its fp16
-                // norm; the nibble layout rounds centroid * norm to fp16 per element before the product
-                // (fused_packed_attention.py:1449-1452), so there the norm is folded into the operand.
-                const bool f16n = su.x & 0x20000u;
-                float nrm[4];
-                uint32_t n2[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t nh = ld16(sm, rowN + (su.x >> 20) + i * kn_row8);
-                    n2[i] = nh | (nh << 16);
-                    nrm[i] = f16n ? 1.0f : __half2float(__ushort_as_half((unsigned short)nh));
-                }
-                float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-                uint32_t cur[4] = {0u, 0u, 0u, 0u};
-                uint32_t r0 = su.y;
-                int left = 0;
-                for (int kt = 0; kt < n_kt; ++kt, ++s) {
-                    const uint4 sl = stepl[s * 32 + lane];
-                    if (left == 0) {        // next unit: 32 bits of this lane's run, four tokens
-                        const uint32_t pbit = k_p0 + sl.w;
-                        const uint32_t wa = rowK + ((pbit >> 5) << 2);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            cur[i] = __funnelshift_r(ld32(sm, wa + i * k_row8), ld32(sm, wa + i * k_row8 + 4), pbit);
-                        left = kpu;
-                        r0 = su.y;
-                    }
-                    --left;
-                    const uint32_t tb = sl.z;
-                    uint32_t lo[4], hi[4];   // fp16x2 of codes (0,1) and (2,3) of this k-tile, per token
-                    if (su.x & 0x10000u) {
-                        const uint32_t r1 = r0 - dp;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            lo[i] = ld32(sm, (rotl32(cur[i], r0) & mask) | tb);
-                            hi[i] = ld32(sm, (rotl32(cur[i], r1) & mask) | tb);
-                        }
-                    } else {                   // raw bytes, one code per lookup
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const uint32_t c0 = ld32(sm, (rotl32(cur[i], r0) & mask) | tb);
-                            const uint32_t c1 = ld32(sm, (rotl32(cur[i], r0 + 24u) & mask) | tb);
-                            const uint32_t c2 = ld32(sm, (rotl32(cur[i], r0 + 16u) & mask) | tb);
-                            const uint32_t c3 = ld32(sm, (rotl32(cur[i], r0 + 8u) & mask) | tb);
-                            lo[i] = c0 | (c1 << 16);
-                            hi[i] = c2 | (c3 << 16);
-                        }
-                    }
-                    r0 -= dr;
-                    if (f16n) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            lo[i] = hmul2_u32(lo[i], n2[i]);
-                            hi[i] = hmul2_u32(hi[i], n2[i]);
-                        }
-                    }
-                    const uint32_t bq[2] = {sl.x, sl.y};
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const uint32_t a[4] = {lo[2 * u], lo[2 * u + 1], hi[2 * u], hi[2 * u + 1]};
-                        mma_16816(acc[u], a, bq);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    S[u][0] = fmaf(nrm[2 * u], acc[u][0], S[u][0]);
-                    S[u][1] = fmaf(nrm[2 * u], acc[u][1], S[u][1]);
-                    S[u][2] = fmaf(nrm[2 * u + 1], acc[u][2], S[u][2]);
-                    S[u][3] = fmaf(nrm[2 * u + 1], acc[u][3], S[u][3]);
-                }
-            }
-            // ---------------- online softmax (log2 domain) over the 32 tokens ----------------
-            float sv[2][4];
-            float x0 = -INFINITY, x1 = -INFINITY;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const bool okA = tok0 + 16 * u < nt, okB = tok0 + 16 * u + 8 < nt;
-                sv[u][0] = okA ? S[u][0] * P.scale_log2 : -INFINITY;
-                sv[u][1] = okA ? S[u][1] * P.scale_log2 : -INFINITY;
-                sv[u][2] = okB ? S[u][2] * P.scale_log2 : -INFINITY;
-                sv[u][3] = okB ? S[u][3] * P.scale_log2 : -INFINITY;
-                x0 = fmaxf(x0, fmaxf(sv[u][0], sv[u][2]));
-                x1 = fmaxf(x1, fmaxf(sv[u][1], sv[u][3]));
-            }
-#pragma unroll
-            for (int o = 4; o < 32; o <<= 1) {
-                x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, o));
-                x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, o));
-            }
-            const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
-            const float z0 = n0 == -INFINITY ? 0.f : n0, z1 = n1 == -INFINITY ? 0.f : n1;
-            const float al0 = exp2f(m0 - z0), al1 = exp2f(m1 - z1);
-            m0 = n0;
-            m1 = n1;
-            uint32_t pf[2][2];
-            float ps0 = 0.f, ps1 = 0.f;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const float p0 = exp2f(sv[u][0] - z0), p1 = exp2f(sv[u][1] - z1);
-                const float p2 = exp2f(sv[u][2] - z0), p3 = exp2f(sv[u][3] - z1);
-                ps0 += p0 + p2;
-                ps1 += p1 + p3;
-                pf[u][0] = movmatrix_trans(pack_half2(p0, p1));
-                pf[u][1] = movmatrix_trans(pack_half2(p2, p3));
-            }
-            l0 = fmaf(l0, al0, ps0);
-            l1 = fmaf(l1, al1, ps1);
-            if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    O[i][0] *= al0;
-                    O[i][1] *= al1;
-                    O[i][2] *= al0;
-                    O[i][3] *= al1;
-                }
-            }
-
-            // ---------------- O^T += Vhat^T . P^T ----------------
-            // Row tile u, this lane: tokens tkv+16u+{0,1} (pair AB) and +{8,9} (pair CD); dims 16r .. 16r+15.
-            constexpr uint32_t M = VCfg<VB>::M, G = VCfg<VB>::GROUPS, FW = 2 * VB;
-            constexpr uint32_t IMS = ((1u << FW) - 1u) << kVSh;
-            constexpr int PER = 8 / G;   // k-tiles (dim pairs) per 32-bit group
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                uint32_t gA[2], gB[2], gC[2], gD[2];
-                const uint32_t rv = sb + v_off + 16u * u * P.vp_st;
-                const uint32_t base = rv & ~3u, bit = ((rv & 3u) << 3) + 16u * VB * r;
-                load_v16<VB>(sm, base, bit, gA);
-                load_v16<VB>(sm, base, bit + 8u * P.vp_st, gB);
-                load_v16<VB>(sm, base, bit + 64u * P.vp_st, gC);
-                load_v16<VB>(sm, base, bit + 72u * P.vp_st, gD);
-                const int tq = tkv + 16 * u;
-                const uint32_t rn = sb + vn_row + 16u * u * P.vn_st;
-                const uint32_t hA = tq + 0 < nt ? ld16(sm, rn) : 0u;
-                const uint32_t hB = tq + 1 < nt ? ld16(sm, rn + P.vn_st) : 0u;
-                const uint32_t hC = tq + 8 < nt ? ld16(sm, rn + 8 * P.vn_st) : 0u;
-                const uint32_t hD = tq + 9 < nt ? ld16(sm, rn + 9 * P.vn_st) : 0u;
-                const uint32_t nab = hA | (hB << 16), ncd = hC | (hD << 16);
-#pragma unroll
-                for (int g = 0; g < (int)G; ++g) {
-                    const uint32_t xab = (gA[g] & M) | ((gB[g] & M) << VB), yab = ((gA[g] >> VB) & M) | (gB[g] & (M << VB));
-                    const uint32_t xcd = (gC[g] & M) | ((gD[g] & M) << VB), ycd = ((gC[g] >> VB) & M) | (gD[g] & (M << VB));
-#pragma unroll
-                    for (int k = 0; k < PER; ++k) {
-                        // index pre-scaled by the entry stride: rotate so the field sits at bit kVSh
-                        const uint32_t rt = (32u + kVSh - FW * k) & 31u;
-                        uint32_t a[4];
-                        a[0] = hmul2_u32(ld32(sm, (rotl32(xab, rt) & IMS) | vtbl), nab);
-                        a[1] = hmul2_u32(ld32(sm, (rotl32(yab, rt) & IMS) | vtbl), nab);
-                        a[2] = hmul2_u32(ld32(sm, (rotl32(xcd, rt) & IMS) | vtbl), ncd);
-                        a[3] = hmul2_u32(ld32(sm, (rotl32(ycd, rt) & IMS) | vtbl), ncd);
-                        mma_16816(O[g * PER + k], a, pf[u]);
-                    }
-                }
+        if (warp * kWarpTok < nt) tile_body(std::integral_constant<int, 2>{}, rows_full, sb, nt);
+        __syncwarp();
+        // Release the stage; the last warp to do so streams the tile that reuses it.  The counter only ever
+        // grows: after `use + 1` rounds of this stage all warps have added to it that many times.
+        if (lane == 0 && it + kStages < n_tiles) {
+            __threadfence_block();
+            if (atomicAdd(&done[st], 1u) == (unsigned)(use + 1) * kConsumerWarps - 1u) {
+                __threadfence_block();
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue_tile(it + kStages, t1, pol);
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[st]);
     }
 
-    // ---------------- merge the four warps, write the split's partial ----------------
+    // ---------------- merge the warps, write the split's partial ----------------
 #pragma unroll
     for (int o = 4; o < 32; o <<= 1) {
         l0 += __shfl_xor_sync(0xffffffffu, l0, o);
