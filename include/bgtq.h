@@ -84,6 +84,8 @@ const char* bgtq_error_string(int code);       /* host pointer to a static strin
 #define BGTQ_ENC_SKIP_V 16
 #define BGTQ_ENC_FORCE_SIMT 32  /* always use the small-batch fp32 kernel (>= 64 rows normally use tensor cores) */
 #define BGTQ_ENC_PROGRAMMATIC 64  /* bgtq_step_prepare only: programmatic dependent launch, see below */
+#define BGTQ_ENC_TCGEN05 128      /* bulk encode: run the rotation with tcgen05.mma and tensor-memory accumulators
+                                   * (128-row tiles; packed K rows up to 124 bytes; otherwise ignored) */
 
 /* Programmatic dependent launch (BGTQ_ENC_PROGRAMMATIC, BGTQ_DEC_PROGRAMMATIC,
  * BGTQ_COMBINE_PROGRAMMATIC).  The kernel is launched with CUDA's programmatic
@@ -130,6 +132,10 @@ int bgtq_encode(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v
                 void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
                 uint8_t* k_codes, uint8_t* v_codes,
                 int32_t flags, const int32_t* pos_dev, void* stream);
+
+/* Sticky device-side status of the BGTQ_ENC_TCGEN05 path on the current device: 0, or 1 after a wait for
+ * the tensor cores ran out (the rows of that launch are then incomplete).  Synchronises the device. */
+int bgtq_encode_tcgen05_status(void);
 
 /* Rotate decode queries into the packed-K basis:
  * q_rot[b, hq, p] = fp16( sum_j fp32(q[b, hq, head_perm[j]]) * rot_k[h][j][p] ),

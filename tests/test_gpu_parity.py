@@ -315,8 +315,9 @@ def test_production_cache_matches_reference():
 @pytest.mark.parametrize("case", ["a3_1to8", "a4_rt1", "u3"])
 @pytest.mark.parametrize("mixed", [False, True])
 def test_encoder_tensor_core_and_fp32_paths_vs_oracle(case, mixed):
-    """Bulk row counts run the tensor-core encoder, small ones (or BGTQ_ENC_FORCE_SIMT) the fp32
-    one.  Both must give the oracle's codes off bin edges, and bytes that are the exact packing
+    """Bulk row counts run the tensor-core encoder (warp MMA by default, tcgen05 + tensor memory with
+    BGTQ_ENC_TCGEN05), small ones (or BGTQ_ENC_FORCE_SIMT) the fp32 one.  All must give the oracle's
+    codes off bin edges, and bytes that are the exact packing
     of the codes each chose; rows land at the requested slot offset; ragged tile tails."""
     from blockgtq_b200 import _lib
     from blockgtq_b200.layer import encode
@@ -330,7 +331,7 @@ def test_encoder_tensor_core_and_fp32_paths_vs_oracle(case, mixed):
     k[2, 1, 11] *= 1e-4
     base = (_lib.ENC_K_MIXED | _lib.ENC_V_NIBBLE) if mixed else 0
     outs = []
-    for extra in (0, _lib.ENC_FORCE_SIMT):
+    for extra in (0, _lib.ENC_FORCE_SIMT, _lib.ENC_TCGEN05):
         kb = lt.max_mixed_bytes if mixed else lt.max_tpb
         kp = torch.full((B, n_kv, t0 + S + 2, kb), 0xEE, dtype=torch.uint8, device=DEV)
         kn = torch.full((B, n_kv, t0 + S + 2, lt.max_ng), -1.0, dtype=torch.float32, device=DEV)
@@ -368,8 +369,10 @@ def test_encoder_tensor_core_and_fp32_paths_vs_oracle(case, mixed):
                 want = O.pack_nibble4(vc[b, h]) if mixed else O.pack_v(vc[b, h], vt.bits)
                 assert np.array_equal(vrows, want)
     # the two paths agree with each other except on bin edges (already bounded above), norms to fp32 noise
-    np.testing.assert_allclose(outs[0][1], outs[1][1], rtol=1e-5, atol=1e-30)
-    assert (outs[0][4] != outs[1][4]).mean() < 2e-3
+    assert _lib.lib().bgtq_encode_tcgen05_status() == 0
+    for other in outs[1:]:
+        np.testing.assert_allclose(outs[0][1], other[1], rtol=1e-5, atol=1e-30)
+        assert (outs[0][4] != other[4]).mean() < 2e-3
 
 
 def test_combine_ranks_matches_single_range():
@@ -534,7 +537,7 @@ def test_bulk_encoder_rows_that_wrap_batches():
     k = torch.stack([torch.stack([synth_head(gen, S, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
     v = torch.randn(B, n_kv, S, HD, generator=gen).half().to(DEV)
     outs = []
-    for extra in (0, _lib.ENC_FORCE_SIMT):
+    for extra in (0, _lib.ENC_FORCE_SIMT, _lib.ENC_TCGEN05):
         kp = torch.zeros(B, n_kv, S + 4, lt.max_tpb, dtype=torch.uint8, device=DEV)
         kn = torch.zeros(B, n_kv, S + 4, lt.max_ng, dtype=torch.float16, device=DEV)
         vp = torch.zeros(B, n_kv, S + 4, lt.vpb, dtype=torch.uint8, device=DEV)
@@ -543,16 +546,19 @@ def test_bulk_encoder_rows_that_wrap_batches():
         encode(lt, k, v, 2, kp, kn, vp, vn, flags=extra, k_codes=kc)
         torch.cuda.synchronize()
         outs.append((kp.cpu().numpy(), kn.cpu().numpy(), vp.cpu().numpy(), vn.cpu().numpy(), kc.cpu().numpy()))
-    a, b = outs
-    assert (a[4] != b[4]).mean() < 2e-3
-    if np.array_equal(a[4], b[4]):
-        assert np.array_equal(a[0], b[0])
-    assert (a[2] != b[2]).mean() < 2e-3
-    np.testing.assert_allclose(a[1].astype(np.float32), b[1].astype(np.float32), rtol=2e-3, atol=1e-6)
-    for h in range(n_kv):
-        for bb in range(B):
-            assert np.array_equal(a[0][bb, h, 2:2 + S], O.pack_k(a[4][bb, h], tabs[h][0].segments, lt.max_tpb))
-    assert (a[0][:, :, :2] == 0).all() and (a[0][:, :, 2 + S:] == 0).all()
+    assert _lib.lib().bgtq_encode_tcgen05_status() == 0
+    b = outs[1]
+    for a in (outs[0], outs[2]):       # 133 rows: the tcgen05 path runs one full 128-row tile and a 5-row tail
+        assert (a[4] != b[4]).mean() < 2e-3
+        if np.array_equal(a[4], b[4]):
+            assert np.array_equal(a[0], b[0])
+        assert (a[2] != b[2]).mean() < 2e-3
+        np.testing.assert_allclose(a[1].astype(np.float32), b[1].astype(np.float32), rtol=2e-3, atol=1e-6)
+        np.testing.assert_allclose(a[3].astype(np.float32), b[3].astype(np.float32), rtol=2e-3, atol=1e-6)
+        for h in range(n_kv):
+            for bb in range(B):
+                assert np.array_equal(a[0][bb, h, 2:2 + S], O.pack_k(a[4][bb, h], tabs[h][0].segments, lt.max_tpb))
+        assert (a[0][:, :, :2] == 0).all() and (a[0][:, :, 2 + S:] == 0).all()
 
 
 @pytest.mark.parametrize("gqa,S_q,offset", [(1, 1, 300), (1, 130, 0), (8, 1, 0)])
