@@ -9,11 +9,13 @@
 //     8-row x 16-byte core matrices, 128 B apart along k and 2048 B apart along rows;
 //   * one thread issues 16 tcgen05.mma (M = 128, N = 128, K = 16): x . hi into tensor-memory columns
 //     [0, 128) and x . lo into [128, 256), then commits them to an mbarrier;
-//   * thread t owns row t of the tile: tensor-memory lane t holds its 128 rotated values, which it reads
-//     with tcgen05.ld, scales by 1 / group norm, bins through the code tables and writes as bytes; the
-//     packing of a row is then a per-thread walk over the head's pack tasks;
-//   * 110 KB of shared memory and 256 tensor-memory columns per CTA: two CTAs per SM, so one CTA's loads
-//     and product overlap the other's quantisation.
+//   * tensor-memory lane r holds the 128 rotated values of row r.  Two threads serve a row (threads r and
+//     r + 128: warps w and w + 4 may read the same 32 lanes): each reads half of the columns with
+//     tcgen05.ld, scales by 1 / group norm, bins through the code tables and writes code bytes; the pack
+//     tasks of the row are shared between the pair the same way.  Loads, norms and the copy of the packed
+//     rows to the cache are warp-cooperative over 16 rows per warp;
+//   * 110 KB of shared memory and 256 tensor-memory columns per CTA: two CTAs (16 warps) per SM, so one
+//     CTA's loads and product overlap the other's quantisation.
 // Every wait is bounded; tensor memory is released on every path out of the kernel.
 #include "bgtq_common.cuh"
 #include "bgtq_encode_params.cuh"
@@ -24,7 +26,7 @@ __device__ int g_t5_status = 0;
 
 namespace {
 
-constexpr int kT5Rows = 128;                  // rows per tile = tensor-memory lanes = threads
+constexpr int kT5Rows = 128;                  // rows per tile = tensor-memory lanes; two threads per row
 constexpr int kT5CodeLd = 132;                // bytes per code row: rows of consecutive lanes fall in distinct banks
 constexpr int kT5StageOff = kT5Rows * kT5CodeLd;
 constexpr int kT5TileBytes = kT5Rows * kHD * 2;
@@ -118,7 +120,7 @@ __device__ __forceinline__ uint32_t t5_squeeze4(uint32_t w, int bw) {
 __device__ void t5_setup(T5Smem& S, const EncParams& P, const BgtqHeadDesc& d, bool is_v, int h) {
     const int tid = threadIdx.x;
     const float* W = (is_v ? P.rot_v : P.rot_k) + (size_t)h * kHD * kHD;
-    for (int i = tid; i < kHD * kHD; i += kT5Rows) {
+    for (int i = tid; i < kHD * kHD; i += 2 * kT5Rows) {
         const int k = i >> 7, n = i & 127;          // W[k][n], coalesced over n; operand row = output position n
         const float w = __ldg(W + i);
         const __half hi = __float2half_rn(w);
@@ -126,8 +128,8 @@ __device__ void t5_setup(T5Smem& S, const EncParams& P, const BgtqHeadDesc& d, b
         *reinterpret_cast<__half*>(S.w_hi + o) = hi;
         *reinterpret_cast<__half*>(S.w_lo + o) = __float2half_rn((w - __half2float(hi)) * kT5LoScale);
     }
-    for (int i = tid; i < BGTQ_MAX_SEGMENTS * BGTQ_N_BINS; i += kT5Rows) S.code_lut[i >> 8][i & 255] = d.code_lut[i >> 8][i & 255];
-    for (int i = tid; i < 512; i += kT5Rows) S.kcent[i] = d.k_cents[i];
+    for (int i = tid; i < BGTQ_MAX_SEGMENTS * BGTQ_N_BINS; i += 2 * kT5Rows) S.code_lut[i >> 8][i & 255] = d.code_lut[i >> 8][i & 255];
+    for (int i = tid; i < 512; i += 2 * kT5Rows) S.kcent[i] = d.k_cents[i];
     if (tid < kHD) S.inv_perm[d.head_perm[tid]] = (uint8_t)tid;
     if (tid < kHD / 2) {
         const int g = d.group_of[2 * tid];
@@ -169,9 +171,10 @@ __device__ void t5_setup(T5Smem& S, const EncParams& P, const BgtqHeadDesc& d, b
 
 template <bool IS_V>
 __device__ __forceinline__ void t5_role(T5Smem& S, const EncParams& P, const int h, const int role_cta, const int role_ctas,
-                                        int* row_b, int* row_s) {
+                                        int64_t* row_src, int64_t* row_dst) {
     constexpr bool is_v = IS_V;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row = tid & (kT5Rows - 1), half = tid >> 7;    // two threads per row: the halves split columns and tasks
     const int n_rows = P.n_batch * P.n_tok;                  // the launcher checks that this fits
     const int n_tiles = (n_rows + kT5Rows - 1) / kT5Rows;
     const int t0 = P.pos_dev ? *P.pos_dev : P.t0;
@@ -185,8 +188,8 @@ __device__ __forceinline__ void t5_role(T5Smem& S, const EncParams& P, const int
     uint8_t* const out_base = is_v ? P.vp + h * P.vp_sh : P.kp + h * P.kp_sh;
     const int64_t o_sb = is_v ? P.vp_sb : P.kp_sb, o_st = is_v ? P.vp_st : P.kp_st;
     const uint32_t tile_u32 = smem_u32(S.tile), whi_u32 = smem_u32(S.w_hi), wlo_u32 = smem_u32(S.w_lo);
-    const uint32_t tmem_lane = S.tmem_base + ((uint32_t)(warp * 32) << 16);
-    const uint32_t my_row = (uint32_t)((tid >> 3) * 2048 + (tid & 7) * 16);      // this thread's row inside the operand tile
+    // warps w and w + 4 read the same 32 tensor-memory lanes (rows), different columns
+    const uint32_t tmem_lane = S.tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
 
     // packed positions of the 8 input columns this lane moves during the load (K only)
     uint32_t koff[8];
@@ -198,29 +201,42 @@ __device__ __forceinline__ void t5_role(T5Smem& S, const EncParams& P, const int
             koff[c] = (dp >> 3) * 128u + (dp & 7u) * 2u;
         }
     }
+    // V with at most 7 boundaries (1-3 bits): boundaries live in registers, code = number of boundaries below y
+    float vb[7];
+    bool v_small = false;
+    if (is_v) {
+        v_small = !(S.vbounds[7] < INFINITY);
+#pragma unroll
+        for (int i = 0; i < 7; ++i) vb[i] = S.vbounds[i];
+    }
 
     int it = 0;
     for (int tl = role_cta; tl < n_tiles; tl += role_ctas, ++it) {
         const int n0 = tl * kT5Rows;
-        {   // (batch entry, token) of this thread's row; -1 past the end
-            const int n = n0 + tid;
-            const int b = n < n_rows ? n / P.n_tok : -1;
-            row_b[tid] = b;
-            row_s[tid] = n < n_rows ? n - b * P.n_tok : 0;
+        // ---- a warp loads and reduces its own 16 rows ----
+        if (lane < 16) {   // source / destination offsets of row 16 warp + lane; -1 past the end
+            const int rr = 16 * warp + lane, n = n0 + rr;
+            int64_t so = -1, dof = -1;
+            if (n < n_rows) {
+                const int b = n / P.n_tok, s = n - b * P.n_tok;
+                so = b * s_sb + s * s_ss;
+                dof = b * o_sb + (int64_t)(t0 + s) * o_st;
+            }
+            row_src[rr] = so;
+            row_dst[rr] = dof;
         }
-        __syncwarp();       // a warp loads, reduces and stores its own 32 rows
-        // ---- load the warp's 32 rows, 16 bytes per lane and step ----
+        __syncwarp();
         // V: lane -> row (lane & 7) of an 8-row group, chunk 4 (q & 3) + (lane >> 3): eight lanes fill one 128-byte
         //    core matrix, so the shared stores are conflict free and a row is read 64 bytes at a time.
         // K: lane -> chunk (lane & 15) of rows 2q + (lane >> 4): the lane's eight packed positions stay fixed.
-#pragma unroll 4
-        for (int q = 0; q < 16; ++q) {
-            const int row = 32 * warp + (is_v ? (q >> 2) * 8 + (lane & 7) : 2 * q + (lane >> 4));
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int rr = 16 * warp + (is_v ? (q >> 2) * 8 + (lane & 7) : 2 * q + (lane >> 4));
             const int chunk = is_v ? 4 * (q & 3) + (lane >> 3) : (lane & 15);
-            const int b = row_b[row];
+            const int64_t so = row_src[rr];
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (b >= 0) v = __ldg(reinterpret_cast<const uint4*>(src_base + b * s_sb + row_s[row] * s_ss) + chunk);
-            uint8_t* xr = S.tile + (row >> 3) * 2048 + (row & 7) * 16;
+            if (so >= 0) v = __ldg(reinterpret_cast<const uint4*>(src_base + so) + chunk);
+            uint8_t* xr = S.tile + (rr >> 3) * 2048 + (rr & 7) * 16;
             if (is_v) {
                 *reinterpret_cast<uint4*>(xr + chunk * 128) = v;
             } else {
@@ -230,20 +246,24 @@ __device__ __forceinline__ void t5_role(T5Smem& S, const EncParams& P, const int
             }
         }
         __syncwarp();
-        // ---- group norms of this thread's row ----
+        // ---- group norms: lane -> row 16 warp + (lane & 15); the two half-warps take alternate pairs ----
         {
-            const uint8_t* xr = S.tile + my_row;
+            const int rr = 16 * warp + (lane & 15), par = lane >> 4;
+            const uint8_t* xr = S.tile + (rr >> 3) * 2048 + (rr & 7) * 16;
             for (int s = 0; s < n_seg; ++s) {
                 const int st = is_v ? 0 : S.seg_start[s], en = is_v ? kHD : st + S.seg_len[s];
                 float acc = 0.f;
-                for (int p = st; p < en; p += 2) {
+                for (int p = st + 2 * par; p < en; p += 4) {
                     const float2 x = __half22float2(*reinterpret_cast<const __half2*>(xr + (p >> 3) * 128 + (p & 7) * 2));
                     acc = fmaf(x.x, x.x, acc);
                     acc = fmaf(x.y, x.y, acc);
                 }
-                const float nr = sqrtf(acc + 1e-30f);
-                S.gn[s][tid] = nr;
-                S.rinv[s][tid] = nr > (is_v ? 1e-8f : 1e-10f) ? 1.0f / nr : 1.0f;
+                acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+                if (par == 0) {
+                    const float nr = sqrtf(acc + 1e-30f);
+                    S.gn[s][rr] = nr;
+                    S.rinv[s][rr] = nr > (is_v ? 1e-8f : 1e-10f) ? 1.0f / nr : 1.0f;
+                }
             }
         }
         // ---- product: the tile is complete in shared memory; one thread issues, everybody waits ----
@@ -266,11 +286,18 @@ __device__ __forceinline__ void t5_role(T5Smem& S, const EncParams& P, const int
             break;
         }
         tc_fence_after_sync();
-        // ---- quantise this thread's row: 32 columns at a time out of tensor memory ----
+        // ---- quantise this thread's half row: 32 columns at a time out of tensor memory ----
         float csq = 0.f;                        // V: sum of squared levels
-        uint8_t* const crow = S.tile + tid * kT5CodeLd;
+        uint8_t* const crow = S.tile + row * kT5CodeLd;
+        uint8_t* const srow = S.tile + kT5StageOff + row * stg_ld;
+        {   // the staged row starts out zero: this thread clears its half of the words
+            const int nw = stg_ld >> 2, w0 = half ? nw >> 1 : 0, w1 = half ? nw : nw >> 1;
+            for (int i = w0; i < w1; ++i) reinterpret_cast<uint32_t*>(srow)[i] = 0u;
+        }
+        const float rv0 = S.rinv[0][row];
 #pragma unroll 1
-        for (int c32 = 0; c32 < kHD / 32; ++c32) {
+        for (int cc32 = 0; cc32 < 2; ++cc32) {
+            const int c32 = 2 * half + cc32;
             float hi[32], lo[32];
             tmem_ld32(tmem_lane + 32u * c32, hi);
             tmem_ld32(tmem_lane + kHD + 32u * c32, lo);
@@ -285,15 +312,20 @@ __device__ __forceinline__ void t5_role(T5Smem& S, const EncParams& P, const int
                     uint32_t code;
                     if (!is_v) {
                         const float4 cp = S.colp[col >> 1];
-                        const float y = acc * S.rinv[__float_as_int(cp.z)][tid];
+                        const float y = acc * S.rinv[__float_as_int(cp.z)][row];
                         float u = (y - cp.x) * cp.y;
                         u = fminf(fmaxf(u, 0.f), 255.f);
                         code = (&S.code_lut[0][0])[__float_as_int(cp.w) + (int)u];
                     } else {
-                        const float y = acc * S.rinv[0][tid];
-                        int cc = 0;      // boundaries are sorted and padded with +inf: four fixed halving steps
+                        const float y = acc * rv0;
+                        int cc = 0;
+                        if (v_small) {
 #pragma unroll
-                        for (int st = 3; st >= 0; --st) cc += y > S.vbounds[cc + (1 << st) - 1] ? (1 << st) : 0;
+                            for (int b = 0; b < 7; ++b) cc += y > vb[b] ? 1 : 0;
+                        } else {         // boundaries are sorted and padded with +inf: four fixed halving steps
+#pragma unroll
+                            for (int st = 3; st >= 0; --st) cc += y > S.vbounds[cc + (1 << st) - 1] ? (1 << st) : 0;
+                        }
                         code = (uint32_t)cc;
                         const float cv = S.vcents[cc];
                         csq = fmaf(cv, cv, csq);
@@ -303,39 +335,43 @@ __device__ __forceinline__ void t5_role(T5Smem& S, const EncParams& P, const int
                 *reinterpret_cast<uint32_t*>(crow + c32 * 32 + i) = word;
             }
         }
-        tc_fence_before_sync();                 // orders the tensor-memory reads before the end-of-tile barrier
-        // ---- norms out ----
-        const int my_b = row_b[tid], my_s = row_s[tid];
-        if (!is_v) {
-            if (mixed) {   // norm correction: divide by the norm of the chosen levels, per group
-                for (int s = 0; s < n_seg; ++s) {
-                    const int st = S.seg_start[s], en = st + S.seg_len[s];
-                    const float* cent = S.kcent + S.seg_lut_off[s];
-                    float acc = 0.f;
-                    for (int p = st; p < en; ++p) {
-                        const float cv = cent[crow[p]];
-                        acc = fmaf(cv, cv, acc);
+        if (is_v) S.gn[1 + half][row] = csq;    // V uses only group 0 of the norm arrays: park the partial sums here
+        tc_fence_before_sync();                 // orders the tensor-memory reads before the barriers below
+        __syncthreads();                        // all codes of the tile written, staged rows cleared
+        // ---- norms out (first thread of the pair) ----
+        if (half == 0) {
+            const int n = n0 + row;
+            if (!is_v) {
+                if (mixed) {   // norm correction: divide by the norm of the chosen levels, per group
+                    for (int s = 0; s < n_seg; ++s) {
+                        const int st = S.seg_start[s], en = st + S.seg_len[s];
+                        const float* cent = S.kcent + S.seg_lut_off[s];
+                        float acc = 0.f;
+                        for (int p = st; p < en; ++p) {
+                            const float cv = cent[crow[p]];
+                            acc = fmaf(cv, cv, acc);
+                        }
+                        S.gn[s][row] = S.gn[s][row] / fmaxf(sqrtf(acc), 1e-10f);
                     }
-                    S.gn[s][tid] = S.gn[s][tid] / fmaxf(sqrtf(acc), 1e-10f);
                 }
-            }
-            if (my_b >= 0) {
-                const size_t o = my_b * P.kn_sb + h * P.kn_sh + (size_t)(t0 + my_s) * P.kn_st;
-                for (int s = 0; s < P.kn_count; ++s) {
-                    const float val = s < n_seg ? S.gn[s][tid] : 0.f;
-                    if (f16n) static_cast<__half*>(P.kn)[o + s] = __float2half_rn(val);
-                    else static_cast<float*>(P.kn)[o + s] = val;
+                if (n < n_rows) {
+                    const int b = n / P.n_tok, sq = n - b * P.n_tok;
+                    const size_t o = b * P.kn_sb + h * P.kn_sh + (size_t)(t0 + sq) * P.kn_st;
+                    for (int s = 0; s < P.kn_count; ++s) {
+                        const float val = s < n_seg ? S.gn[s][row] : 0.f;
+                        if (f16n) static_cast<__half*>(P.kn)[o + s] = __float2half_rn(val);
+                        else static_cast<float*>(P.kn)[o + s] = val;
+                    }
                 }
+            } else if (n < n_rows) {
+                const int b = n / P.n_tok, sq = n - b * P.n_tok;
+                const float cnorm = sqrtf(S.gn[1][row] + S.gn[2][row] + 1e-20f);
+                P.vn[b * P.vn_sb + h * P.vn_sh + (size_t)(t0 + sq) * P.vn_st] =
+                    __float2half_rn(S.gn[0][row] / (cnorm > 1e-10f ? cnorm : 1.0f));
             }
-        } else if (my_b >= 0) {
-            const float cnorm = sqrtf(csq + 1e-20f);
-            P.vn[my_b * P.vn_sb + h * P.vn_sh + (size_t)(t0 + my_s) * P.vn_st] =
-                __float2half_rn(S.gn[0][tid] / (cnorm > 1e-10f ? cnorm : 1.0f));
         }
-        // ---- pack this thread's row: one task = up to 8 codes of one width ----
-        uint8_t* const srow = S.tile + kT5StageOff + tid * stg_ld;
-        for (int i = 0; i < stg_ld; i += 4) *reinterpret_cast<uint32_t*>(srow + i) = 0u;
-        for (int ti = 0; ti < n_tasks; ++ti) {
+        // ---- pack this row: one task = up to 8 codes of one width; the pair takes alternate tasks ----
+        for (int ti = half; ti < n_tasks; ti += 2) {
             const uint32_t tk = S.tasks[ti];
             const int first = tk & 0xFF, n = (tk >> 8) & 0xF, bw = (tk >> 12) & 0xF, out = tk >> 16;
             const uint16_t* cs = reinterpret_cast<const uint16_t*>(crow + first);
@@ -357,29 +393,31 @@ __device__ __forceinline__ void t5_role(T5Smem& S, const EncParams& P, const int
                     if (c < nb) o[c] = (uint8_t)(word >> (8 * c));
             }
         }
-        __syncwarp();
-        // ---- rows out: the warp copies its 32 staged rows, 32 bytes per store ----
-        for (int rr = 0; rr < 32; ++rr) {
-            const int row = 32 * warp + rr;
-            const int b = row_b[row];
-            if (b < 0) break;
-            uint8_t* dst = out_base + b * o_sb + (int64_t)(t0 + row_s[row]) * o_st;
-            const uint8_t* src = S.tile + kT5StageOff + row * stg_ld;
-            for (int p = lane; p < rb; p += 32) dst[p] = src[p];
+        __syncthreads();
+        // ---- rows out: a warp copies 16 staged rows, 32 bytes per store ----
+        for (int r16 = 0; r16 < 16; ++r16) {
+            const int rr = 16 * warp + r16;
+            const int64_t dof = row_dst[rr];
+            if (dof < 0) break;
+            const uint8_t* src = S.tile + kT5StageOff + rr * stg_ld;
+            for (int p = lane; p < rb; p += 32) out_base[dof + p] = src[p];
         }
         uint8_t* const codes_out = is_v ? P.v_codes : P.k_codes;
-        if (codes_out && my_b >= 0) {
-            uint32_t* cd = reinterpret_cast<uint32_t*>(codes_out + (((size_t)my_b * P.n_kv + h) * P.n_tok + my_s) * kHD);
-            for (int i = 0; i < kHD / 4; ++i) cd[i] = *reinterpret_cast<const uint32_t*>(crow + 4 * i);
+        if (codes_out && n0 + row < n_rows) {
+            const int n = n0 + row, b = n / P.n_tok, sq = n - b * P.n_tok;
+            uint32_t* cd = reinterpret_cast<uint32_t*>(codes_out + (((size_t)b * P.n_kv + h) * P.n_tok + sq) * kHD) + 16 * half;
+            for (int i = 0; i < kHD / 8; ++i) cd[i] = *reinterpret_cast<const uint32_t*>(crow + 64 * half + 4 * i);
         }
         __syncthreads();    // tile memory and tensor memory are reused by the next tile
     }
 }
 
-__global__ void __launch_bounds__(kT5Rows, 2) encode_t5_kernel(const EncParams P) {
+constexpr int kT5Threads = 2 * kT5Rows;
+
+__global__ void __launch_bounds__(kT5Threads, 2) encode_t5_kernel(const EncParams P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     T5Smem& S = *reinterpret_cast<T5Smem*>(smem_raw);
-    __shared__ int row_b[kT5Rows], row_s[kT5Rows];
+    __shared__ int64_t row_src[kT5Rows], row_dst[kT5Rows];
     const int h = blockIdx.y, tid = threadIdx.x;
     const bool is_v = blockIdx.z != 0 || (P.flags & BGTQ_ENC_SKIP_K);
     if (tid == 0) {
@@ -392,8 +430,8 @@ __global__ void __launch_bounds__(kT5Rows, 2) encode_t5_kernel(const EncParams P
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    if (is_v) t5_role<true>(S, P, h, blockIdx.x, gridDim.x, row_b, row_s);
-    else t5_role<false>(S, P, h, blockIdx.x, gridDim.x, row_b, row_s);
+    if (is_v) t5_role<true>(S, P, h, blockIdx.x, gridDim.x, row_src, row_dst);
+    else t5_role<false>(S, P, h, blockIdx.x, gridDim.x, row_src, row_dst);
     tc_fence_before_sync();
     __syncthreads();
     if (tid < 32) tmem_dealloc(S.tmem_base, kT5TmemCols);
@@ -423,7 +461,7 @@ int launch_encode_t5(const EncParams& P, cudaStream_t stream) {
         }
         attr_set = true;
     }
-    encode_t5_kernel<<<dim3(grid_x, P.n_kv, roles), kT5Rows, smem, stream>>>(P);
+    encode_t5_kernel<<<dim3(grid_x, P.n_kv, roles), kT5Threads, smem, stream>>>(P);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 
