@@ -20,7 +20,7 @@ N_BINS = 256
 
 OK = 0
 ENC_K_NORMS_F16, ENC_K_MIXED, ENC_V_NIBBLE, ENC_SKIP_K, ENC_SKIP_V, ENC_FORCE_SIMT, ENC_PROGRAMMATIC = 1, 2, 4, 8, 16, 32, 64
-ENC_TCGEN05 = 128
+ENC_NO_TCGEN05 = 128
 DEC_K_MIXED, DEC_V_NIBBLE, DEC_PROGRAMMATIC = 1, 2, 4
 COMBINE_PROGRAMMATIC = 1
 

@@ -520,8 +520,8 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
         };
         if (n_rows >= 64 && n_tok >= 16 && kn_count <= BGTQ_MAX_SEGMENTS && !(flags & BGTQ_ENC_FORCE_SIMT) && al16(do_k ? k : nullptr, k_sb, k_sh, k_ss) &&
             al16(do_v ? v : nullptr, v_sb, v_sh, v_ss)) {
-            if ((flags & BGTQ_ENC_TCGEN05) && n_rows >= 128 && (!do_k || kp_row_bytes <= encode_t5_max_row_bytes()))
-                return launch_encode_t5(P, static_cast<cudaStream_t>(stream));
+            if (!(flags & BGTQ_ENC_NO_TCGEN05) && n_rows >= 128 && (!do_k || kp_row_bytes <= encode_t5w_max_row_bytes()))
+                return launch_encode_t5w(P, static_cast<cudaStream_t>(stream));
             return launch_encode_tc(P, static_cast<cudaStream_t>(stream));
         }
     }

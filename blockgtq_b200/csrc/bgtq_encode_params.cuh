@@ -39,9 +39,9 @@ __device__ __forceinline__ uint32_t enc_pack_byte(const uint8_t* codes, int n, i
 // Tensor-core bulk path (bgtq_encode_tc.cu).  Rows must be 16-byte aligned.
 int launch_encode_tc(const EncParams& P, cudaStream_t stream);
 
-// tcgen05 bulk path (bgtq_encode_t5.cu): same requirements, and packed rows of at most
-// encode_t5_max_row_bytes() bytes.
-int launch_encode_t5(const EncParams& P, cudaStream_t stream);
-int encode_t5_max_row_bytes();
+// tcgen05 bulk path (bgtq_encode_t5w.cu): same requirements, n_tok >= 16, and packed K rows of at most
+// encode_t5w_max_row_bytes() bytes.
+int launch_encode_t5w(const EncParams& P, cudaStream_t stream);
+int encode_t5w_max_row_bytes();
 
 }  // namespace bgtq

@@ -102,8 +102,8 @@ def encode(layer: LayerTables, k, v, t0, k_packed, k_norms, v_packed, v_norms, *
     """Encode ``k``/``v`` (B, n_kv, S, 128) fp16 into rows ``t0 .. t0+S`` of the cache tensors
     ``k_packed`` (B, n_kv, T, bytes) u8, ``k_norms`` (B, n_kv, T, groups) f16|f32,
     ``v_packed`` (B, n_kv, T, bytes) u8 and ``v_norms`` (B, n_kv, T) f16.  Either side may be None.
-    ``flags`` may carry ``_lib.ENC_TCGEN05`` (or set the environment variable ``BGTQ_ENC_TCGEN05``) to run bulk
-    row counts through the tcgen05 / tensor-memory encoder instead of the warp-MMA one."""
+    Bulk row counts (>= 128 rows) run the tcgen05 / tensor-memory encoder; ``_lib.ENC_NO_TCGEN05`` in ``flags``
+    (or the environment variable ``BGTQ_ENC_NO_TCGEN05``) keeps them on the warp-MMA one."""
     L = _lib.lib()
     ref = k if k is not None else v
     _lib.require_cuda(ref, "k/v")
@@ -114,8 +114,8 @@ def encode(layer: LayerTables, k, v, t0, k_packed, k_norms, v_packed, v_norms, *
         flags |= _lib.ENC_SKIP_K
     if v is None:
         flags |= _lib.ENC_SKIP_V
-    if os.environ.get("BGTQ_ENC_TCGEN05"):
-        flags |= _lib.ENC_TCGEN05
+    if os.environ.get("BGTQ_ENC_NO_TCGEN05"):
+        flags |= _lib.ENC_NO_TCGEN05
     ks = _strides3(k) if k is not None else (0, 0, 0)
     vs = _strides3(v) if v is not None else (0, 0, 0)
     if k is not None:

@@ -84,8 +84,8 @@ const char* bgtq_error_string(int code);       /* host pointer to a static strin
 #define BGTQ_ENC_SKIP_V 16
 #define BGTQ_ENC_FORCE_SIMT 32  /* always use the small-batch fp32 kernel (>= 64 rows normally use tensor cores) */
 #define BGTQ_ENC_PROGRAMMATIC 64  /* bgtq_step_prepare only: programmatic dependent launch, see below */
-#define BGTQ_ENC_TCGEN05 128      /* bulk encode: run the rotation with tcgen05.mma and tensor-memory accumulators
-                                   * (128-row tiles; packed K rows up to 124 bytes; otherwise ignored) */
+#define BGTQ_ENC_NO_TCGEN05 128   /* bulk encode: keep the rotation on mma.sync (bulk row counts of >= 128 rows and packed
+                                   * K rows of <= 120 bytes normally use tcgen05.mma with tensor-memory accumulators) */
 
 /* Programmatic dependent launch (BGTQ_ENC_PROGRAMMATIC, BGTQ_DEC_PROGRAMMATIC,
  * BGTQ_COMBINE_PROGRAMMATIC).  The kernel is launched with CUDA's programmatic
@@ -133,7 +133,7 @@ int bgtq_encode(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v
                 uint8_t* k_codes, uint8_t* v_codes,
                 int32_t flags, const int32_t* pos_dev, void* stream);
 
-/* Sticky device-side status of the BGTQ_ENC_TCGEN05 path on the current device: 0, or 1 after a wait for
+/* Sticky device-side status of the tcgen05 bulk encoder on the current device: 0, or 1 after a wait for
  * the tensor cores ran out (the rows of that launch are then incomplete).  Synchronises the device. */
 int bgtq_encode_tcgen05_status(void);
 

@@ -315,8 +315,8 @@ def test_production_cache_matches_reference():
 @pytest.mark.parametrize("case", ["a3_1to8", "a4_rt1", "u3"])
 @pytest.mark.parametrize("mixed", [False, True])
 def test_encoder_tensor_core_and_fp32_paths_vs_oracle(case, mixed):
-    """Bulk row counts run the tensor-core encoder (warp MMA by default, tcgen05 + tensor memory with
-    BGTQ_ENC_TCGEN05), small ones (or BGTQ_ENC_FORCE_SIMT) the fp32 one.  All must give the oracle's
+    """Bulk row counts run the tensor-core encoder (tcgen05 + tensor memory by default, warp MMA with
+    BGTQ_ENC_NO_TCGEN05), small ones (or BGTQ_ENC_FORCE_SIMT) the fp32 one.  All must give the oracle's
     codes off bin edges, and bytes that are the exact packing
     of the codes each chose; rows land at the requested slot offset; ragged tile tails."""
     from blockgtq_b200 import _lib
@@ -331,7 +331,7 @@ def test_encoder_tensor_core_and_fp32_paths_vs_oracle(case, mixed):
     k[2, 1, 11] *= 1e-4
     base = (_lib.ENC_K_MIXED | _lib.ENC_V_NIBBLE) if mixed else 0
     outs = []
-    for extra in (0, _lib.ENC_FORCE_SIMT, _lib.ENC_TCGEN05):
+    for extra in (0, _lib.ENC_FORCE_SIMT, _lib.ENC_NO_TCGEN05):
         kb = lt.max_mixed_bytes if mixed else lt.max_tpb
         kp = torch.full((B, n_kv, t0 + S + 2, kb), 0xEE, dtype=torch.uint8, device=DEV)
         kn = torch.full((B, n_kv, t0 + S + 2, lt.max_ng), -1.0, dtype=torch.float32, device=DEV)
@@ -537,7 +537,7 @@ def test_bulk_encoder_rows_that_wrap_batches():
     k = torch.stack([torch.stack([synth_head(gen, S, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
     v = torch.randn(B, n_kv, S, HD, generator=gen).half().to(DEV)
     outs = []
-    for extra in (0, _lib.ENC_FORCE_SIMT, _lib.ENC_TCGEN05):
+    for extra in (0, _lib.ENC_FORCE_SIMT, _lib.ENC_NO_TCGEN05):
         kp = torch.zeros(B, n_kv, S + 4, lt.max_tpb, dtype=torch.uint8, device=DEV)
         kn = torch.zeros(B, n_kv, S + 4, lt.max_ng, dtype=torch.float16, device=DEV)
         vp = torch.zeros(B, n_kv, S + 4, lt.vpb, dtype=torch.uint8, device=DEV)
@@ -548,7 +548,7 @@ def test_bulk_encoder_rows_that_wrap_batches():
         outs.append((kp.cpu().numpy(), kn.cpu().numpy(), vp.cpu().numpy(), vn.cpu().numpy(), kc.cpu().numpy()))
     assert _lib.lib().bgtq_encode_tcgen05_status() == 0
     b = outs[1]
-    for a in (outs[0], outs[2]):       # 133 rows: the tcgen05 path runs one full 128-row tile and a 5-row tail
+    for a in (outs[0], outs[2]):       # 133 rows: the tcgen05 path (outs[0]) runs one full 128-row tile and a 5-row tail
         assert (a[4] != b[4]).mean() < 2e-3
         if np.array_equal(a[4], b[4]):
             assert np.array_equal(a[0], b[0])
