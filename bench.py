@@ -400,7 +400,7 @@ def run_encode(args, w, rank, world, dev):
                        "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"], "parallelism": f"batch x{world}",
                        "l2": "each layer's fp16 K/V input is 537 MB, larger than L2; no flush",
                        "append_us_per_layer": append_us},
-            "roofline": {"bound": "hbm", "kernel": "encode_tc_kernel", "achieved": alg / (ms_launch * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "kernel": "encode_t5w_kernel", "achieved": alg / (ms_launch * 1e-3) / 1e9,
                          "peak": peak, "unit": "GB/s", "frac": alg / (ms_launch * 1e-3) / 1e9 / peak, "traffic": None,
                          "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback",
                          "algorithmic_bytes_per_launch": alg, "launch_ms": ms_launch},
