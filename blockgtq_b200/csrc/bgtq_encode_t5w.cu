@@ -11,8 +11,10 @@
 //     the register layout of mma.sync accumulator tiles, so quantisation, packing and the stores are the
 //     warp-MMA encoder's, working out of the warp's own 4 KB of the (now dead) operand tile;
 //   * one barrier and one mbarrier wait per tile and group; the two groups run out of phase, so one
-//     group's loads overlap the other's quantisation.  153 KB of shared memory, all 512 tensor-memory
-//     columns, one CTA per SM.
+//     group's loads overlap the other's quantisation.  217 KB of shared memory, all 512 tensor-memory
+//     columns, one CTA per SM;
+//   * a warp's input rows for its NEXT tile are fetched with cp.async into a raw buffer while it works on
+//     the current one.
 // Every wait is bounded; tensor memory is released on every path out of the kernel.
 #include "bgtq_common.cuh"
 #include "bgtq_encode_params.cuh"
@@ -42,6 +44,7 @@ struct WSmem {
     __align__(128) uint8_t w_hi[kHD * kHD * 2];
     __align__(128) uint8_t w_lo[kHD * kHD * 2];
     __align__(128) uint8_t tile[2][kTileRows * kHD * 2];    // A operand of each group; per-warp scratch after the product
+    __align__(128) uint8_t raw[kWarps][kSlabBytes];         // next tile's input rows per warp, fetched with cp.async (16-byte chunks XOR-swizzled by row)
     float gn[kWarps][kSlab][BGTQ_MAX_SEGMENTS];     // group norms (V: [.][0] = raw row norm)
     float rinv[kWarps][kSlab][BGTQ_MAX_SEGMENTS];   // 1 / norm, or 1 where the norm is below the floor
     float4 colp[kHD / 2];                           // per column pair: {lut_off, lut_inv, bits(group), bits(group * 256)}
@@ -170,25 +173,44 @@ __device__ __forceinline__ void w_role(WSmem& S, const EncParams& P, const int h
         }
     }
 
+    // Input rows of tile `tl` -> this warp's raw buffer, asynchronously: lane -> chunk (lane & 15) of rows
+    // 2q + (lane >> 4); rows past the end are zero-filled.  Chunk c of row rr sits at rr * 256 + ((c ^ (rr & 7)) * 16.
+    uint8_t* const raw = S.raw[warp];
+    const uint32_t raw_u32 = smem_u32(raw);
+    auto prefetch = [&](int tl) {
+        const int n0 = tl * kTileRows + slab_i * kSlab;
+        const int b0 = (int)((uint32_t)n0 / (uint32_t)P.n_tok), s0 = n0 - b0 * P.n_tok;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int row = 2 * q + (lane >> 4), chunk = lane & 15;
+            int b = b0, s = s0 + row;
+            if (s >= P.n_tok) { s -= P.n_tok; ++b; }
+            const bool valid = tl < n_tiles && n0 + row < n_rows;
+            const __half* src = valid ? src_base + b * s_sb + s * s_ss + chunk * 8 : src_base;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(raw_u32 + row * 256 + ((chunk ^ (row & 7)) << 4)),
+                         "l"(src), "r"(valid ? 16 : 0)
+                         : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    prefetch(2 * role_cta + grp);
+
     int it = 0;
     for (int tl = 2 * role_cta + grp; tl < n_tiles; tl += 2 * role_ctas, ++it) {
         const int n0 = tl * kTileRows + slab_i * kSlab;
         const int n_valid = n_rows - n0 < kSlab ? (n_rows - n0 > 0 ? n_rows - n0 : 0) : kSlab;
         const int b0 = (int)((uint32_t)n0 / (uint32_t)P.n_tok), s0 = n0 - b0 * P.n_tok;   // n_tok >= kSlab: a slab wraps at most once
-        // ---- load 16 rows into the operand layout (row rr: (rr >> 3) * 2048 + (rr & 7) * 16; chunk c: + 128 c) ----
+        // ---- the prefetched rows -> operand layout (row rr: (rr >> 3) * 2048 + (rr & 7) * 16; chunk c: + 128 c) ----
         // V: lane -> row (lane & 7) of an 8-row group, chunk 4 (q & 3) + (lane >> 3): eight lanes fill one 128-byte
-        //    core matrix, so the shared stores are conflict free and a row is read 64 bytes at a time.
-        // K: lane -> chunk (lane & 15) of rows 2q + (lane >> 4): the lane's eight packed positions stay fixed.
+        //    core matrix; K: lane -> chunk (lane & 15) of rows 2q + (lane >> 4): the lane's eight packed positions
+        //    stay fixed.  Both read patterns are conflict free in the swizzled raw buffer.
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
             const int row = is_v ? (q >> 2) * 8 + (lane & 7) : 2 * q + (lane >> 4);
             const int chunk = is_v ? 4 * (q & 3) + (lane >> 3) : (lane & 15);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (row < n_valid) {
-                int b = b0, s = s0 + row;
-                if (s >= P.n_tok) { s -= P.n_tok; ++b; }
-                v = __ldg(reinterpret_cast<const uint4*>(src_base + b * s_sb + s * s_ss) + chunk);
-            }
+            const uint4 v = *reinterpret_cast<const uint4*>(raw + row * 256 + ((chunk ^ (row & 7)) << 4));
             uint8_t* xr = slab + (row >> 3) * 2048 + (row & 7) * 16;
             if (is_v) {
                 *reinterpret_cast<uint4*>(xr + chunk * 128) = v;
@@ -198,6 +220,8 @@ __device__ __forceinline__ void w_role(WSmem& S, const EncParams& P, const int h
                 for (int c = 0; c < 8; ++c) *reinterpret_cast<__half*>(xr + koff[c]) = e[c];
             }
         }
+        __syncwarp();
+        prefetch(tl + 2 * role_ctas);       // the raw buffer is free again: the next tile's rows arrive during this tile's work
         __syncwarp();
         // ---- group norms: lane -> row (lane & 15); the two half-warps take alternate element pairs ----
         {
@@ -391,6 +415,7 @@ __device__ __forceinline__ void w_role(WSmem& S, const EncParams& P, const int h
         }
         __syncwarp();       // the warp's rows are reloaded next
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");     // the last prefetch (past the end: zero fill) lands before the CTA leaves
 }
 
 __global__ void __launch_bounds__(kWarps * 32, 1) encode_t5w_kernel(const EncParams P) {
