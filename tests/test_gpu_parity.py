@@ -526,6 +526,45 @@ def test_prefill_attention_mixed_layout_matches_decode_kernel():
         assert (out[:, :, i].float() - ref.float()).abs().max().item() <= ATOL
 
 
+def test_bulk_encoder_single_sided_and_strided_cache():
+    """tcgen05 bulk encoder with only K or only V given, writing into a cache whose token stride is larger
+    than the row (the per-row store path), against the warp-MMA path: same bytes off bin edges, the other
+    side's cache untouched, status word clean."""
+    from blockgtq_b200 import _lib
+    from blockgtq_b200.layer import encode
+    lt, tabs = _layer("a3_1to8")
+    gen = torch.Generator().manual_seed(4242)
+    B, n_kv, S = 2, 2, 200                  # 400 rows: three full 128-row tiles and a 16-row tail
+    k = torch.stack([torch.stack([synth_head(gen, S, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
+    v = torch.randn(B, n_kv, S, HD, generator=gen).half().to(DEV)
+    res = []
+    for extra in (0, _lib.ENC_NO_TCGEN05):
+        kp = torch.full((B, n_kv, S + 3, lt.max_tpb + 5), 0xAB, dtype=torch.uint8, device=DEV)[..., :lt.max_tpb]
+        kn = torch.zeros(B, n_kv, S + 3, lt.max_ng, dtype=torch.float16, device=DEV)
+        vp = torch.full((B, n_kv, S + 3, lt.vpb + 3), 0xAB, dtype=torch.uint8, device=DEV)[..., :lt.vpb]
+        vn = torch.full((B, n_kv, S + 3), -2.0, dtype=torch.float16, device=DEV)
+        kc = torch.zeros(B, n_kv, S, HD, dtype=torch.uint8, device=DEV)
+        vc = torch.zeros(B, n_kv, S, HD, dtype=torch.uint8, device=DEV)
+        encode(lt, k, None, 1, kp, kn, None, None, flags=extra, k_codes=kc)
+        torch.cuda.synchronize()
+        assert (vp == 0xAB).all() and (vn == -2.0).all()            # V side untouched by a K-only call
+        encode(lt, None, v, 1, None, None, vp, vn, flags=extra, v_codes=vc)
+        torch.cuda.synchronize()
+        res.append([t.cpu().numpy() for t in (kp, kn, vp, vn, kc, vc)])
+    assert _lib.lib().bgtq_encode_tcgen05_status() == 0
+    a, b = res
+    assert (a[4] != b[4]).mean() < 2e-3 and (a[5] != b[5]).mean() < 2e-3
+    np.testing.assert_allclose(a[1].astype(np.float32), b[1].astype(np.float32), rtol=2e-3, atol=1e-6)
+    np.testing.assert_allclose(a[3].astype(np.float32), b[3].astype(np.float32), rtol=2e-3, atol=1e-6)
+    for r in res:
+        for bb in range(B):
+            for h in range(n_kv):
+                assert np.array_equal(r[0][bb, h, 1:1 + S], O.pack_k(r[4][bb, h], tabs[h][0].segments, lt.max_tpb))
+                assert np.array_equal(r[2][bb, h, 1:1 + S], O.pack_v(r[5][bb, h], tabs[h][1].bits))
+        assert (r[0][:, :, 0] == 0xAB).all() and (r[0][:, :, 1 + S:] == 0xAB).all()
+        assert (r[2][:, :, 0] == 0xAB).all() and (r[2][:, :, 1 + S:] == 0xAB).all()
+
+
 def test_bulk_encoder_rows_that_wrap_batches():
     """Tensor-core path with a token count that is not a multiple of the 16-row slab: slabs span two
     batch entries and take the per-row store path; must equal the fp32 kernel's bytes off bin edges."""
