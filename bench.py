@@ -106,7 +106,7 @@ def clocks_sampler(device_index):
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
     try:
         return subprocess.Popen(["nvidia-smi", "-i", str(device_index), f"--query-gpu={q}",
-                                 "--format=csv,noheader,nounits", "-lms", "100"],
+                                 "--format=csv,noheader,nounits", "-lms", "20"],
                                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
     except OSError:
         return None
