@@ -48,6 +48,9 @@ WORKLOADS = {
     # 16384-token prompt, K3V3; a step = bulk encode + causal prefill attention of one layer
     "llama3.1-8b_k3v3_prefill_t16384": dict(layers=1, n_q=32, n_kv=8, batch=1, ctx=16384, k_bits=3.0, v_bits=3,
                                             theta=5e5, n_sink=0, window=0, mode="prefill"),
+    # small variant of configs[2] for quick runs and profiler captures
+    "llama3.1-8b_k2v2_b32_t16384_sink4_win128_4layers": dict(layers=4, n_q=32, n_kv=8, batch=32, ctx=16384,
+                                                             k_bits=2.0, v_bits=2, theta=5e5, n_sink=4, window=128),
     # small variant of configs[1] for quick runs and profiler captures
     "qwen2.5-3b_k3v3_b8_t32768_4layers": dict(layers=4, n_q=16, n_kv=2, batch=8, ctx=32768, k_bits=3.0, v_bits=3,
                                               theta=1e6, n_sink=0, window=0),

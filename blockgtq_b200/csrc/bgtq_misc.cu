@@ -110,8 +110,9 @@ __global__ void __launch_bounds__(128) buffer_attn_kernel(const __half* q, int64
                                                            int64_t kb_sh, int n_sink_tok, int n_ring_tok,
                                                            int sink_cap, int ring_first, int ring_size, int n_q,
                                                            int n_kv, float scale, float* buf_o, float* buf_lse,
-                                                           const int32_t* pos_dev) {
-    extern __shared__ float sc[];                      // n_tok logits, then 8 floats of scratch
+                                                           const int32_t* pos_dev, int sc_cap) {
+    // shared memory: sc_cap logits / probabilities, 8 floats of scratch, the query (128 floats), 128 partial outputs
+    extern __shared__ __align__(16) float sc[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (pos_dev) {      // region sizes from the device-side token count (one-token blocks, window = ring_size - 1)
         const int avail = *pos_dev + 1;                // tokens including the one appended this step
@@ -126,26 +127,43 @@ __global__ void __launch_bounds__(128) buffer_attn_kernel(const __half* q, int64
     const size_t row = (size_t)b * n_q + hq;
     const int n_tok = n_sink_tok + n_ring_tok;
     // logical token i -> buffer slot: sink prefix, then a ring starting at ring_first
-    auto slot = [&](int i) { return i < n_sink_tok ? i : sink_cap + (ring_first + (i - n_sink_tok)) % ring_size; };
+    auto slot = [&](int i) {
+        if (i < n_sink_tok) return i;
+        const int x = ring_first + (i - n_sink_tok);
+        return sink_cap + (x >= ring_size ? x - ring_size : x);
+    };
     if (n_tok <= 0) {
         buf_o[row * kHD + tid] = 0.f;
         if (tid == 0) buf_lse[row] = -INFINITY;
         return;
     }
-    const __half* qp = q + b * q_sb + hq * q_sh + 4 * lane;
-    const float q0 = __half2float(qp[0]), q1 = __half2float(qp[1]), q2 = __half2float(qp[2]), q3 = __half2float(qp[3]);
+    float* red = sc + sc_cap;
+    float* qs = red + 8;
+    float* po = qs + kHD;
+    qs[tid] = __half2float(q[b * q_sb + hq * q_sh + tid]);
+    __syncthreads();
     const __half* kbase = kb + b * kb_sb + h * kb_sh;
     const __half* vbase = vb + b * kb_sb + h * kb_sh;
-    for (int i = warp; i < n_tok; i += 4) {
-        const __half* kr = kbase + (size_t)slot(i) * kHD + 4 * lane;
-        float s = q0 * __half2float(kr[0]) + q1 * __half2float(kr[1]) + q2 * __half2float(kr[2]) +
-                  q3 * __half2float(kr[3]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (lane == 0) sc[i] = s * scale;
+    // logits: one thread per token walks the 256-byte key row (16-byte loads, the query is broadcast from shared memory)
+    for (int i = tid; i < n_tok; i += 128) {
+        const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)slot(i) * kHD);
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll 4
+        for (int c = 0; c < kHD / 8; ++c) {
+            const uint4 kv = __ldg(kr + c);
+            const float4 qa = *reinterpret_cast<const float4*>(qs + 8 * c), qb = *reinterpret_cast<const float4*>(qs + 8 * c + 4);
+            const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kv.x));
+            const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kv.y));
+            const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kv.z));
+            const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kv.w));
+            s0 = fmaf(qa.x, k0.x, s0); s1 = fmaf(qa.y, k0.y, s1);
+            s0 = fmaf(qa.z, k1.x, s0); s1 = fmaf(qa.w, k1.y, s1);
+            s0 = fmaf(qb.x, k2.x, s0); s1 = fmaf(qb.y, k2.y, s1);
+            s0 = fmaf(qb.z, k3.x, s0); s1 = fmaf(qb.w, k3.y, s1);
+        }
+        sc[i] = (s0 + s1) * scale;
     }
     __syncthreads();
-    float* red = sc + n_tok;
     float mx = -INFINITY;
     for (int i = tid; i < n_tok; i += 128) mx = fmaxf(mx, sc[i]);
 #pragma unroll
@@ -164,9 +182,25 @@ __global__ void __launch_bounds__(128) buffer_attn_kernel(const __half* q, int64
     if (lane == 0) red[4 + warp] = sum;
     __syncthreads();
     sum = red[4] + red[5] + red[6] + red[7];
-    float acc = 0.f;
-    for (int i = 0; i < n_tok; ++i) acc = fmaf(sc[i], __half2float(vbase[(size_t)slot(i) * kHD + tid]), acc);
-    buf_o[row * kHD + tid] = acc / sum;
+    // output: thread -> dims (2 d2, 2 d2 + 1) of every second token; the two halves of the CTA add up through shared memory
+    const int d2 = tid & 63, par = tid >> 6;
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll 4
+    for (int i = par; i < n_tok; i += 2) {
+        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(vbase + (size_t)slot(i) * kHD + 2 * d2));
+        const float pr = sc[i];
+        a0 = fmaf(pr, v.x, a0);
+        a1 = fmaf(pr, v.y, a1);
+    }
+    if (par) {
+        po[2 * d2] = a0;
+        po[2 * d2 + 1] = a1;
+    }
+    __syncthreads();
+    if (!par) {
+        const float inv = 1.0f / sum;
+        *reinterpret_cast<float2*>(buf_o + row * kHD + 2 * d2) = make_float2((a0 + po[2 * d2]) * inv, (a1 + po[2 * d2 + 1]) * inv);
+    }
     if (tid == 0) buf_lse[row] = mx + logf(sum);
 }
 
@@ -251,11 +285,15 @@ extern "C" __attribute__((visibility("default"))) int bgtq_buffer_attn_pos(const
     if (n_buf_tokens > 0 && (!k_buf || !v_buf)) return BGTQ_E_BADARG;
     if (pos_dev && ring_size < 2) return BGTQ_E_BADARG;
     if (n_buf_tokens > 8192 || n_batch > 65535) return BGTQ_E_TOOBIG;
-    const size_t smem = (size_t)(n_buf_tokens + 8) * sizeof(float);
+    if (n_buf_tokens > 0 && ((reinterpret_cast<uintptr_t>(k_buf) & 15u) || (reinterpret_cast<uintptr_t>(v_buf) & 15u) ||
+                             (kb_sb & 7) || (kb_sh & 7) || (reinterpret_cast<uintptr_t>(buf_o) & 7u)))
+        return BGTQ_E_ALIGN;
+    const int sc_cap = (n_buf_tokens + 3) & ~3;       // keeps the query block 16-byte aligned
+    const size_t smem = (size_t)(sc_cap + 8 + 2 * kHD) * sizeof(float);
     buffer_attn_kernel<<<dim3(n_q, n_batch), 128, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(q), q_sb, q_sh, static_cast<const __half*>(k_buf),
         static_cast<const __half*>(v_buf), kb_sb, kb_sh, n_sink_tokens, n_ring_tokens, sink_cap, ring_first,
-        ring_size > 0 ? ring_size : 1, n_q, n_kv, scale, buf_o, buf_lse, pos_dev);
+        ring_size > 0 ? ring_size : 1, n_q, n_kv, scale, buf_o, buf_lse, pos_dev, sc_cap);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 

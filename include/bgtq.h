@@ -290,7 +290,9 @@ int bgtq_decode_fused(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc,
  * sink_cap: recent token i is in slot sink_cap + (ring_first + i) % ring_size,
  * i < n_ring_tokens.
  * Writes one more partial per (b,hq): buf_o (n_batch, n_q, 128) fp32 in the
- * ORIGINAL V basis, buf_lse (n_batch, n_q) fp32 (-inf when there are no tokens). */
+ * ORIGINAL V basis, buf_lse (n_batch, n_q) fp32 (-inf when there are no tokens).
+ * k_buf / v_buf must be 16-byte aligned with kb_sb, kb_sh multiples of 8 elements, buf_o 8-byte aligned
+ * (BGTQ_E_ALIGN otherwise). */
 int bgtq_buffer_attn(const void* q, int64_t q_sb, int64_t q_sh,
                      const void* k_buf, const void* v_buf, int64_t kb_sb, int64_t kb_sh,
                      int32_t n_sink_tokens, int32_t n_ring_tokens, int32_t sink_cap,
