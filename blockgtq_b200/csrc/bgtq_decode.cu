@@ -721,6 +721,15 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_default_splits
     const long pairs = (long)n_batch * n_kv > 0 ? (long)n_batch * n_kv : 1;
     if (n_tokens <= kTileTok) return 1;
     const long slots = 2L * sms;
+    if (2 * pairs > slots) {
+        // More (batch, head) pairs than half the resident slots: the launch runs several waves whatever the
+        // split count.  Measured (256 pairs x 16384 tokens): 4 splits of 16 tiles beat 2 splits of 32 tiles by
+        // 10 % (2: 343 us, 3: 334, 4: 308, 6: 320, 8: 315), because CTAs that start together also set up
+        // together, and many shorter CTAs drift apart and leave a shorter tail.  Aim at 16 tiles per CTA.
+        const long tiles = (n_tokens + kTileTok - 1) / kTileTok;
+        const long ns = (tiles + 8) / 16;
+        return (int)(ns < 1 ? 1 : ns);
+    }
     const long max_ns = (n_tokens + kWarpTok - 1) / kWarpTok;
     long best = 1;
     double best_span = -1.0;

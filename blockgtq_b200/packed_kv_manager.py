@@ -15,6 +15,8 @@ Extensions beyond the reference class (all off by default):
 """
 from __future__ import annotations
 
+import os
+
 import math
 
 import torch
@@ -138,6 +140,8 @@ class BlockGTQKVManager:
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
         # scratch reused by every layer step (stream ordered): rotated queries and split partials
         self._n_splits = default_splits(self.B, self.n_kv, self.max_T) if dev.type == "cuda" else 1
+        if os.environ.get("BGTQ_N_SPLITS"):           # experiments: fix the split count of the decode launch
+            self._n_splits = max(1, int(os.environ["BGTQ_N_SPLITS"]))
         self._q_rot = torch.empty(self.B, self.n_q, self.hd, dtype=torch.float16, device=dev)
         self._part_o = torch.empty(self.B, self.n_q, self._n_splits, self.hd, dtype=torch.float32, device=dev)
         self._part_lse = torch.empty(self.B, self.n_q, self._n_splits, dtype=torch.float32, device=dev)
