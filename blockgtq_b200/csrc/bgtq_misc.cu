@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const
 
 // ---------------------------------------------------------------------------
 // fp16 buffer attention: plain softmax(q k^T) v over a few hundred tokens.
-// One CTA per (query head, batch): warps score tokens, then threads own dims.
+// One CTA per (query head, batch): one thread per token scores it, then threads own half2 columns.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) buffer_attn_kernel(const __half* q, int64_t q_sb, int64_t q_sh,
                                                            const __half* kb, const __half* vb, int64_t kb_sb,
