@@ -151,3 +151,14 @@ def test_calib_cache_round_trip(tmp_path):
             b = calib.build_k_tables(back[li]["q"][h].float(), back[li]["k"][h].float(), head_dim=128, avg_bits=3.0)
             assert torch.equal(a.bit_allocation, b.bit_allocation) and torch.equal(a.code_lut, b.code_lut)
     assert (time.time() - t0) / 8 < 2.0          # vectorised table construction: well under a second per head
+
+
+def test_default_split_counts_for_the_benchmark_shapes():
+    """Host-side split rule of the decode launch (148 SMs assumed without a GPU): one wave of warp-granular
+    splits when the (batch, head) pairs fit in half the resident CTA slots, 16-tile CTAs otherwise."""
+    L = _lib.lib()
+    assert L.bgtq_decode_default_splits(8, 2, 32768) == 18        # 16 pairs x 18 = 288 of 296 slots
+    assert L.bgtq_decode_default_splits(1, 8, 131072) == 37       # 8 pairs x 37 = 296
+    assert L.bgtq_decode_default_splits(32, 8, 16384) == 4        # 256 pairs: several waves, 16 tiles per CTA
+    assert L.bgtq_decode_default_splits(32, 8, 65536) == 16
+    assert L.bgtq_decode_default_splits(1, 1, 100) == 1 and L.bgtq_decode_default_splits(64, 8, 1024) == 1
