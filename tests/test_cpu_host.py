@@ -107,6 +107,14 @@ def test_entry_points_reject_bad_arguments_without_a_gpu():
     assert L.bgtq_combine_ranks(C.addressof(dummy), 2, 8 * 128, 1, 8, C.addressof(dummy), 0, 0, 0, None) == -1
     assert L.bgtq_encode(None, None, None, None, 0, 0, 0, None, 0, 0, 0, 1, 2, 1, 0, None, 0, 0, 0, 8,
                          None, 0, 0, 0, 1, None, 0, 0, 0, None, 0, 0, 0, None, None, 0, None, None) == -1
+    # fp16-region attention: key/value buffers must be 16-byte aligned with strides in multiples of 8 elements
+    buf = (C.c_float * 64)()
+    a = C.addressof(buf)
+    a16 = (a + 15) & ~15
+    args = lambda kb, sb: (a16, 1024, 128, kb, a16, sb, 128 * 8, 2, 3, 4, 0, 5, 1, 8, 2, 0.1, a16, a16, None)
+    assert L.bgtq_buffer_attn(*args(a16 + 2, 4096)) == -3
+    assert L.bgtq_buffer_attn(*args(a16, 4100)) == -3
+    assert L.bgtq_buffer_attn(None, 0, 0, None, None, 0, 0, 0, 0, 4, 0, 5, 1, 8, 2, 0.1, None, None, None) == -1
 
 
 def test_operators_refuse_cpu_tensors():
