@@ -86,8 +86,6 @@ def build_manager(w, device, seed, extra_tokens, ctx=None, graph=None):
     mgr = BlockGTQKVManager(L, n_q, n_kv, HD, max_seq_len=T + extra_tokens, batch_size=B, k_avg_bits=w["k_bits"],
                             v_bits=w["v_bits"], device=device, n_sink=w["n_sink"], recent_window=w["window"],
                             use_cuda_graph=graph)
-    mgr.programmatic = os.environ.get("BGTQ_NO_PROGRAMMATIC", "") == ""
-    mgr.fused_merge = os.environ.get("BGTQ_FUSED_MERGE", "") != ""
     for li in range(L):
         ck = torch.stack([synth_keys(gen, (1, 2048), w["theta"], device)[0] for _ in range(n_kv)])
         cq = torch.stack([synth_keys(gen, (gqa, 2048), w["theta"], device).reshape(-1, HD) for _ in range(n_kv)])
@@ -527,7 +525,6 @@ def main():
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--n-splits", type=int, default=None)
     ap.add_argument("--per-layer-graphs", action="store_true",
                     help="replay one CUDA graph per layer (append_and_attend) instead of one graph per decode step")
     args = ap.parse_args()
@@ -580,7 +577,7 @@ def main():
     hout = torch.empty(L, B, n_q, 1, HD, dtype=torch.float16).pin_memory()
     g_all = mgr.static_qkv_all()                                    # (L, B, n_q + 2 n_kv, 1, hd): per-layer step inputs
     g_in = [mgr.static_inputs(li) for li in range(L)]
-    graph_outputs = mgr._use_graph and args.n_splits is None       # results land in the manager's static output buffer
+    graph_outputs = mgr._use_graph                                 # results land in the manager's static output buffer
     step_no = [0]
 
     dqkv = torch.cat([qs, ks, vs], dim=3)                          # the same inputs, resident in HBM
@@ -603,7 +600,7 @@ def main():
             step_graph.replay()
             _lib.count_launch(launches_per_step)
             return None
-        return [mgr.append_and_attend(li, *g_in[li], n_splits=args.n_splits) for li in range(L)]
+        return [mgr.append_and_attend(li, *g_in[li]) for li in range(L)]
 
     def step_device():
         s = step_no[0]

@@ -75,11 +75,9 @@ _SIGNATURES = {
     "bgtq_rotate_q": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _vp, _i32, _i32, _i32, _vp]),
     "bgtq_decode_plan": (C.c_int, [_vp, _i32, _i32, _vp]),
     "bgtq_decode_default_splits": (C.c_int, [_i32, _i32, _i32]),
-    "bgtq_decode_fused": (C.c_int, [_vp, _vp, _vp,
-                                    _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
-                                    _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
-                                    _i32, _i32, _i32, _i32, _i32, _i32, _f32,
-                                    _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _vp, _vp]),
+    "bgtq_decode_image_bytes": (C.c_int64, [_vp]),
+    "bgtq_decode_build_image": (C.c_int, [_vp, _vp, _vp, _i64]),
+    "bgtq_decode_plan_set_image": (C.c_int, [_vp, _vp]),
     "bgtq_decode": (C.c_int, [_vp, _vp, _vp,
                               _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
                               _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,

@@ -16,7 +16,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from .layer import HD, combine, decode
+from .layer import HD, combine, decode, make_decode_plan
 
 _cache = {}
 
@@ -26,6 +26,7 @@ class _AdHocLayer:
 
     def __init__(self, segments, codebook_flat, v_lut, v_bits, n_kv, nopack, device):
         self.n_kv = n_kv
+        self.device = device
         self.desc_host = (_lib.HeadDesc * n_kv)()
         cb = codebook_flat.detach().to(torch.float16).cpu().view(torch.int16).numpy().astype(np.uint16)
         vl = v_lut.detach().to(torch.float16).cpu().view(torch.int16).numpy().astype(np.uint16)
@@ -47,11 +48,9 @@ class _AdHocLayer:
     def plan(self, flags=0):
         p = self._plans.get(flags)
         if p is None:
-            p = _lib.DecodePlan()
-            _lib.check(_lib.lib().bgtq_decode_plan(C.byref(self.desc_host), self.n_kv, flags, C.byref(p)),
-                       "bgtq_decode_plan")
+            p = make_decode_plan(self.desc_host, self.n_kv, flags, self.device)
             self._plans[flags] = p
-        return p
+        return p[0]
 
 
 def _layer_for(segments, codebook_flat, v_lut, v_bits, n_kv, device):

@@ -1,0 +1,592 @@
+// Fused unpack + dequantise + split-KV attention over the packed cache
+// (kernel b).  One launch covers every (batch, KV head) pair of a layer.
+//
+// Work distribution.  The live tokens of every pair are cut into n_splits
+// "items" of whole 32-token warp units; items are numbered head-major and each
+// CTA (one per SM, 16 warps) takes a contiguous range of them, computed on the
+// device from the live token count.  Consecutive items of one pair inside a
+// CTA form a "run": one stream of tiles, one softmax state, ONE partial (O, LSE)
+// written to the slot of the run's first item; the other slots of the run, and
+// the slots past the live items, get LSE = -inf, which the combine skips.  So
+// every SM works on the same number of tiles (to within one) whatever the
+// batch, head count or length, and per-CTA set-up happens once per SM.
+//
+// Per CTA:
+//   * the head's lookup tables arrive as a prebuilt, lane-replicated image
+//     (bgtq_plan.h) copied into shared memory with bulk (TMA) copies, before
+//     the programmatic dependency wait, and again only when the range crosses
+//     into another head;
+//   * tiles of 16 warps x 32 tokens of the four cache arrays (packed K, K
+//     norms, packed V, V norms) are streamed with 1-D bulk copies completed on
+//     mbarriers, two stages deep.  There is no producer warp: the last warp to
+//     finish with a stage refills it (a counter in shared memory tells a warp
+//     that it is the last);
+//   * each warp owns 32 tokens of a tile.  Codes are expanded straight into
+//     tensor-core operand registers through the tables:
+//        S^T(16 tok x 8 q)  = sum_seg norm_seg[tok] * ( Khat_seg(16 x k) . Qrot_seg^T )
+//        O^T(128 dim x 8 q) += Vhat^T(dim x 16 tok) . P^T(16 tok x 8 q)
+//     so the GQA group (<= 8 query heads) is the N dimension of m16n8k16 and no
+//     tile row is padding.  The K loop is specialised at compile time per stored
+//     width (immediate rotates and masks, one body per width with a run-time
+//     trip count); the segment list of the head drives which bodies run;
+//   * softmax state is fp32 and per warp; warps are merged at the end of a run
+//     through the (then idle) stage buffers.
+//   * rounding points follow the reference kernel
+//     (blockgtq/kernels/fused_packed_attention.py:770-873): fp32 logits,
+//     p rounded to fp16 for the PV product while the denominator uses fp32 p,
+//     vhat = fp16(fp16 centroid * fp16 norm), fp32 accumulation.
+#pragma once
+#include "bgtq_common.cuh"
+#include "bgtq_plan.h"
+
+namespace bgtq {
+
+constexpr int kDecWarps = 16;
+constexpr int kDecThreads = 32 * kDecWarps;
+constexpr int kDecStages = 2;
+constexpr int kMergeStride = 132;  // floats per query row in the end-of-run merge buffer
+// shared-memory layout (byte offsets from the start of dynamic shared memory)
+// [barriers | query fragments | per-warp max / denominators | lookup tables | stages (merge buffer at run end)]
+constexpr uint32_t kOffQf = 1024, kOffMM = kOffQf + kMaxSteps * 32 * 8, kOffLut = kLutAlign;
+static_assert(kOffMM + 2 * kDecWarps * 8 * 4 <= kOffLut, "layout");
+constexpr uint32_t kMergeBytes = kDecWarps * 8 * kMergeStride * 4;
+
+struct DecParams {
+    const __half* q_rot;
+    const uint8_t* kp;
+    const uint8_t* kn;  // byte pointers; strides below are in bytes
+    const uint8_t* vp;
+    const uint8_t* vn;
+    int64_t kp_sb, kp_sh, kn_sb, kn_sh, vp_sb, vp_sh, vn_sb, vn_sh;
+    int32_t kp_st, kn_st, vp_st, vn_st;  // bytes per token
+    int32_t n_batch, n_q, n_kv, gqa;
+    int32_t t_begin, t_end, n_splits;
+    const int32_t* pos_dev;
+    int32_t pos_add;
+    float scale_log2;
+    float* part_o;
+    float* part_lse;
+    int32_t* status;
+    uint32_t stage_off, stage_bytes, off_kn, off_v, off_vn;  // shared-memory layout
+    DecPlanDev plan;
+};
+
+// V unpack parameters per stored width: mask of the even-indexed codes of one
+// 32-bit group, groups per 16 codes, lane replication of the table.
+template <int VB> struct VCfg;
+template <> struct VCfg<1> { static constexpr uint32_t M = 0x5555u, GROUPS = 1, REP_SHIFT = 5; };
+template <> struct VCfg<2> { static constexpr uint32_t M = 0x33333333u, GROUPS = 1, REP_SHIFT = 5; };
+template <> struct VCfg<3> { static constexpr uint32_t M = 0x001C71C7u, GROUPS = 2, REP_SHIFT = 5; };
+template <> struct VCfg<4> { static constexpr uint32_t M = 0x0F0F0F0Fu, GROUPS = 2, REP_SHIFT = 3; };
+
+__device__ __forceinline__ uint32_t ld32(const uint8_t* sm, uint32_t off) {
+    return *reinterpret_cast<const uint32_t*>(sm + off);
+}
+__device__ __forceinline__ uint2 ld64(const uint8_t* sm, uint32_t off) {
+    return *reinterpret_cast<const uint2*>(sm + off);
+}
+__device__ __forceinline__ uint32_t ld16(const uint8_t* sm, uint32_t off) {
+    return *reinterpret_cast<const uint16_t*>(sm + off);
+}
+__device__ __forceinline__ uint32_t rotl32(uint32_t x, uint32_t n) { return __funnelshift_l(x, x, n); }
+
+// 16 codes of one token (bits [bit, bit + 16*VB) past word-aligned offset `row_al`) as one or two
+// 32-bit groups of 8 codes.
+template <int VB>
+__device__ __forceinline__ void load_v16(const uint8_t* sm, uint32_t row_al, uint32_t bit, uint32_t (&g)[2]) {
+    const uint32_t wa = row_al + ((bit >> 5) << 2);
+    const uint32_t w0 = ld32(sm, wa), w1 = ld32(sm, wa + 4);
+    const uint32_t sh = bit & 31u;
+    if constexpr (VB <= 2) {
+        g[0] = __funnelshift_r(w0, w1, sh);
+        g[1] = 0;
+    } else {
+        const uint32_t w2 = (sh + 16u * VB > 64u) ? ld32(sm, wa + 8) : 0u;
+        const uint32_t lo = __funnelshift_r(w0, w1, sh), hi = __funnelshift_r(w1, w2, sh);
+        if constexpr (VB == 3) {
+            g[0] = lo & 0xFFFFFFu;
+            g[1] = __funnelshift_r(lo, hi, 24) & 0xFFFFFFu;
+        } else {
+            g[0] = lo;
+            g[1] = hi;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// One K segment of a warp's token tile: acc[u] += Khat_seg(16 tokens x codes) . Qrot_seg^T.
+// KIND = stored bits per code.  Lane (r, j): token rows r + 8 i (i < 2 NU), the run of `q` codes at bit
+// `lbit` of each row; `tb` = table base with this lane's replica column; `qf` = this lane's query
+// fragments, one uint2 per k-tile, 32 apart.  Returns the number of k-tiles consumed.
+// ---------------------------------------------------------------------------------------------
+template <int KIND, int NU>
+__device__ __forceinline__ int k_segment(float (&acc)[NU][4], const uint8_t* sm, const uint32_t rowK,
+                                         const uint32_t k_row8, const uint32_t lbit, const int q, const uint32_t tb,
+                                         const uint32_t esh8, const uint32_t mask8, const uint2* qf, const bool f16n,
+                                         const uint32_t (&n2)[2 * NU]) {
+    constexpr int SB = KIND;                                   // stored bits
+    constexpr int CAP = KIND == 3 ? 8 : 32 / SB;               // codes per 32-bit unit
+    constexpr int TILES = CAP / 4;                             // k-tiles per unit
+    int step = 0;
+    for (int c = 0; c < q; c += CAP) {
+        const uint32_t pbit = lbit + (uint32_t)(c * SB);
+        const uint32_t wa = rowK + ((pbit >> 5) << 2);
+        uint32_t cur[2 * NU];
+#pragma unroll
+        for (int i = 0; i < 2 * NU; ++i)
+            cur[i] = __funnelshift_r(ld32(sm, wa + i * k_row8), ld32(sm, wa + i * k_row8 + 4), pbit);
+        const int n = q - c;                                   // codes left in the run (even)
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) {
+            if (4 * t >= n) break;
+            const uint2 bq = qf[step * 32];
+            ++step;
+            uint32_t lo[2 * NU], hi[2 * NU];                   // fp16x2 of codes (0,1) and (2,3) of this k-tile, per row
+            if constexpr (KIND == 1 || KIND == 2) {            // quad tables: one 64-bit lookup per row
+                constexpr uint32_t ESH = KIND == 1 ? kEsh1 : kEsh2, FW = 4 * SB;
+                constexpr uint32_t MASK = ((1u << FW) - 1u) << ESH;
+                const uint32_t R = (32u + ESH - FW * t) & 31u;
+#pragma unroll
+                for (int i = 0; i < 2 * NU; ++i) {
+                    const uint2 v = ld64(sm, (rotl32(cur[i], R) & MASK) | tb);
+                    lo[i] = v.x;
+                    hi[i] = v.y;
+                }
+            } else if constexpr (KIND == 3 || KIND == 4) {     // pair tables
+                constexpr uint32_t ESH = KIND == 3 ? kEsh3 : kEsh4, FW = 2 * SB;
+                constexpr uint32_t MASK = ((1u << FW) - 1u) << ESH;
+                const uint32_t R0 = (64u + ESH - 2 * FW * t) & 31u, R1 = (64u + ESH - 2 * FW * t - FW) & 31u;
+                const bool full = n - 4 * t >= 4;              // else codes 2, 3 meet a zero query fragment
+#pragma unroll
+                for (int i = 0; i < 2 * NU; ++i) {
+                    lo[i] = ld32(sm, (rotl32(cur[i], R0) & MASK) | tb);
+                    hi[i] = full ? ld32(sm, (rotl32(cur[i], R1) & MASK) | tb) : 0u;
+                }
+            } else {                                           // raw bytes, one code per lookup (fp16 in both halves)
+                const bool full = n - 4 * t >= 4;
+#pragma unroll
+                for (int i = 0; i < 2 * NU; ++i) {
+                    const uint32_t c0 = ld32(sm, (rotl32(cur[i], esh8) & mask8) | tb);
+                    const uint32_t c1 = ld32(sm, (rotl32(cur[i], esh8 + 24u) & mask8) | tb);
+                    lo[i] = __byte_perm(c0, c1, 0x5410);
+                    if (full) {
+                        const uint32_t c2 = ld32(sm, (rotl32(cur[i], esh8 + 16u) & mask8) | tb);
+                        const uint32_t c3 = ld32(sm, (rotl32(cur[i], esh8 + 8u) & mask8) | tb);
+                        hi[i] = __byte_perm(c2, c3, 0x5410);
+                    } else {
+                        hi[i] = 0u;
+                    }
+                }
+            }
+            if (f16n) {
+#pragma unroll
+                for (int i = 0; i < 2 * NU; ++i) {
+                    lo[i] = hmul2_u32(lo[i], n2[i]);
+                    hi[i] = hmul2_u32(hi[i], n2[i]);
+                }
+            }
+            const uint32_t b[2] = {bq.x, bq.y};
+#pragma unroll
+            for (int u = 0; u < NU; ++u) {
+                const uint32_t a[4] = {lo[2 * u], lo[2 * u + 1], hi[2 * u], hi[2 * u + 1]};
+                mma_16816(acc[u], a, b);
+            }
+        }
+    }
+    return step;
+}
+
+template <int VB, int NU>
+__global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_constant__ DecParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int kWarpTok = 16 * NU;              // tokens per warp and tile
+    constexpr int kTileTok = kDecWarps * kWarpTok; // tokens per CTA tile
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = lane >> 2, j = lane & 3;
+
+    // Everything up to grid_dependency_wait() touches only static tables, so under a programmatic
+    // launch it overlaps the tail of the preceding kernel (the step's append / query rotation).
+    grid_launch_dependents();
+
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);                      // [kDecStages]
+    uint64_t* lutbar = full + kDecStages;
+    unsigned int* done = reinterpret_cast<unsigned int*>(lutbar + 1);        // warps finished with a stage, ever
+    uint2* qfrag = reinterpret_cast<uint2*>(smem + kOffQf);                  // [step][lane]
+    float* mm = reinterpret_cast<float*>(smem + kOffMM);                     // [warp][8] running max
+    float* ml = mm + kDecWarps * 8;                                          // [warp][8] denominators
+    const uint8_t* sm = smem;
+    constexpr uint32_t lut_rel = kOffLut;
+
+    if (tid == 0) {
+        for (int i = 0; i < kDecStages; ++i) {
+            mbar_init(&full[i], 1);
+            done[i] = 0u;
+        }
+        mbar_init(lutbar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // ---- lookup tables of one head: bulk copies of the prebuilt image --------------------------------
+    int h_loaded = -1;
+    uint32_t lut_uses = 0;
+    bool ok = true;
+    auto load_tables = [&](int h) {       // called by all threads; the previous tables are no longer read
+        if (tid == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            const uint32_t bytes = (P.plan.head[h].image_bytes + 15u) & ~15u;
+            const uint8_t* src = P.plan.image + (size_t)h * P.plan.lut_bytes;
+            mbar_arrive_expect_tx(lutbar, bytes);
+            for (uint32_t o = 0; o < bytes; o += 32768u)
+                bulk_g2s(smem + lut_rel + o, src + o, min(32768u, bytes - o), lutbar);
+        }
+        h_loaded = h;
+    };
+    auto wait_tables = [&]() {
+        if (!mbar_wait_bounded(lutbar, lut_uses & 1u)) ok = false;
+        ++lut_uses;
+    };
+    const int n_cta = (int)gridDim.x, cta = (int)blockIdx.x;
+    load_tables(min(P.n_kv - 1, (int)(((int64_t)cta * P.n_kv) / n_cta)));   // the head this CTA most likely starts in
+    bool tables_pending = true;
+
+    grid_dependency_wait();
+    // ---- this CTA's range of items ---------------------------------------------------------------------
+    const int t_live = P.pos_dev ? min(P.t_end, *P.pos_dev + P.pos_add) : P.t_end;
+    const int n_tok = max(0, t_live - P.t_begin);
+    const int units = (n_tok + 31) >> 5;                             // 32-token warp units per pair
+    const int c_units = max(1, (units + P.n_splits - 1) / P.n_splits);  // units per item
+    const int n_live = (units + c_units - 1) / c_units;              // non-empty items per pair (<= n_splits)
+    const int n_pairs = P.n_batch * P.n_kv;
+    const int64_t n_items = (int64_t)n_pairs * n_live;
+    if (n_items == 0) {     // no tokens at all: every slot of every row is an empty split
+        for (int64_t i = (int64_t)cta * kDecThreads + tid; i < (int64_t)P.n_batch * P.n_q * P.n_splits;
+             i += (int64_t)n_cta * kDecThreads)
+            P.part_lse[i] = -INFINITY;
+        if (tables_pending) wait_tables();
+        return;
+    }
+    const int64_t item_lo = (int64_t)cta * n_items / n_cta, item_hi = (int64_t)(cta + 1) * n_items / n_cta;
+
+    const uint64_t pol = l2_evict_first_policy();
+    uint32_t g_it = 0;                      // tiles streamed so far by this CTA (stage = g_it % stages)
+    const uint32_t lane4 = (uint32_t)lane << 2;
+    constexpr uint32_t kVSh = VCfg<VB>::REP_SHIFT + 2;
+
+    for (int64_t item = item_lo; item < item_hi;) {
+        const int pair = (int)(item / n_live), s0 = (int)(item - (int64_t)pair * n_live);
+        const int cnt = (int)min((int64_t)(n_live - s0), item_hi - item);
+        item += cnt;
+        const int h = pair / P.n_batch, b = pair - h * P.n_batch;
+        const DecHeadPlan& hp = P.plan.head[h];
+        const int t0 = P.t_begin + 32 * s0 * c_units;
+        const int t1 = min(t_live, P.t_begin + 32 * (s0 + cnt) * c_units);
+        const int n_tiles = (t1 - t0 + kTileTok - 1) / kTileTok;
+
+        const size_t bh_kp = (size_t)b * P.kp_sb + (size_t)h * P.kp_sh;
+        const size_t bh_kn = (size_t)b * P.kn_sb + (size_t)h * P.kn_sh;
+        const size_t bh_vp = (size_t)b * P.vp_sb + (size_t)h * P.vp_sh;
+        const size_t bh_vn = (size_t)b * P.vn_sb + (size_t)h * P.vn_sh;
+        // One lane streams tile `it` of the run [t0, t1) into its stage.
+        auto issue_tile = [&](int it, uint32_t git) {
+            const int st = git % kDecStages;
+            const int t = t0 + it * kTileTok;
+            const int nt = min(kTileTok, t1 - t);
+            uint8_t* sb = smem + P.stage_off + (size_t)st * P.stage_bytes;
+            const uint8_t* s0p = P.kp + bh_kp + (size_t)t * P.kp_st;
+            const uint8_t* s1p = P.kn + bh_kn + (size_t)t * P.kn_st;
+            const uint8_t* s2p = P.vp + bh_vp + (size_t)t * P.vp_st;
+            const uint8_t* s3p = P.vn + bh_vn + (size_t)t * P.vn_st;
+            const uint32_t p0 = (uint32_t)(reinterpret_cast<uintptr_t>(s0p) & 15u), p1 = (uint32_t)(reinterpret_cast<uintptr_t>(s1p) & 15u);
+            const uint32_t p2 = (uint32_t)(reinterpret_cast<uintptr_t>(s2p) & 15u), p3 = (uint32_t)(reinterpret_cast<uintptr_t>(s3p) & 15u);
+            const uint32_t z0 = (p0 + (uint32_t)nt * P.kp_st + 15u) & ~15u, z1 = (p1 + (uint32_t)nt * P.kn_st + 15u) & ~15u;
+            const uint32_t z2 = (p2 + (uint32_t)nt * P.vp_st + 15u) & ~15u, z3 = (p3 + (uint32_t)nt * P.vn_st + 15u) & ~15u;
+            mbar_arrive_expect_tx(&full[st], z0 + z1 + z2 + z3);
+            bulk_g2s_hint(sb, s0p - p0, z0, &full[st], pol);
+            bulk_g2s_hint(sb + P.off_kn, s1p - p1, z1, &full[st], pol);
+            bulk_g2s_hint(sb + P.off_v, s2p - p2, z2, &full[st], pol);
+            bulk_g2s_hint(sb + P.off_vn, s3p - p3, z3, &full[st], pol);
+        };
+        if (h != h_loaded) {                 // the range crossed into another head (all warps are past the
+            if (tables_pending) {            // previous run's closing barrier, nobody reads the old tables)
+                wait_tables();               // a copy still in flight (wrong first guess) lands before the next
+                __syncthreads();             // one is armed on the same barrier
+            }
+            load_tables(h);
+            tables_pending = true;
+        }
+        if (tid == 0) {                      // first tiles of the run; the stage region is idle (see the run's end)
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            for (int it = 0; it < min(n_tiles, kDecStages); ++it) issue_tile(it, g_it + it);
+        }
+        // query fragments of this pair: step s, lane (g, jj)
+        for (int s = warp; s < hp.n_steps; s += kDecWarps) {
+            const DecStepQ st = hp.steps[s];
+            const int g = lane >> 2, jj = lane & 3;
+            const int pos = (int)st.pos + jj * (int)st.q;
+            const bool q_ok = g < P.gqa;
+            const __half* qrow = P.q_rot + ((size_t)b * P.n_q + (size_t)h * P.gqa + (q_ok ? g : 0)) * kHD;
+            uint2 v;
+            v.x = (q_ok && pos < (int)st.end) ? __ldg(reinterpret_cast<const uint32_t*>(qrow + pos)) : 0u;
+            v.y = (q_ok && (int)st.c4 + 2 < (int)st.q && pos + 2 < (int)st.end)
+                      ? __ldg(reinterpret_cast<const uint32_t*>(qrow + pos + 2)) : 0u;
+            qfrag[s * 32 + lane] = v;
+        }
+        if (tables_pending) {
+            wait_tables();
+            tables_pending = false;
+        }
+        __syncthreads();
+
+        // -------------------------------- the run's tiles --------------------------------
+        float O[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+        // Byte phases of the four arrays inside a stage (tiles advance every array by a multiple of 16
+        // bytes), and this lane's row offsets.  K side: tokens tok0 + 8 i; V side, row tile u: tokens
+        // tkv + 16u + {0, 1, 8, 9}.
+        const uint32_t k_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.kp) + bh_kp + (size_t)t0 * P.kp_st) & 15u);
+        const uint32_t kn_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.kn) + bh_kn + (size_t)t0 * P.kn_st) & 15u);
+        const uint32_t v_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.vp) + bh_vp + (size_t)t0 * P.vp_st) & 15u);
+        const uint32_t vn_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.vn) + bh_vn + (size_t)t0 * P.vn_st) & 15u);
+        const int tok0 = warp * kWarpTok + r, tkv = warp * kWarpTok + 2 * j;
+        const uint32_t k_off = k_pre + tok0 * P.kp_st;
+        const uint32_t k_row_al = k_off & ~3u, k_p0 = (k_off & 3u) << 3;
+        const uint32_t kn_row = P.off_kn + kn_pre + tok0 * P.kn_st;
+        const uint32_t v_off = P.off_v + v_pre + tkv * P.vp_st;
+        const uint32_t vn_row = P.off_vn + vn_pre + tkv * P.vn_st;
+        const uint32_t k_row8 = 8u * P.kp_st, kn_row8 = 8u * P.kn_st;
+        const uint32_t vtbl = lut_rel + hp.v_tbl + (lane4 & ((1u << kVSh) - 1u));
+        const int n_seg = hp.n_seg;
+
+        for (int it = 0; it < n_tiles; ++it, ++g_it) {
+            const int st = g_it % kDecStages;
+            const uint32_t use = g_it / kDecStages;
+            if (!mbar_wait_bounded(&full[st], use & 1u)) ok = false;
+            const int nt = min(kTileTok, t1 - (t0 + it * kTileTok));
+            const uint32_t sb = P.stage_off + st * P.stage_bytes;
+            if (warp * kWarpTok < nt) {
+                // ---------------- S^T = Khat . Qrot^T for NU 16-token row tiles ----------------
+                float S[NU][4];
+#pragma unroll
+                for (int u = 0; u < NU; ++u) S[u][0] = S[u][1] = S[u][2] = S[u][3] = 0.f;
+                const uint32_t rowK = sb + k_row_al, rowN = sb + kn_row;
+                const uint2* qf = qfrag + lane;
+                for (int sg = 0; sg < n_seg; ++sg) {
+                    const DecSeg sd = hp.seg[sg];
+                    // Norm handling: the bit-packed layout scales the fp32 dot product of a segment by its
+                    // fp16 norm; the nibble layout rounds centroid * norm to fp16 per element before the
+                    // product (fused_packed_attention.py:1449-1452), so there the norm is folded into the
+                    // operand.
+                    const bool f16n = sd.f16_norm != 0;
+                    float nrm[2 * NU];
+                    uint32_t n2[2 * NU];
+#pragma unroll
+                    for (int i = 0; i < 2 * NU; ++i) {
+                        const uint32_t nh = ld16(sm, rowN + 2u * sd.norm_idx + i * kn_row8);
+                        n2[i] = nh | (nh << 16);
+                        nrm[i] = f16n ? 1.0f : __half2float(__ushort_as_half((unsigned short)nh));
+                    }
+                    float acc[NU][4];
+#pragma unroll
+                    for (int u = 0; u < NU; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+                    const uint32_t lbit = k_p0 + sd.bit0 + (uint32_t)j * sd.lane_bits;
+                    const uint32_t tb = lut_rel + sd.tbl + (((uint32_t)lane & ((1u << sd.rep_log2) - 1u)) << sd.ent_log2);
+                    const int q = sd.q;
+                    int used;
+                    switch (sd.kind) {
+                        case 1: used = k_segment<1, NU>(acc, sm, rowK, k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
+                        case 2: used = k_segment<2, NU>(acc, sm, rowK, k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
+                        case 3: used = k_segment<3, NU>(acc, sm, rowK, k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
+                        case 4: used = k_segment<4, NU>(acc, sm, rowK, k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
+                        default:
+                            used = k_segment<8, NU>(acc, sm, rowK, k_row8, lbit, q, tb, (uint32_t)sd.esh,
+                                                    ((1u << sd.bw) - 1u) << sd.esh, qf, f16n, n2);
+                            break;
+                    }
+                    qf += used * 32;
+#pragma unroll
+                    for (int u = 0; u < NU; ++u) {
+                        S[u][0] = fmaf(nrm[2 * u], acc[u][0], S[u][0]);
+                        S[u][1] = fmaf(nrm[2 * u], acc[u][1], S[u][1]);
+                        S[u][2] = fmaf(nrm[2 * u + 1], acc[u][2], S[u][2]);
+                        S[u][3] = fmaf(nrm[2 * u + 1], acc[u][3], S[u][3]);
+                    }
+                }
+                // ---------------- online softmax (log2 domain) over the warp's tokens ----------------
+                float sv[NU][4];
+                float x0 = -INFINITY, x1 = -INFINITY;
+#pragma unroll
+                for (int u = 0; u < NU; ++u) {
+                    const bool okA = tok0 + 16 * u < nt, okB = tok0 + 16 * u + 8 < nt;
+                    sv[u][0] = okA ? S[u][0] * P.scale_log2 : -INFINITY;
+                    sv[u][1] = okA ? S[u][1] * P.scale_log2 : -INFINITY;
+                    sv[u][2] = okB ? S[u][2] * P.scale_log2 : -INFINITY;
+                    sv[u][3] = okB ? S[u][3] * P.scale_log2 : -INFINITY;
+                    x0 = fmaxf(x0, fmaxf(sv[u][0], sv[u][2]));
+                    x1 = fmaxf(x1, fmaxf(sv[u][1], sv[u][3]));
+                }
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {
+                    x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, o));
+                    x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, o));
+                }
+                const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+                const float z0 = n0 == -INFINITY ? 0.f : n0, z1 = n1 == -INFINITY ? 0.f : n1;
+                const float al0 = exp2f(m0 - z0), al1 = exp2f(m1 - z1);
+                m0 = n0;
+                m1 = n1;
+                uint32_t pf[NU][2];
+                float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+                for (int u = 0; u < NU; ++u) {
+                    const float p0 = exp2f(sv[u][0] - z0), p1 = exp2f(sv[u][1] - z1);
+                    const float p2 = exp2f(sv[u][2] - z0), p3 = exp2f(sv[u][3] - z1);
+                    ps0 += p0 + p2;
+                    ps1 += p1 + p3;
+                    pf[u][0] = movmatrix_trans(pack_half2(p0, p1));
+                    pf[u][1] = movmatrix_trans(pack_half2(p2, p3));
+                }
+                l0 = fmaf(l0, al0, ps0);
+                l1 = fmaf(l1, al1, ps1);
+                if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        O[i][0] *= al0;
+                        O[i][1] *= al1;
+                        O[i][2] *= al0;
+                        O[i][3] *= al1;
+                    }
+                }
+
+                // ---------------- O^T += Vhat^T . P^T ----------------
+                // Row tile u, this lane: tokens tkv+16u+{0,1} (pair AB) and +{8,9} (pair CD); dims 16r .. 16r+15.
+                constexpr uint32_t M = VCfg<VB>::M, G = VCfg<VB>::GROUPS, FW = 2 * VB;
+                constexpr uint32_t IMS = ((1u << FW) - 1u) << kVSh;
+                constexpr int PER = 8 / G;   // k-tiles (dim pairs) per 32-bit group
+#pragma unroll
+                for (int u = 0; u < NU; ++u) {
+                    uint32_t gA[2], gB[2], gC[2], gD[2];
+                    const uint32_t rv = sb + v_off + 16u * u * P.vp_st;
+                    const uint32_t base = rv & ~3u, bit = ((rv & 3u) << 3) + 16u * VB * r;
+                    load_v16<VB>(sm, base, bit, gA);
+                    load_v16<VB>(sm, base, bit + 8u * P.vp_st, gB);
+                    load_v16<VB>(sm, base, bit + 64u * P.vp_st, gC);
+                    load_v16<VB>(sm, base, bit + 72u * P.vp_st, gD);
+                    const int tq = tkv + 16 * u;
+                    const uint32_t rn = sb + vn_row + 16u * u * P.vn_st;
+                    const uint32_t hA = tq + 0 < nt ? ld16(sm, rn) : 0u;
+                    const uint32_t hB = tq + 1 < nt ? ld16(sm, rn + P.vn_st) : 0u;
+                    const uint32_t hC = tq + 8 < nt ? ld16(sm, rn + 8 * P.vn_st) : 0u;
+                    const uint32_t hD = tq + 9 < nt ? ld16(sm, rn + 9 * P.vn_st) : 0u;
+                    const uint32_t nab = hA | (hB << 16), ncd = hC | (hD << 16);
+#pragma unroll
+                    for (int g = 0; g < (int)G; ++g) {
+                        const uint32_t xab = (gA[g] & M) | ((gB[g] & M) << VB), yab = ((gA[g] >> VB) & M) | (gB[g] & (M << VB));
+                        const uint32_t xcd = (gC[g] & M) | ((gD[g] & M) << VB), ycd = ((gC[g] >> VB) & M) | (gD[g] & (M << VB));
+#pragma unroll
+                        for (int k = 0; k < PER; ++k) {
+                            // index pre-scaled by the entry stride: rotate so the field sits at bit kVSh
+                            const uint32_t rt = (32u + kVSh - FW * k) & 31u;
+                            uint32_t a[4];
+                            a[0] = hmul2_u32(ld32(sm, (rotl32(xab, rt) & IMS) | vtbl), nab);
+                            a[1] = hmul2_u32(ld32(sm, (rotl32(yab, rt) & IMS) | vtbl), nab);
+                            a[2] = hmul2_u32(ld32(sm, (rotl32(xcd, rt) & IMS) | vtbl), ncd);
+                            a[3] = hmul2_u32(ld32(sm, (rotl32(ycd, rt) & IMS) | vtbl), ncd);
+                            mma_16816(O[g * PER + k], a, pf[u]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            // Release the stage; the last warp to do so streams the tile that reuses it.  The counter only ever
+            // grows: after `use + 1` rounds of this stage all warps have added to it that many times.
+            if (lane == 0) {
+                __threadfence_block();
+                if (atomicAdd(&done[st], 1u) == (use + 1u) * kDecWarps - 1u && it + kDecStages < n_tiles) {
+                    __threadfence_block();
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    issue_tile(it + kDecStages, g_it + kDecStages);
+                }
+            }
+        }
+
+        // ---------------- merge the warps, write the run's partial ----------------
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+        }
+        // Every tile of the run has been consumed once all warps are here: the stage region is idle.
+        __syncthreads();
+        float* mo = reinterpret_cast<float*>(smem + P.stage_off);                // [warp][8][kMergeStride]
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            float* base = mo + (warp * 8 + 2 * j) * kMergeStride + 16 * r + 2 * mt;
+            base[0] = O[mt][0];
+            base[kMergeStride] = O[mt][1];
+            base[1] = O[mt][2];
+            base[kMergeStride + 1] = O[mt][3];
+        }
+        if (r == 0) {
+            mm[warp * 8 + 2 * j] = m0;
+            mm[warp * 8 + 2 * j + 1] = m1;
+            ml[warp * 8 + 2 * j] = l0;
+            ml[warp * 8 + 2 * j + 1] = l1;
+        }
+        __syncthreads();
+        {
+            const int qi = tid >> 6, d0 = (tid & 63) * 2;            // 64 threads per query head, two dims each
+            if (qi < P.gqa) {
+                float mx = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < kDecWarps; ++w) mx = fmaxf(mx, mm[w * 8 + qi]);
+                float wgt[kDecWarps], den = 0.f;
+#pragma unroll
+                for (int w = 0; w < kDecWarps; ++w) {
+                    wgt[w] = mx == -INFINITY ? 0.f : exp2f(mm[w * 8 + qi] - mx);
+                    den = fmaf(ml[w * 8 + qi], wgt[w], den);
+                }
+                const float inv = den > 0.f ? 1.f / den : 0.f;
+                float o[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kDecWarps; ++w) v = fmaf(mo[(w * 8 + qi) * kMergeStride + d0 + i], wgt[w], v);
+                    o[i] = v * inv;
+                }
+                const size_t row = ((size_t)b * P.n_q + (size_t)h * P.gqa + qi) * P.n_splits;
+                *reinterpret_cast<float2*>(P.part_o + (row + s0) * kHD + d0) = make_float2(o[0], o[1]);
+                if ((tid & 63) == 0)
+                    P.part_lse[row + s0] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -INFINITY;
+                // slots merged into this partial, and (after the pair's last live item) the slots past them
+                const int s_end = s0 + cnt == n_live ? P.n_splits : s0 + cnt;
+                for (int s = s0 + 1 + (tid & 63); s < s_end; s += 64) P.part_lse[row + s] = -INFINITY;
+            }
+        }
+        __syncthreads();      // the merge buffer is free again before the next run's tiles land in it
+    }
+    if (tables_pending) wait_tables();
+    if (!ok && P.status && lane == 0) atomicExch(P.status, kStatusWaitTimeout);
+}
+
+// Launch one instantiation; defined once per stored V width in its own translation unit.
+template <int VB>
+cudaError_t launch_decode(const DecParams& P, int nu, dim3 grid, size_t smem, cudaStream_t stream, bool programmatic) {
+    auto go = [&](void (*kern)(DecParams)) -> cudaError_t {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        return launch_kernel(kern, grid, dim3(kDecThreads), smem, stream, programmatic, P);
+    };
+    return nu == 2 ? go(decode_kernel<VB, 2>) : go(decode_kernel<VB, 1>);
+}
+
+cudaError_t launch_decode_vb1(const DecParams&, int, dim3, size_t, cudaStream_t, bool);
+cudaError_t launch_decode_vb2(const DecParams&, int, dim3, size_t, cudaStream_t, bool);
+cudaError_t launch_decode_vb3(const DecParams&, int, dim3, size_t, cudaStream_t, bool);
+cudaError_t launch_decode_vb4(const DecParams&, int, dim3, size_t, cudaStream_t, bool);
+
+}  // namespace bgtq

@@ -1,0 +1,196 @@
+// Host side of the decode kernel: the launch plan of a layer's KV heads, the
+// prebuilt lookup-table image the kernel copies into shared memory, and the
+// suggested split count.  No GPU work happens here.
+#include <string.h>
+
+#include "bgtq_common.cuh"
+#include "bgtq_plan.h"
+
+using namespace bgtq;
+
+namespace {
+
+struct TableDims {
+    uint32_t entries, ent_log2, rep_log2;
+    uint32_t bytes() const { return (entries << ent_log2) << rep_log2; }
+};
+
+TableDims k_table_dims(int kind, int bw) {
+    switch (kind) {
+        case 1: return {16u, 3u, kRep1};
+        case 2: return {256u, 3u, kRep2};
+        case 3: return {64u, 2u, kRep3};
+        case 4: return {256u, 2u, kRep4};
+        default: return {1u << bw, 2u, bw <= 6 ? 5u : (bw == 7 ? 4u : 3u)};
+    }
+}
+
+uint32_t v_rep_log2_for(int sbits) { return sbits <= 3 ? 5u : 3u; }
+
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const BgtqHeadDesc* desc_host, int32_t n_kv,
+                                                                       int32_t flags, BgtqDecodePlan* out) {
+    if (!desc_host || !out || n_kv < 1) return BGTQ_E_BADARG;
+    if (n_kv > kMaxPlanHeads) return BGTQ_E_TOOBIG;
+    static_assert(sizeof(DecPlanDev) <= sizeof(BgtqDecodePlan), "plan does not fit its public container");
+    DecPlanDev pl;
+    memset(&pl, 0, sizeof(pl));
+    pl.n_heads = n_kv;
+    pl.flags = flags;
+    pl.v_bits = desc_host[0].v_bits;
+    if (pl.v_bits < 1 || pl.v_bits > 4) return BGTQ_E_UNSUPPORTED;
+    pl.v_sbits = (flags & BGTQ_DEC_V_NIBBLE) ? 4 : pl.v_bits;
+    pl.v_rep_log2 = v_rep_log2_for(pl.v_sbits);
+    const uint32_t v_bytes = ((1u << (2 * pl.v_sbits)) << 2) << pl.v_rep_log2;
+    uint32_t lut_bytes = 0;
+    for (int h = 0; h < n_kv; ++h) {
+        const BgtqHeadDesc& d = desc_host[h];
+        if (d.v_bits != pl.v_bits) return BGTQ_E_UNSUPPORTED;
+        if (d.n_seg < 1 || d.n_seg > BGTQ_MAX_SEGMENTS) return BGTQ_E_BADARG;
+        DecHeadPlan& hp = pl.head[h];
+        hp.n_seg = d.n_seg;
+        uint32_t bytes_of[BGTQ_MAX_SEGMENTS + 1];
+        int step = 0;
+        for (int s = 0; s < d.n_seg; ++s) {
+            const int bw = d.seg_bw[s], len = d.seg_len[s], start = d.seg_start[s];
+            if (bw < 1 || bw > 8 || len < 2 || (len & 1) || start < 0 || start + len > kHD) return BGTQ_E_BADARG;
+            DecSeg& sg = hp.seg[s];
+            uint32_t bit0;
+            if (flags & BGTQ_DEC_K_MIXED) {
+                sg.kind = bw <= 4 ? 4 : 8;
+                bit0 = bw <= 4 ? start * 4u : 8u * (d.nopack_start / 2 + (start - d.nopack_start));
+            } else {
+                sg.kind = bw <= 4 ? bw : 8;
+                bit0 = 8u * d.seg_pack_off[s];
+            }
+            const TableDims td = k_table_dims(sg.kind, bw);
+            sg.bw = (uint8_t)bw;
+            sg.q = (uint8_t)(2 * ((len + 7) / 8));
+            // reference: only segments 0..4 of at least 16 dims take the tensor-core (fp16 operand) path
+            sg.f16_norm = ((flags & BGTQ_DEC_K_MIXED) && len >= 16 && s < 5) ? 1 : 0;
+            sg.lane_bits = (uint16_t)(sg.q * sg.kind);
+            if (bit0 + 3u * sg.lane_bits + 64u > 0xFFFFu) return BGTQ_E_UNSUPPORTED;
+            sg.bit0 = (uint16_t)bit0;
+            sg.ent_log2 = (uint8_t)td.ent_log2;
+            sg.rep_log2 = (uint8_t)td.rep_log2;
+            sg.esh = (uint8_t)(td.ent_log2 + td.rep_log2);
+            sg.norm_idx = (uint8_t)s;
+            bytes_of[s] = td.bytes();
+            if (bytes_of[s] > kLutAlign) return BGTQ_E_UNSUPPORTED;
+            for (int c4 = 0; c4 < sg.q; c4 += 4) {
+                if (step >= kMaxSteps) return BGTQ_E_UNSUPPORTED;
+                DecStepQ& st = hp.steps[step++];
+                st.pos = (uint8_t)(start + c4);
+                st.q = sg.q;
+                st.end = (uint8_t)(start + len);
+                st.c4 = (uint8_t)c4;
+            }
+        }
+        hp.n_steps = step;
+        bytes_of[d.n_seg] = v_bytes;
+        // Place tables largest first: every size is a power of two, so each lands on a multiple of its size.
+        uint32_t off = 0;
+        bool placed[BGTQ_MAX_SEGMENTS + 1] = {false};
+        for (int n = 0; n <= d.n_seg; ++n) {
+            int best = -1;
+            for (int s = 0; s <= d.n_seg; ++s)
+                if (!placed[s] && (best < 0 || bytes_of[s] > bytes_of[best])) best = s;
+            placed[best] = true;
+            if (best < d.n_seg) hp.seg[best].tbl = off;
+            else hp.v_tbl = off;
+            off += bytes_of[best];
+        }
+        hp.image_bytes = off;
+        lut_bytes = off > lut_bytes ? off : lut_bytes;
+    }
+    pl.lut_bytes = (lut_bytes + 127u) / 128u * 128u;
+    pl.image = nullptr;
+    memcpy(out, &pl, sizeof(pl));
+    return BGTQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int64_t bgtq_decode_image_bytes(const BgtqDecodePlan* plan_host) {
+    if (!plan_host) return BGTQ_E_BADARG;
+    DecPlanDev pl;
+    memcpy(&pl, plan_host, sizeof(pl));
+    if (pl.n_heads < 1 || pl.n_heads > kMaxPlanHeads) return BGTQ_E_BADARG;
+    return (int64_t)pl.n_heads * pl.lut_bytes;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_build_image(const BgtqDecodePlan* plan_host,
+                                                                              const BgtqHeadDesc* desc_host,
+                                                                              uint8_t* image_host, int64_t bytes) {
+    if (!plan_host || !desc_host || !image_host) return BGTQ_E_BADARG;
+    DecPlanDev pl;
+    memcpy(&pl, plan_host, sizeof(pl));
+    if (pl.n_heads < 1 || pl.n_heads > kMaxPlanHeads) return BGTQ_E_BADARG;
+    if (bytes < (int64_t)pl.n_heads * pl.lut_bytes) return BGTQ_E_BADARG;
+    memset(image_host, 0, (size_t)pl.n_heads * pl.lut_bytes);
+    for (int h = 0; h < pl.n_heads; ++h) {
+        const BgtqHeadDesc& d = desc_host[h];
+        const DecHeadPlan& hp = pl.head[h];
+        uint8_t* img = image_host + (size_t)h * pl.lut_bytes;
+        auto put = [&](uint32_t off, uint32_t word) { memcpy(img + off, &word, 4); };
+        for (int s = 0; s < hp.n_seg; ++s) {
+            const DecSeg& sg = hp.seg[s];
+            const uint16_t* cb = d.codebook + d.seg_lut_off[s];
+            const uint32_t cm = (1u << sg.bw) - 1u, reps = 1u << sg.rep_log2;
+            const uint32_t sb = sg.kind == 8 ? 8u : sg.kind, smk = (1u << sb) - 1u;
+            const uint32_t entries = sg.kind == 1 ? 16u : sg.kind == 3 ? 64u : sg.kind == 8 ? (1u << sg.bw) : 256u;
+            for (uint32_t e = 0; e < entries; ++e) {
+                uint32_t w0, w1 = 0;
+                if (sg.kind == 8) {
+                    w0 = cb[e & cm] | ((uint32_t)cb[e & cm] << 16);
+                } else {
+                    auto code = [&](int k) { return ((e >> (k * sb)) & smk) & cm; };
+                    w0 = cb[code(0)] | ((uint32_t)cb[code(1)] << 16);
+                    if (sg.kind <= 2) w1 = cb[code(2)] | ((uint32_t)cb[code(3)] << 16);
+                }
+                for (uint32_t r = 0; r < reps; ++r) {
+                    const uint32_t off = sg.tbl + (e << sg.esh) + (r << sg.ent_log2);
+                    put(off, w0);
+                    if (sg.ent_log2 == 3) put(off + 4, w1);
+                }
+            }
+        }
+        const uint32_t vb = (uint32_t)pl.v_sbits, vm = (1u << pl.v_bits) - 1u, smk = (1u << vb) - 1u;
+        const uint32_t vesh = 2u + pl.v_rep_log2;
+        for (uint32_t e = 0; e < (1u << (2 * vb)); ++e) {
+            const uint32_t w = d.v_lut[(e & smk) & vm] | ((uint32_t)d.v_lut[(e >> vb) & vm] << 16);
+            for (uint32_t r = 0; r < (1u << pl.v_rep_log2); ++r) put(hp.v_tbl + (e << vesh) + (r << 2), w);
+        }
+    }
+    return BGTQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan_set_image(BgtqDecodePlan* plan_host,
+                                                                                 const uint8_t* image_dev) {
+    if (!plan_host) return BGTQ_E_BADARG;
+    if (reinterpret_cast<uintptr_t>(image_dev) & 15u) return BGTQ_E_ALIGN;
+    DecPlanDev pl;
+    memcpy(&pl, plan_host, sizeof(pl));
+    pl.image = image_dev;
+    memcpy(plan_host, &pl, sizeof(pl));
+    return BGTQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv,
+                                                                                 int32_t n_tokens) {
+    // The launch cuts every (batch, KV head) pair into n_splits equal items of whole 32-token warp units and
+    // hands each of its CTAs (one per SM) a contiguous run of items; consecutive items of one pair inside a
+    // CTA become ONE partial.  So the split count only sets the granularity at which work is balanced, and
+    // finer is better until the partial buffer and the combine's scan over a row's slots grow: aim at four
+    // items per CTA, items of at most one 512-token tile, at most 256 slots per pair.
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    else cudaGetLastError();
+    const long pairs = (long)n_batch * n_kv > 0 ? (long)n_batch * n_kv : 1;
+    const long units = ((long)(n_tokens > 0 ? n_tokens : 0) + 31) / 32;
+    if (units <= 1) return 1;
+    long c = (pairs * units + 4L * sms - 1) / (4L * sms);
+    c = c < 1 ? 1 : (c > 16 ? 16 : c);
+    const long c_min = (units + 255) / 256;
+    c = c < c_min ? c_min : c;
+    return (int)((units + c - 1) / c);
+}

@@ -3,55 +3,73 @@
 // uniform loads instead of occupying registers or shared-memory bandwidth.
 //
 // Code ownership inside a warp: the four lanes of a quad share one token.  For
-// a K segment of `len` codes, n_kt = ceil(len/16) MMA k-tiles are issued and
-// lane j (0..3) owns the contiguous run of q = 4*n_kt codes starting at code
-// j*q, so ONE unaligned 32-bit shared-memory load ("unit") feeds up to eight
-// k-tiles of that lane (32/16/8/8/4 codes for stored widths 1/2/3/4/8 bits).
+// a K segment of `len` codes, lane j (0..3) owns the contiguous run of
+// q = 2*ceil(len/8) codes starting at code j*q; the run is consumed four codes
+// (one m16n8k16 k-tile) at a time, and one unaligned 32-bit shared-memory load
+// (a "unit") feeds 32/16/8/8/4 codes for stored widths 1/2/3/4/8 bits.  Codes
+// of a lane's run that lie beyond the segment (q rounds up) meet a zero in the
+// query fragment, so whatever bits they pick up contribute nothing.
 //
-// Lookup tables are aligned to their own size inside the LUT region, so the
-// address of an entry is (rotate(unit_word, r) & mask) | table_base: the index
-// lands pre-scaled by the entry stride and ORs into the base.
+// Lookup tables arrive as a prebuilt, lane-replicated image (one per KV head,
+// made on the host next to the plan and kept in device memory by the caller);
+// a CTA copies its head's image into shared memory with bulk copies.  Each
+// table is aligned to its own size inside the image, so the address of an
+// entry is (rotate(unit_word, r) & mask) | table_base: the index lands
+// pre-scaled by the entry stride and ORs into the base.
+//
+//   stored width   entry                      index        replicas  bytes
+//   1 bit          4 codes -> 2 x fp16x2      4 bits       32        4096
+//   2 bits         4 codes -> 2 x fp16x2      8 bits       4         8192
+//   3 bits         2 codes -> fp16x2          6 bits       32        8192
+//   4 bits         2 codes -> fp16x2          8 bits       8         8192
+//   8 bits (5..8)  1 code  -> fp16 (twice)    bw bits      32..8     4096/8192
+//   V (pair of tokens, one dim) -> fp16x2     2*vb bits    32..8     <= 8192
 #pragma once
 #include <stdint.h>
 
 namespace bgtq {
 
-constexpr int kMaxSteps = 16;        // MMA k-tiles per token tile: at most 8 + 7 per head
+constexpr int kMaxSteps = 20;        // m16n8k16 k-tiles per token tile and head: sum over segments of ceil(q/4)
 constexpr int kMaxPlanHeads = 8;     // KV heads per launch
-constexpr uint32_t kLutTableBytes = 4096;  // size cap (and alignment) of one lookup table incl. lane replication
+constexpr uint32_t kLutAlign = 8192; // largest table; the LUT region starts on a multiple of it
 
-// One lookup table (= one K width segment).
-struct DecSegTbl {
-    uint16_t word_off;   // first 32-bit word of the table inside the (aligned) LUT region
-    uint16_t cb_off;     // first codebook entry of the segment
-    uint8_t sbits;       // stored bits per code (1..4, or 8 for raw bytes)
+// log2 of the byte distance between consecutive table entries (entry size x replicas), per stored width
+constexpr uint32_t kEsh1 = 8, kEsh2 = 5, kEsh3 = 7, kEsh4 = 5;
+// log2 of the replica count / of the entry size in bytes, per stored width (kind 8: see DecSeg)
+constexpr uint32_t kRep1 = 5, kRep2 = 2, kRep3 = 5, kRep4 = 3;
+static_assert(kEsh1 == 3 + kRep1 && kEsh2 == 3 + kRep2 && kEsh3 == 2 + kRep3 && kEsh4 == 2 + kRep4,
+              "entry stride = entry size x replicas");
+
+// One K width segment = one lookup table = one norm group.
+struct DecSeg {
+    uint8_t kind;        // stored bits per code: 1, 2, 3, 4, or 8 (raw byte, code widths 5..8)
     uint8_t bw;          // codebook width (entries = 2^bw)
-    uint8_t rep_shift;   // log2 of the per-lane replication
-    uint8_t pair;        // 1: entry = two codes -> fp16x2, 0: one code -> fp16
-    uint32_t n_words;
-    uint8_t n_kt;        // MMA k-tiles of the segment
-    uint8_t kt_per_unit; // k-tiles fed by one 32-bit unit load
+    uint8_t q;           // codes per lane (even)
     uint8_t f16_norm;    // 1: fold the norm into each value as fp16(centroid * norm) (nibble-layout numerics)
-    uint8_t pad;
+    uint16_t bit0;       // bit offset of lane 0's run inside a packed row
+    uint16_t lane_bits;  // q * stored bits: distance between the runs of neighbouring lanes
+    uint32_t tbl;        // byte offset of the table inside the LUT image (a multiple of the table size)
+    uint8_t esh;         // log2(bytes between consecutive entries)
+    uint8_t rep_log2;    // log2(replicas)
+    uint8_t ent_log2;    // log2(entry bytes): 2 or 3
+    uint8_t norm_idx;    // which of the token's norms scales this segment
 };
 
-// One m16n8k16 k-tile.
-struct DecStep {
-    uint32_t a;  // [11:0] bit offset of the unit in a packed row (lane 0), [21:12] bits between lanes' runs,
-                 // [22] load a new unit, [23] pair table, [24] first k-tile of a segment (fetch its norm)
-    uint32_t b;  // [4:0] rotate for the first lookup, [9:5] rotate for the second (pair tables),
-                 // [14:10] log2(bytes per table entry incl. replication), [18:15] segment index
-    uint32_t c;  // [15:0] index mask already shifted by the entry stride, [31:16] table byte offset
-    uint32_t q;  // [7:0] first packed position of lane 0, [13:8] codes per lane in the segment, [21:14] segment end
+// Query fragment of one k-tile: lane (g, j) holds q[g][pos + j*q .. +1] and q[g][pos + j*q + 2 .. +3].
+struct DecStepQ {
+    uint8_t pos;   // packed position of lane 0's first code in this k-tile
+    uint8_t q;     // codes per lane in the segment
+    uint8_t end;   // first packed position past the segment (positions >= end read as zero)
+    uint8_t c4;    // offset of the k-tile inside the lane's run (codes c4 .. c4+3; c4 + 2 >= q: second half is zero)
 };
 
 struct DecHeadPlan {
     int32_t n_steps;
     int32_t n_seg;
-    uint32_t v_word_off;
-    uint32_t pad;
-    DecSegTbl seg[8];
-    DecStep steps[kMaxSteps];
+    uint32_t v_tbl;        // byte offset of the V table inside the LUT image
+    uint32_t image_bytes;  // bytes of this head's image (multiple of 16)
+    DecSeg seg[8];
+    DecStepQ steps[kMaxSteps];
 };
 
 struct DecPlanDev {
@@ -59,10 +77,9 @@ struct DecPlanDev {
     int32_t flags;
     int32_t v_bits;       // codebook width of V
     int32_t v_sbits;      // stored bits per V code
-    uint32_t v_rep_shift;
-    uint32_t v_n_words;
-    uint32_t lut_bytes;   // size of the LUT region (max over heads), multiple of 128
-    uint32_t pad;
+    uint32_t v_rep_log2;
+    uint32_t lut_bytes;   // bytes reserved per head in the image and in shared memory (max over heads, multiple of 128)
+    const uint8_t* image; // device memory: n_heads images, lut_bytes apart (set with bgtq_decode_plan_set_image)
     DecHeadPlan head[kMaxPlanHeads];
 };
 

@@ -56,6 +56,23 @@ def _fill_desc(d: _lib.HeadDesc, kt: KHeadTables, vt: VHeadTables):
     C.memmove(d.group_of, go.ctypes.data, HD)
 
 
+def make_decode_plan(desc_host, n_kv: int, flags: int, device):
+    """Decode plan of a layer's KV heads with its lookup-table image uploaded to ``device``.
+    Returns (plan, image tensor); the caller keeps the image alive as long as the plan is used."""
+    L = _lib.lib()
+    p = _lib.DecodePlan()
+    _lib.check(L.bgtq_decode_plan(C.byref(desc_host), n_kv, flags, C.byref(p)), "bgtq_decode_plan")
+    n = int(L.bgtq_decode_image_bytes(C.byref(p)))
+    if n <= 0:
+        raise RuntimeError("bgtq_decode_image_bytes failed")
+    host = np.zeros(n, dtype=np.uint8)
+    _lib.check(L.bgtq_decode_build_image(C.byref(p), C.byref(desc_host), host.ctypes.data, n),
+               "bgtq_decode_build_image")
+    image = torch.from_numpy(host).to(device)
+    _lib.check(L.bgtq_decode_plan_set_image(C.byref(p), image.data_ptr()), "bgtq_decode_plan_set_image")
+    return p, image
+
+
 class LayerTables:
     """Device-resident static tables for the KV heads of one layer."""
 
@@ -82,11 +99,9 @@ class LayerTables:
     def plan(self, flags: int = 0) -> _lib.DecodePlan:
         p = self._plans.get(flags)
         if p is None:
-            p = _lib.DecodePlan()
-            _lib.check(_lib.lib().bgtq_decode_plan(C.byref(self.desc_host), self.n_kv, flags, C.byref(p)),
-                       "bgtq_decode_plan")
+            p = make_decode_plan(self.desc_host, self.n_kv, flags, self.device)
             self._plans[flags] = p
-        return p
+        return p[0]
 
 
 def _strides3(t: torch.Tensor):
@@ -241,13 +256,11 @@ def default_splits(n_batch: int, n_kv: int, n_tokens: int) -> int:
 
 
 def decode(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_norms, t_begin, t_end, *,
-           n_splits=None, scale=None, flags=0, part_o=None, part_lse=None, status=None, pos_dev=None, pos_add=0,
-           fused_out=None, tickets=None, v_rot=None):
+           n_splits=None, scale=None, flags=0, part_o=None, part_lse=None, status=None, pos_dev=None, pos_add=0):
     """Split-KV attention partials over cache rows [t_begin, t_end).
 
-    Returns (part_o (B, n_q, n_splits, 128) f32, part_lse (B, n_q, n_splits) f32).  With ``fused_out``
-    (fp16 (B, n_q, 128)) and ``tickets`` (zeroed int32 (B * n_kv)) the merge of the splits, V's rotation
-    ``v_rot`` and the fp16 store happen inside the same launch (``bgtq_decode_fused``)."""
+    Returns (part_o (B, n_q, n_splits, 128) f32, part_lse (B, n_q, n_splits) f32); slots that hold no
+    partial have ``part_lse = -inf`` and an undefined ``part_o`` row (see ``bgtq_decode``)."""
     _lib.require_cuda(q_rot, "q_rot")
     B, n_q, _ = q_rot.shape
     if not q_rot.is_contiguous() or q_rot.dtype != torch.float16:
@@ -265,16 +278,6 @@ def decode(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_norms, t_be
     kps, kns, vps = _strides3(k_packed), _strides3(k_norms), _strides3(v_packed)
     vns = (v_norms.stride(0), v_norms.stride(1), v_norms.stride(2))
     plan = layer.plan(flags)
-    if fused_out is not None:
-        _lib.check(_lib.lib().bgtq_decode_fused(
-            C.addressof(plan), _lib.ptr(layer.desc_dev), _lib.ptr(q_rot),
-            _lib.ptr(k_packed), *kps, _lib.ptr(k_norms), *kns, _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns,
-            B, n_q, layer.n_kv, int(t_begin), int(t_end), int(n_splits), float(scale),
-            _lib.ptr(part_o), _lib.ptr(part_lse), _lib.ptr(status), _lib.ptr(pos_dev), int(pos_add),
-            _lib.ptr(v_rot), _lib.ptr(fused_out), fused_out.stride(0), fused_out.stride(1), _lib.ptr(tickets),
-            _lib.stream_ptr(q_rot.device)), "bgtq_decode_fused")
-        _lib.count_launch()
-        return part_o, part_lse
     _lib.check(_lib.lib().bgtq_decode(
         C.addressof(plan), _lib.ptr(layer.desc_dev), _lib.ptr(q_rot),
         _lib.ptr(k_packed), *kps, _lib.ptr(k_norms), *kns, _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns,

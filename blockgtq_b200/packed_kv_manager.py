@@ -68,10 +68,6 @@ class BlockGTQKVManager:
         self.k_mixed, self.v_nibble = bool(k_mixed), bool(v_nibble)
         self.programmatic = True              # chain the step's kernels as programmatic dependent launches
         self._exchange = None                 # sequence sharding: see sharding.SequenceShard
-        # True: the decode launch also merges its splits (bgtq_decode_fused, no combine launch).  Off by default:
-        # with the programmatic chain the separate combine overlaps the decode tail and the step measured
-        # 3.21 ms against 3.30 ms fused (36 layers, batch 8, 32768 tokens)
-        self.fused_merge = False
         self._enc_flags = (_lib.ENC_K_MIXED if k_mixed else 0) | (_lib.ENC_V_NIBBLE if v_nibble else 0)
         self._dec_flags = (_lib.DEC_K_MIXED if k_mixed else 0) | (_lib.DEC_V_NIBBLE if v_nibble else 0)
         # single-token decode steps are captured once per layer and replayed (the reference graphs only
@@ -140,8 +136,6 @@ class BlockGTQKVManager:
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
         # scratch reused by every layer step (stream ordered): rotated queries and split partials
         self._n_splits = default_splits(self.B, self.n_kv, self.max_T) if dev.type == "cuda" else 1
-        if os.environ.get("BGTQ_N_SPLITS"):           # experiments: fix the split count of the decode launch
-            self._n_splits = max(1, int(os.environ["BGTQ_N_SPLITS"]))
         self._q_rot = torch.empty(self.B, self.n_q, self.hd, dtype=torch.float16, device=dev)
         self._part_o = torch.empty(self.B, self.n_q, self._n_splits, self.hd, dtype=torch.float32, device=dev)
         self._part_lse = torch.empty(self.B, self.n_q, self._n_splits, dtype=torch.float32, device=dev)
@@ -149,7 +143,6 @@ class BlockGTQKVManager:
                                   device=dev)
         self._g_out = torch.zeros(self.n_layers, self.B, self.n_q, self.hd, dtype=torch.float16, device=dev)
         self._pos = torch.zeros(1, dtype=torch.int32, device=dev)
-        self._tickets = torch.zeros(self.B * self.n_kv, dtype=torch.int32, device=dev)
         self._g_rope = torch.zeros(2, self.B, self.hd, dtype=torch.float16, device=dev)     # cos, sin of the step
         self._buf_o = torch.zeros(self.B, self.n_q, self.hd, dtype=torch.float32, device=dev)
         self._buf_lse = torch.zeros(self.B, self.n_q, dtype=torch.float32, device=dev)
@@ -314,12 +307,8 @@ class BlockGTQKVManager:
                0, self.max_T, n_splits=self._n_splits, scale=self.scale, status=self._status,
                part_o=self._part_o, part_lse=self._part_lse, pos_dev=self._pos,
                pos_add=1 if (ex is None or ex.is_owner) else 0,
-               flags=self._dec_flags | (_lib.DEC_PROGRAMMATIC if pd else 0),
-               fused_out=self._g_out[li] if (ex is None and self.fused_merge) else None,
-               tickets=self._tickets, v_rot=lt.v_rot)
-        if ex is None and self.fused_merge:
-            pass                                  # merged, rotated and stored by the decode launch itself
-        elif ex is None:
+               flags=self._dec_flags | (_lib.DEC_PROGRAMMATIC if pd else 0))
+        if ex is None:
             combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li], programmatic=pd)
         else:       # local result straight into the message, exchange (all-gather or peer stores), merge of the messages
             combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li], programmatic=pd,
@@ -363,8 +352,7 @@ class BlockGTQKVManager:
             self._graphs[li][use_rope] = g
         else:
             g.replay()
-            _lib.count_launch(4 if self._buffered else
-                              (2 if (self._exchange is None and self.fused_merge) else (5 if self._exchange else 3)))
+            _lib.count_launch(4 if self._buffered else (5 if self._exchange else 3))
         return self._g_out[li]
 
     # -- decode ----------------------------------------------------------------------------

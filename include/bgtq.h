@@ -214,14 +214,27 @@ int bgtq_step_prepare_ring(const BgtqHeadDesc* desc, const float* rot_k, const f
 /* Opaque launch plan of the decode kernel for the KV heads of one layer (host
  * memory, plain bytes, copyable).  Built once per layer from the HOST copy of
  * the head descriptors; at most 8 KV heads per plan (split wider layers into
- * groups of heads). */
+ * groups of heads).  The reference specialises its decode kernel per head with
+ * Triton constexprs (blockgtq/production_cache.py:19-22); here the per-head
+ * layout travels in the plan and in a prebuilt lookup-table image.
+ *
+ * The kernel reads its lookup tables (codebooks expanded into lane-replicated
+ * fp16x2 tables, one set per KV head) from an image in DEVICE memory that the
+ * caller owns: ask for its size, let the library fill a host buffer, copy that
+ * buffer to the device (16-byte aligned) and record the device address in the
+ * plan.  The image must stay valid while launches that use the plan run. */
 typedef struct BgtqDecodePlan {
     uint8_t opaque[4096];
 } BgtqDecodePlan;
 int bgtq_decode_plan(const BgtqHeadDesc* desc_host, int32_t n_kv, int32_t flags, BgtqDecodePlan* plan_host);
+int64_t bgtq_decode_image_bytes(const BgtqDecodePlan* plan_host);            /* > 0, or a negative error code */
+int bgtq_decode_build_image(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc_host,
+                            uint8_t* image_host, int64_t bytes);             /* host buffers only */
+int bgtq_decode_plan_set_image(BgtqDecodePlan* plan_host, const uint8_t* image_dev);
 
-/* Number of token splits the library suggests for a (batch, heads, tokens)
- * shape on the current device (host helper, no GPU work). */
+/* Number of partial slots per (batch, KV head) pair the library suggests for a
+ * (batch, heads, tokens) shape on the current device (host helper, no GPU work):
+ * fine enough that every SM gets the same number of token tiles. */
 int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv, int32_t n_tokens);
 
 /* Fused unpack + dequantise + split-KV attention of one decode query per
@@ -231,25 +244,35 @@ int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv, int32_t n_tokens);
  * (blockgtq/kernels/fused_packed_attention.py:152-894, wrapper :1541-1843), for
  * every KV head of a layer in ONE launch (the reference launches per head).
  *
- * plan_host: from bgtq_decode_plan (host memory); desc: the same descriptors on
- * the device.  q_rot: (n_batch, n_q, 128) fp16 contiguous, already in the
- * packed-K basis; n_q / n_kv <= 8.
+ * plan_host: from bgtq_decode_plan, with its image set (host memory); desc is
+ * unused (the tables come from the image) and may be NULL.  q_rot: (n_batch,
+ * n_q, 128) fp16 contiguous, already in the packed-K basis; n_q / n_kv <= 8.
  * Cache row (b,h,t): k_packed + b*kp_sb + h*kp_sh + t*kp_st  (bytes; rows of one
  * (b,h) must be equally spaced), k_norms fp16 at + b*kn_sb + h*kn_sh + t*kn_st
  * (+ segment index), v_packed / v_norms likewise (v_norms: one fp16 per token).
- * Rows need no particular alignment.
- * Outputs, for split c of n_splits (tokens are cut into n_splits equal runs
- * rounded up to 32 tokens):
+ * Rows need no particular alignment, but tiles are fetched with 16-byte-aligned
+ * bulk copies: up to 15 bytes before the first and after the last row of the
+ * token range of every (b,h) are READ (never used), so each of the four arrays
+ * must have that much addressable memory on either side of a pair's rows (any
+ * allocation whose rows do not start or end exactly on its first / last 16-byte
+ * boundary qualifies; a cache tensor with a few spare token rows always does).
+ *
+ * Work split and outputs.  The live tokens of every pair are cut into n_splits
+ * equal items of whole 32-token units; each CTA (one per SM) takes a contiguous
+ * range of items, and consecutive items of one pair inside a CTA produce ONE
+ * partial, stored in the slot of the first of them:
  *   part_o  (n_batch, n_q, n_splits, 128) fp32  softmax-normalised partial
- *           output, still in V's rotated basis (16-byte aligned)
+ *           output, still in V's rotated basis (8-byte aligned)
  *   part_lse(n_batch, n_q, n_splits)      fp32  log-sum-exp of the scaled
- *           logits of the split; -inf for a split with no tokens (part_o = 0).
+ *           logits of the partial; -inf for a slot that holds no partial (its
+ *           part_o row is then NOT written and must not be read).
+ * Every part_lse element is written by every launch.
  * status: optional int32 on the device; set to a non-zero code if a bounded
  * wait inside the kernel gave up (the output is then invalid).
  * pos_dev / pos_add: optional device int32; when non-NULL the range ends at
- * min(t_end, *pos_dev + pos_add), read when the kernel runs; t_end then only
- * bounds the range and fixes how tokens are cut into splits (graph replay).
- */
+ * min(t_end, *pos_dev + pos_add), read when the kernel runs (after the
+ * programmatic dependency wait), and the items are cut from that live length:
+ * t_end then only bounds the range (graph replay). */
 int bgtq_decode(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot,
                 const uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
                 const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
@@ -259,26 +282,6 @@ int bgtq_decode(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const
                 int32_t t_begin, int32_t t_end, int32_t n_splits, float scale,
                 float* part_o, float* part_lse, int32_t* status,
                 const int32_t* pos_dev, int32_t pos_add, void* stream);
-
-/* bgtq_decode with the split merge folded into the same launch: the last CTA of every (batch, KV head)
- * to finish (a ticket counter per pair) merges that pair's partials, applies V's rotation
- * (v_rot: (n_kv,128,128) fp32 = R, may be NULL) and writes fp16 out (n_batch, n_q, 128) at
- * out + b*o_sb + hq*o_sh (8-byte aligned rows) -- the work of bgtq_combine without its launch, for steps
- * with no fp16-buffer partial to fold in.  part_o / part_lse are still required (scratch).  It saves a
- * launch; inside a programmatic chain the separate bgtq_combine overlaps the decode tail and is as fast.
- * tickets: n_batch * n_kv int32, ZERO before the first use; every launch leaves them zero again, so one
- * buffer serves all layers of a stream.  Two launches that may overlap on the GPU need separate
- * tickets and partial buffers. */
-int bgtq_decode_fused(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot,
-                const uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
-                const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
-                const uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
-                const void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
-                int32_t n_batch, int32_t n_q, int32_t n_kv,
-                int32_t t_begin, int32_t t_end, int32_t n_splits, float scale,
-                float* part_o, float* part_lse, int32_t* status,
-                const int32_t* pos_dev, int32_t pos_add,
-                const float* v_rot, void* out, int64_t o_sb, int64_t o_sh, int32_t* tickets, void* stream);
 
 /* Attention of the same queries over tokens kept unquantised in fp16 (the
  * sink prefix and the recent window of the three-region cache policy,
@@ -408,7 +411,7 @@ int bgtq_exchange_merge(const float* local_buf, int32_t n_ranks, int64_t rank_st
  *   - all calls on a device share the one array: two calls whose kernels can
  *     overlap on the GPU (different streams without ordering) race.  Nothing in
  *     the array has to be cleared between calls: every partial that is read was
- *     written by the same call. */
+ *     written by the same call (slots that hold no partial are marked and skipped). */
 int bgtq_decode_combined_noalloc(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc, const void* q_rot,
                 const uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
                 const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,

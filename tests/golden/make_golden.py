@@ -4,7 +4,8 @@ Run once, in a container where the reference checkout is available:
 
     TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/reference [manager]
 
-(a second argument, ``manager``, ``production`` or ``prefill``, regenerates only that fixture; each has its own seed)
+(a second argument, ``manager``, ``production``, ``prefill`` or the name of a layer-shaped case, regenerates only
+that fixture; each has its own seed)
 
 The reference's Triton kernels are executed by Triton's CPU interpreter
 (``tl.dot`` is a float32 ``np.matmul`` there), so the vectors are the
@@ -17,6 +18,9 @@ Fixtures
   decode_<case>.npz   packed cache + query -> attention output and LSE per KV head
   prefill.npz         packed cache + 24 queries at positions 40..63 -> causal prefill attention output
   manager.npz         BlockGTQKVManager: bulk encode + two append_and_attend steps, batch 2
+  shape_<name>.npz    layer-shaped cases (8 KV heads, thousands of tokens): per-head bit maps, the packed cache
+                      of every head and the decode output for one query past the end; the fp16 K/V inputs
+                      are not stored but regenerated from the seed by ``helpers.synth_layer_case``
   production.npz      BlockGTQProductionCache (nibble/mixed layout): bulk encode + two decode steps, batch 1
 """
 import hashlib
@@ -330,8 +334,72 @@ def dump_prefill(gen, case="a3_1to8", S_q=24, offset=40, B=2, n_kv=2, gqa=4):
     np.savez_compressed(os.path.join(HERE, "prefill.npz"), **rec)
 
 
+SHAPE_CASES = {
+    # name: (avg_bits, min_bits, max_bits, v_bits, n_kv, gqa, T, theta, seed)
+    # one layer of the single-layer op configuration: 32 query / 8 KV heads, context 4096, avg 3.0 in [1, 6], V 3-bit
+    "cfg0_a3_1to6_h8_t4096": (3.0, 1, 6, 3, 8, 4, 4096, 500000.0, 0),
+    # an 8-head K2V2 layer (avg 2.0 in [1, 8], V 2-bit)
+    "k2v2_h8_t2048": (2.0, 1, 8, 2, 8, 4, 2048, 500000.0, 1),
+}
+
+
+def dump_shape_case(name):
+    """One decode query at position T over a T-token cache of one whole layer (batch 1, every KV head), all of
+    it through the reference: calibration per head on the head's own queries and keys, batched encoders,
+    per-head decode kernel with the reference's split rule."""
+    sys.path.insert(0, os.path.dirname(HERE))
+    from helpers import synth_layer_case
+    avg, mn, mx, vb, n_kv, gqa, T, theta, seed = SHAPE_CASES[name]
+    data = synth_layer_case(seed, n_kv, gqa, T, theta)
+    qs = []
+    for hi in range(n_kv):
+        z = BlockGTQQuantizer(HD, avg_bits=avg, min_bits=mn, max_bits=mx, rope_base=theta, device=CPU)
+        z.calibrate(data["q_all"][hi][:, :T].reshape(-1, HD).float(), data["k"][hi].float())
+        z.init_v_quantizer(v_bits=vb, seed=42 + hi)
+        qs.append(z)
+        print("calibrated", hi, flush=True)
+    ba = build_batched_encode_args(qs, device="cpu")
+    kp, kn = compress_k_packed_batched(data["k"].contiguous(), ba)
+    print("K encoded", flush=True)
+    vp, vn = compress_v_packed_batched(data["v"].contiguous(), ba)
+    print("V encoded", flush=True)
+    kp, kn = kp.unsqueeze(0), kn.to(torch.float16).unsqueeze(0)       # (1, n_kv, T, ...)
+    vp, vn = vp.unsqueeze(0), vn.unsqueeze(0)
+    q = data["q"].unsqueeze(0).unsqueeze(2)                            # (1, n_q, 1, hd)
+    t_splits = 1
+    while t_splits < max(1, min((T + 63) // 64, 32)):
+        t_splits *= 2
+    outs, lses, qrots = [], [], []
+    for hi in range(n_kv):
+        z = qs[hi]
+        ka = z.build_kernel_args()
+        q_h = q[:, hi * gqa:(hi + 1) * gqa]
+        q_rot = z.rotate_q_for_packed_kernel(q_h.reshape(-1, HD)).reshape(q_h.shape)
+        o, lse = fused_blockgtq_decode_attention(
+            q_rot, kp[:, hi:hi + 1], kn[:, hi:hi + 1], ka["codebook_flat"], ka["lut_offset"],
+            ka["norm_group"], ka["segments_b"], vp[:, hi:hi + 1], vn[:, hi:hi + 1], z.v_lut,
+            scale=1.0 / HD ** 0.5, t_splits=t_splits, v_bits=z.v_bits,
+            v_rotation=z._v_rot, return_lse=True)
+        outs.append(o)
+        lses.append(lse)
+        qrots.append(q_rot)
+        print("decoded", hi, flush=True)
+    np.savez_compressed(
+        os.path.join(HERE, f"shape_{name}.npz"),
+        case=np.array(SHAPE_CASES[name], dtype=np.float64),
+        alloc=np.stack([z.bit_allocation.numpy() for z in qs]),
+        input_sha=np.array(sha(torch.cat([data["k"].reshape(-1), data["v"].reshape(-1), data["q"].reshape(-1)]))),
+        q=q.numpy(), q_rot=torch.cat(qrots, dim=1).numpy(),
+        k_packed=kp.numpy(), k_norms=kn.numpy(), v_packed=vp.numpy(), v_norms=vn.numpy(),
+        out=torch.cat(outs, dim=1).numpy(), lse=torch.cat(lses, dim=1).numpy(), t_splits=np.array(t_splits))
+
+
 def main():
     only = sys.argv[2] if len(sys.argv) > 2 else None
+    if only in SHAPE_CASES:
+        dump_shape_case(only)
+        print("done", only)
+        return
     gen = torch.Generator().manual_seed(20240607)
     for case in CASES:
         if only is not None:

@@ -70,3 +70,19 @@ def synth_head(gen, n_k, gqa, theta=500000.0, hd=HD):
     k = rope((torch.randn(n_k, hd, generator=gen) * scale).half().float(), pos, theta).half()
     q = rope((torch.randn(gqa, n_k, hd, generator=gen) * scale).half().float(), pos, theta).half()
     return q.reshape(-1, hd), k
+
+
+def synth_layer_case(seed, n_kv, gqa, T, theta):
+    """Inputs of a layer-shaped golden case, regenerated from the seed alone (the fixture stores only their
+    hash): per KV head post-RoPE keys (T, hd) and queries of its ``gqa`` heads at positions 0..T (the last one
+    is the decode query), values N(0,1).  Returns fp16 tensors ``k`` (n_kv, T, hd), ``v`` (n_kv, T, hd),
+    ``q`` (n_kv*gqa, hd) and ``q_all`` (n_kv, gqa, T+1, hd)."""
+    gen = torch.Generator().manual_seed(seed)
+    ks, qs = [], []
+    for _ in range(n_kv):
+        q, k = synth_head(gen, T + 1, gqa, theta=theta)
+        ks.append(k[:T])
+        qs.append(q.reshape(gqa, T + 1, HD))
+    v = torch.randn(n_kv, T, HD, generator=gen).half()
+    q_all = torch.stack(qs)
+    return {"k": torch.stack(ks), "v": v, "q": q_all[:, :, T].reshape(n_kv * gqa, HD), "q_all": q_all}

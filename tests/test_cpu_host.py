@@ -63,7 +63,7 @@ def test_allocator_edges():
 
 def test_library_exports_every_declared_symbol():
     header = open(os.path.join(ROOT, "include", "bgtq.h")).read()
-    declared = sorted(set(re.findall(r"^(?:int|const char\*)\s+(bgtq_\w+)\s*\(", header, flags=re.M)))
+    declared = sorted(set(re.findall(r"^(?:int|int64_t|const char\*)\s+(bgtq_\w+)\s*\(", header, flags=re.M)))
     assert declared, "no declarations found"
     lib = _lib.lib()
     for name in declared:
@@ -162,11 +162,14 @@ def test_calib_cache_round_trip(tmp_path):
 
 
 def test_default_split_counts_for_the_benchmark_shapes():
-    """Host-side split rule of the decode launch (148 SMs assumed without a GPU): one wave of warp-granular
-    splits when the (batch, head) pairs fit in half the resident CTA slots, 16-tile CTAs otherwise."""
+    """Host-side rule for the number of partial slots per (batch, head) pair (148 SMs assumed without a GPU):
+    items of at most one 512-token tile, about four per SM for small launches, at most 256 slots."""
     L = _lib.lib()
-    assert L.bgtq_decode_default_splits(8, 2, 32768) == 18        # 16 pairs x 18 = 288 of 296 slots
-    assert L.bgtq_decode_default_splits(1, 8, 131072) == 37       # 8 pairs x 37 = 296
-    assert L.bgtq_decode_default_splits(32, 8, 16384) == 4        # 256 pairs: several waves, 16 tiles per CTA
-    assert L.bgtq_decode_default_splits(32, 8, 65536) == 16
-    assert L.bgtq_decode_default_splits(1, 1, 100) == 1 and L.bgtq_decode_default_splits(64, 8, 1024) == 1
+    assert L.bgtq_decode_default_splits(8, 2, 32768) == 64        # 1024 one-tile items over 148 CTAs
+    assert L.bgtq_decode_default_splits(1, 8, 131072) == 256
+    assert L.bgtq_decode_default_splits(32, 8, 16384) == 32
+    assert L.bgtq_decode_default_splits(32, 8, 65536) == 128
+    assert L.bgtq_decode_default_splits(1, 8, 4096) == 64         # 1024 units over 592 item slots: 2 units each
+    assert L.bgtq_decode_default_splits(1, 1, 100) == 4 and L.bgtq_decode_default_splits(64, 8, 1024) == 2
+    assert L.bgtq_decode_default_splits(1, 1, 0) == 1 and L.bgtq_decode_default_splits(4, 2, 32) == 1
+    assert L.bgtq_decode_default_splits(1, 1, 1 << 20) == 256     # capped: 128-unit items
