@@ -21,7 +21,7 @@ N_BINS = 256
 OK = 0
 ENC_K_NORMS_F16, ENC_K_MIXED, ENC_V_NIBBLE, ENC_SKIP_K, ENC_SKIP_V, ENC_FORCE_SIMT, ENC_PROGRAMMATIC = 1, 2, 4, 8, 16, 32, 64
 ENC_NO_TCGEN05 = 128
-DEC_K_MIXED, DEC_V_NIBBLE, DEC_PROGRAMMATIC = 1, 2, 4
+DEC_K_MIXED, DEC_V_NIBBLE, DEC_PROGRAMMATIC, DEC_GENERIC = 1, 2, 4, 8
 COMBINE_PROGRAMMATIC = 1
 
 
@@ -78,6 +78,8 @@ _SIGNATURES = {
     "bgtq_decode_image_bytes": (C.c_int64, [_vp]),
     "bgtq_decode_build_image": (C.c_int, [_vp, _vp, _vp, _i64]),
     "bgtq_decode_plan_set_image": (C.c_int, [_vp, _vp]),
+    "bgtq_decode_plan_specialize": (C.c_int, [_vp, _i32, C.c_char_p, _i64]),
+    "bgtq_jit_set_nvrtc_path": (C.c_int, [C.c_char_p]),
     "bgtq_decode": (C.c_int, [_vp, _vp, _vp,
                               _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
                               _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,

@@ -39,18 +39,38 @@ def needs_build() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+JIT_SOURCES = ["bgtq_common.cuh", "bgtq_plan.h", "bgtq_decode_kernel.cuh"]
+
+
+def _embed_jit_sources(objdir: str) -> str:
+    """The decode kernel is also compiled at run time from its own text: write each source file it consists of
+    as a C++ raw string literal (``<name>.str``) for csrc/bgtq_decode_jit.cu to include."""
+    out = os.path.join(objdir, "jit_src")
+    os.makedirs(out, exist_ok=True)
+    for name in JIT_SOURCES:
+        text = open(os.path.join(CSRC, name)).read()
+        lines = [ln for ln in text.splitlines()
+                 if not ln.startswith("#pragma once") and not ln.startswith('#include "')]
+        body = "\n".join(lines)
+        assert ')BGTQSRC"' not in body
+        with open(os.path.join(out, name + ".str"), "w") as f:
+            f.write('R"BGTQSRC(' + body + '\n)BGTQSRC"\n')
+    return out
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
     nvcc = _nvcc()
     objdir = os.path.join(PKG, "build")
     os.makedirs(objdir, exist_ok=True)
+    jit_inc = _embed_jit_sources(objdir)
     procs = []
     for src in sources():
         obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
         cmd = [nvcc] + [f for f in NVCC_FLAGS if f != "--use_fast_math=false"] + \
             (["-Xptxas", "-v"] if verbose else []) + os.environ.get("BGTQ_NVCC_EXTRA", "").split() + \
-            ["-c", src, "-o", obj]
+            ["-I", jit_inc, "-c", src, "-o", obj]
         procs.append((obj, cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)))
     objs = []
     for obj, cmd, p in procs:
@@ -61,7 +81,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out)
         objs.append(obj)
     tmp = LIB + ".tmp"
-    cmd = [nvcc, "-shared", "-o", tmp] + objs + ["-cudart", "shared"]
+    cmd = [nvcc, "-shared", "-o", tmp] + objs + ["-cudart", "shared", "-ldl"]
     r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
     if r.returncode != 0:
         raise RuntimeError("link failed: " + r.stdout.decode())

@@ -1,13 +1,19 @@
 // Device-side helpers shared by the sm_100a kernels: PTX wrappers for bulk
 // (TMA) copies with mbarrier completion, bounded mbarrier waits, warp-level
 // tensor-core MMA and small bit utilities.
+//
+// The decode kernel is also compiled at run time (NVRTC) from this very text, with BGTQ_JIT defined and
+// no headers available: everything it needs is written with built-ins and inline PTX, and the parts that
+// need CUDA's headers are fenced off.
 #pragma once
 
+#ifndef BGTQ_JIT
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "../../include/bgtq.h"
+#endif
 
 namespace bgtq {
 
@@ -131,13 +137,22 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     return d;
 }
 
+// fp16 arithmetic on raw bit patterns (round to nearest even, no flush): what __floats2half2_rn, __hmul2
+// and __half2float compile to.
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
 }
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
-    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
-    return *reinterpret_cast<uint32_t*>(&r);
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ float f16_bits_to_float(uint32_t h) {
+    float f;
+    asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"((unsigned short)h));
+    return f;
 }
 
 // Programmatic dependent launch (a kernel launched with the stream-serialization attribute may start
@@ -148,6 +163,7 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+#ifndef BGTQ_JIT
 // Launch with or without the programmatic stream-serialization attribute.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -165,6 +181,7 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
     return e == cudaSuccess ? cudaGetLastError() : e;
 }
+#endif
 
 __host__ __device__ __forceinline__ int seg_storage_bytes(int bw, int n) {
     return bw == 1 ? (n + 7) / 8 : bw == 2 ? (n + 3) / 4 : bw == 3 ? ((n + 7) / 8) * 3 : bw == 4 ? (n + 1) / 2 : n;

@@ -27,7 +27,7 @@ static int decode_impl(
     if ((reinterpret_cast<uintptr_t>(part_o) & 7u) || (reinterpret_cast<uintptr_t>(q_rot) & 3u)) return BGTQ_E_ALIGN;
     if (n_batch > 65535 || n_splits > 65535) return BGTQ_E_TOOBIG;
 
-    P.q_rot = static_cast<const __half*>(q_rot);
+    P.q_rot = static_cast<const uint16_t*>(q_rot);
     P.kp = k_packed;
     P.kn = static_cast<const uint8_t*>(k_norms);
     P.vp = v_packed;
@@ -72,7 +72,10 @@ static int decode_impl(
     const cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool pdl = (P.plan.flags & BGTQ_DEC_PROGRAMMATIC) != 0;
     cudaError_t e;
-    switch (P.plan.v_sbits) {
+    // the kernel specialised for this layer's heads, when the plan carries one (it exists for the wide tile only)
+    const bool jit = P.plan.jit_kernel != nullptr && nu == 2 && !(P.plan.flags & BGTQ_DEC_GENERIC);
+    if (jit) e = launch_decode_jit(P, grid, smem, st, pdl);
+    else switch (P.plan.v_sbits) {
         case 1: e = launch_decode_vb1(P, nu, grid, smem, st, pdl); break;
         case 2: e = launch_decode_vb2(P, nu, grid, smem, st, pdl); break;
         case 3: e = launch_decode_vb3(P, nu, grid, smem, st, pdl); break;

@@ -35,9 +35,19 @@
 //     (blockgtq/kernels/fused_packed_attention.py:770-873): fp32 logits,
 //     p rounded to fp16 for the PV product while the denominator uses fp32 p,
 //     vhat = fp16(fp16 centroid * fp16 norm), fp32 accumulation.
+//
+// This text is compiled twice.  Ahead of time (nvcc) it yields the general kernel, whose K loop reads the
+// head's segment list from the plan at run time.  At run time (NVRTC, bgtq_decode_jit.cu, with BGTQ_JIT
+// defined and the same text passed as a string after a generated prelude) it yields a kernel specialised
+// for the heads of ONE layer: the prelude spells every head's segment list as compile-time constants, so
+// the K loop unrolls into straight-line code with immediate offsets, rotates and masks -- the reference
+// specialises its Triton kernel per head with constexprs in the same way
+// (blockgtq/production_cache.py:19-22).  Everything but the K side is shared.
 #pragma once
+#ifndef BGTQ_JIT
 #include "bgtq_common.cuh"
 #include "bgtq_plan.h"
+#endif
 
 namespace bgtq {
 
@@ -50,9 +60,10 @@ constexpr int kMergeStride = 132;  // floats per query row in the end-of-run mer
 constexpr uint32_t kOffQf = 1024, kOffMM = kOffQf + kMaxSteps * 32 * 8, kOffLut = kLutAlign;
 static_assert(kOffMM + 2 * kDecWarps * 8 * 4 <= kOffLut, "layout");
 constexpr uint32_t kMergeBytes = kDecWarps * 8 * kMergeStride * 4;
+#define BGTQ_INF __int_as_float(0x7f800000)
 
 struct DecParams {
-    const __half* q_rot;
+    const uint16_t* q_rot;  // fp16 bit patterns
     const uint8_t* kp;
     const uint8_t* kn;  // byte pointers; strides below are in bytes
     const uint8_t* vp;
@@ -113,6 +124,7 @@ __device__ __forceinline__ void load_v16(const uint8_t* sm, uint32_t row_al, uin
     }
 }
 
+#ifndef BGTQ_JIT
 // ---------------------------------------------------------------------------------------------
 // One K segment of a warp's token tile: acc[u] += Khat_seg(16 tokens x codes) . Qrot_seg^T.
 // KIND = stored bits per code.  Lane (r, j): token rows r + 8 i (i < 2 NU), the run of `q` codes at bit
@@ -195,9 +207,183 @@ __device__ __forceinline__ int k_segment(float (&acc)[NU][4], const uint8_t* sm,
     }
     return step;
 }
+#endif
 
+// Lane-constant inputs of the K side of a warp's token tile.
+struct KLane {
+    uint32_t rowK, rowN;       // byte offsets (from the start of shared memory) of the lane's first packed row / norm row
+    uint32_t k_row8, kn_row8;  // byte distance between rows r and r + 8
+    uint32_t k_p0;             // bit phase of the packed rows inside their first aligned word
+    uint32_t j, lane;
+};
+
+#ifndef BGTQ_JIT
+// S^T = Khat . Qrot^T of a warp's NU 16-token row tiles, segment list read from the plan.
+template <int NU>
+__device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const DecHeadPlan& hp,
+                                       const uint2* qf) {
+    const int n_seg = hp.n_seg;
+    for (int sg = 0; sg < n_seg; ++sg) {
+        const DecSeg sd = hp.seg[sg];
+        // Norm handling: the bit-packed layout scales the fp32 dot product of a segment by its fp16 norm; the
+        // nibble layout rounds centroid * norm to fp16 per element before the product
+        // (fused_packed_attention.py:1449-1452), so there the norm is folded into the operand.
+        const bool f16n = sd.f16_norm != 0;
+        float nrm[2 * NU];
+        uint32_t n2[2 * NU];
+#pragma unroll
+        for (int i = 0; i < 2 * NU; ++i) {
+            const uint32_t nh = ld16(sm, kl.rowN + 2u * sd.norm_idx + i * kl.kn_row8);
+            n2[i] = nh | (nh << 16);
+            nrm[i] = f16n ? 1.0f : f16_bits_to_float(nh);
+        }
+        float acc[NU][4];
+#pragma unroll
+        for (int u = 0; u < NU; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+        const uint32_t lbit = kl.k_p0 + sd.bit0 + kl.j * sd.lane_bits;
+        const uint32_t tb = kOffLut + sd.tbl + ((kl.lane & ((1u << sd.rep_log2) - 1u)) << sd.ent_log2);
+        const int q = sd.q;
+        int used;
+        switch (sd.kind) {
+            case 1: used = k_segment<1, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
+            case 2: used = k_segment<2, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
+            case 3: used = k_segment<3, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
+            case 4: used = k_segment<4, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
+            default:
+                used = k_segment<8, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, (uint32_t)sd.esh,
+                                        ((1u << sd.bw) - 1u) << sd.esh, qf, f16n, n2);
+                break;
+        }
+        qf += used * 32;
+#pragma unroll
+        for (int u = 0; u < NU; ++u) {
+            S[u][0] = fmaf(nrm[2 * u], acc[u][0], S[u][0]);
+            S[u][1] = fmaf(nrm[2 * u], acc[u][1], S[u][1]);
+            S[u][2] = fmaf(nrm[2 * u + 1], acc[u][2], S[u][2]);
+            S[u][3] = fmaf(nrm[2 * u + 1], acc[u][3], S[u][3]);
+        }
+    }
+}
+#else
+// ---------------------------------------------------------------------------------------------
+// Specialised K side: the generated prelude declares, per KV head H of the layer,
+//     template <> struct jit::Head<H> { static constexpr int n_seg; static constexpr jit::SegC seg[8]; };
+// and every loop below has a compile-time trip count.
+// ---------------------------------------------------------------------------------------------
+template <class HeadT, int SG, int NU>
+__device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const uint2* qf) {
+    constexpr jit::SegC c = HeadT::seg[SG];
+    constexpr int SB = c.kind, Q = c.q;
+    constexpr int CAP = c.kind == 3 ? 8 : 32 / SB, TILES = CAP / 4;
+    constexpr bool f16n = c.f16_norm != 0;
+    float nrm[2 * NU];
+    uint32_t n2[2 * NU];
+#pragma unroll
+    for (int i = 0; i < 2 * NU; ++i) {
+        const uint32_t nh = ld16(sm, kl.rowN + 2u * c.norm_idx + i * kl.kn_row8);
+        n2[i] = nh | (nh << 16);
+        nrm[i] = f16n ? 1.0f : f16_bits_to_float(nh);
+    }
+    float acc[NU][4];
+#pragma unroll
+    for (int u = 0; u < NU; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+    const uint32_t lbit = kl.k_p0 + (uint32_t)c.bit0 + kl.j * (uint32_t)c.lane_bits;
+    const uint32_t tb = kOffLut + (uint32_t)c.tbl + ((kl.lane & ((1u << c.rep_log2) - 1u)) << c.ent_log2);
+#pragma unroll
+    for (int cc = 0; cc < Q; cc += CAP) {
+        const uint32_t pbit = lbit + (uint32_t)(cc * SB);
+        const uint32_t wa = kl.rowK + ((pbit >> 5) << 2);
+        uint32_t cur[2 * NU];
+#pragma unroll
+        for (int i = 0; i < 2 * NU; ++i)
+            cur[i] = __funnelshift_r(ld32(sm, wa + i * kl.k_row8), ld32(sm, wa + i * kl.k_row8 + 4), pbit);
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) {
+            if (cc + 4 * t < Q) {
+                const bool full = Q - cc - 4 * t >= 4;         // else codes 2, 3 meet a zero query fragment
+                const uint2 bq = qf[(c.step0 + (cc + 4 * t) / 4) * 32];
+                uint32_t lo[2 * NU], hi[2 * NU];
+                if constexpr (c.kind == 1 || c.kind == 2) {    // quad tables: one 64-bit lookup per row
+                    const uint32_t ESH = c.kind == 1 ? kEsh1 : kEsh2, FW = 4 * SB;
+                    const uint32_t MASK = ((1u << FW) - 1u) << ESH, R = (32u + ESH - FW * t) & 31u;
+#pragma unroll
+                    for (int i = 0; i < 2 * NU; ++i) {
+                        const uint2 v = ld64(sm, (rotl32(cur[i], R) & MASK) | tb);
+                        lo[i] = v.x;
+                        hi[i] = v.y;
+                    }
+                } else if constexpr (c.kind == 3 || c.kind == 4) {   // pair tables
+                    const uint32_t ESH = c.kind == 3 ? kEsh3 : kEsh4, FW = 2 * SB;
+                    const uint32_t MASK = ((1u << FW) - 1u) << ESH;
+                    const uint32_t R0 = (64u + ESH - 2 * FW * t) & 31u, R1 = (64u + ESH - 2 * FW * t - FW) & 31u;
+#pragma unroll
+                    for (int i = 0; i < 2 * NU; ++i) {
+                        lo[i] = ld32(sm, (rotl32(cur[i], R0) & MASK) | tb);
+                        hi[i] = full ? ld32(sm, (rotl32(cur[i], R1) & MASK) | tb) : 0u;
+                    }
+                } else {                                       // raw bytes, one code per lookup
+                    const uint32_t ESH = c.esh, MASK = ((1u << c.bw) - 1u) << ESH;
+#pragma unroll
+                    for (int i = 0; i < 2 * NU; ++i) {
+                        const uint32_t c0 = ld32(sm, (rotl32(cur[i], ESH) & MASK) | tb);
+                        const uint32_t c1 = ld32(sm, (rotl32(cur[i], ESH + 24u) & MASK) | tb);
+                        lo[i] = __byte_perm(c0, c1, 0x5410);
+                        if (full) {
+                            const uint32_t c2 = ld32(sm, (rotl32(cur[i], ESH + 16u) & MASK) | tb);
+                            const uint32_t c3 = ld32(sm, (rotl32(cur[i], ESH + 8u) & MASK) | tb);
+                            hi[i] = __byte_perm(c2, c3, 0x5410);
+                        } else {
+                            hi[i] = 0u;
+                        }
+                    }
+                }
+                if (f16n) {
+#pragma unroll
+                    for (int i = 0; i < 2 * NU; ++i) {
+                        lo[i] = hmul2_u32(lo[i], n2[i]);
+                        hi[i] = hmul2_u32(hi[i], n2[i]);
+                    }
+                }
+                const uint32_t b[2] = {bq.x, bq.y};
+#pragma unroll
+                for (int u = 0; u < NU; ++u) {
+                    const uint32_t a[4] = {lo[2 * u], lo[2 * u + 1], hi[2 * u], hi[2 * u + 1]};
+                    mma_16816(acc[u], a, b);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < NU; ++u) {
+        S[u][0] = fmaf(nrm[2 * u], acc[u][0], S[u][0]);
+        S[u][1] = fmaf(nrm[2 * u], acc[u][1], S[u][1]);
+        S[u][2] = fmaf(nrm[2 * u + 1], acc[u][2], S[u][2]);
+        S[u][3] = fmaf(nrm[2 * u + 1], acc[u][3], S[u][3]);
+    }
+}
+template <class HeadT, int SG, int NU>
+__device__ __forceinline__ void k_side_from(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const uint2* qf) {
+    if constexpr (SG < HeadT::n_seg) {
+        k_segment_c<HeadT, SG, NU>(S, sm, kl, qf);
+        k_side_from<HeadT, SG + 1, NU>(S, sm, kl, qf);
+    }
+}
+template <int NU>
+__device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const int h,
+                                       const uint2* qf) {
+#define BGTQ_JIT_CASE(H) case H: k_side_from<jit::Head<H>, 0, NU>(S, sm, kl, qf); break;
+    switch (h) { BGTQ_JIT_CASES }       // one case per head of the layer, spelled by the prelude
+#undef BGTQ_JIT_CASE
+}
+#endif
+
+#ifndef BGTQ_JIT
 template <int VB, int NU>
 __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_constant__ DecParams P) {
+#else
+constexpr int VB = BGTQ_JIT_VB, NU = BGTQ_JIT_NU;
+extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(const __grid_constant__ DecParams P) {
+#endif
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int kWarpTok = 16 * NU;              // tokens per warp and tile
     constexpr int kTileTok = kDecWarps * kWarpTok; // tokens per CTA tile
@@ -262,7 +448,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_con
     if (n_items == 0) {     // no tokens at all: every slot of every row is an empty split
         for (int64_t i = (int64_t)cta * kDecThreads + tid; i < (int64_t)P.n_batch * P.n_q * P.n_splits;
              i += (int64_t)n_cta * kDecThreads)
-            P.part_lse[i] = -INFINITY;
+            P.part_lse[i] = -BGTQ_INF;
         if (tables_pending) wait_tables();
         return;
     }
@@ -325,7 +511,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_con
             const int g = lane >> 2, jj = lane & 3;
             const int pos = (int)st.pos + jj * (int)st.q;
             const bool q_ok = g < P.gqa;
-            const __half* qrow = P.q_rot + ((size_t)b * P.n_q + (size_t)h * P.gqa + (q_ok ? g : 0)) * kHD;
+            const uint16_t* qrow = P.q_rot + ((size_t)b * P.n_q + (size_t)h * P.gqa + (q_ok ? g : 0)) * kHD;
             uint2 v;
             v.x = (q_ok && pos < (int)st.end) ? __ldg(reinterpret_cast<const uint32_t*>(qrow + pos)) : 0u;
             v.y = (q_ok && (int)st.c4 + 2 < (int)st.q && pos + 2 < (int)st.end)
@@ -342,7 +528,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_con
         float O[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
-        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+        float m0 = -BGTQ_INF, m1 = -BGTQ_INF, l0 = 0.f, l1 = 0.f;
 
         // Byte phases of the four arrays inside a stage (tiles advance every array by a multiple of 16
         // bytes), and this lane's row offsets.  K side: tokens tok0 + 8 i; V side, row tile u: tokens
@@ -359,7 +545,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_con
         const uint32_t vn_row = P.off_vn + vn_pre + tkv * P.vn_st;
         const uint32_t k_row8 = 8u * P.kp_st, kn_row8 = 8u * P.kn_st;
         const uint32_t vtbl = lut_rel + hp.v_tbl + (lane4 & ((1u << kVSh) - 1u));
-        const int n_seg = hp.n_seg;
 
         for (int it = 0; it < n_tiles; ++it, ++g_it) {
             const int st = g_it % kDecStages;
@@ -372,59 +557,29 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_con
                 float S[NU][4];
 #pragma unroll
                 for (int u = 0; u < NU; ++u) S[u][0] = S[u][1] = S[u][2] = S[u][3] = 0.f;
-                const uint32_t rowK = sb + k_row_al, rowN = sb + kn_row;
-                const uint2* qf = qfrag + lane;
-                for (int sg = 0; sg < n_seg; ++sg) {
-                    const DecSeg sd = hp.seg[sg];
-                    // Norm handling: the bit-packed layout scales the fp32 dot product of a segment by its
-                    // fp16 norm; the nibble layout rounds centroid * norm to fp16 per element before the
-                    // product (fused_packed_attention.py:1449-1452), so there the norm is folded into the
-                    // operand.
-                    const bool f16n = sd.f16_norm != 0;
-                    float nrm[2 * NU];
-                    uint32_t n2[2 * NU];
-#pragma unroll
-                    for (int i = 0; i < 2 * NU; ++i) {
-                        const uint32_t nh = ld16(sm, rowN + 2u * sd.norm_idx + i * kn_row8);
-                        n2[i] = nh | (nh << 16);
-                        nrm[i] = f16n ? 1.0f : __half2float(__ushort_as_half((unsigned short)nh));
-                    }
-                    float acc[NU][4];
-#pragma unroll
-                    for (int u = 0; u < NU; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
-                    const uint32_t lbit = k_p0 + sd.bit0 + (uint32_t)j * sd.lane_bits;
-                    const uint32_t tb = lut_rel + sd.tbl + (((uint32_t)lane & ((1u << sd.rep_log2) - 1u)) << sd.ent_log2);
-                    const int q = sd.q;
-                    int used;
-                    switch (sd.kind) {
-                        case 1: used = k_segment<1, NU>(acc, sm, rowK, k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
-                        case 2: used = k_segment<2, NU>(acc, sm, rowK, k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
-                        case 3: used = k_segment<3, NU>(acc, sm, rowK, k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
-                        case 4: used = k_segment<4, NU>(acc, sm, rowK, k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
-                        default:
-                            used = k_segment<8, NU>(acc, sm, rowK, k_row8, lbit, q, tb, (uint32_t)sd.esh,
-                                                    ((1u << sd.bw) - 1u) << sd.esh, qf, f16n, n2);
-                            break;
-                    }
-                    qf += used * 32;
-#pragma unroll
-                    for (int u = 0; u < NU; ++u) {
-                        S[u][0] = fmaf(nrm[2 * u], acc[u][0], S[u][0]);
-                        S[u][1] = fmaf(nrm[2 * u], acc[u][1], S[u][1]);
-                        S[u][2] = fmaf(nrm[2 * u + 1], acc[u][2], S[u][2]);
-                        S[u][3] = fmaf(nrm[2 * u + 1], acc[u][3], S[u][3]);
-                    }
-                }
+                KLane kl;
+                kl.rowK = sb + k_row_al;
+                kl.rowN = sb + kn_row;
+                kl.k_row8 = k_row8;
+                kl.kn_row8 = kn_row8;
+                kl.k_p0 = k_p0;
+                kl.j = (uint32_t)j;
+                kl.lane = (uint32_t)lane;
+#ifndef BGTQ_JIT
+                k_side<NU>(S, sm, kl, hp, qfrag + lane);
+#else
+                k_side<NU>(S, sm, kl, h, qfrag + lane);
+#endif
                 // ---------------- online softmax (log2 domain) over the warp's tokens ----------------
                 float sv[NU][4];
-                float x0 = -INFINITY, x1 = -INFINITY;
+                float x0 = -BGTQ_INF, x1 = -BGTQ_INF;
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
                     const bool okA = tok0 + 16 * u < nt, okB = tok0 + 16 * u + 8 < nt;
-                    sv[u][0] = okA ? S[u][0] * P.scale_log2 : -INFINITY;
-                    sv[u][1] = okA ? S[u][1] * P.scale_log2 : -INFINITY;
-                    sv[u][2] = okB ? S[u][2] * P.scale_log2 : -INFINITY;
-                    sv[u][3] = okB ? S[u][3] * P.scale_log2 : -INFINITY;
+                    sv[u][0] = okA ? S[u][0] * P.scale_log2 : -BGTQ_INF;
+                    sv[u][1] = okA ? S[u][1] * P.scale_log2 : -BGTQ_INF;
+                    sv[u][2] = okB ? S[u][2] * P.scale_log2 : -BGTQ_INF;
+                    sv[u][3] = okB ? S[u][3] * P.scale_log2 : -BGTQ_INF;
                     x0 = fmaxf(x0, fmaxf(sv[u][0], sv[u][2]));
                     x1 = fmaxf(x1, fmaxf(sv[u][1], sv[u][3]));
                 }
@@ -434,7 +589,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_con
                     x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, o));
                 }
                 const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
-                const float z0 = n0 == -INFINITY ? 0.f : n0, z1 = n1 == -INFINITY ? 0.f : n1;
+                const float z0 = n0 == -BGTQ_INF ? 0.f : n0, z1 = n1 == -BGTQ_INF ? 0.f : n1;
                 const float al0 = exp2f(m0 - z0), al1 = exp2f(m1 - z1);
                 m0 = n0;
                 m1 = n1;
@@ -540,13 +695,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_con
         {
             const int qi = tid >> 6, d0 = (tid & 63) * 2;            // 64 threads per query head, two dims each
             if (qi < P.gqa) {
-                float mx = -INFINITY;
+                float mx = -BGTQ_INF;
 #pragma unroll
                 for (int w = 0; w < kDecWarps; ++w) mx = fmaxf(mx, mm[w * 8 + qi]);
                 float wgt[kDecWarps], den = 0.f;
 #pragma unroll
                 for (int w = 0; w < kDecWarps; ++w) {
-                    wgt[w] = mx == -INFINITY ? 0.f : exp2f(mm[w * 8 + qi] - mx);
+                    wgt[w] = mx == -BGTQ_INF ? 0.f : exp2f(mm[w * 8 + qi] - mx);
                     den = fmaf(ml[w * 8 + qi], wgt[w], den);
                 }
                 const float inv = den > 0.f ? 1.f / den : 0.f;
@@ -561,10 +716,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_con
                 const size_t row = ((size_t)b * P.n_q + (size_t)h * P.gqa + qi) * P.n_splits;
                 *reinterpret_cast<float2*>(P.part_o + (row + s0) * kHD + d0) = make_float2(o[0], o[1]);
                 if ((tid & 63) == 0)
-                    P.part_lse[row + s0] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -INFINITY;
+                    P.part_lse[row + s0] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -BGTQ_INF;
                 // slots merged into this partial, and (after the pair's last live item) the slots past them
                 const int s_end = s0 + cnt == n_live ? P.n_splits : s0 + cnt;
-                for (int s = s0 + 1 + (tid & 63); s < s_end; s += 64) P.part_lse[row + s] = -INFINITY;
+                for (int s = s0 + 1 + (tid & 63); s < s_end; s += 64) P.part_lse[row + s] = -BGTQ_INF;
             }
         }
         __syncthreads();      // the merge buffer is free again before the next run's tiles land in it
@@ -573,6 +728,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_con
     if (!ok && P.status && lane == 0) atomicExch(P.status, kStatusWaitTimeout);
 }
 
+#ifndef BGTQ_JIT
 // Launch one instantiation; defined once per stored V width in its own translation unit.
 template <int VB>
 cudaError_t launch_decode(const DecParams& P, int nu, dim3 grid, size_t smem, cudaStream_t stream, bool programmatic) {
@@ -588,5 +744,7 @@ cudaError_t launch_decode_vb1(const DecParams&, int, dim3, size_t, cudaStream_t,
 cudaError_t launch_decode_vb2(const DecParams&, int, dim3, size_t, cudaStream_t, bool);
 cudaError_t launch_decode_vb3(const DecParams&, int, dim3, size_t, cudaStream_t, bool);
 cudaError_t launch_decode_vb4(const DecParams&, int, dim3, size_t, cudaStream_t, bool);
+cudaError_t launch_decode_jit(const DecParams&, dim3, size_t, cudaStream_t, bool);
+#endif
 
 }  // namespace bgtq

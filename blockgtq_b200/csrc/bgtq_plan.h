@@ -25,7 +25,9 @@
 //   8 bits (5..8)  1 code  -> fp16 (twice)    bw bits      32..8     4096/8192
 //   V (pair of tokens, one dim) -> fp16x2     2*vb bits    32..8     <= 8192
 #pragma once
+#ifndef BGTQ_JIT
 #include <stdint.h>
+#endif
 
 namespace bgtq {
 
@@ -54,6 +56,7 @@ struct DecSeg {
     uint8_t ent_log2;    // log2(entry bytes): 2 or 3
     uint8_t norm_idx;    // which of the token's norms scales this segment
 };
+static_assert(sizeof(DecSeg) == 16, "DecSeg layout is mirrored by language bindings");
 
 // Query fragment of one k-tile: lane (g, j) holds q[g][pos + j*q .. +1] and q[g][pos + j*q + 2 .. +3].
 struct DecStepQ {
@@ -80,6 +83,7 @@ struct DecPlanDev {
     uint32_t v_rep_log2;
     uint32_t lut_bytes;   // bytes reserved per head in the image and in shared memory (max over heads, multiple of 128)
     const uint8_t* image; // device memory: n_heads images, lut_bytes apart (set with bgtq_decode_plan_set_image)
+    const void* jit_kernel;  // host-side handle of the kernel specialised for these heads (bgtq_decode_plan_specialize), or null
     DecHeadPlan head[kMaxPlanHeads];
 };
 

@@ -70,7 +70,28 @@ def make_decode_plan(desc_host, n_kv: int, flags: int, device):
                "bgtq_decode_build_image")
     image = torch.from_numpy(host).to(device)
     _lib.check(L.bgtq_decode_plan_set_image(C.byref(p), image.data_ptr()), "bgtq_decode_plan_set_image")
+    if not (flags & _lib.DEC_GENERIC) and not os.environ.get("BGTQ_DEC_NO_JIT") and torch.device(device).type == "cuda":
+        _specialize(p)
     return p, image
+
+
+_jit_warned = False
+
+
+def _specialize(plan):
+    """Compile (NVRTC) and attach the decode kernel specialised for the plan's heads.  Without NVRTC the
+    plan keeps using the general kernel; a compile or load failure is an error."""
+    global _jit_warned
+    log = C.create_string_buffer(1 << 16)
+    rc = _lib.lib().bgtq_decode_plan_specialize(C.byref(plan), 0, log, len(log))
+    if rc == -2:
+        if not _jit_warned:
+            import warnings
+            warnings.warn("NVRTC not found: the packed decode runs its general kernel (" + log.value.decode() + ")")
+            _jit_warned = True
+        return
+    if rc != 0:
+        raise RuntimeError("specialising the decode kernel failed:\n" + log.value.decode(errors="replace"))
 
 
 class LayerTables:

@@ -210,6 +210,7 @@ int bgtq_step_prepare_ring(const BgtqHeadDesc* desc, const float* rot_k, const f
 #define BGTQ_DEC_K_MIXED 1        /* k_packed rows are in the nibble/raw mixed layout */
 #define BGTQ_DEC_V_NIBBLE 2       /* v_packed rows are 4-bit nibbles */
 #define BGTQ_DEC_PROGRAMMATIC 4   /* launch bgtq_decode as a programmatic dependent of the preceding kernel */
+#define BGTQ_DEC_GENERIC 8        /* always launch the general kernel, even if the plan holds a specialised one */
 
 /* Opaque launch plan of the decode kernel for the KV heads of one layer (host
  * memory, plain bytes, copyable).  Built once per layer from the HOST copy of
@@ -231,6 +232,19 @@ int64_t bgtq_decode_image_bytes(const BgtqDecodePlan* plan_host);            /* 
 int bgtq_decode_build_image(const BgtqDecodePlan* plan_host, const BgtqHeadDesc* desc_host,
                             uint8_t* image_host, int64_t bytes);             /* host buffers only */
 int bgtq_decode_plan_set_image(BgtqDecodePlan* plan_host, const uint8_t* image_dev);
+
+/* Specialise the decode kernel for the heads of this plan: the kernel's source is compiled at run time
+ * (NVRTC, found with dlopen; bgtq_jit_set_nvrtc_path or the environment variable BGTQ_NVRTC name it
+ * explicitly) with every head's segment layout as compile-time constants, the way the reference
+ * specialises its Triton kernel per head (blockgtq/production_cache.py:19-22), and the resulting kernel is
+ * recorded in the plan; bgtq_decode then launches it instead of the general kernel (same arguments, same
+ * results).  Takes a second or two per distinct layer layout; layouts are cached per process.  Call it
+ * once at set-up, outside any stream capture.  compile_only != 0 stops after the compilation (no GPU
+ * needed; nothing is recorded).  log (host, may be NULL) receives the compiler's messages.
+ * Returns BGTQ_E_UNSUPPORTED when NVRTC cannot be found (the plan stays usable with the general kernel),
+ * BGTQ_E_LAUNCH when compiling or loading fails. */
+int bgtq_decode_plan_specialize(BgtqDecodePlan* plan_host, int32_t compile_only, char* log, int64_t log_bytes);
+int bgtq_jit_set_nvrtc_path(const char* path_host);
 
 /* Number of partial slots per (batch, KV head) pair the library suggests for a
  * (batch, heads, tokens) shape on the current device (host helper, no GPU work):

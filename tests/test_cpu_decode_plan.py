@@ -34,7 +34,8 @@ class HeadPlan(C.Structure):
 
 class Plan(C.Structure):
     _fields_ = [("n_heads", C.c_int32), ("flags", C.c_int32), ("v_bits", C.c_int32), ("v_sbits", C.c_int32),
-                ("v_rep_log2", C.c_uint32), ("lut_bytes", C.c_uint32), ("image", C.c_void_p), ("head", HeadPlan * 8)]
+                ("v_rep_log2", C.c_uint32), ("lut_bytes", C.c_uint32), ("image", C.c_void_p), ("jit_kernel", C.c_void_p),
+                ("head", HeadPlan * 8)]
 
 
 def _plan_and_image(descs, n_kv, flags):
@@ -221,3 +222,23 @@ def test_plan_for_the_mixed_layout_and_limits():
     assert L.bgtq_decode_image_bytes(None) == -1
     assert L.bgtq_decode_plan_set_image(C.byref(raw), 8) == -3          # image must be 16-byte aligned
     assert L.bgtq_decode_plan_set_image(None, 0) == -1
+
+
+@pytest.mark.parametrize("case,flags", [("a3_1to8", 0), ("a2_1to8", 0), ("a4_rt1", 0), ("u3", 0), ("a3_1to8", 3)])
+def test_specialised_kernel_source_compiles_for_sm100a(case, flags):
+    """The run-time (NVRTC) specialisation of the decode kernel for a layer's heads compiles without a GPU;
+    loading it needs one and is covered by the GPU tests."""
+    descs = (_lib.HeadDesc * 2)()
+    for h in range(2):
+        _fill_desc(descs[h], *tables_for(case, h))
+    L = _lib.lib()
+    raw = _lib.DecodePlan()
+    assert L.bgtq_decode_plan(C.byref(descs), 2, flags, C.byref(raw)) == 0
+    log = C.create_string_buffer(1 << 16)
+    rc = L.bgtq_decode_plan_specialize(C.byref(raw), 1, log, len(log))
+    if rc == -2:
+        pytest.skip("NVRTC is not installed here: " + log.value.decode())
+    assert rc == 0, log.value.decode(errors="replace")
+    assert " error" not in log.value.decode(errors="replace")
+    plan = Plan.from_buffer_copy(bytes(raw.opaque)[:C.sizeof(Plan)])
+    assert L.bgtq_decode_plan_specialize(None, 1, None, 0) == -1

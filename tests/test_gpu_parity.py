@@ -661,6 +661,35 @@ def test_decode_result_does_not_depend_on_the_slot_count(gqa, T):
         assert (l - outs[0][1]).abs().max().item() <= 1e-4
 
 
+@pytest.mark.parametrize("case", ["a3_1to6", "a3_1to8", "a2_1to8", "a4_rt1"])
+@pytest.mark.parametrize("mixed", [False, True])
+def test_specialised_and_general_decode_kernels_agree_bit_for_bit(case, mixed):
+    """The kernel compiled at run time for the layer's heads (default) and the general ahead-of-time kernel
+    (BGTQ_DEC_GENERIC) run the same arithmetic in the same order: identical partials."""
+    from blockgtq_b200 import _lib
+    from blockgtq_b200.layer import decode, encode, rotate_q
+    lt, tabs = _layer(case)
+    gen = torch.Generator().manual_seed(99)
+    B, n_kv, gqa, T = 2, 2, 4, 1500
+    n_q = n_kv * gqa
+    k = torch.stack([torch.stack([synth_head(gen, T, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half().to(DEV)
+    kb = lt.max_mixed_bytes if mixed else lt.max_tpb
+    kp = torch.zeros(B, n_kv, T + 8, kb, dtype=torch.uint8, device=DEV)
+    kn = torch.zeros(B, n_kv, T + 8, lt.max_ng, dtype=torch.float16, device=DEV)
+    vp = torch.zeros(B, n_kv, T + 8, HD // 2 if mixed else lt.vpb, dtype=torch.uint8, device=DEV)
+    vn = torch.zeros(B, n_kv, T + 8, dtype=torch.float16, device=DEV)
+    encode(lt, k, v, 0, kp, kn, vp, vn, flags=(_lib.ENC_K_MIXED | _lib.ENC_V_NIBBLE) if mixed else 0)
+    q_rot = rotate_q(lt, (torch.randn(B, n_q, HD, generator=gen) * 2).half().to(DEV))
+    fl = (_lib.DEC_K_MIXED | _lib.DEC_V_NIBBLE) if mixed else 0
+    po_s, pl_s = decode(lt, q_rot, kp, kn, vp, vn, 0, T, n_splits=7, flags=fl)
+    po_g, pl_g = decode(lt, q_rot, kp, kn, vp, vn, 0, T, n_splits=7, flags=fl | _lib.DEC_GENERIC)
+    torch.cuda.synchronize()
+    assert torch.equal(pl_s, pl_g)
+    live = pl_s > -float("inf")
+    assert live.any() and torch.equal(po_s[live], po_g[live])
+
+
 def test_step_prepare_with_fused_rope_is_bit_identical():
     """Rotary embedding applied inside the append kernel against the fp16 expression
     (x * cos) + (rotate_half(x) * sin) evaluated by torch first: same packed rows, norms and q_rot."""
