@@ -160,6 +160,20 @@ int build(const std::string& prelude, bool load, Compiled** out, std::string* lo
         const bool verbose = getenv("BGTQ_JIT_VERBOSE") != nullptr;
         std::vector<const char*> opts = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo"};
         if (verbose) opts.push_back("--ptxas-options=-v");
+        std::vector<std::string> extra;             // BGTQ_JIT_OPTIONS: further NVRTC options, space separated
+        if (const char* e = getenv("BGTQ_JIT_OPTIONS")) {
+            std::string cur;
+            for (const char* ch = e;; ++ch) {
+                if (*ch == ' ' || *ch == 0) {
+                    if (!cur.empty()) extra.push_back(cur);
+                    cur.clear();
+                    if (*ch == 0) break;
+                } else {
+                    cur.push_back(*ch);
+                }
+            }
+        }
+        for (const std::string& x : extra) opts.push_back(x.c_str());
         const int rc = g_nvrtc.CompileProgram(prog, (int)opts.size(), opts.data());
         size_t n = 0;
         if (log && g_nvrtc.GetProgramLogSize(prog, &n) == 0 && n > 1) {

@@ -53,12 +53,20 @@ namespace bgtq {
 
 constexpr int kDecWarps = 16;
 constexpr int kDecThreads = 32 * kDecWarps;
+#ifdef BGTQ_EXP_STAGES
+constexpr int kDecStages = BGTQ_EXP_STAGES;
+#else
 constexpr int kDecStages = 2;
+#endif
 constexpr int kMergeStride = 132;  // floats per query row in the end-of-run merge buffer
 // shared-memory layout (byte offsets from the start of dynamic shared memory)
-// [barriers | query fragments | per-warp max / denominators | lookup tables | stages (merge buffer at run end)]
-constexpr uint32_t kOffQf = 1024, kOffMM = kOffQf + kMaxSteps * 32 * 8, kOffLut = kLutAlign;
-static_assert(kOffMM + 2 * kDecWarps * 8 * 4 <= kOffLut, "layout");
+// [barriers | query fragments | per-warp max / denominators | pad | lookup tables | stages (merge buffer at run end)]
+// The lookup tables start at the first address past kOffMisc whose ABSOLUTE shared-window address is a
+// multiple of kLutAlign (table bases are OR-ed into addresses); the stages follow at a fixed offset that
+// leaves room for the worst-case pad.
+constexpr uint32_t kOffQf = 1024, kOffMM = kOffQf + kMaxSteps * 32 * 8, kOffMisc = kOffMM + 2 * kDecWarps * 8 * 4;
+constexpr uint32_t kOffStagesMin = kOffMisc + kLutAlign;     // + lut_bytes = P.stage_off
+static_assert(kOffMisc % 128 == 0, "layout");
 constexpr uint32_t kMergeBytes = kDecWarps * 8 * kMergeStride * 4;
 #define BGTQ_INF __int_as_float(0x7f800000)
 
@@ -90,14 +98,35 @@ template <> struct VCfg<2> { static constexpr uint32_t M = 0x33333333u, GROUPS =
 template <> struct VCfg<3> { static constexpr uint32_t M = 0x001C71C7u, GROUPS = 2, REP_SHIFT = 5; };
 template <> struct VCfg<4> { static constexpr uint32_t M = 0x0F0F0F0Fu, GROUPS = 2, REP_SHIFT = 3; };
 
-__device__ __forceinline__ uint32_t ld32(const uint8_t* sm, uint32_t off) {
-    return *reinterpret_cast<const uint32_t*>(sm + off);
+// Shared-memory loads of the hot loop take ABSOLUTE 32-bit shared-window addresses: every base the loop uses
+// (stage rows, table bases with the lane's replica column, query fragments) has the window address of the
+// dynamic shared memory folded in once, so a table lookup is rotate/shift + one and-or + the load, with no
+// add in between.  (`sm` is unused; it keeps the call sites readable.)
+__device__ __forceinline__ uint32_t ld32(const uint8_t* sm, uint32_t addr) {
+    (void)sm;
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
 }
-__device__ __forceinline__ uint2 ld64(const uint8_t* sm, uint32_t off) {
-    return *reinterpret_cast<const uint2*>(sm + off);
+__device__ __forceinline__ uint2 ld64(const uint8_t* sm, uint32_t addr) {
+    (void)sm;
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
 }
-__device__ __forceinline__ uint32_t ld16(const uint8_t* sm, uint32_t off) {
-    return *reinterpret_cast<const uint16_t*>(sm + off);
+__device__ __forceinline__ uint32_t ld16(const uint8_t* sm, uint32_t addr) {
+    (void)sm;
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+// 2^x for the softmax: the hardware approximation (relative error 2^-22; the IEEE-style wrapper of exp2f
+// costs two more multiplies and a compare per value for denormal results that the fp16 rounding of p and the
+// fp32 denominator cannot see).  ex2(-inf) = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ uint32_t rotl32(uint32_t x, uint32_t n) { return __funnelshift_l(x, x, n); }
 
@@ -134,7 +163,7 @@ __device__ __forceinline__ void load_v16(const uint8_t* sm, uint32_t row_al, uin
 template <int KIND, int NU>
 __device__ __forceinline__ int k_segment(float (&acc)[NU][4], const uint8_t* sm, const uint32_t rowK,
                                          const uint32_t k_row8, const uint32_t lbit, const int q, const uint32_t tb,
-                                         const uint32_t esh8, const uint32_t mask8, const uint2* qf, const bool f16n,
+                                         const uint32_t esh8, const uint32_t mask8, const uint32_t qf, const bool f16n,
                                          const uint32_t (&n2)[2 * NU]) {
     constexpr int SB = KIND;                                   // stored bits
     constexpr int CAP = KIND == 3 ? 8 : 32 / SB;               // codes per 32-bit unit
@@ -151,7 +180,7 @@ __device__ __forceinline__ int k_segment(float (&acc)[NU][4], const uint8_t* sm,
 #pragma unroll
         for (int t = 0; t < TILES; ++t) {
             if (4 * t >= n) break;
-            const uint2 bq = qf[step * 32];
+            const uint2 bq = ld64(sm, qf + step * 256);
             ++step;
             uint32_t lo[2 * NU], hi[2 * NU];                   // fp16x2 of codes (0,1) and (2,3) of this k-tile, per row
             if constexpr (KIND == 1 || KIND == 2) {            // quad tables: one 64-bit lookup per row
@@ -211,7 +240,9 @@ __device__ __forceinline__ int k_segment(float (&acc)[NU][4], const uint8_t* sm,
 
 // Lane-constant inputs of the K side of a warp's token tile.
 struct KLane {
-    uint32_t rowK, rowN;       // byte offsets (from the start of shared memory) of the lane's first packed row / norm row
+    uint32_t lut;              // absolute shared address of the lookup tables
+    uint32_t qf;               // absolute shared address of this lane's first query fragment
+    uint32_t rowK, rowN;       // absolute shared addresses of the lane's first packed row (word aligned) / norm row
     uint32_t k_row8, kn_row8;  // byte distance between rows r and r + 8
     uint32_t k_p0;             // bit phase of the packed rows inside their first aligned word
     uint32_t j, lane;
@@ -220,9 +251,9 @@ struct KLane {
 #ifndef BGTQ_JIT
 // S^T = Khat . Qrot^T of a warp's NU 16-token row tiles, segment list read from the plan.
 template <int NU>
-__device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const DecHeadPlan& hp,
-                                       const uint2* qf) {
+__device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const DecHeadPlan& hp) {
     const int n_seg = hp.n_seg;
+    uint32_t qf = kl.qf;
     for (int sg = 0; sg < n_seg; ++sg) {
         const DecSeg sd = hp.seg[sg];
         // Norm handling: the bit-packed layout scales the fp32 dot product of a segment by its fp16 norm; the
@@ -241,7 +272,7 @@ __device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, con
 #pragma unroll
         for (int u = 0; u < NU; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
         const uint32_t lbit = kl.k_p0 + sd.bit0 + kl.j * sd.lane_bits;
-        const uint32_t tb = kOffLut + sd.tbl + ((kl.lane & ((1u << sd.rep_log2) - 1u)) << sd.ent_log2);
+        const uint32_t tb = kl.lut + sd.tbl + ((kl.lane & ((1u << sd.rep_log2) - 1u)) << sd.ent_log2);
         const int q = sd.q;
         int used;
         switch (sd.kind) {
@@ -254,7 +285,7 @@ __device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, con
                                         ((1u << sd.bw) - 1u) << sd.esh, qf, f16n, n2);
                 break;
         }
-        qf += used * 32;
+        qf += used * 256;
 #pragma unroll
         for (int u = 0; u < NU; ++u) {
             S[u][0] = fmaf(nrm[2 * u], acc[u][0], S[u][0]);
@@ -270,8 +301,14 @@ __device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, con
 //     template <> struct jit::Head<H> { static constexpr int n_seg; static constexpr jit::SegC seg[8]; };
 // and every loop below has a compile-time trip count.
 // ---------------------------------------------------------------------------------------------
+// Bring the bit field that starts at bit POS of x to bit TO (a plain shift: which pipe executes it is the
+// compiler's choice, unlike a funnel shift).
+// Both positions are constants once the loops around the call are unrolled.
+__device__ __forceinline__ uint32_t field_to(uint32_t x, uint32_t to, uint32_t pos) {
+    return pos < to ? x << (to - pos) : x >> (pos - to);
+}
 template <class HeadT, int SG, int NU>
-__device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const uint2* qf) {
+__device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm, const KLane& kl) {
     constexpr jit::SegC c = HeadT::seg[SG];
     constexpr int SB = c.kind, Q = c.q;
     constexpr int CAP = c.kind == 3 ? 8 : 32 / SB, TILES = CAP / 4;
@@ -284,11 +321,9 @@ __device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm
         n2[i] = nh | (nh << 16);
         nrm[i] = f16n ? 1.0f : f16_bits_to_float(nh);
     }
-    float acc[NU][4];
-#pragma unroll
-    for (int u = 0; u < NU; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+    float acc[NU][4];     // the segment's first k-tile starts it from zero
     const uint32_t lbit = kl.k_p0 + (uint32_t)c.bit0 + kl.j * (uint32_t)c.lane_bits;
-    const uint32_t tb = kOffLut + (uint32_t)c.tbl + ((kl.lane & ((1u << c.rep_log2) - 1u)) << c.ent_log2);
+    const uint32_t tb = kl.lut + (uint32_t)c.tbl + ((kl.lane & ((1u << c.rep_log2) - 1u)) << c.ent_log2);
 #pragma unroll
     for (int cc = 0; cc < Q; cc += CAP) {
         const uint32_t pbit = lbit + (uint32_t)(cc * SB);
@@ -301,36 +336,35 @@ __device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm
         for (int t = 0; t < TILES; ++t) {
             if (cc + 4 * t < Q) {
                 const bool full = Q - cc - 4 * t >= 4;         // else codes 2, 3 meet a zero query fragment
-                const uint2 bq = qf[(c.step0 + (cc + 4 * t) / 4) * 32];
+                const uint2 bq = ld64(sm, kl.qf + (c.step0 + (cc + 4 * t) / 4) * 256);
                 uint32_t lo[2 * NU], hi[2 * NU];
                 if constexpr (c.kind == 1 || c.kind == 2) {    // quad tables: one 64-bit lookup per row
-                    const uint32_t ESH = c.kind == 1 ? kEsh1 : kEsh2, FW = 4 * SB;
-                    const uint32_t MASK = ((1u << FW) - 1u) << ESH, R = (32u + ESH - FW * t) & 31u;
+                    constexpr uint32_t ESH = c.kind == 1 ? kEsh1 : kEsh2, FW = 4 * SB;
+                    constexpr uint32_t MASK = ((1u << FW) - 1u) << ESH;
 #pragma unroll
                     for (int i = 0; i < 2 * NU; ++i) {
-                        const uint2 v = ld64(sm, (rotl32(cur[i], R) & MASK) | tb);
+                        const uint2 v = ld64(sm, (field_to(cur[i], ESH, FW * t) & MASK) | tb);
                         lo[i] = v.x;
                         hi[i] = v.y;
                     }
                 } else if constexpr (c.kind == 3 || c.kind == 4) {   // pair tables
-                    const uint32_t ESH = c.kind == 3 ? kEsh3 : kEsh4, FW = 2 * SB;
-                    const uint32_t MASK = ((1u << FW) - 1u) << ESH;
-                    const uint32_t R0 = (64u + ESH - 2 * FW * t) & 31u, R1 = (64u + ESH - 2 * FW * t - FW) & 31u;
+                    constexpr uint32_t ESH = c.kind == 3 ? kEsh3 : kEsh4, FW = 2 * SB;
+                    constexpr uint32_t MASK = ((1u << FW) - 1u) << ESH;
 #pragma unroll
                     for (int i = 0; i < 2 * NU; ++i) {
-                        lo[i] = ld32(sm, (rotl32(cur[i], R0) & MASK) | tb);
-                        hi[i] = full ? ld32(sm, (rotl32(cur[i], R1) & MASK) | tb) : 0u;
+                        lo[i] = ld32(sm, (field_to(cur[i], ESH, 2 * FW * t) & MASK) | tb);
+                        hi[i] = full ? ld32(sm, (field_to(cur[i], ESH, 2 * FW * t + FW) & MASK) | tb) : 0u;
                     }
                 } else {                                       // raw bytes, one code per lookup
-                    const uint32_t ESH = c.esh, MASK = ((1u << c.bw) - 1u) << ESH;
+                    constexpr uint32_t ESH = c.esh, MASK = ((1u << c.bw) - 1u) << ESH;
 #pragma unroll
                     for (int i = 0; i < 2 * NU; ++i) {
-                        const uint32_t c0 = ld32(sm, (rotl32(cur[i], ESH) & MASK) | tb);
-                        const uint32_t c1 = ld32(sm, (rotl32(cur[i], ESH + 24u) & MASK) | tb);
+                        const uint32_t c0 = ld32(sm, (field_to(cur[i], ESH, 0) & MASK) | tb);
+                        const uint32_t c1 = ld32(sm, (field_to(cur[i], ESH, 8) & MASK) | tb);
                         lo[i] = __byte_perm(c0, c1, 0x5410);
                         if (full) {
-                            const uint32_t c2 = ld32(sm, (rotl32(cur[i], ESH + 16u) & MASK) | tb);
-                            const uint32_t c3 = ld32(sm, (rotl32(cur[i], ESH + 8u) & MASK) | tb);
+                            const uint32_t c2 = ld32(sm, (field_to(cur[i], ESH, 16) & MASK) | tb);
+                            const uint32_t c3 = ld32(sm, (field_to(cur[i], ESH, 24) & MASK) | tb);
                             hi[i] = __byte_perm(c2, c3, 0x5410);
                         } else {
                             hi[i] = 0u;
@@ -348,7 +382,8 @@ __device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
                     const uint32_t a[4] = {lo[2 * u], lo[2 * u + 1], hi[2 * u], hi[2 * u + 1]};
-                    mma_16816(acc[u], a, b);
+                    if (cc + 4 * t == 0) mma_16816_z(acc[u], a, b);
+                    else mma_16816(acc[u], a, b);
                 }
             }
         }
@@ -362,16 +397,15 @@ __device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm
     }
 }
 template <class HeadT, int SG, int NU>
-__device__ __forceinline__ void k_side_from(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const uint2* qf) {
+__device__ __forceinline__ void k_side_from(float (&S)[NU][4], const uint8_t* sm, const KLane& kl) {
     if constexpr (SG < HeadT::n_seg) {
-        k_segment_c<HeadT, SG, NU>(S, sm, kl, qf);
-        k_side_from<HeadT, SG + 1, NU>(S, sm, kl, qf);
+        k_segment_c<HeadT, SG, NU>(S, sm, kl);
+        k_side_from<HeadT, SG + 1, NU>(S, sm, kl);
     }
 }
 template <int NU>
-__device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const int h,
-                                       const uint2* qf) {
-#define BGTQ_JIT_CASE(H) case H: k_side_from<jit::Head<H>, 0, NU>(S, sm, kl, qf); break;
+__device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const int h) {
+#define BGTQ_JIT_CASE(H) case H: k_side_from<jit::Head<H>, 0, NU>(S, sm, kl); break;
     switch (h) { BGTQ_JIT_CASES }       // one case per head of the layer, spelled by the prelude
 #undef BGTQ_JIT_CASE
 }
@@ -381,7 +415,11 @@ __device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, con
 template <int VB, int NU>
 __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_constant__ DecParams P) {
 #else
+#ifdef BGTQ_EXP_NU
+constexpr int VB = BGTQ_JIT_VB, NU = BGTQ_EXP_NU;
+#else
 constexpr int VB = BGTQ_JIT_VB, NU = BGTQ_JIT_NU;
+#endif
 extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(const __grid_constant__ DecParams P) {
 #endif
     extern __shared__ __align__(128) uint8_t smem[];
@@ -401,7 +439,9 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
     float* mm = reinterpret_cast<float*>(smem + kOffMM);                     // [warp][8] running max
     float* ml = mm + kDecWarps * 8;                                          // [warp][8] denominators
     const uint8_t* sm = smem;
-    constexpr uint32_t lut_rel = kOffLut;
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t lut_abs = (sbase + kOffMisc + kLutAlign - 1u) & ~(kLutAlign - 1u);   // see the layout comment
+    const uint32_t lut_rel = lut_abs - sbase;
 
     if (tid == 0) {
         for (int i = 0; i < kDecStages; ++i) {
@@ -544,20 +584,22 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
         const uint32_t v_off = P.off_v + v_pre + tkv * P.vp_st;
         const uint32_t vn_row = P.off_vn + vn_pre + tkv * P.vn_st;
         const uint32_t k_row8 = 8u * P.kp_st, kn_row8 = 8u * P.kn_st;
-        const uint32_t vtbl = lut_rel + hp.v_tbl + (lane4 & ((1u << kVSh) - 1u));
+        const uint32_t vtbl = lut_abs + hp.v_tbl + (lane4 & ((1u << kVSh) - 1u));
 
         for (int it = 0; it < n_tiles; ++it, ++g_it) {
             const int st = g_it % kDecStages;
             const uint32_t use = g_it / kDecStages;
             if (!mbar_wait_bounded(&full[st], use & 1u)) ok = false;
             const int nt = min(kTileTok, t1 - (t0 + it * kTileTok));
-            const uint32_t sb = P.stage_off + st * P.stage_bytes;
+            const uint32_t sb = sbase + P.stage_off + st * P.stage_bytes;
             if (warp * kWarpTok < nt) {
                 // ---------------- S^T = Khat . Qrot^T for NU 16-token row tiles ----------------
                 float S[NU][4];
 #pragma unroll
                 for (int u = 0; u < NU; ++u) S[u][0] = S[u][1] = S[u][2] = S[u][3] = 0.f;
                 KLane kl;
+                kl.lut = lut_abs;
+                kl.qf = sbase + kOffQf + (uint32_t)lane * 8u;
                 kl.rowK = sb + k_row_al;
                 kl.rowN = sb + kn_row;
                 kl.k_row8 = k_row8;
@@ -566,9 +608,11 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                 kl.j = (uint32_t)j;
                 kl.lane = (uint32_t)lane;
 #ifndef BGTQ_JIT
-                k_side<NU>(S, sm, kl, hp, qfrag + lane);
+                k_side<NU>(S, sm, kl, hp);
 #else
-                k_side<NU>(S, sm, kl, h, qfrag + lane);
+#ifndef BGTQ_ABL_NO_K
+                k_side<NU>(S, sm, kl, h);
+#endif
 #endif
                 // ---------------- online softmax (log2 domain) over the warp's tokens ----------------
                 float sv[NU][4];
@@ -590,15 +634,15 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                 }
                 const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
                 const float z0 = n0 == -BGTQ_INF ? 0.f : n0, z1 = n1 == -BGTQ_INF ? 0.f : n1;
-                const float al0 = exp2f(m0 - z0), al1 = exp2f(m1 - z1);
+                const float al0 = fast_exp2(m0 - z0), al1 = fast_exp2(m1 - z1);
                 m0 = n0;
                 m1 = n1;
                 uint32_t pf[NU][2];
                 float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
-                    const float p0 = exp2f(sv[u][0] - z0), p1 = exp2f(sv[u][1] - z1);
-                    const float p2 = exp2f(sv[u][2] - z0), p3 = exp2f(sv[u][3] - z1);
+                    const float p0 = fast_exp2(sv[u][0] - z0), p1 = fast_exp2(sv[u][1] - z1);
+                    const float p2 = fast_exp2(sv[u][2] - z0), p3 = fast_exp2(sv[u][3] - z1);
                     ps0 += p0 + p2;
                     ps1 += p1 + p3;
                     pf[u][0] = movmatrix_trans(pack_half2(p0, p1));
@@ -621,6 +665,7 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                 constexpr uint32_t M = VCfg<VB>::M, G = VCfg<VB>::GROUPS, FW = 2 * VB;
                 constexpr uint32_t IMS = ((1u << FW) - 1u) << kVSh;
                 constexpr int PER = 8 / G;   // k-tiles (dim pairs) per 32-bit group
+#ifndef BGTQ_ABL_NO_V
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
                     uint32_t gA[2], gB[2], gC[2], gD[2];
@@ -654,6 +699,9 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                         }
                     }
                 }
+#else
+                O[0][0] += __uint_as_float(pf[0][0] + pf[NU - 1][1]);
+#endif
             }
             __syncwarp();
             // Release the stage; the last warp to do so streams the tile that reuses it.  The counter only ever
@@ -676,14 +724,16 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
         }
         // Every tile of the run has been consumed once all warps are here: the stage region is idle.
         __syncthreads();
-        float* mo = reinterpret_cast<float*>(smem + P.stage_off);                // [warp][8][kMergeStride]
+        // Merge buffer [warp][8 queries][kMergeStride]; dim d of a row sits at position (d & 15) * 8 + (d >> 4), so
+        // that the 32 lanes of a warp (dims 16 r + c, queries 2 j + e) store to 32 different banks.
+        float* mo = reinterpret_cast<float*>(smem + P.stage_off);
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) {
-            float* base = mo + (warp * 8 + 2 * j) * kMergeStride + 16 * r + 2 * mt;
+            float* base = mo + (warp * 8 + 2 * j) * kMergeStride + 16 * mt + r;    // dim 16 r + 2 mt
             base[0] = O[mt][0];
             base[kMergeStride] = O[mt][1];
-            base[1] = O[mt][2];
-            base[kMergeStride + 1] = O[mt][3];
+            base[8] = O[mt][2];                                                      // dim 16 r + 2 mt + 1
+            base[kMergeStride + 8] = O[mt][3];
         }
         if (r == 0) {
             mm[warp * 8 + 2 * j] = m0;
@@ -693,7 +743,8 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
         }
         __syncthreads();
         {
-            const int qi = tid >> 6, d0 = (tid & 63) * 2;            // 64 threads per query head, two dims each
+            // 64 threads per query head; thread t reads positions 2 t, 2 t + 1 = dims d0 and d0 + 16
+            const int qi = tid >> 6, t2 = (tid & 63) * 2, d0 = (t2 & 7) * 16 + (t2 >> 3);
             if (qi < P.gqa) {
                 float mx = -BGTQ_INF;
 #pragma unroll
@@ -710,11 +761,12 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                 for (int i = 0; i < 2; ++i) {
                     float v = 0.f;
 #pragma unroll
-                    for (int w = 0; w < kDecWarps; ++w) v = fmaf(mo[(w * 8 + qi) * kMergeStride + d0 + i], wgt[w], v);
+                    for (int w = 0; w < kDecWarps; ++w) v = fmaf(mo[(w * 8 + qi) * kMergeStride + t2 + i], wgt[w], v);
                     o[i] = v * inv;
                 }
                 const size_t row = ((size_t)b * P.n_q + (size_t)h * P.gqa + qi) * P.n_splits;
-                *reinterpret_cast<float2*>(P.part_o + (row + s0) * kHD + d0) = make_float2(o[0], o[1]);
+                P.part_o[(row + s0) * kHD + d0] = o[0];
+                P.part_o[(row + s0) * kHD + d0 + 16] = o[1];
                 if ((tid & 63) == 0)
                     P.part_lse[row + s0] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -BGTQ_INF;
                 // slots merged into this partial, and (after the pair's last live item) the slots past them
