@@ -184,9 +184,8 @@ __device__ __forceinline__ int k_segment(float (&acc)[NU][4], const uint8_t* sm,
             ++step;
             uint32_t lo[2 * NU], hi[2 * NU];                   // fp16x2 of codes (0,1) and (2,3) of this k-tile, per row
             if constexpr (KIND == 1 || KIND == 2) {            // quad tables: one 64-bit lookup per row
-                constexpr uint32_t ESH = KIND == 1 ? kEsh1 : kEsh2, FW = 4 * SB;
-                constexpr uint32_t MASK = ((1u << FW) - 1u) << ESH;
-                const uint32_t R = (32u + ESH - FW * t) & 31u;
+                constexpr uint32_t FW = 4 * SB;
+                const uint32_t MASK = ((1u << FW) - 1u) << esh8, R = (32u + esh8 - FW * t) & 31u;
 #pragma unroll
                 for (int i = 0; i < 2 * NU; ++i) {
                     const uint2 v = ld64(sm, (rotl32(cur[i], R) & MASK) | tb);
@@ -194,9 +193,9 @@ __device__ __forceinline__ int k_segment(float (&acc)[NU][4], const uint8_t* sm,
                     hi[i] = v.y;
                 }
             } else if constexpr (KIND == 3 || KIND == 4) {     // pair tables
-                constexpr uint32_t ESH = KIND == 3 ? kEsh3 : kEsh4, FW = 2 * SB;
-                constexpr uint32_t MASK = ((1u << FW) - 1u) << ESH;
-                const uint32_t R0 = (64u + ESH - 2 * FW * t) & 31u, R1 = (64u + ESH - 2 * FW * t - FW) & 31u;
+                constexpr uint32_t FW = 2 * SB;
+                const uint32_t MASK = ((1u << FW) - 1u) << esh8;
+                const uint32_t R0 = (64u + esh8 - 2 * FW * t) & 31u, R1 = (64u + esh8 - 2 * FW * t - FW) & 31u;
                 const bool full = n - 4 * t >= 4;              // else codes 2, 3 meet a zero query fragment
 #pragma unroll
                 for (int i = 0; i < 2 * NU; ++i) {
@@ -276,10 +275,10 @@ __device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, con
         const int q = sd.q;
         int used;
         switch (sd.kind) {
-            case 1: used = k_segment<1, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
-            case 2: used = k_segment<2, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
-            case 3: used = k_segment<3, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
-            case 4: used = k_segment<4, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, 0u, 0u, qf, f16n, n2); break;
+            case 1: used = k_segment<1, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, (uint32_t)sd.esh, 0u, qf, f16n, n2); break;
+            case 2: used = k_segment<2, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, (uint32_t)sd.esh, 0u, qf, f16n, n2); break;
+            case 3: used = k_segment<3, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, (uint32_t)sd.esh, 0u, qf, f16n, n2); break;
+            case 4: used = k_segment<4, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, (uint32_t)sd.esh, 0u, qf, f16n, n2); break;
             default:
                 used = k_segment<8, NU>(acc, sm, kl.rowK, kl.k_row8, lbit, q, tb, (uint32_t)sd.esh,
                                         ((1u << sd.bw) - 1u) << sd.esh, qf, f16n, n2);
@@ -339,7 +338,7 @@ __device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm
                 const uint2 bq = ld64(sm, kl.qf + (c.step0 + (cc + 4 * t) / 4) * 256);
                 uint32_t lo[2 * NU], hi[2 * NU];
                 if constexpr (c.kind == 1 || c.kind == 2) {    // quad tables: one 64-bit lookup per row
-                    constexpr uint32_t ESH = c.kind == 1 ? kEsh1 : kEsh2, FW = 4 * SB;
+                    constexpr uint32_t ESH = c.esh, FW = 4 * SB;
                     constexpr uint32_t MASK = ((1u << FW) - 1u) << ESH;
 #pragma unroll
                     for (int i = 0; i < 2 * NU; ++i) {
@@ -348,7 +347,7 @@ __device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm
                         hi[i] = v.y;
                     }
                 } else if constexpr (c.kind == 3 || c.kind == 4) {   // pair tables
-                    constexpr uint32_t ESH = c.kind == 3 ? kEsh3 : kEsh4, FW = 2 * SB;
+                    constexpr uint32_t ESH = c.esh, FW = 2 * SB;
                     constexpr uint32_t MASK = ((1u << FW) - 1u) << ESH;
 #pragma unroll
                     for (int i = 0; i < 2 * NU; ++i) {

@@ -15,12 +15,12 @@ struct TableDims {
     uint32_t bytes() const { return (entries << ent_log2) << rep_log2; }
 };
 
-TableDims k_table_dims(int kind, int bw) {
+TableDims k_table_dims(int kind, int bw, uint32_t boost) {
     switch (kind) {
         case 1: return {16u, 3u, kRep1};
-        case 2: return {256u, 3u, kRep2};
+        case 2: return {256u, 3u, kRep2 + boost};
         case 3: return {64u, 2u, kRep3};
-        case 4: return {256u, 2u, kRep4};
+        case 4: return {256u, 2u, kRep4 + boost};
         default: return {1u << bw, 2u, bw <= 6 ? 5u : (bw == 7 ? 4u : 3u)};
     }
 }
@@ -43,7 +43,22 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const Bgt
     pl.v_sbits = (flags & BGTQ_DEC_V_NIBBLE) ? 4 : pl.v_bits;
     pl.v_rep_log2 = v_rep_log2_for(pl.v_sbits);
     const uint32_t v_bytes = ((1u << (2 * pl.v_sbits)) << 2) << pl.v_rep_log2;
+    // Shared memory left for the tables once two stages of 512-token tiles of the live row sizes are set aside
+    // (launches with wider, padded rows fall back to 256-token tiles on their own).
+    uint32_t row_bytes = 0;
+    for (int h = 0; h < n_kv; ++h) {
+        const BgtqHeadDesc& d = desc_host[h];
+        const uint32_t kb = (flags & BGTQ_DEC_K_MIXED) ? (uint32_t)d.k_mixed_bytes : (uint32_t)d.k_row_bytes;
+        const uint32_t vb = (flags & BGTQ_DEC_V_NIBBLE) ? kHD / 2u : (uint32_t)d.v_row_bytes;
+        const uint32_t rb = kb + 2u * 8u + vb + 2u;
+        row_bytes = rb > row_bytes ? rb : row_bytes;
+    }
+    const uint32_t stage_est = 2u * (512u * row_bytes + 4u * 64u + 128u);
+    const uint32_t fixed_est = 7168u + kLutAlign + stage_est;
+    const uint32_t lut_budget = fixed_est < 227u * 1024u ? 227u * 1024u - fixed_est : 0u;
     uint32_t lut_bytes = 0;
+    for (uint32_t boost = 1;; --boost) {        // more replicas of the 256-entry tables when they fit
+    lut_bytes = 0;
     for (int h = 0; h < n_kv; ++h) {
         const BgtqHeadDesc& d = desc_host[h];
         if (d.v_bits != pl.v_bits) return BGTQ_E_UNSUPPORTED;
@@ -64,7 +79,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const Bgt
                 sg.kind = bw <= 4 ? bw : 8;
                 bit0 = 8u * d.seg_pack_off[s];
             }
-            const TableDims td = k_table_dims(sg.kind, bw);
+            const TableDims td = k_table_dims(sg.kind, bw, boost);
             sg.bw = (uint8_t)bw;
             sg.q = (uint8_t)(2 * ((len + 7) / 8));
             // reference: only segments 0..4 of at least 16 dims take the tensor-core (fp16 operand) path
@@ -103,6 +118,8 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const Bgt
         }
         hp.image_bytes = off;
         lut_bytes = off > lut_bytes ? off : lut_bytes;
+    }
+    if (boost == 0 || lut_bytes <= lut_budget) break;
     }
     pl.lut_bytes = (lut_bytes + 127u) / 128u * 128u;
     pl.image = nullptr;

@@ -19,11 +19,13 @@
 //
 //   stored width   entry                      index        replicas  bytes
 //   1 bit          4 codes -> 2 x fp16x2      4 bits       32        4096
-//   2 bits         4 codes -> 2 x fp16x2      8 bits       4         8192
+//   2 bits         4 codes -> 2 x fp16x2      8 bits       4 or 8    8192 / 16384
 //   3 bits         2 codes -> fp16x2          6 bits       32        8192
-//   4 bits         2 codes -> fp16x2          8 bits       8         8192
+//   4 bits         2 codes -> fp16x2          8 bits       8 or 16   8192 / 16384
 //   8 bits (5..8)  1 code  -> fp16 (twice)    bw bits      32..8     4096/8192
 //   V (pair of tokens, one dim) -> fp16x2     2*vb bits    32..8     <= 8192
+// (the larger replica counts halve the bank conflicts of the 256-entry tables; the plan uses them when
+// the tables of every head of the layer still leave room for two stages of 512-token tiles)
 #pragma once
 #ifndef BGTQ_JIT
 #include <stdint.h>
@@ -33,14 +35,10 @@ namespace bgtq {
 
 constexpr int kMaxSteps = 20;        // m16n8k16 k-tiles per token tile and head: sum over segments of ceil(q/4)
 constexpr int kMaxPlanHeads = 8;     // KV heads per launch
-constexpr uint32_t kLutAlign = 8192; // largest table; the LUT region starts on a multiple of it
+constexpr uint32_t kLutAlign = 16384; // largest table; the LUT region starts on a multiple of it
 
-// log2 of the byte distance between consecutive table entries (entry size x replicas), per stored width
-constexpr uint32_t kEsh1 = 8, kEsh2 = 5, kEsh3 = 7, kEsh4 = 5;
-// log2 of the replica count / of the entry size in bytes, per stored width (kind 8: see DecSeg)
+// log2 of the replica count per stored width (kind 8: by code width); kinds 2 and 4 take one more when it fits
 constexpr uint32_t kRep1 = 5, kRep2 = 2, kRep3 = 5, kRep4 = 3;
-static_assert(kEsh1 == 3 + kRep1 && kEsh2 == 3 + kRep2 && kEsh3 == 2 + kRep3 && kEsh4 == 2 + kRep4,
-              "entry stride = entry size x replicas");
 
 // One K width segment = one lookup table = one norm group.
 struct DecSeg {

@@ -137,7 +137,7 @@ def test_plan_and_image_reproduce_every_code(case):
             sg = hp.seg[s]
             size = ((16 if sg.kind == 1 else 64 if sg.kind == 3 else (1 << sg.bw) if sg.kind == 8 else 256)
                     << sg.ent_log2) << sg.rep_log2
-            assert sg.esh == sg.ent_log2 + sg.rep_log2 and sg.tbl % size == 0 and size <= 8192
+            assert sg.esh == sg.ent_log2 + sg.rep_log2 and sg.tbl % size == 0 and size <= 16384
             spans.append((sg.tbl, sg.tbl + size))
         v_size = ((1 << (2 * plan.v_sbits)) * 4) << plan.v_rep_log2
         assert hp.v_tbl % v_size == 0
