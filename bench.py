@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the packed-cache decode hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference|triton]
 
 One "step" is one decode step of the hot path over every layer of the workload:
 rotate_q -> encode/append the new token's K,V -> fused packed decode -> combine, for all batch
@@ -9,7 +9,11 @@ entries and KV heads (the model's projections and MLP are not part of this path)
 one JSON line.  With N > 1 (torchrun, one rank per GPU) every rank holds its own batch slice
 (weak scaling, no collective on the data path); the time is the max over ranks.
 
---impl reference times the CPU restatement of the same path (oracle/) on the host cores.
+--impl reference times the reference project's own CPU path (its unaccelerated quantise-dequantise +
+attention, imported from baseline/_ref when that git-ignored copy of the reference package is present,
+else the NumPy restatement under oracle/) on the host cores.  --impl triton times the reference's own
+Triton decode path on this GPU (baseline/_ref again; it never touches this repository's package); the
+default run carries that figure as config.reference_triton.
 """
 import argparse
 import json
@@ -56,9 +60,25 @@ WORKLOADS = {
                                               theta=1e6, n_sink=0, window=0),
 }
 DEFAULT = "qwen2.5-3b_k3v3_b8_t32768"
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch, from the ncu captures summarised
-# under profiles/ (same per-layer shape for the 4-layer and the 36-layer workload)
-DRAM_TRAFFIC_PER_LAUNCH = {"qwen2.5-3b_k3v3_b8_t32768": 63.98e6, "qwen2.5-3b_k3v3_b8_t32768_4layers": 63.98e6}
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def dram_traffic(workload):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture
+    recorded in profiles/dram_traffic.json (which names the command and the kernel source it was taken
+    with).  None when there is no record for the workload or the kernel source changed since the capture."""
+    try:
+        rec = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json")))[workload]
+    except Exception:
+        return None
+    import hashlib
+    h = hashlib.sha256()
+    for f in rec.get("sources", []):
+        try:
+            h.update(open(os.path.join(ROOT, f), "rb").read())
+        except OSError:
+            return None
+    return rec["bytes_per_launch"] if h.hexdigest()[:16] == rec.get("sources_sha16") else None
 
 
 def synth_keys(gen, shape_bt, theta, device):
@@ -171,30 +191,285 @@ def cpu_decode_sample(w, seed=0, t_sample=None):
     return dt, f"1 (batch, KV-head) pair of 1 layer, {T} cached tokens, oracle decode x{reps}"
 
 
+def _import_reference():
+    """The reference package from the git-ignored copy under baseline/_ref, or None."""
+    if not os.path.isdir(os.path.join(REF_DIR, "blockgtq")):
+        return None
+    if REF_DIR not in sys.path:
+        sys.path.insert(0, REF_DIR)
+    try:
+        import blockgtq  # noqa: F401
+        return blockgtq
+    except Exception:
+        return None
+
+
+class RefCpuSlice:
+    """The reference's unaccelerated path (blockgtq/unaccelerated.py:121-131) on one slice of the workload:
+    one layer, batch 1, every KV head: BlockGTQPipeline.compress_decompress of the cached keys,
+    TurboQuantMSE.compress_decompress of the cached values, then scaled_dot_product_attention of the step's
+    queries over the de-quantised cache, with torch using all host cores."""
+
+    def __init__(self, w, cores):
+        from blockgtq.block_gtq_pipeline import BlockGTQPipeline
+        from blockgtq.tq import TurboQuantMSE
+        torch.set_num_threads(cores)
+        gen = torch.Generator().manual_seed(0)
+        T, n_kv, gqa = w["ctx"], w["n_kv"], w["n_q"] // w["n_kv"]
+        ck = synth_keys(gen, (1, 2048), w["theta"], "cpu")[0]
+        cq = synth_keys(gen, (gqa, 2048), w["theta"], "cpu").reshape(-1, HD)
+        # one calibrated pipeline serves every head of the slice: the arithmetic does not depend on the bit map
+        self.kq = BlockGTQPipeline(head_dim=HD, avg_bits=float(w["k_bits"]), device=torch.device("cpu"))
+        self.kq.calibrate(cq.float().contiguous(), ck.float().contiguous())
+        self.vq = TurboQuantMSE(d=HD, bit_width=w["v_bits"], seed=1000, device=torch.device("cpu"))
+        self.k = torch.stack([synth_keys(gen, (1, T), w["theta"], "cpu")[0] for _ in range(n_kv)]).float()
+        self.v = torch.randn(n_kv, T, HD, generator=gen)
+        self.q = torch.randn(1, n_kv * gqa, 1, HD, generator=gen)
+        self.n_kv, self.gqa = n_kv, gqa
+
+    def step(self):
+        import torch.nn.functional as F
+        kh = torch.stack([self.kq.compress_decompress(self.k[h]) for h in range(self.n_kv)])
+        vh = torch.stack([self.vq.compress_decompress(self.v[h]) for h in range(self.n_kv)])
+        kk = kh.repeat_interleave(self.gqa, dim=0).unsqueeze(0)
+        vv = vh.repeat_interleave(self.gqa, dim=0).unsqueeze(0)
+        return F.scaled_dot_product_attention(self.q, kk, vv)
+
+
 def run_reference(args, w, name, rank, world):
-    """CPU arm: the oracle port of the decode path on the host cores, bounded sample."""
+    """CPU arm: the reference's own unaccelerated path on a bounded slice per step (one layer, batch 1), all
+    host cores; the step time of the full workload is the slice time x layers x batch, and says so."""
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    per_pair = []
-    for i in range(max(1, min(args.steps, 3))):
-        dt, sample = cpu_decode_sample(w, seed=i)
-        per_pair.append(dt)
-    dt = statistics.median(per_pair)
-    pairs = w["layers"] * w["batch"] * w["n_kv"]
-    step_s = dt * pairs
-    val = w["batch"] / step_s
+    L, B = w["layers"], w["batch"]
+    if w.get("mode") in ("encode", "prefill"):
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm covers the decode workloads only"}))
+        return
+    times, kind, sample = [], "port", ""
+    if _import_reference() is not None:
+        try:
+            sl = RefCpuSlice(w, cores)
+            for i in range(args.warmup + args.steps):
+                t0 = time.perf_counter()
+                sl.step()
+                if i >= args.warmup:
+                    times.append(time.perf_counter() - t0)
+            kind = "reference"
+            sample = (f"per step: 1 layer x batch 1 x {w['n_kv']} KV heads x {w['ctx']} cached tokens through the "
+                      "reference's BlockGTQPipeline.compress_decompress (K) + TurboQuantMSE.compress_decompress (V) + "
+                      f"scaled_dot_product_attention, torch.set_num_threads({cores}); step time of the workload = "
+                      f"slice x {L * B} (layers x batch)")
+            scale = L * B
+        except Exception as e:                                     # noqa: BLE001
+            sample = f"reference CPU path failed ({type(e).__name__}: {e}); "
+            times = []
+    if not times:
+        for i in range(max(1, min(args.steps, 3))):
+            dt, desc = cpu_decode_sample(w, seed=i)
+            times.append(dt)
+        scale = L * B * w["n_kv"]
+        sample += desc + f" (NumPy restatement, one thread); step time = sample x {scale}"
+    dt = statistics.median(times)
+    step_s = dt * scale
+    val = B / step_s
     line = {
         "impl": "reference", "metric": "decode_tokens_per_s", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "note": "CPU restatement of the packed decode path; step time = sample time x "
-                   f"{pairs} (layers x batch x KV heads), cache encode not timed"},
-        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "steps": len(times), "warmup": args.warmup if kind == "reference" else 0, "ms_per_step": step_s * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(name, w, 1) | {
+            "sample_ms": dt * 1e3, "scaled_by": scale,
+            "note": "ms_per_step is the measured slice time x scaled_by; every step of this arm runs one slice"},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores if kind == "reference" else 1, "kind": kind,
+                         "sample": sample},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def cpu_baseline(w):
+    """The reported CPU baseline of the default run: a few slices of the reference's unaccelerated path (kind
+    "reference") when baseline/_ref is present, else the NumPy restatement (kind "port")."""
+    cores = os.cpu_count() or 1
+    L, B = w["layers"], w["batch"]
+    if _import_reference() is not None:
+        try:
+            sl = RefCpuSlice(w, cores)
+            sl.step()
+            times = []
+            t_end = time.perf_counter() + 12.0
+            while len(times) < 8 and (time.perf_counter() < t_end or not times):
+                t0 = time.perf_counter()
+                sl.step()
+                times.append(time.perf_counter() - t0)
+            dt = statistics.median(times)
+            return {"value": B / (dt * L * B), "unit": "tok/s", "cores": cores, "kind": "reference",
+                    "sample": f"{len(times)} x (1 layer x batch 1 x {w['n_kv']} KV heads x {w['ctx']} cached tokens) through "
+                              "the reference's BlockGTQPipeline.compress_decompress + TurboQuantMSE.compress_decompress "
+                              f"+ scaled_dot_product_attention on {cores} threads, median {dt * 1e3:.0f} ms; step time "
+                              f"= slice x {L * B} (layers x batch)"}
+        except Exception:                                          # noqa: BLE001
+            pass
+    dt, sample = cpu_decode_sample(w)
+    pairs = L * B * w["n_kv"]
+    return {"value": B / (dt * pairs), "unit": "tok/s", "cores": 1, "kind": "port",
+            "sample": sample + f" (NumPy restatement, one thread); step time = sample x {pairs}"}
+
+
+def parity_check(mgr, w, qkv_step, t_before, outs):
+    """Outputs of one decode step of the timed path against the CPU oracle for three sampled (layer, batch,
+    KV head) pairs: attention output of the pair's query heads over the packed rows (and, with fp16
+    regions, the sink + recent tokens), and the packed row the step appended, against the oracle's encoder
+    (skipped for a row with a coordinate on a bin edge).  `qkv_step`: the step's (L, B, n_q + 2 n_kv, 1, hd)
+    inputs; `t_before`: tokens cached before the step."""
+    from helpers import oracle_meta
+    from oracle import bgtq_oracle as O
+    if outs is None:
+        return None
+    L, B, n_q, n_kv = w["layers"], w["batch"], w["n_q"], w["n_kv"]
+    gqa = n_q // n_kv
+    ns, win = mgr.n_sink, mgr.recent_window
+    picks = sorted({(0, 0, 0), (L - 1, B - 1, n_kv - 1), (L // 2, B // 2, n_kv // 2)})
+    max_abs, rows_checked, rows_equal = 0.0, 0, 0
+    for li, b, h in picks:
+        qz = mgr.quantizers[li][h]
+        meta = oracle_meta(qz._tables, qz._v_tables)
+        sl = slice(h * gqa, (h + 1) * gqa)
+        q = qkv_step[li, b, sl, 0].cpu().numpy()
+        qr = O.rotate_q(q, meta)
+        n_packed = t_before + 1 if not mgr._buffered else max(0, t_before - ns - win)
+        tb = qz._total_packed_bytes
+        if n_packed:
+            po, pl = O.attend_packed(qr, mgr._k_packed[li, b, h, :n_packed, :tb].cpu().numpy(),
+                                     mgr._k_norms[li, b, h, :n_packed].cpu().numpy(),
+                                     mgr._v_packed[li, b, h, :n_packed].cpu().numpy(),
+                                     mgr._v_norms[li, b, h, :n_packed].cpu().numpy(), meta, mgr.scale)
+        else:
+            po, pl = np.zeros((gqa, HD)), np.full(gqa, -np.inf)
+        ref = po
+        if mgr._buffered:
+            ring = win + 1
+            idx = list(range(min(ns, t_before + 1)))
+            idx += [ns + i % ring for i in range(n_packed, t_before + 1 - ns)]
+            kb = mgr._k_buf[li, b, h, idx].cpu().numpy()
+            vb = mgr._v_buf[li, b, h, idx].cpu().numpy()
+            bo, bl = O.attend_fp16(q, kb, vb, mgr.scale)
+            m = np.maximum(pl, bl)
+            wp, wb = np.exp(pl - m), np.exp(bl - m)
+            ref = (wp[:, None] * po + wb[:, None] * bo) / (wp + wb)[:, None]
+        got = outs[li][b, sl].float().cpu().numpy()
+        max_abs = max(max_abs, float(np.abs(got - ref).max()))
+        # the row appended by this step (unbuffered caches append at t_before; buffered ones flush token f)
+        row = t_before if not mgr._buffered else (n_packed if t_before - ns - win >= 0 else None)
+        if row is not None:
+            if mgr._buffered:
+                k_src = mgr._k_buf[li, b, h, ns + row % (win + 1)].cpu().numpy()[None]
+            else:
+                k_src = qkv_step[li, b, n_q + h, 0].cpu().numpy()[None]
+            enc = O.encode_k_packed(k_src, meta)
+            if not enc["fragile"].any():
+                rows_checked += 1
+                rows_equal += int(np.array_equal(mgr._k_packed[li, b, h, row, :tb].cpu().numpy(), enc["packed"][0]))
+    return {"pairs": len(picks), "max_abs": max_abs, "tolerance": 2e-3, "appended_rows_checked": rows_checked,
+            "appended_rows_bit_equal": rows_equal, "ok": bool(max_abs <= 2e-3 and rows_equal == rows_checked)}
+
+
+def workload_config(name, w, world):
+    """The workload keys both arms print, so that their `config` dicts compare equal on the shape."""
+    return {"workload": name, "layers": w["layers"], "batch_per_gpu": w["batch"], "n_q": w["n_q"], "n_kv": w["n_kv"],
+            "context": w["ctx"], "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"], "fp16_sink": w["n_sink"],
+            "fp16_window": w["window"], "parallelism": f"batch x{world}"}
+
+
+def run_triton(args, w, name):
+    """The reference's own Triton decode path on this GPU, through its stock classes: BlockGTQKVManager
+    calibrate -> _encode_kv -> append_and_attend (blockgtq/packed_kv_manager.py:85-348), on the same synthetic
+    keys/values and shapes, a few layers of the workload (calibration costs seconds per head there), timed the
+    way the reference times decode steps (bench/bench_decode_e2e.py:130-156: synchronise, perf_counter, 5
+    warm-up + 20 timed steps, median).  Nothing of this repository's package is imported."""
+    if _import_reference() is None:
+        print(json.dumps({"impl": "triton", "unavailable": "baseline/_ref/blockgtq is not present"}))
+        return
+    if w.get("mode") in ("encode", "prefill", "seq") or w["n_sink"] or w["window"]:
+        note = "the reference's packed path has no fp16 sink/window; timed without them" if w["n_sink"] else ""
+    else:
+        note = ""
+    try:
+        from blockgtq.packed_kv_manager import BlockGTQKVManager as RefManager
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        L = max(1, min(w["layers"], args.triton_layers))
+        n_q, n_kv, B, T = w["n_q"], w["n_kv"], w["batch"], w["ctx"]
+        gqa = n_q // n_kv
+        n_steps = args.warmup + args.steps
+        gen = torch.Generator(device=dev).manual_seed(1234)
+        mgr = RefManager(L, n_q, n_kv, HD, max_seq_len=T + n_steps + 8, batch_size=B, k_avg_bits=w["k_bits"],
+                         v_bits=w["v_bits"], device=dev)
+        for li in range(L):
+            ck = torch.stack([synth_keys(gen, (1, 2048), w["theta"], dev)[0] for _ in range(n_kv)])
+            cq = torch.stack([synth_keys(gen, (gqa, 2048), w["theta"], dev).reshape(-1, HD) for _ in range(n_kv)])
+            mgr.calibrate(li, cq.float(), ck.float())
+        for li in range(L):
+            for t in range(0, T, 4096):
+                n = min(4096, T - t)
+                k = torch.stack([synth_keys(gen, (B, n), w["theta"], dev) for _ in range(n_kv)], dim=1)
+                v = torch.randn(B, n_kv, n, HD, generator=gen, device=dev).half()
+                mgr._encode_kv(li, k, v, t, t + n)
+        mgr.seq_len = T
+        qs = (torch.randn(n_steps, L, B, n_q, 1, HD, generator=gen, device=dev) * 2).half()
+        ks = torch.stack([torch.stack([synth_keys(gen, (B * n_kv, 1), w["theta"], dev).reshape(B, n_kv, 1, HD)
+                                       for _ in range(L)]) for _ in range(n_steps)])
+        vs = torch.randn(n_steps, L, B, n_kv, 1, HD, generator=gen, device=dev).half()
+        times = []
+        for s in range(n_steps):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for li in range(L):
+                mgr.append_and_attend(li, qs[s, li], ks[s, li], vs[s, li])
+            mgr.increment_seq_len()
+            torch.cuda.synchronize()
+            if s >= args.warmup:
+                times.append((time.perf_counter() - t0) * 1e3)
+        # the decode kernels alone (attention over the cache, per layer): CUDA events around one more step's
+        # attention calls would need the reference's internals, so report the whole layer step
+        med = statistics.median(times)
+        line = {"impl": "triton", "metric": "decode_tokens_per_s", "unit": "tok/s", "n_gpus": 1,
+                "value": B / (med / L * w["layers"] * 1e-3), "steps": len(times), "warmup": args.warmup,
+                "ms_per_step": med / L * w["layers"], "higher_is_better": True, "scaling": "weak", "dtype": "f16",
+                "data": "synthetic", "config": workload_config(name, w, 1) | {
+                    "layers_timed": L, "ms_per_step_timed_layers": med, "us_per_layer_step": med / L * 1e3,
+                    "protocol": "reference BlockGTQKVManager.append_and_attend per layer, synchronise + perf_counter "
+                                "around each decode step, median; step of the full workload = timed layers scaled "
+                                f"by {w['layers']}/{L}", "note": note,
+                    "triton": __import__("triton").__version__}}
+    except Exception as e:                                         # noqa: BLE001
+        msg = f"{type(e).__name__}: {e}".splitlines()[0][:300]
+        line = {"impl": "triton", "unavailable": msg}
+    print(json.dumps(line), flush=True)
+
+
+def triton_leg(args, name):
+    """Run the Triton arm in a child process (its own CUDA context, none of this package loaded) and return
+    the summary the default line carries."""
+    if not os.path.isdir(os.path.join(REF_DIR, "blockgtq")):
+        return {"unavailable": "baseline/_ref/blockgtq is not present"}
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "triton", "--workload", name, "--steps", "20",
+           "--warmup", "5", "--triton-layers", str(args.triton_layers)]
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=args.triton_timeout)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"the reference's Triton path did not finish within {args.triton_timeout} s"}
+    for ln in reversed(out.stdout.splitlines()):
+        if ln.startswith("{"):
+            d = json.loads(ln)
+            if "unavailable" in d:
+                return {"unavailable": d["unavailable"]}
+            c = d["config"]
+            return {"ms_per_step": d["ms_per_step"], "tok_s": d["value"], "us_per_layer_step": c["us_per_layer_step"],
+                    "layers_timed": c["layers_timed"], "steps": d["steps"], "protocol": c["protocol"],
+                    "note": c["note"], "triton": c["triton"]}
+    return {"unavailable": ("no result line; stderr tail: " + out.stderr.strip().splitlines()[-1][:200])
+            if out.stderr.strip() else "no result line"}
 
 
 def run_seq_sharded(args, w, rank, world, dev):
@@ -523,8 +798,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "triton"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-triton", action="store_true", help="skip the reference-Triton leg of the default run")
+    ap.add_argument("--triton-layers", type=int, default=4, help="layers the reference-Triton leg builds and times")
+    ap.add_argument("--triton-timeout", type=int, default=420)
+    ap.add_argument("--no-parity-check", action="store_true")
     ap.add_argument("--per-layer-graphs", action="store_true",
                     help="replay one CUDA graph per layer (append_and_attend) instead of one graph per decode step")
     args = ap.parse_args()
@@ -536,6 +815,10 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, w, args.workload, rank, world)
+        return
+    if args.impl == "triton":
+        if rank == 0:
+            run_triton(args, w, args.workload)
         return
 
     if not torch.cuda.is_available():
@@ -649,34 +932,55 @@ def main():
     clocks = clocks_summary(sampler)
     live_bytes = mgr.live_bytes_per_step()
 
-    # per-launch duration of the dominant kernel (fused decode): the decode of every layer launched back to
-    # back on the current stream (each layer's cache is a different 60+ MB, so L2 never holds the next input),
-    # bracketed by CUDA events; the queue stays full, so the figure is kernel time, not host launch time
+    # per-launch duration of the dominant kernel (fused decode): the decode of every layer, launched as in the
+    # step (programmatic dependent launches, the manager's flags and slot count) back to back, captured in a
+    # CUDA graph so that no host launch time enters, and bracketed by CUDA events on the launching stream; each
+    # layer's cache is a different 60+ MB and a pass over all layers exceeds L2, so no launch finds its input
+    # in cache
     from blockgtq_b200.layer import decode as decode_op
     sink, n_packed, n_rec = mgr._region_sizes(mgr.seq_len)
     q_rot = torch.randn(B, n_q, HD, generator=gen, device=dev).half()
+    dflags = mgr._dec_flags | (_lib.DEC_PROGRAMMATIC if mgr.programmatic else 0)
 
     def decode_all_layers():
         for li in range(L):
             decode_op(mgr._layers[li], q_rot, mgr._k_packed[li], mgr._k_norms[li], mgr._v_packed[li],
                       mgr._v_norms[li], 0, n_packed, n_splits=mgr._n_splits, scale=mgr.scale,
-                      part_o=mgr._part_o, part_lse=mgr._part_lse)
+                      part_o=mgr._part_o, part_lse=mgr._part_lse, flags=dflags)
 
     decode_all_layers()
-    n_prof = 3
+    n_prof = max(3, min(20, 240 // L))
+    torch.cuda.synchronize()
+    dec_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(dec_graph):
+        decode_all_layers()
+    dec_graph.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(n_prof):
-        decode_all_layers()
+        dec_graph.replay()
     e1.record()
     torch.cuda.synchronize()
     dec_avg_ms = e0.elapsed_time(e1) / (n_prof * L)
+    del dec_graph
     packed_bytes_per_launch = (live_bytes - (sink + n_rec) * HD * 4 * n_kv * B * L) / L
 
     for _ in range(W):
         step_e2e()
     ms_e2e = timed(step_e2e, K)
+
+    parity = None
+    if rank == 0 and not args.no_parity_check:
+        # one more step of the timed path, then sampled (layer, batch, KV head) pairs of its outputs and of the
+        # rows it appended against the CPU oracle on the same packed cache
+        t_before = mgr.seq_len
+        s_idx = step_no[0]
+        step_device()
+        torch.cuda.synchronize()
+        mgr.check_status()
+        parity = parity_check(mgr, w, dqkv[s_idx], t_before,
+                              [mgr.static_outputs()[li] for li in range(L)] if graph_outputs else None)
 
     if rank == 0:
         peaks = {}
@@ -691,17 +995,17 @@ def main():
             "metric": "decode_tokens_per_s", "value": world * B / (ms_step * 1e-3), "unit": "tok/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": args.workload, "layers": L, "batch_per_gpu": B, "n_q": n_q, "n_kv": n_kv,
-                       "context": w["ctx"], "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"],
-                       "fp16_sink": w["n_sink"], "fp16_window": w["window"], "parallelism": f"batch x{world}",
+            "config": workload_config(args.workload, w, world) | {
                        "l2": "inputs larger than L2 (packed cache bytes per step >> 126 MB), no flush",
                        "graphs": "one per decode step" if step_graph is not None else
                                  ("one per layer" if graph_outputs else "none (eager launches)"),
                        "decode_us_per_layer": dec_avg_ms * 1e3, "step_hbm_gbs": live_bytes / (ms_step * 1e-3) / 1e9,
-                       "step_frac_of_8tbs": live_bytes / (ms_step * 1e-3) / 8e12},
+                       "step_frac_of_8tbs": live_bytes / (ms_step * 1e-3) / 8e12,
+                       "decode_kernel": "specialised per layer at run time (NVRTC)"
+                                        if not os.environ.get("BGTQ_DEC_NO_JIT") else "general (ahead of time)"},
             "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": DRAM_TRAFFIC_PER_LAUNCH.get(args.workload),
+                         "traffic": dram_traffic(args.workload),
                          "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback",
                          "algorithmic_bytes_per_launch": packed_bytes_per_launch, "launch_ms": dec_avg_ms},
             "e2e": {"value": world * B / (ms_e2e / K * 1e-3), "unit": "tok/s",
@@ -710,13 +1014,12 @@ def main():
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if parity is not None:
+            line["parity_check"] = parity
         if not args.no_cpu_baseline and world == 1:
-            cores = os.cpu_count() or 1
-            torch.set_num_threads(cores)
-            dt, sample = cpu_decode_sample(w)
-            pairs = L * B * n_kv
-            line["cpu_baseline"] = {"value": B / (dt * pairs), "unit": "tok/s", "cores": cores, "kind": "port",
-                                    "sample": sample + f"; step time = sample x {pairs}"}
+            line["cpu_baseline"] = cpu_baseline(w)
+        if not args.no_triton and world == 1:
+            line["config"]["reference_triton"] = triton_leg(args, args.workload)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
