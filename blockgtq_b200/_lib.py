@@ -58,20 +58,20 @@ _SIGNATURES = {
                               _vp, _i64, _i64, _i64, _i32,
                               _vp, _i64, _i64, _i64,
                               _vp, _i64, _i64, _i64,
-                              _vp, _vp, _i32, _vp, _vp]),
+                              _vp, _vp, _i32, _vp, _i32, _vp, _vp]),
     "bgtq_step_prepare_ring": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i32,
                                     _vp, _i64, _i64, _vp, _i64, _i64, _i32, _i32, _i32,
                                     _vp, _i64, _i64, _i64, _i32, _vp, _i64, _i64, _i64, _i32,
-                                    _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _vp,
+                                    _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _vp, _i32, _vp,
                                     _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "bgtq_step_prepare_rope": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i32,
                                     _vp, _i64, _i64, _vp, _i64, _i64, _i32, _i32, _i32,
                                     _vp, _i64, _i64, _i64, _i32, _vp, _i64, _i64, _i64, _i32,
-                                    _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _i64, _vp]),
+                                    _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _vp, _i32, _vp, _vp, _vp, _i64, _vp]),
     "bgtq_step_prepare": (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i32,
                                     _vp, _i64, _i64, _vp, _i64, _i64, _i32, _i32, _i32,
                                     _vp, _i64, _i64, _i64, _i32, _vp, _i64, _i64, _i64, _i32,
-                                    _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _vp, _vp]),
+                                    _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _vp, _i32, _vp, _vp]),
     "bgtq_rotate_q": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _vp, _i32, _i32, _i32, _vp]),
     "bgtq_decode_plan": (C.c_int, [_vp, _i32, _i32, _vp]),
     "bgtq_decode_default_splits": (C.c_int, [_i32, _i32, _i32]),

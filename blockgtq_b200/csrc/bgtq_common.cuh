@@ -21,6 +21,7 @@ constexpr int kHD = BGTQ_HEAD_DIM;
 
 // Error codes a kernel may leave in the caller's status word.
 constexpr int kStatusWaitTimeout = 1;
+constexpr int kStatusOverflow = 2;     // an append at a device-side position would leave the cache
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

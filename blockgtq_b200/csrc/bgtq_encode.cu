@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
     const int h = blockIdx.y;
     const bool is_v = blockIdx.z == 1;
     const int t0 = P.pos_dev ? *P.pos_dev : P.t0;   // first destination token slot
+    if (P.pos_dev && !enc_range_ok(P, t0, P.n_tok)) return;
     if (is_v ? (P.flags & BGTQ_ENC_SKIP_V) : (P.flags & BGTQ_ENC_SKIP_K)) return;
     const BgtqHeadDesc& d = P.desc[h];
     const int64_t n_rows = (int64_t)P.n_batch * P.n_tok;
@@ -344,6 +345,7 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     grid_launch_dependents();
     grid_dependency_wait();       // inputs and the slot position come from earlier work in the stream
     int t0 = E.pos_dev ? *E.pos_dev : E.t0;
+    if (E.pos_dev && kind != 0 && P.k_buf == nullptr && !enc_range_ok(E, t0, 1)) return;
     const __half* k_src = E.k + b * E.k_sb + h * E.k_sh;
     const __half* v_src = E.v + b * E.v_sb + h * E.v_sh;
     if (P.k_buf != nullptr && kind != 0) {
@@ -358,6 +360,7 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
         k_src = P.k_buf + b * P.kb_sb + h * P.kb_sh + slot * kHD;
         v_src = P.v_buf + b * P.kb_sb + h * P.kb_sh + slot * kHD;
         t0 = f0;
+        if (E.pos_dev && !enc_range_ok(E, t0, 1)) return;
     }
 
     float x = 0.f;
@@ -495,9 +498,10 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
                            int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count, uint8_t* v_packed,
                            int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
                            int64_t vn_st, uint8_t* k_codes, uint8_t* v_codes, int32_t flags, const int32_t* pos_dev,
-                           void* stream) {
+                           int32_t t_capacity, int32_t* status, void* stream) {
     const bool do_k = !(flags & BGTQ_ENC_SKIP_K), do_v = !(flags & BGTQ_ENC_SKIP_V);
-    if (!desc || n_batch < 1 || n_kv < 1 || n_tok < 0 || t0 < 0) return BGTQ_E_BADARG;
+    if (!desc || n_batch < 1 || n_kv < 1 || n_tok < 0 || t0 < 0 || t_capacity < 0) return BGTQ_E_BADARG;
+    if (!pos_dev && t_capacity > 0 && (int64_t)t0 + n_tok > t_capacity) return BGTQ_E_BADARG;
     if (do_k && (!rot_k || !k || !k_packed || !k_norms)) return BGTQ_E_BADARG;
     if (do_v && (!rot_v || !v || !v_packed || !v_norms)) return BGTQ_E_BADARG;
     if (do_k && (kp_row_bytes < 1 || kp_row_bytes > kHD || kn_count < 1 || kn_count > BGTQ_MAX_SEGMENTS))
@@ -512,7 +516,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
     P.kn = k_norms; P.kn_sb = kn_sb; P.kn_sh = kn_sh; P.kn_st = kn_st; P.kn_count = kn_count;
     P.vp = v_packed; P.vp_sb = vp_sb; P.vp_sh = vp_sh; P.vp_st = vp_st;
     P.vn = static_cast<__half*>(v_norms); P.vn_sb = vn_sb; P.vn_sh = vn_sh; P.vn_st = vn_st;
-    P.k_codes = k_codes; P.v_codes = v_codes; P.flags = flags;
+    P.k_codes = k_codes; P.v_codes = v_codes; P.flags = flags; P.capacity = t_capacity; P.status = status;
     const int64_t n_rows = (int64_t)n_batch * n_tok;
     {   // bulk row counts go to the tensor-core kernel when every input row is 16-byte aligned
         auto al16 = [](const void* ptr, int64_t a, int64_t b2, int64_t c) {
@@ -529,13 +533,10 @@ extern "C" __attribute__((visibility("default"))) int bgtq_encode(const BgtqHead
     if (gx > 0x7fffffffLL || n_kv > 65535) return BGTQ_E_TOOBIG;
     dim3 grid((unsigned)gx, n_kv, 2);
     constexpr int kWsmBytes = kHD * kHD * (int)sizeof(float);
-    static bool attr_set = false;   // same value every time; racing first calls are harmless
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(encode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsmBytes) != cudaSuccess) {
-            cudaGetLastError();
-            return BGTQ_E_LAUNCH;
-        }
-        attr_set = true;
+    // the attribute is per device: set it on every launch (cheap, and legal under stream capture)
+    if (cudaFuncSetAttribute(encode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsmBytes) != cudaSuccess) {
+        cudaGetLastError();
+        return BGTQ_E_LAUNCH;
     }
     encode_kernel<<<grid, 128, kWsmBytes, static_cast<cudaStream_t>(stream)>>>(P);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
@@ -547,13 +548,14 @@ static int step_prepare_impl(
     int32_t n_batch, int32_t n_kv, int32_t t0, uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
     int32_t kp_row_bytes, void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
     uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
-    int64_t vn_st, int32_t flags, const int32_t* pos_dev, void* stream, const void* rope_cos, const void* rope_sin,
-    int64_t rope_sb, void* k_buf = nullptr, void* v_buf = nullptr, int64_t kb_sb = 0, int64_t kb_sh = 0,
+    int64_t vn_st, int32_t flags, const int32_t* pos_dev, int32_t t_capacity, int32_t* status, void* stream,
+    const void* rope_cos, const void* rope_sin, int64_t rope_sb, void* k_buf = nullptr, void* v_buf = nullptr, int64_t kb_sb = 0, int64_t kb_sh = 0,
     int32_t n_sink = 0, int32_t window = 0) {
     if (!desc || !rot_k || !rot_v || !k || !v || !k_packed || !k_norms || !v_packed || !v_norms) return BGTQ_E_BADARG;
     if (n_batch < 1 || n_kv < 1 || t0 < 0 || kp_row_bytes < 1 || kp_row_bytes > kHD || kn_count < 1 ||
-        kn_count > BGTQ_MAX_SEGMENTS)
+        kn_count > BGTQ_MAX_SEGMENTS || t_capacity < 0)
         return BGTQ_E_BADARG;
+    if (!pos_dev && !k_buf && t_capacity > 0 && t0 >= t_capacity) return BGTQ_E_BADARG;
     const bool do_rot = q != nullptr && q_rot != nullptr;
     if (do_rot && (n_q < n_kv || n_q % n_kv)) return BGTQ_E_BADARG;
     PrepParams P;
@@ -566,7 +568,7 @@ static int step_prepare_impl(
     E.kn = k_norms; E.kn_sb = kn_sb; E.kn_sh = kn_sh; E.kn_st = kn_st; E.kn_count = kn_count;
     E.vp = v_packed; E.vp_sb = vp_sb; E.vp_sh = vp_sh; E.vp_st = vp_st;
     E.vn = static_cast<__half*>(v_norms); E.vn_sb = vn_sb; E.vn_sh = vn_sh; E.vn_st = vn_st;
-    E.k_codes = nullptr; E.v_codes = nullptr; E.flags = flags;
+    E.k_codes = nullptr; E.v_codes = nullptr; E.flags = flags; E.capacity = t_capacity; E.status = status;
     P.q = static_cast<const __half*>(q); P.q_sb = q_sb; P.q_sh = q_sh; P.q_rot = static_cast<__half*>(q_rot);
     P.n_q = n_q; P.do_rot = do_rot ? 1 : 0;
     P.rope_cos = static_cast<const __half*>(rope_cos); P.rope_sin = static_cast<const __half*>(rope_sin);
@@ -585,10 +587,10 @@ extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare(
     int32_t n_batch, int32_t n_kv, int32_t t0, uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
     int32_t kp_row_bytes, void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
     uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
-    int64_t vn_st, int32_t flags, const int32_t* pos_dev, void* stream) {
+    int64_t vn_st, int32_t flags, const int32_t* pos_dev, int32_t t_capacity, int32_t* status, void* stream) {
     return step_prepare_impl(desc, rot_k, rot_v, q, q_sb, q_sh, q_rot, n_q, k, k_sb, k_sh, v, v_sb, v_sh, n_batch, n_kv, t0, k_packed,
                              kp_sb, kp_sh, kp_st, kp_row_bytes, k_norms, kn_sb, kn_sh, kn_st, kn_count, v_packed, vp_sb, vp_sh,
-                             vp_st, v_norms, vn_sb, vn_sh, vn_st, flags, pos_dev, stream, nullptr, nullptr, 0);
+                             vp_st, v_norms, vn_sb, vn_sh, vn_st, flags, pos_dev, t_capacity, status, stream, nullptr, nullptr, 0);
 }
 
 extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare_rope(
@@ -597,11 +599,12 @@ extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare_rope(
     int32_t n_batch, int32_t n_kv, int32_t t0, uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
     int32_t kp_row_bytes, void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
     uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
-    int64_t vn_st, int32_t flags, const int32_t* pos_dev, const void* rope_cos, const void* rope_sin, int64_t rope_sb, void* stream) {
+    int64_t vn_st, int32_t flags, const int32_t* pos_dev, int32_t t_capacity, int32_t* status, const void* rope_cos,
+    const void* rope_sin, int64_t rope_sb, void* stream) {
     if (!rope_cos || !rope_sin) return BGTQ_E_BADARG;
     return step_prepare_impl(desc, rot_k, rot_v, q, q_sb, q_sh, q_rot, n_q, k, k_sb, k_sh, v, v_sb, v_sh, n_batch, n_kv, t0, k_packed,
                              kp_sb, kp_sh, kp_st, kp_row_bytes, k_norms, kn_sb, kn_sh, kn_st, kn_count, v_packed, vp_sb, vp_sh,
-                             vp_st, v_norms, vn_sb, vn_sh, vn_st, flags, pos_dev, stream, rope_cos, rope_sin, rope_sb);
+                             vp_st, v_norms, vn_sb, vn_sh, vn_st, flags, pos_dev, t_capacity, status, stream, rope_cos, rope_sin, rope_sb);
 }
 
 extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare_ring(
@@ -610,11 +613,12 @@ extern "C" __attribute__((visibility("default"))) int bgtq_step_prepare_ring(
     int32_t n_batch, int32_t n_kv, int32_t t0, uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
     int32_t kp_row_bytes, void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
     uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st, void* v_norms, int64_t vn_sb, int64_t vn_sh,
-    int64_t vn_st, int32_t flags, const int32_t* pos_dev, void* k_buf, void* v_buf, int64_t kb_sb, int64_t kb_sh, int32_t n_sink,
+    int64_t vn_st, int32_t flags, const int32_t* pos_dev, int32_t t_capacity, int32_t* status, void* k_buf, void* v_buf,
+    int64_t kb_sb, int64_t kb_sh, int32_t n_sink,
     int32_t window, void* stream) {
     if (!k_buf || !v_buf || n_sink < 0 || window < 1) return BGTQ_E_BADARG;
     return step_prepare_impl(desc, rot_k, rot_v, q, q_sb, q_sh, q_rot, n_q, k, k_sb, k_sh, v, v_sb, v_sh, n_batch, n_kv, t0, k_packed,
                              kp_sb, kp_sh, kp_st, kp_row_bytes, k_norms, kn_sb, kn_sh, kn_st, kn_count, v_packed, vp_sb, vp_sh,
-                             vp_st, v_norms, vn_sb, vn_sh, vn_st, flags, pos_dev, stream, nullptr, nullptr, 0, k_buf, v_buf, kb_sb, kb_sh,
+                             vp_st, v_norms, vn_sb, vn_sh, vn_st, flags, pos_dev, t_capacity, status, stream, nullptr, nullptr, 0, k_buf, v_buf, kb_sb, kb_sh,
                              n_sink, window);
 }

@@ -20,7 +20,19 @@ struct EncParams {
     uint8_t* k_codes;
     uint8_t* v_codes;
     int32_t flags;
+    int32_t capacity;   // token slots per (batch, head) in the destination arrays, 0 = unknown
+    int32_t* status;    // optional device word for kStatusOverflow
 };
+
+// With a device-side position the host cannot check the destination range: a launch whose rows would land
+// outside [0, capacity) stores nothing and reports it.  Uniform over the launch (every thread sees the same slot).
+__device__ __forceinline__ bool enc_range_ok(const EncParams& P, int t0, int n_tok) {
+    if (P.capacity > 0 && (t0 < 0 || t0 + n_tok > P.capacity)) {
+        if (P.status && threadIdx.x == 0) atomicExch(P.status, kStatusOverflow);
+        return false;
+    }
+    return true;
+}
 
 // Byte `t` of a bit-packed run: codes of width bw (1..4) starting at codes[0].
 __device__ __forceinline__ uint32_t enc_pack_byte(const uint8_t* codes, int n, int bw, int t) {

@@ -423,6 +423,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) encode_t5w_kernel(const EncPar
     WSmem& S = *reinterpret_cast<WSmem*>(smem_raw);
     const int h = blockIdx.y, tid = threadIdx.x;
     const bool is_v = blockIdx.z != 0 || (P.flags & BGTQ_ENC_SKIP_K);
+    // whole launch, before barriers or tensor memory exist
+    if (P.pos_dev && !enc_range_ok(P, *P.pos_dev, P.n_tok)) return;
     if (tid == 0) {
         mbar_init(&S.mma_bar[0], 1);
         mbar_init(&S.mma_bar[1], 1);
@@ -458,13 +460,10 @@ int launch_encode_t5w(const EncParams& P, cudaStream_t stream) {
     const int useful = (n_tiles + 1) / 2;       // a CTA works on two tiles at a time
     const int grid_x = per < useful ? per : useful;
     const int smem = (int)sizeof(WSmem);
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(encode_t5w_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
-            cudaGetLastError();
-            return BGTQ_E_LAUNCH;
-        }
-        attr_set = true;
+    // the attribute is per device: set it on every launch (cheap, and legal under stream capture)
+    if (cudaFuncSetAttribute(encode_t5w_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return BGTQ_E_LAUNCH;
     }
     encode_t5w_kernel<<<dim3(grid_x, P.n_kv, roles), kWarps * 32, smem, stream>>>(P);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;

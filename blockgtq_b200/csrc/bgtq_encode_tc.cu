@@ -401,6 +401,7 @@ __global__ void __launch_bounds__(kTcWarps * 32, 1) encode_tc_kernel(const EncPa
     extern __shared__ __align__(128) uint8_t smem_raw[];
     TcSmem& S = *reinterpret_cast<TcSmem*>(smem_raw);
     const int h = blockIdx.y;
+    if (P.pos_dev && !enc_range_ok(P, *P.pos_dev, P.n_tok)) return;      // whole launch, before any set-up
     if (n_k_ctas < 0) {      // bulk: every CTA takes its share of the K slabs, then of the V slabs
         if (!(P.flags & BGTQ_ENC_SKIP_K)) {
             tc_setup(S, P, P.desc[h], false, h);
@@ -442,13 +443,10 @@ int launch_encode_tc(const EncParams& P, cudaStream_t stream) {
     else if (do_k) { n_k = fill; grid_x = fill; }
     else { n_k = 0; grid_x = fill; }
     const int smem = (int)sizeof(TcSmem);
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
-            cudaGetLastError();
-            return BGTQ_E_LAUNCH;
-        }
-        attr_set = true;
+    // the attribute is per device: set it on every launch (cheap, and legal under stream capture)
+    if (cudaFuncSetAttribute(encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return BGTQ_E_LAUNCH;
     }
     encode_tc_kernel<<<dim3(grid_x, P.n_kv), kTcWarps * 32, smem, stream>>>(P, n_k);
     return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;

@@ -134,7 +134,7 @@ def _strides3(t: torch.Tensor):
 
 
 def encode(layer: LayerTables, k, v, t0, k_packed, k_norms, v_packed, v_norms, *, flags=0,
-           k_codes=None, v_codes=None, pos_dev=None):
+           k_codes=None, v_codes=None, pos_dev=None, status=None):
     """Encode ``k``/``v`` (B, n_kv, S, 128) fp16 into rows ``t0 .. t0+S`` of the cache tensors
     ``k_packed`` (B, n_kv, T, bytes) u8, ``k_norms`` (B, n_kv, T, groups) f16|f32,
     ``v_packed`` (B, n_kv, T, bytes) u8 and ``v_norms`` (B, n_kv, T) f16.  Either side may be None.
@@ -183,7 +183,9 @@ def encode(layer: LayerTables, k, v, t0, k_packed, k_norms, v_packed, v_norms, *
         _lib.ptr(k), *ks, _lib.ptr(v), *vs, B, H, S, int(t0),
         _lib.ptr(k_packed), *kps, kp_bytes, _lib.ptr(k_norms), *kns, kn_count,
         _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns,
-        _lib.ptr(k_codes), _lib.ptr(v_codes), flags, _lib.ptr(pos_dev), _lib.stream_ptr(ref.device)), "bgtq_encode")
+        _lib.ptr(k_codes), _lib.ptr(v_codes), flags, _lib.ptr(pos_dev),
+        int((k_packed if k is not None else v_packed).shape[2]), _lib.ptr(status),
+        _lib.stream_ptr(ref.device)), "bgtq_encode")
     _lib.count_launch()
 
 
@@ -218,7 +220,7 @@ def rotate_q_bulk(layer: LayerTables, q: torch.Tensor) -> torch.Tensor:
 
 
 def step_prepare(layer: LayerTables, q, k, v, t0, k_packed, k_norms, v_packed, v_norms, *, q_rot=None,
-                 flags=0, pos_dev=None, rope=None, ring=None):
+                 flags=0, pos_dev=None, rope=None, ring=None, status=None):
     """``ring=(k_buf, v_buf, n_sink, window)``: three-region mode (``bgtq_step_prepare_ring``), see bgtq.h.
     Rotate q (B, n_q, [1,] 128) into ``q_rot`` and append one token k/v (B, n_kv, 1, 128) at slot
     ``t0`` (or ``*pos_dev``) of the cache tensors, in one launch.  ``q=None`` skips the rotation.
@@ -249,7 +251,8 @@ def step_prepare(layer: LayerTables, q, k, v, t0, k_packed, k_norms, v_packed, v
               _lib.ptr(q_rot) if q is not None else 0, n_q,
               _lib.ptr(k), k.stride(0), k.stride(1), _lib.ptr(v), v.stride(0), v.stride(1), B, H, int(t0),
               _lib.ptr(k_packed), *kps, k_packed.shape[3], _lib.ptr(k_norms), *kns, k_norms.shape[3],
-              _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns, flags, _lib.ptr(pos_dev))
+              _lib.ptr(v_packed), *vps, _lib.ptr(v_norms), *vns, flags, _lib.ptr(pos_dev),
+              int(k_packed.shape[2]), _lib.ptr(status))
     if ring is not None:
         if rope is not None:
             raise NotImplementedError("fused RoPE and the three-region mode cannot be combined")

@@ -280,12 +280,14 @@ class BlockGTQKVManager:
         # the one before it drains, and waits on the device before touching the step's data
         pd = self.programmatic
         ex = self._exchange
-        q_rot = gq[:, :, 0].contiguous() if baked else self._q_rot
+        q_rot = self._q_rot
+        if baked:                   # queries arrive in the packed-K basis already: stage them without allocating
+            self._q_rot.copy_(gq[:, :, 0])
         if self._buffered:          # three regions, everything derived from the device-side token count
             ns, win = self.n_sink, self.recent_window
             step_prepare(lt, None if baked else gq, gk, gv, 0, self._k_packed[li], self._k_norms[li],
                          self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos,
-                         flags=self._enc_flags | (_lib.ENC_PROGRAMMATIC if pd else 0),
+                         flags=self._enc_flags | (_lib.ENC_PROGRAMMATIC if pd else 0), status=self._status,
                          ring=(self._k_buf[li], self._v_buf[li], ns, win))
             decode(lt, q_rot, self._k_packed[li], self._k_norms[li], self._v_packed[li], self._v_norms[li],
                    0, self.max_T, n_splits=self._n_splits, scale=self.scale, status=self._status,
@@ -299,7 +301,7 @@ class BlockGTQKVManager:
         if ex is None or ex.is_owner:
             step_prepare(lt, None if baked else gq, gk, gv, 0, self._k_packed[li], self._k_norms[li],
                          self._v_packed[li], self._v_norms[li], q_rot=self._q_rot, pos_dev=self._pos,
-                         flags=self._enc_flags | (_lib.ENC_PROGRAMMATIC if pd else 0),
+                         flags=self._enc_flags | (_lib.ENC_PROGRAMMATIC if pd else 0), status=self._status,
                          rope=(self._g_rope[0], self._g_rope[1]) if rope else None)
         elif not baked:                           # this rank does not hold the tail: nothing to append
             rotate_q(lt, gq[:, :, 0], out=self._q_rot)
@@ -321,8 +323,13 @@ class BlockGTQKVManager:
         current stream: no allocation, no synchronisation, position read on the device.  This is the form to
         call inside a caller's own CUDA-graph capture of a whole decode step (a serving engine capturing its
         model forward); :meth:`append_and_attend` wraps the same launches in one graph per layer.  Call
-        :meth:`increment_seq_len` once per step, outside the captured region or after the replay."""
+        :meth:`increment_seq_len` once per step, outside the captured region or after the replay.
+
+        The host-side length is checked here; a captured step replayed past the capacity is caught on the
+        device instead (the append kernel stores nothing and :meth:`check_status` raises)."""
         self._ensure_storage()
+        if self._seq_len + 1 > self.max_T and (self._exchange is None or self._exchange.is_owner):
+            raise ValueError("cache overflow")
         self._sync_pos()
         self._layer_step(layer_idx, rope)
 
@@ -427,9 +434,15 @@ class BlockGTQKVManager:
         self._graphs = [dict() for _ in range(self.n_layers)]
 
     def check_status(self):
-        """Synchronise and raise if a kernel reported a timed-out wait."""
+        """Synchronise and raise if a kernel reported a timed-out wait (1: the outputs of that launch are
+        invalid) or an append past the end of the cache (2: nothing was stored).  Covers the decode / append
+        status word and the bulk tcgen05 encoder's own sticky status."""
         if self._status is not None and int(self._status.item()) != 0:
-            raise RuntimeError(f"decode kernel reported status {int(self._status.item())}")
+            code = int(self._status.item())
+            what = {1: "a bounded wait inside a kernel gave up", 2: "an append past the end of the cache was refused"}
+            raise RuntimeError(f"kernel status {code}: {what.get(code, 'unknown')}")
+        if self.device.type == "cuda" and _lib.lib().bgtq_encode_tcgen05_status() != 0:
+            raise RuntimeError("the tcgen05 bulk encoder reported a timed-out wait: the rows of that launch are incomplete")
 
     def bake_q_permutations(self, model, n_kv_heads: int, n_q_heads: int):
         """Bake each head's permutation + rotation into q_proj (packed_kv_manager.py:354-373)."""

@@ -121,6 +121,12 @@ const char* bgtq_error_string(int code);       /* host pointer to a static strin
  * pos_dev: optional device int32; when non-NULL the first destination slot is
  * *pos_dev instead of t0, read when the kernel runs (lets a captured CUDA graph
  * append at a position that advances between replays).
+ * t_capacity: token slots every (b,h) has in the destination arrays (0 = not
+ * checked).  With t0 given on the host a range that leaves it is refused with
+ * BGTQ_E_BADARG; with pos_dev the kernel checks: a launch whose rows would land
+ * outside [0, t_capacity) stores NOTHING and sets *status (optional device
+ * int32) to 2, so a step replayed past the end of the cache cannot overwrite
+ * its neighbours.
  */
 int bgtq_encode(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v,
                 const void* k, int64_t k_sb, int64_t k_sh, int64_t k_ss,
@@ -131,7 +137,7 @@ int bgtq_encode(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v
                 uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
                 void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
                 uint8_t* k_codes, uint8_t* v_codes,
-                int32_t flags, const int32_t* pos_dev, void* stream);
+                int32_t flags, const int32_t* pos_dev, int32_t t_capacity, int32_t* status, void* stream);
 
 /* Sticky device-side status of the tcgen05 bulk encoder on the current device: 0, or 1 after a wait for
  * the tensor cores ran out (the rows of that launch are then incomplete).  Synchronises the device. */
@@ -155,7 +161,9 @@ int bgtq_rotate_q(const BgtqHeadDesc* desc, const float* rot_k,
  * and step, the n_kv rotate_q_for_packed_kernel calls and the CUDA-graphed T=1
  * encode of the reference (blockgtq/packed_kv_manager.py:221-257, 318-329).
  * The rotation sums are formed in a different order than in bgtq_encode, so a
- * coordinate sitting exactly on a bin edge may land on the neighbouring code. */
+ * coordinate sitting exactly on a bin edge may land on the neighbouring code.
+ * t_capacity / status: as for bgtq_encode (the query rotation still runs when
+ * the append is refused). */
 int bgtq_step_prepare(const BgtqHeadDesc* desc, const float* rot_k, const float* rot_v,
                       const void* q, int64_t q_sb, int64_t q_sh, void* q_rot, int32_t n_q,
                       const void* k, int64_t k_sb, int64_t k_sh,
@@ -165,7 +173,7 @@ int bgtq_step_prepare(const BgtqHeadDesc* desc, const float* rot_k, const float*
                       void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
                       uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
                       void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
-                      int32_t flags, const int32_t* pos_dev, void* stream);
+                      int32_t flags, const int32_t* pos_dev, int32_t t_capacity, int32_t* status, void* stream);
 
 /* bgtq_step_prepare for queries and keys that have NOT been through the rotary embedding yet: the kernel
  * applies it first, x' = x*cos + rotate_half(x)*sin in the split-half convention (dims d and d+64 form a
@@ -183,7 +191,7 @@ int bgtq_step_prepare_rope(const BgtqHeadDesc* desc, const float* rot_k, const f
                       void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
                       uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
                       void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
-                      int32_t flags, const int32_t* pos_dev,
+                      int32_t flags, const int32_t* pos_dev, int32_t t_capacity, int32_t* status,
                       const void* rope_cos, const void* rope_sin, int64_t rope_sb, void* stream);
 
 /* bgtq_step_prepare for the three-region cache policy (fp16 sink + packed middle + fp16 recent window,
@@ -202,7 +210,7 @@ int bgtq_step_prepare_ring(const BgtqHeadDesc* desc, const float* rot_k, const f
                       void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st, int32_t kn_count,
                       uint8_t* v_packed, int64_t vp_sb, int64_t vp_sh, int64_t vp_st,
                       void* v_norms, int64_t vn_sb, int64_t vn_sh, int64_t vn_st,
-                      int32_t flags, const int32_t* pos_dev,
+                      int32_t flags, const int32_t* pos_dev, int32_t t_capacity, int32_t* status,
                       void* k_buf, void* v_buf, int64_t kb_sb, int64_t kb_sh, int32_t n_sink, int32_t window,
                       void* stream);
 

@@ -106,7 +106,12 @@ def test_entry_points_reject_bad_arguments_without_a_gpu():
     dummy = (C.c_float * 4)()           # never dereferenced: the stride check fails first
     assert L.bgtq_combine_ranks(C.addressof(dummy), 2, 8 * 128, 1, 8, C.addressof(dummy), 0, 0, 0, None) == -1
     assert L.bgtq_encode(None, None, None, None, 0, 0, 0, None, 0, 0, 0, 1, 2, 1, 0, None, 0, 0, 0, 8,
-                         None, 0, 0, 0, 1, None, 0, 0, 0, None, 0, 0, 0, None, None, 0, None, None) == -1
+                         None, 0, 0, 0, 1, None, 0, 0, 0, None, 0, 0, 0, None, None, 0, None, 0, None, None) == -1
+    # a destination range given on the host that leaves the cache is refused before anything is dereferenced
+    d = (C.c_float * 4)()
+    p = C.addressof(d)
+    assert L.bgtq_encode(p, p, p, p, 0, 0, 0, p, 0, 0, 0, 1, 2, 4, 61, p, 0, 0, 0, 8,
+                         p, 0, 0, 0, 1, p, 0, 0, 0, p, 0, 0, 0, None, None, 0, None, 64, None, None) == -1
     # fp16-region attention: key/value buffers must be 16-byte aligned with strides in multiples of 8 elements
     buf = (C.c_float * 64)()
     a = C.addressof(buf)

@@ -93,3 +93,42 @@ def test_layer_major_prefill_then_decode_tracks_the_fp16_model():
         logits = production_decode_step(model, ids[:, t:t + 1], torch.tensor([[t]], device=DEV), cache)
         cos = torch.nn.functional.cosine_similarity(logits[:, 0].float(), full[:, t].float()).item()
         assert cos >= 0.985, (t, cos)
+
+
+def test_captured_step_replayed_past_the_capacity_stores_nothing():
+    """A step captured in the caller's own graph reads its position on the device; replaying it once more than
+    the cache has room for must not write anywhere: the append kernel reports status 2 and stores nothing (the
+    first row of the next (batch, head) pair, which an unchecked append would hit, stays as it was)."""
+    import torch
+    from blockgtq_b200 import BlockGTQKVManager
+    from helpers import HD, synth_head
+    dev = "cuda:0"
+    gen = torch.Generator().manual_seed(5)
+    B, n_kv, gqa, cap = 2, 2, 2, 64            # 64 = the allocation's own granularity: no spare rows behind max_T
+    n_q = n_kv * gqa
+    mgr = BlockGTQKVManager(1, n_q, n_kv, HD, max_seq_len=cap, batch_size=B, device=dev)
+    cal = [synth_head(gen, 256, gqa) for _ in range(n_kv)]
+    mgr.calibrate(0, torch.stack([c[0] for c in cal]).float(), torch.stack([c[1] for c in cal]).float())
+    k0 = torch.randn(B, n_kv, cap - 1, HD, generator=gen).half().to(dev)
+    mgr._encode_kv(0, k0, k0.clone(), 0, cap - 1)
+    mgr.seq_len = cap - 1
+    gq, gk, gv = mgr.static_inputs(0)
+    gq.copy_(torch.randn(gq.shape, generator=gen).half())
+    gk.copy_(torch.randn(gk.shape, generator=gen).half())
+    gv.copy_(torch.randn(gv.shape, generator=gen).half())
+    mgr.layer_step(0)                          # fills the last slot (eager, sets kernel attributes)
+    mgr.increment_seq_len()
+    torch.cuda.synchronize()
+    mgr.check_status()
+    with pytest.raises(ValueError):
+        mgr.layer_step(0)                      # the host-side check
+    # the device-side check: launch the step kernels with the position one past the end, as a replayed graph would
+    snap = [t.clone() for t in (mgr._k_packed, mgr._k_norms, mgr._v_packed, mgr._v_norms)]
+    mgr._sync_pos()
+    mgr._layer_step(0)
+    torch.cuda.synchronize()
+    for a, b in zip(snap, (mgr._k_packed, mgr._k_norms, mgr._v_packed, mgr._v_norms)):
+        assert torch.equal(a, b)
+    assert int(mgr._status.item()) == 2
+    with pytest.raises(RuntimeError):
+        mgr.check_status()
