@@ -243,8 +243,16 @@ class BlockGTQQuantizer:
     @torch.no_grad()
     def bake_permutation_into_qproj(self, q_proj_weight, kv_head_idx: int, n_kv_heads: int, n_q_heads: int,
                                     q_proj_bias: Optional[torch.Tensor] = None) -> None:
-        """Fold permutation + rotation into the q_proj rows of this KV head's query group,
-        in place: W <- (R^T @ W[head_perm])[pack_perm] (quantizer.py:1189-1243)."""
+        """Fold permutation + rotation into the q_proj rows of this KV head's query group, in place, so
+        that the projection's output already is ``rotate_q_for_packed_kernel`` of the original output and
+        the decode step can skip the rotation (quantizer.py:1189-1243).
+
+        With ``rot_T = block_rot_T`` the rotation of a query row is ``q[head_perm] @ rot_T``, i.e. the
+        baked weight is ``(rot_T.T @ W[head_perm])[pack_perm]``.  The reference's function multiplies by
+        ``rot_T`` itself (quantizer.py:1232), which equals the rotation only for a symmetric matrix: on
+        random data its baked projection differs from its own ``rotate_q_for_packed_kernel`` by more than
+        the values themselves.  This implementation follows the documented intent, and a test holds it to
+        the rotation."""
         assert self._calibrated and kv_head_idx < n_kv_heads
         hd, gqa = self.head_dim, n_q_heads // n_kv_heads
         assert q_proj_weight.shape[0] == n_q_heads * hd
@@ -254,10 +262,10 @@ class BlockGTQQuantizer:
         for g in range(gqa):
             s = (kv_head_idx * gqa + g) * hd
             w = q_proj_weight[s:s + hd].detach().clone().cpu()[hp].float()
-            q_proj_weight[s:s + hd] = (rt @ w).to(q_proj_weight.dtype)[pp].to(q_proj_weight.device)
+            q_proj_weight[s:s + hd] = (rt.T @ w).to(q_proj_weight.dtype)[pp].to(q_proj_weight.device)
             if q_proj_bias is not None:
                 bv = q_proj_bias[s:s + hd].detach().clone().cpu()[hp].float()
-                q_proj_bias[s:s + hd] = (rt @ bv.unsqueeze(1)).squeeze(1)[pp].to(q_proj_bias.dtype).to(
+                q_proj_bias[s:s + hd] = (rt.T @ bv.unsqueeze(1)).squeeze(1)[pp].to(q_proj_bias.dtype).to(
                     q_proj_bias.device)
         self._q_perm_baked = True
 
@@ -286,8 +294,41 @@ def build_batched_encode_args(quantizers: list, device="cuda") -> dict:
     def mx(bw):
         return max((pm[bw]["length"] if bw in pm else 0) for pm in pms)
 
+    # Tables the reference's Triton kernels index directly (quantizer.py:1722-1730).  The CUDA kernels read the
+    # same values from the uploaded head descriptors; the stacks are kept for callers that inspect them.
+    dev = torch.device(device)
+    max_ncb = max(q._n_codebooks for q in quantizers)
+    max_ng = max(q._n_groups for q in quantizers)
+    clut_stride = q0._code_lut.stride(0)
+    clut = torch.zeros(n_kv, max_ncb, clut_stride, dtype=q0._code_lut.dtype, device=dev)
+    max_nc = max(q._pos_centroids.shape[1] for q in quantizers)
+    pos_cents = torch.zeros(n_kv, hd, max_nc, dtype=torch.float32, device=dev)
+    grp = torch.zeros(n_kv, hd, dtype=torch.long, device=dev)
+    gmask = torch.zeros(n_kv, max_ng, hd, dtype=torch.float32, device=dev)
+    pack_params = torch.zeros(n_kv, 16, dtype=torch.int32, device=dev)
+    for i, q in enumerate(quantizers):
+        clut[i, :q._n_codebooks] = q._code_lut.to(dev)
+        pos_cents[i, :, :q._pos_centroids.shape[1]] = q._pos_centroids.to(dev)
+        if q._group_of is not None:
+            grp[i] = q._group_of.to(dev)
+        ipp = q._inv_pack_perm.to(dev)
+        for g in range(q._n_groups):
+            in_g = (q._group_of.to(dev) == g) if q._group_of is not None else torch.ones(hd, dtype=torch.bool, device=dev)
+            gmask[i, g] = in_g[ipp].float()
+        m = q._pack_meta
+        row = []
+        for bw in (1, 2, 3, 4):
+            row += [m[bw]["start"], m[bw]["length"], m[bw]["pack_offset"]] if bw in m else [0, 0, 0]
+        row += [m["nopack_start"], m["nopack_len"], m["nopack_off"], q._n_groups]
+        pack_params[i] = torch.tensor(row, dtype=torch.int32)
+
     return {
         "_layer": lt,
+        "k_clut_stack": clut, "k_pos_cents_stack": pos_cents,
+        "k_ptcb_stack": torch.stack([q._pos_to_cb.to(dev) for q in quantizers]),
+        "k_loff_stack": torch.stack([q._lut_offsets.to(dev) for q in quantizers]),
+        "k_linv_stack": torch.stack([q._lut_inv_scales.to(dev) for q in quantizers]),
+        "k_grp_stack": grp, "k_group_mask_stack": gmask, "k_pack_params": pack_params, "k_clut_stride": clut_stride,
         "v_rot_T_stack": lt.rot_v, "v_bound_stack": torch.stack([q._v_boundaries for q in quantizers]),
         "v_cent_stack": torch.stack([q._v_centroids_f32 for q in quantizers]),
         "v_bits": lt.v_bits, "v_n_cents": 1 << lt.v_bits, "v_packed_bytes": lt.vpb, "v_nibble_bytes": hd // 2,

@@ -18,6 +18,7 @@ Fixtures
   decode_<case>.npz   packed cache + query -> attention output and LSE per KV head
   prefill.npz         packed cache + 24 queries at positions 40..63 -> causal prefill attention output
   manager.npz         BlockGTQKVManager: bulk encode + two append_and_attend steps, batch 2
+  buffer_policy.npz   the reference's fp16 sink / recent-window flush policy, recorded from its own hook
   shape_<name>.npz    layer-shaped cases (8 KV heads, thousands of tokens): per-head bit maps, the packed cache
                       of every head and the decode output for one query past the end; the fp16 K/V inputs
                       are not stored but regenerated from the seed by ``helpers.synth_layer_case``
@@ -394,8 +395,47 @@ def dump_shape_case(name):
         out=torch.cat(outs, dim=1).numpy(), lse=torch.cat(lses, dim=1).numpy(), t_splits=np.array(t_splits))
 
 
+BUFFER_SETTINGS = [(4, 128, 1), (0, 16, 1), (4, 32, 8), (2, 0, 4)]     # (n_sink, recent_window, block_size)
+
+
+def dump_buffer_policy(n_steps=300, prefill=37):
+    """The three-region flush policy as the reference executes it: its _BufferedKVPatch hook
+    (blockgtq/unaccelerated.py:163-244) is driven with a stub model and a fake ``past_key_values`` whose
+    caches grow by a prefill and then one token per forward; ``_flush`` is replaced by a recorder.  Stored per
+    setting: the sequence length after every forward, the packed-token count (n_flushed) after it, and every
+    (start, end) flush call."""
+    import types
+    from blockgtq.unaccelerated import _BufferedKVPatch
+    rec = {"settings": np.array(BUFFER_SETTINGS, dtype=np.int64)}
+    for si, (n_sink, window, bs) in enumerate(BUFFER_SETTINGS):
+        stub = torch.nn.Identity()
+        patch = _BufferedKVPatch(stub, None, None, HD, 1, 1, block_size=bs, recent_window=window, n_sink_token=n_sink)
+        calls = []
+        patch._flush = lambda k, v, li, start, end, calls=calls: calls.append((start, end))
+        seqs, flushed, call_step = [], [], []
+        seq = 0
+        for step in range(n_steps):
+            seq += prefill if step == 0 else 1
+            pkv = types.SimpleNamespace(key_cache=[torch.zeros(1, 1, seq, HD)], value_cache=[torch.zeros(1, 1, seq, HD)])
+            n_before = len(calls)
+            patch._hook_fn(stub, (), {"past_key_values": pkv}, None)
+            seqs.append(seq)
+            flushed.append(patch.state[0]["n_flushed"])
+            call_step += [step] * (len(calls) - n_before)
+        patch.remove()
+        rec[f"s{si}_seq"] = np.array(seqs, dtype=np.int64)
+        rec[f"s{si}_n_flushed"] = np.array(flushed, dtype=np.int64)
+        rec[f"s{si}_flush_calls"] = np.array(calls, dtype=np.int64).reshape(-1, 2)
+        rec[f"s{si}_flush_step"] = np.array(call_step, dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "buffer_policy.npz"), **rec)
+
+
 def main():
     only = sys.argv[2] if len(sys.argv) > 2 else None
+    if only == "buffer_policy":
+        dump_buffer_policy()
+        print("done buffer_policy")
+        return
     if only in SHAPE_CASES:
         dump_shape_case(only)
         print("done", only)

@@ -178,3 +178,85 @@ def test_default_split_counts_for_the_benchmark_shapes():
     assert L.bgtq_decode_default_splits(1, 1, 100) == 4 and L.bgtq_decode_default_splits(64, 8, 1024) == 2
     assert L.bgtq_decode_default_splits(1, 1, 0) == 1 and L.bgtq_decode_default_splits(4, 2, 32) == 1
     assert L.bgtq_decode_default_splits(1, 1, 1 << 20) == 256     # capped: 128-unit items
+
+
+def test_baked_q_projection_reproduces_the_query_rotation():
+    """bake_permutation_into_qproj folds head permutation + rotation into q_proj: projecting with the baked
+    weight (and bias) must give what rotating the original projection's output gives (the oracle's rotate_q,
+    itself pinned on the reference's rotate_q_for_packed_kernel by the decode goldens' q_rot)."""
+    from blockgtq_b200 import BlockGTQQuantizer
+    from oracle import bgtq_oracle as O
+    from helpers import oracle_meta
+    gt = load("tables_a3_1to8")
+    gen = torch.Generator().manual_seed(3)
+    n_kv, gqa = 2, 2
+    qs = []
+    for h in range(n_kv):
+        z = BlockGTQQuantizer(HD, avg_bits=3.0, device="cpu")
+        z.calibrate(None, None, bit_allocation=torch.from_numpy(gt[f"h{h}_alloc"]))
+        z.init_v_quantizer(v_bits=3, seed=42 + h)
+        qs.append(z)
+    W = torch.randn(n_kv * gqa * HD, 96, generator=gen)
+    bias = torch.randn(n_kv * gqa * HD, generator=gen)
+    x = torch.randn(7, 96, generator=gen)
+    q_plain = (x @ W.T + bias).reshape(7, n_kv * gqa, HD)
+    Wb, bb = W.clone(), bias.clone()
+    for h in range(n_kv):
+        assert not qs[h]._q_perm_baked
+        qs[h].bake_permutation_into_qproj(Wb, kv_head_idx=h, n_kv_heads=n_kv, n_q_heads=n_kv * gqa, q_proj_bias=bb)
+        assert qs[h]._q_perm_baked
+    q_baked = (x @ Wb.T + bb).reshape(7, n_kv * gqa, HD)
+    for h in range(n_kv):
+        meta = oracle_meta(qs[h]._tables, qs[h]._v_tables)
+        sl = slice(h * gqa, (h + 1) * gqa)
+        want = q_plain[:, sl].reshape(-1, HD).double().numpy()[:, meta["head_perm"]] @ meta["rot_t"].astype(np.float64)
+        got = q_baked[:, sl].reshape(-1, HD).double().numpy()
+        assert np.abs(got - want).max() <= 1e-4 * np.abs(want).max()
+        # and the fp16 rotation the decode kernels consume agrees with the oracle's fp16 rotate_q to an ulp
+        r16 = O.rotate_q(q_plain[:, sl].reshape(-1, HD).half().numpy(), meta).astype(np.float32)
+        assert np.abs(r16 - want).max() <= 4e-3 * np.abs(want).max()
+
+
+def test_bake_helpers_rewrite_every_layers_q_proj():
+    """BlockGTQKVManager.bake_q_permutations and calibration.bake_q_rotations walk the model's layers and
+    fold each KV head's permutation + rotation into the q_proj rows of its query group (weights and flags
+    checked against the per-head formula).  Note: with rotary embeddings applied AFTER q_proj the baked
+    projection is not equivalent to rotating the post-RoPE query (the block rotation mixes dims of different
+    RoPE blocks); the reference has the same limitation and leaves a TODO in its decode path
+    (blockgtq/packed_kv_manager.py:318-322), so no model-level equivalence is claimed."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from blockgtq_b200 import BlockGTQKVManager
+    from blockgtq_b200.calibration import bake_q_rotations
+    from helpers import synth_head
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                      num_hidden_layers=2, intermediate_size=128, vocab_size=64, max_position_embeddings=128)
+    model = LlamaForCausalLM(cfg).eval()
+    L, nq, nkv = 2, 4, 2
+    gen = torch.Generator().manual_seed(11)
+    mgr = BlockGTQKVManager(L, nq, nkv, HD, max_seq_len=64, batch_size=1, device="cpu")
+    for li in range(L):
+        cal = [synth_head(gen, 128, nq // nkv) for _ in range(nkv)]
+        mgr.calibrate(li, torch.stack([c[0] for c in cal]).float(), torch.stack([c[1] for c in cal]).float())
+    before = [model.model.layers[li].self_attn.q_proj.weight.data.clone() for li in range(L)]
+    twin = LlamaForCausalLM(cfg).eval()
+    twin.load_state_dict(model.state_dict())
+    mgr.bake_q_permutations(model, nkv, nq)
+    for li in range(L):
+        w = model.model.layers[li].self_attn.q_proj.weight.data
+        for h in range(nkv):
+            z = mgr.quantizers[li][h]
+            assert z._q_perm_baked
+            for g in range(nq // nkv):
+                s = (h * (nq // nkv) + g) * HD
+                want = (z._block_rot_T.float().T @ before[li][s:s + HD][z._head_perm].float())[z._pack_perm]
+                assert torch.allclose(w[s:s + HD], want.to(w.dtype), atol=1e-5, rtol=1e-4)
+    # the calibration-module helper does the same walk
+    for row in mgr.quantizers:
+        for z in row:
+            z._q_perm_baked = False
+    bake_q_rotations(twin, mgr.quantizers, L, nkv, nq)
+    for li in range(L):
+        assert torch.equal(twin.model.layers[li].self_attn.q_proj.weight.data,
+                           model.model.layers[li].self_attn.q_proj.weight.data)
+    assert all(z._q_perm_baked for row in mgr.quantizers for z in row)

@@ -87,15 +87,28 @@ def test_combine_handles_empty_splits():
     np.testing.assert_allclose(out[0], (w[0] * po[0, 0] + w[1] * po[2, 0]) / w.sum())
 
 
-def test_three_region_plan_matches_flush_loop():
-    """Closed form vs the literal loop of unaccelerated.py:226-233."""
-    for n_sink, window, bs in [(4, 128, 1), (0, 16, 4), (3, 0, 1), (2, 5, 3)]:
-        flushed = 0
-        for seq in range(0, 300):
+def test_three_region_policy_matches_the_reference_hook():
+    """The packed / fp16 split of the three-region cache against the reference's own policy, recorded by
+    driving its _BufferedKVPatch hook (tests/golden/buffer_policy.npz: a 37-token prefill, then one token per
+    forward, four (sink, window, block) settings): the oracle's closed form, the manager's bookkeeping, and the
+    (start, end) ranges the manager would flush must all agree with what the hook did."""
+    from blockgtq_b200 import BlockGTQKVManager
+    g = load("buffer_policy")
+    for si, (n_sink, window, bs) in enumerate(g["settings"].tolist()):
+        mgr = BlockGTQKVManager(1, 2, 1, HD, max_seq_len=512, device="cpu", n_sink=n_sink, recent_window=window,
+                                block_size=bs, use_cuda_graph=False)
+        seqs, flushed = g[f"s{si}_seq"], g[f"s{si}_n_flushed"]
+        calls, call_step = g[f"s{si}_flush_calls"], g[f"s{si}_flush_step"]
+        prev = 0
+        for step, (seq, nf) in enumerate(zip(seqs.tolist(), flushed.tolist())):
             avail = max(0, seq - n_sink)
-            while avail - flushed >= bs + window:
-                flushed += bs
-            assert O.three_region_plan(seq, n_sink, window, bs) == (min(seq, n_sink), flushed, avail - flushed)
+            assert O.three_region_plan(seq, n_sink, window, bs) == (min(seq, n_sink), nf, avail - nf)
+            assert mgr._region_sizes(seq) == (min(seq, n_sink), nf, avail - nf)
+            assert mgr._flushed(avail) == nf
+            # the hook's flush calls of this forward tile [n_sink + prev, n_sink + nf) in block_size pieces
+            mine = [(n_sink + f, n_sink + f + bs) for f in range(prev, nf, bs)]
+            assert calls[call_step == step].tolist() == [list(c) for c in mine]
+            prev = nf
 
 
 def test_oracle_prefill_attention_vs_reference_golden():
