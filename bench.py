@@ -472,7 +472,7 @@ def triton_leg(args, name):
             if out.stderr.strip() else "no result line"}
 
 
-def run_seq_sharded(args, w, rank, world, dev):
+def run_seq_sharded(args, w, rank, world, dev, emit=True, shard=True):
     """One long sequence cut into per-rank chunks: per layer the local split-KV decode + combine, one
     exchange of the (O, LSE) messages and the merge of the ranks' messages; the rank that owns the tail also
     appends the step's token; all layers of a step are one CUDA graph.  Strong scaling: the total context is
@@ -484,12 +484,13 @@ def run_seq_sharded(args, w, rank, world, dev):
     K, W = args.steps, args.warmup
     n_total = 2 * (K + W) + 4
     L, B, n_q, n_kv, T = w["layers"], w["batch"], w["n_q"], w["n_kv"], w["ctx"]
-    lo, hi = chunk_bounds(T, world, rank)
+    sharded = shard and world > 1           # shard=False: every rank that calls this holds the whole sequence
+    lo, hi = chunk_bounds(T, world, rank) if sharded else (0, T)
     owner = world - 1                       # appended tokens extend the last chunk
     mgr, gen = build_manager(w, dev, seed=1234, extra_tokens=n_total + 16, ctx=hi - lo)
-    if world > 1:
+    transport = args.seq_transport if sharded else "none"
+    if sharded:
         from blockgtq_b200.sharding import SequenceShard
-        transport = os.environ.get("BGTQ_SEQ_TRANSPORT", "nccl")     # "p2p" = the library's peer-memory exchange
         SequenceShard(mgr, owner=owner, transport=transport)
     qs = (torch.randn(n_total, L, B, n_q, 1, HD, generator=gen, device=dev) * 2).half()
     ks = torch.stack([torch.stack([synth_keys(gen, (B * n_kv, 1), w["theta"], dev).reshape(B, n_kv, 1, HD)
@@ -509,7 +510,7 @@ def run_seq_sharded(args, w, rank, world, dev):
     with torch.cuda.graph(step_graph):
         for li in range(L):
             mgr.layer_step(li)
-    per_step = (5 if world > 1 else 3) * L
+    per_step = ((4 if transport == "p2p" else 5) if sharded else 3) * L
 
     def step_device():
         g_all.copy_(dq[step_no[0]])
@@ -528,7 +529,7 @@ def run_seq_sharded(args, w, rank, world, dev):
         step_no[0] += 1
 
     def barrier():
-        if world > 1:
+        if sharded:
             dist.barrier()
         torch.cuda.synchronize()
 
@@ -541,7 +542,7 @@ def run_seq_sharded(args, w, rank, world, dev):
         e1.record()
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
+        if sharded:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
@@ -556,8 +557,16 @@ def run_seq_sharded(args, w, rank, world, dev):
         step_e2e()
     ms_e2e = timed(step_e2e, K)
     live = torch.tensor([float(mgr.live_bytes_per_step())], device=dev)
-    if world > 1:
+    if sharded:
         dist.all_reduce(live)
+    torch.cuda.synchronize()
+    mgr.check_status()
+    result = {"ms_per_step": ms_total / K, "ms_per_step_e2e": ms_e2e / K, "transport": transport, "layers": L,
+              "tokens_per_gpu": hi - lo}
+    mgr.release_graphs()
+    del step_graph
+    if not emit:
+        return result
     if rank == 0:
         ms_step = ms_total / K
         peaks = {}
@@ -573,8 +582,7 @@ def run_seq_sharded(args, w, rank, world, dev):
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": args.workload, "layers": L, "batch": B, "n_q": n_q, "n_kv": n_kv, "context": T,
                        "tokens_per_gpu": hi - lo, "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"],
-                       "parallelism": f"sequence chunks x{world}, one exchange of (O, LSE) per layer "
-                                      f"({os.environ.get('BGTQ_SEQ_TRANSPORT', 'nccl') if world > 1 else 'none'})",
+                       "parallelism": f"sequence chunks x{world}, one exchange of (O, LSE) per layer ({transport})",
                        "exchange_bytes_per_layer": B * n_q * (HD + 1) * 4,
                        "l2": "inputs larger than L2 (packed cache bytes per step >> 126 MB), no flush"},
             "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": gbs, "peak": peak,
@@ -583,6 +591,32 @@ def run_seq_sharded(args, w, rank, world, dev):
             "e2e": {"value": B / (ms_e2e / K * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": int(L * hq[0, 0].numel() * 2),
                     "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": ms_e2e / K},
             "gpu_launches": launches, "clocks": clocks}), flush=True)
+    return result
+
+
+def seqshard_leg(args, rank, world, dev):
+    """Next to the batch-sharded default workload at N > 1: the sequence-sharded one (one 131072-token
+    sequence, Llama-3.1-8B shape, K2V2, 8 of its 32 layers so the leg stays short), timed on all N ranks with
+    the (O, LSE) exchange and then on rank 0 alone holding the whole sequence."""
+    import torch.distributed as dist
+    w = dict(WORKLOADS["llama3.1-8b_k2v2_b1_t131072_seqshard"], layers=8)
+    sub = argparse.Namespace(**vars(args))
+    sub.steps, sub.warmup, sub.workload = 10, 3, "llama3.1-8b_k2v2_b1_t131072_seqshard"
+    many = run_seq_sharded(sub, w, rank, world, dev, emit=False)
+    torch.cuda.empty_cache()
+    dist.barrier()
+    one = run_seq_sharded(sub, w, rank, world, dev, emit=False, shard=False) if rank == 0 else None
+    dist.barrier()
+    if rank != 0:
+        return None
+    L = w["layers"]
+    return {"workload": "llama3.1-8b_k2v2_b1_t131072_seqshard, 8 of 32 layers", "n_gpus": world,
+            "ms_per_step": many["ms_per_step"], "tok_s": 1.0 / (many["ms_per_step"] * 1e-3),
+            "ms_per_step_1gpu": one["ms_per_step"], "speedup_vs_1gpu": one["ms_per_step"] / many["ms_per_step"],
+            "us_per_layer": many["ms_per_step"] / L * 1e3, "us_per_layer_1gpu": one["ms_per_step"] / L * 1e3,
+            "transport": many["transport"], "tokens_per_gpu": many["tokens_per_gpu"],
+            "exchange_bytes_per_layer": w["n_q"] * (HD + 1) * 4,
+            "note": "1-GPU figure: the same code on rank 0 holding all 131072 tokens, same run"}
 
 
 def run_encode(args, w, rank, world, dev):
@@ -804,6 +838,9 @@ def main():
     ap.add_argument("--triton-layers", type=int, default=4, help="layers the reference-Triton leg builds and times")
     ap.add_argument("--triton-timeout", type=int, default=420)
     ap.add_argument("--no-parity-check", action="store_true")
+    ap.add_argument("--seq-transport", default="p2p", choices=["p2p", "nccl"],
+                    help="exchange of the sequence-sharded workload: peer-memory stores or one NCCL all-gather")
+    ap.add_argument("--no-seqshard", action="store_true", help="at N > 1, skip the sequence-sharded leg")
     ap.add_argument("--per-layer-graphs", action="store_true",
                     help="replay one CUDA graph per layer (append_and_attend) instead of one graph per decode step")
     args = ap.parse_args()
@@ -1020,6 +1057,14 @@ def main():
             line["cpu_baseline"] = cpu_baseline(w)
         if not args.no_triton and world == 1:
             line["config"]["reference_triton"] = triton_leg(args, args.workload)
+    seq = None
+    if world > 1 and not args.no_seqshard and args.workload == DEFAULT:
+        del mgr, dqkv, hqkv, qs, ks, vs, step_graph
+        torch.cuda.empty_cache()
+        seq = seqshard_leg(args, rank, world, dev)
+    if rank == 0:
+        if seq is not None:
+            line["seqshard"] = seq
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

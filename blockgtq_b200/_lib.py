@@ -99,6 +99,8 @@ _SIGNATURES = {
     "bgtq_prefill_attention": (C.c_int, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
                                          _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
                                          _i32, _i32, C.c_float, _i32, _vp, _vp]),
+    "bgtq_combine_publish": (C.c_int, [_vp, _vp, _i32, _vp, _i32, _i32, _i32, _vp, _i64, _i64, _vp, _i32, _i32, _vp, _vp,
+                                      _i32, _vp]),
     "bgtq_exchange_publish": (C.c_int, [_vp, _i64, _vp, _i64, _i64, _vp, _i32, _i32, _vp, _vp, _vp]),
     "bgtq_exchange_merge": (C.c_int, [_vp, _i32, _i64, _i64, _vp, _vp, _i32, _i32, _vp, _i64, _i64, _vp, _vp, _vp]),
     "bgtq_combine_ranks": (C.c_int, [_vp, _i32, _i64, _i32, _i32, _vp, _i64, _i64, _i32, _vp]),

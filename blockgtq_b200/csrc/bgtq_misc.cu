@@ -27,6 +27,18 @@ __global__ void __launch_bounds__(128) rotate_q_kernel(const BgtqHeadDesc* desc,
     q_rot[((size_t)b * n_q + hq) * kHD + p] = __float2half_rn(acc);
 }
 
+// Optional last step of the combine on a sequence-sharded cache: the row's fp32 result and LSE go straight
+// into this rank's slot of EVERY rank's exchange buffer (plain peer stores over NVLink), and the last CTA of
+// the grid raises this rank's flag on every rank.  Layout and protocol: see the exchange kernels below.
+struct PublishArgs {
+    float* const* peer_bufs;
+    int32_t* const* peer_flags;
+    int64_t slot_off, parity_stride, rows;
+    const int32_t* seq_dev;
+    int32_t* ticket;
+    int32_t rank, n_ranks;
+};
+
 // ---------------------------------------------------------------------------
 // combine: merge split partials (and optionally the fp16-buffer partial).
 // One CTA per (query head, batch), one thread per output dim.
@@ -34,7 +46,8 @@ __global__ void __launch_bounds__(128) rotate_q_kernel(const BgtqHeadDesc* desc,
 __global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const float* part_lse, int n_splits,
                                                        const float* v_rot, const float* buf_o, const float* buf_lse,
                                                        int n_q, int n_kv, __half* out, int64_t o_sb, int64_t o_sh,
-                                                       float* out_f32, float* lse_out, int64_t rank_stride) {
+                                                       float* out_f32, float* lse_out, int64_t rank_stride,
+                                                       const PublishArgs pub) {
     // rank_stride == 0: partial s of row r at part_o[(r * n_splits + s) * 128], part_lse[r * n_splits + s];
     // rank_stride  > 0: partial s is a whole (rows, 128) block + (rows) block, rank_stride floats apart
     // (the receive buffer of an all-gather of per-rank results)
@@ -85,20 +98,44 @@ __global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const
         __syncthreads();
         o = (pnum[0][d] + pnum[1][d]) + (pnum[2][d] + pnum[3][d]);
     }
-    if (c != 0) return;
-    if (buf_o) {
-        const float lb = buf_lse[row];
-        const float m2 = fmaxf(tot, lb);
-        if (m2 > -INFINITY) {
-            const float wp = tot == -INFINITY ? 0.f : expf(tot - m2);
-            const float wb = lb == -INFINITY ? 0.f : expf(lb - m2);
-            o = (wp * o + wb * buf_o[row * kHD + d]) / (wp + wb);
-            tot = m2 + logf(wp + wb);
+    if (c == 0) {
+        if (buf_o) {
+            const float lb = buf_lse[row];
+            const float m2 = fmaxf(tot, lb);
+            if (m2 > -INFINITY) {
+                const float wp = tot == -INFINITY ? 0.f : expf(tot - m2);
+                const float wb = lb == -INFINITY ? 0.f : expf(lb - m2);
+                o = (wp * o + wb * buf_o[row * kHD + d]) / (wp + wb);
+                tot = m2 + logf(wp + wb);
+            }
+        }
+        if (out) out[b * o_sb + hq * o_sh + d] = __float2half_rn(o);
+        if (out_f32) out_f32[row * kHD + d] = o;
+        if (lse_out && d == 0) lse_out[row] = tot;
+        if (pub.n_ranks > 0) {
+            const int seq = *pub.seq_dev;
+            for (int p = 0; p < pub.n_ranks; ++p) {
+                float* dst = pub.peer_bufs[p] + (seq & 1) * pub.parity_stride + pub.slot_off;
+                dst[row * kHD + d] = o;
+                if (d == 0) dst[pub.rows * kHD + row] = tot;
+            }
+            __threadfence_system();
         }
     }
-    if (out) out[b * o_sb + hq * o_sh + d] = __float2half_rn(o);
-    if (out_f32) out_f32[row * kHD + d] = o;
-    if (lse_out && d == 0) lse_out[row] = tot;
+    if (pub.n_ranks == 0) return;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int seq = *pub.seq_dev;
+        const int t = atomicAdd(pub.ticket, 1);
+        if (t == (int)(gridDim.x * gridDim.y) - 1) {    // every CTA's stores are fenced: raise the flag everywhere
+            *pub.ticket = 0;
+            __threadfence_system();
+            for (int p = 0; p < pub.n_ranks; ++p) {
+                volatile int32_t* f = pub.peer_flags[p] + pub.rank;
+                *f = seq + 1;
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -238,7 +275,28 @@ extern "C" __attribute__((visibility("default"))) int bgtq_combine(const float* 
     if (n_batch > 65535) return BGTQ_E_TOOBIG;
     return launch_kernel(combine_kernel, dim3(n_q, n_batch), dim3(512), 0, static_cast<cudaStream_t>(stream),
                          (flags & BGTQ_COMBINE_PROGRAMMATIC) != 0, part_o, part_lse, n_splits, v_rot, buf_o, buf_lse,
-                         n_q, n_kv, static_cast<__half*>(out), o_sb, o_sh, out_f32, lse_out, (int64_t)0) == cudaSuccess
+                         n_q, n_kv, static_cast<__half*>(out), o_sb, o_sh, out_f32, lse_out, (int64_t)0,
+                         PublishArgs{}) == cudaSuccess
+               ? BGTQ_OK : BGTQ_E_LAUNCH;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_combine_publish(
+    const float* part_o, const float* part_lse, int32_t n_splits, const float* v_rot, int32_t n_batch, int32_t n_q,
+    int32_t n_kv, float* const* peer_bufs, int64_t slot_off, int64_t parity_stride, int32_t* const* peer_flags,
+    int32_t rank, int32_t n_ranks, const int32_t* seq_dev, int32_t* ticket, int32_t flags, void* stream) {
+    if (!part_o || !part_lse || n_splits < 1 || n_batch < 1 || n_kv < 1 || n_q < n_kv || n_q % n_kv)
+        return BGTQ_E_BADARG;
+    if (!peer_bufs || !peer_flags || !seq_dev || !ticket || n_ranks < 1 || rank < 0 || rank >= n_ranks)
+        return BGTQ_E_BADARG;
+    if (n_batch > 65535) return BGTQ_E_TOOBIG;
+    PublishArgs pub;
+    pub.peer_bufs = peer_bufs; pub.peer_flags = peer_flags; pub.slot_off = slot_off; pub.parity_stride = parity_stride;
+    pub.rows = (int64_t)n_batch * n_q; pub.seq_dev = seq_dev; pub.ticket = ticket; pub.rank = rank; pub.n_ranks = n_ranks;
+    return launch_kernel(combine_kernel, dim3(n_q, n_batch), dim3(512), 0, static_cast<cudaStream_t>(stream),
+                         (flags & BGTQ_COMBINE_PROGRAMMATIC) != 0, part_o, part_lse, n_splits, v_rot,
+                         static_cast<const float*>(nullptr), static_cast<const float*>(nullptr), n_q, n_kv,
+                         static_cast<__half*>(nullptr), (int64_t)0, (int64_t)0, static_cast<float*>(nullptr),
+                         static_cast<float*>(nullptr), (int64_t)0, pub) == cudaSuccess
                ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 
@@ -253,7 +311,8 @@ extern "C" __attribute__((visibility("default"))) int bgtq_combine_ranks(const f
                          (flags & BGTQ_COMBINE_PROGRAMMATIC) != 0, gathered, gathered + rows * kHD, n_ranks,
                          static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
                          static_cast<const float*>(nullptr), n_q, 1, static_cast<__half*>(out), o_sb, o_sh,
-                         static_cast<float*>(nullptr), static_cast<float*>(nullptr), rank_stride) == cudaSuccess
+                         static_cast<float*>(nullptr), static_cast<float*>(nullptr), rank_stride,
+                         PublishArgs{}) == cudaSuccess
                ? BGTQ_OK : BGTQ_E_LAUNCH;
 }
 
@@ -345,6 +404,8 @@ __global__ void __launch_bounds__(128) merge_ranks_kernel(const float* local_buf
                                                           int32_t* status, int32_t* ticket) {
     __shared__ int ok;
     const int d = threadIdx.x, hq = blockIdx.x, b = blockIdx.y;
+    grid_launch_dependents();
+    grid_dependency_wait();       // the step counter and the local message come from the stream's earlier kernels
     const int seq = *seq_dev;
     if (d == 0) {
         int good = 1;
@@ -415,8 +476,10 @@ extern "C" __attribute__((visibility("default"))) int bgtq_exchange_merge(
     const int64_t rows = (int64_t)n_batch * n_q;
     if (rank_stride < rows * (kHD + 1) || parity_stride < rank_stride * n_ranks) return BGTQ_E_BADARG;
     if (n_batch > 65535) return BGTQ_E_TOOBIG;
-    merge_ranks_kernel<<<dim3(n_q, n_batch), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        local_buf, n_ranks, rank_stride, parity_stride, flags, seq_dev, n_q, rows, static_cast<__half*>(out), o_sb, o_sh,
-        status, ticket);
-    return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+    // launched as a programmatic dependent: its blocks may become resident while the step's previous kernel
+    // drains; they wait for it on the device before reading anything
+    return launch_kernel(merge_ranks_kernel, dim3(n_q, n_batch), dim3(128), 0, static_cast<cudaStream_t>(stream), true,
+                         local_buf, n_ranks, rank_stride, parity_stride, flags, seq_dev, n_q, rows,
+                         static_cast<__half*>(out), o_sb, o_sh, status, ticket) == cudaSuccess
+               ? BGTQ_OK : BGTQ_E_LAUNCH;
 }

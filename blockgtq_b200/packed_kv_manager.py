@@ -312,7 +312,10 @@ class BlockGTQKVManager:
                flags=self._dec_flags | (_lib.DEC_PROGRAMMATIC if pd else 0))
         if ex is None:
             combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li], programmatic=pd)
-        else:       # local result straight into the message, exchange (all-gather or peer stores), merge of the messages
+        elif ex.transport == "p2p":     # combine + peer stores in one launch, then the bounded wait + merge
+            ex.combine_publish(self._part_o, self._part_lse, self.n_kv, lt.v_rot, programmatic=pd)
+            ex.exchange_and_merge(self._g_out[li])
+        else:       # local result straight into the message, one all-gather, merge of the messages
             combine(self._part_o, self._part_lse, self.n_kv, v_rot=lt.v_rot, out=self._g_out[li], programmatic=pd,
                     o32_out=ex.msg_o, lse_out=ex.msg_lse)
             ex.exchange_and_merge(self._g_out[li])
@@ -359,7 +362,8 @@ class BlockGTQKVManager:
             self._graphs[li][use_rope] = g
         else:
             g.replay()
-            _lib.count_launch(4 if self._buffered else (5 if self._exchange else 3))
+            _lib.count_launch(4 if self._buffered else
+                              ((4 if self._exchange.transport == "p2p" else 5) if self._exchange else 3))
         return self._g_out[li]
 
     # -- decode ----------------------------------------------------------------------------

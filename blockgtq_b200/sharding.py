@@ -136,20 +136,36 @@ class SequenceShard:
             torch.cuda.synchronize(dev) if dev.type == "cuda" else None
         mgr._exchange = self
 
+    def combine_publish(self, part_o, part_lse, n_kv, v_rot, programmatic=False):
+        """Peer-memory transport: merge this rank's split partials and store the result straight into every
+        rank's exchange buffer (one launch; ``exchange_and_merge`` then only waits and merges)."""
+        from . import _lib
+        B, n_q, S, _ = part_o.shape
+        _lib.check(_lib.lib().bgtq_combine_publish(
+            _lib.ptr(part_o), _lib.ptr(part_lse), S, _lib.ptr(v_rot), B, n_q, n_kv, _lib.ptr(self._peer_bufs),
+            self.rank * self.stride, self.world * self.stride, _lib.ptr(self._peer_flags), self.rank, self.world,
+            _lib.ptr(self._seq), _lib.ptr(self._tickets), _lib.COMBINE_PROGRAMMATIC if programmatic else 0,
+            _lib.stream_ptr(part_o.device)), "bgtq_combine_publish")
+        _lib.count_launch()
+        self._published = True
+
     def exchange_and_merge(self, out):
         """Make every rank's message visible here and merge them into ``out`` (B, n_q, 128) fp16."""
         if self.transport == "p2p":
             from . import _lib
             L, sp = _lib.lib(), _lib.stream_ptr(self.msg.device)
-            _lib.check(L.bgtq_exchange_publish(
-                _lib.ptr(self.msg), self.stride, _lib.ptr(self._peer_bufs), self.rank * self.stride,
-                self.world * self.stride, _lib.ptr(self._peer_flags), self.rank, self.world, _lib.ptr(self._seq),
-                _lib.ptr(self._tickets), sp), "bgtq_exchange_publish")
+            if not getattr(self, "_published", False):      # message produced by a plain combine: publish it
+                _lib.check(L.bgtq_exchange_publish(
+                    _lib.ptr(self.msg), self.stride, _lib.ptr(self._peer_bufs), self.rank * self.stride,
+                    self.world * self.stride, _lib.ptr(self._peer_flags), self.rank, self.world, _lib.ptr(self._seq),
+                    _lib.ptr(self._tickets), sp), "bgtq_exchange_publish")
+                _lib.count_launch()
+            self._published = False
             _lib.check(L.bgtq_exchange_merge(
                 _lib.ptr(self._buf), self.world, self.stride, self.world * self.stride, _lib.ptr(self._flags),
                 _lib.ptr(self._seq), self.B, self.n_q, _lib.ptr(out), out.stride(0), out.stride(1),
                 _lib.ptr(self._status), _lib.ptr(self._tickets[1:]), sp), "bgtq_exchange_merge")
-            _lib.count_launch(2)
+            _lib.count_launch()
             return out
         from .layer import combine_ranks
         self.all_gather()

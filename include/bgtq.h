@@ -404,6 +404,16 @@ int bgtq_combine_ranks(const float* gathered, int32_t n_ranks, int64_t rank_stri
  *     bgtq_combine_ranks from the LOCAL buffer, writes fp16 out and advances *seq_dev.
  * Only plain loads/stores and system-scope fences are used (no multicast).  All ranks must run the same
  * sequence of steps; each rank's kernels run on its own GPU. */
+/* bgtq_combine with bgtq_exchange_publish folded into its last step: each (batch, query head) row's fp32
+ * result and LSE are stored straight into this rank's slot [*seq_dev & 1][rank] of every rank's exchange
+ * buffer, and the last block raises this rank's flag on every rank -- a sequence-sharded layer step is then
+ * decode -> combine+publish -> merge.  Arguments as for bgtq_combine (no fp16-buffer partial, no local
+ * output) and bgtq_exchange_publish (rank_stride of the buffers = n_batch * n_q * 129 floats or more). */
+int bgtq_combine_publish(const float* part_o, const float* part_lse, int32_t n_splits, const float* v_rot,
+                         int32_t n_batch, int32_t n_q, int32_t n_kv,
+                         float* const* peer_bufs, int64_t slot_off, int64_t parity_stride,
+                         int32_t* const* peer_flags, int32_t rank, int32_t n_ranks,
+                         const int32_t* seq_dev, int32_t* ticket, int32_t flags, void* stream);
 int bgtq_exchange_publish(const float* msg, int64_t n_floats, float* const* peer_bufs, int64_t slot_off,
                           int64_t parity_stride, int32_t* const* peer_flags, int32_t rank, int32_t n_ranks,
                           const int32_t* seq_dev, int32_t* ticket, void* stream);

@@ -17,18 +17,8 @@ def _free_port():
 
 
 def _worker(rank, world, port, transport, ret):
-    import faulthandler
     import sys
     import torch.distributed as dist
-    _dbg = os.environ.get("BGTQ_TEST_TRACE")          # optional: file prefix for per-rank stage traces
-    _fh = open(f"{_dbg}{rank}.log", "w") if _dbg else None
-    if _fh:
-        faulthandler.dump_traceback_later(90, repeat=False, file=_fh)
-
-    def log(msg):
-        if _fh:
-            _fh.write(msg + "\n")
-            _fh.flush()
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     from helpers import HD, synth_head
     from blockgtq_b200 import BlockGTQKVManager
@@ -37,9 +27,7 @@ def _worker(rank, world, port, transport, ret):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    log("init pg")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    log("pg ready")
     try:
         gen = torch.Generator().manual_seed(2024)               # same data on every rank
         B, n_kv, gqa, T, steps = 2, 2, 2, 600, 3
@@ -63,21 +51,16 @@ def _worker(rank, world, port, transport, ret):
             return m
 
         full = manager(0, T)
-        log("full manager built")
         lo, hi = chunk_bounds(T, world, rank)
         part = manager(lo, hi)
-        log("part manager built")
         SequenceShard(part, transport=transport)
-        log("shard attached")
         worst = 0.0
         for s in range(steps):
             want = full.append_and_attend(0, qs[s].to(dev), ks[s].to(dev), vs[s].to(dev))
-            log(f"step {s}: full done")
             full.increment_seq_len()
             got = part.append_and_attend(0, qs[s].to(dev), ks[s].to(dev), vs[s].to(dev))
             part.increment_seq_len()
             torch.cuda.synchronize()
-            log(f"step {s}: sharded done")
             worst = max(worst, (got.float() - want.float()).abs().max().item())
         part.check_status()
         ret[rank] = worst
@@ -85,10 +68,8 @@ def _worker(rank, world, port, transport, ret):
         part.release_graphs()
         del part, full
         torch.cuda.synchronize()
-        log("released")
     finally:
         dist.destroy_process_group()
-        log("pg destroyed")
 
 
 @pytest.mark.parametrize("transport", ["nccl", "p2p"])
