@@ -843,6 +843,8 @@ def main():
     ap.add_argument("--no-seqshard", action="store_true", help="at N > 1, skip the sequence-sharded leg")
     ap.add_argument("--per-layer-graphs", action="store_true",
                     help="replay one CUDA graph per layer (append_and_attend) instead of one graph per decode step")
+    ap.add_argument("--eager-step", action="store_true",
+                    help="launch the step's kernels one by one instead of replaying a graph (for profiler launch lists)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]
@@ -905,7 +907,7 @@ def main():
     # engine captures its model forward around these launches; --per-layer-graphs replays one graph per layer
     # through append_and_attend instead.
     step_graph = None
-    if graph_outputs and not args.per_layer_graphs:
+    if graph_outputs and not args.per_layer_graphs and not args.eager_step:
         for li in range(L):
             mgr.layer_step(li)                                      # eager once: kernel attributes, shapes
         torch.cuda.synchronize()
@@ -919,6 +921,10 @@ def main():
         if step_graph is not None:
             step_graph.replay()
             _lib.count_launch(launches_per_step)
+            return None
+        if args.eager_step and graph_outputs:
+            for li in range(L):
+                mgr.layer_step(li)
             return None
         return [mgr.append_and_attend(li, *g_in[li]) for li in range(L)]
 
@@ -1035,7 +1041,7 @@ def main():
             "config": workload_config(args.workload, w, world) | {
                        "l2": "inputs larger than L2 (packed cache bytes per step >> 126 MB), no flush",
                        "graphs": "one per decode step" if step_graph is not None else
-                                 ("one per layer" if graph_outputs else "none (eager launches)"),
+                                 ("none (eager launches)" if args.eager_step or not graph_outputs else "one per layer"),
                        "decode_us_per_layer": dec_avg_ms * 1e3, "step_hbm_gbs": live_bytes / (ms_step * 1e-3) / 1e9,
                        "step_frac_of_8tbs": live_bytes / (ms_step * 1e-3) / 8e12,
                        "decode_kernel": "specialised per layer at run time (NVRTC)"

@@ -69,16 +69,51 @@ __global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const
     const float* lse = rank_stride ? part_lse + row : part_lse + row * n_splits;
     const float* po = rank_stride ? part_o + row * kHD + d : part_o + row * n_splits * kHD + d;
     const int64_t sl = rank_stride ? rank_stride : 1, so = rank_stride ? rank_stride : kHD;
+    // The slot count only sets the granularity of the decode launch's work split: most slots hold no partial
+    // (LSE = -inf).  The block finds the maximum and the live slots together (each thread looks at one slot per
+    // 512), keeps them in slot order, and only then walks the live ones: no thread scans the whole row alone.
+    __shared__ float s_red[16];
+    __shared__ int s_cnt[16];
+    __shared__ int s_slot[512];
+    __shared__ float s_w[512];
+    const int warp = tid >> 5, lane = tid & 31;
     float mx = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, lse[s * sl]);
+    for (int s = tid; s < n_splits; s += 512) mx = fmaxf(mx, lse[s * sl]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    mx = s_red[0];
+#pragma unroll
+    for (int i = 1; i < 16; ++i) mx = fmaxf(mx, s_red[i]);
     float num = 0.f, den = 0.f;
     if (mx > -INFINITY) {
-        for (int s = c; s < n_splits; s += 4) {
-            const float l = lse[s * sl];
-            if (l == -INFINITY) continue;
-            const float a = expf(l - mx);
-            den += a;
-            num = fmaf(a, po[s * so], num);
+        for (int base = 0; base < n_splits; base += 512) {
+            const int s = base + tid;
+            const float l = s < n_splits ? lse[s * sl] : -INFINITY;
+            const bool live = l > -INFINITY;
+            const unsigned bal = __ballot_sync(0xffffffffu, live);
+            __syncthreads();                               // the previous chunk's list has been consumed
+            if (lane == 0) s_cnt[warp] = __popc(bal);
+            __syncthreads();
+            int off = 0, total = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int n = s_cnt[i];
+                off += i < warp ? n : 0;
+                total += n;
+            }
+            if (live) {
+                const int pos = off + __popc(bal & ((1u << lane) - 1u));
+                s_slot[pos] = s;
+                s_w[pos] = expf(l - mx);
+            }
+            __syncthreads();
+            for (int i = c; i < total; i += 4) {           // quarter c of the live slots
+                const float a = s_w[i];
+                den += a;
+                num = fmaf(a, po[(int64_t)s_slot[i] * so], num);
+            }
         }
     }
     pnum[c][d] = num;
