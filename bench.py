@@ -63,6 +63,18 @@ DEFAULT = "qwen2.5-3b_k3v3_b8_t32768"
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 
 
+TRAFFIC_SOURCES = ["blockgtq_b200/csrc/bgtq_decode_kernel.cuh", "blockgtq_b200/csrc/bgtq_decode_plan.cu",
+                   "blockgtq_b200/csrc/bgtq_plan.h", "blockgtq_b200/csrc/bgtq_decode.cu"]
+
+
+def sources_key(files):
+    import hashlib
+    h = hashlib.sha256()
+    for f in files:
+        h.update(open(os.path.join(ROOT, f), "rb").read())
+    return h.hexdigest()[:16]
+
+
 def dram_traffic(workload):
     """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture
     recorded in profiles/dram_traffic.json (which names the command and the kernel source it was taken
@@ -71,14 +83,10 @@ def dram_traffic(workload):
         rec = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json")))[workload]
     except Exception:
         return None
-    import hashlib
-    h = hashlib.sha256()
-    for f in rec.get("sources", []):
-        try:
-            h.update(open(os.path.join(ROOT, f), "rb").read())
-        except OSError:
-            return None
-    return rec["bytes_per_launch"] if h.hexdigest()[:16] == rec.get("sources_sha16") else None
+    try:
+        return rec["bytes_per_launch"] if sources_key(rec.get("sources", [])) == rec.get("sources_sha16") else None
+    except OSError:
+        return None
 
 
 def synth_keys(gen, shape_bt, theta, device):
@@ -835,8 +843,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "triton"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-triton", action="store_true", help="skip the reference-Triton leg of the default run")
-    ap.add_argument("--triton-layers", type=int, default=4, help="layers the reference-Triton leg builds and times")
-    ap.add_argument("--triton-timeout", type=int, default=420)
+    ap.add_argument("--triton-layers", type=int, default=2, help="layers the reference-Triton leg builds and times")
+    ap.add_argument("--triton-timeout", type=int, default=300)
     ap.add_argument("--no-parity-check", action="store_true")
     ap.add_argument("--seq-transport", default="p2p", choices=["p2p", "nccl"],
                     help="exchange of the sequence-sharded workload: peer-memory stores or one NCCL all-gather")
@@ -845,7 +853,12 @@ def main():
                     help="replay one CUDA graph per layer (append_and_attend) instead of one graph per decode step")
     ap.add_argument("--eager-step", action="store_true",
                     help="launch the step's kernels one by one instead of replaying a graph (for profiler launch lists)")
+    ap.add_argument("--traffic-key", action="store_true",
+                    help="print the hash of the decode kernel sources that a record in profiles/dram_traffic.json carries")
     args = ap.parse_args()
+    if args.traffic_key:
+        print(json.dumps({"sources": TRAFFIC_SOURCES, "sources_sha16": sources_key(TRAFFIC_SOURCES)}))
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -888,7 +901,10 @@ def main():
 
     K, W = args.steps, args.warmup
     n_steps_total = 2 * (K + W) + min(K, 5) + 2
-    mgr, gen = build_manager(w, dev, seed=1234 + rank, extra_tokens=n_steps_total + 16)
+    # The cache is filled so that the LAST step of the run attends over the nominal context: every step sees a
+    # cache of at most w["ctx"] tokens (ctx - n_steps_total + 1 ... ctx).
+    ctx_start = max(64, w["ctx"] - n_steps_total)
+    mgr, gen = build_manager(w, dev, seed=1234 + rank, extra_tokens=n_steps_total + 16, ctx=ctx_start)
     L, B, n_q, n_kv = w["layers"], w["batch"], w["n_q"], w["n_kv"]
     # one decode token per layer per step, pre-generated; device copies for `value`, pinned host for `e2e`
     qs = (torch.randn(n_steps_total, L, B, n_q, 1, HD, generator=gen, device=dev) * 2).half()
@@ -966,13 +982,16 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    # clocks are sampled from the warm-up to the end of the end-to-end timing: warm-up, timed steps, kernel
+    # timing and end-to-end steps all keep the GPU under the step's load, and 20 steps alone last only tens of
+    # milliseconds
+    sampler = clocks_sampler(local) if rank == 0 else None
+    t_sampler = time.perf_counter()
     for _ in range(W):
         step_device()
-    sampler = clocks_sampler(local) if rank == 0 else None
     launches0 = _lib.launches
     ms_total = timed(step_device, K)
     launches = _lib.launches - launches0
-    clocks = clocks_summary(sampler)
     live_bytes = mgr.live_bytes_per_step()
 
     # per-launch duration of the dominant kernel (fused decode): the decode of every layer, launched as in the
@@ -1006,12 +1025,18 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     dec_avg_ms = e0.elapsed_time(e1) / (n_prof * L)
+    # a short run ends before the clock sampler has written a handful of lines: keep the decode launches going
+    # (untimed; they append nothing) until it has had half a second of this load
+    while time.perf_counter() - t_sampler < 0.5:
+        dec_graph.replay()
+        torch.cuda.synchronize()
     del dec_graph
     packed_bytes_per_launch = (live_bytes - (sink + n_rec) * HD * 4 * n_kv * B * L) / L
 
     for _ in range(W):
         step_e2e()
     ms_e2e = timed(step_e2e, K)
+    clocks = clocks_summary(sampler)
 
     parity = None
     if rank == 0 and not args.no_parity_check:
@@ -1042,6 +1067,8 @@ def main():
                        "l2": "inputs larger than L2 (packed cache bytes per step >> 126 MB), no flush",
                        "graphs": "one per decode step" if step_graph is not None else
                                  ("none (eager launches)" if args.eager_step or not graph_outputs else "one per layer"),
+                       "cache_lengths": [ctx_start + 1, int(mgr.seq_len)],      # first step's .. after the last one
+                       "decode_item_ranges": "cost-balanced table (bgtq_decode_partition)",
                        "decode_us_per_layer": dec_avg_ms * 1e3, "step_hbm_gbs": live_bytes / (ms_step * 1e-3) / 1e9,
                        "step_frac_of_8tbs": live_bytes / (ms_step * 1e-3) / 8e12,
                        "decode_kernel": "specialised per layer at run time (NVRTC)"

@@ -1,7 +1,6 @@
 // C entry points of the fused decode (kernel b): argument checks, shared-memory layout and launch.
 // The kernel itself lives in bgtq_decode_kernel.cuh (one translation unit per stored V width), the
 // plan / table-image builders in bgtq_decode_plan.cu.
-#include <stdlib.h>
 #include "bgtq_decode_kernel.cuh"
 
 using namespace bgtq;
@@ -46,9 +45,7 @@ static int decode_impl(
     // Tiles of 16 warps x 32 tokens, two stages; rows too wide for that (padded strides, the nibble layout with
     // large tables) fall back to 16 tokens per warp.
     auto r16 = [](uint32_t x) { return (x + 15u) & ~15u; };
-    int nu = getenv("BGTQ_EXP_NU") ? atoi(getenv("BGTQ_EXP_NU")) : 2;
-    const int n_stages = getenv("BGTQ_EXP_STAGES") ? atoi(getenv("BGTQ_EXP_STAGES")) : kDecStages;
-    const int nu_req = nu;
+    int nu = 2;
     size_t smem = 0;
     for (;; --nu) {
         if (nu == 0) return BGTQ_E_TOOBIG;
@@ -59,7 +56,7 @@ static int decode_impl(
         P.off_kn = sz_k; P.off_v = sz_k + sz_kn; P.off_vn = sz_k + sz_kn + sz_v;
         P.stage_bytes = (sz_k + sz_kn + sz_v + sz_vn + 127u) & ~127u;
         P.stage_off = kOffStagesMin + P.plan.lut_bytes;
-        const uint32_t region = n_stages * P.stage_bytes > kMergeBytes ? n_stages * P.stage_bytes : kMergeBytes;
+        const uint32_t region = kDecStages * P.stage_bytes > kMergeBytes ? kDecStages * P.stage_bytes : kMergeBytes;
         smem = (size_t)P.stage_off + region;
         if (smem <= 227 * 1024) break;
     }
@@ -71,12 +68,14 @@ static int decode_impl(
         return BGTQ_E_LAUNCH;
     }
     const int64_t max_items = (int64_t)n_batch * n_kv * n_splits;
+    // the kernel cuts the item range among its CTAs in 32-bit arithmetic: (CTA index + 1) * items must fit
+    if (max_items * ((int64_t)sms + 1) > 0xFFFFFFFFll) return BGTQ_E_TOOBIG;
     dim3 grid((unsigned)(max_items < sms ? max_items : sms));
     const cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool pdl = (P.plan.flags & BGTQ_DEC_PROGRAMMATIC) != 0;
     cudaError_t e;
     // the kernel specialised for this layer's heads, when the plan carries one (it exists for the wide tile only)
-    const bool jit = P.plan.jit_kernel != nullptr && nu == nu_req && !(P.plan.flags & BGTQ_DEC_GENERIC);
+    const bool jit = P.plan.jit_kernel != nullptr && nu == 2 && !(P.plan.flags & BGTQ_DEC_GENERIC);
     if (jit) e = launch_decode_jit(P, grid, smem, st, pdl);
     else switch (P.plan.v_sbits) {
         case 1: e = launch_decode_vb1(P, nu, grid, smem, st, pdl); break;

@@ -110,7 +110,7 @@ std::string make_prelude(const DecPlanDev& pl) {
          "typedef int int32_t;\ntypedef long long int64_t;\ntypedef unsigned long long uint64_t;\n"
          "typedef unsigned long long uintptr_t;\n"
          "namespace bgtq { namespace jit {\n"
-         "struct SegC { int kind, bw, q, f16_norm, bit0, lane_bits, tbl, esh, rep_log2, ent_log2, norm_idx, step0; };\n"
+         "struct SegC { int kind, bw, q, f16_norm, bit0, lane_bits, tbl, esh, rep_log2, ent_log2, norm_idx, step0, jv; };\n"
          "template <int H> struct Head;\n";
     for (int h = 0; h < pl.n_heads; ++h) {
         const DecHeadPlan& hp = pl.head[h];
@@ -121,11 +121,15 @@ std::string make_prelude(const DecPlanDev& pl) {
         for (int g = 0; g < 8; ++g) {
             if (g < hp.n_seg) {
                 const DecSeg& c = hp.seg[g];
-                snprintf(buf, sizeof(buf), "        {%d, %d, %d, %d, %d, %d, %u, %d, %d, %d, %d, %d},\n", c.kind, c.bw, c.q,
-                         c.f16_norm, c.bit0, c.lane_bits, c.tbl, c.esh, c.rep_log2, c.ent_log2, c.norm_idx, step0);
+                // lanes of a quad that hold codes of the segment: its length over the codes per lane
+                const int len = (int)hp.steps[step0].end - (int)hp.steps[step0].pos;
+                const int jv = c.q > 0 ? (len + c.q - 1) / c.q : 4;
+                snprintf(buf, sizeof(buf), "        {%d, %d, %d, %d, %d, %d, %u, %d, %d, %d, %d, %d, %d},\n", c.kind, c.bw, c.q,
+                         c.f16_norm, c.bit0, c.lane_bits, c.tbl, c.esh, c.rep_log2, c.ent_log2, c.norm_idx, step0,
+                         jv < 1 ? 1 : (jv > 4 ? 4 : jv));
                 step0 += (c.q + 3) / 4;
             } else {
-                snprintf(buf, sizeof(buf), "        {1, 1, 0, 0, 0, 0, 0u, 0, 0, 0, 0, 0},\n");
+                snprintf(buf, sizeof(buf), "        {1, 1, 0, 0, 0, 0, 0u, 0, 0, 0, 0, 0, 4},\n");
             }
             s += buf;
         }
@@ -140,56 +144,66 @@ std::string make_prelude(const DecPlanDev& pl) {
     return s;
 }
 
+// Compile one prelude to a cubin.  Runs without the lock: NVRTC is thread safe, and callers specialise the
+// layers of a model from several threads.
+int compile(const std::string& prelude, std::vector<char>* cubin, std::string* log) {
+    const std::string src = prelude + kSrcCommon + "\n" + kSrcPlan + "\n" + kSrcKernel + "\n";
+    nvrtcProgram prog = nullptr;
+    if (g_nvrtc.CreateProgram(&prog, src.c_str(), "bgtq_decode_jit.cu", 0, nullptr, nullptr) != 0) return BGTQ_E_LAUNCH;
+    std::vector<const char*> opts = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo"};
+    if (getenv("BGTQ_JIT_VERBOSE")) opts.push_back("--ptxas-options=-v");
+    std::vector<std::string> extra;             // BGTQ_JIT_OPTIONS: further NVRTC options, space separated
+    if (const char* e = getenv("BGTQ_JIT_OPTIONS")) {
+        std::string cur;
+        for (const char* ch = e;; ++ch) {
+            if (*ch == ' ' || *ch == 0) {
+                if (!cur.empty()) extra.push_back(cur);
+                cur.clear();
+                if (*ch == 0) break;
+            } else {
+                cur.push_back(*ch);
+            }
+        }
+    }
+    for (const std::string& x : extra) opts.push_back(x.c_str());
+    const int rc = g_nvrtc.CompileProgram(prog, (int)opts.size(), opts.data());
+    size_t n = 0;
+    if (log && g_nvrtc.GetProgramLogSize(prog, &n) == 0 && n > 1) {
+        log->resize(n);
+        g_nvrtc.GetProgramLog(prog, &(*log)[0]);
+    }
+    size_t sz = 0;
+    if (rc != 0 || g_nvrtc.GetCUBINSize(prog, &sz) != 0 || sz == 0) {
+        g_nvrtc.DestroyProgram(&prog);
+        return BGTQ_E_LAUNCH;
+    }
+    cubin->resize(sz);
+    g_nvrtc.GetCUBIN(prog, cubin->data());
+    g_nvrtc.DestroyProgram(&prog);
+    return BGTQ_OK;
+}
+
 // Compile (or find) the kernel of a prelude.  `load`: also load it into the CUDA runtime (needs a GPU).
-int build(const std::string& prelude, bool load, Compiled** out, std::string* log) {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    Compiled& c = g_cache[prelude];
-    if (c.cubin.empty()) {
+int build(const std::string& prelude, bool load, cudaKernel_t* kernel, std::string* log) {
+    bool have = false;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
         std::string why;
         if (!load_nvrtc(&why)) {
             if (log) *log = why;
-            g_cache.erase(prelude);
             return BGTQ_E_UNSUPPORTED;
         }
-        const std::string src = prelude + kSrcCommon + "\n" + kSrcPlan + "\n" + kSrcKernel + "\n";
-        nvrtcProgram prog = nullptr;
-        if (g_nvrtc.CreateProgram(&prog, src.c_str(), "bgtq_decode_jit.cu", 0, nullptr, nullptr) != 0) {
-            g_cache.erase(prelude);
-            return BGTQ_E_LAUNCH;
-        }
-        const bool verbose = getenv("BGTQ_JIT_VERBOSE") != nullptr;
-        std::vector<const char*> opts = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo"};
-        if (verbose) opts.push_back("--ptxas-options=-v");
-        std::vector<std::string> extra;             // BGTQ_JIT_OPTIONS: further NVRTC options, space separated
-        if (const char* e = getenv("BGTQ_JIT_OPTIONS")) {
-            std::string cur;
-            for (const char* ch = e;; ++ch) {
-                if (*ch == ' ' || *ch == 0) {
-                    if (!cur.empty()) extra.push_back(cur);
-                    cur.clear();
-                    if (*ch == 0) break;
-                } else {
-                    cur.push_back(*ch);
-                }
-            }
-        }
-        for (const std::string& x : extra) opts.push_back(x.c_str());
-        const int rc = g_nvrtc.CompileProgram(prog, (int)opts.size(), opts.data());
-        size_t n = 0;
-        if (log && g_nvrtc.GetProgramLogSize(prog, &n) == 0 && n > 1) {
-            log->resize(n);
-            g_nvrtc.GetProgramLog(prog, &(*log)[0]);
-        }
-        size_t sz = 0;
-        if (rc != 0 || g_nvrtc.GetCUBINSize(prog, &sz) != 0 || sz == 0) {
-            g_nvrtc.DestroyProgram(&prog);
-            g_cache.erase(prelude);
-            return BGTQ_E_LAUNCH;
-        }
-        c.cubin.resize(sz);
-        g_nvrtc.GetCUBIN(prog, c.cubin.data());
-        g_nvrtc.DestroyProgram(&prog);
+        auto it = g_cache.find(prelude);
+        have = it != g_cache.end() && !it->second.cubin.empty();
     }
+    std::vector<char> cubin;
+    if (!have) {
+        const int rc = compile(prelude, &cubin, log);      // two threads with the same layout both compile; one wins
+        if (rc != BGTQ_OK) return rc;
+    }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Compiled& c = g_cache[prelude];
+    if (c.cubin.empty()) c.cubin.swap(cubin);
     if (load && !c.kernel) {
         if (cudaLibraryLoadData(&c.lib, c.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0) != cudaSuccess ||
             cudaLibraryGetKernel(&c.kernel, c.lib, "bgtq_decode_jit") != cudaSuccess) {
@@ -199,7 +213,7 @@ int build(const std::string& prelude, bool load, Compiled** out, std::string* lo
             return BGTQ_E_LAUNCH;
         }
     }
-    if (out) *out = &c;
+    if (kernel) *kernel = c.kernel;
     return BGTQ_OK;
 }
 
@@ -226,12 +240,12 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan_specializ
     memcpy(&pl, plan_host, sizeof(pl));
     if (pl.n_heads < 1 || pl.n_heads > kMaxPlanHeads) return BGTQ_E_BADARG;
     std::string text;
-    Compiled* c = nullptr;
-    const int rc = build(make_prelude(pl), compile_only == 0, &c, &text);
+    cudaKernel_t kernel = nullptr;
+    const int rc = build(make_prelude(pl), compile_only == 0, &kernel, &text);
     copy_log(text, log, log_bytes);
     if (rc != BGTQ_OK) return rc;
     if (!compile_only) {
-        pl.jit_kernel = c->kernel;
+        pl.jit_kernel = kernel;
         memcpy(plan_host, &pl, sizeof(pl));
     }
     return BGTQ_OK;

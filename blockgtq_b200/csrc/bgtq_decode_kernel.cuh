@@ -53,21 +53,18 @@ namespace bgtq {
 
 constexpr int kDecWarps = 16;
 constexpr int kDecThreads = 32 * kDecWarps;
-#ifdef BGTQ_EXP_STAGES
-constexpr int kDecStages = BGTQ_EXP_STAGES;
-#else
 constexpr int kDecStages = 2;
-#endif
-constexpr int kMergeStride = 132;  // floats per query row in the end-of-run merge buffer
+constexpr int kMergeSlot = 9 * 32;   // float4 per warp in the end-of-run merge buffer: 8 of O and (m, l), per lane
 // shared-memory layout (byte offsets from the start of dynamic shared memory)
-// [barriers | query fragments | per-warp max / denominators | pad | lookup tables | stages (merge buffer at run end)]
+// [barriers | query fragments | pad | lookup tables | stages (merge buffer at run end)]
 // The lookup tables start at the first address past kOffMisc whose ABSOLUTE shared-window address is a
 // multiple of kLutAlign (table bases are OR-ed into addresses); the stages follow at a fixed offset that
 // leaves room for the worst-case pad.
-constexpr uint32_t kOffQf = 1024, kOffMM = kOffQf + kMaxSteps * 32 * 8, kOffMisc = kOffMM + 2 * kDecWarps * 8 * 4;
+constexpr uint32_t kOffQf = 1024, kOffMisc = kOffQf + kMaxSteps * 32 * 8;
 constexpr uint32_t kOffStagesMin = kOffMisc + kLutAlign;     // + lut_bytes = P.stage_off
 static_assert(kOffMisc % 128 == 0, "layout");
-constexpr uint32_t kMergeBytes = kDecWarps * 8 * kMergeStride * 4;
+// two regions the tree merge alternates between: 8 slots (first level) and 4 (second); later levels fit in them
+constexpr uint32_t kMergeBytes = (kDecWarps / 2 + kDecWarps / 4) * kMergeSlot * 16;
 #define BGTQ_INF __int_as_float(0x7f800000)
 
 struct DecParams {
@@ -183,7 +180,7 @@ __device__ __forceinline__ int k_segment(float (&acc)[NU][4], const uint8_t* sm,
             const uint2 bq = ld64(sm, qf + step * 256);
             ++step;
             uint32_t lo[2 * NU], hi[2 * NU];                   // fp16x2 of codes (0,1) and (2,3) of this k-tile, per row
-            if constexpr (KIND == 1 || KIND == 2) {            // quad tables: one 64-bit lookup per row
+            if constexpr (KIND == 1) {                         // quad table: one 64-bit lookup per row
                 constexpr uint32_t FW = 4 * SB;
                 const uint32_t MASK = ((1u << FW) - 1u) << esh8, R = (32u + esh8 - FW * t) & 31u;
 #pragma unroll
@@ -192,7 +189,7 @@ __device__ __forceinline__ int k_segment(float (&acc)[NU][4], const uint8_t* sm,
                     lo[i] = v.x;
                     hi[i] = v.y;
                 }
-            } else if constexpr (KIND == 3 || KIND == 4) {     // pair tables
+            } else if constexpr (KIND <= 4) {                  // pair tables
                 constexpr uint32_t FW = 2 * SB;
                 const uint32_t MASK = ((1u << FW) - 1u) << esh8;
                 const uint32_t R0 = (64u + esh8 - 2 * FW * t) & 31u, R1 = (64u + esh8 - 2 * FW * t - FW) & 31u;
@@ -245,6 +242,7 @@ struct KLane {
     uint32_t k_row8, kn_row8;  // byte distance between rows r and r + 8
     uint32_t k_p0;             // bit phase of the packed rows inside their first aligned word
     uint32_t j, lane;
+    bool kn_words;             // norm rows start on 4-byte boundaries
 };
 
 #ifndef BGTQ_JIT
@@ -306,23 +304,42 @@ __device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, con
 __device__ __forceinline__ uint32_t field_to(uint32_t x, uint32_t to, uint32_t pos) {
     return pos < to ? x << (to - pos) : x >> (pos - to);
 }
-template <class HeadT, int SG, int NU>
-__device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm, const KLane& kl) {
+// PW = index of the 32-bit word of the token's norm row that `nw` holds (norms 2 PW and 2 PW + 1), -1: none yet.
+template <class HeadT, int SG, int NU, int PW>
+__device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, uint32_t (&nw)[2 * NU]) {
     constexpr jit::SegC c = HeadT::seg[SG];
     constexpr int SB = c.kind, Q = c.q;
     constexpr int CAP = c.kind == 3 ? 8 : 32 / SB, TILES = CAP / 4;
     constexpr bool f16n = c.f16_norm != 0;
+    constexpr int W = c.norm_idx >> 1;
+    if constexpr (W != PW) {
+        // the token's norms two at a time when its norm row sits on a 4-byte boundary (the four lanes of a quad
+        // read one address, so a row costs one wavefront either way, but half as many loads)
+        if (kl.kn_words) {
+#pragma unroll
+            for (int i = 0; i < 2 * NU; ++i) nw[i] = ld32(sm, kl.rowN + 4u * W + i * kl.kn_row8);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 2 * NU; ++i)
+                nw[i] = ld16(sm, kl.rowN + 4u * W + i * kl.kn_row8) | (ld16(sm, kl.rowN + 4u * W + 2u + i * kl.kn_row8) << 16);
+        }
+    }
     float nrm[2 * NU];
     uint32_t n2[2 * NU];
 #pragma unroll
     for (int i = 0; i < 2 * NU; ++i) {
-        const uint32_t nh = ld16(sm, kl.rowN + 2u * c.norm_idx + i * kl.kn_row8);
-        n2[i] = nh | (nh << 16);
-        nrm[i] = f16n ? 1.0f : f16_bits_to_float(nh);
+        n2[i] = __byte_perm(nw[i], 0u, (c.norm_idx & 1) ? 0x3232 : 0x1010);
+        nrm[i] = f16n ? 1.0f : f16_bits_to_float((c.norm_idx & 1) ? nw[i] >> 16 : nw[i]);
     }
     float acc[NU][4];     // the segment's first k-tile starts it from zero
-    const uint32_t lbit = kl.k_p0 + (uint32_t)c.bit0 + kl.j * (uint32_t)c.lane_bits;
-    const uint32_t tb = kl.lut + (uint32_t)c.tbl + ((kl.lane & ((1u << c.rep_log2) - 1u)) << c.ent_log2);
+    // Lanes of a quad past the segment's last code (short segments: c.jv < 4 lanes hold codes) meet zero query
+    // fragments.  They read what the quad's last live lane reads, and the lookup-table replica is chosen per
+    // (token row, live lane), so that the 8 c.jv distinct addresses of a lookup fall into different banks
+    // whenever the table has that many replicas.
+    const uint32_t jj = c.jv < 4 ? min(kl.j, (uint32_t)(c.jv - 1)) : kl.j;
+    const uint32_t rep = c.jv < 4 ? (kl.lane >> 2) * (uint32_t)c.jv + jj : kl.lane;
+    const uint32_t lbit = kl.k_p0 + (uint32_t)c.bit0 + jj * (uint32_t)c.lane_bits;
+    const uint32_t tb = kl.lut + (uint32_t)c.tbl + ((rep & ((1u << c.rep_log2) - 1u)) << c.ent_log2);
 #pragma unroll
     for (int cc = 0; cc < Q; cc += CAP) {
         const uint32_t pbit = lbit + (uint32_t)(cc * SB);
@@ -337,7 +354,7 @@ __device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm
                 const bool full = Q - cc - 4 * t >= 4;         // else codes 2, 3 meet a zero query fragment
                 const uint2 bq = ld64(sm, kl.qf + (c.step0 + (cc + 4 * t) / 4) * 256);
                 uint32_t lo[2 * NU], hi[2 * NU];
-                if constexpr (c.kind == 1 || c.kind == 2) {    // quad tables: one 64-bit lookup per row
+                if constexpr (c.kind == 1) {                   // quad table: one 64-bit lookup per row
                     constexpr uint32_t ESH = c.esh, FW = 4 * SB;
                     constexpr uint32_t MASK = ((1u << FW) - 1u) << ESH;
 #pragma unroll
@@ -346,7 +363,7 @@ __device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm
                         lo[i] = v.x;
                         hi[i] = v.y;
                     }
-                } else if constexpr (c.kind == 3 || c.kind == 4) {   // pair tables
+                } else if constexpr (c.kind <= 4) {            // pair tables
                     constexpr uint32_t ESH = c.esh, FW = 2 * SB;
                     constexpr uint32_t MASK = ((1u << FW) - 1u) << ESH;
 #pragma unroll
@@ -395,16 +412,17 @@ __device__ __forceinline__ void k_segment_c(float (&S)[NU][4], const uint8_t* sm
         S[u][3] = fmaf(nrm[2 * u + 1], acc[u][3], S[u][3]);
     }
 }
-template <class HeadT, int SG, int NU>
-__device__ __forceinline__ void k_side_from(float (&S)[NU][4], const uint8_t* sm, const KLane& kl) {
+template <class HeadT, int SG, int NU, int PW>
+__device__ __forceinline__ void k_side_from(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, uint32_t (&nw)[2 * NU]) {
     if constexpr (SG < HeadT::n_seg) {
-        k_segment_c<HeadT, SG, NU>(S, sm, kl);
-        k_side_from<HeadT, SG + 1, NU>(S, sm, kl);
+        k_segment_c<HeadT, SG, NU, PW>(S, sm, kl, nw);
+        k_side_from<HeadT, SG + 1, NU, (HeadT::seg[SG].norm_idx >> 1)>(S, sm, kl, nw);
     }
 }
 template <int NU>
 __device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, const KLane& kl, const int h) {
-#define BGTQ_JIT_CASE(H) case H: k_side_from<jit::Head<H>, 0, NU>(S, sm, kl); break;
+    uint32_t nw[2 * NU];
+#define BGTQ_JIT_CASE(H) case H: k_side_from<jit::Head<H>, 0, NU, -1>(S, sm, kl, nw); break;
     switch (h) { BGTQ_JIT_CASES }       // one case per head of the layer, spelled by the prelude
 #undef BGTQ_JIT_CASE
 }
@@ -414,11 +432,7 @@ __device__ __forceinline__ void k_side(float (&S)[NU][4], const uint8_t* sm, con
 template <int VB, int NU>
 __global__ void __launch_bounds__(kDecThreads, 1) decode_kernel(const __grid_constant__ DecParams P) {
 #else
-#ifdef BGTQ_EXP_NU
-constexpr int VB = BGTQ_JIT_VB, NU = BGTQ_EXP_NU;
-#else
 constexpr int VB = BGTQ_JIT_VB, NU = BGTQ_JIT_NU;
-#endif
 extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(const __grid_constant__ DecParams P) {
 #endif
     extern __shared__ __align__(128) uint8_t smem[];
@@ -435,8 +449,6 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
     uint64_t* lutbar = full + kDecStages;
     unsigned int* done = reinterpret_cast<unsigned int*>(lutbar + 1);        // warps finished with a stage, ever
     uint2* qfrag = reinterpret_cast<uint2*>(smem + kOffQf);                  // [step][lane]
-    float* mm = reinterpret_cast<float*>(smem + kOffMM);                     // [warp][8] running max
-    float* ml = mm + kDecWarps * 8;                                          // [warp][8] denominators
     const uint8_t* sm = smem;
     const uint32_t sbase = smem_u32(smem);
     const uint32_t lut_abs = (sbase + kOffMisc + kLutAlign - 1u) & ~(kLutAlign - 1u);   // see the layout comment
@@ -477,13 +489,25 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
 
     grid_dependency_wait();
     // ---- this CTA's range of items ---------------------------------------------------------------------
+    // (32-bit unsigned arithmetic: a 64-bit division costs a few hundred cycles of every CTA's start-up, and
+    // item counts that need one do not occur: the launch wrapper rejects them)
+    // (the item-range table, if the plan carries one, is requested first: its latency passes behind the divisions)
+    const int32_t* part = P.plan.partition;
+    uint32_t pk0 = 0, pk1 = 0, pk2 = 0, pk3 = 0, p_lo = 0, p_hi = 0;
+    if (part) {
+        pk0 = (uint32_t)__ldg(part);
+        pk1 = (uint32_t)__ldg(part + 1);
+        pk2 = (uint32_t)__ldg(part + 2);
+        pk3 = (uint32_t)__ldg(part + 3);
+        p_lo = (uint32_t)__ldg(part + kPartHeader + cta);
+        p_hi = (uint32_t)__ldg(part + kPartHeader + cta + 1);
+    }
     const int t_live = P.pos_dev ? min(P.t_end, *P.pos_dev + P.pos_add) : P.t_end;
-    const int n_tok = max(0, t_live - P.t_begin);
-    const int units = (n_tok + 31) >> 5;                             // 32-token warp units per pair
-    const int c_units = max(1, (units + P.n_splits - 1) / P.n_splits);  // units per item
-    const int n_live = (units + c_units - 1) / c_units;              // non-empty items per pair (<= n_splits)
-    const int n_pairs = P.n_batch * P.n_kv;
-    const int64_t n_items = (int64_t)n_pairs * n_live;
+    const uint32_t n_tok = (uint32_t)max(0, t_live - P.t_begin);
+    const uint32_t units = (n_tok + 31u) >> 5;                          // 32-token warp units per pair
+    const uint32_t c_units = max(1u, (units + (uint32_t)P.n_splits - 1u) / (uint32_t)P.n_splits);  // units per item
+    const uint32_t n_live = (units + c_units - 1u) / c_units;           // non-empty items per pair (<= n_splits)
+    const uint32_t n_items = (uint32_t)(P.n_batch * P.n_kv) * n_live;
     if (n_items == 0) {     // no tokens at all: every slot of every row is an empty split
         for (int64_t i = (int64_t)cta * kDecThreads + tid; i < (int64_t)P.n_batch * P.n_q * P.n_splits;
              i += (int64_t)n_cta * kDecThreads)
@@ -491,47 +515,72 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
         if (tables_pending) wait_tables();
         return;
     }
-    const int64_t item_lo = (int64_t)cta * n_items / n_cta, item_hi = (int64_t)(cta + 1) * n_items / n_cta;
+    // Equal item counts, unless the caller's table was made for exactly this launch (the same items per pair,
+    // pairs, CTAs and units per item: every CTA sees the same four words, so all take the same branch)
+    uint32_t item_lo = (uint32_t)cta * n_items / (uint32_t)n_cta;
+    uint32_t item_hi = ((uint32_t)cta + 1u) * n_items / (uint32_t)n_cta;
+    if (part && pk0 == n_live && pk1 == (uint32_t)(P.n_batch * P.n_kv) && pk2 == (uint32_t)n_cta && pk3 == c_units) {
+        item_lo = min(p_lo, n_items);
+        item_hi = min(max(p_hi, item_lo), n_items);
+    }
 
     const uint64_t pol = l2_evict_first_policy();
     uint32_t g_it = 0;                      // tiles streamed so far by this CTA (stage = g_it % stages)
     const uint32_t lane4 = (uint32_t)lane << 2;
     constexpr uint32_t kVSh = VCfg<VB>::REP_SHIFT + 2;
 
-    for (int64_t item = item_lo; item < item_hi;) {
-        const int pair = (int)(item / n_live), s0 = (int)(item - (int64_t)pair * n_live);
-        const int cnt = (int)min((int64_t)(n_live - s0), item_hi - item);
-        item += cnt;
-        const int h = pair / P.n_batch, b = pair - h * P.n_batch;
+    // The run that starts at item `item`: consecutive items of one (head, batch) pair, up to the CTA's last.
+    struct Run { int h, b, s0, cnt, t0, t1; };
+    auto run_at = [&](uint32_t item) {
+        Run R;
+        const uint32_t pair = item / n_live;
+        R.s0 = (int)(item - pair * n_live);
+        R.cnt = (int)min(n_live - (uint32_t)R.s0, item_hi - item);
+        R.h = (int)(item / (n_live * (uint32_t)P.n_batch));     // = pair / n_batch, without waiting for `pair`
+        R.b = (int)pair - R.h * P.n_batch;
+        R.t0 = P.t_begin + 32 * R.s0 * (int)c_units;
+        R.t1 = min(t_live, P.t_begin + 32 * (R.s0 + R.cnt) * (int)c_units);
+        return R;
+    };
+    // Stream tile `it` of a run into the stage of running tile number `git`.  Called by a whole warp: lanes
+    // 0..3 each request one of the four arrays (packed K, K norms, packed V, V norms), so the address
+    // arithmetic of a tile takes one lane's worth of time instead of four.
+    auto issue_tile = [&](const Run& R, int it, uint32_t git) {
+        const int st = git % kDecStages;
+        const int t = R.t0 + it * kTileTok;
+        const int nt = min(kTileTok, R.t1 - t);
+        const int a = lane & 3;
+        const uint8_t* base = a == 0 ? P.kp : a == 1 ? P.kn : a == 2 ? P.vp : P.vn;
+        const int64_t sb_ = a == 0 ? P.kp_sb : a == 1 ? P.kn_sb : a == 2 ? P.vp_sb : P.vn_sb;
+        const int64_t sh_ = a == 0 ? P.kp_sh : a == 1 ? P.kn_sh : a == 2 ? P.vp_sh : P.vn_sh;
+        const uint32_t st_ = (uint32_t)(a == 0 ? P.kp_st : a == 1 ? P.kn_st : a == 2 ? P.vp_st : P.vn_st);
+        const uint32_t off = a == 0 ? 0u : a == 1 ? P.off_kn : a == 2 ? P.off_v : P.off_vn;
+        const uint8_t* src = base + (size_t)R.b * sb_ + (size_t)R.h * sh_ + (size_t)t * st_;
+        const uint32_t ph = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15u);
+        const uint32_t z = (ph + (uint32_t)nt * st_ + 15u) & ~15u;
+        uint32_t tot = z + __shfl_xor_sync(0xffffffffu, z, 1);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+        if (lane < 4) {
+            // the stage was last touched through the generic proxy (its previous tile's readers, or the merge)
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (lane == 0) mbar_arrive_expect_tx(&full[st], tot);
+            bulk_g2s_hint(smem + P.stage_off + (size_t)st * P.stage_bytes + off, src - ph, z, &full[st], pol);
+        }
+    };
+    // A run's first tile may already be on its way: the previous run's end requests it before merging its warps.
+    bool first_tile_issued = false;
+
+    for (uint32_t item = item_lo; item < item_hi;) {
+        const Run R = run_at(item);
+        item += (uint32_t)R.cnt;
+        const int h = R.h, b = R.b, s0 = R.s0, cnt = R.cnt, t0 = R.t0, t1 = R.t1;
         const DecHeadPlan& hp = P.plan.head[h];
-        const int t0 = P.t_begin + 32 * s0 * c_units;
-        const int t1 = min(t_live, P.t_begin + 32 * (s0 + cnt) * c_units);
         const int n_tiles = (t1 - t0 + kTileTok - 1) / kTileTok;
 
         const size_t bh_kp = (size_t)b * P.kp_sb + (size_t)h * P.kp_sh;
         const size_t bh_kn = (size_t)b * P.kn_sb + (size_t)h * P.kn_sh;
         const size_t bh_vp = (size_t)b * P.vp_sb + (size_t)h * P.vp_sh;
         const size_t bh_vn = (size_t)b * P.vn_sb + (size_t)h * P.vn_sh;
-        // One lane streams tile `it` of the run [t0, t1) into its stage.
-        auto issue_tile = [&](int it, uint32_t git) {
-            const int st = git % kDecStages;
-            const int t = t0 + it * kTileTok;
-            const int nt = min(kTileTok, t1 - t);
-            uint8_t* sb = smem + P.stage_off + (size_t)st * P.stage_bytes;
-            const uint8_t* s0p = P.kp + bh_kp + (size_t)t * P.kp_st;
-            const uint8_t* s1p = P.kn + bh_kn + (size_t)t * P.kn_st;
-            const uint8_t* s2p = P.vp + bh_vp + (size_t)t * P.vp_st;
-            const uint8_t* s3p = P.vn + bh_vn + (size_t)t * P.vn_st;
-            const uint32_t p0 = (uint32_t)(reinterpret_cast<uintptr_t>(s0p) & 15u), p1 = (uint32_t)(reinterpret_cast<uintptr_t>(s1p) & 15u);
-            const uint32_t p2 = (uint32_t)(reinterpret_cast<uintptr_t>(s2p) & 15u), p3 = (uint32_t)(reinterpret_cast<uintptr_t>(s3p) & 15u);
-            const uint32_t z0 = (p0 + (uint32_t)nt * P.kp_st + 15u) & ~15u, z1 = (p1 + (uint32_t)nt * P.kn_st + 15u) & ~15u;
-            const uint32_t z2 = (p2 + (uint32_t)nt * P.vp_st + 15u) & ~15u, z3 = (p3 + (uint32_t)nt * P.vn_st + 15u) & ~15u;
-            mbar_arrive_expect_tx(&full[st], z0 + z1 + z2 + z3);
-            bulk_g2s_hint(sb, s0p - p0, z0, &full[st], pol);
-            bulk_g2s_hint(sb + P.off_kn, s1p - p1, z1, &full[st], pol);
-            bulk_g2s_hint(sb + P.off_v, s2p - p2, z2, &full[st], pol);
-            bulk_g2s_hint(sb + P.off_vn, s3p - p3, z3, &full[st], pol);
-        };
         if (h != h_loaded) {                 // the range crossed into another head (all warps are past the
             if (tables_pending) {            // previous run's closing barrier, nobody reads the old tables)
                 wait_tables();               // a copy still in flight (wrong first guess) lands before the next
@@ -540,12 +589,11 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
             load_tables(h);
             tables_pending = true;
         }
-        if (tid == 0) {                      // first tiles of the run; the stage region is idle (see the run's end)
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            for (int it = 0; it < min(n_tiles, kDecStages); ++it) issue_tile(it, g_it + it);
+        if (warp == 0) {                     // first tiles of the run; their stages are idle (see the run's end)
+            for (int it = first_tile_issued ? 1 : 0; it < min(n_tiles, kDecStages); ++it) issue_tile(R, it, g_it + it);
         }
         // query fragments of this pair: step s, lane (g, jj)
-        for (int s = warp; s < hp.n_steps; s += kDecWarps) {
+        for (int s = kDecWarps - 1 - warp; s < hp.n_steps; s += kDecWarps) {     // (warp 0 is busy with the tiles)
             const DecStepQ st = hp.steps[s];
             const int g = lane >> 2, jj = lane & 3;
             const int pos = (int)st.pos + jj * (int)st.q;
@@ -581,8 +629,9 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
         const uint32_t k_row_al = k_off & ~3u, k_p0 = (k_off & 3u) << 3;
         const uint32_t kn_row = P.off_kn + kn_pre + tok0 * P.kn_st;
         const uint32_t v_off = P.off_v + v_pre + tkv * P.vp_st;
-        const uint32_t vn_row = P.off_vn + vn_pre + tkv * P.vn_st;
+        const uint32_t vn_rowS = P.off_vn + vn_pre + tok0 * P.vn_st;   // V norms of the lane's score rows
         const uint32_t k_row8 = 8u * P.kp_st, kn_row8 = 8u * P.kn_st;
+        const bool kn_words = ((P.kn_st | (P.off_kn + kn_pre)) & 3u) == 0u;
         const uint32_t vtbl = lut_abs + hp.v_tbl + (lane4 & ((1u << kVSh) - 1u));
 
         for (int it = 0; it < n_tiles; ++it, ++g_it) {
@@ -606,46 +655,53 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                 kl.k_p0 = k_p0;
                 kl.j = (uint32_t)j;
                 kl.lane = (uint32_t)lane;
+                kl.kn_words = kn_words;
 #ifndef BGTQ_JIT
                 k_side<NU>(S, sm, kl, hp);
 #else
-#ifndef BGTQ_ABL_NO_K
                 k_side<NU>(S, sm, kl, h);
 #endif
-#endif
                 // ---------------- online softmax (log2 domain) over the warp's tokens ----------------
-                float sv[NU][4];
+                // Scores stay unscaled until the exponent: 2^(S * scale - max) is one fused multiply-add per value.
                 float x0 = -BGTQ_INF, x1 = -BGTQ_INF;
+                bool okA[NU], okB[NU];
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
-                    const bool okA = tok0 + 16 * u < nt, okB = tok0 + 16 * u + 8 < nt;
-                    sv[u][0] = okA ? S[u][0] * P.scale_log2 : -BGTQ_INF;
-                    sv[u][1] = okA ? S[u][1] * P.scale_log2 : -BGTQ_INF;
-                    sv[u][2] = okB ? S[u][2] * P.scale_log2 : -BGTQ_INF;
-                    sv[u][3] = okB ? S[u][3] * P.scale_log2 : -BGTQ_INF;
-                    x0 = fmaxf(x0, fmaxf(sv[u][0], sv[u][2]));
-                    x1 = fmaxf(x1, fmaxf(sv[u][1], sv[u][3]));
+                    okA[u] = tok0 + 16 * u < nt;
+                    okB[u] = tok0 + 16 * u + 8 < nt;
+                    S[u][0] = okA[u] ? S[u][0] : -BGTQ_INF;
+                    S[u][1] = okA[u] ? S[u][1] : -BGTQ_INF;
+                    S[u][2] = okB[u] ? S[u][2] : -BGTQ_INF;
+                    S[u][3] = okB[u] ? S[u][3] : -BGTQ_INF;
+                    x0 = fmaxf(x0, fmaxf(S[u][0], S[u][2]));
+                    x1 = fmaxf(x1, fmaxf(S[u][1], S[u][3]));
                 }
 #pragma unroll
                 for (int o = 4; o < 32; o <<= 1) {
                     x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, o));
                     x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, o));
                 }
-                const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+                const float n0 = fmaxf(m0, x0 * P.scale_log2), n1 = fmaxf(m1, x1 * P.scale_log2);
                 const float z0 = n0 == -BGTQ_INF ? 0.f : n0, z1 = n1 == -BGTQ_INF ? 0.f : n1;
                 const float al0 = fast_exp2(m0 - z0), al1 = fast_exp2(m1 - z1);
                 m0 = n0;
                 m1 = n1;
+                // P^T fragments carry the V norm of their token (one fp16 per token), so the V side multiplies
+                // nothing: sum_t p_t * (n_t * c_t) = sum_t (p_t * n_t) * c_t.  Rows past the run's end hold
+                // stale bytes: their norm reads as zero, like their p.
                 uint32_t pf[NU][2];
                 float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
-                    const float p0 = fast_exp2(sv[u][0] - z0), p1 = fast_exp2(sv[u][1] - z1);
-                    const float p2 = fast_exp2(sv[u][2] - z0), p3 = fast_exp2(sv[u][3] - z1);
+                    const float p0 = fast_exp2(fmaf(S[u][0], P.scale_log2, -z0)), p1 = fast_exp2(fmaf(S[u][1], P.scale_log2, -z1));
+                    const float p2 = fast_exp2(fmaf(S[u][2], P.scale_log2, -z0)), p3 = fast_exp2(fmaf(S[u][3], P.scale_log2, -z1));
                     ps0 += p0 + p2;
                     ps1 += p1 + p3;
-                    pf[u][0] = movmatrix_trans(pack_half2(p0, p1));
-                    pf[u][1] = movmatrix_trans(pack_half2(p2, p3));
+                    const uint32_t rn = sb + vn_rowS + 16u * u * P.vn_st;
+                    const float nA = okA[u] ? f16_bits_to_float(ld16(sm, rn)) : 0.f;
+                    const float nB = okB[u] ? f16_bits_to_float(ld16(sm, rn + 8u * P.vn_st)) : 0.f;
+                    pf[u][0] = movmatrix_trans(pack_half2(p0 * nA, p1 * nA));
+                    pf[u][1] = movmatrix_trans(pack_half2(p2 * nB, p3 * nB));
                 }
                 l0 = fmaf(l0, al0, ps0);
                 l1 = fmaf(l1, al1, ps1);
@@ -664,7 +720,6 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                 constexpr uint32_t M = VCfg<VB>::M, G = VCfg<VB>::GROUPS, FW = 2 * VB;
                 constexpr uint32_t IMS = ((1u << FW) - 1u) << kVSh;
                 constexpr int PER = 8 / G;   // k-tiles (dim pairs) per 32-bit group
-#ifndef BGTQ_ABL_NO_V
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
                     uint32_t gA[2], gB[2], gC[2], gD[2];
@@ -674,13 +729,6 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                     load_v16<VB>(sm, base, bit + 8u * P.vp_st, gB);
                     load_v16<VB>(sm, base, bit + 64u * P.vp_st, gC);
                     load_v16<VB>(sm, base, bit + 72u * P.vp_st, gD);
-                    const int tq = tkv + 16 * u;
-                    const uint32_t rn = sb + vn_row + 16u * u * P.vn_st;
-                    const uint32_t hA = tq + 0 < nt ? ld16(sm, rn) : 0u;
-                    const uint32_t hB = tq + 1 < nt ? ld16(sm, rn + P.vn_st) : 0u;
-                    const uint32_t hC = tq + 8 < nt ? ld16(sm, rn + 8 * P.vn_st) : 0u;
-                    const uint32_t hD = tq + 9 < nt ? ld16(sm, rn + 9 * P.vn_st) : 0u;
-                    const uint32_t nab = hA | (hB << 16), ncd = hC | (hD << 16);
 #pragma unroll
                     for (int g = 0; g < (int)G; ++g) {
                         const uint32_t xab = (gA[g] & M) | ((gB[g] & M) << VB), yab = ((gA[g] >> VB) & M) | (gB[g] & (M << VB));
@@ -690,29 +738,26 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                             // index pre-scaled by the entry stride: rotate so the field sits at bit kVSh
                             const uint32_t rt = (32u + kVSh - FW * k) & 31u;
                             uint32_t a[4];
-                            a[0] = hmul2_u32(ld32(sm, (rotl32(xab, rt) & IMS) | vtbl), nab);
-                            a[1] = hmul2_u32(ld32(sm, (rotl32(yab, rt) & IMS) | vtbl), nab);
-                            a[2] = hmul2_u32(ld32(sm, (rotl32(xcd, rt) & IMS) | vtbl), ncd);
-                            a[3] = hmul2_u32(ld32(sm, (rotl32(ycd, rt) & IMS) | vtbl), ncd);
+                            a[0] = ld32(sm, (rotl32(xab, rt) & IMS) | vtbl);
+                            a[1] = ld32(sm, (rotl32(yab, rt) & IMS) | vtbl);
+                            a[2] = ld32(sm, (rotl32(xcd, rt) & IMS) | vtbl);
+                            a[3] = ld32(sm, (rotl32(ycd, rt) & IMS) | vtbl);
                             mma_16816(O[g * PER + k], a, pf[u]);
                         }
                     }
                 }
-#else
-                O[0][0] += __uint_as_float(pf[0][0] + pf[NU - 1][1]);
-#endif
             }
             __syncwarp();
             // Release the stage; the last warp to do so streams the tile that reuses it.  The counter only ever
             // grows: after `use + 1` rounds of this stage all warps have added to it that many times.
+            uint32_t refill = 0u;
             if (lane == 0) {
                 __threadfence_block();
-                if (atomicAdd(&done[st], 1u) == (use + 1u) * kDecWarps - 1u && it + kDecStages < n_tiles) {
-                    __threadfence_block();
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    issue_tile(it + kDecStages, g_it + kDecStages);
-                }
+                refill = atomicAdd(&done[st], 1u) == (use + 1u) * kDecWarps - 1u && it + kDecStages < n_tiles;
+                __threadfence_block();
             }
+            __syncwarp();
+            if (__shfl_sync(0xffffffffu, refill, 0)) issue_tile(R, it + kDecStages, g_it + kDecStages);
         }
 
         // ---------------- merge the warps, write the run's partial ----------------
@@ -721,55 +766,74 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
             l0 += __shfl_xor_sync(0xffffffffu, l0, o);
             l1 += __shfl_xor_sync(0xffffffffu, l1, o);
         }
-        // Every tile of the run has been consumed once all warps are here: the stage region is idle.
+        // Every tile of the run has been consumed once all warps are here: both stages are idle.
         __syncthreads();
-        // Merge buffer [warp][8 queries][kMergeStride]; dim d of a row sits at position (d & 15) * 8 + (d >> 4), so
-        // that the 32 lanes of a warp (dims 16 r + c, queries 2 j + e) store to 32 different banks.
-        float* mo = reinterpret_cast<float*>(smem + P.stage_off);
+        // If this CTA has another run, that run's first tile is requested NOW, into the stage it will use (the
+        // one the last tile did not), so its DRAM latency passes behind the merge, which then stays inside the
+        // other stage.  Otherwise the merge may spread over both.
+        const bool ahead = item < item_hi && kDecStages == 2 && P.stage_bytes >= kMergeBytes;
+        if (ahead && warp == 0) issue_tile(run_at(item), 0, g_it);
+        first_tile_issued = ahead;
+        // Tree merge: at each level the upper half of the live warps hands its (O, m, l) to the lower half through
+        // shared memory, fragment for fragment (thread t of warp w + n stores what thread t of warp w reads, 16
+        // bytes per access), and the lower half folds it into its registers.  Levels alternate between two
+        // regions, so one barrier per level is enough.
+        float4* const mb = reinterpret_cast<float4*>(smem + P.stage_off + (ahead ? ((g_it + 1u) % kDecStages) * P.stage_bytes : 0u));
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            float* base = mo + (warp * 8 + 2 * j) * kMergeStride + 16 * mt + r;    // dim 16 r + 2 mt
-            base[0] = O[mt][0];
-            base[kMergeStride] = O[mt][1];
-            base[8] = O[mt][2];                                                      // dim 16 r + 2 mt + 1
-            base[kMergeStride + 8] = O[mt][3];
+        for (int n = kDecWarps / 2, lvl = 0; n >= 1; n >>= 1, ++lvl) {
+            float4* const reg = mb + ((lvl & 1) ? (kDecWarps / 2) * kMergeSlot : 0);
+            if (warp >= n && warp < 2 * n) {
+                float4* dst = reg + (warp - n) * kMergeSlot + lane;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dst[i * 32] = make_float4(O[i][0], O[i][1], O[i][2], O[i][3]);
+                dst[8 * 32] = make_float4(m0, m1, l0, l1);
+            }
+            __syncthreads();
+            if (warp < n) {
+                const float4* src = reg + warp * kMergeSlot + lane;
+                const float4 ms = src[8 * 32];
+                const float M0 = fmaxf(m0, ms.x), M1 = fmaxf(m1, ms.y);
+                const float Z0 = M0 == -BGTQ_INF ? 0.f : M0, Z1 = M1 == -BGTQ_INF ? 0.f : M1;
+                const float a0 = fast_exp2(m0 - Z0), a1 = fast_exp2(m1 - Z1);
+                const float b0 = fast_exp2(ms.x - Z0), b1 = fast_exp2(ms.y - Z1);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float4 v = src[i * 32];
+                    O[i][0] = fmaf(O[i][0], a0, v.x * b0);
+                    O[i][1] = fmaf(O[i][1], a1, v.y * b1);
+                    O[i][2] = fmaf(O[i][2], a0, v.z * b0);
+                    O[i][3] = fmaf(O[i][3], a1, v.w * b1);
+                }
+                l0 = fmaf(l0, a0, ms.z * b0);
+                l1 = fmaf(l1, a1, ms.w * b1);
+                m0 = M0;
+                m1 = M1;
+            }
         }
-        if (r == 0) {
-            mm[warp * 8 + 2 * j] = m0;
-            mm[warp * 8 + 2 * j + 1] = m1;
-            ml[warp * 8 + 2 * j] = l0;
-            ml[warp * 8 + 2 * j + 1] = l1;
+        if (warp == 0) {
+            // lane (r, j): query heads 2 j, 2 j + 1; dims 16 r + 2 mt, + 1
+            const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int qi = 2 * j + e;
+                if (qi < P.gqa) {
+                    const size_t row = ((size_t)b * P.n_q + (size_t)h * P.gqa + qi) * P.n_splits + s0;
+                    const float inv = e ? i1 : i0;
+#pragma unroll
+                    for (int mt = 0; mt < 8; ++mt)
+                        *reinterpret_cast<float2*>(P.part_o + row * kHD + 16 * r + 2 * mt) =
+                            make_float2(O[mt][e] * inv, O[mt][2 + e] * inv);
+                    const float le = e ? l1 : l0, me = e ? m1 : m0;
+                    if (r == 0) P.part_lse[row] = le > 0.f ? (me + log2f(le)) * 0.6931471805599453f : -BGTQ_INF;
+                }
+            }
         }
-        __syncthreads();
         {
-            // 64 threads per query head; thread t reads positions 2 t, 2 t + 1 = dims d0 and d0 + 16
-            const int qi = tid >> 6, t2 = (tid & 63) * 2, d0 = (t2 & 7) * 16 + (t2 >> 3);
+            // slots merged into this partial, and (after the pair's last live item) the slots past them
+            const int qi = tid >> 6;
             if (qi < P.gqa) {
-                float mx = -BGTQ_INF;
-#pragma unroll
-                for (int w = 0; w < kDecWarps; ++w) mx = fmaxf(mx, mm[w * 8 + qi]);
-                float wgt[kDecWarps], den = 0.f;
-#pragma unroll
-                for (int w = 0; w < kDecWarps; ++w) {
-                    wgt[w] = mx == -BGTQ_INF ? 0.f : exp2f(mm[w * 8 + qi] - mx);
-                    den = fmaf(ml[w * 8 + qi], wgt[w], den);
-                }
-                const float inv = den > 0.f ? 1.f / den : 0.f;
-                float o[2];
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    float v = 0.f;
-#pragma unroll
-                    for (int w = 0; w < kDecWarps; ++w) v = fmaf(mo[(w * 8 + qi) * kMergeStride + t2 + i], wgt[w], v);
-                    o[i] = v * inv;
-                }
                 const size_t row = ((size_t)b * P.n_q + (size_t)h * P.gqa + qi) * P.n_splits;
-                P.part_o[(row + s0) * kHD + d0] = o[0];
-                P.part_o[(row + s0) * kHD + d0 + 16] = o[1];
-                if ((tid & 63) == 0)
-                    P.part_lse[row + s0] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -BGTQ_INF;
-                // slots merged into this partial, and (after the pair's last live item) the slots past them
-                const int s_end = s0 + cnt == n_live ? P.n_splits : s0 + cnt;
+                const int s_end = s0 + cnt == (int)n_live ? P.n_splits : s0 + cnt;
                 for (int s = s0 + 1 + (tid & 63); s < s_end; s += 64) P.part_lse[row + s] = -BGTQ_INF;
             }
         }

@@ -18,7 +18,7 @@ struct TableDims {
 TableDims k_table_dims(int kind, int bw, uint32_t boost) {
     switch (kind) {
         case 1: return {16u, 3u, kRep1};
-        case 2: return {256u, 3u, kRep2 + boost};
+        case 2: return {16u, 2u, kRep2};
         case 3: return {64u, 2u, kRep3};
         case 4: return {256u, 2u, kRep4 + boost};
         default: return {1u << bw, 2u, bw <= 6 ? 5u : (bw == 7 ? 4u : 3u)};
@@ -57,7 +57,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan(const Bgt
     const uint32_t fixed_est = 7168u + kLutAlign + stage_est;
     const uint32_t lut_budget = fixed_est < 227u * 1024u ? 227u * 1024u - fixed_est : 0u;
     uint32_t lut_bytes = 0;
-    for (uint32_t boost = 1;; --boost) {        // more replicas of the 256-entry tables when they fit
+    for (uint32_t boost = 1;; --boost) {        // more replicas of the 256-entry table when they fit
     lut_bytes = 0;
     for (int h = 0; h < n_kv; ++h) {
         const BgtqHeadDesc& d = desc_host[h];
@@ -154,7 +154,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_build_image(co
             const uint16_t* cb = d.codebook + d.seg_lut_off[s];
             const uint32_t cm = (1u << sg.bw) - 1u, reps = 1u << sg.rep_log2;
             const uint32_t sb = sg.kind == 8 ? 8u : sg.kind, smk = (1u << sb) - 1u;
-            const uint32_t entries = sg.kind == 1 ? 16u : sg.kind == 3 ? 64u : sg.kind == 8 ? (1u << sg.bw) : 256u;
+            const uint32_t entries = sg.kind <= 2 ? 16u : sg.kind == 3 ? 64u : sg.kind == 8 ? (1u << sg.bw) : 256u;
             for (uint32_t e = 0; e < entries; ++e) {
                 uint32_t w0, w1 = 0;
                 if (sg.kind == 8) {
@@ -162,7 +162,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_build_image(co
                 } else {
                     auto code = [&](int k) { return ((e >> (k * sb)) & smk) & cm; };
                     w0 = cb[code(0)] | ((uint32_t)cb[code(1)] << 16);
-                    if (sg.kind <= 2) w1 = cb[code(2)] | ((uint32_t)cb[code(3)] << 16);
+                    if (sg.ent_log2 == 3) w1 = cb[code(2)] | ((uint32_t)cb[code(3)] << 16);
                 }
                 for (uint32_t r = 0; r < reps; ++r) {
                     const uint32_t off = sg.tbl + (e << sg.esh) + (r << sg.ent_log2);
@@ -192,13 +192,116 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan_set_image
     return BGTQ_OK;
 }
 
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan_set_partition(BgtqDecodePlan* plan_host,
+                                                                                     const int32_t* partition_dev) {
+    if (!plan_host) return BGTQ_E_BADARG;
+    if (reinterpret_cast<uintptr_t>(partition_dev) & 3u) return BGTQ_E_ALIGN;
+    DecPlanDev pl;
+    memcpy(&pl, plan_host, sizeof(pl));
+    pl.partition = partition_dev;
+    memcpy(plan_host, &pl, sizeof(pl));
+    return BGTQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_grid_size(int32_t n_batch, int32_t n_kv,
+                                                                           int32_t n_splits) {
+    if (n_batch < 1 || n_kv < 1 || n_splits < 1) return BGTQ_E_BADARG;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    else cudaGetLastError();
+    const int64_t items = (int64_t)n_batch * n_kv * n_splits;
+    return (int)(items < sms ? items : sms);
+}
+
+// Item ranges per CTA that even out what the CTAs spend, not what they stream: a CTA pays kRunCostUnits for
+// every run it starts (prologue, merge of its sixteen warps, one more partial), so one whose range straddles
+// a pair boundary gets fewer items than one that stays inside a pair.  Greedy fill under a cost cap, the
+// smallest cap that needs no more than n_cta CTAs found by bisection.  Any non-decreasing table from 0 to the
+// item count gives the same attention result; this one only moves the boundaries.
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_partition(int32_t n_batch, int32_t n_kv,
+                                                                           int32_t n_tokens, int32_t n_splits,
+                                                                           int32_t n_cta, int32_t* table_host,
+                                                                           int32_t table_len) {
+    if (!table_host || n_batch < 1 || n_kv < 1 || n_splits < 1 || n_cta < 1 || n_tokens < 0) return BGTQ_E_BADARG;
+    if (table_len < kPartHeader + n_cta + 1) return BGTQ_E_BADARG;
+    const int64_t units = ((int64_t)n_tokens + 31) / 32;
+    const int64_t c_units = units == 0 ? 1 : (units + n_splits - 1) / n_splits;
+    const int64_t n_live = (units + c_units - 1) / c_units;
+    const int64_t n_pairs = (int64_t)n_batch * n_kv, n_items = n_pairs * n_live;
+    if (n_items * ((int64_t)n_cta + 1) > 0xFFFFFFFFll) return BGTQ_E_TOOBIG;
+    table_host[0] = (int32_t)n_live;
+    table_host[1] = (int32_t)n_pairs;
+    table_host[2] = n_cta;
+    table_host[3] = (int32_t)c_units;
+    int32_t* off = table_host + kPartHeader;
+    const int64_t last_units = units - (n_live - 1) * c_units;     // the last item of a pair may be shorter
+    // What streaming a run of `u` units costs: whole 512-token tiles, and a last partial tile that keeps fewer
+    // warps busy but takes at least half the time of a full one (a tile's time is mostly the latency of one
+    // warp's share of it, which fewer neighbours shorten only so far).
+    auto stream_cost = [](int64_t u) -> int64_t {
+        const int64_t part = u % 16;
+        return u - part + (part ? (part < 8 ? 8 : part) : 0);
+    };
+    // CTAs the greedy fill needs under cost cap `cap` (units); fills `off` when `write`
+    auto fill = [&](int64_t cap, bool write) -> int64_t {
+        int64_t cta = 0, closed = 0, run = 0;        // cost of this CTA's finished runs; units of its open run
+        if (write) off[0] = 0;
+        for (int64_t p = 0; p < n_pairs; ++p) {
+            for (int64_t s = 0; s < n_live; ++s) {
+                const int64_t u = s + 1 == n_live ? last_units : c_units;
+                if (closed + kRunCostUnits + stream_cost(run + u) > cap) {
+                    if (closed == 0 && run == 0) return INT64_MAX;     // not even one item fits a fresh CTA
+                    ++cta;
+                    if (write && cta <= n_cta) off[cta] = (int32_t)(p * n_live + s);
+                    closed = run = 0;
+                    if (kRunCostUnits + stream_cost(u) > cap) return INT64_MAX;
+                }
+                run += u;
+            }
+            if (run) {                               // the pair ends: so does the CTA's run
+                closed += kRunCostUnits + stream_cost(run);
+                run = 0;
+            }
+        }
+        const int64_t used = n_items ? cta + 1 : 0;
+        if (write)
+            for (int64_t c = used; c <= n_cta; ++c) off[c] = (int32_t)n_items;
+        return used;
+    };
+    int64_t lo = kRunCostUnits + 1, hi = n_items * (c_units + 8) + n_pairs * kRunCostUnits + kRunCostUnits;
+    while (lo < hi) {
+        const int64_t mid = lo + (hi - lo) / 2;
+        if (fill(mid, false) <= n_cta) hi = mid;
+        else lo = mid + 1;
+    }
+    // What the equal-count split costs under the same model; the table is only worth using when it is cheaper.
+    int64_t equal_max = 0;
+    for (int64_t c = 0; c < n_cta; ++c) {
+        int64_t cost = 0;
+        for (int64_t it = c * n_items / n_cta, end = (c + 1) * n_items / n_cta; it < end;) {
+            const int64_t s0 = it % n_live, cnt = (n_live - s0 < end - it) ? n_live - s0 : end - it;
+            const int64_t u = cnt * c_units - (s0 + cnt == n_live ? c_units - last_units : 0);
+            cost += kRunCostUnits + stream_cost(u);
+            it += cnt;
+        }
+        equal_max = cost > equal_max ? cost : equal_max;
+    }
+    if (lo >= equal_max) {
+        table_host[0] = -1;          // matches no launch: the kernel keeps its equal-count split
+        for (int64_t c = 0; c <= n_cta; ++c) off[c] = (int32_t)(c * n_items / n_cta);
+        return BGTQ_OK;
+    }
+    fill(lo, true);
+    return BGTQ_OK;
+}
+
 extern "C" __attribute__((visibility("default"))) int bgtq_decode_default_splits(int32_t n_batch, int32_t n_kv,
                                                                                  int32_t n_tokens) {
     // The launch cuts every (batch, KV head) pair into n_splits equal items of whole 32-token warp units and
     // hands each of its CTAs (one per SM) a contiguous run of items; consecutive items of one pair inside a
-    // CTA become ONE partial.  So the split count only sets the granularity at which work is balanced, and
-    // finer is better until the partial buffer and the combine's scan over a row's slots grow: aim at four
-    // items per CTA, items of at most one 512-token tile, at most 256 slots per pair.
+    // CTA become ONE partial.  So the split count only sets the granularity at which work is balanced.  Items
+    // of one 512-token tile keep every run a whole number of tiles (a finer cut leaves each run a partial last
+    // tile, which costs more than it balances); below that, aim at four items per CTA; at most 256 slots.
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     else cudaGetLastError();

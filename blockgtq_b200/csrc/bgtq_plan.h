@@ -19,13 +19,15 @@
 //
 //   stored width   entry                      index        replicas  bytes
 //   1 bit          4 codes -> 2 x fp16x2      4 bits       32        4096
-//   2 bits         4 codes -> 2 x fp16x2      8 bits       4 or 8    8192 / 16384
+//   2 bits         2 codes -> fp16x2          4 bits       32        2048
 //   3 bits         2 codes -> fp16x2          6 bits       32        8192
 //   4 bits         2 codes -> fp16x2          8 bits       8 or 16   8192 / 16384
 //   8 bits (5..8)  1 code  -> fp16 (twice)    bw bits      32..8     4096/8192
 //   V (pair of tokens, one dim) -> fp16x2     2*vb bits    32..8     <= 8192
-// (the larger replica counts halve the bank conflicts of the 256-entry tables; the plan uses them when
-// the tables of every head of the layer still leave room for two stages of 512-token tiles)
+// (the larger replica count halves the bank conflicts of the 256-entry table; the plan uses it when the
+// tables of every head of the layer still leave room for two stages of 512-token tiles.  A quad table for
+// 2-bit codes would halve their lookups but, at the 8 replicas that fit, each 64-bit lookup costs twice the
+// wavefronts of two conflict-free 32-bit ones.)
 #pragma once
 #ifndef BGTQ_JIT
 #include <stdint.h>
@@ -37,8 +39,8 @@ constexpr int kMaxSteps = 20;        // m16n8k16 k-tiles per token tile and head
 constexpr int kMaxPlanHeads = 8;     // KV heads per launch
 constexpr uint32_t kLutAlign = 16384; // largest table; the LUT region starts on a multiple of it
 
-// log2 of the replica count per stored width (kind 8: by code width); kinds 2 and 4 take one more when it fits
-constexpr uint32_t kRep1 = 5, kRep2 = 2, kRep3 = 5, kRep4 = 3;
+// log2 of the replica count per stored width (kind 8: by code width); kind 4 takes one more when it fits
+constexpr uint32_t kRep1 = 5, kRep2 = 5, kRep3 = 5, kRep4 = 3;
 
 // One K width segment = one lookup table = one norm group.
 struct DecSeg {
@@ -82,7 +84,14 @@ struct DecPlanDev {
     uint32_t lut_bytes;   // bytes reserved per head in the image and in shared memory (max over heads, multiple of 128)
     const uint8_t* image; // device memory: n_heads images, lut_bytes apart (set with bgtq_decode_plan_set_image)
     const void* jit_kernel;  // host-side handle of the kernel specialised for these heads (bgtq_decode_plan_specialize), or null
+    const int32_t* partition;  // device memory: item ranges per CTA (bgtq_decode_partition), or null: equal item counts
     DecHeadPlan head[kMaxPlanHeads];
 };
+
+// Item-range table of a launch (bgtq_decode_partition): kPartHeader key words the kernel compares with the
+// values it derives itself (items per pair, pairs, CTAs, units per item), then n_cta + 1 item offsets.
+constexpr int kPartHeader = 4;
+// What starting a run costs a CTA (its prologue and the merge of its warps), in 32-token units of streaming.
+constexpr int kRunCostUnits = 16;
 
 }  // namespace bgtq

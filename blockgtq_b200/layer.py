@@ -116,13 +116,28 @@ class LayerTables:
         self.max_mixed_bytes = max(t.pack_meta["nopack_start"] // 2 + t.pack_meta["nopack_len"] for t in k_tables)
         self.head_perm = torch.stack([t.head_perm for t in k_tables]).long().to(self.device)   # (n_kv, 128)
         self._plans = {}
+        self._partition = None
 
     def plan(self, flags: int = 0) -> _lib.DecodePlan:
         p = self._plans.get(flags)
         if p is None:
             p = make_decode_plan(self.desc_host, self.n_kv, flags, self.device)
+            if self._partition is not None:
+                _lib.check(_lib.lib().bgtq_decode_plan_set_partition(C.byref(p[0]), self._partition.data_ptr()),
+                           "bgtq_decode_plan_set_partition")
             self._plans[flags] = p
         return p[0]
+
+    def set_partition(self, table_dev) -> None:
+        """Attach (or, with None, detach) a device copy of a ``decode_partition`` table to this layer's decode
+        plans; the kernel uses it for launches it was made for and ignores it otherwise."""
+        if table_dev is not None and (table_dev.dtype != torch.int32 or not table_dev.is_contiguous()
+                                      or table_dev.device != self.device):
+            raise ValueError("partition table must be a contiguous int32 tensor on the layer's device")
+        self._partition = table_dev
+        ptr = table_dev.data_ptr() if table_dev is not None else None
+        for p in self._plans.values():
+            _lib.check(_lib.lib().bgtq_decode_plan_set_partition(C.byref(p[0]), ptr), "bgtq_decode_plan_set_partition")
 
 
 def _strides3(t: torch.Tensor):
@@ -277,6 +292,26 @@ def step_prepare(layer: LayerTables, q, k, v, t0, k_packed, k_norms, v_packed, v
 
 def default_splits(n_batch: int, n_kv: int, n_tokens: int) -> int:
     return _lib.lib().bgtq_decode_default_splits(n_batch, n_kv, n_tokens)
+
+
+def decode_grid_size(n_batch: int, n_kv: int, n_splits: int) -> int:
+    """CTAs ``decode`` launches for this shape on the current device."""
+    n = _lib.lib().bgtq_decode_grid_size(n_batch, n_kv, n_splits)
+    if n < 1:
+        _lib.check(n, "bgtq_decode_grid_size")
+    return n
+
+
+def decode_partition(n_batch: int, n_kv: int, n_tokens: int, n_splits: int, n_cta: int = None, out=None):
+    """Item-range table (host int32 tensor, ``n_cta + 5`` words) that gives CTAs whose range straddles two
+    (batch, head) pairs fewer items; copy it to the device and attach it with ``LayerTables.set_partition``."""
+    if n_cta is None:
+        n_cta = decode_grid_size(n_batch, n_kv, n_splits)
+    if out is None:
+        out = torch.empty(n_cta + 5, dtype=torch.int32)
+    _lib.check(_lib.lib().bgtq_decode_partition(n_batch, n_kv, n_tokens, n_splits, n_cta, out.data_ptr(), out.numel()),
+               "bgtq_decode_partition")
+    return out
 
 
 def decode(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_norms, t_begin, t_end, *,

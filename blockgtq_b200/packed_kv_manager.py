@@ -23,7 +23,8 @@ import torch
 
 from . import _lib
 from .calib import packed_v_bytes
-from .layer import (HD, LayerTables, buffer_attn, combine, combine_ranks, decode, default_splits, encode, rotate_q,
+from .layer import (HD, LayerTables, buffer_attn, combine, combine_ranks, decode, decode_grid_size, decode_partition,
+                    default_splits, encode, rotate_q,
                     step_prepare)
 from .quantizer import BlockGTQQuantizer, build_batched_encode_args
 
@@ -56,6 +57,7 @@ class BlockGTQKVManager:
         self._max_k_packed_bytes = 0
         self._max_n_groups = 0
         self._k_packed = self._k_norms = self._v_packed = self._v_norms = None
+        self._part_dev = self._part_key = None
         # three-region policy
         self.n_sink, self.recent_window, self.block_size = int(n_sink), int(recent_window), int(block_size)
         self._buffered = self.n_sink > 0 or self.recent_window > 0
@@ -136,6 +138,18 @@ class BlockGTQKVManager:
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
         # scratch reused by every layer step (stream ordered): rotated queries and split partials
         self._n_splits = default_splits(self.B, self.n_kv, self.max_T) if dev.type == "cuda" else 1
+        # item ranges of the step's decode launches (one table for every layer: same shape, same length),
+        # refreshed when the cache length changes the way the kernel cuts it into items
+        self._part_key = None
+        self._part_dev = None
+        if dev.type == "cuda":
+            self._part_cta = decode_grid_size(self.B, self.n_kv, self._n_splits)
+            self._part_host = torch.empty(self._part_cta + 5, dtype=torch.int32)
+            self._part_dev = torch.full((self._part_cta + 5,), -1, dtype=torch.int32, device=dev)
+            for lt in self._layers:
+                if lt is not None:
+                    lt.set_partition(self._part_dev)
+        self._prepare_decode_plans()
         self._q_rot = torch.empty(self.B, self.n_q, self.hd, dtype=torch.float16, device=dev)
         self._part_o = torch.empty(self.B, self.n_q, self._n_splits, self.hd, dtype=torch.float32, device=dev)
         self._part_lse = torch.empty(self.B, self.n_q, self._n_splits, dtype=torch.float32, device=dev)
@@ -150,6 +164,18 @@ class BlockGTQKVManager:
             self._k_buf = torch.zeros(self.n_layers, self.B, self.n_kv, self._buf_cap, self.hd,
                                       dtype=torch.float16, device=dev)
             self._v_buf = torch.zeros_like(self._k_buf)
+
+    def _prepare_decode_plans(self):
+        """Build every layer's decode plan (table image + kernel specialised for the layer, a second or two of
+        NVRTC each) up front and on several host threads, instead of one by one at the first decode step."""
+        if self.device.type != "cuda":
+            return
+        from concurrent.futures import ThreadPoolExecutor
+        layers = [lt for lt in self._layers if lt is not None]
+        pd = _lib.DEC_PROGRAMMATIC
+        flag_sets = {self._dec_flags, self._dec_flags | pd}
+        with ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as ex:     # one layer per job: its flag
+            list(ex.map(lambda lt: [lt.plan(f) for f in sorted(flag_sets)], layers))  # variants share one kernel
 
     # -- encode --------------------------------------------------------------------------
     def _encode_kv(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, t_start: int, t_end: int):
@@ -270,6 +296,30 @@ class BlockGTQKVManager:
         if self._pos_dirty:
             self._pos.fill_(self._seq_len)
             self._pos_dirty = False
+        self._refresh_partition()
+
+    def _step_decode_pos_add(self) -> int:
+        """What the step's decode adds to the device-side position to get its live token count."""
+        if self._buffered:
+            return -(self.n_sink + self.recent_window)
+        return 1 if (self._exchange is None or self._exchange.is_owner) else 0
+
+    def _refresh_partition(self):
+        """Keep the decode launches' item-range table in step with the cache length.  The table depends on the
+        length only through the number of items per (batch, head) pair and their size, which change every few
+        hundred tokens; a table made for another length is ignored by the kernel, so this is about balance
+        only."""
+        if self._part_dev is None or torch.cuda.is_current_stream_capturing():
+            return      # (inside a caller's capture the table is refreshed by increment_seq_len, outside it)
+        n_tok = max(0, min(self.max_T, self._seq_len + self._step_decode_pos_add()))
+        units = (n_tok + 31) // 32
+        c_units = max(1, -(-units // self._n_splits))
+        key = (-(-units // c_units), c_units)
+        if key == self._part_key:
+            return
+        self._part_key = key
+        decode_partition(self.B, self.n_kv, n_tok, self._n_splits, self._part_cta, out=self._part_host)
+        self._part_dev.copy_(self._part_host)      # stream ordered: lands before the next step's launches
 
     def _layer_step(self, li: int, rope: bool = False):
         """rotate_q -> append K,V at *pos -> decode over [0, *pos + 1) -> combine, all on static buffers."""
@@ -430,6 +480,8 @@ class BlockGTQKVManager:
         if self._pos is not None and not self._pos_dirty:
             self._pos.add_(by)
         _, self.n_packed, _ = self._region_sizes(self._seq_len)
+        if self._k_packed is not None:
+            self._refresh_partition()
 
     def release_graphs(self):
         """Drop the captured per-layer CUDA graphs (they are re-captured on the next step).  Call this before

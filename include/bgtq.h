@@ -254,6 +254,21 @@ int bgtq_decode_plan_set_image(BgtqDecodePlan* plan_host, const uint8_t* image_d
 int bgtq_decode_plan_specialize(BgtqDecodePlan* plan_host, int32_t compile_only, char* log, int64_t log_bytes);
 int bgtq_jit_set_nvrtc_path(const char* path_host);
 
+/* Optional item-range table of a launch.  bgtq_decode cuts every (batch, KV head) pair into items and hands
+ * each of its CTAs a contiguous range of them; by default every CTA gets the same number.  A CTA whose range
+ * straddles two pairs merges its warps and writes a partial twice, so it finishes later than the others:
+ * bgtq_decode_partition fills a table (host memory, table_len >= n_cta + 5 words) that gives such CTAs fewer
+ * items.  n_cta = bgtq_decode_grid_size(...) for the same shape and n_splits.  The caller copies the table
+ * to device memory (4-byte aligned) and records the address with bgtq_decode_plan_set_partition (NULL takes it
+ * out again); the kernel uses it only when its first four words match the launch (same number of live items
+ * per pair, pairs, CTAs and item size) and falls back to equal counts otherwise, so a stale table costs
+ * balance, never correctness.  The table depends on the shape and on the token count through
+ * ceil(tokens / 32) only; the reference has no counterpart (its kernel takes one program per split). */
+int bgtq_decode_grid_size(int32_t n_batch, int32_t n_kv, int32_t n_splits);
+int bgtq_decode_partition(int32_t n_batch, int32_t n_kv, int32_t n_tokens, int32_t n_splits, int32_t n_cta,
+                          int32_t* table_host, int32_t table_len);
+int bgtq_decode_plan_set_partition(BgtqDecodePlan* plan_host, const int32_t* partition_dev);
+
 /* Number of partial slots per (batch, KV head) pair the library suggests for a
  * (batch, heads, tokens) shape on the current device (host helper, no GPU work):
  * fine enough that every SM gets the same number of token tiles. */

@@ -34,7 +34,7 @@ class HeadPlan(C.Structure):
 
 class Plan(C.Structure):
     _fields_ = [("n_heads", C.c_int32), ("flags", C.c_int32), ("v_bits", C.c_int32), ("v_sbits", C.c_int32),
-                ("v_rep_log2", C.c_uint32), ("lut_bytes", C.c_uint32), ("image", C.c_void_p), ("jit_kernel", C.c_void_p),
+                ("v_rep_log2", C.c_uint32), ("lut_bytes", C.c_uint32), ("image", C.c_void_p), ("jit_kernel", C.c_void_p), ("partition", C.c_void_p),
                 ("head", HeadPlan * 8)]
 
 
@@ -86,13 +86,13 @@ def _kernel_values(row, sg, img, lane):
             if 4 * t >= n:
                 break
             full = n - 4 * t >= 4
-            if kind in (1, 2):
+            if kind == 1:
                 fw = 4 * sb
                 mask = ((1 << fw) - 1) << sg.esh
                 a = (_rotl(cur, (32 + sg.esh - fw * t) & 31) & mask) | tb
                 assert a % 8 == 0
                 lo, hi = w32(a), w32(a + 4)
-            elif kind in (3, 4):
+            elif kind <= 4:
                 fw = 2 * sb
                 mask = ((1 << fw) - 1) << sg.esh
                 lo = w32((_rotl(cur, (64 + sg.esh - 2 * fw * t) & 31) & mask) | tb)
@@ -135,7 +135,7 @@ def test_plan_and_image_reproduce_every_code(case):
         spans = []
         for s in range(hp.n_seg):
             sg = hp.seg[s]
-            size = ((16 if sg.kind == 1 else 64 if sg.kind == 3 else (1 << sg.bw) if sg.kind == 8 else 256)
+            size = ((16 if sg.kind <= 2 else 64 if sg.kind == 3 else (1 << sg.bw) if sg.kind == 8 else 256)
                     << sg.ent_log2) << sg.rep_log2
             assert sg.esh == sg.ent_log2 + sg.rep_log2 and sg.tbl % size == 0 and size <= 16384
             spans.append((sg.tbl, sg.tbl + size))

@@ -260,3 +260,42 @@ def test_bake_helpers_rewrite_every_layers_q_proj():
         assert torch.equal(twin.model.layers[li].self_attn.q_proj.weight.data,
                            model.model.layers[li].self_attn.q_proj.weight.data)
     assert all(z._q_perm_baked for row in mgr.quantizers for z in row)
+
+
+def test_decode_partition_tables():
+    """bgtq_decode_partition: header = what the kernel derives for the launch; offsets non-decreasing from 0 to
+    the item count; CTAs whose range straddles two (batch, head) pairs get fewer items than those inside one
+    pair; shapes where the equal-count split is already as good carry a header that matches no launch."""
+    L = _lib.lib()
+
+    def table(B, H, T, ns, n_cta):
+        buf = (C.c_int32 * (n_cta + 5))()
+        assert L.bgtq_decode_partition(B, H, T, ns, n_cta, buf, n_cta + 5) == 0
+        return np.frombuffer(buf, dtype=np.int32).copy()
+
+    for B, H, T, ns, n_cta in [(8, 2, 32768, 64, 148), (8, 2, 8192, 37, 148), (8, 2, 65536, 128, 148),
+                               (32, 8, 16384, 32, 148), (1, 2, 8192, 256, 148), (8, 2, 100, 4, 64),
+                               (8, 2, 0, 4, 64), (2, 2, 33, 7, 28), (5, 3, 12345, 11, 132)]:
+        t = table(B, H, T, ns, n_cta)
+        units = (T + 31) // 32
+        c_units = max(1, -(-units // ns))
+        n_live = -(-units // c_units)
+        assert t[1] == B * H and t[2] == n_cta and t[3] == c_units
+        assert t[0] in (n_live, -1)
+        off = t[4:]
+        assert off[0] == 0 and off[-1] == B * H * n_live and (np.diff(off) >= 0).all()
+    # the headline shape: 16 pairs of 64 one-tile items on 148 CTAs; ranges that straddle a pair take 6, the others 7
+    t = table(8, 2, 32768, 64, 148)
+    assert t[0] == 64
+    off = t[4:].astype(np.int64)
+    n = np.diff(off)
+    straddles = (off[:-1] // 64) != ((off[1:] - 1) // 64)
+    assert straddles.sum() == 12 and (n[straddles] == 6).all() and (n[~straddles] == 7).all()
+    # nothing to gain: many short pairs per CTA
+    assert table(32, 8, 16384, 32, 148)[0] == -1
+    # argument checks
+    buf = (C.c_int32 * 8)()
+    assert L.bgtq_decode_partition(8, 2, 1000, 4, 64, buf, 8) == -1
+    assert L.bgtq_decode_partition(0, 2, 1000, 4, 64, buf, 8) == -1
+    assert L.bgtq_decode_partition(8, 2, 1000, 4, 64, None, 100) == -1
+    assert L.bgtq_decode_plan_set_partition(None, None) == -1

@@ -661,6 +661,66 @@ def test_decode_result_does_not_depend_on_the_slot_count(gqa, T):
         assert (l - outs[0][1]).abs().max().item() <= 1e-4
 
 
+@pytest.mark.parametrize("B,T,n_splits", [(8, 20000, 40), (8, 4000, 18), (3, 9000, 256)])
+def test_decode_with_an_item_range_table(B, T, n_splits):
+    """An item-range table (bgtq_decode_partition) moves the boundaries between the CTAs' ranges and nothing
+    else: same attention output as the equal-count split; a table made for another cache length is ignored
+    (bit-identical partials to a launch without one); one whose ranges are degenerate (every item in the last
+    CTA) still covers every item."""
+    from blockgtq_b200.layer import combine, decode, decode_grid_size, decode_partition, encode, rotate_q
+    lt, tabs = _layer("a3_1to8")
+    gen = torch.Generator().manual_seed(777 + T)
+    n_kv, gqa = 2, 4
+    n_q = n_kv * gqa
+    k = torch.stack([torch.stack([synth_head(gen, T, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half().to(DEV)
+    kp = torch.zeros(B, n_kv, T + 8, lt.max_tpb, dtype=torch.uint8, device=DEV)
+    kn = torch.zeros(B, n_kv, T + 8, lt.max_ng, dtype=torch.float16, device=DEV)
+    vp = torch.zeros(B, n_kv, T + 8, lt.vpb, dtype=torch.uint8, device=DEV)
+    vn = torch.zeros(B, n_kv, T + 8, dtype=torch.float16, device=DEV)
+    encode(lt, k, v, 0, kp, kn, vp, vn)
+    q_rot = rotate_q(lt, (torch.randn(B, n_q, HD, generator=gen) * 2).half().to(DEV))
+
+    def run():
+        po = torch.full((B, n_q, n_splits, HD), float("nan"), dtype=torch.float32, device=DEV)
+        pl = torch.full((B, n_q, n_splits), float("nan"), dtype=torch.float32, device=DEV)
+        decode(lt, q_rot, kp, kn, vp, vn, 0, T, n_splits=n_splits, part_o=po, part_lse=pl)
+        out, _, lse = combine(po, pl, n_kv, v_rot=lt.v_rot, want_lse=True)
+        torch.cuda.synchronize()
+        assert not torch.isnan(pl).any(), "a slot's LSE was left unwritten"
+        return po, pl, out.float(), lse
+
+    try:
+        po0, pl0, out0, lse0 = run()
+        n_cta = decode_grid_size(B, n_kv, n_splits)
+        table = decode_partition(B, n_kv, T, n_splits, n_cta)
+        lt.set_partition(table.to(DEV))
+        _, pl1, out1, lse1 = run()
+        assert (out1 - out0).abs().max().item() <= 1e-3 and (lse1 - lse0).abs().max().item() <= 1e-4
+        # every item in the last CTA's range: legal, if slow
+        worst = table.clone()
+        worst[0:4] = torch.tensor([int(x) for x in _kernel_item_key(B, n_kv, T, n_splits, n_cta)], dtype=torch.int32)
+        worst[4:4 + n_cta] = 0
+        lt.set_partition(worst.to(DEV))
+        _, pl2, out2, lse2 = run()
+        assert (out2 - out0).abs().max().item() <= 1e-3 and (lse2 - lse0).abs().max().item() <= 1e-4
+        # a table for another length: ignored
+        lt.set_partition(decode_partition(B, n_kv, T // 3, n_splits, n_cta).to(DEV))
+        po3, pl3, _, _ = run()
+        assert torch.equal(pl3, pl0)
+        live = pl0 > -float("inf")
+        assert torch.equal(po3[live], po0[live])
+    finally:
+        lt.set_partition(None)
+
+
+def _kernel_item_key(B, n_kv, T, n_splits, n_cta):
+    """The four words the decode kernel derives for a launch and compares with a table's header."""
+    units = (T + 31) // 32
+    c_units = max(1, -(-units // n_splits))
+    return -(-units // c_units), B * n_kv, n_cta, c_units
+
+
 @pytest.mark.parametrize("case", ["a3_1to6", "a3_1to8", "a2_1to8", "a4_rt1"])
 @pytest.mark.parametrize("mixed", [False, True])
 def test_specialised_and_general_decode_kernels_agree_bit_for_bit(case, mixed):
