@@ -79,6 +79,8 @@ _SIGNATURES = {
     "bgtq_decode_build_image": (C.c_int, [_vp, _vp, _vp, _i64]),
     "bgtq_decode_plan_set_image": (C.c_int, [_vp, _vp]),
     "bgtq_decode_plan_set_partition": (C.c_int, [_vp, _vp]),
+    "bgtq_decode_plan_set_early_fetch": (C.c_int, [_vp, _i32]),
+    "bgtq_decode_plan_set_row_strides": (C.c_int, [_vp, _i32, _i32, _i32, _i32]),
     "bgtq_decode_grid_size": (C.c_int, [_i32, _i32, _i32]),
     "bgtq_decode_partition": (C.c_int, [_i32, _i32, _i32, _i32, _i32, _vp, _i32]),
     "bgtq_decode_plan_specialize": (C.c_int, [_vp, _i32, C.c_char_p, _i64]),

@@ -44,17 +44,13 @@ static int decode_impl(
 
     // Tiles of 16 warps x 32 tokens, two stages; rows too wide for that (padded strides, the nibble layout with
     // large tables) fall back to 16 tokens per warp.
-    auto r16 = [](uint32_t x) { return (x + 15u) & ~15u; };
     int nu = 2;
     size_t smem = 0;
     for (;; --nu) {
         if (nu == 0) return BGTQ_E_TOOBIG;
-        const uint32_t tile = kDecWarps * 16u * nu;
-        // each array: one tile of rows + 15 bytes of leading phase + rounding + slack for the bit-field over-read
-        const uint32_t sz_k = r16(tile * P.kp_st + 48), sz_kn = r16(tile * P.kn_st + 48);
-        const uint32_t sz_v = r16(tile * P.vp_st + 48), sz_vn = r16(tile * P.vn_st + 48);
-        P.off_kn = sz_k; P.off_v = sz_k + sz_kn; P.off_vn = sz_k + sz_kn + sz_v;
-        P.stage_bytes = (sz_k + sz_kn + sz_v + sz_vn + 127u) & ~127u;
+        const StageLayout sl = stage_layout(kDecWarps * 16u * nu, P.kp_st, P.kn_st, P.vp_st, P.vn_st);
+        P.off_kn = sl.off_kn; P.off_v = sl.off_v; P.off_vn = sl.off_vn;
+        P.stage_bytes = sl.stage_bytes;
         P.stage_off = kOffStagesMin + P.plan.lut_bytes;
         const uint32_t region = kDecStages * P.stage_bytes > kMergeBytes ? kDecStages * P.stage_bytes : kMergeBytes;
         smem = (size_t)P.stage_off + region;
@@ -75,7 +71,18 @@ static int decode_impl(
     const bool pdl = (P.plan.flags & BGTQ_DEC_PROGRAMMATIC) != 0;
     cudaError_t e;
     // the kernel specialised for this layer's heads, when the plan carries one (it exists for the wide tile only)
-    const bool jit = P.plan.jit_kernel != nullptr && nu == 2 && !(P.plan.flags & BGTQ_DEC_GENERIC);
+    bool jit = P.plan.jit_kernel != nullptr && nu == 2 && !(P.plan.flags & BGTQ_DEC_GENERIC);
+    if (jit && P.plan.row_st[0] > 0) {
+        // compiled for fixed row strides and for arrays whose every (batch, head) slice and first row start on a
+        // 16-byte boundary: any other launch takes the general kernel
+        const int32_t* rs = P.plan.row_st;
+        auto al16 = [&](const void* p, int64_t sb, int64_t sh, int64_t st) {
+            return ((reinterpret_cast<uintptr_t>(p) | (uint64_t)sb | (uint64_t)sh | (uint64_t)((int64_t)t_begin * st)) & 15u) == 0;
+        };
+        jit = rs[0] == P.kp_st && rs[1] == P.kn_st && rs[2] == P.vp_st && rs[3] == P.vn_st &&
+              al16(P.kp, P.kp_sb, P.kp_sh, P.kp_st) && al16(P.kn, P.kn_sb, P.kn_sh, P.kn_st) &&
+              al16(P.vp, P.vp_sb, P.vp_sh, P.vp_st) && al16(P.vn, P.vn_sb, P.vn_sh, P.vn_st);
+    }
     if (jit) e = launch_decode_jit(P, grid, smem, st, pdl);
     else switch (P.plan.v_sbits) {
         case 1: e = launch_decode_vb1(P, nu, grid, smem, st, pdl); break;

@@ -106,6 +106,12 @@ std::string make_prelude(const DecPlanDev& pl) {
     s += "#define BGTQ_JIT 1\n#define BGTQ_HEAD_DIM 128\n";
     snprintf(buf, sizeof(buf), "#define BGTQ_JIT_VB %d\n#define BGTQ_JIT_NU 2\n", pl.v_sbits);
     s += buf;
+    if (pl.row_st[0] > 0) {       // row strides fixed at compile time (and 16-byte aligned slices promised at launch)
+        snprintf(buf, sizeof(buf), "#define BGTQ_JIT_STRIDES 1\n#define BGTQ_JIT_KP_ST %du\n#define BGTQ_JIT_KN_ST %du\n"
+                                   "#define BGTQ_JIT_VP_ST %du\n#define BGTQ_JIT_VN_ST %du\n#define BGTQ_JIT_STAGE_OFF %uu\n",
+                 pl.row_st[0], pl.row_st[1], pl.row_st[2], pl.row_st[3], kOffStagesMin + pl.lut_bytes);
+        s += buf;
+    }
     s += "typedef unsigned char uint8_t;\ntypedef unsigned short uint16_t;\ntypedef unsigned int uint32_t;\n"
          "typedef int int32_t;\ntypedef long long int64_t;\ntypedef unsigned long long uint64_t;\n"
          "typedef unsigned long long uintptr_t;\n"

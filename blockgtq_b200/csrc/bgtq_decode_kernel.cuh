@@ -126,6 +126,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 __device__ __forceinline__ uint32_t rotl32(uint32_t x, uint32_t n) { return __funnelshift_l(x, x, n); }
+// a / b (b > 0) for the start-up arithmetic every CTA waits on: dividends below 2^22 through the fp32 reciprocal
+// (quotient within one of the truth, then corrected), a third of the latency of the integer sequence.
+__device__ __forceinline__ uint32_t udiv_fast(uint32_t a, uint32_t b) {
+    if (a >= (1u << 22)) return a / b;
+    uint32_t q = (uint32_t)__fdividef(__uint2float_rn(a), __uint2float_rn(b));
+    const uint32_t p = q * b;
+    if (p > a) --q;
+    else if (a - p >= b) ++q;
+    return q;
+}
 
 // 16 codes of one token (bits [bit, bit + 16*VB) past word-aligned offset `row_al`) as one or two
 // 32-bit groups of 8 codes.
@@ -440,6 +450,21 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
     constexpr int kTileTok = kDecWarps * kWarpTok; // tokens per CTA tile
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, j = lane & 3;
+    // Row strides and the stage layout: compile-time constants when the kernel was specialised for them (the
+    // launch wrapper then also guarantees 16-byte aligned array slices, so every phase below is zero and row
+    // offsets fold into the load instructions), launch parameters otherwise.
+#ifdef BGTQ_JIT_STRIDES
+    constexpr uint32_t kp_st = BGTQ_JIT_KP_ST, kn_st = BGTQ_JIT_KN_ST, vp_st = BGTQ_JIT_VP_ST, vn_st = BGTQ_JIT_VN_ST;
+    constexpr StageLayout kSL = stage_layout(kTileTok, kp_st, kn_st, vp_st, vn_st);
+    constexpr uint32_t off_kn = kSL.off_kn, off_v = kSL.off_v, off_vn = kSL.off_vn, stage_bytes = kSL.stage_bytes;
+    constexpr uint32_t stage_off = BGTQ_JIT_STAGE_OFF;
+    constexpr bool kAligned = true;
+#else
+    const uint32_t kp_st = (uint32_t)P.kp_st, kn_st = (uint32_t)P.kn_st, vp_st = (uint32_t)P.vp_st, vn_st = (uint32_t)P.vn_st;
+    const uint32_t off_kn = P.off_kn, off_v = P.off_v, off_vn = P.off_vn, stage_bytes = P.stage_bytes;
+    const uint32_t stage_off = P.stage_off;
+    constexpr bool kAligned = false;
+#endif
 
     // Everything up to grid_dependency_wait() touches only static tables, so under a programmatic
     // launch it overlaps the tail of the preceding kernel (the step's append / query rotation).
@@ -486,12 +511,9 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
     const int n_cta = (int)gridDim.x, cta = (int)blockIdx.x;
     load_tables(min(P.n_kv - 1, (int)(((int64_t)cta * P.n_kv) / n_cta)));   // the head this CTA most likely starts in
     bool tables_pending = true;
-
-    grid_dependency_wait();
-    // ---- this CTA's range of items ---------------------------------------------------------------------
-    // (32-bit unsigned arithmetic: a 64-bit division costs a few hundred cycles of every CTA's start-up, and
-    // item counts that need one do not occur: the launch wrapper rejects them)
-    // (the item-range table, if the plan carries one, is requested first: its latency passes behind the divisions)
+    // The item-range table, if the plan carries one, is requested here, ahead of the dependency wait, so that its
+    // latency passes behind the start-up work (it is written by a copy ordered before the launch that precedes
+    // this one, never by that launch itself).
     const int32_t* part = P.plan.partition;
     uint32_t pk0 = 0, pk1 = 0, pk2 = 0, pk3 = 0, p_lo = 0, p_hi = 0;
     if (part) {
@@ -502,13 +524,22 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
         p_lo = (uint32_t)__ldg(part + kPartHeader + cta);
         p_hi = (uint32_t)__ldg(part + kPartHeader + cta + 1);
     }
+
+    // With early fetch (see bgtq_decode_plan_set_early_fetch) the wait moves behind the first tile requests.
+    const int early_fresh = P.plan.early_fresh;
+    bool dep_waited = early_fresh <= 0;
+    if (dep_waited) grid_dependency_wait();
+    // ---- this CTA's range of items ---------------------------------------------------------------------
+    // (32-bit unsigned arithmetic: a 64-bit division costs a few hundred cycles of every CTA's start-up, and
+    // item counts that need one do not occur: the launch wrapper rejects them)
     const int t_live = P.pos_dev ? min(P.t_end, *P.pos_dev + P.pos_add) : P.t_end;
     const uint32_t n_tok = (uint32_t)max(0, t_live - P.t_begin);
     const uint32_t units = (n_tok + 31u) >> 5;                          // 32-token warp units per pair
-    const uint32_t c_units = max(1u, (units + (uint32_t)P.n_splits - 1u) / (uint32_t)P.n_splits);  // units per item
-    const uint32_t n_live = (units + c_units - 1u) / c_units;           // non-empty items per pair (<= n_splits)
+    const uint32_t c_units = max(1u, udiv_fast(units + (uint32_t)P.n_splits - 1u, (uint32_t)P.n_splits));  // units per item
+    const uint32_t n_live = udiv_fast(units + c_units - 1u, c_units);   // non-empty items per pair (<= n_splits)
     const uint32_t n_items = (uint32_t)(P.n_batch * P.n_kv) * n_live;
     if (n_items == 0) {     // no tokens at all: every slot of every row is an empty split
+        if (!dep_waited) grid_dependency_wait();
         for (int64_t i = (int64_t)cta * kDecThreads + tid; i < (int64_t)P.n_batch * P.n_q * P.n_splits;
              i += (int64_t)n_cta * kDecThreads)
             P.part_lse[i] = -BGTQ_INF;
@@ -517,11 +548,13 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
     }
     // Equal item counts, unless the caller's table was made for exactly this launch (the same items per pair,
     // pairs, CTAs and units per item: every CTA sees the same four words, so all take the same branch)
-    uint32_t item_lo = (uint32_t)cta * n_items / (uint32_t)n_cta;
-    uint32_t item_hi = ((uint32_t)cta + 1u) * n_items / (uint32_t)n_cta;
+    uint32_t item_lo, item_hi;
     if (part && pk0 == n_live && pk1 == (uint32_t)(P.n_batch * P.n_kv) && pk2 == (uint32_t)n_cta && pk3 == c_units) {
         item_lo = min(p_lo, n_items);
         item_hi = min(max(p_hi, item_lo), n_items);
+    } else {
+        item_lo = udiv_fast((uint32_t)cta * n_items, (uint32_t)n_cta);
+        item_hi = udiv_fast(((uint32_t)cta + 1u) * n_items, (uint32_t)n_cta);
     }
 
     const uint64_t pol = l2_evict_first_policy();
@@ -533,10 +566,10 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
     struct Run { int h, b, s0, cnt, t0, t1; };
     auto run_at = [&](uint32_t item) {
         Run R;
-        const uint32_t pair = item / n_live;
+        const uint32_t pair = udiv_fast(item, n_live);
         R.s0 = (int)(item - pair * n_live);
         R.cnt = (int)min(n_live - (uint32_t)R.s0, item_hi - item);
-        R.h = (int)(item / (n_live * (uint32_t)P.n_batch));     // = pair / n_batch, without waiting for `pair`
+        R.h = (int)udiv_fast(item, n_live * (uint32_t)P.n_batch);   // = pair / n_batch, without waiting for `pair`
         R.b = (int)pair - R.h * P.n_batch;
         R.t0 = P.t_begin + 32 * R.s0 * (int)c_units;
         R.t1 = min(t_live, P.t_begin + 32 * (R.s0 + R.cnt) * (int)c_units);
@@ -553,10 +586,10 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
         const uint8_t* base = a == 0 ? P.kp : a == 1 ? P.kn : a == 2 ? P.vp : P.vn;
         const int64_t sb_ = a == 0 ? P.kp_sb : a == 1 ? P.kn_sb : a == 2 ? P.vp_sb : P.vn_sb;
         const int64_t sh_ = a == 0 ? P.kp_sh : a == 1 ? P.kn_sh : a == 2 ? P.vp_sh : P.vn_sh;
-        const uint32_t st_ = (uint32_t)(a == 0 ? P.kp_st : a == 1 ? P.kn_st : a == 2 ? P.vp_st : P.vn_st);
-        const uint32_t off = a == 0 ? 0u : a == 1 ? P.off_kn : a == 2 ? P.off_v : P.off_vn;
+        const uint32_t st_ = a == 0 ? kp_st : a == 1 ? kn_st : a == 2 ? vp_st : vn_st;
+        const uint32_t off = a == 0 ? 0u : a == 1 ? off_kn : a == 2 ? off_v : off_vn;
         const uint8_t* src = base + (size_t)R.b * sb_ + (size_t)R.h * sh_ + (size_t)t * st_;
-        const uint32_t ph = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15u);
+        const uint32_t ph = kAligned ? 0u : (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15u);
         const uint32_t z = (ph + (uint32_t)nt * st_ + 15u) & ~15u;
         uint32_t tot = z + __shfl_xor_sync(0xffffffffu, z, 1);
         tot += __shfl_xor_sync(0xffffffffu, tot, 2);
@@ -564,7 +597,7 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
             // the stage was last touched through the generic proxy (its previous tile's readers, or the merge)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             if (lane == 0) mbar_arrive_expect_tx(&full[st], tot);
-            bulk_g2s_hint(smem + P.stage_off + (size_t)st * P.stage_bytes + off, src - ph, z, &full[st], pol);
+            bulk_g2s_hint(smem + stage_off + (size_t)st * stage_bytes + off, src - ph, z, &full[st], pol);
         }
     };
     // A run's first tile may already be on its way: the previous run's end requests it before merging its warps.
@@ -589,8 +622,23 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
             load_tables(h);
             tables_pending = true;
         }
-        if (warp == 0) {                     // first tiles of the run; their stages are idle (see the run's end)
-            for (int it = first_tile_issued ? 1 : 0; it < min(n_tiles, kDecStages); ++it) issue_tile(R, it, g_it + it);
+        // first tiles of the run; their stages are idle (see the run's end).  Before the dependency wait only
+        // tiles that end below the rows the preceding launch may still be writing are requested.
+        {
+            const int first = first_tile_issued ? 1 : 0, last = min(n_tiles, kDecStages);
+            int held = last;                 // first tile held back until the wait
+            if (!dep_waited) {
+                held = first;
+                while (held < last && t0 + (held + 1) * kTileTok <= t_live - early_fresh) ++held;
+            }
+            if (warp == 0)
+                for (int it = first; it < held; ++it) issue_tile(R, it, g_it + it);
+            if (!dep_waited) {
+                grid_dependency_wait();
+                dep_waited = true;
+                if (warp == 0)
+                    for (int it = held; it < last; ++it) issue_tile(R, it, g_it + it);
+            }
         }
         // query fragments of this pair: step s, lane (g, jj)
         for (int s = kDecWarps - 1 - warp; s < hp.n_steps; s += kDecWarps) {     // (warp 0 is busy with the tiles)
@@ -620,18 +668,18 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
         // Byte phases of the four arrays inside a stage (tiles advance every array by a multiple of 16
         // bytes), and this lane's row offsets.  K side: tokens tok0 + 8 i; V side, row tile u: tokens
         // tkv + 16u + {0, 1, 8, 9}.
-        const uint32_t k_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.kp) + bh_kp + (size_t)t0 * P.kp_st) & 15u);
-        const uint32_t kn_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.kn) + bh_kn + (size_t)t0 * P.kn_st) & 15u);
-        const uint32_t v_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.vp) + bh_vp + (size_t)t0 * P.vp_st) & 15u);
-        const uint32_t vn_pre = (uint32_t)((reinterpret_cast<uintptr_t>(P.vn) + bh_vn + (size_t)t0 * P.vn_st) & 15u);
+        const uint32_t k_pre = kAligned ? 0u : (uint32_t)((reinterpret_cast<uintptr_t>(P.kp) + bh_kp + (size_t)t0 * kp_st) & 15u);
+        const uint32_t kn_pre = kAligned ? 0u : (uint32_t)((reinterpret_cast<uintptr_t>(P.kn) + bh_kn + (size_t)t0 * kn_st) & 15u);
+        const uint32_t v_pre = kAligned ? 0u : (uint32_t)((reinterpret_cast<uintptr_t>(P.vp) + bh_vp + (size_t)t0 * vp_st) & 15u);
+        const uint32_t vn_pre = kAligned ? 0u : (uint32_t)((reinterpret_cast<uintptr_t>(P.vn) + bh_vn + (size_t)t0 * vn_st) & 15u);
         const int tok0 = warp * kWarpTok + r, tkv = warp * kWarpTok + 2 * j;
-        const uint32_t k_off = k_pre + tok0 * P.kp_st;
+        const uint32_t k_off = k_pre + tok0 * kp_st;
         const uint32_t k_row_al = k_off & ~3u, k_p0 = (k_off & 3u) << 3;
-        const uint32_t kn_row = P.off_kn + kn_pre + tok0 * P.kn_st;
-        const uint32_t v_off = P.off_v + v_pre + tkv * P.vp_st;
-        const uint32_t vn_rowS = P.off_vn + vn_pre + tok0 * P.vn_st;   // V norms of the lane's score rows
-        const uint32_t k_row8 = 8u * P.kp_st, kn_row8 = 8u * P.kn_st;
-        const bool kn_words = ((P.kn_st | (P.off_kn + kn_pre)) & 3u) == 0u;
+        const uint32_t kn_row = off_kn + kn_pre + tok0 * kn_st;
+        const uint32_t v_off = off_v + v_pre + tkv * vp_st;
+        const uint32_t vn_rowS = off_vn + vn_pre + tok0 * vn_st;   // V norms of the lane's score rows
+        const uint32_t k_row8 = 8u * kp_st, kn_row8 = 8u * kn_st;
+        const bool kn_words = ((kn_st | (off_kn + kn_pre)) & 3u) == 0u;
         const uint32_t vtbl = lut_abs + hp.v_tbl + (lane4 & ((1u << kVSh) - 1u));
 
         for (int it = 0; it < n_tiles; ++it, ++g_it) {
@@ -639,7 +687,7 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
             const uint32_t use = g_it / kDecStages;
             if (!mbar_wait_bounded(&full[st], use & 1u)) ok = false;
             const int nt = min(kTileTok, t1 - (t0 + it * kTileTok));
-            const uint32_t sb = sbase + P.stage_off + st * P.stage_bytes;
+            const uint32_t sb = sbase + stage_off + st * stage_bytes;
             if (warp * kWarpTok < nt) {
                 // ---------------- S^T = Khat . Qrot^T for NU 16-token row tiles ----------------
                 float S[NU][4];
@@ -697,9 +745,9 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                     const float p2 = fast_exp2(fmaf(S[u][2], P.scale_log2, -z0)), p3 = fast_exp2(fmaf(S[u][3], P.scale_log2, -z1));
                     ps0 += p0 + p2;
                     ps1 += p1 + p3;
-                    const uint32_t rn = sb + vn_rowS + 16u * u * P.vn_st;
+                    const uint32_t rn = sb + vn_rowS + 16u * u * vn_st;
                     const float nA = okA[u] ? f16_bits_to_float(ld16(sm, rn)) : 0.f;
-                    const float nB = okB[u] ? f16_bits_to_float(ld16(sm, rn + 8u * P.vn_st)) : 0.f;
+                    const float nB = okB[u] ? f16_bits_to_float(ld16(sm, rn + 8u * vn_st)) : 0.f;
                     pf[u][0] = movmatrix_trans(pack_half2(p0 * nA, p1 * nA));
                     pf[u][1] = movmatrix_trans(pack_half2(p2 * nB, p3 * nB));
                 }
@@ -723,12 +771,12 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
                     uint32_t gA[2], gB[2], gC[2], gD[2];
-                    const uint32_t rv = sb + v_off + 16u * u * P.vp_st;
+                    const uint32_t rv = sb + v_off + 16u * u * vp_st;
                     const uint32_t base = rv & ~3u, bit = ((rv & 3u) << 3) + 16u * VB * r;
                     load_v16<VB>(sm, base, bit, gA);
-                    load_v16<VB>(sm, base, bit + 8u * P.vp_st, gB);
-                    load_v16<VB>(sm, base, bit + 64u * P.vp_st, gC);
-                    load_v16<VB>(sm, base, bit + 72u * P.vp_st, gD);
+                    load_v16<VB>(sm, base, bit + 8u * vp_st, gB);
+                    load_v16<VB>(sm, base, bit + 64u * vp_st, gC);
+                    load_v16<VB>(sm, base, bit + 72u * vp_st, gD);
 #pragma unroll
                     for (int g = 0; g < (int)G; ++g) {
                         const uint32_t xab = (gA[g] & M) | ((gB[g] & M) << VB), yab = ((gA[g] >> VB) & M) | (gB[g] & (M << VB));
@@ -771,16 +819,19 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
         // If this CTA has another run, that run's first tile is requested NOW, into the stage it will use (the
         // one the last tile did not), so its DRAM latency passes behind the merge, which then stays inside the
         // other stage.  Otherwise the merge may spread over both.
-        const bool ahead = item < item_hi && kDecStages == 2 && P.stage_bytes >= kMergeBytes;
+        const bool ahead = item < item_hi && kDecStages == 2 && stage_bytes >= kMergeBytes;
         if (ahead && warp == 0) issue_tile(run_at(item), 0, g_it);
         first_tile_issued = ahead;
-        // Tree merge: at each level the upper half of the live warps hands its (O, m, l) to the lower half through
-        // shared memory, fragment for fragment (thread t of warp w + n stores what thread t of warp w reads, 16
-        // bytes per access), and the lower half folds it into its registers.  Levels alternate between two
-        // regions, so one barrier per level is enough.
-        float4* const mb = reinterpret_cast<float4*>(smem + P.stage_off + (ahead ? ((g_it + 1u) % kDecStages) * P.stage_bytes : 0u));
+        // Merge of the sixteen warps' (O, m, l).  Two tree levels (16 -> 8 -> 4): the upper half of the live warps
+        // hands its state to the lower half through shared memory, fragment for fragment (thread t of warp w + n
+        // stores what thread t of warp w reads, 16 bytes per access), and the lower half folds it into its
+        // registers.  Then the four remaining warps split the eight dim tiles between them: each sends the other
+        // three the tiles they own, sums what it receives for its own two, normalises and writes them, so the
+        // run's partial leaves through four warps' stores.  The levels alternate between two regions of the
+        // buffer; one barrier per level.
+        float4* const mb = reinterpret_cast<float4*>(smem + stage_off + (ahead ? ((g_it + 1u) % kDecStages) * stage_bytes : 0u));
 #pragma unroll
-        for (int n = kDecWarps / 2, lvl = 0; n >= 1; n >>= 1, ++lvl) {
+        for (int n = kDecWarps / 2, lvl = 0; n >= 4; n >>= 1, ++lvl) {
             float4* const reg = mb + ((lvl & 1) ? (kDecWarps / 2) * kMergeSlot : 0);
             if (warp >= n && warp < 2 * n) {
                 float4* dst = reg + (warp - n) * kMergeSlot + lane;
@@ -810,9 +861,59 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                 m1 = M1;
             }
         }
-        if (warp == 0) {
-            // lane (r, j): query heads 2 j, 2 j + 1; dims 16 r + 2 mt, + 1
-            const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+        // Warp w < 4 owns dim tiles 2 w and 2 w + 1.  Region 0 again (its first-level readers are past the
+        // second level's barrier): piece (owner o, sender w, k) at ((o * 4 + w) * 2 + k) * 32 + lane, the
+        // senders' (m, l) behind the 32 pieces.
+        if (warp < 4) {
+#pragma unroll
+            for (int o = 0; o < 4; ++o)
+                if (o != warp) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k)
+                        mb[((o * 4 + warp) * 2 + k) * 32 + lane] =
+                            make_float4(O[2 * o + k][0], O[2 * o + k][1], O[2 * o + k][2], O[2 * o + k][3]);
+                }
+            mb[(32 + warp) * 32 + lane] = make_float4(m0, m1, l0, l1);
+        }
+        __syncthreads();
+        if (warp < 4) {
+            float4 ms[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) ms[w] = w == warp ? make_float4(m0, m1, l0, l1) : mb[(32 + w) * 32 + lane];
+            const float M0 = fmaxf(fmaxf(ms[0].x, ms[1].x), fmaxf(ms[2].x, ms[3].x));
+            const float M1 = fmaxf(fmaxf(ms[0].y, ms[1].y), fmaxf(ms[2].y, ms[3].y));
+            const float Z0 = M0 == -BGTQ_INF ? 0.f : M0, Z1 = M1 == -BGTQ_INF ? 0.f : M1;
+            float w0[4], w1[4], L0 = 0.f, L1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                w0[w] = fast_exp2(ms[w].x - Z0);
+                w1[w] = fast_exp2(ms[w].y - Z1);
+                L0 = fmaf(ms[w].z, w0[w], L0);
+                L1 = fmaf(ms[w].w, w1[w], L1);
+            }
+            float4 acc[2];
+#pragma unroll
+            for (int o = 0; o < 4; ++o)
+                if (o == warp) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k)
+                        acc[k] = make_float4(O[2 * o + k][0] * w0[o], O[2 * o + k][1] * w1[o], O[2 * o + k][2] * w0[o],
+                                             O[2 * o + k][3] * w1[o]);
+                }
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+                if (w != warp) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const float4 v = mb[((warp * 4 + w) * 2 + k) * 32 + lane];
+                        acc[k].x = fmaf(v.x, w0[w], acc[k].x);
+                        acc[k].y = fmaf(v.y, w1[w], acc[k].y);
+                        acc[k].z = fmaf(v.z, w0[w], acc[k].z);
+                        acc[k].w = fmaf(v.w, w1[w], acc[k].w);
+                    }
+                }
+            // lane (r, j): query heads 2 j, 2 j + 1; dims 16 r + 2 mt, + 1 for mt = 2 warp + k
+            const float i0 = L0 > 0.f ? 1.f / L0 : 0.f, i1 = L1 > 0.f ? 1.f / L1 : 0.f;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int qi = 2 * j + e;
@@ -820,11 +921,12 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                     const size_t row = ((size_t)b * P.n_q + (size_t)h * P.gqa + qi) * P.n_splits + s0;
                     const float inv = e ? i1 : i0;
 #pragma unroll
-                    for (int mt = 0; mt < 8; ++mt)
-                        *reinterpret_cast<float2*>(P.part_o + row * kHD + 16 * r + 2 * mt) =
-                            make_float2(O[mt][e] * inv, O[mt][2 + e] * inv);
-                    const float le = e ? l1 : l0, me = e ? m1 : m0;
-                    if (r == 0) P.part_lse[row] = le > 0.f ? (me + log2f(le)) * 0.6931471805599453f : -BGTQ_INF;
+                    for (int k = 0; k < 2; ++k)
+                        *reinterpret_cast<float2*>(P.part_o + row * kHD + 16 * r + 2 * (2 * warp + k)) =
+                            e ? make_float2(acc[k].y * inv, acc[k].w * inv) : make_float2(acc[k].x * inv, acc[k].z * inv);
+                    const float le = e ? L1 : L0, me = e ? M1 : M0;
+                    if (warp == 0 && r == 0)
+                        P.part_lse[row] = le > 0.f ? (me + log2f(le)) * 0.6931471805599453f : -BGTQ_INF;
                 }
             }
         }
@@ -840,6 +942,7 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
         __syncthreads();      // the merge buffer is free again before the next run's tiles land in it
     }
     if (tables_pending) wait_tables();
+    if (!dep_waited) grid_dependency_wait();     // (a CTA without items: the launch still completes behind its predecessor)
     if (!ok && P.status && lane == 0) atomicExch(P.status, kStatusWaitTimeout);
 }
 

@@ -192,6 +192,34 @@ extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan_set_image
     return BGTQ_OK;
 }
 
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan_set_row_strides(BgtqDecodePlan* plan_host,
+                                                                                       int32_t kp_st, int32_t kn_st,
+                                                                                       int32_t vp_st, int32_t vn_st) {
+    if (!plan_host) return BGTQ_E_BADARG;
+    const bool clear = kp_st == 0 && kn_st == 0 && vp_st == 0 && vn_st == 0;
+    if (!clear && (kp_st < 1 || kp_st > 160 || vp_st < 1 || vp_st > 128 || kn_st < 1 || kn_st > 16 || vn_st < 1 || vn_st > 8))
+        return BGTQ_E_UNSUPPORTED;
+    DecPlanDev pl;
+    memcpy(&pl, plan_host, sizeof(pl));
+    if (pl.jit_kernel) return BGTQ_E_BADARG;       // already specialised: the strides are part of that kernel
+    pl.row_st[0] = kp_st;
+    pl.row_st[1] = 2 * kn_st;                      // bytes, like the kernel's own parameters
+    pl.row_st[2] = vp_st;
+    pl.row_st[3] = 2 * vn_st;
+    memcpy(plan_host, &pl, sizeof(pl));
+    return BGTQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan_set_early_fetch(BgtqDecodePlan* plan_host,
+                                                                                      int32_t fresh_rows) {
+    if (!plan_host || fresh_rows < 0) return BGTQ_E_BADARG;
+    DecPlanDev pl;
+    memcpy(&pl, plan_host, sizeof(pl));
+    pl.early_fresh = fresh_rows;
+    memcpy(plan_host, &pl, sizeof(pl));
+    return BGTQ_OK;
+}
+
 extern "C" __attribute__((visibility("default"))) int bgtq_decode_plan_set_partition(BgtqDecodePlan* plan_host,
                                                                                      const int32_t* partition_dev) {
     if (!plan_host) return BGTQ_E_BADARG;

@@ -85,8 +85,27 @@ struct DecPlanDev {
     const uint8_t* image; // device memory: n_heads images, lut_bytes apart (set with bgtq_decode_plan_set_image)
     const void* jit_kernel;  // host-side handle of the kernel specialised for these heads (bgtq_decode_plan_specialize), or null
     const int32_t* partition;  // device memory: item ranges per CTA (bgtq_decode_partition), or null: equal item counts
+    int32_t early_fresh;       // > 0: rows below (live length - early_fresh) and *pos_dev may be read BEFORE the
+                               // programmatic dependency wait (bgtq_decode_plan_set_early_fetch); 0: nothing is
+    int32_t row_st[4];         // bytes per token of packed K, K norms, packed V, V norms the specialised kernel was
+                               // compiled for (bgtq_decode_plan_set_row_strides), or zeros: strides read at run time
     DecHeadPlan head[kMaxPlanHeads];
 };
+
+// Layout of one stage (a tile of each of the four arrays) in shared memory: byte offsets of the K norms, packed V
+// and V norms behind the packed K, and the stage size.  Each array: one tile of rows + 15 bytes of leading phase
+// + rounding + slack for the bit-field over-read.
+struct StageLayout {
+    uint32_t off_kn, off_v, off_vn, stage_bytes;
+};
+#ifdef BGTQ_JIT
+__device__
+#endif
+constexpr StageLayout stage_layout(uint32_t tile_tokens, uint32_t kp_st, uint32_t kn_st, uint32_t vp_st, uint32_t vn_st) {
+    const uint32_t sz_k = (tile_tokens * kp_st + 48u + 15u) & ~15u, sz_kn = (tile_tokens * kn_st + 48u + 15u) & ~15u;
+    const uint32_t sz_v = (tile_tokens * vp_st + 48u + 15u) & ~15u, sz_vn = (tile_tokens * vn_st + 48u + 15u) & ~15u;
+    return StageLayout{sz_k, sz_k + sz_kn, sz_k + sz_kn + sz_v, (sz_k + sz_kn + sz_v + sz_vn + 127u) & ~127u};
+}
 
 // Item-range table of a launch (bgtq_decode_partition): kPartHeader key words the kernel compares with the
 // values it derives itself (items per pair, pairs, CTAs, units per item), then n_cta + 1 item offsets.

@@ -56,9 +56,11 @@ def _fill_desc(d: _lib.HeadDesc, kt: KHeadTables, vt: VHeadTables):
     C.memmove(d.group_of, go.ctypes.data, HD)
 
 
-def make_decode_plan(desc_host, n_kv: int, flags: int, device):
+def make_decode_plan(desc_host, n_kv: int, flags: int, device, row_strides=None):
     """Decode plan of a layer's KV heads with its lookup-table image uploaded to ``device``.
-    Returns (plan, image tensor); the caller keeps the image alive as long as the plan is used."""
+    Returns (plan, image tensor); the caller keeps the image alive as long as the plan is used.
+    ``row_strides`` = (packed-K bytes, K-norm values, packed-V bytes, V-norm values) per token fixes them in
+    the specialised kernel (launches with other strides or unaligned slices then run the general kernel)."""
     L = _lib.lib()
     p = _lib.DecodePlan()
     _lib.check(L.bgtq_decode_plan(C.byref(desc_host), n_kv, flags, C.byref(p)), "bgtq_decode_plan")
@@ -71,6 +73,9 @@ def make_decode_plan(desc_host, n_kv: int, flags: int, device):
     image = torch.from_numpy(host).to(device)
     _lib.check(L.bgtq_decode_plan_set_image(C.byref(p), image.data_ptr()), "bgtq_decode_plan_set_image")
     if not (flags & _lib.DEC_GENERIC) and not os.environ.get("BGTQ_DEC_NO_JIT") and torch.device(device).type == "cuda":
+        if row_strides is not None:
+            _lib.check(L.bgtq_decode_plan_set_row_strides(C.byref(p), *[int(x) for x in row_strides]),
+                       "bgtq_decode_plan_set_row_strides")
         _specialize(p)
     return p, image
 
@@ -117,16 +122,36 @@ class LayerTables:
         self.head_perm = torch.stack([t.head_perm for t in k_tables]).long().to(self.device)   # (n_kv, 128)
         self._plans = {}
         self._partition = None
+        self._row_strides = {}
+        self._early_fresh = 0
 
     def plan(self, flags: int = 0) -> _lib.DecodePlan:
         p = self._plans.get(flags)
         if p is None:
-            p = make_decode_plan(self.desc_host, self.n_kv, flags, self.device)
+            p = make_decode_plan(self.desc_host, self.n_kv, flags, self.device,
+                                 row_strides=self._row_strides.get(bool(flags & _lib.DEC_K_MIXED)))
             if self._partition is not None:
                 _lib.check(_lib.lib().bgtq_decode_plan_set_partition(C.byref(p[0]), self._partition.data_ptr()),
                            "bgtq_decode_plan_set_partition")
+            if self._early_fresh:
+                _lib.check(_lib.lib().bgtq_decode_plan_set_early_fetch(C.byref(p[0]), self._early_fresh),
+                           "bgtq_decode_plan_set_early_fetch")
             self._plans[flags] = p
         return p[0]
+
+    def set_row_strides(self, kp_st: int, kn_st: int, vp_st: int, vn_st: int, mixed: bool = False) -> None:
+        """Row strides (packed-K bytes, K-norm values, packed-V bytes, V-norm values per token) of the cache
+        this layer's decode launches will read, for plans made after this call: their specialised kernel is
+        compiled for exactly these (see ``bgtq_decode_plan_set_row_strides``)."""
+        self._row_strides[bool(mixed)] = (kp_st, kn_st, vp_st, vn_st)
+
+    def set_early_fetch(self, fresh_rows: int) -> None:
+        """Let programmatic decode launches of this layer stream the cache before their dependency wait; the
+        caller promises what ``bgtq_decode_plan_set_early_fetch`` asks for (0 turns it off again)."""
+        self._early_fresh = int(fresh_rows)
+        for p in self._plans.values():
+            _lib.check(_lib.lib().bgtq_decode_plan_set_early_fetch(C.byref(p[0]), self._early_fresh),
+                       "bgtq_decode_plan_set_early_fetch")
 
     def set_partition(self, table_dev) -> None:
         """Attach (or, with None, detach) a device copy of a ``decode_partition`` table to this layer's decode

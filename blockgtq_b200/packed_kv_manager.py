@@ -132,7 +132,8 @@ class BlockGTQKVManager:
         shape = (self.n_layers, self.B, self.n_kv, cap)
         dev = self.device
         self._k_packed = torch.zeros(*shape, self._max_k_packed_bytes, dtype=torch.uint8, device=dev)[:, :, :, :self.max_T]
-        self._k_norms = torch.zeros(*shape, self._max_n_groups, dtype=torch.float16, device=dev)[:, :, :, :self.max_T]
+        # norm rows of an even number of fp16 values: the decode kernel then reads a token's norms two per load
+        self._k_norms = torch.zeros(*shape, self._norm_row_groups(), dtype=torch.float16, device=dev)[:, :, :, :self.max_T]
         self._v_packed = torch.zeros(*shape, vpb, dtype=torch.uint8, device=dev)[:, :, :, :self.max_T]
         self._v_norms = torch.zeros(*shape, dtype=torch.float16, device=dev)[:, :, :, :self.max_T]
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -149,6 +150,13 @@ class BlockGTQKVManager:
             for lt in self._layers:
                 if lt is not None:
                     lt.set_partition(self._part_dev)
+                    # the cache rows every decode launch of this manager reads (16-byte aligned slices: the
+                    # token capacity is a multiple of 64)
+                    lt.set_row_strides(self._max_k_packed_bytes, self._norm_row_groups(), vpb, 1, mixed=self.k_mixed)
+                    # In a layer step the launch before the decode is the append (one new row + the rotated
+                    # query), and the position is advanced between steps: the decode may start streaming early.
+                    if not os.environ.get("BGTQ_DEC_NO_EARLY_FETCH"):
+                        lt.set_early_fetch(1)
         self._prepare_decode_plans()
         self._q_rot = torch.empty(self.B, self.n_q, self.hd, dtype=torch.float16, device=dev)
         self._part_o = torch.empty(self.B, self.n_q, self._n_splits, self.hd, dtype=torch.float32, device=dev)
@@ -164,6 +172,9 @@ class BlockGTQKVManager:
             self._k_buf = torch.zeros(self.n_layers, self.B, self.n_kv, self._buf_cap, self.hd,
                                       dtype=torch.float16, device=dev)
             self._v_buf = torch.zeros_like(self._k_buf)
+
+    def _norm_row_groups(self) -> int:
+        return self._max_n_groups + (self._max_n_groups & 1)
 
     def _prepare_decode_plans(self):
         """Build every layer's decode plan (table image + kernel specialised for the layer, a second or two of
@@ -513,7 +524,7 @@ class BlockGTQKVManager:
     def cache_memory_bytes(self) -> int:
         """Compressed cache bytes for the current length, padding included (packed_kv_manager.py:375-382)."""
         _, T, n_rec = self._region_sizes(self.seq_len)
-        per_tok = self._max_k_packed_bytes + packed_v_bytes(self.hd, self.v_bits) + self._max_n_groups * 2 + 2
+        per_tok = self._max_k_packed_bytes + packed_v_bytes(self.hd, self.v_bits) + self._norm_row_groups() * 2 + 2
         packed = per_tok * T * self.n_kv * self.B * self.n_layers
         fp16 = (min(self.seq_len, self.n_sink) + n_rec) * self.hd * 2 * 2 * self.n_kv * self.B * self.n_layers
         return packed + fp16

@@ -252,7 +252,23 @@ int bgtq_decode_plan_set_image(BgtqDecodePlan* plan_host, const uint8_t* image_d
  * Returns BGTQ_E_UNSUPPORTED when NVRTC cannot be found (the plan stays usable with the general kernel),
  * BGTQ_E_LAUNCH when compiling or loading fails. */
 int bgtq_decode_plan_specialize(BgtqDecodePlan* plan_host, int32_t compile_only, char* log, int64_t log_bytes);
+/* Before bgtq_decode_plan_specialize: also fix the cache row strides the specialised kernel is compiled for
+ * (kp_st, vp_st in bytes, kn_st, vn_st in fp16 elements, as bgtq_decode takes them), so that row offsets fold
+ * into its load instructions.  bgtq_decode then launches that kernel only for calls with exactly these row
+ * strides whose four arrays, batch strides, head strides and first row (t_begin) all sit on 16-byte
+ * boundaries, and the general kernel for any other call.  All zeros: strides stay launch parameters (default). */
+int bgtq_decode_plan_set_row_strides(BgtqDecodePlan* plan_host, int32_t kp_st, int32_t kn_st, int32_t vp_st,
+                                     int32_t vn_st);
 int bgtq_jit_set_nvrtc_path(const char* path_host);
+
+/* Optional, for launches with BGTQ_DEC_PROGRAMMATIC: let the kernel start streaming the cache before its
+ * programmatic-dependency wait.  fresh_rows > 0 promises that, when the launch that PRECEDES the decode in the
+ * stream starts, (1) the value at pos_dev is final and (2) every cache row below (live length - fresh_rows) is
+ * final: the preceding launch writes nothing but the newest fresh_rows rows (the step's append), the query and
+ * buffers the decode does not read.  The kernel then reads pos_dev, cuts its ranges and requests its first tiles
+ * right away (tiles that reach into the fresh rows are held back), and only waits before it reads the query and
+ * before it writes anything.  0 (default): everything waits.  No counterpart in the reference. */
+int bgtq_decode_plan_set_early_fetch(BgtqDecodePlan* plan_host, int32_t fresh_rows);
 
 /* Optional item-range table of a launch.  bgtq_decode cuts every (batch, KV head) pair into items and hands
  * each of its CTAs a contiguous range of them; by default every CTA gets the same number.  A CTA whose range
@@ -262,7 +278,8 @@ int bgtq_jit_set_nvrtc_path(const char* path_host);
  * to device memory (4-byte aligned) and records the address with bgtq_decode_plan_set_partition (NULL takes it
  * out again); the kernel uses it only when its first four words match the launch (same number of live items
  * per pair, pairs, CTAs and item size) and falls back to equal counts otherwise, so a stale table costs
- * balance, never correctness.  The table depends on the shape and on the token count through
+ * balance, never correctness.  The kernel reads the table before its programmatic-dependency wait: write it with a
+ * copy that is ordered before the launch that precedes the decode, not by that launch.  The table depends on the shape and on the token count through
  * ceil(tokens / 32) only; the reference has no counterpart (its kernel takes one program per split). */
 int bgtq_decode_grid_size(int32_t n_batch, int32_t n_kv, int32_t n_splits);
 int bgtq_decode_partition(int32_t n_batch, int32_t n_kv, int32_t n_tokens, int32_t n_splits, int32_t n_cta,

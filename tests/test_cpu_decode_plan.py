@@ -34,7 +34,7 @@ class HeadPlan(C.Structure):
 
 class Plan(C.Structure):
     _fields_ = [("n_heads", C.c_int32), ("flags", C.c_int32), ("v_bits", C.c_int32), ("v_sbits", C.c_int32),
-                ("v_rep_log2", C.c_uint32), ("lut_bytes", C.c_uint32), ("image", C.c_void_p), ("jit_kernel", C.c_void_p), ("partition", C.c_void_p),
+                ("v_rep_log2", C.c_uint32), ("lut_bytes", C.c_uint32), ("image", C.c_void_p), ("jit_kernel", C.c_void_p), ("partition", C.c_void_p), ("early_fresh", C.c_int32), ("row_st", C.c_int32 * 4),
                 ("head", HeadPlan * 8)]
 
 

@@ -147,7 +147,9 @@ def test_manager_matches_reference():
     same = (mgr._k_packed[:, :, :, :T].cpu().numpy() == g["k_packed"]).mean()
     assert same > 0.9999, same
     assert (mgr._v_packed[:, :, :, :T].cpu().numpy() == g["v_packed"]).mean() > 0.9999
-    kn = mgr._k_norms[:, :, :, :T].float().cpu().numpy()
+    ng = g["k_norms"].shape[-1]          # (the manager pads norm rows to an even number of values, zeros behind)
+    assert not mgr._k_norms[..., ng:].any()
+    kn = mgr._k_norms[:, :, :, :T, :ng].float().cpu().numpy()
     assert (np.abs(kn - g["k_norms"].astype(np.float32)) <= np.abs(kn) * 1e-3).all()
 
 
