@@ -338,7 +338,7 @@ def parity_check(mgr, w, qkv_step, t_before, outs):
     gqa = n_q // n_kv
     ns, win = mgr.n_sink, mgr.recent_window
     picks = sorted({(0, 0, 0), (L - 1, B - 1, n_kv - 1), (L // 2, B // 2, n_kv // 2)})
-    max_abs, rows_checked, rows_equal = 0.0, 0, 0
+    max_abs, max_excess, max_ref, rows_checked, rows_equal = 0.0, 0.0, 0.0, 0, 0
     for li, b, h in picks:
         qz = mgr.quantizers[li][h]
         meta = oracle_meta(qz._tables, qz._v_tables)
@@ -366,7 +366,11 @@ def parity_check(mgr, w, qkv_step, t_before, outs):
             wp, wb = np.exp(pl - m), np.exp(bl - m)
             ref = (wp[:, None] * po + wb[:, None] * bo) / (wp + wb)[:, None]
         got = outs[li][b, sl].float().cpu().numpy()
-        max_abs = max(max_abs, float(np.abs(got - ref).max()))
+        err = np.abs(got - ref)
+        max_abs = max(max_abs, float(err.max()))
+        max_ref = max(max_ref, float(np.abs(ref).max()))
+        # the step's outputs are fp16: half an fp16 ulp of the value itself is not the kernel's error
+        max_excess = max(max_excess, float((err - np.abs(ref) * 2.0 ** -11).max()))
         # the row appended by this step (unbuffered caches append at t_before; buffered ones flush token f)
         row = t_before if not mgr._buffered else (n_packed if t_before - ns - win >= 0 else None)
         if row is not None:
@@ -378,8 +382,10 @@ def parity_check(mgr, w, qkv_step, t_before, outs):
             if not enc["fragile"].any():
                 rows_checked += 1
                 rows_equal += int(np.array_equal(mgr._k_packed[li, b, h, row, :tb].cpu().numpy(), enc["packed"][0]))
-    return {"pairs": len(picks), "max_abs": max_abs, "tolerance": 2e-3, "appended_rows_checked": rows_checked,
-            "appended_rows_bit_equal": rows_equal, "ok": bool(max_abs <= 2e-3 and rows_equal == rows_checked)}
+    return {"pairs": len(picks), "max_abs": max_abs, "max_abs_beyond_fp16_output_rounding": max(0.0, max_excess),
+            "largest_output": max_ref, "tolerance": 2e-3, "appended_rows_checked": rows_checked,
+            "appended_rows_bit_equal": rows_equal,
+            "ok": bool(max_excess <= 2e-3 and rows_equal == rows_checked)}
 
 
 def workload_config(name, w, world):

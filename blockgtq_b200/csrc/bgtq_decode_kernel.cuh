@@ -139,7 +139,9 @@ __device__ __forceinline__ uint32_t udiv_fast(uint32_t a, uint32_t b) {
 
 // 16 codes of one token (bits [bit, bit + 16*VB) past word-aligned offset `row_al`) as one or two
 // 32-bit groups of 8 codes.
-template <int VB>
+// WORD_ROWS: the token's row starts on a 32-bit boundary, so the 16-code group (16 VB bits at a multiple of
+// 16 VB) never reaches into a third word.
+template <int VB, bool WORD_ROWS>
 __device__ __forceinline__ void load_v16(const uint8_t* sm, uint32_t row_al, uint32_t bit, uint32_t (&g)[2]) {
     const uint32_t wa = row_al + ((bit >> 5) << 2);
     const uint32_t w0 = ld32(sm, wa), w1 = ld32(sm, wa + 4);
@@ -148,7 +150,7 @@ __device__ __forceinline__ void load_v16(const uint8_t* sm, uint32_t row_al, uin
         g[0] = __funnelshift_r(w0, w1, sh);
         g[1] = 0;
     } else {
-        const uint32_t w2 = (sh + 16u * VB > 64u) ? ld32(sm, wa + 8) : 0u;
+        const uint32_t w2 = (!WORD_ROWS && sh + 16u * VB > 64u) ? ld32(sm, wa + 8) : 0u;
         const uint32_t lo = __funnelshift_r(w0, w1, sh), hi = __funnelshift_r(w1, w2, sh);
         if constexpr (VB == 3) {
             g[0] = lo & 0xFFFFFFu;
@@ -459,11 +461,13 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
     constexpr uint32_t off_kn = kSL.off_kn, off_v = kSL.off_v, off_vn = kSL.off_vn, stage_bytes = kSL.stage_bytes;
     constexpr uint32_t stage_off = BGTQ_JIT_STAGE_OFF;
     constexpr bool kAligned = true;
+    constexpr bool kWordRowsV = vp_st % 4u == 0u && (off_v % 4u) == 0u;
 #else
     const uint32_t kp_st = (uint32_t)P.kp_st, kn_st = (uint32_t)P.kn_st, vp_st = (uint32_t)P.vp_st, vn_st = (uint32_t)P.vn_st;
     const uint32_t off_kn = P.off_kn, off_v = P.off_v, off_vn = P.off_vn, stage_bytes = P.stage_bytes;
     const uint32_t stage_off = P.stage_off;
     constexpr bool kAligned = false;
+    constexpr bool kWordRowsV = false;
 #endif
 
     // Everything up to grid_dependency_wait() touches only static tables, so under a programmatic
@@ -712,15 +716,19 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                 // ---------------- online softmax (log2 domain) over the warp's tokens ----------------
                 // Scores stay unscaled until the exponent: 2^(S * scale - max) is one fused multiply-add per value.
                 float x0 = -BGTQ_INF, x1 = -BGTQ_INF;
-                bool okA[NU], okB[NU];
+                const bool partial = nt < kTileTok;     // only a run's last tile can hold rows past its end
+                if (partial) {
+#pragma unroll
+                    for (int u = 0; u < NU; ++u) {
+                        const bool okA = tok0 + 16 * u < nt, okB = tok0 + 16 * u + 8 < nt;
+                        S[u][0] = okA ? S[u][0] : -BGTQ_INF;
+                        S[u][1] = okA ? S[u][1] : -BGTQ_INF;
+                        S[u][2] = okB ? S[u][2] : -BGTQ_INF;
+                        S[u][3] = okB ? S[u][3] : -BGTQ_INF;
+                    }
+                }
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
-                    okA[u] = tok0 + 16 * u < nt;
-                    okB[u] = tok0 + 16 * u + 8 < nt;
-                    S[u][0] = okA[u] ? S[u][0] : -BGTQ_INF;
-                    S[u][1] = okA[u] ? S[u][1] : -BGTQ_INF;
-                    S[u][2] = okB[u] ? S[u][2] : -BGTQ_INF;
-                    S[u][3] = okB[u] ? S[u][3] : -BGTQ_INF;
                     x0 = fmaxf(x0, fmaxf(S[u][0], S[u][2]));
                     x1 = fmaxf(x1, fmaxf(S[u][1], S[u][3]));
                 }
@@ -746,8 +754,11 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                     ps0 += p0 + p2;
                     ps1 += p1 + p3;
                     const uint32_t rn = sb + vn_rowS + 16u * u * vn_st;
-                    const float nA = okA[u] ? f16_bits_to_float(ld16(sm, rn)) : 0.f;
-                    const float nB = okB[u] ? f16_bits_to_float(ld16(sm, rn + 8u * vn_st)) : 0.f;
+                    float nA = f16_bits_to_float(ld16(sm, rn)), nB = f16_bits_to_float(ld16(sm, rn + 8u * vn_st));
+                    if (partial) {
+                        nA = tok0 + 16 * u < nt ? nA : 0.f;
+                        nB = tok0 + 16 * u + 8 < nt ? nB : 0.f;
+                    }
                     pf[u][0] = movmatrix_trans(pack_half2(p0 * nA, p1 * nA));
                     pf[u][1] = movmatrix_trans(pack_half2(p2 * nB, p3 * nB));
                 }
@@ -773,10 +784,10 @@ extern "C" __global__ void __launch_bounds__(kDecThreads, 1) bgtq_decode_jit(con
                     uint32_t gA[2], gB[2], gC[2], gD[2];
                     const uint32_t rv = sb + v_off + 16u * u * vp_st;
                     const uint32_t base = rv & ~3u, bit = ((rv & 3u) << 3) + 16u * VB * r;
-                    load_v16<VB>(sm, base, bit, gA);
-                    load_v16<VB>(sm, base, bit + 8u * vp_st, gB);
-                    load_v16<VB>(sm, base, bit + 64u * vp_st, gC);
-                    load_v16<VB>(sm, base, bit + 72u * vp_st, gD);
+                    load_v16<VB, kWordRowsV>(sm, base, bit, gA);
+                    load_v16<VB, kWordRowsV>(sm, base, bit + 8u * vp_st, gB);
+                    load_v16<VB, kWordRowsV>(sm, base, bit + 64u * vp_st, gC);
+                    load_v16<VB, kWordRowsV>(sm, base, bit + 72u * vp_st, gD);
 #pragma unroll
                     for (int g = 0; g < (int)G; ++g) {
                         const uint32_t xab = (gA[g] & M) | ((gB[g] & M) << VB), yab = ((gA[g] >> VB) & M) | (gB[g] & (M << VB));
