@@ -64,7 +64,8 @@ REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 
 
 TRAFFIC_SOURCES = ["blockgtq_b200/csrc/bgtq_decode_kernel.cuh", "blockgtq_b200/csrc/bgtq_decode_plan.cu",
-                   "blockgtq_b200/csrc/bgtq_plan.h", "blockgtq_b200/csrc/bgtq_decode.cu"]
+                   "blockgtq_b200/csrc/bgtq_plan.h", "blockgtq_b200/csrc/bgtq_decode.cu",
+                   "blockgtq_b200/csrc/bgtq_decode_jit.cu", "blockgtq_b200/csrc/bgtq_common.cuh"]
 
 
 def sources_key(files):

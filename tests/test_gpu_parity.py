@@ -716,6 +716,42 @@ def test_decode_with_an_item_range_table(B, T, n_splits):
         lt.set_partition(None)
 
 
+def test_specialised_kernel_with_fixed_row_strides_and_its_fallback():
+    """A layer whose specialised kernel was compiled for fixed row strides: launches with exactly those strides and
+    16-byte aligned slices run it; launches with wider rows, or with slices that start off a 16-byte boundary, run
+    the general kernel.  All three give bit-identical partials to a layer specialised without fixed strides."""
+    from blockgtq_b200.layer import LayerTables, decode, encode, rotate_q
+    lt0, tabs = _layer("a3_1to8")
+    lt1 = LayerTables(lt0.k_tables, lt0.v_tables, DEV)
+    ng = lt1.max_ng + (lt1.max_ng & 1)
+    lt1.set_row_strides(lt1.max_tpb, ng, lt1.vpb, 1)
+    gen = torch.Generator().manual_seed(5150)
+    B, n_kv, gqa, T = 2, 2, 4, 1300
+    n_q = n_kv * gqa
+    k = torch.stack([torch.stack([synth_head(gen, T, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half().to(DEV)
+    q_rot = rotate_q(lt0, (torch.randn(B, n_q, HD, generator=gen) * 2).half().to(DEV))
+
+    rows = 1376                        # a multiple of 16: every (batch, head) slice starts on a 16-byte boundary
+
+    def cache(kb, first_row):          # rows [first_row, first_row + T + 8) of the allocation
+        kp = torch.zeros(B, n_kv, rows, kb, dtype=torch.uint8, device=DEV)[:, :, first_row:first_row + T + 8]
+        kn = torch.zeros(B, n_kv, rows, ng, dtype=torch.float16, device=DEV)[:, :, first_row:first_row + T + 8]
+        vp = torch.zeros(B, n_kv, rows, lt0.vpb, dtype=torch.uint8, device=DEV)[:, :, first_row:first_row + T + 8]
+        vn = torch.zeros(B, n_kv, rows, dtype=torch.float16, device=DEV)[:, :, first_row:first_row + T + 8]
+        encode(lt0, k, v, 0, kp, kn, vp, vn)
+        return kp, kn, vp, vn
+
+    ref = decode(lt0, q_rot, *cache(lt0.max_tpb, 0), 0, T, n_splits=5)
+    torch.cuda.synchronize()
+    live = ref[1] > -float("inf")
+    for kb, first_row in ((lt0.max_tpb, 0), (lt0.max_tpb + 3, 0), (lt0.max_tpb, 1)):
+        po, pl = decode(lt1, q_rot, *cache(kb, first_row), 0, T, n_splits=5)
+        torch.cuda.synchronize()
+        assert torch.equal(pl, ref[1]), (kb, first_row)
+        assert torch.equal(po[live], ref[0][live]), (kb, first_row)
+
+
 def _kernel_item_key(B, n_kv, T, n_splits, n_cta):
     """The four words the decode kernel derives for a launch and compares with a table's header."""
     units = (T + 31) // 32
