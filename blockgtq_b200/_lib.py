@@ -22,6 +22,7 @@ OK = 0
 ENC_K_NORMS_F16, ENC_K_MIXED, ENC_V_NIBBLE, ENC_SKIP_K, ENC_SKIP_V, ENC_FORCE_SIMT, ENC_PROGRAMMATIC = 1, 2, 4, 8, 16, 32, 64
 ENC_NO_TCGEN05 = 128
 DEC_K_MIXED, DEC_V_NIBBLE, DEC_PROGRAMMATIC, DEC_GENERIC = 1, 2, 4, 8
+PF_NO_TCGEN05 = 16
 COMBINE_PROGRAMMATIC = 1
 
 
@@ -51,6 +52,7 @@ _SIGNATURES = {
     "bgtq_desc_size": (C.c_int, []),
     "bgtq_error_string": (C.c_char_p, [C.c_int]),
     "bgtq_encode_tcgen05_status": (C.c_int, []),
+    "bgtq_prefill_tcgen05_status": (C.c_int, []),
     "bgtq_encode": (C.c_int, [_vp, _vp, _vp,
                               _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
                               _i32, _i32, _i32, _i32,

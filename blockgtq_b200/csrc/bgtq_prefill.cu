@@ -12,12 +12,13 @@
 //   O += P . Vhat    with vhat = fp16(centroid * norm)
 // on mma.sync m16n8k16.  The result is written as fp32 in V's rotated basis; the caller applies V's
 // rotation as one plain GEMM.
-#include "bgtq_common.cuh"
+#include "bgtq_prefill_common.cuh"
 
 namespace bgtq {
+// the tcgen05 form (bgtq_prefill_t5.cu); returns false when the shape does not fit it
+bool launch_prefill_t5(const PfParams& P, int n_batch, cudaStream_t stream, cudaError_t* err);
 namespace {
 
-constexpr int kPfTok = 64;        // cache tokens per tile
 constexpr int kPfRows = 256;      // query rows per CTA
 // m16 tiles per warp: every K/V fragment loaded from shared memory feeds this many MMAs.  2 halves the
 // ldmatrix traffic but needs 255 registers, i.e. 8 warps per SM: measured 17.7 ms against 14.8 ms with 1
@@ -25,19 +26,6 @@ constexpr int kPfRows = 256;      // query rows per CTA
 constexpr int kPfMt = 1;
 constexpr int kPfWarps = kPfRows / (16 * kPfMt);
 constexpr int kPfLd = 136;        // halfs per row of the dequantised tiles (conflict-free ldmatrix)
-constexpr int kPfMaxTasks = 32;
-
-struct PfParams {
-    const BgtqHeadDesc* desc;
-    const __half* q;
-    int64_t q_sb, q_sh, q_ss;
-    const uint8_t *kp, *kn, *vp, *vn;
-    int64_t kp_sb, kp_sh, kn_sb, kn_sh, vp_sb, vp_sh, vn_sb, vn_sh;
-    int32_t kp_st, kn_st, vp_st, vn_st;      // bytes between token rows
-    int32_t n_q, n_kv, gqa, s_q, n_tok, q_pos_offset, causal, flags;
-    float scale_log2;
-    float* out;
-};
 
 struct PfSmem {
     __half qs[kPfRows * kPfLd];                      // the CTA's query rows (packed-K basis)
@@ -79,80 +67,11 @@ __device__ __forceinline__ void pf_stage(uint8_t* dst, const uint8_t* src, int n
 }
 __device__ __forceinline__ void pf_stage_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-// Tables of one head: dequantisation tasks of 8 consecutive codes of one width.
+// Tables of one head: codebooks and the dequantisation tasks.
 __device__ void pf_setup(PfSmem& S, const PfParams& P, const BgtqHeadDesc& d) {
     const int tid = threadIdx.x;
     for (int i = tid; i < 528; i += kPfWarps * 32) S.cb[i] = i < 512 ? d.codebook[i] : d.v_lut[i - 512];
-    if (tid == 0) {
-        const bool mixed = P.flags & BGTQ_DEC_K_MIXED;
-        int nt = 0;
-        for (int s = 0; s < d.n_seg; ++s) {
-            const int bw = d.seg_bw[s], st = d.seg_start[s], len = d.seg_len[s];
-            const int sb = mixed ? (bw <= 4 ? 4 : 8) : (bw <= 4 ? bw : 8);
-            // nibble-layout numerics of the reference (fused_packed_attention.py:1449-1452), as in the decode
-            // plan: long low-width segments round centroid * norm to fp16
-            const int fold = (mixed && len >= 16 && s < 5) ? 1 : 0;
-            const int base = mixed ? (bw <= 4 ? st / 2 : d.nopack_start / 2 + (st - d.nopack_start)) : d.seg_pack_off[s];
-            for (int c = 0; c < len; c += 8) {
-                const int n = len - c < 8 ? len - c : 8;
-                S.ktask[nt] = make_uint2((uint32_t)(st + c) | (uint32_t)n << 8 | (uint32_t)sb << 12 | (uint32_t)s << 16 | (uint32_t)fold << 20,
-                                         (uint32_t)(base + (c * sb) / 8) | (uint32_t)d.seg_lut_off[s] << 16);
-                ++nt;
-            }
-        }
-        S.n_ktask = nt;
-        const int vsb = (P.flags & BGTQ_DEC_V_NIBBLE) ? 4 : d.v_bits;
-        for (int c = 0; c < kHD; c += 8)
-            S.vtask[c / 8] = make_uint2((uint32_t)c | 8u << 8 | (uint32_t)vsb << 12, (uint32_t)((c * vsb) / 8) | 512u << 16);
-        S.n_vtask = kHD / 8;
-    }
-}
-
-// Up to 8 codes of `sb` bits starting at byte p -> fp16 values (optionally times an fp16 norm) at dst.
-__device__ __forceinline__ void pf_dequant8(const uint8_t* p, int n, int sb, const uint16_t* cb, bool fold, __half nrm,
-                                            __half* dst) {
-    const int nbytes = (n * sb + 7) >> 3;
-    uint64_t w = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-        if (i < nbytes) w |= (uint64_t)p[i] << (8 * i);
-    const uint32_t m = (1u << sb) - 1u;
-#pragma unroll
-    for (int i = 0; i < 8; i += 2) {
-        if (i < n) {
-            __half a = __ushort_as_half(cb[(uint32_t)(w >> (i * sb)) & m]);
-            __half b = __ushort_as_half(cb[(uint32_t)(w >> ((i + 1) * sb)) & m]);
-            if (fold) {
-                a = __hmul(a, nrm);
-                b = __hmul(b, nrm);
-            }
-            *reinterpret_cast<__half2*>(dst + i) = __halves2half2(a, b);
-        }
-    }
-}
-
-// K variant: value = fp16 centroid * fp16 norm, exact in fp32 (22 significant bits), stored as the sum of
-// two fp16 numbers so that the tensor-core product with fp32 accumulation keeps the fp32 norm scaling of
-// the decode kernel without a per-segment accumulator.
-__device__ __forceinline__ void pf_dequant8_k(const uint8_t* p, int n, int sb, const uint16_t* cb, float nrm,
-                                              bool round16, __half* dst_hi, __half* dst_lo) {
-    const int nbytes = (n * sb + 7) >> 3;
-    uint64_t w = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-        if (i < nbytes) w |= (uint64_t)p[i] << (8 * i);
-    const uint32_t m = (1u << sb) - 1u;
-#pragma unroll
-    for (int i = 0; i < 8; i += 2) {
-        if (i < n) {
-            const float a = __half2float(__ushort_as_half(cb[(uint32_t)(w >> (i * sb)) & m])) * nrm;
-            const float b = __half2float(__ushort_as_half(cb[(uint32_t)(w >> ((i + 1) * sb)) & m])) * nrm;
-            const __half2 hi = __floats2half2_rn(a, b);
-            const float2 hf = __half22float2(hi);
-            *reinterpret_cast<__half2*>(dst_hi + i) = hi;
-            *reinterpret_cast<__half2*>(dst_lo + i) = round16 ? __floats2half2_rn(0.f, 0.f) : __floats2half2_rn(a - hf.x, b - hf.y);
-        }
-    }
+    if (tid == 0) pf_build_tasks(P, d, S.ktask, S.vtask, &S.n_ktask, &S.n_vtask);
 }
 
 __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_kernel(const PfParams P) {
@@ -422,6 +341,17 @@ extern "C" __attribute__((visibility("default"))) int bgtq_prefill_attention(
     P.q_pos_offset = q_pos_offset; P.causal = causal ? 1 : 0; P.flags = flags;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.out = out_rot;
+    P.status = nullptr;
+    if (!(flags & BGTQ_PF_NO_TCGEN05)) {     // the tensor-memory form, when the shape fits it
+        cudaError_t e = cudaSuccess;
+        if (launch_prefill_t5(P, n_batch, static_cast<cudaStream_t>(stream), &e)) {
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                return BGTQ_E_LAUNCH;
+            }
+            return BGTQ_OK;
+        }
+    }
     const int smem = (int)sizeof(PfSmem);
     if (cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
         cudaGetLastError();

@@ -1,0 +1,367 @@
+// Packed-cache prefill attention on the fifth-generation tensor cores (tcgen05) with accumulators in tensor
+// memory.  Same contract and arithmetic as prefill_kernel in bgtq_prefill.cu; this is the form for sm_100a.
+//
+// One CTA owns 128 query rows of one (batch, KV head) (row = position * gqa + head of the group): the M of
+// every product.  Cache tokens are walked in tiles of 64:
+//   1. the tile's packed rows (fetched with cp.async while the previous tile was multiplied) are
+//      dequantised ONCE into shared memory, directly in the tensor cores' operand layout: khat = fp16 centroid
+//      * fp16 norm held exactly as a high and a low fp16 tile [token][dim], vhat = fp16(centroid * norm)
+//      transposed [dim][token];
+//   2. one thread issues S = Q . Khat_hi^T + Q . Khat_lo^T: 16 tcgen05.mma (M 128, N 64, K 16), fp32
+//      accumulator in 64 tensor-memory columns;
+//   3. 128 threads, one per query row, read their row of S with tcgen05.ld, apply the causal limit, keep the
+//      running maximum and denominator, and write P (fp16) to shared memory as the next product's A operand.
+//      The accumulator O is only rescaled when a row's maximum grew by more than 2^8 since the value the row
+//      scales by was set (the final division undoes either scale): tcgen05.ld / st of the row;
+//   4. the same thread issues O += P . Vhat: 4 tcgen05.mma (M 128, N 128, K 16) into 128 more columns.
+// The phases of one CTA run one after the other; two CTAs share an SM (256 of its 512 tensor-memory columns
+// each), so one CTA's dequantisation and softmax overlap the other's products.
+// Every wait is bounded: a wait that gives up is recorded in a sticky status word, the CTA leaves its loop
+// together, releases its tensor memory and returns.
+#include "bgtq_prefill_common.cuh"
+#include "bgtq_tcgen05.cuh"
+
+namespace bgtq {
+
+__device__ int g_pf5_status = 0;
+
+namespace {
+
+constexpr int kT5Rows = 128;            // query rows per CTA = M
+constexpr int kT5Threads = 256;
+constexpr uint32_t kT5TmemCols = 256;   // S: columns [0, 64); O: columns [64, 192)
+constexpr uint32_t kColS = 0, kColO = 64;
+// instruction descriptors: D fp32, A and B fp16, both K-major, M = 128, N = 64 / 128
+constexpr uint32_t kIdescS = (1u << 4) | ((uint32_t)(kPfTok >> 3) << 17) | ((uint32_t)(kT5Rows >> 4) << 24);
+constexpr uint32_t kIdescO = (1u << 4) | ((uint32_t)(kHD >> 3) << 17) | ((uint32_t)(kT5Rows >> 4) << 24);
+constexpr float kLazyLog2 = 8.0f;       // a row rescales O only when its maximum grew by more than 2^8
+
+// Operand layout (no swizzle, K-major): 8 x 8 core matrices of 128 B (8 rows of 16 B); along K they follow each
+// other 128 B apart, 8-row groups are `sbo` apart: element (row, k) at
+//     (row / 8) * sbo + (k / 8) * 128 + (row % 8) * 16 + (k % 8) * 2.
+// 128-deep operands (Q, Khat): sbo = 2048; 64-deep ones (P, Vhat^T): sbo = 1024.
+struct T5Smem {
+    __align__(128) uint8_t q[kT5Rows * kHD * 2];
+    __align__(128) uint8_t kh[kPfTok * kHD * 2];
+    __align__(128) uint8_t kl[kPfTok * kHD * 2];
+    __align__(128) uint8_t vt[kHD * kPfTok * 2];
+    __align__(128) uint8_t p[kT5Rows * kPfTok * 2];
+    uint16_t cb[528];                               // 512 K entries + 16 V entries (fp16 bits)
+    uint2 ktask[kPfMaxTasks];
+    uint2 vtask[16];
+    int32_t n_ktask, n_vtask;
+    __align__(8) uint64_t bar_s, bar_o;
+    uint32_t tmem_base;
+};
+
+struct T5Raw {      // byte offsets of the tile's packed rows behind T5Smem (each region 16-byte aligned, + 4 bytes of phase)
+    uint32_t k, kn, v, vn, total;
+};
+
+__device__ __forceinline__ void t5_stage(uint8_t* dst, const uint8_t* src, int n_bytes, int tid) {
+    // dst[(src & 3) + i] = src[i]: whole 32-bit words asynchronously, the ragged tail byte by byte
+    const uint32_t ph = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 3u);
+    const uint8_t* s4 = src - ph;
+    const uint32_t d4 = smem_u32(dst);
+    const int n_words = (int)((ph + n_bytes) >> 2);
+    for (int i = tid; i < n_words; i += kT5Threads)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d4 + 4u * i), "l"(s4 + 4 * i) : "memory");
+    const int tail = (int)((ph + n_bytes) & 3u);
+    if (tid < tail) dst[4 * n_words + tid] = __ldg(s4 + 4 * n_words + tid);
+}
+
+// Up to 8 codes of `sb` bits starting at byte p, as one 64-bit word.
+__device__ __forceinline__ uint64_t t5_codes(const uint8_t* p, int n, int sb) {
+    const int nbytes = (n * sb + 7) >> 3;
+    uint64_t w = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (i < nbytes) w |= (uint64_t)p[i] << (8 * i);
+    return w;
+}
+
+__global__ void __launch_bounds__(kT5Threads, 2) prefill_t5_kernel(const PfParams P, const T5Raw R) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    T5Smem& S = *reinterpret_cast<T5Smem*>(smem_raw);
+    uint8_t* const raw = smem_raw + sizeof(T5Smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int bq = kT5Rows / P.gqa;                  // query positions per CTA
+    const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * bq;      // latest positions (most tiles under the causal mask) first
+    const BgtqHeadDesc& d = P.desc[h];
+
+    for (int i = tid; i < 528; i += kT5Threads) S.cb[i] = i < 512 ? d.codebook[i] : d.v_lut[i - 512];
+    if (tid == 0) {
+        pf_build_tasks(P, d, S.ktask, S.vtask, &S.n_ktask, &S.n_vtask);
+        mbar_init(&S.bar_s, 1);
+        mbar_init(&S.bar_o, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(&S.tmem_base, kT5TmemCols);
+    // the CTA's query rows -> the A operand (16-byte chunks of 8 dims); rows past the end are zero
+    for (int i = tid; i < kT5Rows * 16; i += kT5Threads) {
+        const int row = i >> 4, kc = i & 15;
+        const int qi_ = row / P.gqa, hq_ = h * P.gqa + row % P.gqa;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (q0 + qi_ < P.s_q) {
+            const __half* src = P.q + b * P.q_sb + hq_ * P.q_sh + (int64_t)(q0 + qi_) * P.q_ss + kc * 8;
+            if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) v = __ldg(reinterpret_cast<const uint4*>(src));
+            else {
+                const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src);
+                v = make_uint4(__ldg(s32), __ldg(s32 + 1), __ldg(s32 + 2), __ldg(s32 + 3));
+            }
+        }
+        *reinterpret_cast<uint4*>(S.q + (row >> 3) * 2048 + kc * 128 + (row & 7) * 16) = v;
+    }
+    // this thread's query row (threads 0..127)
+    const int row = tid & (kT5Rows - 1);
+    const int qi = row / P.gqa, hq = h * P.gqa + row % P.gqa;
+    const bool rok = q0 + qi < P.s_q;
+    const int lim = !rok ? 0 : (P.causal ? min(P.n_tok, P.q_pos_offset + q0 + qi + 1) : P.n_tok);
+    const int last_q = min(q0 + bq, P.s_q) - 1;
+    const int t_max = P.causal ? min(P.n_tok, P.q_pos_offset + last_q + 1) : P.n_tok;
+
+    const size_t bh_kp = (size_t)b * P.kp_sb + (size_t)h * P.kp_sh, bh_kn = (size_t)b * P.kn_sb + (size_t)h * P.kn_sh;
+    const size_t bh_vp = (size_t)b * P.vp_sb + (size_t)h * P.vp_sh, bh_vn = (size_t)b * P.vn_sb + (size_t)h * P.vn_sh;
+    const uint32_t q_u32 = smem_u32(S.q), kh_u32 = smem_u32(S.kh), kl_u32 = smem_u32(S.kl), vt_u32 = smem_u32(S.vt),
+                   p_u32 = smem_u32(S.p);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // Q: generic-proxy stores -> tensor-core reads
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = S.tmem_base;
+    const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's quarter of the lanes
+    const int n_ktask = S.n_ktask, n_vtask = S.n_vtask;
+
+    auto stage_tile = [&](int t0) {
+        const int nt = min(kPfTok, t_max - t0);
+        t5_stage(raw + R.k, P.kp + bh_kp + (size_t)t0 * P.kp_st, nt * P.kp_st, tid);
+        t5_stage(raw + R.kn, P.kn + bh_kn + (size_t)t0 * P.kn_st, nt * P.kn_st, tid);
+        t5_stage(raw + R.v, P.vp + bh_vp + (size_t)t0 * P.vp_st, nt * P.vp_st, tid);
+        t5_stage(raw + R.vn, P.vn + bh_vn + (size_t)t0 * P.vn_st, nt * P.vn_st, tid);
+    };
+    if (t_max > 0) stage_tile(0);
+
+    float m_used = -INFINITY, lsum = 0.f;    // the maximum this row scales by (log2 domain), its denominator
+    bool ok = true;
+    int it = 0;
+    for (int t0 = 0; t0 < t_max; t0 += kPfTok, ++it) {
+        const int nt = min(kPfTok, t_max - t0);
+        // ---- 1. the tile's packed rows have landed; dequantise them into the operand tiles ----
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();
+        const uint8_t* rk = raw + R.k + (reinterpret_cast<uintptr_t>(P.kp + bh_kp + (size_t)t0 * P.kp_st) & 3u);
+        const uint8_t* rn = raw + R.kn + (reinterpret_cast<uintptr_t>(P.kn + bh_kn + (size_t)t0 * P.kn_st) & 3u);
+        const uint8_t* rv = raw + R.v + (reinterpret_cast<uintptr_t>(P.vp + bh_vp + (size_t)t0 * P.vp_st) & 3u);
+        const uint8_t* rw = raw + R.vn + (reinterpret_cast<uintptr_t>(P.vn + bh_vn + (size_t)t0 * P.vn_st) & 3u);
+        // task index = (task << 6) | token: a warp works on one width at a time, its lanes on 32 tokens.  The
+        // four 8-token groups of a warp start their task at different pairs / dims, so that their stores (same
+        // banks, 2048 / 128 B apart) do not collide.
+        const int rot = lane >> 3;
+        for (int i = tid; i < kPfTok * n_ktask; i += kT5Threads) {
+            const int tok = i & (kPfTok - 1);
+            const uint2 tk = S.ktask[i >> 6];
+            const int first = tk.x & 0xFF, n = (tk.x >> 8) & 0xF, sb = (tk.x >> 12) & 0xF, sg = (tk.x >> 16) & 0xF;
+            const bool round16 = (tk.x >> 20) & 1u;
+            const uint32_t trow = (uint32_t)((tok >> 3) * 2048 + (tok & 7) * 16);
+            uint64_t w = 0;
+            float nrm = 0.f;
+            if (tok < nt) {
+                nrm = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + tok * P.kn_st + 2 * sg)));
+                w = t5_codes(rk + tok * P.kp_st + (tk.y & 0xFFFFu), n, sb);
+            }
+            const uint16_t* cb = S.cb + (tk.y >> 16);
+            const uint32_t m = (1u << sb) - 1u;
+#pragma unroll
+            for (int pi0 = 0; pi0 < 4; ++pi0) {
+                const int c = 2 * ((pi0 + rot) & 3);
+                if (c < n) {
+                    const int dd = first + c;
+                    const uint32_t off = trow + (uint32_t)((dd >> 3) * 128 + (dd & 7) * 2);
+                    uint32_t hi = 0u, lo = 0u;
+                    if (tok < nt) {
+                        const float a = __half2float(__ushort_as_half(cb[(uint32_t)(w >> (c * sb)) & m])) * nrm;
+                        const float bb = __half2float(__ushort_as_half(cb[(uint32_t)(w >> ((c + 1) * sb)) & m])) * nrm;
+                        const __half2 h2 = __floats2half2_rn(a, bb);
+                        const float2 hf = __half22float2(h2);
+                        hi = *reinterpret_cast<const uint32_t*>(&h2);
+                        if (!round16) {
+                            const __half2 l2 = __floats2half2_rn(a - hf.x, bb - hf.y);
+                            lo = *reinterpret_cast<const uint32_t*>(&l2);
+                        }
+                    }
+                    *reinterpret_cast<uint32_t*>(S.kh + off) = hi;
+                    *reinterpret_cast<uint32_t*>(S.kl + off) = lo;
+                }
+            }
+        }
+        for (int i = tid; i < kPfTok * n_vtask; i += kT5Threads) {
+            const int tok = i & (kPfTok - 1);
+            const uint2 tk = S.vtask[i >> 6];
+            const int first = tk.x & 0xFF, sb = (tk.x >> 12) & 0xF;
+            uint64_t w = 0;
+            __half nrm = __float2half_rn(0.f);
+            if (tok < nt) {
+                nrm = __ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + tok * P.vn_st));
+                w = t5_codes(rv + tok * P.vp_st + (tk.y & 0xFFFFu), 8, sb);
+            }
+            const uint32_t m = (1u << sb) - 1u;
+            uint8_t* const col = S.vt + (first >> 3) * 1024 + (tok >> 3) * 128 + (tok & 7) * 2;
+#pragma unroll
+            for (int i0 = 0; i0 < 8; ++i0) {
+                const int c = (i0 + 2 * rot) & 7;
+                __half v = __float2half_rn(0.f);
+                if (tok < nt) v = __hmul(__ushort_as_half(S.cb[512 + ((uint32_t)(w >> (c * sb)) & m)]), nrm);
+                *reinterpret_cast<__half*>(col + c * 16) = v;
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (t0 + kPfTok < t_max) stage_tile(t0 + kPfTok);      // the packed rows are consumed: fetch the next tile's
+        // ---- 2. S = Q . Khat^T ----
+        if (tid == 0) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < kHD / 16; ++ks)
+                umma_f16(tmem + kColS, umma_desc(q_u32 + 256u * ks), umma_desc(kl_u32 + 256u * ks), kIdescS, ks > 0);
+#pragma unroll
+            for (int ks = 0; ks < kHD / 16; ++ks)
+                umma_f16(tmem + kColS, umma_desc(q_u32 + 256u * ks), umma_desc(kh_u32 + 256u * ks), kIdescS, 1u);
+            umma_commit(&S.bar_s);
+        }
+        // ---- 3. softmax of the tile, one thread per query row ----
+        if (warp < 4) {
+            if (!mbar_wait_bounded(&S.bar_s, it & 1)) ok = false;
+            tc_fence_after_sync();
+            float sv[kPfTok];
+            {
+                float (&s0)[32] = *reinterpret_cast<float (*)[32]>(&sv[0]);
+                float (&s1)[32] = *reinterpret_cast<float (*)[32]>(&sv[32]);
+                tmem_ld32(tlane + kColS, s0);
+                tmem_ld32(tlane + kColS + 32u, s1);
+                tmem_ld_wait();
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < kPfTok; ++c) {
+                sv[c] = t0 + c < lim ? sv[c] : -INFINITY;
+                mx = fmaxf(mx, sv[c]);
+            }
+            const float m_new = fmaxf(m_used, mx * P.scale_log2);
+            float alpha = 1.f;
+            if (m_used == -INFINITY) m_used = m_new;                 // nothing accumulated for this row yet
+            else if (m_new > m_used + kLazyLog2) {
+                alpha = exp2f(m_used - m_new);
+                m_used = m_new;
+            }
+            if (__any_sync(0xffffffffu, alpha != 1.f)) {             // (the previous tile's product has completed)
+                lsum *= alpha;
+#pragma unroll 1
+                for (int ch = 0; ch < kHD / 32; ++ch) {
+                    float o[32];
+                    tmem_ld32(tlane + kColO + 32u * ch, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] *= alpha;
+                    tmem_st32(tlane + kColO + 32u * ch, o);
+                }
+                tmem_st_wait();
+            }
+            const float z = m_used == -INFINITY ? 0.f : m_used;
+            float ps = 0.f;
+            uint8_t* const prow = S.p + (row >> 3) * 1024 + (row & 7) * 16;
+#pragma unroll
+            for (int kc = 0; kc < kPfTok / 8; ++kc) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = exp2f(fmaf(sv[kc * 8 + 2 * e], P.scale_log2, -z));
+                    const float p1 = exp2f(fmaf(sv[kc * 8 + 2 * e + 1], P.scale_log2, -z));
+                    ps += p0 + p1;
+                    pk[e] = pack_half2(p0, p1);
+                }
+                *reinterpret_cast<uint4*>(prow + kc * 128) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            lsum += ps;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before_sync();
+        }
+        __syncthreads();
+        // ---- 4. O += P . Vhat ----
+        if (tid == 0) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < kPfTok / 16; ++ks)
+                umma_f16(tmem + kColO, umma_desc_sbo(p_u32 + 256u * ks, 1024u), umma_desc_sbo(vt_u32 + 256u * ks, 1024u), kIdescO,
+                         (it > 0 || ks > 0) ? 1u : 0u);
+            umma_commit(&S.bar_o);
+        }
+        // the product reads the tile buffers and P: everyone waits for it before the next tile overwrites them
+        if (!mbar_wait_bounded(&S.bar_o, it & 1)) ok = false;
+        tc_fence_after_sync();
+        ok = __syncthreads_and(ok ? 1 : 0) != 0;
+        if (!ok) break;
+    }
+
+    // ---- normalise and write (fp32, V's rotated basis) ----
+    if (warp < 4 && ok) {
+        const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+        float* dst = P.out + (((size_t)b * P.n_q + hq) * P.s_q + (q0 + qi)) * kHD;
+#pragma unroll 1
+        for (int ch = 0; ch < kHD / 32; ++ch) {
+            float o[32];
+            if (t_max > 0) {
+                tmem_ld32(tlane + kColO + 32u * ch, o);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[c] = 0.f;
+            }
+            if (rok) {
+#pragma unroll
+                for (int c = 0; c < 32; c += 4)
+                    *reinterpret_cast<float4*>(dst + 32 * ch + c) =
+                        make_float4(o[c] * inv, o[c + 1] * inv, o[c + 2] * inv, o[c + 3] * inv);
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kT5TmemCols);
+    if (!ok && tid == 0) atomicExch(&g_pf5_status, kStatusWaitTimeout);
+}
+
+}  // namespace
+
+// Launch the tcgen05 form if the shape fits it (group size divides 128; the tile's packed rows fit next to the
+// operand tiles); returns false otherwise, without touching *err.
+bool launch_prefill_t5(const PfParams& P, int n_batch, cudaStream_t stream, cudaError_t* err) {
+    if (kT5Rows % P.gqa) return false;
+    auto r16 = [](uint32_t x) { return (x + 15u) & ~15u; };
+    T5Raw R;
+    R.k = 0;
+    R.kn = R.k + r16((uint32_t)kPfTok * P.kp_st + 8u);
+    R.v = R.kn + r16((uint32_t)kPfTok * P.kn_st + 8u);
+    R.vn = R.v + r16((uint32_t)kPfTok * P.vp_st + 8u);
+    R.total = R.vn + r16((uint32_t)kPfTok * P.vn_st + 8u);
+    const size_t smem = sizeof(T5Smem) + R.total;
+    if (smem > 227u * 1024u) return false;
+    const int bq = kT5Rows / P.gqa;
+    const int64_t q_blocks = ((int64_t)P.s_q + bq - 1) / bq;
+    *err = cudaFuncSetAttribute(prefill_t5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (*err != cudaSuccess) return true;
+    prefill_t5_kernel<<<dim3((unsigned)q_blocks, P.n_kv, n_batch), kT5Threads, smem, stream>>>(P, R);
+    *err = cudaGetLastError();
+    return true;
+}
+
+}  // namespace bgtq
+
+extern "C" __attribute__((visibility("default"))) int bgtq_prefill_tcgen05_status(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, bgtq::g_pf5_status, sizeof(v)) != cudaSuccess) {
+        cudaGetLastError();
+        return BGTQ_E_LAUNCH;
+    }
+    return v;
+}

@@ -399,7 +399,13 @@ int bgtq_combine(const float* part_o, const float* part_lse, int32_t n_splits,
  * flags (BGTQ_DEC_K_MIXED, BGTQ_DEC_V_NIBBLE) are as for bgtq_decode.
  * out_rot: (n_batch, n_q, s_q, 128) fp32 contiguous, softmax-normalised and still in V's rotated basis:
  * multiply each KV head's rows by its R (one plain GEMM) to finish.  A query with no visible token
- * yields zeros.  n_q / n_kv <= 16. */
+ * yields zeros.  n_q / n_kv <= 16.
+ * Two kernels: the products run on tcgen05 with accumulators in tensor memory when n_q / n_kv divides 128
+ * (bgtq_prefill_t5.cu), else, or with BGTQ_PF_NO_TCGEN05 in flags, on mma.sync (bgtq_prefill.cu).  The tcgen05
+ * kernel bounds its waits; bgtq_prefill_tcgen05_status() returns 1 (sticky, per process) if one ever gave up,
+ * in which case that launch's output is invalid. */
+#define BGTQ_PF_NO_TCGEN05 16
+int bgtq_prefill_tcgen05_status(void);
 int bgtq_prefill_attention(const BgtqHeadDesc* desc, const void* q_rot, int64_t q_sb, int64_t q_sh, int64_t q_ss,
                 const uint8_t* k_packed, int64_t kp_sb, int64_t kp_sh, int64_t kp_st,
                 const void* k_norms, int64_t kn_sb, int64_t kn_sh, int64_t kn_st,
