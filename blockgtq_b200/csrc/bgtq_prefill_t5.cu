@@ -95,53 +95,66 @@ __device__ __forceinline__ float t5_exp2(float x) {      // hardware 2^x; ex2(-i
     return y;
 }
 
-// One K task of one token: up to 8 codes of SB stored bits at `src` -> khat = centroid * norm as a high and a low
-// fp16 tile.  hi = fp16(centroid * norm); lo = fp16(centroid * norm - hi) with one rounding (fused), i.e. the two
-// fp16 numbers the exact fp32 product splits into.  A token past the tile's end stores zeros.
+// One K task of TWO tokens (lane and lane + 32 of the tile: two independent chains per lane): up to 8 codes of SB
+// stored bits at src[e] -> khat = centroid * norm as a high and a low fp16 tile.  hi = fp16(centroid * norm);
+// lo = fp16(centroid * norm - hi) with one rounding (fused), i.e. the two fp16 numbers the exact fp32 product
+// splits into.  A token past the tile's end stores zeros.
 template <int SB>
-__device__ __forceinline__ void t5_k_task(uint8_t* kh, uint8_t* kl, const uint8_t* src, const uint32_t* pt, const uint16_t* cb,
-                                          __half2 n2, bool round16, int first, int n, uint32_t trow, uint32_t rot, bool live) {
-    uint32_t w0 = 0u, w1 = 0u;
-    if (live) t5_words(src, SB == 8, w0, w1);
+__device__ __forceinline__ void t5_k_task(uint8_t* kh, uint8_t* kl, const uint8_t* const (&src)[2], const uint32_t* pt,
+                                          const uint16_t* cb, const __half2 (&n2)[2], bool round16, int first, int n,
+                                          const uint32_t (&trow)[2], uint32_t rot, const bool (&live)[2]) {
+    uint32_t w0[2] = {0u, 0u}, w1[2] = {0u, 0u};
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+        if (live[e]) t5_words(src[e], SB == 8, w0[e], w1[e]);
 #pragma unroll
     for (int pi0 = 0; pi0 < 4; ++pi0) {
         const uint32_t c = 2u * ((pi0 + rot) & 3u);
         if ((int)c < n) {
             const int dd = first + (int)c;
-            const uint32_t off = trow + (uint32_t)((dd >> 3) * 128 + (dd & 7) * 2);
-            uint32_t cc;       // the two centroids as fp16x2
-            if constexpr (SB == 8) {
-                const uint32_t two = (c < 4u ? w0 : w1) >> ((c & 2u) * 8u);
-                cc = (uint32_t)cb[two & 0xFFu] | (uint32_t)cb[(two >> 8) & 0xFFu] << 16;
-            } else {
-                cc = pt[(w0 >> (c * SB)) & ((1u << (2 * SB)) - 1u)];
+            const uint32_t doff = (uint32_t)((dd >> 3) * 128 + (dd & 7) * 2);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                uint32_t cc;       // the two centroids as fp16x2
+                if constexpr (SB == 8) {
+                    const uint32_t two = (c < 4u ? w0[e] : w1[e]) >> ((c & 2u) * 8u);
+                    cc = (uint32_t)cb[two & 0xFFu] | (uint32_t)cb[(two >> 8) & 0xFFu] << 16;
+                } else {
+                    cc = pt[(w0[e] >> (c * SB)) & ((1u << (2 * SB)) - 1u)];
+                }
+                const __half2 c2 = *reinterpret_cast<const __half2*>(&cc);
+                const __half2 h2 = __hmul2(c2, n2[e]);
+                const __half2 l2 = __hfma2(c2, n2[e], __hneg2(h2));
+                uint32_t hi = *reinterpret_cast<const uint32_t*>(&h2), lo = *reinterpret_cast<const uint32_t*>(&l2);
+                if (round16) lo = 0u;
+                if (!live[e]) hi = lo = 0u;
+                *reinterpret_cast<uint32_t*>(kh + trow[e] + doff) = hi;
+                *reinterpret_cast<uint32_t*>(kl + trow[e] + doff) = lo;
             }
-            const __half2 c2 = *reinterpret_cast<const __half2*>(&cc);
-            const __half2 h2 = __hmul2(c2, n2);
-            const __half2 l2 = __hfma2(c2, n2, __hneg2(h2));
-            uint32_t hi = *reinterpret_cast<const uint32_t*>(&h2), lo = *reinterpret_cast<const uint32_t*>(&l2);
-            if (round16) lo = 0u;
-            if (!live) hi = lo = 0u;
-            *reinterpret_cast<uint32_t*>(kh + off) = hi;
-            *reinterpret_cast<uint32_t*>(kl + off) = lo;
         }
     }
 }
-// One V task of one token: 8 codes -> vhat = fp16(centroid * norm), stored down the token's column of the
-// transposed tile (`col` = the task's first dim, this token).
+// One V task of two tokens: 8 codes each -> vhat = fp16(centroid * norm), stored down each token's column of the
+// transposed tile (`col` = the task's first dim, token `lane`; token lane + 32 sits 4 k-chunks = 512 B further).
 template <int SB>
-__device__ __forceinline__ void t5_v_task(uint8_t* col, const uint8_t* src, const uint32_t* vpt, __half2 n2, uint32_t rot, bool live) {
-    uint32_t w0 = 0u, w1 = 0u;
-    if (live) t5_words(src, false, w0, w1);
+__device__ __forceinline__ void t5_v_task(uint8_t* col, const uint8_t* const (&src)[2], const uint32_t* vpt, const __half2 (&n2)[2],
+                                          uint32_t rot, const bool (&live)[2]) {
+    uint32_t w0[2] = {0u, 0u}, w1 = 0u;
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+        if (live[e]) t5_words(src[e], false, w0[e], w1);
 #pragma unroll
     for (int pi0 = 0; pi0 < 4; ++pi0) {
         const uint32_t c = 2u * ((pi0 + rot) & 3u);
-        const uint32_t cc = vpt[(w0 >> (c * SB)) & ((1u << (2 * SB)) - 1u)];
-        const __half2 v2 = __hmul2(*reinterpret_cast<const __half2*>(&cc), n2);
-        uint32_t v = *reinterpret_cast<const uint32_t*>(&v2);
-        if (!live) v = 0u;
-        *reinterpret_cast<uint16_t*>(col + c * 16u) = (uint16_t)v;
-        *reinterpret_cast<uint16_t*>(col + (c + 1u) * 16u) = (uint16_t)(v >> 16);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const uint32_t cc = vpt[(w0[e] >> (c * SB)) & ((1u << (2 * SB)) - 1u)];
+            const __half2 v2 = __hmul2(*reinterpret_cast<const __half2*>(&cc), n2[e]);
+            uint32_t v = *reinterpret_cast<const uint32_t*>(&v2);
+            if (!live[e]) v = 0u;
+            *reinterpret_cast<uint16_t*>(col + e * 512 + c * 16u) = (uint16_t)v;
+            *reinterpret_cast<uint16_t*>(col + e * 512 + (c + 1u) * 16u) = (uint16_t)(v >> 16);
+        }
     }
 }
 
@@ -241,22 +254,23 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
         const uint8_t* rn = raw + R.kn + (reinterpret_cast<uintptr_t>(P.kn + bh_kn + (size_t)t0 * P.kn_st) & 3u);
         const uint8_t* rv = raw + R.v + (reinterpret_cast<uintptr_t>(P.vp + bh_vp + (size_t)t0 * P.vp_st) & 3u);
         const uint8_t* rw = raw + R.vn + (reinterpret_cast<uintptr_t>(P.vn + bh_vn + (size_t)t0 * P.vn_st) & 3u);
-        // One warp per (task, 32-token half): the task's fields are uniform, the lanes are 32 tokens.  The four
-        // 8-token groups of a warp walk a task's four pairs in different order, so that their stores (same banks,
-        // 2048 / 128 B apart) do not collide.
+        // One warp per task: the task's fields are uniform; lane l dequantises tokens l and l + 32.  The four 8-token
+        // groups of a warp walk a task's four pairs in different order, so that their stores (same banks, 2048 /
+        // 128 B apart) do not collide.
         const uint32_t rot = (uint32_t)lane >> 3;
-        for (int u = warp; u < 2 * n_ktask; u += kT5Threads / 32) {
-            const uint2 tk = S.ktask[u >> 1];
-            const int tok = (u & 1) * 32 + lane;
+        const bool live[2] = {lane < nt, lane + 32 < nt};
+        for (int u = warp; u < n_ktask; u += kT5Threads / 32) {
+            const uint2 tk = S.ktask[u];
             const int first = tk.x & 0xFF, n = (tk.x >> 8) & 0xF, sg = (tk.x >> 16) & 0xF;
             const uint32_t sb = (tk.x >> 12) & 0xF;
             const bool round16 = (tk.x >> 20) & 1u;
-            const uint32_t trow = (uint32_t)((tok >> 3) * 2048 + (tok & 7) * 16);
-            const uint8_t* src = rk + tok * P.kp_st + (tk.y & 0xFFFFu);
-            const __half2 n2 = __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + tok * P.kn_st + 2 * sg)));
+            const uint32_t trow[2] = {(uint32_t)((lane >> 3) * 2048 + (lane & 7) * 16), (uint32_t)(((lane >> 3) + 4) * 2048 + (lane & 7) * 16)};
+            const uint8_t* const src[2] = {rk + lane * P.kp_st + (tk.y & 0xFFFFu), rk + (lane + 32) * P.kp_st + (tk.y & 0xFFFFu)};
+            const __half2 n2[2] = {
+                __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + lane * P.kn_st + 2 * sg))),
+                __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + (lane + 32) * P.kn_st + 2 * sg)))};
             const uint32_t* pt = S.pt + S.seg_pt[sg];
             const uint16_t* cb = S.cb + (tk.y >> 16);
-            const bool live = tok < nt;
             switch (sb) {
                 case 1: t5_k_task<1>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
                 case 2: t5_k_task<2>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
@@ -343,14 +357,13 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
         if (warp >= 4 * kT5Blocks) {     // ---- 3b. meanwhile the other warps dequantise V for the second product ----
             const uint32_t* vpt = S.pt + S.seg_pt[BGTQ_MAX_SEGMENTS];
             const uint32_t vsb = (S.vtask[0].x >> 12) & 0xF;
-            for (int u = warp - 4 * kT5Blocks; u < 2 * n_vtask; u += kT5Threads / 32 - 4 * kT5Blocks) {
-                const uint2 tk = S.vtask[u >> 1];
-                const int tok = (u & 1) * 32 + lane;
+            for (int u = warp - 4 * kT5Blocks; u < n_vtask; u += kT5Threads / 32 - 4 * kT5Blocks) {
+                const uint2 tk = S.vtask[u];
                 const int first = tk.x & 0xFF;
-                uint8_t* const col = S.vt + (first >> 3) * 1024 + (tok >> 3) * 128 + (tok & 7) * 2;
-                const uint8_t* src = rv + tok * P.vp_st + (tk.y & 0xFFFFu);
-                const __half2 n2 = __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + tok * P.vn_st)));
-                const bool live = tok < nt;
+                uint8_t* const col = S.vt + (first >> 3) * 1024 + (lane >> 3) * 128 + (lane & 7) * 2;
+                const uint8_t* const src[2] = {rv + lane * P.vp_st + (tk.y & 0xFFFFu), rv + (lane + 32) * P.vp_st + (tk.y & 0xFFFFu)};
+                const __half2 n2[2] = {__half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + lane * P.vn_st))),
+                                       __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + (lane + 32) * P.vn_st)))};
                 switch (vsb) {
                     case 1: t5_v_task<1>(col, src, vpt, n2, rot, live); break;
                     case 2: t5_v_task<2>(col, src, vpt, n2, rot, live); break;
