@@ -33,27 +33,28 @@ namespace {
 
 constexpr int kT5Rows = 128;            // M of every product
 constexpr int kT5Blocks = 2;            // 128-row blocks per CTA: both read the same dequantised tile
+constexpr int kT5Tok = 128;             // cache tokens per tile = N of the S product, K of the O product
 constexpr int kT5Threads = 512;
-constexpr uint32_t kT5TmemCols = 512;   // S of block m: columns [64 m, 64 m + 64); O of block m: [128 + 128 m, 256 + 128 m)
-constexpr uint32_t kColS = 0, kColO = 128;
+constexpr uint32_t kT5TmemCols = 512;   // S of block m: columns [128 m, 128 m + 128); O of block m: [256 + 128 m, 384 + 128 m)
+constexpr uint32_t kColS = 0, kColO = 256;
 // instruction descriptors: D fp32, A and B fp16, both K-major, M = 128, N = 64 / 128
-constexpr uint32_t kIdescS = (1u << 4) | ((uint32_t)(kPfTok >> 3) << 17) | ((uint32_t)(kT5Rows >> 4) << 24);
+constexpr uint32_t kIdescS = (1u << 4) | ((uint32_t)(kT5Tok >> 3) << 17) | ((uint32_t)(kT5Rows >> 4) << 24);
 constexpr uint32_t kIdescO = (1u << 4) | ((uint32_t)(kHD >> 3) << 17) | ((uint32_t)(kT5Rows >> 4) << 24);
 constexpr float kLazyLog2 = 8.0f;       // a row rescales O only when its maximum grew by more than 2^8
 constexpr int kPtWords = BGTQ_MAX_SEGMENTS * 256 + 256;
-static_assert(kT5Rows * kPfTok * 2 <= kPfTok * kHD * 2, "P fits the low-part tile it replaces");
+static_assert(kT5Rows * kT5Tok * 2 <= kT5Tok * kHD * 2, "P fits the K tile it replaces");
 
 // Operand layout (no swizzle, K-major): 8 x 8 core matrices of 128 B (8 rows of 16 B); along K they follow each
 // other 128 B apart, 8-row groups are `sbo` apart: element (row, k) at
 //     (row / 8) * sbo + (k / 8) * 128 + (row % 8) * 16 + (k % 8) * 2.
-// 128-deep operands (Q, Khat): sbo = 2048; 64-deep ones (P, Vhat^T): sbo = 1024.
+// All four operands are 128 deep (dims for Q and Khat, tokens for P and Vhat^T): sbo = 2048.
 struct T5Smem {
     __align__(128) uint8_t q[kT5Blocks][kT5Rows * kHD * 2];
-    __align__(128) uint8_t kh[kPfTok * kHD * 2];
-    __align__(128) uint8_t kl[kPfTok * kHD * 2];
-    __align__(128) uint8_t vt[kHD * kPfTok * 2];
-    // (P of block 0, 128 rows x 64 tokens, is written over `kl` once the S products have completed)
-    __align__(128) uint8_t p1[kT5Rows * kPfTok * 2];     // P of block 1
+    __align__(128) uint8_t kh[kT5Tok * kHD * 2];
+    __align__(128) uint8_t kl[kT5Tok * kHD * 2];
+    __align__(128) uint8_t vt[kHD * kT5Tok * 2];
+    // (P, 128 rows x 128 tokens per block, is written over the K tiles once the S products have completed:
+    // block 0 over `kl`, block 1 over `kh`)
     __align__(16) uint32_t pt[kPtWords];            // pair tables: (code, code) -> fp16x2, per K segment of <= 4 stored bits, then V
     uint16_t seg_pt[BGTQ_MAX_SEGMENTS + 1];         // first word of each segment's pair table; last entry: V's
     uint16_t cb[528];                               // 512 K entries + 16 V entries (fp16 bits)
@@ -220,19 +221,19 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
     const size_t bh_kp = (size_t)b * P.kp_sb + (size_t)h * P.kp_sh, bh_kn = (size_t)b * P.kn_sb + (size_t)h * P.kn_sh;
     const size_t bh_vp = (size_t)b * P.vp_sb + (size_t)h * P.vp_sh, bh_vn = (size_t)b * P.vn_sb + (size_t)h * P.vn_sh;
     const uint32_t q_u32 = smem_u32(S.q[0]), kh_u32 = smem_u32(S.kh), kl_u32 = smem_u32(S.kl), vt_u32 = smem_u32(S.vt),
-                   p_u32 = smem_u32(S.kl), p1_u32 = smem_u32(S.p1);
+                   p_u32 = smem_u32(S.kl), p1_u32 = smem_u32(S.kh);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // Q: generic-proxy stores -> tensor-core reads
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = S.tmem_base;
     const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's quarter of the lanes
-    const uint32_t colS = kColS + 64u * mb, colO = kColO + 128u * mb;      // this row's block
+    const uint32_t colS = kColS + 128u * mb, colO = kColO + 128u * mb;      // this row's block
     const int n_ktask = S.n_ktask, n_vtask = S.n_vtask;
 
     auto stage_tile = [&](int t0, int buf) {
         uint8_t* const raw = raw0 + (size_t)buf * R.total;
-        const int nt = min(kPfTok, t_max - t0);
+        const int nt = min(kT5Tok, t_max - t0);
         t5_stage(raw + R.k, P.kp + bh_kp + (size_t)t0 * P.kp_st, nt * P.kp_st, tid);
         t5_stage(raw + R.kn, P.kn + bh_kn + (size_t)t0 * P.kn_st, nt * P.kn_st, tid);
         t5_stage(raw + R.v, P.vp + bh_vp + (size_t)t0 * P.vp_st, nt * P.vp_st, tid);
@@ -243,12 +244,12 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
     float m_used = -INFINITY, lsum = 0.f;    // the maximum this row scales by (log2 domain), its denominator
     bool ok = true;
     int it = 0;
-    for (int t0 = 0; t0 < t_max; t0 += kPfTok, ++it) {
-        const int nt = min(kPfTok, t_max - t0);
+    for (int t0 = 0; t0 < t_max; t0 += kT5Tok, ++it) {
+        const int nt = min(kT5Tok, t_max - t0);
         // ---- 1. the tile's packed rows have landed; dequantise them into the operand tiles ----
         asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();
-        if (t0 + kPfTok < t_max) stage_tile(t0 + kPfTok, (it + 1) & 1);     // the next tile's rows, a whole tile ahead
+        if (t0 + kT5Tok < t_max) stage_tile(t0 + kT5Tok, (it + 1) & 1);     // the next tile's rows, a whole tile ahead
         const uint8_t* const raw = raw0 + (size_t)(it & 1) * R.total;
         const uint8_t* rk = raw + R.k + (reinterpret_cast<uintptr_t>(P.kp + bh_kp + (size_t)t0 * P.kp_st) & 3u);
         const uint8_t* rn = raw + R.kn + (reinterpret_cast<uintptr_t>(P.kn + bh_kn + (size_t)t0 * P.kn_st) & 3u);
@@ -258,17 +259,18 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
         // groups of a warp walk a task's four pairs in different order, so that their stores (same banks, 2048 /
         // 128 B apart) do not collide.
         const uint32_t rot = (uint32_t)lane >> 3;
-        const bool live[2] = {lane < nt, lane + 32 < nt};
-        for (int u = warp; u < n_ktask; u += kT5Threads / 32) {
-            const uint2 tk = S.ktask[u];
+        for (int u = warp; u < 2 * n_ktask; u += kT5Threads / 32) {      // (task, 64-token half)
+            const uint2 tk = S.ktask[u >> 1];
+            const int tb = (u & 1) * 64 + lane;                            // this lane's tokens: tb and tb + 32
+            const bool live[2] = {tb < nt, tb + 32 < nt};
             const int first = tk.x & 0xFF, n = (tk.x >> 8) & 0xF, sg = (tk.x >> 16) & 0xF;
             const uint32_t sb = (tk.x >> 12) & 0xF;
             const bool round16 = (tk.x >> 20) & 1u;
-            const uint32_t trow[2] = {(uint32_t)((lane >> 3) * 2048 + (lane & 7) * 16), (uint32_t)(((lane >> 3) + 4) * 2048 + (lane & 7) * 16)};
-            const uint8_t* const src[2] = {rk + lane * P.kp_st + (tk.y & 0xFFFFu), rk + (lane + 32) * P.kp_st + (tk.y & 0xFFFFu)};
+            const uint32_t trow[2] = {(uint32_t)((tb >> 3) * 2048 + (tb & 7) * 16), (uint32_t)(((tb >> 3) + 4) * 2048 + (tb & 7) * 16)};
+            const uint8_t* const src[2] = {rk + tb * P.kp_st + (tk.y & 0xFFFFu), rk + (tb + 32) * P.kp_st + (tk.y & 0xFFFFu)};
             const __half2 n2[2] = {
-                __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + lane * P.kn_st + 2 * sg))),
-                __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + (lane + 32) * P.kn_st + 2 * sg)))};
+                __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + tb * P.kn_st + 2 * sg))),
+                __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + (tb + 32) * P.kn_st + 2 * sg)))};
             const uint32_t* pt = S.pt + S.seg_pt[sg];
             const uint16_t* cb = S.cb + (tk.y >> 16);
             switch (sb) {
@@ -289,10 +291,10 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
                 const uint32_t qa = q_u32 + (uint32_t)m * (kT5Rows * kHD * 2);
 #pragma unroll
                 for (int ks = 0; ks < kHD / 16; ++ks)
-                    umma_f16(tmem + kColS + 64u * m, umma_desc(qa + 256u * ks), umma_desc(kl_u32 + 256u * ks), kIdescS, ks > 0);
+                    umma_f16(tmem + kColS + 128u * m, umma_desc(qa + 256u * ks), umma_desc(kl_u32 + 256u * ks), kIdescS, ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < kHD / 16; ++ks)
-                    umma_f16(tmem + kColS + 64u * m, umma_desc(qa + 256u * ks), umma_desc(kh_u32 + 256u * ks), kIdescS, 1u);
+                    umma_f16(tmem + kColS + 128u * m, umma_desc(qa + 256u * ks), umma_desc(kh_u32 + 256u * ks), kIdescS, 1u);
             }
             umma_commit(&S.bar_s);
         }
@@ -300,55 +302,73 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
         if (warp < 4 * kT5Blocks) {
             if (!mbar_wait_bounded(&S.bar_s, it & 1)) ok = false;
             tc_fence_after_sync();
-            float sv[kPfTok];
-            {
-                float (&s0)[32] = *reinterpret_cast<float (*)[32]>(&sv[0]);
-                float (&s1)[32] = *reinterpret_cast<float (*)[32]>(&sv[32]);
-                tmem_ld32(tlane + colS, s0);
-                tmem_ld32(tlane + colS + 32u, s1);
-                tmem_ld_wait();
-            }
-            float mx = -INFINITY;
-            if (!__all_sync(0xffffffffu, t0 + kPfTok <= lim)) {      // only tiles that reach a row's causal limit
-#pragma unroll
-                for (int c = 0; c < kPfTok; ++c) sv[c] = t0 + c < lim ? sv[c] : -INFINITY;
-            }
-#pragma unroll
-            for (int c = 0; c < kPfTok; ++c) mx = fmaxf(mx, sv[c]);
-            const float m_new = fmaxf(m_used, mx * P.scale_log2);
-            float alpha = 1.f;
-            if (m_used == -INFINITY) m_used = m_new;                 // nothing accumulated for this row yet
-            else if (m_new > m_used + kLazyLog2) {
-                alpha = t5_exp2(m_used - m_new);
-                m_used = m_new;
-            }
-            if (__any_sync(0xffffffffu, alpha != 1.f)) {             // (the previous tile's product has completed)
-                lsum *= alpha;
-#pragma unroll 1
-                for (int ch = 0; ch < kHD / 32; ++ch) {
-                    float o[32];
-                    tmem_ld32(tlane + colO + 32u * ch, o);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) o[c] *= alpha;
-                    tmem_st32(tlane + colO + 32u * ch, o);
-                }
-                tmem_st_wait();
-            }
-            const float z = m_used == -INFINITY ? 0.f : m_used;
+            const bool masked = !__all_sync(0xffffffffu, t0 + kT5Tok <= lim);     // only tiles that reach a row's causal limit
+            uint8_t* const prow = (mb ? S.kh : S.kl) + (r128 >> 3) * 2048 + (r128 & 7) * 16;
             float ps = 0.f;
-            uint8_t* const prow = (mb ? S.p1 : S.kl) + (r128 >> 3) * 1024 + (r128 & 7) * 16;
-#pragma unroll
-            for (int kc = 0; kc < kPfTok / 8; ++kc) {
-                uint32_t pk[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = t5_exp2(fmaf(sv[kc * 8 + 2 * e], P.scale_log2, -z));
-                    const float p1 = t5_exp2(fmaf(sv[kc * 8 + 2 * e + 1], P.scale_log2, -z));
-                    ps += p0 + p1;
-                    pk[e] = pack_half2(p0, p1);
+#pragma unroll 1
+            for (int hf = 0; hf < kT5Tok / 64; ++hf) {      // 64 columns of the row at a time
+                float sv[64];
+                {
+                    float (&s0)[32] = *reinterpret_cast<float (*)[32]>(&sv[0]);
+                    float (&s1)[32] = *reinterpret_cast<float (*)[32]>(&sv[32]);
+                    tmem_ld32(tlane + colS + 64u * hf, s0);
+                    tmem_ld32(tlane + colS + 64u * hf + 32u, s1);
+                    tmem_ld_wait();
                 }
-                *reinterpret_cast<uint4*>(prow + kc * 128) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                float mx = -INFINITY;
+                if (masked) {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) sv[c] = t0 + 64 * hf + c < lim ? sv[c] : -INFINITY;
+                }
+#pragma unroll
+                for (int c = 0; c < 64; ++c) mx = fmaxf(mx, sv[c]);
+                const float m_new = fmaxf(m_used, mx * P.scale_log2);
+                float alpha = 1.f;
+                if (m_used == -INFINITY) m_used = m_new;                 // nothing accumulated for this row yet
+                else if (m_new > m_used + kLazyLog2) {
+                    alpha = t5_exp2(m_used - m_new);
+                    m_used = m_new;
+                }
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {             // (the previous tile's product has completed)
+                    lsum *= alpha;
+                    ps *= alpha;                                          // (the first half of this tile, already in P)
+                    if (hf > 0) {                                         // rescale what this row put into P so far
+#pragma unroll 1
+                        for (int kc = 0; kc < 8 * hf; ++kc) {
+                            uint4 v = *reinterpret_cast<uint4*>(prow + kc * 128);
+                            const __half2 a2 = __float2half2_rn(alpha);
+                            __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) h[e] = __hmul2(h[e], a2);
+                            *reinterpret_cast<uint4*>(prow + kc * 128) = v;
+                        }
+                    }
+                    if (it > 0) {
+#pragma unroll 1
+                        for (int ch = 0; ch < kHD / 32; ++ch) {
+                            float o[32];
+                            tmem_ld32(tlane + colO + 32u * ch, o);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) o[c] *= alpha;
+                            tmem_st32(tlane + colO + 32u * ch, o);
+                        }
+                        tmem_st_wait();
+                    }
+                }
+                const float z = m_used == -INFINITY ? 0.f : m_used;
+#pragma unroll
+                for (int kc = 0; kc < 8; ++kc) {
+                    uint32_t pk[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float p0 = t5_exp2(fmaf(sv[kc * 8 + 2 * e], P.scale_log2, -z));
+                        const float p1 = t5_exp2(fmaf(sv[kc * 8 + 2 * e + 1], P.scale_log2, -z));
+                        ps += p0 + p1;
+                        pk[e] = pack_half2(p0, p1);
+                    }
+                    *reinterpret_cast<uint4*>(prow + (8 * hf + kc) * 128) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                }
             }
             lsum += ps;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -357,13 +377,15 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
         if (warp >= 4 * kT5Blocks) {     // ---- 3b. meanwhile the other warps dequantise V for the second product ----
             const uint32_t* vpt = S.pt + S.seg_pt[BGTQ_MAX_SEGMENTS];
             const uint32_t vsb = (S.vtask[0].x >> 12) & 0xF;
-            for (int u = warp - 4 * kT5Blocks; u < n_vtask; u += kT5Threads / 32 - 4 * kT5Blocks) {
-                const uint2 tk = S.vtask[u];
+            for (int u = warp - 4 * kT5Blocks; u < 2 * n_vtask; u += kT5Threads / 32 - 4 * kT5Blocks) {      // (task, 64-token half)
+                const uint2 tk = S.vtask[u >> 1];
                 const int first = tk.x & 0xFF;
-                uint8_t* const col = S.vt + (first >> 3) * 1024 + (lane >> 3) * 128 + (lane & 7) * 2;
-                const uint8_t* const src[2] = {rv + lane * P.vp_st + (tk.y & 0xFFFFu), rv + (lane + 32) * P.vp_st + (tk.y & 0xFFFFu)};
-                const __half2 n2[2] = {__half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + lane * P.vn_st))),
-                                       __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + (lane + 32) * P.vn_st)))};
+                const int tb = (u & 1) * 64 + lane;
+                const bool live[2] = {tb < nt, tb + 32 < nt};
+                uint8_t* const col = S.vt + (first >> 3) * 2048 + (tb >> 3) * 128 + (tb & 7) * 2;
+                const uint8_t* const src[2] = {rv + tb * P.vp_st + (tk.y & 0xFFFFu), rv + (tb + 32) * P.vp_st + (tk.y & 0xFFFFu)};
+                const __half2 n2[2] = {__half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + tb * P.vn_st))),
+                                       __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + (tb + 32) * P.vn_st)))};
                 switch (vsb) {
                     case 1: t5_v_task<1>(col, src, vpt, n2, rot, live); break;
                     case 2: t5_v_task<2>(col, src, vpt, n2, rot, live); break;
@@ -380,9 +402,9 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
 #pragma unroll
             for (int m = 0; m < kT5Blocks; ++m)
 #pragma unroll
-                for (int ks = 0; ks < kPfTok / 16; ++ks)
-                    umma_f16(tmem + kColO + 128u * m, umma_desc_sbo((m ? p1_u32 : p_u32) + 256u * ks, 1024u),
-                             umma_desc_sbo(vt_u32 + 256u * ks, 1024u), kIdescO, (it > 0 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < kT5Tok / 16; ++ks)
+                    umma_f16(tmem + kColO + 128u * m, umma_desc((m ? p1_u32 : p_u32) + 256u * ks), umma_desc(vt_u32 + 256u * ks), kIdescO,
+                             (it > 0 || ks > 0) ? 1u : 0u);
             umma_commit(&S.bar_o);
         }
         // the product reads the tile buffers and P: everyone waits for it before the next tile overwrites them
@@ -429,10 +451,10 @@ bool launch_prefill_t5(const PfParams& P, int n_batch, cudaStream_t stream, cuda
     auto r16 = [](uint32_t x) { return (x + 15u) & ~15u; };
     T5Raw R;
     R.k = 0;
-    R.kn = R.k + r16((uint32_t)kPfTok * P.kp_st + 8u);
-    R.v = R.kn + r16((uint32_t)kPfTok * P.kn_st + 8u);
-    R.vn = R.v + r16((uint32_t)kPfTok * P.vp_st + 8u);
-    R.total = R.vn + r16((uint32_t)kPfTok * P.vn_st + 8u);
+    R.kn = R.k + r16((uint32_t)kT5Tok * P.kp_st + 8u);
+    R.v = R.kn + r16((uint32_t)kT5Tok * P.kn_st + 8u);
+    R.vn = R.v + r16((uint32_t)kT5Tok * P.vp_st + 8u);
+    R.total = R.vn + r16((uint32_t)kT5Tok * P.vn_st + 8u);
     const size_t smem = sizeof(T5Smem) + 2u * (size_t)R.total;      // two staging buffers
     if (smem > 227u * 1024u) return false;
     const int bq = kT5Rows * kT5Blocks / P.gqa;
