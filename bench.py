@@ -831,7 +831,7 @@ def run_prefill(args, w, rank, world, dev):
                        "tokens": T, "k_avg_bits": w["k_bits"], "v_bits": w["v_bits"], "parallelism": f"batch x{world}",
                        "l2": "q/k/v inputs of a layer are 0.8 GB, larger than L2; no flush",
                        "attention_kernel_ms": ms_kernel},
-            "roofline": {"bound": "tensor", "kernel": "prefill_kernel", "achieved": tf, "peak": peak, "unit": "TFLOP/s",
+            "roofline": {"bound": "tensor", "kernel": "prefill_t5_kernel (tcgen05, tensor memory)", "achieved": tf, "peak": peak, "unit": "TFLOP/s",
                          "frac": tf / peak, "traffic": None,
                          "peak_source": "MEASURED_PEAKS.json (bf16 burst)" if peaks else "fallback",
                          "algorithmic_flops_per_launch": flops, "launch_ms": ms_kernel},

@@ -377,8 +377,11 @@ def prefill_attention(layer: LayerTables, q_rot, k_packed, k_norms, v_packed, v_
     """Attention of q_rot (B, n_q, S_q, 128) fp16 (packed-K basis) over the first ``n_tokens`` cache rows;
     query i has absolute position ``q_pos_offset + i`` and, when ``causal``, sees tokens up to it.
     ``v_rot`` (n_kv, 128, 128) fp32 = R finishes V's rotation with one batched fp32 GEMM.
-    Returns (B, n_q, S_q, 128) fp16."""
+    Returns (B, n_q, S_q, 128) fp16.  ``_lib.PF_NO_TCGEN05`` in ``flags`` (or the environment variable
+    ``BGTQ_PF_NO_TCGEN05``) keeps the products on mma.sync instead of tcgen05 / tensor memory."""
     _lib.require_cuda(q_rot, "q_rot")
+    if os.environ.get("BGTQ_PF_NO_TCGEN05"):
+        flags |= _lib.PF_NO_TCGEN05
     B, n_q, S_q, D = q_rot.shape
     if D != HD or q_rot.dtype != torch.float16 or q_rot.stride(3) != 1:
         raise ValueError("q_rot must be float16 (B, n_q, S_q, 128) with contiguous rows")

@@ -510,6 +510,8 @@ class BlockGTQKVManager:
             raise RuntimeError(f"kernel status {code}: {what.get(code, 'unknown')}")
         if self.device.type == "cuda" and _lib.lib().bgtq_encode_tcgen05_status() != 0:
             raise RuntimeError("the tcgen05 bulk encoder reported a timed-out wait: the rows of that launch are incomplete")
+        if self.device.type == "cuda" and _lib.lib().bgtq_prefill_tcgen05_status() != 0:
+            raise RuntimeError("the tcgen05 prefill attention reported a timed-out wait: the output of that launch is invalid")
 
     def bake_q_permutations(self, model, n_kv_heads: int, n_q_heads: int):
         """Bake each head's permutation + rotation into q_proj (packed_kv_manager.py:354-373)."""

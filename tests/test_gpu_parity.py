@@ -627,6 +627,39 @@ def test_prefill_attention_edge_shapes(gqa, S_q, offset):
         assert (out[:, :, i].float() - ref.float()).abs().max().item() <= ATOL
 
 
+@pytest.mark.parametrize("gqa,S_q,offset,mixed", [(4, 300, 700, False), (8, 40, 1500, False), (2, 513, 0, True), (3, 50, 200, False)])
+def test_prefill_tcgen05_and_mma_sync_kernels_agree(gqa, S_q, offset, mixed):
+    """The tensor-memory kernel (default when the group size divides 256) and the mma.sync kernel
+    (BGTQ_PF_NO_TCGEN05, and the only one for a group of 3) dequantise to the same fp16 operands and differ in
+    the order of the fp32 sums and in when the accumulator is rescaled only: fp16 outputs within 1e-3 plus one fp16
+    ulp of the value (outputs reach magnitude 4, where an ulp is 2e-3), several 128-token
+    tiles, a partial last tile, rows past the end of the last block, both cache layouts; and no bounded wait of
+    the tensor-memory kernel gave up."""
+    from blockgtq_b200 import _lib
+    from blockgtq_b200.layer import encode, prefill_attention, rotate_q_bulk
+    lt, tabs = _layer("a3_1to8")
+    gen = torch.Generator().manual_seed(1234 + S_q)
+    B, n_kv = 2, 2
+    n_q, T = n_kv * gqa, offset + S_q
+    k = torch.stack([torch.stack([synth_head(gen, T, 1)[1] for _ in range(n_kv)]) for _ in range(B)]).to(DEV)
+    q = (torch.randn(B, n_q, S_q, HD, generator=gen) * 2).half().to(DEV)
+    v = torch.randn(B, n_kv, T, HD, generator=gen).half().to(DEV)
+    kp = torch.zeros(B, n_kv, T + 1, lt.max_mixed_bytes if mixed else lt.max_tpb, dtype=torch.uint8, device=DEV)
+    kn = torch.zeros(B, n_kv, T + 1, lt.max_ng, dtype=torch.float16, device=DEV)
+    vp = torch.zeros(B, n_kv, T + 1, HD // 2 if mixed else lt.vpb, dtype=torch.uint8, device=DEV)
+    vn = torch.zeros(B, n_kv, T + 1, dtype=torch.float16, device=DEV)
+    encode(lt, k, v, 0, kp, kn, vp, vn, flags=(_lib.ENC_K_MIXED | _lib.ENC_V_NIBBLE) if mixed else 0)
+    q_rot = rotate_q_bulk(lt, q)
+    fl = (_lib.DEC_K_MIXED | _lib.DEC_V_NIBBLE) if mixed else 0
+    a = prefill_attention(lt, q_rot, kp, kn, vp, vn, T, q_pos_offset=offset, causal=True, v_rot=lt.v_rot, flags=fl)
+    b = prefill_attention(lt, q_rot, kp, kn, vp, vn, T, q_pos_offset=offset, causal=True, v_rot=lt.v_rot,
+                          flags=fl | _lib.PF_NO_TCGEN05)
+    torch.cuda.synchronize()
+    assert torch.isfinite(a.float()).all()
+    assert ((a.float() - b.float()).abs() <= 1e-3 + b.float().abs() * 2.0 ** -10).all()
+    assert _lib.lib().bgtq_prefill_tcgen05_status() == 0
+
+
 @pytest.mark.parametrize("gqa,T", [(4, 1000), (8, 300), (2, 64), (4, 2500)])
 def test_decode_result_does_not_depend_on_the_slot_count(gqa, T):
     """The number of partial slots only sets how finely the launch balances its work: one slot, a few, the
