@@ -100,18 +100,19 @@ __device__ __forceinline__ float t5_exp2(float x) {      // hardware 2^x; ex2(-i
 // stored bits at src[e] -> khat = centroid * norm as a high and a low fp16 tile.  hi = fp16(centroid * norm);
 // lo = fp16(centroid * norm - hi) with one rounding (fused), i.e. the two fp16 numbers the exact fp32 product
 // splits into.  A token past the tile's end stores zeros.
-template <int SB>
+// FAST: a full task (8 codes) of two live tokens whose low part is kept: no per-pair checks.
+template <int SB, bool FAST>
 __device__ __forceinline__ void t5_k_task(uint8_t* kh, uint8_t* kl, const uint8_t* const (&src)[2], const uint32_t* pt,
                                           const uint16_t* cb, const __half2 (&n2)[2], bool round16, int first, int n,
                                           const uint32_t (&trow)[2], uint32_t rot, const bool (&live)[2]) {
     uint32_t w0[2] = {0u, 0u}, w1[2] = {0u, 0u};
 #pragma unroll
     for (int e = 0; e < 2; ++e)
-        if (live[e]) t5_words(src[e], SB == 8, w0[e], w1[e]);
+        if (FAST || live[e]) t5_words(src[e], SB == 8, w0[e], w1[e]);
 #pragma unroll
     for (int pi0 = 0; pi0 < 4; ++pi0) {
         const uint32_t c = 2u * ((pi0 + rot) & 3u);
-        if ((int)c < n) {
+        if (FAST || (int)c < n) {
             const int dd = first + (int)c;
             const uint32_t doff = (uint32_t)((dd >> 3) * 128 + (dd & 7) * 2);
 #pragma unroll
@@ -127,8 +128,10 @@ __device__ __forceinline__ void t5_k_task(uint8_t* kh, uint8_t* kl, const uint8_
                 const __half2 h2 = __hmul2(c2, n2[e]);
                 const __half2 l2 = __hfma2(c2, n2[e], __hneg2(h2));
                 uint32_t hi = *reinterpret_cast<const uint32_t*>(&h2), lo = *reinterpret_cast<const uint32_t*>(&l2);
-                if (round16) lo = 0u;
-                if (!live[e]) hi = lo = 0u;
+                if (!FAST) {
+                    if (round16) lo = 0u;
+                    if (!live[e]) hi = lo = 0u;
+                }
                 *reinterpret_cast<uint32_t*>(kh + trow[e] + doff) = hi;
                 *reinterpret_cast<uint32_t*>(kl + trow[e] + doff) = lo;
             }
@@ -137,13 +140,13 @@ __device__ __forceinline__ void t5_k_task(uint8_t* kh, uint8_t* kl, const uint8_
 }
 // One V task of two tokens: 8 codes each -> vhat = fp16(centroid * norm), stored down each token's column of the
 // transposed tile (`col` = the task's first dim, token `lane`; token lane + 32 sits 4 k-chunks = 512 B further).
-template <int SB>
+template <int SB, bool FAST>
 __device__ __forceinline__ void t5_v_task(uint8_t* col, const uint8_t* const (&src)[2], const uint32_t* vpt, const __half2 (&n2)[2],
                                           uint32_t rot, const bool (&live)[2]) {
     uint32_t w0[2] = {0u, 0u}, w1 = 0u;
 #pragma unroll
     for (int e = 0; e < 2; ++e)
-        if (live[e]) t5_words(src[e], false, w0[e], w1);
+        if (FAST || live[e]) t5_words(src[e], false, w0[e], w1);
 #pragma unroll
     for (int pi0 = 0; pi0 < 4; ++pi0) {
         const uint32_t c = 2u * ((pi0 + rot) & 3u);
@@ -152,7 +155,7 @@ __device__ __forceinline__ void t5_v_task(uint8_t* col, const uint8_t* const (&s
             const uint32_t cc = vpt[(w0[e] >> (c * SB)) & ((1u << (2 * SB)) - 1u)];
             const __half2 v2 = __hmul2(*reinterpret_cast<const __half2*>(&cc), n2[e]);
             uint32_t v = *reinterpret_cast<const uint32_t*>(&v2);
-            if (!live[e]) v = 0u;
+            if (!FAST && !live[e]) v = 0u;
             *reinterpret_cast<uint16_t*>(col + e * 512 + c * 16u) = (uint16_t)v;
             *reinterpret_cast<uint16_t*>(col + e * 512 + (c + 1u) * 16u) = (uint16_t)(v >> 16);
         }
@@ -273,12 +276,22 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
                 __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rn + (tb + 32) * P.kn_st + 2 * sg)))};
             const uint32_t* pt = S.pt + S.seg_pt[sg];
             const uint16_t* cb = S.cb + (tk.y >> 16);
-            switch (sb) {
-                case 1: t5_k_task<1>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
-                case 2: t5_k_task<2>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
-                case 3: t5_k_task<3>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
-                case 4: t5_k_task<4>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
-                default: t5_k_task<8>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+            if (nt == kT5Tok && n == 8 && !round16) {       // (uniform over the warp)
+                switch (sb) {
+                    case 1: t5_k_task<1, true>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+                    case 2: t5_k_task<2, true>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+                    case 3: t5_k_task<3, true>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+                    case 4: t5_k_task<4, true>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+                    default: t5_k_task<8, true>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+                }
+            } else {
+                switch (sb) {
+                    case 1: t5_k_task<1, false>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+                    case 2: t5_k_task<2, false>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+                    case 3: t5_k_task<3, false>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+                    case 4: t5_k_task<4, false>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+                    default: t5_k_task<8, false>(S.kh, S.kl, src, pt, cb, n2, round16, first, n, trow, rot, live); break;
+                }
             }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -386,11 +399,20 @@ __global__ void __launch_bounds__(kT5Threads, 1) prefill_t5_kernel(const PfParam
                 const uint8_t* const src[2] = {rv + tb * P.vp_st + (tk.y & 0xFFFFu), rv + (tb + 32) * P.vp_st + (tk.y & 0xFFFFu)};
                 const __half2 n2[2] = {__half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + tb * P.vn_st))),
                                        __half2half2(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rw + (tb + 32) * P.vn_st)))};
-                switch (vsb) {
-                    case 1: t5_v_task<1>(col, src, vpt, n2, rot, live); break;
-                    case 2: t5_v_task<2>(col, src, vpt, n2, rot, live); break;
-                    case 3: t5_v_task<3>(col, src, vpt, n2, rot, live); break;
-                    default: t5_v_task<4>(col, src, vpt, n2, rot, live); break;
+                if (nt == kT5Tok) {
+                    switch (vsb) {
+                        case 1: t5_v_task<1, true>(col, src, vpt, n2, rot, live); break;
+                        case 2: t5_v_task<2, true>(col, src, vpt, n2, rot, live); break;
+                        case 3: t5_v_task<3, true>(col, src, vpt, n2, rot, live); break;
+                        default: t5_v_task<4, true>(col, src, vpt, n2, rot, live); break;
+                    }
+                } else {
+                    switch (vsb) {
+                        case 1: t5_v_task<1, false>(col, src, vpt, n2, rot, live); break;
+                        case 2: t5_v_task<2, false>(col, src, vpt, n2, rot, live); break;
+                        case 3: t5_v_task<3, false>(col, src, vpt, n2, rot, live); break;
+                        default: t5_v_task<4, false>(col, src, vpt, n2, rot, live); break;
+                    }
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
