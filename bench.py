@@ -220,6 +220,11 @@ class RefCpuSlice:
     queries over the de-quantised cache, with torch using all host cores."""
 
     def __init__(self, w, cores):
+        import contextlib
+        with contextlib.redirect_stdout(sys.stderr):      # (the reference prints its bit map: stdout is for the JSON line)
+            self._init(w, cores)
+
+    def _init(self, w, cores):
         from blockgtq.block_gtq_pipeline import BlockGTQPipeline
         from blockgtq.tq import TurboQuantMSE
         torch.set_num_threads(cores)
@@ -409,6 +414,8 @@ def run_triton(args, w, name):
         note = "the reference's packed path has no fp16 sink/window; timed without them" if w["n_sink"] else ""
     else:
         note = ""
+    real_stdout = sys.stdout
+    sys.stdout = sys.stderr          # the reference prints while it calibrates: stdout is for the JSON line
     try:
         from blockgtq.packed_kv_manager import BlockGTQKVManager as RefManager
         dev = torch.device("cuda", 0)
@@ -460,6 +467,8 @@ def run_triton(args, w, name):
     except Exception as e:                                         # noqa: BLE001
         msg = f"{type(e).__name__}: {e}".splitlines()[0][:300]
         line = {"impl": "triton", "unavailable": msg}
+    finally:
+        sys.stdout = real_stdout
     print(json.dumps(line), flush=True)
 
 
