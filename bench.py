@@ -1089,7 +1089,7 @@ def main():
                        "step_frac_of_8tbs": live_bytes / (ms_step * 1e-3) / 8e12,
                        "decode_kernel": "specialised per layer at run time (NVRTC)"
                                         if not os.environ.get("BGTQ_DEC_NO_JIT") else "general (ahead of time)"},
-            "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "bgtq_decode_jit" if not os.environ.get("BGTQ_DEC_NO_JIT") else "decode_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak,
                          "traffic": dram_traffic(args.workload),
                          "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback",

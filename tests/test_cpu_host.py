@@ -299,3 +299,32 @@ def test_decode_partition_tables():
     assert L.bgtq_decode_partition(0, 2, 1000, 4, 64, buf, 8) == -1
     assert L.bgtq_decode_partition(8, 2, 1000, 4, 64, None, 100) == -1
     assert L.bgtq_decode_plan_set_partition(None, None) == -1
+
+
+def test_decode_plan_option_setters_check_their_arguments():
+    """Row strides, early fetch and the item-range table are options of a decode plan: the setters take only what
+    the kernel can honour (strides inside the launch wrapper's limits, before the specialisation that bakes them
+    in; a non-negative row count; a 4-byte aligned table) and leave the plan usable."""
+    from test_cpu_decode_plan import Plan, _fill_desc
+    L = _lib.lib()
+    descs = (_lib.HeadDesc * 2)()
+    for h in range(2):
+        _fill_desc(descs[h], *tables_for("a3_1to8", h))
+    raw = _lib.DecodePlan()
+    assert L.bgtq_decode_plan(C.byref(descs), 2, 0, C.byref(raw)) == 0
+    view = lambda: Plan.from_buffer_copy(bytes(raw.opaque)[:C.sizeof(Plan)])
+    assert list(view().row_st) == [0, 0, 0, 0] and view().early_fresh == 0 and not view().partition
+    assert L.bgtq_decode_plan_set_row_strides(C.byref(raw), 57, 8, 48, 1) == 0
+    assert list(view().row_st) == [57, 16, 48, 2]                       # bytes, like the kernel's parameters
+    assert L.bgtq_decode_plan_set_row_strides(C.byref(raw), 161, 8, 48, 1) == -2
+    assert L.bgtq_decode_plan_set_row_strides(C.byref(raw), 57, 17, 48, 1) == -2
+    assert L.bgtq_decode_plan_set_row_strides(C.byref(raw), 0, 0, 0, 0) == 0 and list(view().row_st) == [0, 0, 0, 0]
+    assert L.bgtq_decode_plan_set_row_strides(None, 57, 8, 48, 1) == -1
+    assert L.bgtq_decode_plan_set_early_fetch(C.byref(raw), 1) == 0 and view().early_fresh == 1
+    assert L.bgtq_decode_plan_set_early_fetch(C.byref(raw), -1) == -1
+    assert L.bgtq_decode_plan_set_early_fetch(C.byref(raw), 0) == 0 and view().early_fresh == 0
+    assert L.bgtq_decode_plan_set_partition(C.byref(raw), C.c_void_p(0x1002)) == -3
+    assert L.bgtq_decode_plan_set_partition(C.byref(raw), C.c_void_p(0x1000)) == 0 and view().partition == 0x1000
+    assert L.bgtq_decode_plan_set_partition(C.byref(raw), None) == 0 and not view().partition
+    assert L.bgtq_decode_grid_size(8, 2, 64) == 148 and L.bgtq_decode_grid_size(1, 2, 4) == 8
+    assert L.bgtq_decode_grid_size(0, 2, 4) == -1
