@@ -897,7 +897,8 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(minutes=5))
 
     if w.get("mode") == "prefill":
         run_prefill(args, w, rank, world, dev)
@@ -1110,7 +1111,11 @@ def main():
     if world > 1 and not args.no_seqshard and args.workload == DEFAULT:
         del mgr, dqkv, hqkv, qs, ks, vs, step_graph
         torch.cuda.empty_cache()
-        seq = seqshard_leg(args, rank, world, dev)
+        # A failure that every rank meets the same way (a missing feature, memory) must not cost the main line
+        try:
+            seq = seqshard_leg(args, rank, world, dev)
+        except Exception as e:                                     # noqa: BLE001
+            seq = {"unavailable": f"{type(e).__name__}: {e}".splitlines()[0][:300]}
     if rank == 0:
         if seq is not None:
             line["seqshard"] = seq
