@@ -259,13 +259,17 @@ __global__ void __launch_bounds__(128) encode_kernel(const EncParams P) {
 // prefetches 32 entries of column p of the rotation before the inputs arrive and
 // produces a quarter of the dot product; the four quarters are added in order.
 // Work items: [0, n_rot) query rows (b, hq); then K rows (b, h); then V rows (b, h).
+// With rot_group == 4 (four or a multiple of four query heads per KV head) a query item is four consecutive
+// query heads of one KV head: quarter c of the CTA fetches row c, every thread applies its 32 rotation entries
+// to all four rows, and quarter c adds up and stores row c.  Same sums in the same order as one row per CTA,
+// a quarter of the rotation reads and of the CTAs.
 // ---------------------------------------------------------------------------
 struct PrepParams {
     EncParams e;            // n_tok == 1
     const __half* q;
     int64_t q_sb, q_sh;
     __half* q_rot;
-    int32_t n_q, do_rot;
+    int32_t n_q, do_rot, rot_group;
     const __half* rope_cos;   // optional (n_batch, 128) fp16 tables of the step's position: q and k arrive pre-RoPE
     const __half* rope_sin;
     int64_t rope_sb;
@@ -296,12 +300,13 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     __shared__ uint8_t codes[kHD];
     const EncParams& E = P.e;
     const int tid = threadIdx.x, p = tid & 127, c = tid >> 7, warp = tid >> 5, lane = tid & 31;
-    const int n_rot = P.do_rot ? E.n_batch * P.n_q : 0;
+    const int n_rot = P.do_rot ? E.n_batch * P.n_q / P.rot_group : 0;
     const int n_rows = E.n_batch * E.n_kv;
     int item = blockIdx.x, kind;   // 0 rotate, 1 K, 2 V, 3 / 4: copy the new K / V token into its fp16 buffer slot
     int b, h, hq = 0;
     if (item < n_rot) {
-        kind = 0; b = item / P.n_q; hq = item % P.n_q; h = hq / (P.n_q / E.n_kv);
+        const int per_b = P.n_q / P.rot_group;
+        kind = 0; b = item / per_b; hq = (item % per_b) * P.rot_group; h = hq / (P.n_q / E.n_kv);
     } else {
         item -= n_rot;
         kind = 1 + item / n_rows;
@@ -363,11 +368,30 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
         if (E.pos_dev && !enc_range_ok(E, t0, 1)) return;
     }
 
+    const __half* cs = P.rope_cos ? P.rope_cos + b * P.rope_sb : nullptr;
+    const __half* sn = P.rope_cos ? P.rope_sin + b * P.rope_sb : nullptr;
+    if (kind == 0 && P.rot_group == 4) {
+        __shared__ float xg[4][kHD];
+        __shared__ float pg[4][4][kHD];
+        xg[c][p] = rope_element(P.q + b * P.q_sb + (hq + c) * P.q_sh, perm_p, cs, sn);
+        __syncthreads();
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            a0 = fmaf(xg[0][32 * c + i], w[i], a0);
+            a1 = fmaf(xg[1][32 * c + i], w[i], a1);
+            a2 = fmaf(xg[2][32 * c + i], w[i], a2);
+            a3 = fmaf(xg[3][32 * c + i], w[i], a3);
+        }
+        pg[0][c][p] = a0; pg[1][c][p] = a1; pg[2][c][p] = a2; pg[3][c][p] = a3;
+        __syncthreads();
+        const float yq = (pg[c][0][p] + pg[c][1][p]) + (pg[c][2][p] + pg[c][3][p]);
+        P.q_rot[((size_t)b * P.n_q + hq + c) * kHD + p] = __float2half_rn(yq);
+        return;
+    }
     float x = 0.f;
     int g = 0;
     if (c == 0) {
-        const __half* cs = P.rope_cos ? P.rope_cos + b * P.rope_sb : nullptr;
-        const __half* sn = P.rope_cos ? P.rope_sin + b * P.rope_sb : nullptr;
         if (kind == 0) x = rope_element(P.q + b * P.q_sb + hq * P.q_sh, perm_p, cs, sn);
         else if (kind == 1) x = rope_element(k_src, perm_p, cs, sn);
         else x = __half2float(v_src[p]);
@@ -571,11 +595,12 @@ static int step_prepare_impl(
     E.k_codes = nullptr; E.v_codes = nullptr; E.flags = flags; E.capacity = t_capacity; E.status = status;
     P.q = static_cast<const __half*>(q); P.q_sb = q_sb; P.q_sh = q_sh; P.q_rot = static_cast<__half*>(q_rot);
     P.n_q = n_q; P.do_rot = do_rot ? 1 : 0;
+    P.rot_group = do_rot && (n_q / n_kv) % 4 == 0 ? 4 : 1;
     P.rope_cos = static_cast<const __half*>(rope_cos); P.rope_sin = static_cast<const __half*>(rope_sin);
     P.rope_sb = rope_sb;
     P.k_buf = static_cast<__half*>(k_buf); P.v_buf = static_cast<__half*>(v_buf);
     P.kb_sb = kb_sb; P.kb_sh = kb_sh; P.n_sink = n_sink; P.window = window;
-    const int64_t items = (int64_t)(do_rot ? n_batch * n_q : 0) + (k_buf ? 4LL : 2LL) * n_batch * n_kv;
+    const int64_t items = (int64_t)(do_rot ? n_batch * n_q / P.rot_group : 0) + (k_buf ? 4LL : 2LL) * n_batch * n_kv;
     if (items > 0x7fffffffLL) return BGTQ_E_TOOBIG;
     return launch_kernel(prep_kernel, dim3((unsigned)items), dim3(512), 0, static_cast<cudaStream_t>(stream),
                          (flags & BGTQ_ENC_PROGRAMMATIC) != 0, P) == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;

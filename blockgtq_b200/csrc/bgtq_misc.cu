@@ -42,8 +42,13 @@ struct PublishArgs {
 // ---------------------------------------------------------------------------
 // combine: merge split partials (and optionally the fp16-buffer partial).
 // One CTA per (query head, batch), one thread per output dim.
+// kPrefetch: every thread holds its 32 rotation entries in registers and requests them before the partials
+// exist, which takes their latency off a single wave of CTAs but leaves room for one CTA per SM.  With more
+// rows than SMs the CTAs queue up instead, so that variant reads the entries where it uses them and fits
+// three CTAs per SM, whose latency chains overlap.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const float* part_lse, int n_splits,
+template <bool kPrefetch>
+__global__ void __launch_bounds__(512, kPrefetch ? 1 : 3) combine_kernel(const float* part_o, const float* part_lse, int n_splits,
                                                        const float* v_rot, const float* buf_o, const float* buf_lse,
                                                        int n_q, int n_kv, __half* out, int64_t o_sb, int64_t o_sh,
                                                        float* out_f32, float* lse_out, int64_t rank_stride,
@@ -58,9 +63,10 @@ __global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const
     const int tid = threadIdx.x, d = tid & 127, c = tid >> 7;
     const int hq = blockIdx.x, b = blockIdx.y;
     const size_t row = (size_t)b * n_q + hq;
-    float w[32];
-    if (v_rot) {   // rows 32c .. 32c+31 of column d, requested before anything depends on them
-        const float* R = v_rot + (size_t)(hq / (n_q / n_kv)) * kHD * kHD + (size_t)(32 * c) * kHD + d;
+    // rows 32c .. 32c+31 of column d of the head's rotation
+    const float* R = v_rot ? v_rot + (size_t)(hq / (n_q / n_kv)) * kHD * kHD + (size_t)(32 * c) * kHD + d : nullptr;
+    float w[kPrefetch ? 32 : 1];
+    if (kPrefetch && v_rot) {   // requested before anything depends on them
 #pragma unroll
         for (int i = 0; i < 32; ++i) w[i] = __ldg(R + (size_t)i * kHD);
     }
@@ -126,8 +132,13 @@ __global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const
         if (c == 0) merged[d] = o;
         __syncthreads();
         float acc = 0.f;
+        if (kPrefetch) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc = fmaf(merged[32 * c + i], w[i], acc);
+            for (int i = 0; i < 32; ++i) acc = fmaf(merged[32 * c + i], w[i], acc);
+        } else {
+#pragma unroll 8
+            for (int i = 0; i < 32; ++i) acc = fmaf(merged[32 * c + i], __ldg(R + (size_t)i * kHD), acc);
+        }
         __syncthreads();
         pnum[c][d] = acc;
         __syncthreads();
@@ -174,16 +185,138 @@ __global__ void __launch_bounds__(512) combine_kernel(const float* part_o, const
 }
 
 // ---------------------------------------------------------------------------
-// fp16 buffer attention: plain softmax(q k^T) v over a few hundred tokens.
-// One CTA per (query head, batch): one thread per token scores it, then threads own half2 columns.
+// combine for many rows: one CTA per FOUR consecutive query heads of one KV head (and batch element).  Quarter c
+// of the CTA (128 threads, one per output dim) merges the live partial slots of row c; every thread then applies
+// its 32 rotation entries to all four merged rows, and quarter c adds up, merges the fp16-region partial and
+// stores row c.  A quarter of the CTAs and of the rotation reads of the one-row kernel, which is what bounds a
+// launch of a thousand rows.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) buffer_attn_kernel(const __half* q, int64_t q_sb, int64_t q_sh,
+__global__ void __launch_bounds__(512) combine4_kernel(const float* part_o, const float* part_lse, int n_splits,
+                                                        const float* v_rot, const float* buf_o, const float* buf_lse,
+                                                        int n_q, int n_kv, __half* out, int64_t o_sb, int64_t o_sh,
+                                                        float* out_f32, float* lse_out, const PublishArgs pub) {
+    __shared__ float merged[4][kHD];
+    __shared__ float pnum[4][4][kHD];
+    __shared__ float s_red[16];
+    __shared__ int s_cnt[16];
+    __shared__ int s_slot[4][128];
+    __shared__ float s_w[4][128];
+    const int tid = threadIdx.x, d = tid & 127, c = tid >> 7, warp = tid >> 5, lane = tid & 31;
+    const int hq0 = blockIdx.x * 4, hq = hq0 + c, b = blockIdx.y;
+    const size_t row = (size_t)b * n_q + hq;
+    const float* R = v_rot + (size_t)(hq0 / (n_q / n_kv)) * kHD * kHD + (size_t)(32 * c) * kHD + d;
+    float w[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) w[i] = __ldg(R + (size_t)i * kHD);
+    grid_launch_dependents();
+    grid_dependency_wait();       // the partials come from the preceding kernel
+    const float* lse = part_lse + row * n_splits;
+    const float* po = part_o + row * n_splits * kHD + d;
+    float mx = -INFINITY;
+    for (int s = d; s < n_splits; s += 128) mx = fmaxf(mx, lse[s]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(s_red[4 * c], s_red[4 * c + 1]), fmaxf(s_red[4 * c + 2], s_red[4 * c + 3]));
+    float num = 0.f, den = 0.f;
+    for (int base = 0; base < n_splits; base += 128) {     // the same trip count in every quarter
+        const int s = base + d;
+        const float l = s < n_splits ? lse[s] : -INFINITY;
+        const bool live = l > -INFINITY;
+        const unsigned bal = __ballot_sync(0xffffffffu, live);
+        __syncthreads();                                   // the previous chunk's lists have been consumed
+        if (lane == 0) s_cnt[warp] = __popc(bal);
+        __syncthreads();
+        int off = 0, total = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int n = s_cnt[4 * c + i];
+            off += 4 * c + i < warp ? n : 0;
+            total += n;
+        }
+        if (live) {
+            const int pos = off + __popc(bal & ((1u << lane) - 1u));
+            s_slot[c][pos] = s;
+            s_w[c][pos] = expf(l - mx);
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int i = 0; i < total; ++i) {                  // live slots of row c, in slot order
+            const float a = s_w[c][i];
+            den += a;
+            num = fmaf(a, po[(int64_t)s_slot[c][i] * kHD], num);
+        }
+    }
+    float o = den > 0.f ? num / den : 0.f;
+    float tot = den > 0.f ? mx + logf(den) : -INFINITY;
+    merged[c][d] = o;
+    __syncthreads();
+    {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            a0 = fmaf(merged[0][32 * c + i], w[i], a0);
+            a1 = fmaf(merged[1][32 * c + i], w[i], a1);
+            a2 = fmaf(merged[2][32 * c + i], w[i], a2);
+            a3 = fmaf(merged[3][32 * c + i], w[i], a3);
+        }
+        pnum[0][c][d] = a0; pnum[1][c][d] = a1; pnum[2][c][d] = a2; pnum[3][c][d] = a3;
+    }
+    __syncthreads();
+    o = (pnum[c][0][d] + pnum[c][1][d]) + (pnum[c][2][d] + pnum[c][3][d]);
+    if (buf_o) {
+        const float lb = buf_lse[row];
+        const float m2 = fmaxf(tot, lb);
+        if (m2 > -INFINITY) {
+            const float wp = tot == -INFINITY ? 0.f : expf(tot - m2);
+            const float wb = lb == -INFINITY ? 0.f : expf(lb - m2);
+            o = (wp * o + wb * buf_o[row * kHD + d]) / (wp + wb);
+            tot = m2 + logf(wp + wb);
+        }
+    }
+    if (out) out[b * o_sb + hq * o_sh + d] = __float2half_rn(o);
+    if (out_f32) out_f32[row * kHD + d] = o;
+    if (lse_out && d == 0) lse_out[row] = tot;
+    if (pub.n_ranks == 0) return;
+    {
+        const int seq = *pub.seq_dev;
+        for (int p = 0; p < pub.n_ranks; ++p) {
+            float* dst = pub.peer_bufs[p] + (seq & 1) * pub.parity_stride + pub.slot_off;
+            dst[row * kHD + d] = o;
+            if (d == 0) dst[pub.rows * kHD + row] = tot;
+        }
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int seq = *pub.seq_dev;
+        const int t = atomicAdd(pub.ticket, 1);
+        if (t == (int)(gridDim.x * gridDim.y) - 1) {    // every CTA's stores are fenced: raise the flag everywhere
+            *pub.ticket = 0;
+            __threadfence_system();
+            for (int p = 0; p < pub.n_ranks; ++p) {
+                volatile int32_t* f = pub.peer_flags[p] + pub.rank;
+                *f = seq + 1;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// fp16 buffer attention: plain softmax(q k^T) v over a few hundred tokens.
+// One CTA of 256 threads per (query head, batch): one thread per token scores it, then thread (column pair,
+// quarter) adds up every fourth token.  The kernel is a chain of memory latencies (a few hundred tokens per
+// row): the width and the unroll depths below set how many loads of the chain are in flight at once.
+// ---------------------------------------------------------------------------
+constexpr int kBufThreads = 256;
+__global__ void __launch_bounds__(kBufThreads) buffer_attn_kernel(const __half* q, int64_t q_sb, int64_t q_sh,
                                                            const __half* kb, const __half* vb, int64_t kb_sb,
                                                            int64_t kb_sh, int n_sink_tok, int n_ring_tok,
                                                            int sink_cap, int ring_first, int ring_size, int n_q,
                                                            int n_kv, float scale, float* buf_o, float* buf_lse,
                                                            const int32_t* pos_dev, int sc_cap) {
-    // shared memory: sc_cap logits / probabilities, 8 floats of scratch, the query (128 floats), 128 partial outputs
+    // shared memory: sc_cap logits / probabilities, 16 floats of scratch, the query (128 floats), 3 x 128 partial outputs
     extern __shared__ __align__(16) float sc[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (pos_dev) {      // region sizes from the device-side token count (one-token blocks, window = ring_size - 1)
@@ -205,22 +338,22 @@ __global__ void __launch_bounds__(128) buffer_attn_kernel(const __half* q, int64
         return sink_cap + (x >= ring_size ? x - ring_size : x);
     };
     if (n_tok <= 0) {
-        buf_o[row * kHD + tid] = 0.f;
+        if (tid < kHD) buf_o[row * kHD + tid] = 0.f;
         if (tid == 0) buf_lse[row] = -INFINITY;
         return;
     }
     float* red = sc + sc_cap;
-    float* qs = red + 8;
+    float* qs = red + 16;
     float* po = qs + kHD;
-    qs[tid] = __half2float(q[b * q_sb + hq * q_sh + tid]);
+    if (tid < kHD) qs[tid] = __half2float(q[b * q_sb + hq * q_sh + tid]);
     __syncthreads();
     const __half* kbase = kb + b * kb_sb + h * kb_sh;
     const __half* vbase = vb + b * kb_sb + h * kb_sh;
     // logits: one thread per token walks the 256-byte key row (16-byte loads, the query is broadcast from shared memory)
-    for (int i = tid; i < n_tok; i += 128) {
+    for (int i = tid; i < n_tok; i += kBufThreads) {
         const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)slot(i) * kHD);
         float s0 = 0.f, s1 = 0.f;
-#pragma unroll 4
+#pragma unroll 8
         for (int c = 0; c < kHD / 8; ++c) {
             const uint4 kv = __ldg(kr + c);
             const float4 qa = *reinterpret_cast<const float4*>(qs + 8 * c), qb = *reinterpret_cast<const float4*>(qs + 8 * c + 4);
@@ -237,43 +370,66 @@ __global__ void __launch_bounds__(128) buffer_attn_kernel(const __half* q, int64
     }
     __syncthreads();
     float mx = -INFINITY;
-    for (int i = tid; i < n_tok; i += 128) mx = fmaxf(mx, sc[i]);
+    for (int i = tid; i < n_tok; i += kBufThreads) mx = fmaxf(mx, sc[i]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) red[warp] = mx;
     __syncthreads();
-    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    mx = fmaxf(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), fmaxf(fmaxf(red[4], red[5]), fmaxf(red[6], red[7])));
     float sum = 0.f;
-    for (int i = tid; i < n_tok; i += 128) {
+    for (int i = tid; i < n_tok; i += kBufThreads) {
         const float pv = expf(sc[i] - mx);
         sc[i] = pv;
         sum += pv;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (lane == 0) red[4 + warp] = sum;
+    if (lane == 0) red[8 + warp] = sum;
     __syncthreads();
-    sum = red[4] + red[5] + red[6] + red[7];
-    // output: thread -> dims (2 d2, 2 d2 + 1) of every second token; the two halves of the CTA add up through shared memory
+    sum = ((red[8] + red[9]) + (red[10] + red[11])) + ((red[12] + red[13]) + (red[14] + red[15]));
+    // output: thread -> dims (2 d2, 2 d2 + 1) of every fourth token; the quarters add up through shared memory
+    // (sixteen threads per row with 16-byte loads and eight rows in flight measured slower than this)
     const int d2 = tid & 63, par = tid >> 6;
     float a0 = 0.f, a1 = 0.f;
-#pragma unroll 4
-    for (int i = par; i < n_tok; i += 2) {
+#pragma unroll 8
+    for (int i = par; i < n_tok; i += 4) {
         const float2 v = __half22float2(*reinterpret_cast<const __half2*>(vbase + (size_t)slot(i) * kHD + 2 * d2));
         const float pr = sc[i];
         a0 = fmaf(pr, v.x, a0);
         a1 = fmaf(pr, v.y, a1);
     }
-    if (par) {
-        po[2 * d2] = a0;
-        po[2 * d2 + 1] = a1;
-    }
+    if (par) *reinterpret_cast<float2*>(po + (par - 1) * kHD + 2 * d2) = make_float2(a0, a1);
     __syncthreads();
     if (!par) {
         const float inv = 1.0f / sum;
-        *reinterpret_cast<float2*>(buf_o + row * kHD + 2 * d2) = make_float2((a0 + po[2 * d2]) * inv, (a1 + po[2 * d2 + 1]) * inv);
+        const float2 p1 = *reinterpret_cast<const float2*>(po + 2 * d2), p2 = *reinterpret_cast<const float2*>(po + kHD + 2 * d2),
+                     p3 = *reinterpret_cast<const float2*>(po + 2 * kHD + 2 * d2);
+        *reinterpret_cast<float2*>(buf_o + row * kHD + 2 * d2) =
+            make_float2(((a0 + p1.x) + (p2.x + p3.x)) * inv, ((a1 + p1.y) + (p2.y + p3.y)) * inv);
     }
     if (tid == 0) buf_lse[row] = mx + logf(sum);
+}
+
+// The combine variant for a launch of n_q x n_batch rows: one row per CTA with its rotation entries in registers
+// while all CTAs fit the GPU at once; beyond that four rows of one KV head per CTA where the head grouping
+// allows it, else the lean one-row variant.
+cudaError_t launch_combine(int n_batch, cudaStream_t stream, bool programmatic, const float* part_o, const float* part_lse,
+                           int n_splits, const float* v_rot, const float* buf_o, const float* buf_lse, int n_q, int n_kv,
+                           __half* out, int64_t o_sb, int64_t o_sh, float* out_f32, float* lse_out, int64_t rank_stride,
+                           const PublishArgs& pub) {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        sms = n > 0 ? n : 148;
+    }
+    const bool single_wave = (int64_t)n_q * n_batch <= sms;
+    if (!single_wave && v_rot && rank_stride == 0 && (n_q / n_kv) % 4 == 0)
+        return launch_kernel(combine4_kernel, dim3(n_q / 4, n_batch), dim3(512), 0, stream, programmatic, part_o, part_lse,
+                             n_splits, v_rot, buf_o, buf_lse, n_q, n_kv, out, o_sb, o_sh, out_f32, lse_out, pub);
+    return launch_kernel(single_wave ? combine_kernel<true> : combine_kernel<false>, dim3(n_q, n_batch), dim3(512), 0,
+                         stream, programmatic, part_o, part_lse, n_splits, v_rot, buf_o, buf_lse, n_q, n_kv, out, o_sb,
+                         o_sh, out_f32, lse_out, rank_stride, pub);
 }
 
 const char* const kErrNames[] = {"ok", "bad argument", "unsupported shape or mode", "misaligned pointer",
@@ -308,7 +464,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_combine(const float* 
     if ((buf_o == nullptr) != (buf_lse == nullptr)) return BGTQ_E_BADARG;
     if (!out && !out_f32) return BGTQ_E_BADARG;
     if (n_batch > 65535) return BGTQ_E_TOOBIG;
-    return launch_kernel(combine_kernel, dim3(n_q, n_batch), dim3(512), 0, static_cast<cudaStream_t>(stream),
+    return launch_combine(n_batch, static_cast<cudaStream_t>(stream),
                          (flags & BGTQ_COMBINE_PROGRAMMATIC) != 0, part_o, part_lse, n_splits, v_rot, buf_o, buf_lse,
                          n_q, n_kv, static_cast<__half*>(out), o_sb, o_sh, out_f32, lse_out, (int64_t)0,
                          PublishArgs{}) == cudaSuccess
@@ -327,7 +483,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_combine_publish(
     PublishArgs pub;
     pub.peer_bufs = peer_bufs; pub.peer_flags = peer_flags; pub.slot_off = slot_off; pub.parity_stride = parity_stride;
     pub.rows = (int64_t)n_batch * n_q; pub.seq_dev = seq_dev; pub.ticket = ticket; pub.rank = rank; pub.n_ranks = n_ranks;
-    return launch_kernel(combine_kernel, dim3(n_q, n_batch), dim3(512), 0, static_cast<cudaStream_t>(stream),
+    return launch_combine(n_batch, static_cast<cudaStream_t>(stream),
                          (flags & BGTQ_COMBINE_PROGRAMMATIC) != 0, part_o, part_lse, n_splits, v_rot,
                          static_cast<const float*>(nullptr), static_cast<const float*>(nullptr), n_q, n_kv,
                          static_cast<__half*>(nullptr), (int64_t)0, (int64_t)0, static_cast<float*>(nullptr),
@@ -342,7 +498,7 @@ extern "C" __attribute__((visibility("default"))) int bgtq_combine_ranks(const f
     const int64_t rows = (int64_t)n_batch * n_q;
     if (rank_stride < rows * (kHD + 1)) return BGTQ_E_BADARG;
     if (n_batch > 65535) return BGTQ_E_TOOBIG;
-    return launch_kernel(combine_kernel, dim3(n_q, n_batch), dim3(512), 0, static_cast<cudaStream_t>(stream),
+    return launch_combine(n_batch, static_cast<cudaStream_t>(stream),
                          (flags & BGTQ_COMBINE_PROGRAMMATIC) != 0, gathered, gathered + rows * kHD, n_ranks,
                          static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
                          static_cast<const float*>(nullptr), n_q, 1, static_cast<__half*>(out), o_sb, o_sh,
@@ -383,8 +539,8 @@ extern "C" __attribute__((visibility("default"))) int bgtq_buffer_attn_pos(const
                              (kb_sb & 7) || (kb_sh & 7) || (reinterpret_cast<uintptr_t>(buf_o) & 7u)))
         return BGTQ_E_ALIGN;
     const int sc_cap = (n_buf_tokens + 3) & ~3;       // keeps the query block 16-byte aligned
-    const size_t smem = (size_t)(sc_cap + 8 + 2 * kHD) * sizeof(float);
-    buffer_attn_kernel<<<dim3(n_q, n_batch), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+    const size_t smem = (size_t)(sc_cap + 16 + 4 * kHD) * sizeof(float);
+    buffer_attn_kernel<<<dim3(n_q, n_batch), kBufThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(q), q_sb, q_sh, static_cast<const __half*>(k_buf),
         static_cast<const __half*>(v_buf), kb_sb, kb_sh, n_sink_tokens, n_ring_tokens, sink_cap, ring_first,
         ring_size > 0 ? ring_size : 1, n_q, n_kv, scale, buf_o, buf_lse, pos_dev, sc_cap);

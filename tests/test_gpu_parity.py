@@ -858,3 +858,91 @@ def test_step_prepare_with_fused_rope_is_bit_identical():
         outs.append((qr, kp, kn, vp, vn))
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("gqa", [4, 2])
+def test_large_batch_step_kernels_match_the_small_batch_ones(gqa):
+    """Beyond one wave of CTAs the combine switches to four rows of a KV head per CTA (or, where the head grouping
+    does not allow it, to a leaner one-row variant), and the query rotation always takes four heads per CTA when
+    it can.  A batch of 48 against six batches of 8: the rotation and the append in the same bits, the combine
+    within fp32 summation order."""
+    from blockgtq_b200.layer import combine, step_prepare
+    lt, tabs = _layer("a3_1to8")
+    gen = torch.Generator().manual_seed(99 + gqa)
+    B, n_kv, S, chunk = 48, 2, 6, 8
+    n_q = n_kv * gqa
+    q = (torch.randn(B, n_q, 1, HD, generator=gen) * 3).half().to(DEV)
+    k = (torch.randn(B, n_kv, 1, HD, generator=gen) * 3).half().to(DEV)
+    v = torch.randn(B, n_kv, 1, HD, generator=gen).half().to(DEV)
+
+    def cache(nb):
+        return (torch.zeros(nb, n_kv, 8, lt.max_tpb, dtype=torch.uint8, device=DEV),
+                torch.zeros(nb, n_kv, 8, lt.max_ng, dtype=torch.float16, device=DEV),
+                torch.zeros(nb, n_kv, 8, lt.vpb, dtype=torch.uint8, device=DEV),
+                torch.zeros(nb, n_kv, 8, dtype=torch.float16, device=DEV))
+
+    big = cache(B)
+    qr_big = step_prepare(lt, q, k, v, 5, *big)
+    for b0 in range(0, B, chunk):
+        sl = slice(b0, b0 + chunk)
+        small = cache(chunk)
+        qr = step_prepare(lt, q[sl], k[sl], v[sl], 5, *small)
+        torch.cuda.synchronize()
+        assert torch.equal(qr, qr_big[sl])
+        for a, b in zip(small, big):
+            assert torch.equal(a, b[sl])
+    assert qr_big.float().abs().max() > 1.0
+    po = torch.randn(B, n_q, S, HD, generator=gen).to(DEV)
+    pl = (torch.randn(B, n_q, S, generator=gen) * 3).to(DEV)
+    pl[3, 1, :] = float("-inf")
+    pl[:, :, 2] = float("-inf")
+    bo = torch.randn(B, n_q, HD, generator=gen).to(DEV)
+    bl = torch.randn(B, n_q, generator=gen).to(DEV)
+    out_big, o32_big, lse_big = combine(po, pl, n_kv, v_rot=lt.rot_v, buf_o=bo, buf_lse=bl, want_f32=True, want_lse=True)
+    torch.cuda.synchronize()
+    assert torch.equal(out_big, o32_big.half())
+    for b0 in range(0, B, chunk):
+        sl = slice(b0, b0 + chunk)
+        out, o32, lse = combine(po[sl].contiguous(), pl[sl].contiguous(), n_kv, v_rot=lt.rot_v, buf_o=bo[sl].contiguous(),
+                                buf_lse=bl[sl].contiguous(), want_f32=True, want_lse=True)
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(o32.cpu().numpy(), o32_big[sl].cpu().numpy(), atol=5e-6)
+        np.testing.assert_allclose(lse.cpu().numpy(), lse_big[sl].cpu().numpy(), atol=5e-6)
+    # and the big launch against the float64 oracle, un-rotation applied on the host
+    ro, rl = O.combine(po.cpu().numpy().transpose(2, 0, 1, 3).reshape(S, B * n_q, HD),
+                       pl.cpu().numpy().transpose(2, 0, 1).reshape(S, -1))
+    rot = lt.rot_v.double().cpu().numpy()
+    ro = ro.reshape(B, n_q, HD).astype(np.float64)
+    ro = np.stack([ro[:, h] @ rot[h // gqa] for h in range(n_q)], 1)
+    rl = rl.reshape(B, n_q).astype(np.float64)
+    blc, boc = bl.double().cpu().numpy(), bo.double().cpu().numpy()
+    m2 = np.maximum(rl, blc)
+    wp, wb = np.exp(rl - m2), np.exp(blc - m2)
+    want = (wp[..., None] * ro + wb[..., None] * boc) / (wp + wb)[..., None]
+    np.testing.assert_allclose(o32_big.cpu().numpy(), want, atol=2e-5)
+    np.testing.assert_allclose(lse_big.cpu().numpy(), m2 + np.log(wp + wb), atol=2e-5)
+
+
+@pytest.mark.parametrize("n_sink,n_ring", [(4, 128), (0, 1), (7, 600), (256, 0)])
+def test_buffer_attention_lengths_vs_oracle(n_sink, n_ring):
+    """fp16 buffer attention at lengths below, at and above one pass of the CTA's threads."""
+    from blockgtq_b200.layer import buffer_attn
+    gen = torch.Generator().manual_seed(1000 + n_sink + n_ring)
+    B, n_kv, gqa = 2, 2, 4
+    n_q = n_kv * gqa
+    ring = max(n_ring, 1) + 1
+    cap = n_sink + ring
+    kb = (torch.randn(B, n_kv, cap, HD, generator=gen) * 1.5).half()
+    vb = torch.randn(B, n_kv, cap, HD, generator=gen).half()
+    q = torch.randn(B, n_q, HD, generator=gen).half()
+    first = ring // 2
+    bo, bl = buffer_attn(q.to(DEV), kb.to(DEV), vb.to(DEV), n_kv, 0.0884, n_sink_tokens=n_sink,
+                         n_ring_tokens=n_ring, sink_cap=n_sink, ring_first=first, ring_size=ring)
+    torch.cuda.synchronize()
+    slots = list(range(n_sink)) + [n_sink + (first + i) % ring for i in range(n_ring)]
+    for b in range(B):
+        for hq in range(n_q):
+            h = hq // gqa
+            ro, rl = O.attend_fp16(q[b, hq:hq + 1].numpy(), kb[b, h, slots].numpy(), vb[b, h, slots].numpy(), 0.0884)
+            np.testing.assert_allclose(bo[b, hq].cpu().numpy(), ro[0], atol=3e-5)
+            np.testing.assert_allclose(bl[b, hq].cpu().numpy(), rl[0], atol=3e-5)
