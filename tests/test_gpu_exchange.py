@@ -37,12 +37,15 @@ def _merge(rk, B, n_q, out):
 
 
 @pytest.mark.parametrize("fused", [True, False])
-def test_two_rank_exchange_protocol_on_one_gpu(fused):
+@pytest.mark.parametrize("B,gqa", [(2, 2), (24, 4), (48, 2)])
+def test_two_rank_exchange_protocol_on_one_gpu(fused, B, gqa):
     """Three steps (both buffer parities, the step counter advancing on the device): every rank's merged
-    output must equal the merge of the two ranks' combine results computed directly."""
+    output must equal the merge of the two ranks' combine results computed directly.  The larger shapes have
+    more rows than SMs, where the combine (and its publishing tail) runs as the four-heads-per-CTA kernel
+    (gqa 4) or the lean one-row variant (gqa 2)."""
     from blockgtq_b200.layer import combine, combine_ranks
     L = _lib.lib()
-    B, n_kv, gqa, S, world = 2, 2, 2, 5, 2
+    n_kv, S, world = 2, 5, 2
     n_q, rows = n_kv * gqa, B * n_kv * gqa
     gen = torch.Generator(device=DEV).manual_seed(0)
     ranks = [_Rank(r, world, rows) for r in range(world)]
@@ -77,7 +80,12 @@ def test_two_rank_exchange_protocol_on_one_gpu(fused):
             _merge(rk, B, n_q, out)
             torch.cuda.synchronize()
             assert int(rk.status.item()) == 0 and int(rk.seq.item()) == step + 1
-            assert torch.equal(out, want), f"step {step} rank {rk.rank}"
+            # the exchange's merge adds the ranks with one fused multiply-add chain, the direct merge in two
+            # halves: fp32 results one ulp apart, which at these sizes flips an fp16 rounding now and then
+            diff = (out.float() - want.float()).abs()
+            assert bool((diff <= 2.0 ** -10 * want.float().abs().clamp(min=2.0 ** -14)).all()), f"step {step} rank {rk.rank}"
+            if B == 2:
+                assert torch.equal(out, want), f"step {step} rank {rk.rank}"
             assert int(rk.flags[0].item()) == step + 1 and int(rk.flags[1].item()) == step + 1
             assert rk.tickets.eq(0).all()
 
