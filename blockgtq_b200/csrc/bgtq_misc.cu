@@ -410,6 +410,169 @@ __global__ void __launch_bounds__(kBufThreads) buffer_attn_kernel(const __half* 
     if (tid == 0) buf_lse[row] = mx + logf(sum);
 }
 
+// ---------------------------------------------------------------------------
+// fp16 buffer attention for grouped query heads: one CTA per (KV head, batch) serves its NREP query heads.  The
+// live key and value rows are first copied into shared memory with cp.async (all of them in flight at once: the
+// kernel's time is otherwise a chain of dependent memory latencies, and a row crosses L2 -> SM once instead of
+// NREP times); the arithmetic then runs out of shared memory, the same sums in the same order as
+// buffer_attn_kernel, head by head.  Rows are kBufRowLd bytes apart so that a warp's 16-byte reads of 32
+// different rows do not collide.
+// Shared memory: key rows, value rows (cap_rows x kBufRowLd bytes each, indexed by buffer slot), then
+// NREP x (sc_cap logits / probabilities, 16 floats of scratch, the query, 3 x 128 partial outputs).
+// ---------------------------------------------------------------------------
+constexpr int kBufRowLd = 2 * kHD + 16;
+template <int NREP>
+__global__ void __launch_bounds__(kBufThreads) buffer_attn_group_kernel(const __half* q, int64_t q_sb, int64_t q_sh,
+                                                                         const __half* kb, const __half* vb, int64_t kb_sb,
+                                                                         int64_t kb_sh, int n_sink_tok, int n_ring_tok,
+                                                                         int sink_cap, int ring_first, int ring_size, int n_q,
+                                                                         float scale, float* buf_o, float* buf_lse,
+                                                                         const int32_t* pos_dev, int sc_cap, int cap_rows) {
+    extern __shared__ __align__(16) uint8_t smem_rows[];
+    uint8_t* const ks = smem_rows;
+    uint8_t* const vs = smem_rows + (size_t)cap_rows * kBufRowLd;
+    float* const sc = reinterpret_cast<float*>(smem_rows + 2 * (size_t)cap_rows * kBufRowLd);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (pos_dev) {      // region sizes from the device-side token count (one-token blocks, window = ring_size - 1)
+        const int avail = *pos_dev + 1;                // tokens including the one appended this step
+        const int a0 = max(0, avail - 1 - sink_cap), a1 = max(0, avail - sink_cap);
+        const int f0 = max(0, a0 - (ring_size - 1));
+        n_sink_tok = min(avail, sink_cap);
+        n_ring_tok = a1 - f0;
+        ring_first = f0 % ring_size;
+    }
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int hq0 = h * NREP;
+    const size_t row0 = (size_t)b * n_q + hq0;
+    const int n_tok = n_sink_tok + n_ring_tok;
+    auto slot = [&](int i) {
+        if (i < n_sink_tok) return i;
+        const int x = ring_first + (i - n_sink_tok);
+        return sink_cap + (x >= ring_size ? x - ring_size : x);
+    };
+    if (n_tok <= 0) {
+        for (int e = tid; e < NREP * kHD; e += kBufThreads) buf_o[row0 * kHD + e] = 0.f;
+        if (tid < NREP) buf_lse[row0 + tid] = -INFINITY;
+        return;
+    }
+    float* red = sc + NREP * sc_cap;        // [2][8 warps][NREP]
+    float* qs = red + 16 * NREP;            // [NREP][128]
+    float* po = qs + NREP * kHD;            // [3][NREP][128]
+    const __half* kbase = kb + b * kb_sb + h * kb_sh;
+    const __half* vbase = vb + b * kb_sb + h * kb_sh;
+    // live rows -> shared memory, 16 bytes per request: first all key rows (one group), then all value rows
+    for (int which = 0; which < 2; ++which) {
+        const __half* src = which ? vbase : kbase;
+        const uint32_t dst = smem_u32(which ? vs : ks);
+        for (int e = tid; e < n_tok * 16; e += kBufThreads) {
+            const int sl = slot(e >> 4), c = e & 15;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + sl * kBufRowLd + c * 16),
+                         "l"(src + (size_t)sl * kHD + c * 8)
+                         : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int e = tid; e < NREP * kHD; e += kBufThreads)
+        qs[e] = __half2float(q[b * q_sb + (hq0 + (e >> 7)) * q_sh + (e & 127)]);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");      // the key rows have landed
+    __syncthreads();
+    // logits: one thread per token, its key row used for every head
+    for (int i = tid; i < n_tok; i += kBufThreads) {
+        const uint4* kr = reinterpret_cast<const uint4*>(ks + (size_t)slot(i) * kBufRowLd);
+        float s0[NREP], s1[NREP];
+#pragma unroll
+        for (int g = 0; g < NREP; ++g) s0[g] = s1[g] = 0.f;
+#pragma unroll
+        for (int c = 0; c < kHD / 8; ++c) {
+            const uint4 kv = kr[c];
+            const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kv.x));
+            const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kv.y));
+            const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kv.z));
+            const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kv.w));
+#pragma unroll
+            for (int g = 0; g < NREP; ++g) {
+                const float4 qa = *reinterpret_cast<const float4*>(qs + g * kHD + 8 * c);
+                const float4 qb = *reinterpret_cast<const float4*>(qs + g * kHD + 8 * c + 4);
+                s0[g] = fmaf(qa.x, k0.x, s0[g]); s1[g] = fmaf(qa.y, k0.y, s1[g]);
+                s0[g] = fmaf(qa.z, k1.x, s0[g]); s1[g] = fmaf(qa.w, k1.y, s1[g]);
+                s0[g] = fmaf(qb.x, k2.x, s0[g]); s1[g] = fmaf(qb.y, k2.y, s1[g]);
+                s0[g] = fmaf(qb.z, k3.x, s0[g]); s1[g] = fmaf(qb.w, k3.y, s1[g]);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < NREP; ++g) sc[g * sc_cap + i] = (s0[g] + s1[g]) * scale;
+    }
+    __syncthreads();
+    float mx[NREP];
+#pragma unroll
+    for (int g = 0; g < NREP; ++g) {
+        float m = -INFINITY;
+        for (int i = tid; i < n_tok; i += kBufThreads) m = fmaxf(m, sc[g * sc_cap + i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) red[warp * NREP + g] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < NREP; ++g) {
+        float m = red[g];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w * NREP + g]);
+        mx[g] = m;
+        float sm = 0.f;
+        for (int i = tid; i < n_tok; i += kBufThreads) {
+            const float pv = expf(sc[g * sc_cap + i] - m);
+            sc[g * sc_cap + i] = pv;
+            sm += pv;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+        if (lane == 0) red[(8 + warp) * NREP + g] = sm;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");      // the value rows have landed
+    __syncthreads();
+    // the eight warps' sums of head g, added in a fixed order (read again after the value phase: red stays as it is)
+    auto head_sum = [&](int g) {
+        const float* r8 = red + 8 * NREP + g;
+        return ((r8[0] + r8[NREP]) + (r8[2 * NREP] + r8[3 * NREP])) + ((r8[4 * NREP] + r8[5 * NREP]) + (r8[6 * NREP] + r8[7 * NREP]));
+    };
+#pragma unroll
+    for (int g = 0; g < NREP; ++g)
+        if (tid == g) buf_lse[row0 + g] = mx[g] + logf(head_sum(g));
+    // output: thread -> dims (2 d2, 2 d2 + 1) of every fourth token for all heads
+    const int d2 = tid & 63, par = tid >> 6;
+    float a0[NREP], a1[NREP];
+#pragma unroll
+    for (int g = 0; g < NREP; ++g) a0[g] = a1[g] = 0.f;
+#pragma unroll 2
+    for (int i = par; i < n_tok; i += 4) {
+        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(vs + (size_t)slot(i) * kBufRowLd + 4 * d2));
+#pragma unroll
+        for (int g = 0; g < NREP; ++g) {
+            const float pr = sc[g * sc_cap + i];
+            a0[g] = fmaf(pr, v.x, a0[g]);
+            a1[g] = fmaf(pr, v.y, a1[g]);
+        }
+    }
+    if (par) {
+#pragma unroll
+        for (int g = 0; g < NREP; ++g)
+            *reinterpret_cast<float2*>(po + ((par - 1) * NREP + g) * kHD + 2 * d2) = make_float2(a0[g], a1[g]);
+    }
+    __syncthreads();
+    if (!par) {
+#pragma unroll
+        for (int g = 0; g < NREP; ++g) {
+            const float inv = 1.0f / head_sum(g);
+            const float2 p1 = *reinterpret_cast<const float2*>(po + g * kHD + 2 * d2),
+                         p2 = *reinterpret_cast<const float2*>(po + (NREP + g) * kHD + 2 * d2),
+                         p3 = *reinterpret_cast<const float2*>(po + (2 * NREP + g) * kHD + 2 * d2);
+            *reinterpret_cast<float2*>(buf_o + (row0 + g) * kHD + 2 * d2) =
+                make_float2(((a0[g] + p1.x) + (p2.x + p3.x)) * inv, ((a1[g] + p1.y) + (p2.y + p3.y)) * inv);
+        }
+    }
+}
+
 // The combine variant for a launch of n_q x n_batch rows: one row per CTA with its rotation entries in registers
 // while all CTAs fit the GPU at once; beyond that four rows of one KV head per CTA where the head grouping
 // allows it, else the lean one-row variant.
@@ -539,6 +702,23 @@ extern "C" __attribute__((visibility("default"))) int bgtq_buffer_attn_pos(const
                              (kb_sb & 7) || (kb_sh & 7) || (reinterpret_cast<uintptr_t>(buf_o) & 7u)))
         return BGTQ_E_ALIGN;
     const int sc_cap = (n_buf_tokens + 3) & ~3;       // keeps the query block 16-byte aligned
+    const int n_rep = n_q / n_kv;
+    const int cap_rows = sink_cap + (ring_size > 0 ? ring_size : 1);      // buffer slots a live token can sit in
+    const size_t smem_group = 2 * (size_t)cap_rows * kBufRowLd + (size_t)n_rep * (sc_cap + 16 + 4 * kHD) * sizeof(float);
+    if ((n_rep == 2 || n_rep == 4 || n_rep == 8) && n_buf_tokens > 0 && smem_group <= 200 * 1024) {
+        // grouped heads with the rows staged in shared memory: one CTA per KV head
+        auto kern = n_rep == 2 ? buffer_attn_group_kernel<2> : n_rep == 4 ? buffer_attn_group_kernel<4> : buffer_attn_group_kernel<8>;
+        // the attribute is per device: set it on every launch (cheap, and legal under stream capture)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+            cudaGetLastError();
+            return BGTQ_E_LAUNCH;
+        }
+        kern<<<dim3(n_kv, n_batch), kBufThreads, smem_group, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const __half*>(q), q_sb, q_sh, static_cast<const __half*>(k_buf), static_cast<const __half*>(v_buf),
+            kb_sb, kb_sh, n_sink_tokens, n_ring_tokens, sink_cap, ring_first, ring_size > 0 ? ring_size : 1, n_q, scale,
+            buf_o, buf_lse, pos_dev, sc_cap, cap_rows);
+        return cudaGetLastError() == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
+    }
     const size_t smem = (size_t)(sc_cap + 16 + 4 * kHD) * sizeof(float);
     buffer_attn_kernel<<<dim3(n_q, n_batch), kBufThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(q), q_sb, q_sh, static_cast<const __half*>(k_buf),

@@ -946,3 +946,10 @@ def test_buffer_attention_lengths_vs_oracle(n_sink, n_ring):
             ro, rl = O.attend_fp16(q[b, hq:hq + 1].numpy(), kb[b, h, slots].numpy(), vb[b, h, slots].numpy(), 0.0884)
             np.testing.assert_allclose(bo[b, hq].cpu().numpy(), ro[0], atol=3e-5)
             np.testing.assert_allclose(bl[b, hq].cpu().numpy(), rl[0], atol=3e-5)
+    # one CTA per KV head with the rows staged in shared memory (grouped heads, small buffers) and one CTA per
+    # query head reading global memory (every head its own KV head here) add the same terms in the same order
+    bo1, bl1 = buffer_attn(q.to(DEV), kb.repeat_interleave(gqa, 1).contiguous().to(DEV),
+                           vb.repeat_interleave(gqa, 1).contiguous().to(DEV), n_q, 0.0884, n_sink_tokens=n_sink,
+                           n_ring_tokens=n_ring, sink_cap=n_sink, ring_first=first, ring_size=ring)
+    torch.cuda.synchronize()
+    assert torch.equal(bo1, bo) and torch.equal(bl1, bl)
