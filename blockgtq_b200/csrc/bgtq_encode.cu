@@ -302,8 +302,9 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     const int tid = threadIdx.x, p = tid & 127, c = tid >> 7, warp = tid >> 5, lane = tid & 31;
     const int n_rot = P.do_rot ? E.n_batch * P.n_q / P.rot_group : 0;
     const int n_rows = E.n_batch * E.n_kv;
-    int item = blockIdx.x, kind;   // 0 rotate, 1 K, 2 V, 3 / 4: copy the new K / V token into its fp16 buffer slot
+    int item = blockIdx.x, kind;   // 0 rotate, 1 K, 2 V
     int b, h, hq = 0;
+    bool skip = false;
     if (item < n_rot) {
         const int per_b = P.n_q / P.rot_group;
         kind = 0; b = item / per_b; hq = (item % per_b) * P.rot_group; h = hq / (P.n_q / E.n_kv);
@@ -312,20 +313,8 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
         kind = 1 + item / n_rows;
         item %= n_rows;
         b = item / E.n_kv; h = item % E.n_kv;
-        if ((kind == 1 && (E.flags & BGTQ_ENC_SKIP_K)) || (kind == 2 && (E.flags & BGTQ_ENC_SKIP_V))) return;
-    }
-    if (kind >= 3) {            // three-region mode: the new token enters the sink (first n_sink tokens) or the ring
-        grid_launch_dependents();
-        grid_dependency_wait();
-        if (tid < kHD) {
-            const int pos = E.pos_dev ? *E.pos_dev : E.t0;
-            const int ring = P.window + 1;
-            const int slot = pos < P.n_sink ? pos : P.n_sink + (pos - P.n_sink) % ring;
-            const __half* src = kind == 3 ? E.k + b * E.k_sb + h * E.k_sh : E.v + b * E.v_sb + h * E.v_sh;
-            __half* dst = (kind == 3 ? P.k_buf : P.v_buf) + b * P.kb_sb + h * P.kb_sh + (int64_t)slot * kHD;
-            dst[tid] = src[tid];
-        }
-        return;
+        skip = (kind == 1 && (E.flags & BGTQ_ENC_SKIP_K)) || (kind == 2 && (E.flags & BGTQ_ENC_SKIP_V));
+        if (skip && P.k_buf == nullptr) return;
     }
     const BgtqHeadDesc& d = E.desc[h];
     // rotation column p, rows 32c .. 32c+31: independent loads issued before anything else
@@ -350,6 +339,18 @@ __global__ void __launch_bounds__(512) prep_kernel(const PrepParams P) {
     grid_launch_dependents();
     grid_dependency_wait();       // inputs and the slot position come from earlier work in the stream
     int t0 = E.pos_dev ? *E.pos_dev : E.t0;
+    if (P.k_buf != nullptr && kind != 0) {
+        // three-region mode: the step's token enters the sink (first n_sink tokens) or its ring slot, copied by
+        // the last quarter of the CTA; the token this CTA encodes below sits in another slot of the ring
+        if (c == 3) {
+            const int ring = P.window + 1;
+            const int slot = t0 < P.n_sink ? t0 : P.n_sink + (t0 - P.n_sink) % ring;
+            const __half* src = kind == 1 ? E.k + b * E.k_sb + h * E.k_sh : E.v + b * E.v_sb + h * E.v_sh;
+            __half* dst = (kind == 1 ? P.k_buf : P.v_buf) + b * P.kb_sb + h * P.kb_sh + (int64_t)slot * kHD;
+            dst[p] = src[p];
+        }
+        if (skip) return;
+    }
     if (E.pos_dev && kind != 0 && P.k_buf == nullptr && !enc_range_ok(E, t0, 1)) return;
     const __half* k_src = E.k + b * E.k_sb + h * E.k_sh;
     const __half* v_src = E.v + b * E.v_sb + h * E.v_sh;
@@ -600,7 +601,7 @@ static int step_prepare_impl(
     P.rope_sb = rope_sb;
     P.k_buf = static_cast<__half*>(k_buf); P.v_buf = static_cast<__half*>(v_buf);
     P.kb_sb = kb_sb; P.kb_sh = kb_sh; P.n_sink = n_sink; P.window = window;
-    const int64_t items = (int64_t)(do_rot ? n_batch * n_q / P.rot_group : 0) + (k_buf ? 4LL : 2LL) * n_batch * n_kv;
+    const int64_t items = (int64_t)(do_rot ? n_batch * n_q / P.rot_group : 0) + 2LL * n_batch * n_kv;
     if (items > 0x7fffffffLL) return BGTQ_E_TOOBIG;
     return launch_kernel(prep_kernel, dim3((unsigned)items), dim3(512), 0, static_cast<cudaStream_t>(stream),
                          (flags & BGTQ_ENC_PROGRAMMATIC) != 0, P) == cudaSuccess ? BGTQ_OK : BGTQ_E_LAUNCH;
