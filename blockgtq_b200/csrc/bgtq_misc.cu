@@ -115,10 +115,22 @@ __global__ void __launch_bounds__(512, kPrefetch ? 1 : 3) combine_kernel(const f
                 s_w[pos] = expf(l - mx);
             }
             __syncthreads();
-            for (int i = c; i < total; i += 4) {           // quarter c of the live slots
-                const float a = s_w[i];
-                den += a;
-                num = fmaf(a, po[(int64_t)s_slot[i] * so], num);
+            // quarter c of the live slots, four of its partials requested before the first is used (a slot past
+            // the end contributes exact zeros)
+            for (int i0 = c; i0 < total; i0 += 16) {
+                float a[4], x[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + 4 * u;
+                    const bool ok = i < total;
+                    a[u] = ok ? s_w[i] : 0.f;
+                    x[u] = ok ? po[(int64_t)s_slot[i] * so] : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    den += a[u];
+                    num = fmaf(a[u], x[u], num);
+                }
             }
         }
     }
